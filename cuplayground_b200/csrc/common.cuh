@@ -1,0 +1,86 @@
+// Internal helpers shared by the kernels and the host code of libaristos_moe.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/aristos_moe.h"
+
+namespace aristos {
+
+// Bits OR-ed into the device status word by kernels; mapped to aristos_status_t by the host.
+enum : int32_t { DEV_FAULT_TIMEOUT = 1, DEV_FAULT_BOUNDS = 2 };
+
+void set_last_error(const char* fmt, ...);
+aristos_status_t cuda_fail(cudaError_t e, const char* what);
+
+#define ARISTOS_CUDA_TRY(expr)                                                  \
+    do {                                                                        \
+        cudaError_t _e = (expr);                                                \
+        if (_e != cudaSuccess) return ::aristos::cuda_fail(_e, #expr);          \
+    } while (0)
+
+#define ARISTOS_TRY(expr)                                                       \
+    do {                                                                        \
+        aristos_status_t _s = (expr);                                           \
+        if (_s != ARISTOS_OK) return _s;                                        \
+    } while (0)
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline size_t dtype_bytes(int dtype) {
+    switch (dtype) {
+        case ARISTOS_DTYPE_F32: case ARISTOS_DTYPE_TF32: return 4;
+        case ARISTOS_DTYPE_BF16: case ARISTOS_DTYPE_F16: return 2;
+        case ARISTOS_DTYPE_FP8_E4M3: return 1;
+        default: return 0;
+    }
+}
+inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// Number of SMs of the current device (cached per device).
+int device_sm_count();
+
+// Per-thread launch counter, read by the layer to report how many kernels it launched.
+int64_t& launch_counter();
+#define ARISTOS_COUNT_LAUNCH() (++::aristos::launch_counter())
+
+#ifdef __CUDACC__
+// ---- device-side loads of the two storage types as fp32 ---------------------------------------------------------
+// 8 consecutive elements starting at p (16 B for bf16, 32 B for fp32).
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&v)[8]) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        v[2 * i] = __uint_as_float(w[i] << 16);
+        v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+    }
+}
+__device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p);
+    const float4 b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+    v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&v)[8]) {
+    uint4 u;
+    __nv_bfloat162 t;
+    t = __floats2bfloat162_rn(v[0], v[1]); u.x = *reinterpret_cast<uint32_t*>(&t);
+    t = __floats2bfloat162_rn(v[2], v[3]); u.y = *reinterpret_cast<uint32_t*>(&t);
+    t = __floats2bfloat162_rn(v[4], v[5]); u.z = *reinterpret_cast<uint32_t*>(&t);
+    t = __floats2bfloat162_rn(v[6], v[7]); u.w = *reinterpret_cast<uint32_t*>(&t);
+    *reinterpret_cast<uint4*>(p) = u;
+}
+__device__ __forceinline__ void store8(float* p, const float (&v)[8]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+
+__device__ __forceinline__ float act_relu(float v) { return v > 0.0f ? v : 0.0f; }
+__device__ __forceinline__ float act_gelu(float v) { return 0.5f * v * (1.0f + erff(v * 0.70710678118654752440f)); }
+__device__ __forceinline__ float act_silu(float v) { return v / (1.0f + __expf(-v)); }
+#endif
+
+}  // namespace aristos

@@ -1,0 +1,26 @@
+// Expert-parallel exchange over NCCL: the library is loaded at run time (dlopen of libnccl.so.2, so a process that
+// already holds NCCL - e.g. through torch - shares that copy) and only when world > 1.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include "../../include/aristos_moe.h"
+
+namespace aristos {
+
+struct EpComm;  // opaque
+
+aristos_status_t ep_unique_id(void* out_128_bytes);
+aristos_status_t ep_comm_create(const void* unique_id_128, int rank, int world, EpComm** out);
+void ep_comm_destroy(EpComm* c);
+
+// One grouped exchange. For every peer d != rank and every block b < blocks_per_peer:
+//   send  bytes [ (d*blocks_per_peer + b) * block_stride + offset, +len )  of send_buf to d
+//   recv  bytes [ (d*blocks_per_peer + b) * block_stride + offset, +len )  of recv_buf from d
+// The rank's own blocks are copied device-to-device on the same stream.
+aristos_status_t ep_all_to_all_blocks(EpComm* c, const void* send_buf, void* recv_buf, int blocks_per_peer,
+                                      size_t block_stride, size_t offset, size_t len, cudaStream_t stream);
+
+}  // namespace aristos

@@ -1,0 +1,376 @@
+// Expert FFN on the 5th-generation tensor cores: a persistent, warp-specialised grouped GEMM.
+//
+// Replaces, for bf16, the reference's fused expert tile fGET / deviceCollectiveMMA (mma.cuh:46-179, :198-369: one
+// CTA per 128x64 tile, CUTLASS sm80 cp.async mainloop, mma.sync, accumulators transposed through shared memory,
+// epilogue act(acc + bias) from processor/tiling.cuh:29-57) and its software tile schedulers sK / wScheduler
+// (auditorium/scheduling.cuh:202-265, warpScheduler.cuh:267-344: doorbells and ready queues in global memory that
+// hand GEMM0 / GEMM1 tile ids to persistent "processor" CTAs).
+//
+// One launch computes  out[g, r, n0:n0+W] = epi( A[g, r, :] * B[expert(g), n, :]^T )  for every row group g:
+//   up-projection   : A = gathered tokens (groups, rows, H), B = W1 (and W3), out = h, epi = relu | gelu | swiglu
+//   down-projection : A = h (groups, rows, I),               B = W2,          out = y, epi = identity
+// Operands are (rows, K) row-major = K-major, the reference's A (M,K) / B (N,K) convention (mma.cuh:394-397).
+//
+// Per CTA (one per SM, 192 threads):
+//   warp 0    TMA producer: 3-D tiled loads (K, rows, group) of a 128x64 A box and two 128x64 B boxes per stage
+//             into 128-byte-swizzled shared memory, completion on an mbarrier
+//   warp 1    MMA issuer: one thread issues tcgen05.mma (M128 x N256 x K16, bf16 -> fp32) into one of two
+//             256-column TMEM accumulators; tcgen05.commit releases the stage / publishes the accumulator
+//   warps 2-5 epilogue: tcgen05.ld the accumulator (each warp its 32-lane quarter), activation, bf16, 16-byte
+//             stores masked by the group's row count; runs under the next tile's main loop
+// SwiGLU puts W1 rows in B rows 0-127 and W3 rows in B rows 128-255 of the same MMA, so gate and up share one pass
+// over A and the epilogue multiplies silu(acc[:, c]) * acc[:, 128 + c].
+// Tile schedule: every CTA builds the same prefix over groups of (valid 128-row tiles x column tiles) from the
+// device-resident counts and walks tiles blockIdx, blockIdx + grid, ... (row tile fastest, so concurrently running
+// CTAs share B panels through L2). Nothing is read back to the host and empty tiles cost nothing.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "ptx_sm100.cuh"
+
+namespace aristos {
+
+namespace {
+
+constexpr int BM = 128;          // rows per tile
+constexpr int BN = 256;          // MMA N (B rows per stage)
+constexpr int BK = 64;           // K per stage (128 bytes of bf16 = one swizzle row)
+constexpr int UMMA_K = 16;
+constexpr int STAGES = 4;
+constexpr int A_STAGE_BYTES = BM * BK * 2;
+constexpr int B_HALF_BYTES = 128 * BK * 2;
+constexpr int B_STAGE_BYTES = 2 * B_HALF_BYTES;
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int FFN_THREADS = 192;
+constexpr int EPI_THREADS = 128;
+constexpr int TMEM_COLS = 512;   // two 256-column accumulators
+constexpr int MAX_GROUPS = 1024;
+constexpr int SMEM_AUX_BYTES = 256 + (MAX_GROUPS + 1) * 4;
+constexpr int SMEM_BYTES = 1024 /*alignment slack*/ + STAGES * STAGE_BYTES + SMEM_AUX_BYTES;
+
+struct FfnGemmParams {
+    const int32_t* count;   // valid rows per group
+    int groups;
+    int experts;            // expert of group g = g % experts
+    int rows_per_group;
+    int row_begin, row_end; // row window inside every group
+    int N;                  // output columns
+    int K;
+    int gated;              // 1: B half 1 comes from the second weight tensor at the same rows (SwiGLU)
+    int act;                // ARISTOS_ACT_* for the non-gated epilogue
+    __nv_bfloat16* out;     // (groups * rows_per_group, N)
+    int32_t* dev_status;
+};
+
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+    __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&t);
+}
+
+__global__ void __launch_bounds__(FFN_THREADS, 1)
+ffn_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB0,
+                        const __grid_constant__ CUtensorMap tmB1, const FfnGemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* aux = smem + STAGES * STAGE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(aux);             // full[S], empty[S], tfull[2], tempty[2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aux + 128);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(aux + 132);
+    int* prefix = reinterpret_cast<int*>(aux + 256);               // [groups + 1] tiles before group g
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t bar_full = ptx::smem_u32(bars);
+    const uint32_t bar_empty = bar_full + 8 * STAGES;
+    const uint32_t bar_tfull = bar_empty + 8 * STAGES;
+    const uint32_t bar_tempty = bar_tfull + 16;
+    const uint32_t smem_base = ptx::smem_u32(smem);
+
+    const int out_w = p.gated ? 128 : 256;             // output columns per tile
+    const int n_tiles = (p.N + out_w - 1) / out_w;
+    const int window = p.row_end - p.row_begin;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            ptx::mbar_init(bar_full + 8 * s, 1);
+            ptx::mbar_init(bar_empty + 8 * s, 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            ptx::mbar_init(bar_tfull + 8 * b, 1);
+            ptx::mbar_init(bar_tempty + 8 * b, EPI_THREADS);
+        }
+        *abort_flag = 0;
+        ptx::fence_mbar_init();
+    }
+    if (warp == 0) {
+        // inclusive warp scan over groups, 32 at a time
+        int running = 0;
+        if (lane == 0) prefix[0] = 0;
+        for (int g0 = 0; g0 < p.groups; g0 += 32) {
+            const int g = g0 + lane;
+            int v = 0;
+            if (g < p.groups) {
+                int rows = p.count[g] - p.row_begin;
+                rows = max(0, min(rows, window));
+                v = ((rows + BM - 1) / BM) * n_tiles;
+            }
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const int o = __shfl_up_sync(0xffffffffu, v, d);
+                if (lane >= d) v += o;
+            }
+            if (g < p.groups) prefix[g + 1] = running + v;
+            running += __shfl_sync(0xffffffffu, v, 31);
+        }
+    } else if (warp == 1) {
+        ptx::tmem_alloc(ptx::smem_u32(tmem_slot), TMEM_COLS);
+    }
+    ptx::tcgen05_fence_before();
+    __syncthreads();
+    ptx::tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const int total_tiles = prefix[p.groups];
+    const int kblocks = p.K / BK;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            ptx::prefetch_tensormap(&tmA);
+            ptx::prefetch_tensormap(&tmB0);
+            ptx::prefetch_tensormap(&tmB1);
+            int stage = 0;
+            uint32_t phase = 0;
+            int g = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+                while (tile >= prefix[g + 1]) ++g;
+                const int local = tile - prefix[g];
+                const int mt = (prefix[g + 1] - prefix[g]) / n_tiles;
+                const int m0 = p.row_begin + (local % mt) * BM;
+                const int n0 = (local / mt) * out_w;
+                const int e = g % p.experts;
+                const int n1 = p.gated ? n0 : n0 + 128;
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    ok = ptx::mbar_wait_bounded(bar_empty + 8 * stage, phase ^ 1u, abort_flag, p.dev_status);
+                    if (!ok) break;
+                    const uint32_t full = bar_full + 8 * stage;
+                    const uint32_t sa = smem_base + stage * STAGE_BYTES;
+                    ptx::mbar_arrive_expect_tx(full, STAGE_BYTES);
+                    ptx::tma_load_3d(sa, &tmA, kb * BK, m0, g, full);
+                    ptx::tma_load_3d(sa + A_STAGE_BYTES, &tmB0, kb * BK, n0, e, full);
+                    ptx::tma_load_3d(sa + A_STAGE_BYTES + B_HALF_BYTES, &tmB1, kb * BK, n1, e, full);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = ptx::umma_idesc_bf16(BM, BN);
+            int stage = 0;
+            uint32_t phase = 0;
+            int it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
+                const int buf = it & 1;
+                const uint32_t aphase = (it >> 1) & 1u;
+                ok = ptx::mbar_wait_bounded(bar_tempty + 8 * buf, aphase ^ 1u, abort_flag, p.dev_status);
+                if (!ok) break;
+                ptx::tcgen05_fence_after();
+                const uint32_t tmem_d = tmem_base + buf * BN;
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    ok = ptx::mbar_wait_bounded(bar_full + 8 * stage, phase, abort_flag, p.dev_status);
+                    if (!ok) break;
+                    ptx::tcgen05_fence_after();
+                    const uint32_t sa = smem_base + stage * STAGE_BYTES;
+                    const uint64_t da = ptx::umma_desc_k_sw128(sa);
+                    const uint64_t db = ptx::umma_desc_k_sw128(sa + A_STAGE_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        // advance 32 bytes (16 bf16) along K inside the swizzled row: +2 in 16-byte units
+                        ptx::umma_f16(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                    }
+                    ptx::umma_commit(bar_empty + 8 * stage);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+                if (ok) ptx::umma_commit(bar_tfull + 8 * buf);
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------------ epilogue (warps 2..5)
+        const int quarter = warp & 3;                 // TMEM lanes this warp may read
+        const int row_in_tile = quarter * 32 + lane;
+        int g = 0;
+        int it = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
+            while (tile >= prefix[g + 1]) ++g;
+            const int local = tile - prefix[g];
+            const int mt = (prefix[g + 1] - prefix[g]) / n_tiles;
+            const int m0 = p.row_begin + (local % mt) * BM;
+            const int n0 = (local / mt) * out_w;
+            const int buf = it & 1;
+            const uint32_t aphase = (it >> 1) & 1u;
+            ok = ptx::mbar_wait_bounded(bar_tfull + 8 * buf, aphase, abort_flag, p.dev_status);
+            ok = __all_sync(0xffffffffu, ok);   // the TMEM loads below need the whole warp
+            if (!ok) break;
+            ptx::tcgen05_fence_after();
+            const int row = m0 + row_in_tile;
+            const int row_limit = min(p.count[g], p.row_end);
+            const bool row_ok = row < row_limit;
+            __nv_bfloat16* orow = p.out + ((size_t)g * p.rows_per_group + row) * p.N + n0;
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
+            if (p.gated) {
+#pragma unroll 1
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t ga[32], up[32];
+                    ptx::tmem_ld_32x32b_x32(taddr + c * 32, ga);
+                    ptx::tmem_ld_32x32b_x32(taddr + 128 + c * 32, up);
+                    ptx::tmem_ld_wait();
+                    if (c == 3) {
+                        ptx::tcgen05_fence_before();
+                        ptx::mbar_arrive(bar_tempty + 8 * buf);
+                    }
+                    if (row_ok && n0 + c * 32 < p.N) {
+                        uint32_t o[16];
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            const float h0 = act_silu(__uint_as_float(ga[2 * i])) * __uint_as_float(up[2 * i]);
+                            const float h1 = act_silu(__uint_as_float(ga[2 * i + 1])) * __uint_as_float(up[2 * i + 1]);
+                            o[i] = pack_bf16(h0, h1);
+                        }
+                        uint4* dst = reinterpret_cast<uint4*>(orow + c * 32);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) dst[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+                    }
+                }
+            } else {
+#pragma unroll 1
+                for (int c = 0; c < 8; ++c) {
+                    uint32_t acc[32];
+                    ptx::tmem_ld_32x32b_x32(taddr + c * 32, acc);
+                    ptx::tmem_ld_wait();
+                    if (c == 7) {
+                        ptx::tcgen05_fence_before();
+                        ptx::mbar_arrive(bar_tempty + 8 * buf);
+                    }
+                    if (row_ok && n0 + c * 32 < p.N) {
+                        uint32_t o[16];
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            float v0 = __uint_as_float(acc[2 * i]), v1 = __uint_as_float(acc[2 * i + 1]);
+                            if (p.act == ARISTOS_ACT_RELU) { v0 = act_relu(v0); v1 = act_relu(v1); }
+                            else if (p.act == ARISTOS_ACT_GELU) { v0 = act_gelu(v0); v1 = act_gelu(v1); }
+                            o[i] = pack_bf16(v0, v1);
+                        }
+                        uint4* dst = reinterpret_cast<uint4*>(orow + c * 32);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) dst[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+                    }
+                }
+            }
+        }
+    }
+
+    ptx::tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tcgen05_fence_after();
+        ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+// ---- host side ------------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            return nullptr;
+        fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+    return fn;
+}
+
+// (outer, rows, K) bf16 tensor, K contiguous; box = 64 x 128 x 1 with the 128-byte swizzle.
+aristos_status_t make_map_3d(CUtensorMap* tm, const void* base, int K, int rows, int outer) {
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) { set_last_error("cuTensorMapEncodeTiled is not available from the driver"); return ARISTOS_ERR_CUDA; }
+    const cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)rows, (cuuint64_t)outer};
+    const cuuint64_t strides[2] = {(cuuint64_t)K * 2, (cuuint64_t)K * 2 * (cuuint64_t)rows};
+    const cuuint32_t box[3] = {BK, 128, 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_last_error("cuTensorMapEncodeTiled failed with %d (K=%d rows=%d outer=%d)", (int)r, K, rows, outer);
+        return ARISTOS_ERR_CUDA;
+    }
+    return ARISTOS_OK;
+}
+
+aristos_status_t launch_gemm(const void* A, const void* B0, const void* B1, const FfnGemmParams& p, int grid_limit,
+                             cudaStream_t st) {
+    CUtensorMap tmA, tmB0, tmB1;
+    ARISTOS_TRY(make_map_3d(&tmA, A, p.K, p.rows_per_group, p.groups));
+    ARISTOS_TRY(make_map_3d(&tmB0, B0, p.K, p.N, p.experts));
+    ARISTOS_TRY(make_map_3d(&tmB1, B1, p.K, p.N, p.experts));
+    ARISTOS_CUDA_TRY(cudaFuncSetAttribute(ffn_grouped_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          SMEM_BYTES));
+    const int out_w = p.gated ? 128 : 256;
+    const int64_t bound = (int64_t)p.groups * ceil_div(p.row_end - p.row_begin, BM) * ceil_div(p.N, out_w);
+    int sms = device_sm_count();
+    if (sms <= 0) { set_last_error("no CUDA device"); return ARISTOS_ERR_CUDA; }
+    if (grid_limit > 0 && grid_limit < sms) sms = grid_limit;
+    const int grid = (int)(bound < sms ? bound : sms);
+    if (grid <= 0) return ARISTOS_OK;
+    ffn_grouped_gemm_kernel<<<grid, FFN_THREADS, SMEM_BYTES, st>>>(tmA, tmB0, tmB1, p);
+    ARISTOS_COUNT_LAUNCH();
+    ARISTOS_CUDA_TRY(cudaGetLastError());
+    return ARISTOS_OK;
+}
+
+}  // namespace
+
+aristos_status_t expert_ffn_bf16_sm100(const void* xg, const int32_t* count, int groups, int rows_per_group,
+                                       int experts, const void* w1, const void* w3, const void* w2, void* h_scratch,
+                                       void* y, int H, int I, int hidden_act, int row_begin, int row_end,
+                                       int sm_limit, int32_t* dev_status, cudaStream_t st) {
+    if (groups > MAX_GROUPS) { set_last_error("expert_ffn: more than %d row groups", MAX_GROUPS); return ARISTOS_ERR_CONFIG; }
+    if (H % BK != 0 || I % BK != 0) { set_last_error("expert_ffn: H and I must be multiples of 64"); return ARISTOS_ERR_CONFIG; }
+    if (row_begin % BM != 0) { set_last_error("expert_ffn: row_begin must be a multiple of 128"); return ARISTOS_ERR_INVALID_ARG; }
+    const bool gated = hidden_act == ARISTOS_ACT_SWIGLU;
+    FfnGemmParams p{};
+    p.count = count;
+    p.groups = groups;
+    p.experts = experts;
+    p.rows_per_group = rows_per_group;
+    p.row_begin = row_begin;
+    p.row_end = row_end;
+    p.dev_status = dev_status;
+    // up-projection: h = epi(xg * W1^T [, xg * W3^T])
+    p.N = I;
+    p.K = H;
+    p.gated = gated ? 1 : 0;
+    p.act = hidden_act;
+    p.out = static_cast<__nv_bfloat16*>(h_scratch);
+    ARISTOS_TRY(launch_gemm(xg, w1, gated ? w3 : w1, p, sm_limit, st));
+    // down-projection: y = h * W2^T
+    p.N = H;
+    p.K = I;
+    p.gated = 0;
+    p.act = ARISTOS_ACT_IDENTITY;
+    p.out = static_cast<__nv_bfloat16*>(y);
+    ARISTOS_TRY(launch_gemm(h_scratch, w2, w2, p, sm_limit, st));
+    return ARISTOS_OK;
+}
+
+}  // namespace aristos

@@ -1,0 +1,319 @@
+// Layer handle: workspace planning and the orchestration gate -> dispatch -> (all-to-all) -> expert FFN ->
+// (all-to-all) -> combine behind aristos_moe_forward.
+//
+// Replaces the reference's host harnesses, which allocate one slab, copy inputs in, launch and synchronise inside a
+// zero-argument function (mma.cuh:371-443 testCollective; auditorium/overlap.cuh:159-242 overlapPrototype, whose
+// per-peer pipeline "put tile -> wait flag -> GEMM -> put result -> wait flag" (:94-153) becomes the chunked
+// exchange below: rows travel in row windows of every expert block, the GEMMs of window c run while window c+1 is
+// still in flight, and the results of window c return while window c+1 is being computed).
+#include <cmath>
+#include <cstdlib>
+#include <cstring>
+#include <new>
+#include <vector>
+
+#include "common.cuh"
+#include "ep_nccl.h"
+
+namespace aristos {
+aristos_status_t dispatch_impl(const int32_t* topk_idx, int S, int k, int E, int cap, int32_t* count,
+                               int32_t* slot_of, int32_t* token_of_slot, void* scratch, size_t scratch_bytes,
+                               int32_t* dev_status, cudaStream_t st);
+}
+
+using namespace aristos;
+
+struct aristos_moe {
+    aristos_config_t cfg;
+    int rank = 0, world = 1, device = 0;
+    int S = 0, H = 0, I = 0, E = 0, k = 0, cap = 0, E_local = 0, groups = 0;
+    size_t elt = 2;
+    // workspace
+    void* ws = nullptr;
+    size_t ws_bytes = 0;
+    bool ws_owned = false;
+    // carve-up of the workspace
+    int32_t *topk_idx = nullptr, *count = nullptr, *slot_of = nullptr, *token_of_slot = nullptr, *rcount = nullptr,
+            *dev_status = nullptr;
+    float *topk_w = nullptr, *gate_bias = nullptr;
+    void *dispatch_scratch = nullptr, *xg = nullptr, *xr = nullptr, *h = nullptr, *yr = nullptr, *yg = nullptr,
+         *x_stage = nullptr, *out_stage = nullptr;
+    size_t dispatch_scratch_bytes = 0;
+    bool bias_ready = false;
+    // expert parallel
+    EpComm* comm = nullptr;
+    cudaStream_t comm_stream = nullptr;
+    cudaEvent_t ev_dispatched = nullptr, ev_returned = nullptr;
+    std::vector<cudaEvent_t> ev_in, ev_out;
+    int chunks = 1, chunk_rows = 0, ffn_sm_limit = 0;
+    int64_t launches = 0;
+};
+
+namespace {
+
+struct Carver {
+    size_t off = 0;
+    size_t take(size_t bytes) {
+        const size_t o = off;
+        off = align_up(off + bytes, 1024);
+        return o;
+    }
+};
+
+// Lays the buffers out; with base == nullptr only the total size is computed.
+size_t plan_workspace(aristos_moe* L, char* base) {
+    Carver c;
+    const size_t S = L->S, k = L->k, E = L->E, cap = L->cap, H = L->H, I = L->I, elt = L->elt;
+    const size_t rows_local = (size_t)L->groups * cap;   // rows this rank's experts may receive
+#define CARVE(field, type, bytes)                                   \
+    {                                                               \
+        const size_t o = c.take(bytes);                             \
+        if (base) L->field = reinterpret_cast<type>(base + o);      \
+    }
+    CARVE(dev_status, int32_t*, 4)
+    CARVE(topk_idx, int32_t*, S * k * 4)
+    CARVE(topk_w, float*, S * k * 4)
+    CARVE(count, int32_t*, E * 4)
+    CARVE(rcount, int32_t*, (size_t)L->groups * 4)
+    CARVE(slot_of, int32_t*, S * k * 4)
+    CARVE(token_of_slot, int32_t*, E * cap * 4)
+    CARVE(gate_bias, float*, E * 4)
+    CARVE(dispatch_scratch, void*, L->dispatch_scratch_bytes)
+    CARVE(xg, void*, E * cap * H * elt)
+    CARVE(h, void*, rows_local * I * elt)
+    CARVE(yr, void*, rows_local * H * elt)
+    if (L->world > 1) {
+        CARVE(xr, void*, rows_local * H * elt)
+        CARVE(yg, void*, E * cap * H * elt)
+    } else if (base) {
+        L->xr = L->xg;
+        L->yg = L->yr;
+    }
+    CARVE(x_stage, void*, S * H * elt)
+    CARVE(out_stage, void*, S * H * elt)
+#undef CARVE
+    return c.off;
+}
+
+aristos_status_t ensure_workspace(aristos_moe* L) {
+    if (L->ws) return ARISTOS_OK;
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, L->ws_bytes);
+    if (e != cudaSuccess) {
+        set_last_error("cudaMalloc of the %zu-byte layer workspace failed: %s", L->ws_bytes, cudaGetErrorString(e));
+        return ARISTOS_ERR_NOMEM;
+    }
+    L->ws = p;
+    L->ws_owned = true;
+    plan_workspace(L, static_cast<char*>(p));
+    ARISTOS_CUDA_TRY(cudaMemset(L->dev_status, 0, 4));
+    L->bias_ready = false;
+    return ARISTOS_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+aristos_status_t aristos_moe_create(const aristos_config_t* cfg, int rank, int world, const void* nccl_unique_id,
+                                    aristos_moe_t** out) {
+    if (!cfg || !out) return ARISTOS_ERR_INVALID_ARG;
+    ARISTOS_TRY(aristos_config_validate(cfg));
+    if (world < 1 || rank < 0 || rank >= world) { set_last_error("create: bad rank/world"); return ARISTOS_ERR_INVALID_ARG; }
+    if (cfg->ep_world != world) { set_last_error("create: config ep_world (%d) != world (%d)", cfg->ep_world, world); return ARISTOS_ERR_CONFIG; }
+    if (world > 1 && !nccl_unique_id) { set_last_error("create: world > 1 needs a NCCL unique id"); return ARISTOS_ERR_INVALID_ARG; }
+    if (cfg->torch_dtype != ARISTOS_DTYPE_F32 && cfg->torch_dtype != ARISTOS_DTYPE_BF16) {
+        set_last_error("create: torch_dtype %d not implemented (0 = fp32 and 2 = bf16 are)", cfg->torch_dtype);
+        return ARISTOS_ERR_UNSUPPORTED;
+    }
+    int dev = 0;
+    ARISTOS_CUDA_TRY(cudaGetDevice(&dev));
+    aristos_moe* L = new (std::nothrow) aristos_moe();
+    if (!L) return ARISTOS_ERR_NOMEM;
+    L->cfg = *cfg;
+    L->rank = rank;
+    L->world = world;
+    L->device = dev;
+    L->S = aristos_config_tokens(cfg);
+    L->H = cfg->hidden_size;
+    L->I = cfg->intermediate_size;
+    L->E = cfg->num_experts;
+    L->k = cfg->expert_top_k;
+    L->cap = aristos_config_capacity(cfg);
+    L->E_local = L->E / world;
+    L->groups = L->E_local * world;
+    L->elt = dtype_bytes(cfg->torch_dtype);
+    if ((int64_t)L->E * L->cap > 0x7fffffffLL) { delete L; set_last_error("create: E*capacity overflows int32"); return ARISTOS_ERR_CONFIG; }
+    if (L->groups > 1024) { delete L; set_last_error("create: more than 1024 row groups per rank"); return ARISTOS_ERR_CONFIG; }
+    L->dispatch_scratch_bytes = aristos_dispatch_scratch_bytes(L->S, L->k, L->E);
+    L->ws_bytes = plan_workspace(L, nullptr);
+    if (world > 1) {
+        aristos_status_t s = ep_comm_create(nccl_unique_id, rank, world, &L->comm);
+        if (s != ARISTOS_OK) { delete L; return s; }
+        cudaError_t e = cudaStreamCreateWithFlags(&L->comm_stream, cudaStreamNonBlocking);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&L->ev_dispatched, cudaEventDisableTiming);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&L->ev_returned, cudaEventDisableTiming);
+        // row windows: a multiple of 128 rows, at most 4 per forward, at least 512 rows each
+        int chunks = 4;
+        while (chunks > 1 && ceil_div(L->cap, chunks) < 512) --chunks;
+        L->chunk_rows = ceil_div(ceil_div(L->cap, chunks), 128) * 128;
+        L->chunks = ceil_div(L->cap, L->chunk_rows);
+        const char* env = getenv("ARISTOS_EP_CHUNKS");
+        if (env && atoi(env) >= 1) {
+            L->chunk_rows = ceil_div(ceil_div(L->cap, atoi(env)), 128) * 128;
+            L->chunks = ceil_div(L->cap, L->chunk_rows);
+        }
+        // leave SMs for the NCCL kernels that run beside the GEMMs
+        L->ffn_sm_limit = device_sm_count() - 16;
+        const char* env2 = getenv("ARISTOS_EP_FFN_SMS");
+        if (env2 && atoi(env2) >= 1) L->ffn_sm_limit = atoi(env2);
+        L->ev_in.resize(L->chunks);
+        L->ev_out.resize(L->chunks);
+        for (int c = 0; c < L->chunks && e == cudaSuccess; ++c) {
+            e = cudaEventCreateWithFlags(&L->ev_in[c], cudaEventDisableTiming);
+            if (e == cudaSuccess) e = cudaEventCreateWithFlags(&L->ev_out[c], cudaEventDisableTiming);
+        }
+        if (e != cudaSuccess) { aristos_moe_destroy(L); return cuda_fail(e, "stream/event creation"); }
+    }
+    *out = L;
+    return ARISTOS_OK;
+}
+
+size_t aristos_moe_workspace_bytes(const aristos_moe_t* L) { return L ? L->ws_bytes : 0; }
+
+aristos_status_t aristos_moe_set_workspace(aristos_moe_t* L, void* workspace, size_t bytes) {
+    if (!L || !workspace) return ARISTOS_ERR_INVALID_ARG;
+    if (bytes < L->ws_bytes) { set_last_error("workspace: %zu bytes given, %zu needed", bytes, L->ws_bytes); return ARISTOS_ERR_WORKSPACE; }
+    if (reinterpret_cast<uintptr_t>(workspace) % 1024 != 0) { set_last_error("workspace must be 1024-byte aligned"); return ARISTOS_ERR_INVALID_ARG; }
+    if (L->ws && L->ws_owned) cudaFree(L->ws);
+    L->ws = workspace;
+    L->ws_owned = false;
+    plan_workspace(L, static_cast<char*>(workspace));
+    ARISTOS_CUDA_TRY(cudaMemset(L->dev_status, 0, 4));
+    L->bias_ready = false;
+    return ARISTOS_OK;
+}
+
+aristos_status_t aristos_moe_forward(aristos_moe_t* L, const void* x, const void* w_gate, const float* gate_bias,
+                                     const void* w1, const void* w3, const void* w2, const void* scales, void* out,
+                                     void* stream) {
+    (void)scales;
+    if (!L || !x || !w_gate || !w1 || !w2 || !out) { set_last_error("forward: NULL pointer"); return ARISTOS_ERR_INVALID_ARG; }
+    if (L->cfg.hidden_act == ARISTOS_ACT_SWIGLU && !w3) { set_last_error("forward: SwiGLU needs w3"); return ARISTOS_ERR_INVALID_ARG; }
+    ARISTOS_TRY(ensure_workspace(L));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int64_t launches0 = launch_counter();
+    const int dt = L->cfg.torch_dtype;
+
+    const float* bias = gate_bias;
+    if (!bias && L->cfg.gate_bias_zipf_s > 0.0) {
+        if (!L->bias_ready) {
+            std::vector<float> b(L->E);
+            aristos_zipf_bias_host(b.data(), L->E, L->cfg.gate_bias_zipf_s);
+            ARISTOS_CUDA_TRY(cudaMemcpyAsync(L->gate_bias, b.data(), sizeof(float) * L->E, cudaMemcpyHostToDevice, st));
+            ARISTOS_CUDA_TRY(cudaStreamSynchronize(st));   // b goes out of scope
+            L->bias_ready = true;
+        }
+        bias = L->gate_bias;
+    }
+
+    ARISTOS_TRY(aristos_gate_topk(x, w_gate, bias, L->S, L->H, L->E, L->k, L->cfg.gate_fn, L->cfg.renorm_topk, dt,
+                                  L->topk_idx, L->topk_w, nullptr, st));
+    ARISTOS_TRY(dispatch_impl(L->topk_idx, L->S, L->k, L->E, L->cap, L->count, L->slot_of, L->token_of_slot,
+                              L->dispatch_scratch, L->dispatch_scratch_bytes, L->dev_status, st));
+    ARISTOS_TRY(aristos_permute(x, L->slot_of, L->S, L->k, L->H, dt, L->xg, st));
+
+    if (L->world == 1) {
+        ARISTOS_TRY(aristos_expert_ffn(L->xg, L->count, L->E, L->cap, L->E, w1, w3, w2, L->h, L->yr, L->H, L->I,
+                                       L->cfg.hidden_act, dt, 0, L->cap, 0, L->dev_status, st));
+    } else {
+        const size_t row_bytes = (size_t)L->H * L->elt;
+        const size_t block_stride = (size_t)L->cap * row_bytes;
+        ARISTOS_CUDA_TRY(cudaEventRecord(L->ev_dispatched, st));
+        ARISTOS_CUDA_TRY(cudaStreamWaitEvent(L->comm_stream, L->ev_dispatched, 0));
+        // per-(source, local expert) row counts
+        ARISTOS_TRY(ep_all_to_all_blocks(L->comm, L->count, L->rcount, 1, (size_t)L->E_local * 4, 0,
+                                         (size_t)L->E_local * 4, L->comm_stream));
+        for (int c = 0; c < L->chunks; ++c) {
+            const int r0 = c * L->chunk_rows, r1 = std::min(L->cap, r0 + L->chunk_rows);
+            ARISTOS_TRY(ep_all_to_all_blocks(L->comm, L->xg, L->xr, L->E_local, block_stride, (size_t)r0 * row_bytes,
+                                             (size_t)(r1 - r0) * row_bytes, L->comm_stream));
+            ARISTOS_CUDA_TRY(cudaEventRecord(L->ev_in[c], L->comm_stream));
+        }
+        for (int c = 0; c < L->chunks; ++c) {
+            const int r0 = c * L->chunk_rows, r1 = std::min(L->cap, r0 + L->chunk_rows);
+            ARISTOS_CUDA_TRY(cudaStreamWaitEvent(st, L->ev_in[c], 0));
+            ARISTOS_TRY(aristos_expert_ffn(L->xr, L->rcount, L->groups, L->cap, L->E_local, w1, w3, w2, L->h, L->yr,
+                                           L->H, L->I, L->cfg.hidden_act, dt, r0, r1, L->ffn_sm_limit, L->dev_status,
+                                           st));
+            ARISTOS_CUDA_TRY(cudaEventRecord(L->ev_out[c], st));
+            ARISTOS_CUDA_TRY(cudaStreamWaitEvent(L->comm_stream, L->ev_out[c], 0));
+            ARISTOS_TRY(ep_all_to_all_blocks(L->comm, L->yr, L->yg, L->E_local, block_stride, (size_t)r0 * row_bytes,
+                                             (size_t)(r1 - r0) * row_bytes, L->comm_stream));
+        }
+        ARISTOS_CUDA_TRY(cudaEventRecord(L->ev_returned, L->comm_stream));
+        ARISTOS_CUDA_TRY(cudaStreamWaitEvent(st, L->ev_returned, 0));
+    }
+    ARISTOS_TRY(aristos_combine(L->yg, L->slot_of, L->topk_w, L->S, L->k, L->H, dt, out, st));
+    L->launches += launch_counter() - launches0;
+    return ARISTOS_OK;
+}
+
+aristos_status_t aristos_moe_forward_host(aristos_moe_t* L, const void* x_host, const void* w_gate,
+                                          const float* gate_bias, const void* w1, const void* w3, const void* w2,
+                                          const void* scales, void* out_host, void* stream) {
+    if (!L || !x_host || !out_host) { set_last_error("forward_host: NULL pointer"); return ARISTOS_ERR_INVALID_ARG; }
+    ARISTOS_TRY(ensure_workspace(L));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const size_t bytes = (size_t)L->S * L->H * L->elt;
+    ARISTOS_CUDA_TRY(cudaMemcpyAsync(L->x_stage, x_host, bytes, cudaMemcpyHostToDevice, st));
+    ARISTOS_TRY(aristos_moe_forward(L, L->x_stage, w_gate, gate_bias, w1, w3, w2, scales, L->out_stage, stream));
+    ARISTOS_CUDA_TRY(cudaMemcpyAsync(out_host, L->out_stage, bytes, cudaMemcpyDeviceToHost, st));
+    ARISTOS_CUDA_TRY(cudaStreamSynchronize(st));
+    return ARISTOS_OK;
+}
+
+aristos_status_t aristos_moe_routing(const aristos_moe_t* L, aristos_routing_t* out) {
+    if (!L || !out) return ARISTOS_ERR_INVALID_ARG;
+    if (!L->ws) { set_last_error("routing: no forward has run yet"); return ARISTOS_ERR_INVALID_ARG; }
+    out->topk_idx = L->topk_idx;
+    out->topk_w = L->topk_w;
+    out->count = L->count;
+    out->slot_of = L->slot_of;
+    out->token_of_slot = L->token_of_slot;
+    out->tokens = L->S;
+    out->top_k = L->k;
+    out->num_experts = L->E;
+    out->capacity = L->cap;
+    return ARISTOS_OK;
+}
+
+aristos_status_t aristos_moe_status(aristos_moe_t* L) {
+    if (!L) return ARISTOS_ERR_INVALID_ARG;
+    ARISTOS_CUDA_TRY(cudaDeviceSynchronize());
+    if (!L->ws) return ARISTOS_OK;
+    int32_t bits = 0;
+    ARISTOS_CUDA_TRY(cudaMemcpy(&bits, L->dev_status, 4, cudaMemcpyDeviceToHost));
+    if (bits) ARISTOS_CUDA_TRY(cudaMemset(L->dev_status, 0, 4));
+    if (bits & DEV_FAULT_TIMEOUT) { set_last_error("a bounded device-side wait expired"); return ARISTOS_ERR_DEVICE_TIMEOUT; }
+    if (bits & DEV_FAULT_BOUNDS) { set_last_error("a routing index was out of range"); return ARISTOS_ERR_DEVICE_BOUNDS; }
+    return ARISTOS_OK;
+}
+
+int64_t aristos_moe_launch_count(const aristos_moe_t* L) { return L ? L->launches : 0; }
+
+aristos_status_t aristos_moe_destroy(aristos_moe_t* L) {
+    if (!L) return ARISTOS_OK;
+    cudaDeviceSynchronize();
+    for (cudaEvent_t e : L->ev_in) if (e) cudaEventDestroy(e);
+    for (cudaEvent_t e : L->ev_out) if (e) cudaEventDestroy(e);
+    if (L->ev_dispatched) cudaEventDestroy(L->ev_dispatched);
+    if (L->ev_returned) cudaEventDestroy(L->ev_returned);
+    if (L->comm_stream) cudaStreamDestroy(L->comm_stream);
+    if (L->comm) ep_comm_destroy(L->comm);
+    if (L->ws && L->ws_owned) cudaFree(L->ws);
+    delete L;
+    return ARISTOS_OK;
+}
+
+}  // extern "C"

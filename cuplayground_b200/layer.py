@@ -1,0 +1,197 @@
+"""Host-side mirror of the C ABI: the MoE layer handle and the stage entry points on torch tensors.
+
+torch is used for device memory, streams and (by callers) torch.distributed; every computation goes through
+libaristos_moe.so. Nothing here falls back to PyTorch ops."""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+
+from . import _lib
+from .config import AristosConfig
+
+_TORCH_DTYPE = {_lib.DTYPE_F32: torch.float32, _lib.DTYPE_BF16: torch.bfloat16, _lib.DTYPE_F16: torch.float16}
+_ARISTOS_DTYPE = {v: k for k, v in _TORCH_DTYPE.items()}
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    if t is None:
+        return None
+    if not t.is_contiguous():
+        raise ValueError("tensors passed to the C ABI must be contiguous")
+    return C.c_void_p(t.data_ptr())
+
+
+def _stream_ptr(stream: Optional[torch.cuda.Stream] = None):
+    s = stream if stream is not None else torch.cuda.current_stream()
+    return C.c_void_p(s.cuda_stream)
+
+
+def _dt(t: torch.Tensor) -> int:
+    try:
+        return _ARISTOS_DTYPE[t.dtype]
+    except KeyError:
+        raise TypeError(f"unsupported tensor dtype {t.dtype}") from None
+
+
+def nccl_unique_id() -> bytes:
+    buf = C.create_string_buffer(128)
+    _lib.check(_lib.load().aristos_nccl_unique_id(buf))
+    return buf.raw
+
+
+def fill_normal(t: torch.Tensor, mean: float, std: float, seed: int, stream_id: int) -> torch.Tensor:
+    _lib.check(_lib.load().aristos_fill_normal(_ptr(t), t.numel(), mean, std, seed, stream_id, _dt(t), _stream_ptr()))
+    return t
+
+
+# ---- stage entry points ---------------------------------------------------------------------------------------------
+def gate_topk(x, w_gate, k: int, gate_fn: int = 0, renorm: int = 0, gate_bias=None, want_logits: bool = False):
+    S, H = x.shape
+    E = w_gate.shape[0]
+    idx = torch.empty((S, k), dtype=torch.int32, device=x.device)
+    w = torch.empty((S, k), dtype=torch.float32, device=x.device)
+    logits = torch.empty((S, E), dtype=torch.float32, device=x.device) if want_logits else None
+    _lib.check(_lib.load().aristos_gate_topk(_ptr(x), _ptr(w_gate), _ptr(gate_bias), S, H, E, k, gate_fn, renorm,
+                                             _dt(x), _ptr(idx), _ptr(w), _ptr(logits), _stream_ptr()))
+    return (idx, w, logits) if want_logits else (idx, w)
+
+
+def dispatch(topk_idx, E: int, cap: int):
+    S, k = topk_idx.shape
+    dev = topk_idx.device
+    lib = _lib.load()
+    nbytes = lib.aristos_dispatch_scratch_bytes(S, k, E)
+    scratch = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=dev)
+    count = torch.empty(E, dtype=torch.int32, device=dev)
+    slot_of = torch.empty((S, k), dtype=torch.int32, device=dev)
+    tos = torch.empty(E * cap, dtype=torch.int32, device=dev)
+    _lib.check(lib.aristos_dispatch(_ptr(topk_idx), S, k, E, cap, _ptr(count), _ptr(slot_of), _ptr(tos),
+                                    _ptr(scratch), nbytes, _stream_ptr()))
+    return count, slot_of, tos
+
+
+def permute(x, slot_of, nslots: int, zero: bool = False):
+    S, H = x.shape
+    k = slot_of.shape[1]
+    xg = (torch.zeros if zero else torch.empty)((nslots, H), dtype=x.dtype, device=x.device)
+    _lib.check(_lib.load().aristos_permute(_ptr(x), _ptr(slot_of), S, k, H, _dt(x), _ptr(xg), _stream_ptr()))
+    return xg
+
+
+def expert_ffn(xg, count, w1, w3, w2, hidden_act: int, *, experts: Optional[int] = None, row_begin: int = 0,
+               row_end: Optional[int] = None, sm_limit: int = 0, dev_status=None, y=None, h=None):
+    """xg (groups, rows, H); w1/w3 (experts, I, H); w2 (experts, H, I) -> y (groups, rows, H)."""
+    groups, rows, H = xg.shape
+    I = w1.shape[1]
+    experts = w1.shape[0] if experts is None else experts
+    row_end = rows if row_end is None else row_end
+    if h is None:
+        h = torch.empty((groups, rows, I), dtype=xg.dtype, device=xg.device)
+    if y is None:
+        y = torch.zeros((groups, rows, H), dtype=xg.dtype, device=xg.device)
+    _lib.check(_lib.load().aristos_expert_ffn(_ptr(xg), _ptr(count), groups, rows, experts, _ptr(w1), _ptr(w3),
+                                              _ptr(w2), _ptr(h), _ptr(y), H, I, hidden_act, _dt(xg), row_begin,
+                                              row_end, sm_limit, _ptr(dev_status), _stream_ptr()))
+    return y
+
+
+def combine(y, slot_of, topk_w):
+    S, k = slot_of.shape
+    H = y.shape[-1]
+    out = torch.empty((S, H), dtype=y.dtype, device=y.device)
+    _lib.check(_lib.load().aristos_combine(_ptr(y), _ptr(slot_of), _ptr(topk_w), S, k, H, _dt(y), _ptr(out),
+                                           _stream_ptr()))
+    return out
+
+
+# ---- layer ----------------------------------------------------------------------------------------------------------
+class MoELayer:
+    """One MoE layer on the current CUDA device (aristos_moe_create ... aristos_moe_destroy)."""
+
+    def __init__(self, cfg: AristosConfig, rank: int = 0, world: int = 1, nccl_uid: Optional[bytes] = None):
+        if not torch.cuda.is_available():
+            raise RuntimeError("cuplayground_b200 needs a CUDA device (sm_100a); there is no CPU fallback")
+        self.cfg = cfg
+        self.rank, self.world = rank, world
+        self._lib = _lib.load()
+        self._h = C.c_void_p()
+        s = cfg.to_struct()
+        uid = C.create_string_buffer(nccl_uid, 128) if nccl_uid is not None else None
+        _lib.check(self._lib.aristos_moe_create(C.byref(s), rank, world, uid, C.byref(self._h)))
+        self.S, self.H, self.I = cfg.S, cfg.hidden_size, cfg.intermediate_size
+        self.E, self.k, self.cap = cfg.num_experts, cfg.expert_top_k, cfg.capacity
+        self.E_local = self.E // world
+        self.dtype = _TORCH_DTYPE[cfg.torch_dtype]
+        self._ws = None
+
+    @property
+    def workspace_bytes(self) -> int:
+        return int(self._lib.aristos_moe_workspace_bytes(self._h))
+
+    def use_torch_workspace(self) -> None:
+        """Allocate the workspace from torch's caching allocator instead of cudaMalloc inside the library."""
+        self._ws = torch.empty(self.workspace_bytes + 1024, dtype=torch.uint8, device="cuda")
+        base = (self._ws.data_ptr() + 1023) // 1024 * 1024
+        _lib.check(self._lib.aristos_moe_set_workspace(self._h, C.c_void_p(base), self.workspace_bytes))
+
+    def forward(self, x, w_gate, w1, w3, w2, gate_bias=None, out=None, stream=None):
+        if out is None:
+            out = torch.empty_like(x)
+        _lib.check(self._lib.aristos_moe_forward(self._h, _ptr(x), _ptr(w_gate), _ptr(gate_bias), _ptr(w1), _ptr(w3),
+                                                 _ptr(w2), None, _ptr(out), _stream_ptr(stream)))
+        return out
+
+    def forward_host(self, x_host, w_gate, w1, w3, w2, out_host, gate_bias=None, stream=None):
+        """x_host / out_host: CPU tensors (pinned for full speed); weights stay on the device. Synchronous."""
+        if x_host.is_cuda or out_host.is_cuda:
+            raise ValueError("forward_host takes host tensors")
+        _lib.check(self._lib.aristos_moe_forward_host(self._h, _ptr(x_host), _ptr(w_gate), _ptr(gate_bias), _ptr(w1),
+                                                      _ptr(w3), _ptr(w2), None, _ptr(out_host), _stream_ptr(stream)))
+        return out_host
+
+    def routing(self) -> dict:
+        """Copies of the routing tensors of the last forward (torch tensors on the device)."""
+        r = _lib.AristosRoutingStruct()
+        _lib.check(self._lib.aristos_moe_routing(self._h, C.byref(r)))
+        torch.cuda.synchronize()
+
+        def view(ptr, n, dtype):
+            t = torch.empty(n, dtype=dtype, device="cuda")
+            nbytes = t.numel() * t.element_size()
+            _cudart_memcpy_d2d(t.data_ptr(), ptr, nbytes)
+            return t
+
+        S, k, E, cap = r.tokens, r.top_k, r.num_experts, r.capacity
+        return dict(topk_idx=view(r.topk_idx, S * k, torch.int32).view(S, k),
+                    topk_w=view(r.topk_w, S * k, torch.float32).view(S, k),
+                    count=view(r.count, E, torch.int32),
+                    slot_of=view(r.slot_of, S * k, torch.int32).view(S, k),
+                    token_of_slot=view(r.token_of_slot, E * cap, torch.int32), capacity=cap)
+
+    def status(self) -> None:
+        _lib.check(self._lib.aristos_moe_status(self._h))
+
+    @property
+    def launch_count(self) -> int:
+        return int(self._lib.aristos_moe_launch_count(self._h))
+
+    def close(self) -> None:
+        if self._h:
+            self._lib.aristos_moe_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def _cudart_memcpy_d2d(dst: int, src: int, nbytes: int) -> None:
+    rt = torch.cuda.cudart()
+    err = rt.cudaMemcpy(dst, src, nbytes, 3)   # cudaMemcpyDeviceToDevice
+    if int(err) != 0:
+        raise RuntimeError(f"cudaMemcpy failed: {err}")

@@ -1,0 +1,191 @@
+/*
+ * aristos_moe.h - C ABI of the B200 (sm_100a) fused distributed MoE forward layer.
+ *
+ * The reference project (osayamenja/cuPlayground) exposes its MoE prototypes as zero-argument C++ harnesses that
+ * allocate, launch and free inside one function (mma.cuh:371-443 testCollective, auditorium/combine.cuh:207-238
+ * hostCombine, auditorium/overlap.cuh:159-242 overlapPrototype, auditorium/scheduling.cuh:267-288 and
+ * warpScheduler.cuh:346-372 hostSchedule) and is configured by aristos_config.json (aristos_config.json:1-13,
+ * aristos_config.schema.json:1-71, CMakeLists.txt:167-216). This header is the callable replacement of that
+ * surface: the same configuration keys, the same tensor conventions (activations row-major (tokens, features),
+ * weights row-major (out_features, in_features), fp32 accumulation - mma.cuh:394-397, :415-427), behind plain
+ * pointers and sizes. No C++ or torch type crosses this boundary.
+ *
+ * Conventions
+ *   - every tensor pointer is a DEVICE pointer, 16-byte aligned, unless the name ends in _host;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream); calls are asynchronous
+ *     with respect to it unless stated otherwise;
+ *   - every function returns an aristos_status_t (never exits, never throws - the reference's CHECK_ERROR_EXIT,
+ *     util.cuh:24-36, calls exit(1) instead);
+ *   - there is no CPU fallback: without a usable CUDA device the compute entry points return ARISTOS_ERR_CUDA.
+ */
+#ifndef ARISTOS_MOE_H
+#define ARISTOS_MOE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define ARISTOS_API __attribute__((visibility("default")))
+#else
+#define ARISTOS_API
+#endif
+
+typedef enum aristos_status {
+    ARISTOS_OK = 0,
+    ARISTOS_ERR_INVALID_ARG = 1,    /* NULL pointer, negative size, misaligned pointer */
+    ARISTOS_ERR_CONFIG = 2,         /* configuration violates the schema or a kernel constraint */
+    ARISTOS_ERR_IO = 3,             /* configuration file unreadable */
+    ARISTOS_ERR_CUDA = 4,           /* a CUDA runtime/driver call failed (see aristos_last_error) */
+    ARISTOS_ERR_NCCL = 5,           /* NCCL missing or a NCCL call failed */
+    ARISTOS_ERR_UNSUPPORTED = 6,    /* valid request that this build does not implement */
+    ARISTOS_ERR_WORKSPACE = 7,      /* caller-provided workspace too small */
+    ARISTOS_ERR_DEVICE_TIMEOUT = 8, /* a bounded device-side wait expired (kernel returned early) */
+    ARISTOS_ERR_DEVICE_BOUNDS = 9,  /* a routing-derived index was out of range (access skipped) */
+    ARISTOS_ERR_NOMEM = 10
+} aristos_status_t;
+
+/* torch_dtype (aristos_config.schema.json:54-58) and hidden_act (:24-28), with the extension values. */
+enum { ARISTOS_DTYPE_F32 = 0, ARISTOS_DTYPE_TF32 = 1, ARISTOS_DTYPE_BF16 = 2, ARISTOS_DTYPE_F16 = 3,
+       ARISTOS_DTYPE_FP8_E4M3 = 4 /* extension */ };
+enum { ARISTOS_ACT_RELU = 0, ARISTOS_ACT_GELU = 1, ARISTOS_ACT_SWIGLU = 2 /* extension */,
+       ARISTOS_ACT_IDENTITY = 3 /* extension, second projection */ };
+enum { ARISTOS_GATE_SOFTMAX = 0, ARISTOS_GATE_SIGMOID = 1 };
+
+/*
+ * Layer description. The first eleven fields are the keys of aristos_config.json (aristos_config.json:2-12);
+ * the reference turns them into -D macros at configure time (CMakeLists.txt:167-216), here they are read at run
+ * time. The remaining fields are extension keys; a file that omits them gets the defaults shown.
+ */
+typedef struct aristos_config {
+    double capacity_factor;   /* schema: integer >= 1; extension: any real >= 0 (1.25) */
+    int drop_tokens;          /* 0: capacity = tokens (nothing is dropped); 1: capacity = ceil(cf*S*k/E) */
+    int expert_top_k;
+    int is_training;          /* read and ignored (forward only), as in the reference */
+    int hidden_act;           /* ARISTOS_ACT_* */
+    int hidden_size;          /* H, multiple of 64 */
+    int intermediate_size;    /* I, multiple of 64 */
+    int micro_batch;
+    int num_experts;          /* E, global */
+    int sequence_len;
+    int torch_dtype;          /* ARISTOS_DTYPE_* */
+    /* extension keys */
+    int tokens;               /* "tokens": S per rank; 0 = micro_batch * sequence_len */
+    int gate_fn;              /* "gate_fn": ARISTOS_GATE_*; default softmax */
+    int renorm_topk;          /* "renorm_topk": divide the k weights by their sum; default 0 */
+    double gate_bias_zipf_s;  /* "gate_bias_zipf_s": s > 0 adds -s*ln(e+1) to logit e; default 0 (off) */
+    int ep_world;             /* "ep_world": ranks the experts are sharded over; default 1 */
+    uint64_t seed;            /* "seed": only used by the synthetic-input helpers; default 0 */
+} aristos_config_t;
+
+/* Routing tensors of the last forward (device pointers owned by the layer handle, valid until destroy). */
+typedef struct aristos_routing {
+    const int32_t* topk_idx;       /* (S,k)   selected experts, by decreasing logit, ties -> lower index */
+    const float* topk_w;           /* (S,k)   combine weights */
+    const int32_t* count;          /* (E)     rows kept per expert (<= capacity) */
+    const int32_t* slot_of;        /* (S,k)   expert*capacity + position, -1 = dropped */
+    const int32_t* token_of_slot;  /* (E*cap) owning token of a slot, -1 = unused */
+    int tokens, top_k, num_experts, capacity;
+} aristos_routing_t;
+
+typedef struct aristos_moe aristos_moe_t; /* opaque layer handle */
+
+/* ---- status / errors ------------------------------------------------------------------------------------- */
+ARISTOS_API const char* aristos_status_str(aristos_status_t s);
+/* Text of the last failure on the calling thread (CUDA/NCCL error string, parser message). Never NULL. */
+ARISTOS_API const char* aristos_last_error(void);
+ARISTOS_API int aristos_version(void);
+
+/* ---- configuration: replaces CMakeLists.txt:167-216 (JSON -> -D macros) ------------------------------------ */
+ARISTOS_API aristos_status_t aristos_config_default(aristos_config_t* out); /* values of aristos_config.json:2-12 */
+ARISTOS_API aristos_status_t aristos_config_parse(const char* json_text, aristos_config_t* out);
+ARISTOS_API aristos_status_t aristos_config_load(const char* json_path, aristos_config_t* out);
+/* Schema rules (aristos_config.schema.json) plus the kernel constraints of this build. */
+ARISTOS_API aristos_status_t aristos_config_validate(const aristos_config_t* cfg);
+ARISTOS_API int aristos_config_tokens(const aristos_config_t* cfg);   /* S per rank */
+ARISTOS_API int aristos_config_capacity(const aristos_config_t* cfg); /* rows per expert per source rank */
+/* Host helper: the Zipf prior of the skewed-routing case, bias_host[e] = -s*ln(e+1) as fp32. */
+ARISTOS_API aristos_status_t aristos_zipf_bias_host(float* bias_host, int num_experts, double s);
+
+/* ---- layer: replaces the allocate/launch/sync/free harnesses (mma.cuh:371-443, overlap.cuh:159-242) -------- */
+/* nccl_unique_id: 128 bytes from aristos_nccl_unique_id on rank 0, shared by the caller; NULL when world == 1.
+ * The CUDA device current at this call becomes the layer's device. */
+ARISTOS_API aristos_status_t aristos_moe_create(const aristos_config_t* cfg, int rank, int world,
+                                                const void* nccl_unique_id, aristos_moe_t** out);
+ARISTOS_API aristos_status_t aristos_nccl_unique_id(void* out_128_bytes);
+ARISTOS_API size_t aristos_moe_workspace_bytes(const aristos_moe_t* layer);
+/* Optional: hand the layer a caller-owned device workspace (>= aristos_moe_workspace_bytes, 1024-byte aligned).
+ * Without it the first forward allocates one with cudaMalloc and keeps it until destroy. */
+ARISTOS_API aristos_status_t aristos_moe_set_workspace(aristos_moe_t* layer, void* workspace, size_t bytes);
+/*
+ * One forward of the layer on this rank.
+ *   x (S,H) activations          w_gate (E,H)        gate_bias (E) fp32 or NULL (NULL + gate_bias_zipf_s > 0 =
+ *   the layer's own Zipf prior)   w1 (E_local,I,H)    w3 (E_local,I,H), SwiGLU only, else NULL
+ *   w2 (E_local,H,I)             scales: fp8 only, else NULL          out (S,H), same dtype as x
+ * E_local = num_experts / world; rank r owns experts [r*E_local, (r+1)*E_local). Dropped tokens give zero rows.
+ */
+ARISTOS_API aristos_status_t aristos_moe_forward(aristos_moe_t* layer, const void* x, const void* w_gate,
+                                                 const float* gate_bias, const void* w1, const void* w3,
+                                                 const void* w2, const void* scales, void* out, void* stream);
+/* Same call with HOST activations: copies x_host to the device, runs the forward, copies the result into
+ * out_host and synchronises `stream` (the reference harness shape: host slab -> H2D -> kernels -> D2H,
+ * mma.cuh:392-413, auditorium/overlap.cuh:192-237). Weights stay device-resident. */
+ARISTOS_API aristos_status_t aristos_moe_forward_host(aristos_moe_t* layer, const void* x_host, const void* w_gate,
+                                                      const float* gate_bias, const void* w1, const void* w3,
+                                                      const void* w2, const void* scales, void* out_host,
+                                                      void* stream);
+ARISTOS_API aristos_status_t aristos_moe_routing(const aristos_moe_t* layer, aristos_routing_t* out);
+/* Synchronises the layer's streams and reports device-side faults of the forwards since the last call
+ * (ARISTOS_ERR_DEVICE_TIMEOUT / ARISTOS_ERR_DEVICE_BOUNDS), then clears them. */
+ARISTOS_API aristos_status_t aristos_moe_status(aristos_moe_t* layer);
+/* Kernels launched by this library for `layer` since create (the benchmark's launch count). */
+ARISTOS_API int64_t aristos_moe_launch_count(const aristos_moe_t* layer);
+ARISTOS_API aristos_status_t aristos_moe_destroy(aristos_moe_t* layer);
+
+/* ---- stage entry points (what the layer calls, exported for parity tests and for callers that fuse the
+ *      stages into their own pipeline) ------------------------------------------------------------------------ */
+/* Gate: logits = x * w_gate^T (+ gate_bias) in fp32 with a fixed reduction order, top-k on the logits (ties ->
+ * lower expert index), softmax or sigmoid weights. The reference has no gate; its expert-tile contract
+ * C = act(A*B^T + bias) with B stored (N,K) (mma.cuh:46-161) fixes the operand layout. logits_out may be NULL. */
+ARISTOS_API aristos_status_t aristos_gate_topk(const void* x, const void* w_gate, const float* gate_bias, int S,
+                                               int H, int E, int k, int gate_fn, int renorm, int dtype,
+                                               int32_t* topk_idx, float* topk_w, float* logits_out, void* stream);
+/* Dispatch bookkeeping (capacity-bounded per-expert token lists, overflow dropped in token order). Replaces the
+ * task-queue bookkeeping of auditorium/scheduling.cuh:218-252. scratch: aristos_dispatch_scratch_bytes(). */
+ARISTOS_API size_t aristos_dispatch_scratch_bytes(int S, int k, int E);
+ARISTOS_API aristos_status_t aristos_dispatch(const int32_t* topk_idx, int S, int k, int E, int cap,
+                                              int32_t* count, int32_t* slot_of, int32_t* token_of_slot,
+                                              void* scratch, size_t scratch_bytes, void* stream);
+/* Gather token rows into expert-major order: xg[slot_of[t,j]] = x[t]. xg is (E*cap, H). */
+ARISTOS_API aristos_status_t aristos_permute(const void* x, const int32_t* slot_of, int S, int k, int H, int dtype,
+                                             void* xg, void* stream);
+/*
+ * Expert FFN over `groups` row groups of `rows_per_group` rows each; group g uses expert (g % experts) and has
+ * count[g] valid rows. Only rows in [row_begin, row_end) of every group are computed (row_begin % 128 == 0).
+ *   h = act(xg * w1^T) or silu(xg * w1^T) * (xg * w3^T);   y = h * w2^T
+ * Replaces fGET / deviceCollectiveMMA (mma.cuh:46-179, :198-369), BlockMM (processor/tiling.cuh:273-323) and the
+ * in-kernel schedulers sK / wScheduler (auditorium/scheduling.cuh:202-265, warpScheduler.cuh:267-344).
+ * h_scratch: (groups*rows_per_group, I) in dtype. dev_status: one int32 the kernels OR fault bits into (may be
+ * NULL). sm_limit: CTAs of the persistent grid, 0 = all SMs.
+ */
+ARISTOS_API aristos_status_t aristos_expert_ffn(const void* xg, const int32_t* count, int groups,
+                                                int rows_per_group, int experts, const void* w1, const void* w3,
+                                                const void* w2, void* h_scratch, void* y, int H, int I,
+                                                int hidden_act, int dtype, int row_begin, int row_end,
+                                                int sm_limit, int32_t* dev_status, void* stream);
+/* Combine: out[t] = sum_j topk_w[t,j] * y[slot_of[t,j]] in increasing j (fp32), dropped assignments add
+ * nothing. Replaces Combine / VAA / deviceCombine (auditorium/combine.cuh:19-205). */
+ARISTOS_API aristos_status_t aristos_combine(const void* y, const int32_t* slot_of, const float* topk_w, int S,
+                                             int k, int H, int dtype, void* out, void* stream);
+/* Synthetic inputs: Philox4x32-10 + Box-Muller normal fill (the reference draws inputs from Philox,
+ * main.cu:22-31). Element i uses counter (i/4, 0, stream_id, 0), key = seed, output word i%4. */
+ARISTOS_API aristos_status_t aristos_fill_normal(void* dst, int64_t n, float mean, float std, uint64_t seed,
+                                                 uint32_t stream_id, int dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ARISTOS_MOE_H */

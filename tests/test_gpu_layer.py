@@ -1,0 +1,163 @@
+"""GPU parity of the whole layer (aristos_moe_forward through the C ABI) against the CPU oracle."""
+import numpy as np
+import pytest
+
+from helpers import TOL_BF16_MAX, TOL_BF16_MEAN, TOL_F32_MAX, make_inputs, rel_errors, to_dev
+
+pytestmark = pytest.mark.gpu
+
+
+def _mods():
+    import torch
+    import cuplayground_b200 as cp
+    import cuplayground_b200.layer as layer
+    return torch, cp, layer
+
+
+def _check_routing(r, ref):
+    np.testing.assert_array_equal(r["topk_idx"].cpu().numpy(), ref["topk_idx"])
+    np.testing.assert_array_equal(r["count"].cpu().numpy(), ref["count"])
+    np.testing.assert_array_equal(r["slot_of"].cpu().numpy(), ref["slot_of"])
+    np.testing.assert_array_equal(r["token_of_slot"].cpu().numpy(), ref["token_of_slot"])
+    np.testing.assert_allclose(r["topk_w"].cpu().numpy(), ref["topk_w"], rtol=2e-5, atol=1e-7)
+
+
+def _run_layer(cfg, seed, oracle, w_std=0.02, only_rows=None):
+    torch, cp, layer = _mods()
+    bf16 = cfg.torch_dtype == 2
+    dt = torch.bfloat16 if bf16 else torch.float32
+    swiglu = cfg.hidden_act == 2
+    x, wg, w1, w3, w2 = make_inputs(cfg.S, cfg.hidden_size, cfg.intermediate_size, cfg.num_experts, seed,
+                                    swiglu=swiglu, bf16=bf16, w_std=w_std)
+    L = layer.MoELayer(cfg)
+    out = L.forward(*(to_dev(a, dt) for a in (x, wg, w1, w3, w2)))
+    L.status()
+    r = L.routing()
+    bias = oracle.zipf_bias(cfg.num_experts, cfg.gate_bias_zipf_s) if cfg.gate_bias_zipf_s > 0 else None
+    ref = oracle.moe_forward(x, wg, w1, w3, w2, k=cfg.expert_top_k, cap=cfg.capacity, gate_fn=cfg.gate_fn,
+                             renorm=cfg.renorm_topk, hidden_act=cfg.hidden_act, gate_bias=bias, only_rows=only_rows)
+    got = out.float().cpu().numpy()
+    L.close()
+    return got, r, ref
+
+
+def test_config1_fp32_reference_case(oracle):
+    """S=128, H=256, I=512, E=8, top-1 softmax, cf 1.0 (cap 16), ReLU, fp32, seed 0."""
+    torch, cp, layer = _mods()
+    cfg = cp.baseline_config(1)
+    assert cfg.capacity == 16
+    got, r, ref = _run_layer(cfg, 0, oracle)
+    _check_routing(r, ref)
+    mx, _ = rel_errors(got, ref["out"])
+    assert mx < TOL_F32_MAX, mx
+    dropped = (ref["slot_of"] < 0).all(axis=1)
+    assert dropped.any() and (got[dropped] == 0).all(), "dropped tokens give zero rows"
+
+
+@pytest.mark.parametrize("S,H,I,E,k,act,cf,renorm,zipf", [
+    (512, 256, 512, 8, 2, 1, 1.25, 1, 0.0),       # GELU, renormalised top-2 (shape of the single-GPU case, scaled)
+    (640, 512, 1024, 8, 2, 2, 1.25, 0, 0.0),      # SwiGLU (Mixtral-shaped, scaled)
+    (1024, 256, 256, 32, 4, 1, 1.0, 0, 1.2),      # skewed routing with drops
+    (300, 128, 192, 4, 1, 0, 0.5, 0, 0.0),        # ragged token count, heavy drops, ReLU
+])
+def test_layer_bf16_small(oracle, S, H, I, E, k, act, cf, renorm, zipf):
+    torch, cp, layer = _mods()
+    cfg = cp.AristosConfig(capacity_factor=cf, drop_tokens=1, expert_top_k=k, hidden_act=act, hidden_size=H,
+                           intermediate_size=I, num_experts=E, torch_dtype=2, tokens=S, renorm_topk=renorm,
+                           gate_bias_zipf_s=zipf)
+    got, r, ref = _run_layer(cfg, 7, oracle, w_std=0.05)
+    _check_routing(r, ref)
+    mx, mean = rel_errors(got, ref["out"])
+    assert mx < TOL_BF16_MAX and mean < TOL_BF16_MEAN, (mx, mean)
+    dropped = (ref["slot_of"] < 0).all(axis=1)
+    assert (got[dropped] == 0).all()
+
+
+def test_layer_no_drop(oracle):
+    torch, cp, layer = _mods()
+    cfg = cp.AristosConfig(drop_tokens=0, expert_top_k=2, hidden_act=2, hidden_size=128, intermediate_size=256,
+                           num_experts=8, torch_dtype=2, tokens=256)
+    assert cfg.capacity == 256
+    got, r, ref = _run_layer(cfg, 3, oracle, w_std=0.05)
+    _check_routing(r, ref)
+    assert (ref["slot_of"] >= 0).all()
+    mx, mean = rel_errors(got, ref["out"])
+    assert mx < TOL_BF16_MAX and mean < TOL_BF16_MEAN, (mx, mean)
+
+
+def _full_size(n, seed, oracle, n_sample):
+    """Full-size configuration generated on the device; routing checked on every token, outputs on a sample."""
+    torch, cp, layer = _mods()
+    cfg = cp.baseline_config(n)
+    S, H, I, E = cfg.S, cfg.hidden_size, cfg.intermediate_size, cfg.num_experts
+    dt = torch.bfloat16
+    mk = lambda shape, std, sid: layer.fill_normal(torch.empty(shape, dtype=dt, device="cuda"), 0.0, std, seed, sid)
+    x, wg = mk((S, H), 1.0, 0), mk((E, H), 0.02, 1)
+    w1, w2 = mk((E, I, H), 0.02, 2), mk((E, H, I), 0.02, 4)
+    w3 = mk((E, I, H), 0.02, 3) if cfg.hidden_act == 2 else None
+    L = layer.MoELayer(cfg)
+    out = L.forward(x, wg, w1, w3, w2)
+    L.status()
+    out2 = L.forward(x, wg, w1, w3, w2)
+    L.status()
+    assert torch.equal(out, out2), "the forward is deterministic"
+    r = L.routing()
+    rows = np.random.default_rng(n).choice(S, size=n_sample, replace=False).astype(np.int32)
+    host = lambda t: None if t is None else t.float().cpu().numpy()
+    bias = oracle.zipf_bias(E, cfg.gate_bias_zipf_s) if cfg.gate_bias_zipf_s > 0 else None
+    ref = oracle.moe_forward(host(x), host(wg), host(w1), host(w3), host(w2), k=cfg.expert_top_k, cap=cfg.capacity,
+                             gate_fn=cfg.gate_fn, renorm=cfg.renorm_topk, hidden_act=cfg.hidden_act, gate_bias=bias,
+                             only_rows=rows)
+    _check_routing(r, ref)
+    got = out[torch.from_numpy(rows.astype(np.int64)).cuda()].float().cpu().numpy()
+    mx, mean = rel_errors(got, ref["out"])
+    assert mx < TOL_BF16_MAX and mean < TOL_BF16_MEAN, (mx, mean)
+    # size-independent properties: kept rows per expert never exceed the capacity; every slot maps back to a token
+    # that selected that expert; tokens whose assignments were all dropped give zero rows
+    count = r["count"].cpu().numpy()
+    assert (count <= cfg.capacity).all() and count.sum() == (ref["slot_of"] >= 0).sum()
+    all_dropped = torch.from_numpy((ref["slot_of"] < 0).all(axis=1)).cuda()
+    assert not out[all_dropped].any()
+    L.close()
+    return ref
+
+
+def test_config2_full_size(oracle):
+    """S=8192, H=2048, I=2048, E=64, top-2 renormalised softmax, GELU, cf 1.25, bf16, seed 1."""
+    _full_size(2, 1, oracle, n_sample=256)
+
+
+def test_config5_full_size_skewed(oracle):
+    """S=8192, H=2048, I=1024, E=128, top-4, Zipf(1.2) prior, cf 1.0 with drops, GELU, bf16, seed 4."""
+    ref = _full_size(5, 4, oracle, n_sample=256)
+    assert (ref["slot_of"] < 0).sum() > 0, "the skewed case must overflow some experts"
+
+
+def test_config3_full_size_mixtral_shaped(oracle):
+    """S=16384, H=4096, I=14336, E=8, top-2 softmax, SwiGLU, cf 1.25, bf16, seed 2 (one rank holds all experts)."""
+    _full_size(3, 2, oracle, n_sample=64)
+
+
+def test_forward_host_matches_device_forward(oracle):
+    torch, cp, layer = _mods()
+    cfg = cp.AristosConfig(capacity_factor=1.25, drop_tokens=1, expert_top_k=2, hidden_act=1, hidden_size=256,
+                           intermediate_size=512, num_experts=8, torch_dtype=2, tokens=512)
+    x, wg, w1, w3, w2 = make_inputs(512, 256, 512, 8, 5)
+    dt = torch.bfloat16
+    dev = [to_dev(a, dt) for a in (x, wg, w1, w3, w2)]
+    L = layer.MoELayer(cfg)
+    out = L.forward(*dev)
+    xh = torch.from_numpy(x).to(dt).pin_memory()
+    oh = torch.empty_like(xh).pin_memory()
+    L.forward_host(xh, dev[1], dev[2], dev[3], dev[4], oh)
+    L.status()
+    assert torch.equal(oh, out.cpu())
+    L.close()
+
+
+def test_unsupported_dtype_fails_loudly():
+    torch, cp, layer = _mods()
+    cfg = cp.AristosConfig(hidden_size=128, intermediate_size=128, num_experts=4, torch_dtype=3, tokens=128)
+    with pytest.raises(cp.AristosError) as e:
+        layer.MoELayer(cfg)
+    assert e.value.status == 6
