@@ -64,6 +64,7 @@ PROTOTYPES = {
     "aristos_moe_forward": (_st, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "aristos_moe_forward_host": (_st, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "aristos_moe_routing": (_st, [_vp, C.POINTER(AristosRoutingStruct)]),
+    "aristos_moe_routing_to_host": (_st, [_vp, _vp, _vp, _vp, _vp, _vp]),
     "aristos_moe_status": (_st, [_vp]),
     "aristos_moe_launch_count": (C.c_int64, [_vp]),
     "aristos_moe_destroy": (_st, [_vp]),

@@ -155,7 +155,7 @@ namespace aristos {
 aristos_status_t dispatch_impl(const int32_t* topk_idx, int S, int k, int E, int cap, int32_t* count,
                                int32_t* slot_of, int32_t* token_of_slot, void* scratch, size_t scratch_bytes,
                                int32_t* dev_status, cudaStream_t st) {
-    if (!topk_idx || !count || !slot_of || !token_of_slot || !scratch) {
+    if ((!topk_idx && S > 0) || (!slot_of && S > 0) || !count || !token_of_slot || !scratch) {
         set_last_error("dispatch: NULL pointer");
         return ARISTOS_ERR_INVALID_ARG;
     }

@@ -288,6 +288,22 @@ aristos_status_t aristos_moe_routing(const aristos_moe_t* L, aristos_routing_t* 
     return ARISTOS_OK;
 }
 
+aristos_status_t aristos_moe_routing_to_host(const aristos_moe_t* L, int32_t* topk_idx_host, float* topk_w_host,
+                                             int32_t* count_host, int32_t* slot_of_host,
+                                             int32_t* token_of_slot_host) {
+    if (!L) return ARISTOS_ERR_INVALID_ARG;
+    if (!L->ws) { set_last_error("routing: no forward has run yet"); return ARISTOS_ERR_INVALID_ARG; }
+    ARISTOS_CUDA_TRY(cudaDeviceSynchronize());
+    const size_t sk = (size_t)L->S * L->k;
+    if (topk_idx_host) ARISTOS_CUDA_TRY(cudaMemcpy(topk_idx_host, L->topk_idx, sk * 4, cudaMemcpyDeviceToHost));
+    if (topk_w_host) ARISTOS_CUDA_TRY(cudaMemcpy(topk_w_host, L->topk_w, sk * 4, cudaMemcpyDeviceToHost));
+    if (count_host) ARISTOS_CUDA_TRY(cudaMemcpy(count_host, L->count, (size_t)L->E * 4, cudaMemcpyDeviceToHost));
+    if (slot_of_host) ARISTOS_CUDA_TRY(cudaMemcpy(slot_of_host, L->slot_of, sk * 4, cudaMemcpyDeviceToHost));
+    if (token_of_slot_host)
+        ARISTOS_CUDA_TRY(cudaMemcpy(token_of_slot_host, L->token_of_slot, (size_t)L->E * L->cap * 4, cudaMemcpyDeviceToHost));
+    return ARISTOS_OK;
+}
+
 aristos_status_t aristos_moe_status(aristos_moe_t* L) {
     if (!L) return ARISTOS_ERR_INVALID_ARG;
     ARISTOS_CUDA_TRY(cudaDeviceSynchronize());

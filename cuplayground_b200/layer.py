@@ -153,23 +153,16 @@ class MoELayer:
         return out_host
 
     def routing(self) -> dict:
-        """Copies of the routing tensors of the last forward (torch tensors on the device)."""
-        r = _lib.AristosRoutingStruct()
-        _lib.check(self._lib.aristos_moe_routing(self._h, C.byref(r)))
-        torch.cuda.synchronize()
-
-        def view(ptr, n, dtype):
-            t = torch.empty(n, dtype=dtype, device="cuda")
-            nbytes = t.numel() * t.element_size()
-            _cudart_memcpy_d2d(t.data_ptr(), ptr, nbytes)
-            return t
-
-        S, k, E, cap = r.tokens, r.top_k, r.num_experts, r.capacity
-        return dict(topk_idx=view(r.topk_idx, S * k, torch.int32).view(S, k),
-                    topk_w=view(r.topk_w, S * k, torch.float32).view(S, k),
-                    count=view(r.count, E, torch.int32),
-                    slot_of=view(r.slot_of, S * k, torch.int32).view(S, k),
-                    token_of_slot=view(r.token_of_slot, E * cap, torch.int32), capacity=cap)
+        """Host copies (CPU torch tensors) of the routing tensors of the last forward."""
+        S, k, E, cap = self.S, self.k, self.E, self.cap
+        idx = torch.empty((S, k), dtype=torch.int32)
+        w = torch.empty((S, k), dtype=torch.float32)
+        count = torch.empty(E, dtype=torch.int32)
+        slot_of = torch.empty((S, k), dtype=torch.int32)
+        tos = torch.empty(E * cap, dtype=torch.int32)
+        _lib.check(self._lib.aristos_moe_routing_to_host(self._h, _ptr(idx), _ptr(w), _ptr(count), _ptr(slot_of),
+                                                         _ptr(tos)))
+        return dict(topk_idx=idx, topk_w=w, count=count, slot_of=slot_of, token_of_slot=tos, capacity=cap)
 
     def status(self) -> None:
         _lib.check(self._lib.aristos_moe_status(self._h))
@@ -188,10 +181,3 @@ class MoELayer:
             self.close()
         except Exception:
             pass
-
-
-def _cudart_memcpy_d2d(dst: int, src: int, nbytes: int) -> None:
-    rt = torch.cuda.cudart()
-    err = rt.cudaMemcpy(dst, src, nbytes, 3)   # cudaMemcpyDeviceToDevice
-    if int(err) != 0:
-        raise RuntimeError(f"cudaMemcpy failed: {err}")

@@ -138,6 +138,11 @@ ARISTOS_API aristos_status_t aristos_moe_forward_host(aristos_moe_t* layer, cons
                                                       const void* w2, const void* scales, void* out_host,
                                                       void* stream);
 ARISTOS_API aristos_status_t aristos_moe_routing(const aristos_moe_t* layer, aristos_routing_t* out);
+/* Copies the routing tensors of the last forward into host buffers sized as in aristos_routing_t (any pointer may
+ * be NULL); synchronises the device first. */
+ARISTOS_API aristos_status_t aristos_moe_routing_to_host(const aristos_moe_t* layer, int32_t* topk_idx_host,
+                                                         float* topk_w_host, int32_t* count_host,
+                                                         int32_t* slot_of_host, int32_t* token_of_slot_host);
 /* Synchronises the layer's streams and reports device-side faults of the forwards since the last call
  * (ARISTOS_ERR_DEVICE_TIMEOUT / ARISTOS_ERR_DEVICE_BOUNDS), then clears them. */
 ARISTOS_API aristos_status_t aristos_moe_status(aristos_moe_t* layer);
