@@ -1,0 +1,339 @@
+#!/usr/bin/env python
+"""Benchmark of the fused MoE forward: tokens/s at 1/2/4/8 B200, max over ranks.
+
+    python bench.py --gpus 1 --steps 10 --warmup 3                      # this library (default workload: config 3)
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N --steps K --warmup W
+    python bench.py --impl reference ...                                # the CPU restatement on the host cores
+
+One "step" is one forward of the layer over one batch of synthetic tokens (weights stay resident). The timed region
+is bracketed by a barrier and a device synchronisation and timed with CUDA events on the launching stream; the
+reported time is the maximum over ranks. Prints ONE JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    "config2": (2, "single-B200: S=8192 H=2048 I=2048 E=64 top-2 renorm softmax GELU cf=1.25 bf16 seed 1"),
+    "config3": (3, "Mixtral-shaped: H=4096 I=14336 SwiGLU E=8 top-2 softmax cf=1.25 bf16, 16384 tokens per rank, "
+                   "experts sharded over the ranks, seed 2"),
+    # one quarter of config3 (2 of its 8 experts, a quarter of the tokens: the same 5120 rows per expert), small
+    # enough for a multi-pass profiler capture
+    "config3-profile": (3, "Mixtral-shaped, reduced for profiling: H=4096 I=14336 SwiGLU E=2 top-2 cf=1.25 bf16, "
+                           "4096 tokens"),
+    "config5": (5, "skewed routing: H=2048 I=1024 GELU E=128 top-4 Zipf(1.2) prior cf=1.0 bf16, 8192 tokens per "
+                   "rank, seed 4"),
+}
+
+
+def read_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return dict(hbm_gbs=p["hbm_gbs"], bf16_burst=p["bf16_tflops"], bf16_sustained=p["bf16_tflops_sustained"],
+                    source="measured")
+    return dict(hbm_gbs=6650.0, bf16_burst=1590.0, bf16_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clock, power and throttle reasons of one GPU every 10 ms during the timed region through NVML
+    (read-only queries; nothing is set)."""
+    REASONS = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20, "sw_power_cap": 0x4}
+
+    def __init__(self, index: int):
+        import threading
+        self.samples = []
+        self.error = None
+        self._stop = threading.Event()
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.sm_max = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception as e:      # NVML missing: report it, do not fail the benchmark
+            self.error = repr(e)
+            self.thread = None
+            return
+        self.thread = threading.Thread(target=self._run, daemon=True)
+        self.thread.start()
+
+    def _run(self):
+        nv = self.nv
+        while not self._stop.is_set():
+            try:
+                sm = nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)
+                pw = nv.nvmlDeviceGetPowerUsage(self.h) / 1000.0
+                rs = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                self.samples.append((sm, pw, rs))
+            except Exception as e:
+                self.error = repr(e)
+                return
+            time.sleep(0.01)
+
+    def stop(self) -> dict:
+        if self.thread is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [f"NVML unavailable: {self.error}"]}
+        self._stop.set()
+        self.thread.join(timeout=2)
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.sm_max, "reasons": ["no samples"]}
+        bits = 0
+        for _, _, rs in self.samples:
+            bits |= rs
+        return {"sm_mhz": statistics.median(s[0] for s in self.samples), "sm_max_mhz": self.sm_max,
+                "sm_min_mhz": min(s[0] for s in self.samples), "power_w_max": max(s[1] for s in self.samples),
+                "samples": len(self.samples),
+                "reasons": sorted(n for n, b in self.REASONS.items() if bits & b)}
+
+
+def layer_flops(cfg, kept_assignments: int) -> float:
+    m = 3 if cfg.hidden_act == 2 else 2
+    return 2.0 * kept_assignments * cfg.hidden_size * cfg.intermediate_size * m + \
+        2.0 * cfg.S * cfg.hidden_size * cfg.num_experts
+
+
+def layer_roofline(cfg, world, kept, elt=2):
+    """The layer roofline of the build spec: the slowest of FLOPs at the dense tensor peak, minimum HBM bytes at
+    8 TB/s and all-to-all bytes at 900 GB/s per direction (dispatch and return summed). Seconds per rank."""
+    m = 3 if cfg.hidden_act == 2 else 2
+    H, I, E, S = cfg.hidden_size, cfg.intermediate_size, cfg.num_experts, cfg.S
+    t_tc = layer_flops(cfg, kept) / 2250e12
+    hbm = (E // world) * m * H * I * elt + S * H * elt + S * H * elt + E * H * elt
+    t_hbm = hbm / 8e12
+    t_a2a = 2.0 * kept * (world - 1) / world * H * elt / 900e9 if world > 1 else 0.0
+    return max(t_tc, t_hbm, t_a2a), dict(t_tensor_ms=t_tc * 1e3, t_hbm_ms=t_hbm * 1e3, t_a2a_ms=t_a2a * 1e3)
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+def cpu_sample_forward(oracle, cfg, tensors, n_tokens):
+    """One oracle forward over the first n_tokens tokens (capacity scaled to the sample). Returns seconds."""
+    x, wg, w1, w3, w2, bias = tensors
+    cap = oracle.capacity(n_tokens, cfg.num_experts, cfg.expert_top_k, cfg.capacity_factor, cfg.drop_tokens)
+    t0 = time.perf_counter()
+    oracle.moe_forward(x[:n_tokens], wg, w1, w3, w2, k=cfg.expert_top_k, cap=cap, gate_fn=cfg.gate_fn,
+                       renorm=cfg.renorm_topk, hidden_act=cfg.hidden_act, gate_bias=bias)
+    return time.perf_counter() - t0
+
+
+def cpu_calibrate(oracle, cfg, tensors, target_s):
+    """Pick a sample size that takes about target_s seconds on this host."""
+    n0 = min(64, cfg.S)
+    t = cpu_sample_forward(oracle, cfg, tensors, n0)
+    rate = n0 / max(t, 1e-6)
+    n = int(max(64, min(cfg.S, rate * target_s)))
+    return max(64, n // 64 * 64)
+
+
+def host_tensors_from_oracle(oracle, cfg, n_tokens):
+    import numpy as np
+    H, I, E = cfg.hidden_size, cfg.intermediate_size, cfg.num_experts
+    seed = cfg.seed
+    rb = oracle.round_bf16
+    x = rb(oracle.fill_normal(n_tokens * H, 0.0, 1.0, seed, 0)).reshape(n_tokens, H)
+    wg = rb(oracle.fill_normal(E * H, 0.0, 0.02, seed, 1)).reshape(E, H)
+    w1 = rb(oracle.fill_normal(E * I * H, 0.0, 0.02, seed, 2)).reshape(E, I, H)
+    w3 = rb(oracle.fill_normal(E * I * H, 0.0, 0.02, seed, 3)).reshape(E, I, H) if cfg.hidden_act == 2 else None
+    w2 = rb(oracle.fill_normal(E * H * I, 0.0, 0.02, seed, 4)).reshape(E, H, I)
+    bias = oracle.zipf_bias(E, cfg.gate_bias_zipf_s) if cfg.gate_bias_zipf_s > 0 else None
+    return x, wg, w1, w3, w2, bias
+
+
+def run_reference(args, cfg, workload_desc):
+    """The CPU implementation of the path (the oracle: the reference tree has no runnable CPU or GPU MoE forward)
+    on all host cores; each step is a bounded sample of the workload."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import moe_oracle as oracle
+    oracle.build()
+    n_probe = min(cfg.S, 4096)
+    tensors = host_tensors_from_oracle(oracle, cfg, n_probe)
+    n = min(n_probe, cpu_calibrate(oracle, cfg, tensors, target_s=4.0))
+    for _ in range(args.warmup):
+        cpu_sample_forward(oracle, cfg, tensors, n)
+    t = 0.0
+    for _ in range(args.steps):
+        t += cpu_sample_forward(oracle, cfg, tensors, n)
+    value = n * args.steps / t
+    cores = oracle.num_threads()
+    sample = f"first {n} tokens of the workload per step (capacity scaled to the sample), fp32, OpenMP"
+    line = {"impl": "reference", "metric": "moe_fwd_tokens_per_s", "value": value, "unit": "tokens/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": t / args.steps * 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": workload_desc, "name": args.workload, "tokens_per_step": n},
+            "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+def run_ours(args, cfg, workload_desc):
+    import torch
+    import torch.distributed as dist
+    import cuplayground_b200.layer as layer
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU fallback "
+                         "(use --impl reference for the CPU baseline)")
+    torch.cuda.set_device(local_rank)
+    uid = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        box = [layer.nccl_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        uid = box[0]
+
+    S, H, I, E = cfg.S, cfg.hidden_size, cfg.intermediate_size, cfg.num_experts
+    El = E // world
+    dt = torch.bfloat16
+    x, wg, w1, w3, w2 = layer.synthetic_tensors(cfg, rank, world)
+    L = layer.MoELayer(cfg, rank, world, uid)
+    out = torch.empty_like(x)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    # ---- device-resident throughput ---------------------------------------------------------------------------------
+    L.set_profiling(True)
+    for _ in range(args.warmup):
+        L.forward(x, wg, w1, w3, w2, out=out)
+    L.status()
+    kept = int(L.routing()["count"].sum())
+    barrier()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    launches0 = L.launch_count
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    stage_acc = dict(gate=0.0, dispatch=0.0, ffn=0.0, combine=0.0, total=0.0)
+    ev0.record()
+    for _ in range(args.steps):
+        L.forward(x, wg, w1, w3, w2, out=out)
+    ev1.record()
+    barrier()
+    clocks = sampler.stop() if sampler else None
+    launches = L.launch_count - launches0
+    L.status()
+    ms = ev0.elapsed_time(ev1)
+    # stage times of the last timed step (events recorded inside the same timed region)
+    stage = L.stage_ms()
+    t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+    kept_t = torch.tensor([kept], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(kept_t, op=dist.ReduceOp.SUM)
+    ms = float(t.item())
+    kept_all = float(kept_t.item())
+    value = S * world * args.steps / (ms * 1e-3)
+
+    # ---- end to end: host activations in, host result out, through aristos_moe_forward_host ---------------------------
+    L.set_profiling(False)
+    xh = x.cpu().pin_memory()
+    oh = torch.empty_like(xh).pin_memory()
+    L.forward_host(xh, wg, w1, w3, w2, oh)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2e_steps = max(3, min(args.steps, 10))
+    e0.record()
+    for _ in range(e2e_steps):
+        L.forward_host(xh, wg, w1, w3, w2, oh)
+    e1.record()
+    barrier()
+    te = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(te, op=dist.ReduceOp.MAX)
+    e2e_value = S * world * e2e_steps / (float(te.item()) * 1e-3)
+    L.status()
+
+    if rank == 0:
+        peaks = read_peaks()
+        # dominant kernel: the grouped expert GEMM (two launches per forward, up- and down-projection)
+        m = 3 if cfg.hidden_act == 2 else 2
+        ffn_flops = 2.0 * kept * H * I * m            # this rank's experts' rows (equal across ranks in expectation)
+        if world > 1:
+            ffn_flops = 2.0 * (kept_all / world) * H * I * m
+        ffn_s = stage["ffn"] * 1e-3
+        achieved = ffn_flops / ffn_s / 1e12
+        roofline = {"bound": "tensor", "kernel": "ffn_grouped_gemm_kernel", "achieved": achieved,
+                    "peak": peaks["bf16_sustained"], "unit": "TFLOP/s", "frac": achieved / peaks["bf16_sustained"],
+                    "traffic": None, "peak_source": f"{peaks['source']} bf16 sustained (kernel timed inside a "
+                    "back-to-back loop of steps)", "launches_per_step": int(launches) // args.steps - 6,
+                    "flops_per_step": ffn_flops, "ms_per_step": stage["ffn"]}
+        t_roof, terms = layer_roofline(cfg, world, kept_all / world)
+        line = {"metric": "moe_fwd_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+                "data": "synthetic",
+                "config": {"workload": workload_desc, "name": args.workload, "tokens_per_rank": S,
+                           "parallelism": f"ep{world}", "l2": "weights (>= 0.4 GB per rank) exceed the 126 MB L2, "
+                           "no flush needed between steps", "kept_assignments": kept_all},
+                "clocks": clocks,
+                "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": xh.numel() * 2 * world,
+                        "d2h_bytes_per_step": oh.numel() * 2 * world, "steps": e2e_steps,
+                        "api": "aristos_moe_forward_host (pinned host activations in, host result out)"},
+                "gpu_launches": int(launches),
+                "roofline": roofline,
+                "layer_roofline": {"seconds": t_roof, **terms, "frac": t_roof / (ms / args.steps * 1e-3),
+                                   "constants": "2250 TFLOP/s dense bf16, 8 TB/s HBM, 900 GB/s NVLink per direction"},
+                "stage_ms": stage}
+        if world == 1 and not args.no_cpu_baseline:
+            from oracle import moe_oracle as oracle
+            oracle.build()
+            host = lambda a: None if a is None else a.float().cpu().numpy()
+            n_probe = min(S, 4096)
+            bias = oracle.zipf_bias(E, cfg.gate_bias_zipf_s) if cfg.gate_bias_zipf_s > 0 else None
+            tensors = (host(x[:n_probe]), host(wg), host(w1), host(w3), host(w2), bias)
+            n = min(n_probe, cpu_calibrate(oracle, cfg, tensors, target_s=12.0))
+            tc = cpu_sample_forward(oracle, cfg, tensors, n)
+            line["cpu_baseline"] = {"value": n / tc, "unit": "tokens/s", "cores": oracle.num_threads(),
+                                    "kind": "port", "sample": f"first {n} tokens of the same workload, one forward "
+                                    f"({tc:.1f} s), capacity scaled to the sample, fp32 OpenMP oracle"}
+        print(json.dumps(line), flush=True)
+    L.close()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS), default="config3")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "ours":
+        args.warmup = 3     # timing rule: at least three warm-up steps
+    import cuplayground_b200 as cp
+    n, desc = WORKLOADS[args.workload]
+    cfg = cp.baseline_config(n, world=args.gpus if args.impl == "ours" else 1)
+    if args.workload == "config3-profile":
+        cfg.num_experts, cfg.tokens = 2, 4096
+    if args.impl == "reference":
+        run_reference(args, cfg, desc)
+    else:
+        run_ours(args, cfg, desc)
+
+
+if __name__ == "__main__":
+    main()

@@ -66,6 +66,8 @@ PROTOTYPES = {
     "aristos_moe_routing": (_st, [_vp, C.POINTER(AristosRoutingStruct)]),
     "aristos_moe_routing_to_host": (_st, [_vp, _vp, _vp, _vp, _vp, _vp]),
     "aristos_moe_status": (_st, [_vp]),
+    "aristos_moe_set_profiling": (_st, [_vp, _i]),
+    "aristos_moe_stage_ms": (_st, [_vp, C.POINTER(C.c_float)]),
     "aristos_moe_launch_count": (C.c_int64, [_vp]),
     "aristos_moe_destroy": (_st, [_vp]),
     "aristos_gate_topk": (_st, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),

@@ -47,6 +47,9 @@ struct aristos_moe {
     std::vector<cudaEvent_t> ev_in, ev_out;
     int chunks = 1, chunk_rows = 0, ffn_sm_limit = 0;
     int64_t launches = 0;
+    // stage stopwatch
+    bool profiling = false, profiled = false;
+    cudaEvent_t ev_prof[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
 };
 
 namespace {
@@ -217,11 +220,15 @@ aristos_status_t aristos_moe_forward(aristos_moe_t* L, const void* x, const void
         bias = L->gate_bias;
     }
 
+#define PROF_MARK(i) do { if (L->profiling) ARISTOS_CUDA_TRY(cudaEventRecord(L->ev_prof[i], st)); } while (0)
+    PROF_MARK(0);
     ARISTOS_TRY(aristos_gate_topk(x, w_gate, bias, L->S, L->H, L->E, L->k, L->cfg.gate_fn, L->cfg.renorm_topk, dt,
                                   L->topk_idx, L->topk_w, nullptr, st));
+    PROF_MARK(1);
     ARISTOS_TRY(dispatch_impl(L->topk_idx, L->S, L->k, L->E, L->cap, L->count, L->slot_of, L->token_of_slot,
                               L->dispatch_scratch, L->dispatch_scratch_bytes, L->dev_status, st));
     ARISTOS_TRY(aristos_permute(x, L->slot_of, L->S, L->k, L->H, dt, L->xg, st));
+    PROF_MARK(2);
 
     if (L->world == 1) {
         ARISTOS_TRY(aristos_expert_ffn(L->xg, L->count, L->E, L->cap, L->E, w1, w3, w2, L->h, L->yr, L->H, L->I,
@@ -254,7 +261,11 @@ aristos_status_t aristos_moe_forward(aristos_moe_t* L, const void* x, const void
         ARISTOS_CUDA_TRY(cudaEventRecord(L->ev_returned, L->comm_stream));
         ARISTOS_CUDA_TRY(cudaStreamWaitEvent(st, L->ev_returned, 0));
     }
+    PROF_MARK(3);
     ARISTOS_TRY(aristos_combine(L->yg, L->slot_of, L->topk_w, L->S, L->k, L->H, dt, out, st));
+    PROF_MARK(4);
+#undef PROF_MARK
+    L->profiled = L->profiling;
     L->launches += launch_counter() - launches0;
     return ARISTOS_OK;
 }
@@ -316,6 +327,24 @@ aristos_status_t aristos_moe_status(aristos_moe_t* L) {
     return ARISTOS_OK;
 }
 
+aristos_status_t aristos_moe_set_profiling(aristos_moe_t* L, int enable) {
+    if (!L) return ARISTOS_ERR_INVALID_ARG;
+    if (enable && !L->ev_prof[0])
+        for (int i = 0; i < 5; ++i) ARISTOS_CUDA_TRY(cudaEventCreate(&L->ev_prof[i]));
+    L->profiling = enable != 0;
+    L->profiled = false;
+    return ARISTOS_OK;
+}
+
+aristos_status_t aristos_moe_stage_ms(aristos_moe_t* L, float out_ms[5]) {
+    if (!L || !out_ms) return ARISTOS_ERR_INVALID_ARG;
+    if (!L->profiled) { set_last_error("stage_ms: no forward has run with profiling on"); return ARISTOS_ERR_INVALID_ARG; }
+    ARISTOS_CUDA_TRY(cudaEventSynchronize(L->ev_prof[4]));
+    for (int i = 0; i < 4; ++i) ARISTOS_CUDA_TRY(cudaEventElapsedTime(&out_ms[i], L->ev_prof[i], L->ev_prof[i + 1]));
+    ARISTOS_CUDA_TRY(cudaEventElapsedTime(&out_ms[4], L->ev_prof[0], L->ev_prof[4]));
+    return ARISTOS_OK;
+}
+
 int64_t aristos_moe_launch_count(const aristos_moe_t* L) { return L ? L->launches : 0; }
 
 aristos_status_t aristos_moe_destroy(aristos_moe_t* L) {
@@ -323,6 +352,7 @@ aristos_status_t aristos_moe_destroy(aristos_moe_t* L) {
     cudaDeviceSynchronize();
     for (cudaEvent_t e : L->ev_in) if (e) cudaEventDestroy(e);
     for (cudaEvent_t e : L->ev_out) if (e) cudaEventDestroy(e);
+    for (cudaEvent_t e : L->ev_prof) if (e) cudaEventDestroy(e);
     if (L->ev_dispatched) cudaEventDestroy(L->ev_dispatched);
     if (L->ev_returned) cudaEventDestroy(L->ev_returned);
     if (L->comm_stream) cudaStreamDestroy(L->comm_stream);

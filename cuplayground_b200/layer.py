@@ -47,6 +47,27 @@ def fill_normal(t: torch.Tensor, mean: float, std: float, seed: int, stream_id: 
     return t
 
 
+def synthetic_tensors(cfg: AristosConfig, rank: int = 0, world: int = 1):
+    """Seeded synthetic inputs of one rank, generated on the device: x ~ N(0,1) (a different stream per rank),
+    gate weights and this rank's expert weights ~ N(0, 0.02). Expert e draws from its own Philox streams, so the
+    shards of every world size are slices of the same global weights. Returns (x, w_gate, w1, w3, w2)."""
+    dt = _TORCH_DTYPE[cfg.torch_dtype]
+    S, H, I, E = cfg.S, cfg.hidden_size, cfg.intermediate_size, cfg.num_experts
+    El = E // world
+    new = lambda *shape: torch.empty(shape, dtype=dt, device="cuda")
+    x = fill_normal(new(S, H), 0.0, 1.0, cfg.seed, 0 if rank == 0 else 0x1000 + rank)
+    wg = fill_normal(new(E, H), 0.0, 0.02, cfg.seed, 1)
+    w1, w2 = new(El, I, H), new(El, H, I)
+    w3 = new(El, I, H) if cfg.hidden_act == _lib.ACT_SWIGLU else None
+    for el in range(El):
+        e = rank * El + el
+        fill_normal(w1[el], 0.0, 0.02, cfg.seed, 16 * (e + 1) + 2)
+        if w3 is not None:
+            fill_normal(w3[el], 0.0, 0.02, cfg.seed, 16 * (e + 1) + 3)
+        fill_normal(w2[el], 0.0, 0.02, cfg.seed, 16 * (e + 1) + 4)
+    return x, wg, w1, w3, w2
+
+
 # ---- stage entry points ---------------------------------------------------------------------------------------------
 def gate_topk(x, w_gate, k: int, gate_fn: int = 0, renorm: int = 0, gate_bias=None, want_logits: bool = False):
     S, H = x.shape
@@ -163,6 +184,15 @@ class MoELayer:
         _lib.check(self._lib.aristos_moe_routing_to_host(self._h, _ptr(idx), _ptr(w), _ptr(count), _ptr(slot_of),
                                                          _ptr(tos)))
         return dict(topk_idx=idx, topk_w=w, count=count, slot_of=slot_of, token_of_slot=tos, capacity=cap)
+
+    def set_profiling(self, enable: bool) -> None:
+        _lib.check(self._lib.aristos_moe_set_profiling(self._h, int(enable)))
+
+    def stage_ms(self) -> dict:
+        """Milliseconds of the stages of the last forward (profiling must be on)."""
+        ms = (C.c_float * 5)()
+        _lib.check(self._lib.aristos_moe_stage_ms(self._h, ms))
+        return dict(gate=ms[0], dispatch=ms[1], ffn=ms[2], combine=ms[3], total=ms[4])
 
     def status(self) -> None:
         _lib.check(self._lib.aristos_moe_status(self._h))
