@@ -48,8 +48,10 @@ struct aristos_moe {
     int chunks = 1, chunk_rows = 0, ffn_sm_limit = 0;
     int64_t launches = 0;
     // stage stopwatch
-    bool profiling = false, profiled = false;
-    cudaEvent_t ev_prof[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
+    static constexpr int PROF_SETS = 64;      // ring of event sets: stage times average over the last 64 forwards
+    bool profiling = false;
+    int64_t prof_n = 0;
+    std::vector<cudaEvent_t> ev_prof;         // [PROF_SETS][5]
 };
 
 namespace {
@@ -220,7 +222,8 @@ aristos_status_t aristos_moe_forward(aristos_moe_t* L, const void* x, const void
         bias = L->gate_bias;
     }
 
-#define PROF_MARK(i) do { if (L->profiling) ARISTOS_CUDA_TRY(cudaEventRecord(L->ev_prof[i], st)); } while (0)
+    const int prof_set = (int)(L->prof_n % aristos_moe::PROF_SETS) * 5;
+#define PROF_MARK(i) do { if (L->profiling) ARISTOS_CUDA_TRY(cudaEventRecord(L->ev_prof[prof_set + i], st)); } while (0)
     PROF_MARK(0);
     ARISTOS_TRY(aristos_gate_topk(x, w_gate, bias, L->S, L->H, L->E, L->k, L->cfg.gate_fn, L->cfg.renorm_topk, dt,
                                   L->topk_idx, L->topk_w, nullptr, st));
@@ -265,7 +268,7 @@ aristos_status_t aristos_moe_forward(aristos_moe_t* L, const void* x, const void
     ARISTOS_TRY(aristos_combine(L->yg, L->slot_of, L->topk_w, L->S, L->k, L->H, dt, out, st));
     PROF_MARK(4);
 #undef PROF_MARK
-    L->profiled = L->profiling;
+    if (L->profiling) L->prof_n += 1;
     L->launches += launch_counter() - launches0;
     return ARISTOS_OK;
 }
@@ -329,19 +332,30 @@ aristos_status_t aristos_moe_status(aristos_moe_t* L) {
 
 aristos_status_t aristos_moe_set_profiling(aristos_moe_t* L, int enable) {
     if (!L) return ARISTOS_ERR_INVALID_ARG;
-    if (enable && !L->ev_prof[0])
-        for (int i = 0; i < 5; ++i) ARISTOS_CUDA_TRY(cudaEventCreate(&L->ev_prof[i]));
+    if (enable && L->ev_prof.empty()) {
+        L->ev_prof.assign(aristos_moe::PROF_SETS * 5, nullptr);
+        for (cudaEvent_t& e : L->ev_prof) ARISTOS_CUDA_TRY(cudaEventCreate(&e));
+    }
     L->profiling = enable != 0;
-    L->profiled = false;
+    L->prof_n = 0;
     return ARISTOS_OK;
 }
 
 aristos_status_t aristos_moe_stage_ms(aristos_moe_t* L, float out_ms[5]) {
     if (!L || !out_ms) return ARISTOS_ERR_INVALID_ARG;
-    if (!L->profiled) { set_last_error("stage_ms: no forward has run with profiling on"); return ARISTOS_ERR_INVALID_ARG; }
-    ARISTOS_CUDA_TRY(cudaEventSynchronize(L->ev_prof[4]));
-    for (int i = 0; i < 4; ++i) ARISTOS_CUDA_TRY(cudaEventElapsedTime(&out_ms[i], L->ev_prof[i], L->ev_prof[i + 1]));
-    ARISTOS_CUDA_TRY(cudaEventElapsedTime(&out_ms[4], L->ev_prof[0], L->ev_prof[4]));
+    if (L->prof_n == 0) { set_last_error("stage_ms: no forward has run since profiling was switched on"); return ARISTOS_ERR_INVALID_ARG; }
+    const int n = (int)std::min<int64_t>(L->prof_n, aristos_moe::PROF_SETS);
+    double acc[5] = {0, 0, 0, 0, 0};
+    for (int j = 0; j < n; ++j) {
+        const int set = (int)((L->prof_n - 1 - j) % aristos_moe::PROF_SETS) * 5;
+        ARISTOS_CUDA_TRY(cudaEventSynchronize(L->ev_prof[set + 4]));
+        for (int i = 0; i < 5; ++i) {
+            float ms = 0.0f;
+            ARISTOS_CUDA_TRY(cudaEventElapsedTime(&ms, L->ev_prof[set + (i < 4 ? i : 0)], L->ev_prof[set + (i < 4 ? i + 1 : 4)]));
+            acc[i] += ms;
+        }
+    }
+    for (int i = 0; i < 5; ++i) out_ms[i] = (float)(acc[i] / n);
     return ARISTOS_OK;
 }
 

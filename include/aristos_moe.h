@@ -148,7 +148,8 @@ ARISTOS_API aristos_status_t aristos_moe_routing_to_host(const aristos_moe_t* la
 ARISTOS_API aristos_status_t aristos_moe_status(aristos_moe_t* layer);
 /* Stage stopwatch (the reference times its kernels with %globaltimer reads and cudaEvents, mma.cuh:56,163,
  * auditorium/overlap.cuh:207-224). With profiling on, every forward records CUDA events on its stream at the stage
- * boundaries; aristos_moe_stage_ms waits for the last forward and returns milliseconds for
+ * boundaries; aristos_moe_stage_ms waits for the last forward and returns milliseconds, averaged over the forwards
+ * since profiling was switched on (at most the last 64), for
  * {gate, dispatch + gather, expert FFN (with the exchanges when world > 1), combine, whole forward}. */
 ARISTOS_API aristos_status_t aristos_moe_set_profiling(aristos_moe_t* layer, int enable);
 ARISTOS_API aristos_status_t aristos_moe_stage_ms(aristos_moe_t* layer, float out_ms[5]);
