@@ -73,6 +73,7 @@ PROTOTYPES = {
     "aristos_gate_topk": (_st, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "aristos_dispatch_scratch_bytes": (_sz, [_i, _i, _i]),
     "aristos_dispatch": (_st, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "aristos_dispatch_static": (_st, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "aristos_permute": (_st, [_vp, _vp, _i, _i, _i, _i, _vp, _vp]),
     "aristos_expert_ffn": (_st, [_vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp]),
     "aristos_combine": (_st, [_vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp]),

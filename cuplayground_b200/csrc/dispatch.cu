@@ -189,6 +189,41 @@ extern "C" aristos_status_t aristos_dispatch(const int32_t* topk_idx, int S, int
                          static_cast<cudaStream_t>(stream));
 }
 
+// ---- dispatch without any allocation ---------------------------------------------------------------------------------
+// The per-chunk histograms of the dispatch live in this fixed array instead of caller-provided scratch memory. Every
+// GPU that loads the library holds these 64 KiB until the process exits.
+constexpr int STATIC_MAX_ASSIGN = 131072;                              // S * k
+constexpr int STATIC_MAX_EXPERTS = 256;
+constexpr int STATIC_MAX_CHUNKS = STATIC_MAX_ASSIGN / aristos::DSP_CHUNK;
+static __device__ __align__(256) int32_t g_dispatch_static_scratch[STATIC_MAX_CHUNKS * STATIC_MAX_EXPERTS];
+
+extern "C" aristos_status_t aristos_dispatch_static(const int32_t* topk_idx, int S, int k, int E, int cap,
+                                                    int32_t* count, int32_t* slot_of, int32_t* token_of_slot,
+                                                    void* stream) {
+    if (S < 0 || k <= 0 || E <= 0) { set_last_error("dispatch_static: bad size"); return ARISTOS_ERR_INVALID_ARG; }
+    if ((int64_t)S * k > STATIC_MAX_ASSIGN || E > STATIC_MAX_EXPERTS) {
+        set_last_error("dispatch_static: S*k = %lld (limit %d) or E = %d (limit %d) exceeds the built-in scratch; "
+                       "use aristos_dispatch with caller scratch", (long long)S * k, STATIC_MAX_ASSIGN, E,
+                       STATIC_MAX_EXPERTS);
+        return ARISTOS_ERR_CONFIG;
+    }
+    // The array's name is only a host-side handle: the kernels need its device address, looked up once per device
+    // with that device current.
+    constexpr int MAX_DEVICES = 64;
+    static int32_t* scratch_of_device[MAX_DEVICES] = {nullptr};
+    int dev = 0;
+    ARISTOS_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= MAX_DEVICES) { set_last_error("dispatch_static: device index %d not supported", dev); return ARISTOS_ERR_UNSUPPORTED; }
+    if (!scratch_of_device[dev]) {
+        void* p = nullptr;
+        ARISTOS_CUDA_TRY(cudaGetSymbolAddress(&p, g_dispatch_static_scratch));
+        scratch_of_device[dev] = static_cast<int32_t*>(p);
+    }
+    return dispatch_impl(topk_idx, S, k, E, cap, count, slot_of, token_of_slot, scratch_of_device[dev],
+                         sizeof(int32_t) * STATIC_MAX_CHUNKS * STATIC_MAX_EXPERTS, nullptr,
+                         static_cast<cudaStream_t>(stream));
+}
+
 extern "C" aristos_status_t aristos_permute(const void* x, const int32_t* slot_of, int S, int k, int H, int dtype,
                                             void* xg, void* stream) {
     if (!x || !slot_of || !xg) { set_last_error("permute: NULL pointer"); return ARISTOS_ERR_INVALID_ARG; }

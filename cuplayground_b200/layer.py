@@ -94,6 +94,19 @@ def dispatch(topk_idx, E: int, cap: int):
     return count, slot_of, tos
 
 
+def dispatch_static(topk_idx, E: int, cap: int):
+    """aristos_dispatch_static: the dispatch for callers that cannot allocate device memory (the library's built-in
+    64 KiB scratch; S*k <= 131072, E <= 256). The outputs are still the caller's (here: torch) buffers."""
+    S, k = topk_idx.shape
+    dev = topk_idx.device
+    count = torch.empty(E, dtype=torch.int32, device=dev)
+    slot_of = torch.empty((S, k), dtype=torch.int32, device=dev)
+    tos = torch.empty(E * cap, dtype=torch.int32, device=dev)
+    _lib.check(_lib.load().aristos_dispatch_static(_ptr(topk_idx), S, k, E, cap, _ptr(count), _ptr(slot_of),
+                                                   _ptr(tos), _stream_ptr()))
+    return count, slot_of, tos
+
+
 def permute(x, slot_of, nslots: int, zero: bool = False):
     S, H = x.shape
     k = slot_of.shape[1]

@@ -171,6 +171,20 @@ ARISTOS_API size_t aristos_dispatch_scratch_bytes(int S, int k, int E);
 ARISTOS_API aristos_status_t aristos_dispatch(const int32_t* topk_idx, int S, int k, int E, int cap,
                                               int32_t* count, int32_t* slot_of, int32_t* token_of_slot,
                                               void* scratch, size_t scratch_bytes, void* stream);
+/*
+ * Same dispatch, for callers that must not allocate device memory: a serving engine that has already handed all of
+ * the GPU's memory to its own pool, or a latency-critical loop in which a cudaMalloc (which may synchronise the
+ * device or simply fail) is not acceptable. It has no counterpart in the reference. The scratch is a fixed 64 KiB
+ * array inside the library (held on every GPU that loads it until the process exits), so the sizes are limited to
+ * S*k <= 131072 and E <= 256; larger requests are rejected with ARISTOS_ERR_CONFIG. The call allocates nothing.
+ * The first call on each device looks up the array's device address (cudaGetSymbolAddress); make that first call
+ * outside any stream capture. All calls share the one array and it keeps the previous call's contents: nothing in it
+ * has to start at zero (the first kernel overwrites every entry the later ones read), but two calls whose kernels
+ * overlap on the GPU (different streams, no ordering) race on it - order them.
+ */
+ARISTOS_API aristos_status_t aristos_dispatch_static(const int32_t* topk_idx, int S, int k, int E, int cap,
+                                                     int32_t* count, int32_t* slot_of, int32_t* token_of_slot,
+                                                     void* stream);
 /* Gather token rows into expert-major order: xg[slot_of[t,j]] = x[t]. xg is (E*cap, H). */
 ARISTOS_API aristos_status_t aristos_permute(const void* x, const int32_t* slot_of, int S, int k, int H, int dtype,
                                              void* xg, void* stream);
