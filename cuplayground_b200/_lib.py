@@ -59,6 +59,8 @@ PROTOTYPES = {
     "aristos_zipf_bias_host": (_st, [C.POINTER(C.c_float), _i, C.c_double]),
     "aristos_moe_create": (_st, [C.POINTER(AristosConfigStruct), _i, _i, _vp, C.POINTER(_vp)]),
     "aristos_nccl_unique_id": (_st, [_vp]),
+    "aristos_ep_exchange_plan": (_i, [_i, _i, _i, _sz, _sz, _sz, C.POINTER(C.c_int64), _i]),
+    "aristos_ep_row_windows": (_st, [_i, C.POINTER(_i), C.POINTER(_i)]),
     "aristos_moe_workspace_bytes": (_sz, [_vp]),
     "aristos_moe_set_workspace": (_st, [_vp, _vp, _sz]),
     "aristos_moe_forward": (_st, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),

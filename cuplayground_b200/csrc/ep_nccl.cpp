@@ -11,6 +11,7 @@
 #include <nccl.h>
 
 #include <cstring>
+#include <vector>
 
 #include "common.cuh"
 
@@ -106,29 +107,50 @@ void ep_comm_destroy(EpComm* c) {
     delete c;
 }
 
+// The exchange of one row window as a flat list of transfers; entry 0 is the rank's own copy.
+std::vector<EpTransfer> ep_exchange_plan(int rank, int world, int blocks_per_peer, size_t block_stride, size_t offset,
+                                         size_t len) {
+    std::vector<EpTransfer> plan;
+    for (int step = 0; step < world; ++step) {
+        const int to = (rank + step) % world;
+        const int from = (rank - step + world) % world;
+        for (int b = 0; b < blocks_per_peer; ++b) {
+            EpTransfer t;
+            t.send_to = to;
+            t.recv_from = from;
+            t.send_offset = ((size_t)to * blocks_per_peer + b) * block_stride + offset;
+            t.recv_offset = ((size_t)from * blocks_per_peer + b) * block_stride + offset;
+            t.bytes = len;
+            plan.push_back(t);
+        }
+    }
+    return plan;
+}
+
+void ep_row_windows(int cap, int max_windows, int min_rows, int* window_rows, int* windows) {
+    int n = max_windows < 1 ? 1 : max_windows;
+    while (n > 1 && (cap + n - 1) / n < min_rows) --n;
+    const int rows = ((cap + n - 1) / n + 127) / 128 * 128;
+    *window_rows = rows;
+    *windows = (cap + rows - 1) / rows;
+}
+
 aristos_status_t ep_all_to_all_blocks(EpComm* c, const void* send_buf, void* recv_buf, int blocks_per_peer,
                                       size_t block_stride, size_t offset, size_t len, cudaStream_t stream) {
     if (!c || !send_buf || !recv_buf || blocks_per_peer <= 0) return ARISTOS_ERR_INVALID_ARG;
     if (len == 0) return ARISTOS_OK;
     const char* sb = static_cast<const char*>(send_buf);
     char* rb = static_cast<char*>(recv_buf);
-    // own blocks: one strided device-to-device copy
-    {
-        const size_t base = (size_t)c->rank * blocks_per_peer * block_stride + offset;
-        ARISTOS_CUDA_TRY(cudaMemcpy2DAsync(rb + base, block_stride, sb + base, block_stride, len, blocks_per_peer,
-                                           cudaMemcpyDeviceToDevice, stream));
-    }
+    const std::vector<EpTransfer> plan = ep_exchange_plan(c->rank, c->world, blocks_per_peer, block_stride, offset, len);
+    // own blocks (the first blocks_per_peer entries): one strided device-to-device copy
+    ARISTOS_CUDA_TRY(cudaMemcpy2DAsync(rb + plan[0].recv_offset, block_stride, sb + plan[0].send_offset, block_stride,
+                                       len, blocks_per_peer, cudaMemcpyDeviceToDevice, stream));
     NCCL_TRY(api().GroupStart());
-    for (int step = 1; step < c->world; ++step) {
-        const int to = (c->rank + step) % c->world;
-        const int from = (c->rank - step + c->world) % c->world;
-        for (int b = 0; b < blocks_per_peer; ++b) {
-            const size_t so = ((size_t)to * blocks_per_peer + b) * block_stride + offset;
-            const size_t ro = ((size_t)from * blocks_per_peer + b) * block_stride + offset;
-            ncclResult_t r = api().Send(sb + so, len, ncclInt8, to, c->comm, stream);
-            if (r == ncclSuccess) r = api().Recv(rb + ro, len, ncclInt8, from, c->comm, stream);
-            if (r != ncclSuccess) { api().GroupEnd(); return nccl_fail(r, "ncclSend/ncclRecv"); }
-        }
+    for (size_t i = blocks_per_peer; i < plan.size(); ++i) {
+        const EpTransfer& t = plan[i];
+        ncclResult_t r = api().Send(sb + t.send_offset, t.bytes, ncclInt8, t.send_to, c->comm, stream);
+        if (r == ncclSuccess) r = api().Recv(rb + t.recv_offset, t.bytes, ncclInt8, t.recv_from, c->comm, stream);
+        if (r != ncclSuccess) { api().GroupEnd(); return nccl_fail(r, "ncclSend/ncclRecv"); }
     }
     NCCL_TRY(api().GroupEnd());
     return ARISTOS_OK;
@@ -137,3 +159,26 @@ aristos_status_t ep_all_to_all_blocks(EpComm* c, const void* send_buf, void* rec
 }  // namespace aristos
 
 extern "C" aristos_status_t aristos_nccl_unique_id(void* out_128_bytes) { return aristos::ep_unique_id(out_128_bytes); }
+
+extern "C" int aristos_ep_exchange_plan(int rank, int world, int blocks_per_peer, size_t block_stride, size_t offset,
+                                        size_t len, int64_t* out, int max_entries) {
+    if (world < 1 || rank < 0 || rank >= world || blocks_per_peer < 1) return -1;
+    const std::vector<aristos::EpTransfer> plan =
+        aristos::ep_exchange_plan(rank, world, blocks_per_peer, block_stride, offset, len);
+    if (out) {
+        for (size_t i = 0; i < plan.size() && (int)i < max_entries; ++i) {
+            out[5 * i + 0] = plan[i].send_to;
+            out[5 * i + 1] = (int64_t)plan[i].send_offset;
+            out[5 * i + 2] = plan[i].recv_from;
+            out[5 * i + 3] = (int64_t)plan[i].recv_offset;
+            out[5 * i + 4] = (int64_t)plan[i].bytes;
+        }
+    }
+    return (int)plan.size();
+}
+
+extern "C" aristos_status_t aristos_ep_row_windows(int cap, int* window_rows, int* windows) {
+    if (cap < 1 || !window_rows || !windows) return ARISTOS_ERR_INVALID_ARG;
+    aristos::ep_row_windows(cap, 4, 512, window_rows, windows);
+    return ARISTOS_OK;
+}

@@ -6,6 +6,8 @@
 #include <stddef.h>
 #include <stdint.h>
 
+#include <vector>
+
 #include "../../include/aristos_moe.h"
 
 namespace aristos {
@@ -15,6 +17,19 @@ struct EpComm;  // opaque
 aristos_status_t ep_unique_id(void* out_128_bytes);
 aristos_status_t ep_comm_create(const void* unique_id_128, int rank, int world, EpComm** out);
 void ep_comm_destroy(EpComm* c);
+
+// One transfer of an exchange: this rank sends `bytes` at send_offset of its send buffer to send_to and receives
+// as many from recv_from into recv_offset of its receive buffer.
+struct EpTransfer {
+    int send_to, recv_from;
+    size_t send_offset, recv_offset, bytes;
+};
+// Pure host logic (no CUDA, no NCCL): the transfers of one exchange, the rank's own blocks first.
+std::vector<EpTransfer> ep_exchange_plan(int rank, int world, int blocks_per_peer, size_t block_stride, size_t offset,
+                                         size_t len);
+// Row windows of the overlapped pipeline: at most max_windows windows of a multiple of 128 rows, none smaller than
+// min_rows unless the capacity itself is.
+void ep_row_windows(int cap, int max_windows, int min_rows, int* window_rows, int* windows);
 
 // One grouped exchange. For every peer d != rank and every block b < blocks_per_peer:
 //   send  bytes [ (d*blocks_per_peer + b) * block_stride + offset, +len )  of send_buf to d

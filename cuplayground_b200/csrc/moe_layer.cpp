@@ -158,16 +158,10 @@ aristos_status_t aristos_moe_create(const aristos_config_t* cfg, int rank, int w
         cudaError_t e = cudaStreamCreateWithFlags(&L->comm_stream, cudaStreamNonBlocking);
         if (e == cudaSuccess) e = cudaEventCreateWithFlags(&L->ev_dispatched, cudaEventDisableTiming);
         if (e == cudaSuccess) e = cudaEventCreateWithFlags(&L->ev_returned, cudaEventDisableTiming);
-        // row windows: a multiple of 128 rows, at most 4 per forward, at least 512 rows each
-        int chunks = 4;
-        while (chunks > 1 && ceil_div(L->cap, chunks) < 512) --chunks;
-        L->chunk_rows = ceil_div(ceil_div(L->cap, chunks), 128) * 128;
-        L->chunks = ceil_div(L->cap, L->chunk_rows);
+        // row windows of the overlapped exchange
+        ep_row_windows(L->cap, 4, 512, &L->chunk_rows, &L->chunks);
         const char* env = getenv("ARISTOS_EP_CHUNKS");
-        if (env && atoi(env) >= 1) {
-            L->chunk_rows = ceil_div(ceil_div(L->cap, atoi(env)), 128) * 128;
-            L->chunks = ceil_div(L->cap, L->chunk_rows);
-        }
+        if (env && atoi(env) >= 1) ep_row_windows(L->cap, atoi(env), 128, &L->chunk_rows, &L->chunks);
         // leave SMs for the NCCL kernels that run beside the GEMMs
         L->ffn_sm_limit = device_sm_count() - 16;
         const char* env2 = getenv("ARISTOS_EP_FFN_SMS");

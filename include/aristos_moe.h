@@ -116,6 +116,16 @@ ARISTOS_API aristos_status_t aristos_zipf_bias_host(float* bias_host, int num_ex
 ARISTOS_API aristos_status_t aristos_moe_create(const aristos_config_t* cfg, int rank, int world,
                                                 const void* nccl_unique_id, aristos_moe_t** out);
 ARISTOS_API aristos_status_t aristos_nccl_unique_id(void* out_128_bytes);
+/* Host-only helpers that expose the layout logic of the expert-parallel exchange (no CUDA, no NCCL), so that it can
+ * be checked with CPU ranks; they replace the symmetric-heap slot arithmetic of auditorium/overlap.cuh:28-35,183-190.
+ * aristos_ep_exchange_plan writes up to max_entries rows {send_to, send_offset, recv_from, recv_offset, bytes} of the
+ * exchange of one row window (the rank's own blocks first) and returns the number of transfers (-1 on bad arguments):
+ * block (d*blocks_per_peer + b) of the send buffer goes to rank d and lands in block (src*blocks_per_peer + b) of
+ * the receiver's buffer, `offset`/`len` select the window inside every block. aristos_ep_row_windows gives the row
+ * windows a layer uses for a capacity. */
+ARISTOS_API int aristos_ep_exchange_plan(int rank, int world, int blocks_per_peer, size_t block_stride, size_t offset,
+                                         size_t len, int64_t* out, int max_entries);
+ARISTOS_API aristos_status_t aristos_ep_row_windows(int cap, int* window_rows, int* windows);
 ARISTOS_API size_t aristos_moe_workspace_bytes(const aristos_moe_t* layer);
 /* Optional: hand the layer a caller-owned device workspace (>= aristos_moe_workspace_bytes, 1024-byte aligned).
  * Without it the first forward allocates one with cudaMalloc and keeps it until destroy. */

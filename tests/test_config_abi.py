@@ -1,0 +1,124 @@
+"""CPU tests of the host side: configuration parsing/validation through the C ABI, and that the shared library loads
+and exports every symbol include/aristos_moe.h declares (no compute call is made here)."""
+import ctypes as C
+import json
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+# the reference's shipped aristos_config.json (aristos_config.json:1-13), restated
+REFERENCE_JSON = json.dumps({"capacity_factor": 1, "drop_tokens": 0, "expert_top_k": 1, "is_training": 0,
+                             "hidden_act": 0, "hidden_size": 1024, "intermediate_size": 4096, "micro_batch": 4,
+                             "num_experts": 1, "sequence_len": 2048, "torch_dtype": 0})
+
+
+@pytest.fixture(scope="module")
+def cp():
+    from cuplayground_b200 import build
+    build.build_library()
+    import cuplayground_b200
+    return cuplayground_b200
+
+
+def test_library_exports_every_declared_symbol(cp):
+    header = open(os.path.join(ROOT, "include", "aristos_moe.h")).read()
+    declared = set(re.findall(r"ARISTOS_API\s+[\w\s\*]+?\b(aristos_\w+)\s*\(", header))
+    assert len(declared) >= 30
+    lib = C.CDLL(cp._lib.LIB_PATH)
+    missing = [name for name in sorted(declared) if not hasattr(lib, name)]
+    assert not missing, missing
+    assert declared == set(cp._lib.PROTOTYPES), declared ^ set(cp._lib.PROTOTYPES)
+    cp._lib.load()
+    assert cp._lib.load().aristos_version() >= 100
+    assert cp._lib.load().aristos_status_str(8) == b"device-side wait timed out"
+
+
+def test_reference_config_parses(cp):
+    c = cp.AristosConfig.from_json(REFERENCE_JSON)
+    assert (c.hidden_size, c.intermediate_size, c.num_experts, c.expert_top_k) == (1024, 4096, 1, 1)
+    assert c.S == 4 * 2048                       # tokens = micro_batch * sequence_len
+    assert c.capacity == c.S                     # drop_tokens = 0 -> nothing is dropped
+    assert c.gate_fn == 0 and c.ep_world == 1    # extension keys default
+
+
+def test_config_file_and_extensions(cp, tmp_path):
+    d = json.loads(REFERENCE_JSON)
+    d.update(capacity_factor=1.25, drop_tokens=1, expert_top_k=2, hidden_act=2, num_experts=8, torch_dtype=2,
+             tokens=16384, hidden_size=4096, intermediate_size=14336, unknown_key={"nested": [1, 2, "x"]})
+    p = tmp_path / "aristos_config.json"
+    p.write_text(json.dumps(d))
+    c = cp.AristosConfig.load(str(p))
+    assert c.S == 16384 and c.capacity == 5120 and c.hidden_act == 2 and c.capacity_factor == 1.25
+    with pytest.raises(cp.AristosError) as e:
+        cp.AristosConfig.load(str(tmp_path / "missing.json"))
+    assert e.value.status == 3
+
+
+@pytest.mark.parametrize("patch,needle", [
+    ({"hidden_size": 100}, "hidden_size"),            # multipleOf 64   (aristos_config.schema.json:29-33)
+    ({"intermediate_size": 0}, "intermediate_size"),
+    ({"sequence_len": 100}, "sequence_len"),          # multipleOf 128  (:49-53)
+    ({"micro_batch": 3}, "micro_batch"),              # multipleOf 2    (:39-43)
+    ({"drop_tokens": 2}, "drop_tokens"),              # enum 0/1        (:11-14)
+    ({"hidden_act": 7}, "hidden_act"),
+    ({"torch_dtype": 9}, "torch_dtype"),
+    ({"num_experts": 0}, "num_experts"),
+    ({"expert_top_k": 0}, "expert_top_k"),
+    ({"expert_top_k": 3, "num_experts": 2}, "expert_top_k"),
+    ({"capacity_factor": 0}, "capacity_factor"),
+    ({"num_experts": 6, "ep_world": 4}, "ep_world"),
+    ({"hidden_size": 64.5}, "integer"),
+])
+def test_schema_violations_are_rejected(cp, patch, needle):
+    d = json.loads(REFERENCE_JSON)
+    d.update(patch)
+    with pytest.raises(cp.AristosError) as e:
+        cp.AristosConfig.from_json(json.dumps(d))
+    assert e.value.status == 2 and needle in str(e.value)
+
+
+def test_missing_required_key_and_bad_json(cp):
+    d = json.loads(REFERENCE_JSON)
+    del d["torch_dtype"]
+    with pytest.raises(cp.AristosError) as e:
+        cp.AristosConfig.from_json(json.dumps(d))
+    assert "torch_dtype" in str(e.value)
+    d2 = json.loads(REFERENCE_JSON)
+    del d2["is_training"]                      # not in the schema's "required" list
+    cp.AristosConfig.from_json(json.dumps(d2))
+    for bad in ("", "{", '{"hidden_size": }', "[1,2]", '{"hidden_size": 64,, }'):
+        with pytest.raises(cp.AristosError):
+            cp.AristosConfig.from_json(bad)
+
+
+def test_baseline_configs_validate(cp, oracle):
+    caps = {1: 16, 2: 320, 3: 5120, 4: 4096, 5: 256}
+    for n, cap in caps.items():
+        c = cp.baseline_config(n)
+        c.validate()
+        assert c.capacity == cap
+        assert c.capacity == oracle.capacity(c.S, c.num_experts, c.expert_top_k, c.capacity_factor, c.drop_tokens)
+
+
+def test_zipf_bias_matches_oracle(cp, oracle):
+    import numpy as np
+    b = (C.c_float * 128)()
+    cp._lib.check(cp._lib.load().aristos_zipf_bias_host(b, 128, 1.2))
+    np.testing.assert_array_equal(np.frombuffer(b, dtype=np.float32), oracle.zipf_bias(128, 1.2))
+
+
+def test_compute_entry_points_fail_loudly_without_a_device(cp):
+    """No CPU fallback: on a machine without a CUDA device creating a layer returns a CUDA error."""
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    import cuplayground_b200.layer as layer
+    with pytest.raises(RuntimeError):
+        layer.MoELayer(cp.baseline_config(1))
+    s = cp.baseline_config(1).to_struct()
+    h = C.c_void_p()
+    st = cp._lib.load().aristos_moe_create(C.byref(s), 0, 1, None, C.byref(h))
+    assert st == 4, "aristos_moe_create must report ARISTOS_ERR_CUDA without a device"

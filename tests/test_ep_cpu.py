@@ -1,0 +1,165 @@
+"""Expert-parallel path on CPU ranks (gloo, world_size 2 and 4): the product's host-side exchange logic
+(aristos_ep_exchange_plan / aristos_ep_row_windows, the same functions the NCCL path executes) moves real rows between
+processes, the CPU oracle stands in for the kernels, and every rank's output must equal an independent single-rank
+oracle run over the global weights (capacity is per source rank)."""
+import ctypes as C
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _plan(lib, rank, world, bpp, stride, offset, length):
+    n = lib.aristos_ep_exchange_plan(rank, world, bpp, stride, offset, length, None, 0)
+    buf = (C.c_int64 * (5 * n))()
+    assert lib.aristos_ep_exchange_plan(rank, world, bpp, stride, offset, length, buf, n) == n
+    return np.frombuffer(buf, dtype=np.int64).reshape(n, 5)
+
+
+def _exchange(dist, torch, plan, send: np.ndarray, recv: np.ndarray, rank):
+    """Executes a plan on flat byte buffers with gloo point-to-point operations."""
+    sb, rb = send.view(np.uint8).reshape(-1), recv.view(np.uint8).reshape(-1)
+    reqs, landing = [], []
+    for to, so, frm, ro, n in plan:
+        if to == rank:
+            assert frm == rank
+            rb[ro:ro + n] = sb[so:so + n]
+            continue
+        reqs.append(dist.isend(torch.from_numpy(sb[so:so + n].copy()), dst=int(to)))
+        t = torch.empty(int(n), dtype=torch.uint8)
+        reqs.append(dist.irecv(t, src=int(frm)))
+        landing.append((t, int(ro), int(n)))
+    for r in reqs:
+        r.wait()
+    for t, ro, n in landing:
+        rb[ro:ro + n] = t.numpy()
+
+
+def _worker(rank, world, port, E, S, H, I, k, cf, act, q):
+    try:
+        sys.path.insert(0, ROOT)
+        sys.path.insert(0, os.path.join(ROOT, "tests"))
+        import torch
+        import torch.distributed as dist
+        from helpers import make_inputs
+        from oracle import moe_oracle as O
+        import cuplayground_b200 as cp
+
+        os.environ["OMP_NUM_THREADS"] = "2"
+        lib = cp._lib.load()
+        dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+        El = E // world
+        cap = O.capacity(S, E, k, cf)
+        _, wg, w1, w3, w2 = make_inputs(S, H, I, E, seed=100, swiglu=(act == 2), w_std=0.1)        # shared weights
+        x = make_inputs(S, H, I, E, seed=200 + rank, w_std=0.1)[0]                               # this rank's tokens
+        loc = slice(rank * El, (rank + 1) * El)
+        w1l, w3l, w2l = w1[loc], (None if w3 is None else w3[loc]), w2[loc]
+
+        # local routing + gather (what gate / dispatch / permute do on the GPU)
+        idx, w = O.gate_topk(O.gate_logits(x, wg), k, 0, 1)
+        count, slot_of, tos = O.dispatch(idx, E, cap)
+        xg = O.permute(x, tos)                                              # (E*cap, H) send layout
+
+        # counts: one block of E_local int32 per peer
+        rcount = np.zeros(world * El, np.int32)
+        _exchange(dist, torch, _plan(lib, rank, world, 1, El * 4, 0, El * 4), count, rcount, rank)
+        all_counts = [torch.zeros(E, dtype=torch.int32) for _ in range(world)]
+        dist.all_gather(all_counts, torch.from_numpy(count))
+        expect = np.concatenate([c.numpy()[loc] for c in all_counts])
+        assert (rcount == expect).all(), "count exchange landed in the wrong group"
+
+        # rows travel in the layer's row windows; the FFN runs per window on (source, local expert) groups
+        wr, nw = C.c_int(), C.c_int()
+        cp._lib.check(lib.aristos_ep_row_windows(cap, C.byref(wr), C.byref(nw)))
+        assert wr.value % 128 == 0 and wr.value * nw.value >= cap > wr.value * (nw.value - 1)
+        row_bytes, stride = H * 4, cap * H * 4
+        xr = np.zeros((world * El * cap, H), np.float32)
+        yr = np.zeros((world * El, cap, H), np.float32)
+        yg = np.zeros((E * cap, H), np.float32)
+        groups_w1 = np.concatenate([w1l] * world)
+        groups_w3 = None if w3l is None else np.concatenate([w3l] * world)
+        groups_w2 = np.concatenate([w2l] * world)
+        for c in range(nw.value):
+            r0, r1 = c * wr.value, min(cap, (c + 1) * wr.value)
+            _exchange(dist, torch, _plan(lib, rank, world, El, stride, r0 * row_bytes, (r1 - r0) * row_bytes), xg, xr, rank)
+            cnt_w = np.clip(rcount - r0, 0, r1 - r0).astype(np.int32)
+            y_w = O.expert_ffn(xr.reshape(world * El, cap, H)[:, r0:r1].copy(), cnt_w, groups_w1, groups_w3,
+                               groups_w2, act)
+            yr[:, r0:r1] = y_w
+            _exchange(dist, torch, _plan(lib, rank, world, El, stride, r0 * row_bytes, (r1 - r0) * row_bytes),
+                      yr.reshape(-1, H), yg, rank)
+        out = O.combine(yg, slot_of, w)
+
+        ref = O.moe_forward(x, wg, w1, w3, w2, k=k, cap=cap, renorm=1, hidden_act=act)
+        assert (ref["slot_of"] == slot_of).all()
+        np.testing.assert_allclose(out, ref["out"], rtol=1e-5, atol=1e-6)
+        dist.barrier()
+        dist.destroy_process_group()
+        q.put((rank, "ok"))
+    except Exception as e:      # pragma: no cover - reported to the parent
+        import traceback
+        q.put((rank, "".join(traceback.format_exception(e))))
+
+
+@pytest.mark.parametrize("world,E,S,k,cf,act", [(2, 4, 96, 2, 1.0, 1), (2, 8, 640, 2, 1.25, 2), (4, 8, 64, 2, 1.5, 0),
+                                                  (2, 4, 2200, 2, 1.0, 1)])   # cap 1100: two row windows
+def test_expert_parallel_on_cpu_ranks(world, E, S, k, cf, act):
+    import torch.multiprocessing as mp
+    from cuplayground_b200 import build
+    build.build_library()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, E, S, 64, 128, k, cf, act, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=240) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    bad = [r for r in results if r[1] != "ok"]
+    assert not bad, bad[0][1]
+
+
+def test_exchange_plan_is_a_permutation():
+    """Every (destination rank, block) is written exactly once and sends pair up with receives."""
+    import cuplayground_b200 as cp
+    from cuplayground_b200 import build
+    build.build_library()
+    lib = cp._lib.load()
+    world, bpp, stride, off, ln = 8, 3, 1000, 128, 256
+    plans = [_plan(lib, r, world, bpp, stride, off, ln) for r in range(world)]
+    written = set()
+    for r, plan in enumerate(plans):
+        assert len(plan) == world * bpp
+        assert (plan[:bpp, 0] == r).all() and (plan[:bpp, 2] == r).all(), "own blocks come first"
+        for to, so, frm, ro, n in plan:
+            assert n == ln and (so - off) % stride == 0 and (so - off) // stride // bpp == to
+            assert (ro - off) // stride // bpp == frm
+            # the matching send on the peer targets this receive
+            peer = plans[frm]
+            match = [(t2, s2) for t2, s2, _, _, _ in peer if t2 == r and (s2 - off) // stride % bpp == (ro - off) // stride % bpp]
+            assert len(match) == 1
+            written.add((r, int(ro)))
+    assert len(written) == world * world * bpp
+    assert lib.aristos_ep_exchange_plan(3, 2, 1, 8, 0, 8, None, 0) == -1
+
+
+def test_row_windows():
+    import cuplayground_b200 as cp
+    lib = cp._lib.load()
+    for cap, exp_rows, exp_n in ((5120, 1280, 4), (320, 384, 1), (256, 256, 1), (1100, 640, 2), (16, 128, 1)):
+        wr, nw = C.c_int(), C.c_int()
+        cp._lib.check(lib.aristos_ep_row_windows(cap, C.byref(wr), C.byref(nw)))
+        assert (wr.value, nw.value) == (exp_rows, exp_n), (cap, wr.value, nw.value)

@@ -1,0 +1,158 @@
+"""CPU tests of the oracle: the reference's hand-written fixtures as known answers, independent numpy restatements
+of each stage, and the committed golden vectors of the fp32 reference case."""
+import os
+
+import numpy as np
+import pytest
+
+from helpers import make_inputs
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+# ---- known answers from the reference's own fixtures ----------------------------------------------------------------
+def test_reference_fixture_testCollective(oracle):
+    """mma.cuh:399-411: A[0:2,0:2]=[[0,1],[2,3]], B[0:2,0:2]=[[4,5],[6,7]], bias[0:2]=[1,2], everything else zero,
+    ReLU epilogue act(acc + bias) (processor/tiling.cuh:29-57) -> C[0:2,0:2] = [[6,9],[24,35]], zero elsewhere."""
+    M, N, K = 128, 64, 64
+    A = np.zeros((M, K), np.float32); A[:2, :2] = [[0, 1], [2, 3]]
+    B = np.zeros((N, K), np.float32); B[:2, :2] = [[4, 5], [6, 7]]
+    bias = np.zeros(N, np.float32); bias[:2] = [1, 2]
+    C = oracle.gemm_bias_act(A, B, bias, act=0)
+    assert (C[:2, :2] == [[6, 9], [24, 35]]).all()
+    assert (C[2:, :2] == [1, 2]).all(), "rows of zeros keep ReLU(bias)"
+    assert np.count_nonzero(C[:, 2:]) == 0
+
+
+def test_reference_fixture_bias_broadcast(oracle):
+    """benchmarks.cuh:480-488: t=[[0,1],[2,3]] plus broadcast bias [4,5] -> [[4,6],[6,8]] (identity GEMM)."""
+    t = np.array([[0, 1], [2, 3]], np.float32)
+    C = oracle.gemm_bias_act(t, np.eye(2, dtype=np.float32), np.array([4, 5], np.float32), act=3)
+    assert (C == [[4, 6], [6, 8]]).all()
+
+
+def test_reference_fixture_hostCombine(oracle):
+    """auditorium/combine.cuh:219-231: identity indices, row i filled with i+1 -> activations row i == i+1."""
+    M, N = 128, 64
+    y = np.repeat(np.arange(1, M + 1, dtype=np.float32)[:, None], N, axis=1)
+    out = oracle.combine(y, np.arange(M, dtype=np.int32)[:, None], np.ones((M, 1), np.float32))
+    assert (out == y).all()
+
+
+# ---- stage semantics against independent restatements ---------------------------------------------------------------
+def test_capacity_formula(oracle):
+    assert oracle.capacity(128, 8, 1, 1.0) == 16          # config 1: cap = S/E
+    assert oracle.capacity(8192, 64, 2, 1.25) == 320
+    assert oracle.capacity(16384, 8, 2, 1.25) == 5120
+    assert oracle.capacity(8192, 128, 4, 1.0) == 256
+    assert oracle.capacity(100, 8, 1, 1.0) == 13          # ceil
+    assert oracle.capacity(4096, 256, 8, 1.0, drop_tokens=0) == 4096
+
+
+def test_gate_logits_order_and_value(oracle):
+    rng = np.random.default_rng(0)
+    S, H, E = 17, 320, 5
+    x = rng.standard_normal((S, H)).astype(np.float32)
+    wg = rng.standard_normal((E, H)).astype(np.float32)
+    got = oracle.gate_logits(x, wg)
+    # independent restatement of the contract: 32 strided partial sums with fused multiply-add, xor butterfly
+    ref = np.zeros((S, E), np.float32)
+    for t in range(S):
+        for e in range(E):
+            p = [np.float32(0)] * 32
+            for q in range(H // 8):
+                c = q % 32
+                for v in range(8):
+                    h = q * 8 + v
+                    p[c] = np.float32(np.float64(x[t, h]) * np.float64(wg[e, h]) + np.float64(p[c]))  # exact product, one rounding
+            for m in (16, 8, 4, 2, 1):
+                p = [np.float32(p[c] + p[c ^ m]) for c in range(32)]
+            ref[t, e] = p[0]
+    np.testing.assert_array_equal(got.view(np.uint32), ref.view(np.uint32))
+    np.testing.assert_allclose(got, x.astype(np.float64) @ wg.astype(np.float64).T, rtol=1e-4, atol=1e-4)
+
+
+def test_gate_topk_ties_and_weights(oracle):
+    logits = np.array([[1.0, 3.0, 3.0, 0.5], [2.0, 2.0, 2.0, 2.0], [0.1, 0.2, 0.3, 0.4]], np.float32)
+    idx, w = oracle.gate_topk(logits, 2, gate_fn=0, renorm=0)
+    assert idx.tolist() == [[1, 2], [0, 1], [3, 2]]        # ties -> lower expert index
+    sm = np.exp(logits - logits.max(1, keepdims=True)); sm /= sm.sum(1, keepdims=True)
+    np.testing.assert_allclose(w, np.take_along_axis(sm, idx, 1), rtol=1e-6)
+    _, wr = oracle.gate_topk(logits, 2, gate_fn=0, renorm=1)
+    np.testing.assert_allclose(wr.sum(1), 1.0, rtol=1e-6)
+    idx_s, ws = oracle.gate_topk(logits, 3, gate_fn=1, renorm=1)     # sigmoid, normalised over the selected
+    sg = 1 / (1 + np.exp(-np.take_along_axis(logits, idx_s, 1)))
+    np.testing.assert_allclose(ws, sg / sg.sum(1, keepdims=True), rtol=1e-6)
+
+
+def test_dispatch_drops_in_token_order(oracle):
+    topk = np.array([[0], [0], [1], [0], [1], [0]], np.int32)
+    count, slot_of, tos = oracle.dispatch(topk, E=2, cap=2)
+    assert count.tolist() == [2, 2]
+    assert slot_of[:, 0].tolist() == [0, 1, 2, -1, 3, -1]   # tokens 3 and 5 overflow expert 0, in token order
+    assert tos.tolist() == [0, 1, 2, 4]
+    # k = 2: (t,j) order is token-major then j
+    topk2 = np.array([[0, 1], [1, 0], [0, 1]], np.int32)
+    count, slot_of, tos = oracle.dispatch(topk2, E=2, cap=2)
+    assert slot_of.tolist() == [[0, 2], [3, 1], [-1, -1]]
+    assert tos.tolist() == [0, 1, 0, 1]
+
+
+@pytest.mark.parametrize("act", [0, 1, 2])
+def test_expert_ffn_against_numpy(oracle, act):
+    from math import erf
+    E, rows, H, I = 2, 9, 64, 128
+    x, _, w1, w3, w2 = make_inputs(E * rows, H, I, E, seed=4, swiglu=(act == 2), bf16=False, w_std=0.1)
+    xg = x.reshape(E, rows, H)
+    count = np.array([9, 4], np.int32)
+    y = oracle.expert_ffn(xg, count, w1, w3, w2, act)
+    for e in range(E):
+        a = xg[e, :count[e]].astype(np.float64)
+        g = a @ w1[e].astype(np.float64).T
+        if act == 0:
+            h = np.maximum(g, 0)
+        elif act == 1:
+            h = 0.5 * g * (1 + np.vectorize(erf)(g / np.sqrt(2)))
+        else:
+            h = g / (1 + np.exp(-g)) * (a @ w3[e].astype(np.float64).T)
+        np.testing.assert_allclose(y[e, :count[e]], h @ w2[e].astype(np.float64).T, rtol=2e-4, atol=2e-5)
+        assert (y[e, count[e]:] == 0).all()
+
+
+def test_layer_equals_composed_stages(oracle):
+    """moe_forward (token-major recomputation) == gate -> dispatch -> permute -> expert_ffn -> combine."""
+    S, H, I, E, k = 96, 64, 128, 4, 2
+    cap = oracle.capacity(S, E, k, 1.0)
+    x, wg, w1, w3, w2 = make_inputs(S, H, I, E, seed=8, swiglu=True, bf16=True, w_std=0.1)
+    r = oracle.moe_forward(x, wg, w1, w3, w2, k=k, cap=cap, renorm=1, hidden_act=2)
+    idx, w = oracle.gate_topk(oracle.gate_logits(x, wg), k, 0, 1)
+    count, slot_of, tos = oracle.dispatch(idx, E, cap)
+    xg = oracle.permute(x, tos).reshape(E, cap, H)
+    y = oracle.expert_ffn(xg, count, w1, w3, w2, 2)
+    out = oracle.combine(y, slot_of, w)
+    np.testing.assert_array_equal(r["slot_of"], slot_of)
+    np.testing.assert_allclose(r["out"], out, rtol=1e-5, atol=1e-7)
+    assert (r["slot_of"] < 0).any(), "cf = 1.0 must overflow somewhere in this case"
+
+
+def test_only_rows_is_a_slice_of_the_full_output(oracle):
+    S, H, I, E, k = 64, 64, 64, 4, 2
+    x, wg, w1, w3, w2 = make_inputs(S, H, I, E, seed=1, bf16=True, w_std=0.1)
+    full = oracle.moe_forward(x, wg, w1, None, w2, k=k, cap=40, hidden_act=1)["out"]
+    rows = np.array([3, 60, 17], np.int32)
+    part = oracle.moe_forward(x, wg, w1, None, w2, k=k, cap=40, hidden_act=1, only_rows=rows)["out"]
+    np.testing.assert_array_equal(part, full[rows])
+
+
+# ---- golden vectors -------------------------------------------------------------------------------------------------
+def test_golden_config1(oracle):
+    g = np.load(os.path.join(HERE, "golden", "config1_oracle.npz"))
+    np.testing.assert_allclose(oracle.fill_normal(16, 0.0, 1.0, 0, 0), g["philox_head"], rtol=0, atol=1e-6)
+    x, wg, w1, _, w2 = make_inputs(128, 256, 512, 8, seed=0, bf16=False)
+    np.testing.assert_array_equal(oracle.gate_logits(x, wg).view(np.uint32), g["logits_bits"])
+    r = oracle.moe_forward(x, wg, w1, None, w2, k=1, cap=16, hidden_act=0)
+    for name in ("topk_idx", "count", "slot_of", "token_of_slot"):
+        np.testing.assert_array_equal(r[name], g[name])
+    np.testing.assert_allclose(r["topk_w"], g["topk_w"], rtol=1e-6)
+    np.testing.assert_allclose(r["out"], g["out"], rtol=1e-5, atol=1e-8)
+    assert g["count"].max() == 16 and g["count"].sum() == (g["slot_of"] >= 0).sum() < 128   # cap 16, some drops
