@@ -1,0 +1,87 @@
+"""Expert-parallel forward on 2 (and 4) GPUs over NCCL, one process per GPU: every rank's routing must be bit-exact
+and its output within the bf16 tolerance of an independent single-rank oracle run over the global weights."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _worker(rank, world, uid, S, H, I, E, k, cf, act, q):
+    try:
+        sys.path.insert(0, ROOT)
+        sys.path.insert(0, os.path.join(ROOT, "tests"))
+        import torch
+        from helpers import TOL_BF16_MAX, TOL_BF16_MEAN, make_inputs, rel_errors, to_dev
+        from oracle import moe_oracle as O
+        import cuplayground_b200 as cp
+        import cuplayground_b200.layer as layer
+
+        torch.cuda.set_device(rank)
+        El = E // world
+        _, wg, w1, w3, w2 = make_inputs(S, H, I, E, seed=100, swiglu=(act == 2), w_std=0.05)     # shared weights
+        x = make_inputs(S, H, I, E, seed=200 + rank, w_std=0.05)[0]                              # this rank's tokens
+        loc = slice(rank * El, (rank + 1) * El)
+        cfg = cp.AristosConfig(capacity_factor=cf, drop_tokens=1, expert_top_k=k, hidden_act=act, hidden_size=H,
+                               intermediate_size=I, num_experts=E, torch_dtype=2, tokens=S, renorm_topk=1,
+                               ep_world=world)
+        dt = torch.bfloat16
+        L = layer.MoELayer(cfg, rank, world, uid)
+        dev = [to_dev(a, dt) for a in (x, wg, w1[loc], None if w3 is None else w3[loc], w2[loc])]
+        out = L.forward(*dev)
+        L.status()
+        out2 = L.forward(*dev)
+        L.status()
+        assert torch.equal(out, out2), "two forwards must agree bit for bit"
+        r = L.routing()
+        ref = O.moe_forward(x, wg, w1, w3, w2, k=k, cap=cfg.capacity, renorm=1, hidden_act=act)
+        for name in ("topk_idx", "count", "slot_of", "token_of_slot"):
+            assert np.array_equal(r[name].numpy(), ref[name]), name
+        mx, mean = rel_errors(out.float().cpu().numpy(), ref["out"])
+        assert mx < TOL_BF16_MAX and mean < TOL_BF16_MEAN, (mx, mean)
+        L.close()
+        q.put((rank, "ok"))
+    except Exception as e:      # pragma: no cover - reported to the parent
+        import traceback
+        q.put((rank, "".join(traceback.format_exception(e))))
+
+
+def _run(world, S, H, I, E, k, cf, act):
+    import torch
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    import torch.multiprocessing as mp
+    import cuplayground_b200.layer as layer
+    uid = layer.nccl_unique_id()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, world, uid, S, H, I, E, k, cf, act, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = []
+    try:
+        for _ in procs:
+            results.append(q.get(timeout=300))
+    finally:
+        for p in procs:
+            p.join(timeout=30)
+            if p.is_alive():
+                p.kill()
+    bad = [r for r in results if r[1] != "ok"]
+    assert not bad, bad[0][1]
+
+
+def test_expert_parallel_2gpu_single_window():
+    _run(2, S=1024, H=256, I=512, E=8, k=2, cf=1.25, act=2)       # cap 320: one row window
+
+
+def test_expert_parallel_2gpu_four_windows():
+    _run(2, S=4096, H=128, I=256, E=4, k=2, cf=1.0, act=1)        # cap 2048: four windows of 512 rows
+
+
+def test_expert_parallel_4gpu():
+    _run(4, S=1024, H=256, I=256, E=8, k=2, cf=1.0, act=0)
