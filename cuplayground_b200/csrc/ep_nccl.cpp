@@ -23,6 +23,7 @@ struct NcclApi {
     void* handle = nullptr;
     ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
     ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+    ncclResult_t (*CommInitRankConfig)(ncclComm_t*, int, ncclUniqueId, int, ncclConfig_t*) = nullptr;   // optional
     ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
     ncclResult_t (*Send)(const void*, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
     ncclResult_t (*Recv)(void*, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
@@ -55,6 +56,7 @@ NcclApi& api() {
     LOAD(GroupEnd, "ncclGroupEnd")
     LOAD(GetErrorString, "ncclGetErrorString")
 #undef LOAD
+    a.CommInitRankConfig = reinterpret_cast<decltype(a.CommInitRankConfig)>(dlsym(a.handle, "ncclCommInitRankConfig"));
     a.ok = true;
     return a;
 }
@@ -87,7 +89,7 @@ aristos_status_t ep_unique_id(void* out) {
     return ARISTOS_OK;
 }
 
-aristos_status_t ep_comm_create(const void* uid, int rank, int world, EpComm** out) {
+aristos_status_t ep_comm_create(const void* uid, int rank, int world, int max_ctas, EpComm** out) {
     if (!uid || !out || world < 2 || rank < 0 || rank >= world) return ARISTOS_ERR_INVALID_ARG;
     if (!api().ok) { set_last_error("libnccl.so.2 could not be loaded"); return ARISTOS_ERR_NCCL; }
     ncclUniqueId id;
@@ -95,7 +97,17 @@ aristos_status_t ep_comm_create(const void* uid, int rank, int world, EpComm** o
     EpComm* c = new EpComm();
     c->rank = rank;
     c->world = world;
-    ncclResult_t r = api().CommInitRank(&c->comm, world, id, rank);
+    ncclResult_t r;
+    if (max_ctas > 0 && api().CommInitRankConfig) {
+        // bound the CTAs of NCCL's copy kernels: they run beside the persistent GEMM grid, which leaves them that
+        // many SMs
+        ncclConfig_t config = NCCL_CONFIG_INITIALIZER;
+        config.maxCTAs = max_ctas;
+        config.minCTAs = 1;
+        r = api().CommInitRankConfig(&c->comm, world, id, rank, &config);
+    } else {
+        r = api().CommInitRank(&c->comm, world, id, rank);
+    }
     if (r != ncclSuccess) { delete c; return nccl_fail(r, "ncclCommInitRank"); }
     *out = c;
     return ARISTOS_OK;

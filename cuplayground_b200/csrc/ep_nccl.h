@@ -15,7 +15,8 @@ namespace aristos {
 struct EpComm;  // opaque
 
 aristos_status_t ep_unique_id(void* out_128_bytes);
-aristos_status_t ep_comm_create(const void* unique_id_128, int rank, int world, EpComm** out);
+// max_ctas > 0 bounds the CTAs NCCL's kernels may use (ncclConfig_t.maxCTAs); 0 = NCCL's default.
+aristos_status_t ep_comm_create(const void* unique_id_128, int rank, int world, int max_ctas, EpComm** out);
 void ep_comm_destroy(EpComm* c);
 
 // One transfer of an exchange: this rank sends `bytes` at send_offset of its send buffer to send_to and receives

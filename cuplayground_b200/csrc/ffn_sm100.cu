@@ -25,6 +25,10 @@
 // CTAs share B panels through L2). Nothing is read back to the host and empty tiles cost nothing.
 #include <cuda.h>
 
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+
 #include "common.cuh"
 #include "ptx_sm100.cuh"
 
@@ -65,6 +69,104 @@ struct FfnGemmParams {
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
     __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
     return *reinterpret_cast<uint32_t*>(&t);
+}
+
+// Epilogue of one tile for one thread (= one accumulator row): TMEM -> registers -> activation -> bf16 -> global.
+// The accumulator buffer is handed back (arrive on `tempty`, a CTA-local or shared::cluster address) as soon as the
+// last TMEM load has landed, before the last stores.
+__device__ __forceinline__ void epilogue_tile(const FfnGemmParams& p, int g, int m0, int n0, int row_in_tile,
+                                              uint32_t taddr, uint32_t tempty, bool tempty_is_cluster_addr) {
+    const int row = m0 + row_in_tile;
+    const int row_limit = min(p.count[g], p.row_end);
+    const bool row_ok = row < row_limit;
+    __nv_bfloat16* orow = p.out + ((size_t)g * p.rows_per_group + row) * p.N + n0;
+    if (p.gated) {
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+            uint32_t ga[32], up[32];
+            ptx::tmem_ld_32x32b_x32(taddr + c * 32, ga);
+            ptx::tmem_ld_32x32b_x32(taddr + 128 + c * 32, up);
+            ptx::tmem_ld_wait();
+            if (c == 3) {
+                ptx::tcgen05_fence_before();
+                if (tempty_is_cluster_addr) ptx::mbar_arrive_cluster(tempty); else ptx::mbar_arrive(tempty);
+            }
+            if (row_ok && n0 + c * 32 < p.N) {
+                uint32_t o[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float h0 = act_silu(__uint_as_float(ga[2 * i])) * __uint_as_float(up[2 * i]);
+                    const float h1 = act_silu(__uint_as_float(ga[2 * i + 1])) * __uint_as_float(up[2 * i + 1]);
+                    o[i] = pack_bf16(h0, h1);
+                }
+                uint4* dst = reinterpret_cast<uint4*>(orow + c * 32);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) dst[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+            }
+        }
+    } else {
+#pragma unroll 1
+        for (int c = 0; c < 8; ++c) {
+            uint32_t acc[32];
+            ptx::tmem_ld_32x32b_x32(taddr + c * 32, acc);
+            ptx::tmem_ld_wait();
+            if (c == 7) {
+                ptx::tcgen05_fence_before();
+                if (tempty_is_cluster_addr) ptx::mbar_arrive_cluster(tempty); else ptx::mbar_arrive(tempty);
+            }
+            if (row_ok && n0 + c * 32 < p.N) {
+                uint32_t o[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    float v0 = __uint_as_float(acc[2 * i]), v1 = __uint_as_float(acc[2 * i + 1]);
+                    if (p.act == ARISTOS_ACT_RELU) { v0 = act_relu(v0); v1 = act_relu(v1); }
+                    else if (p.act == ARISTOS_ACT_GELU) { v0 = act_gelu(v0); v1 = act_gelu(v1); }
+                    o[i] = pack_bf16(v0, v1);
+                }
+                uint4* dst = reinterpret_cast<uint4*>(orow + c * 32);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) dst[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+            }
+        }
+    }
+}
+
+// Pair variant: after the warp's last TMEM load one lane arrives on the first CTA's "accumulator free" barrier.
+__device__ __forceinline__ void epilogue_tile_pair(const FfnGemmParams& p, int g, int m0, int n0, int row_in_tile,
+                                                   uint32_t taddr, uint32_t tempty_cluster, int lane) {
+    const int row = m0 + row_in_tile;
+    const int row_limit = min(p.count[g], p.row_end);
+    const bool row_ok = row < row_limit;
+    __nv_bfloat16* orow = p.out + ((size_t)g * p.rows_per_group + row) * p.N + n0;
+    const int chunks = p.gated ? 4 : 8;
+#pragma unroll 1
+    for (int c = 0; c < chunks; ++c) {
+        uint32_t a[32], b[32];
+        ptx::tmem_ld_32x32b_x32(taddr + c * 32, a);
+        if (p.gated) ptx::tmem_ld_32x32b_x32(taddr + 128 + c * 32, b);
+        ptx::tmem_ld_wait();
+        if (c == chunks - 1) {
+            ptx::tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive_cluster(tempty_cluster);
+        }
+        if (row_ok && n0 + c * 32 < p.N) {
+            uint32_t o[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                float v0 = __uint_as_float(a[2 * i]), v1 = __uint_as_float(a[2 * i + 1]);
+                if (p.gated) {
+                    v0 = act_silu(v0) * __uint_as_float(b[2 * i]);
+                    v1 = act_silu(v1) * __uint_as_float(b[2 * i + 1]);
+                } else if (p.act == ARISTOS_ACT_RELU) { v0 = act_relu(v0); v1 = act_relu(v1); }
+                else if (p.act == ARISTOS_ACT_GELU) { v0 = act_gelu(v0); v1 = act_gelu(v1); }
+                o[i] = pack_bf16(v0, v1);
+            }
+            uint4* dst = reinterpret_cast<uint4*>(orow + c * 32);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) dst[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+        }
+    }
 }
 
 __global__ void __launch_bounds__(FFN_THREADS, 1)
@@ -216,60 +318,8 @@ ffn_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
             ok = __all_sync(0xffffffffu, ok);   // the TMEM loads below need the whole warp
             if (!ok) break;
             ptx::tcgen05_fence_after();
-            const int row = m0 + row_in_tile;
-            const int row_limit = min(p.count[g], p.row_end);
-            const bool row_ok = row < row_limit;
-            __nv_bfloat16* orow = p.out + ((size_t)g * p.rows_per_group + row) * p.N + n0;
-            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
-            if (p.gated) {
-#pragma unroll 1
-                for (int c = 0; c < 4; ++c) {
-                    uint32_t ga[32], up[32];
-                    ptx::tmem_ld_32x32b_x32(taddr + c * 32, ga);
-                    ptx::tmem_ld_32x32b_x32(taddr + 128 + c * 32, up);
-                    ptx::tmem_ld_wait();
-                    if (c == 3) {
-                        ptx::tcgen05_fence_before();
-                        ptx::mbar_arrive(bar_tempty + 8 * buf);
-                    }
-                    if (row_ok && n0 + c * 32 < p.N) {
-                        uint32_t o[16];
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) {
-                            const float h0 = act_silu(__uint_as_float(ga[2 * i])) * __uint_as_float(up[2 * i]);
-                            const float h1 = act_silu(__uint_as_float(ga[2 * i + 1])) * __uint_as_float(up[2 * i + 1]);
-                            o[i] = pack_bf16(h0, h1);
-                        }
-                        uint4* dst = reinterpret_cast<uint4*>(orow + c * 32);
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) dst[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
-                    }
-                }
-            } else {
-#pragma unroll 1
-                for (int c = 0; c < 8; ++c) {
-                    uint32_t acc[32];
-                    ptx::tmem_ld_32x32b_x32(taddr + c * 32, acc);
-                    ptx::tmem_ld_wait();
-                    if (c == 7) {
-                        ptx::tcgen05_fence_before();
-                        ptx::mbar_arrive(bar_tempty + 8 * buf);
-                    }
-                    if (row_ok && n0 + c * 32 < p.N) {
-                        uint32_t o[16];
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) {
-                            float v0 = __uint_as_float(acc[2 * i]), v1 = __uint_as_float(acc[2 * i + 1]);
-                            if (p.act == ARISTOS_ACT_RELU) { v0 = act_relu(v0); v1 = act_relu(v1); }
-                            else if (p.act == ARISTOS_ACT_GELU) { v0 = act_gelu(v0); v1 = act_gelu(v1); }
-                            o[i] = pack_bf16(v0, v1);
-                        }
-                        uint4* dst = reinterpret_cast<uint4*>(orow + c * 32);
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) dst[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
-                    }
-                }
-            }
+            epilogue_tile(p, g, m0, n0, row_in_tile, tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN,
+                          bar_tempty + 8 * buf, false);
         }
     }
 
@@ -278,6 +328,188 @@ ffn_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     if (warp == 1) {
         ptx::tcgen05_fence_after();
         ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+// ---- CTA-pair variant --------------------------------------------------------------------------------------------------
+// Two CTAs on the two SMs of a TPC work on one 256 x 256 tile with tcgen05 cta_group::2: each CTA stages its own 128
+// rows of A and its own 128 rows of B (for SwiGLU: CTA 0 the W1 rows, CTA 1 the W3 rows), the first CTA's MMA thread
+// issues M256 x N256 x K16 instructions that read both CTAs' shared memory, and each CTA's TMEM receives its 128 rows
+// of the accumulator. Per SM that halves the B bytes staged and read per FLOP (32 KB instead of 48 KB per stage,
+// six stages instead of four). Used when the row groups are large; small groups keep the single-CTA tiles.
+constexpr int P_STAGES = 6;
+constexpr int P_STAGE_BYTES = A_STAGE_BYTES + B_HALF_BYTES;     // 32 KB per CTA and stage
+constexpr int P_SMEM_BYTES = 1024 + P_STAGES * P_STAGE_BYTES + SMEM_AUX_BYTES;
+constexpr int PBM = 256;                                         // rows per pair tile
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(FFN_THREADS, 1)
+ffn_grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB0,
+                             const __grid_constant__ CUtensorMap tmB1, const FfnGemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* aux = smem + P_STAGES * P_STAGE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(aux);             // full[S], empty[S], tfull[2], tempty[2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aux + 128);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(aux + 132);
+    int* prefix = reinterpret_cast<int*>(aux + 256);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t cta = ptx::cluster_ctarank();                   // 0 = the CTA that issues the MMAs
+    const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+    const uint32_t bar_full = ptx::smem_u32(bars);                 // used in CTA 0 only
+    const uint32_t bar_empty = bar_full + 8 * P_STAGES;            // one per CTA
+    const uint32_t bar_tfull = bar_empty + 8 * P_STAGES;           // one per CTA
+    const uint32_t bar_tempty = bar_tfull + 16;                    // used in CTA 0 only
+    const uint32_t smem_base = ptx::smem_u32(smem);
+
+    const int out_w = p.gated ? 128 : 256;
+    const int n_tiles = (p.N + out_w - 1) / out_w;
+    const int window = p.row_end - p.row_begin;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < P_STAGES; ++s) {
+            ptx::mbar_init(bar_full + 8 * s, 1);
+            ptx::mbar_init(bar_empty + 8 * s, 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            ptx::mbar_init(bar_tfull + 8 * b, 1);
+            ptx::mbar_init(bar_tempty + 8 * b, 8);                 // one elected lane of 4 epilogue warps x 2 CTAs
+        }
+        *abort_flag = 0;
+        ptx::fence_mbar_init();
+    }
+    if (warp == 0) {
+        int running = 0;
+        if (lane == 0) prefix[0] = 0;
+        for (int g0 = 0; g0 < p.groups; g0 += 32) {
+            const int g = g0 + lane;
+            int v = 0;
+            if (g < p.groups) {
+                int rows = p.count[g] - p.row_begin;
+                rows = max(0, min(rows, window));
+                v = ((rows + PBM - 1) / PBM) * n_tiles;
+            }
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const int o = __shfl_up_sync(0xffffffffu, v, d);
+                if (lane >= d) v += o;
+            }
+            if (g < p.groups) prefix[g + 1] = running + v;
+            running += __shfl_sync(0xffffffffu, v, 31);
+        }
+    } else if (warp == 1) {
+        ptx::tmem_alloc_pair(ptx::smem_u32(tmem_slot), TMEM_COLS);
+    }
+    ptx::tcgen05_fence_before();
+    __syncthreads();
+    ptx::cluster_sync();               // both CTAs' barriers are initialised before anything signals them
+    ptx::tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const int total_tiles = prefix[p.groups];
+    const int kblocks = p.K / BK;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer (both CTAs)
+        if (lane == 0) {
+            ptx::prefetch_tensormap(&tmA);
+            ptx::prefetch_tensormap(&tmB0);
+            ptx::prefetch_tensormap(&tmB1);
+            const CUtensorMap* tmB = (cta == 0) ? &tmB0 : &tmB1;
+            const uint32_t full0 = ptx::mapa_shared(bar_full, 0);   // the full barriers live in CTA 0
+            int stage = 0;
+            uint32_t phase = 0;
+            int g = 0;
+            bool ok = true;
+            for (int tile = pair; ok && tile < total_tiles; tile += num_pairs) {
+                while (tile >= prefix[g + 1]) ++g;
+                const int local = tile - prefix[g];
+                const int mt = (prefix[g + 1] - prefix[g]) / n_tiles;
+                const int m0 = p.row_begin + (local % mt) * PBM + (int)cta * BM;
+                const int n0 = (local / mt) * out_w;
+                const int e = g % p.experts;
+                const int nb = p.gated ? n0 : n0 + (int)cta * 128;
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    ok = ptx::mbar_wait_bounded(bar_empty + 8 * stage, phase ^ 1u, abort_flag, p.dev_status);
+                    if (!ok) break;
+                    const uint32_t sa = smem_base + stage * P_STAGE_BYTES;
+                    if (cta == 0) ptx::mbar_arrive_expect_tx(bar_full + 8 * stage, 2 * P_STAGE_BYTES);
+                    ptx::tma_load_3d_pair(sa, &tmA, kb * BK, m0, g, full0 + 8 * stage);
+                    ptx::tma_load_3d_pair(sa + A_STAGE_BYTES, tmB, kb * BK, nb, e, full0 + 8 * stage);
+                    if (++stage == P_STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer (CTA 0 only)
+        if (lane == 0 && cta == 0) {
+            constexpr uint32_t idesc = ptx::umma_idesc_bf16(PBM, BN);
+            const uint32_t empty_peer = ptx::mapa_shared(bar_empty, 1);
+            const uint32_t tfull_peer = ptx::mapa_shared(bar_tfull, 1);
+            int stage = 0;
+            uint32_t phase = 0;
+            int it = 0;
+            bool ok = true;
+            for (int tile = pair; ok && tile < total_tiles; tile += num_pairs, ++it) {
+                const int buf = it & 1;
+                const uint32_t aphase = (it >> 1) & 1u;
+                ok = ptx::mbar_wait_bounded(bar_tempty + 8 * buf, aphase ^ 1u, abort_flag, p.dev_status);
+                if (!ok) break;
+                ptx::tcgen05_fence_after();
+                const uint32_t tmem_d = tmem_base + buf * BN;
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    ok = ptx::mbar_wait_bounded(bar_full + 8 * stage, phase, abort_flag, p.dev_status);
+                    if (!ok) break;
+                    ptx::tcgen05_fence_after();
+                    const uint32_t sa = smem_base + stage * P_STAGE_BYTES;
+                    const uint64_t da = ptx::umma_desc_k_sw128(sa);
+                    const uint64_t db = ptx::umma_desc_k_sw128(sa + A_STAGE_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        ptx::umma_f16_pair(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                    // release the stage in both CTAs
+                    ptx::umma_commit_pair(bar_empty + 8 * stage);
+                    ptx::umma_commit_pair(empty_peer + 8 * stage);
+                    if (++stage == P_STAGES) { stage = 0; phase ^= 1u; }
+                }
+                if (ok) {
+                    ptx::umma_commit_pair(bar_tfull + 8 * buf);
+                    ptx::umma_commit_pair(tfull_peer + 8 * buf);
+                }
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------------ epilogue (warps 2..5 of both CTAs)
+        const int quarter = warp & 3;
+        const int row_in_tile = quarter * 32 + lane;
+        const uint32_t tempty0 = ptx::mapa_shared(bar_tempty, 0);
+        int g = 0;
+        int it = 0;
+        bool ok = true;
+        for (int tile = pair; ok && tile < total_tiles; tile += num_pairs, ++it) {
+            while (tile >= prefix[g + 1]) ++g;
+            const int local = tile - prefix[g];
+            const int mt = (prefix[g + 1] - prefix[g]) / n_tiles;
+            const int m0 = p.row_begin + (local % mt) * PBM + (int)cta * BM;
+            const int n0 = (local / mt) * out_w;
+            const int buf = it & 1;
+            const uint32_t aphase = (it >> 1) & 1u;
+            ok = ptx::mbar_wait_bounded(bar_tfull + 8 * buf, aphase, abort_flag, p.dev_status);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            ptx::tcgen05_fence_after();
+            epilogue_tile_pair(p, g, m0, n0, row_in_tile,
+                               tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN, tempty0 + 8 * buf, lane);
+        }
+    }
+
+    ptx::tcgen05_fence_before();
+    __syncthreads();
+    ptx::cluster_sync();               // nobody leaves (or frees TMEM) while the other CTA may still signal it
+    if (warp == 1) {
+        ptx::tcgen05_fence_after();
+        ptx::tmem_dealloc_pair(tmem_base, TMEM_COLS);
     }
 }
 
@@ -317,22 +549,63 @@ aristos_status_t make_map_3d(CUtensorMap* tm, const void* base, int K, int rows,
     return ARISTOS_OK;
 }
 
+// Tile shape: CTA pairs (256-row tiles) pay off when the row groups are long; short groups would mostly pad them.
+// ARISTOS_FFN_TILES=single|pair overrides the choice (for measurements).
+bool use_pair_tiles(int window_rows) {
+    static int forced = -1;
+    if (forced < 0) {
+        const char* env = getenv("ARISTOS_FFN_TILES");
+        forced = !env ? 0 : (!strcmp(env, "pair") ? 2 : (!strcmp(env, "single") ? 1 : 0));
+    }
+    if (forced == 2) return true;
+    if (forced == 1) return false;
+    return window_rows >= 1024;
+}
+
 aristos_status_t launch_gemm(const void* A, const void* B0, const void* B1, const FfnGemmParams& p, int grid_limit,
                              cudaStream_t st) {
     CUtensorMap tmA, tmB0, tmB1;
     ARISTOS_TRY(make_map_3d(&tmA, A, p.K, p.rows_per_group, p.groups));
     ARISTOS_TRY(make_map_3d(&tmB0, B0, p.K, p.N, p.experts));
     ARISTOS_TRY(make_map_3d(&tmB1, B1, p.K, p.N, p.experts));
-    ARISTOS_CUDA_TRY(cudaFuncSetAttribute(ffn_grouped_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          SMEM_BYTES));
     const int out_w = p.gated ? 128 : 256;
-    const int64_t bound = (int64_t)p.groups * ceil_div(p.row_end - p.row_begin, BM) * ceil_div(p.N, out_w);
     int sms = device_sm_count();
     if (sms <= 0) { set_last_error("no CUDA device"); return ARISTOS_ERR_CUDA; }
     if (grid_limit > 0 && grid_limit < sms) sms = grid_limit;
-    const int grid = (int)(bound < sms ? bound : sms);
-    if (grid <= 0) return ARISTOS_OK;
-    ffn_grouped_gemm_kernel<<<grid, FFN_THREADS, SMEM_BYTES, st>>>(tmA, tmB0, tmB1, p);
+    const int window = p.row_end - p.row_begin;
+    if (use_pair_tiles(window)) {
+        ARISTOS_CUDA_TRY(cudaFuncSetAttribute(ffn_grouped_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                              P_SMEM_BYTES));
+        const int64_t bound = (int64_t)p.groups * ceil_div(window, PBM) * ceil_div(p.N, out_w);
+        // a persistent grid must be fully co-resident: ask how many 2-CTA clusters the device can hold at once
+        static int max_clusters = -1;
+        if (max_clusters < 0) {
+            cudaLaunchConfig_t lc = {};
+            lc.gridDim = dim3(2 * (device_sm_count() / 2));
+            lc.blockDim = dim3(FFN_THREADS);
+            lc.dynamicSmemBytes = P_SMEM_BYTES;
+            cudaLaunchAttribute at;
+            at.id = cudaLaunchAttributeClusterDimension;
+            at.val.clusterDim.x = 2; at.val.clusterDim.y = 1; at.val.clusterDim.z = 1;
+            lc.attrs = &at;
+            lc.numAttrs = 1;
+            int n = 0;
+            ARISTOS_CUDA_TRY(cudaOccupancyMaxActiveClusters(&n, ffn_grouped_gemm_pair_kernel, &lc));
+            max_clusters = n;
+            if (getenv("ARISTOS_DEBUG")) fprintf(stderr, "[aristos] co-resident 2-CTA clusters: %d\n", n);
+        }
+        int pairs = sms / 2 < max_clusters ? sms / 2 : max_clusters;
+        if (bound < pairs) pairs = (int)bound;
+        if (pairs <= 0) return ARISTOS_OK;
+        ffn_grouped_gemm_pair_kernel<<<2 * pairs, FFN_THREADS, P_SMEM_BYTES, st>>>(tmA, tmB0, tmB1, p);
+    } else {
+        ARISTOS_CUDA_TRY(cudaFuncSetAttribute(ffn_grouped_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                              SMEM_BYTES));
+        const int64_t bound = (int64_t)p.groups * ceil_div(window, BM) * ceil_div(p.N, out_w);
+        const int grid = (int)(bound < sms ? bound : sms);
+        if (grid <= 0) return ARISTOS_OK;
+        ffn_grouped_gemm_kernel<<<grid, FFN_THREADS, SMEM_BYTES, st>>>(tmA, tmB0, tmB1, p);
+    }
     ARISTOS_COUNT_LAUNCH();
     ARISTOS_CUDA_TRY(cudaGetLastError());
     return ARISTOS_OK;

@@ -153,19 +153,21 @@ aristos_status_t aristos_moe_create(const aristos_config_t* cfg, int rank, int w
     L->dispatch_scratch_bytes = aristos_dispatch_scratch_bytes(L->S, L->k, L->E);
     L->ws_bytes = plan_workspace(L, nullptr);
     if (world > 1) {
-        aristos_status_t s = ep_comm_create(nccl_unique_id, rank, world, &L->comm);
+        // SMs handed to NCCL's copy kernels while the persistent GEMM grid runs on the rest
+        int nccl_ctas = 8;
+        if (const char* env = getenv("ARISTOS_EP_NCCL_CTAS")) nccl_ctas = atoi(env);
+        aristos_status_t s = ep_comm_create(nccl_unique_id, rank, world, nccl_ctas, &L->comm);
         if (s != ARISTOS_OK) { delete L; return s; }
         cudaError_t e = cudaStreamCreateWithFlags(&L->comm_stream, cudaStreamNonBlocking);
         if (e == cudaSuccess) e = cudaEventCreateWithFlags(&L->ev_dispatched, cudaEventDisableTiming);
         if (e == cudaSuccess) e = cudaEventCreateWithFlags(&L->ev_returned, cudaEventDisableTiming);
         // row windows of the overlapped exchange
         ep_row_windows(L->cap, 4, 512, &L->chunk_rows, &L->chunks);
-        const char* env = getenv("ARISTOS_EP_CHUNKS");
-        if (env && atoi(env) >= 1) ep_row_windows(L->cap, atoi(env), 128, &L->chunk_rows, &L->chunks);
-        // leave SMs for the NCCL kernels that run beside the GEMMs
-        L->ffn_sm_limit = device_sm_count() - 16;
-        const char* env2 = getenv("ARISTOS_EP_FFN_SMS");
-        if (env2 && atoi(env2) >= 1) L->ffn_sm_limit = atoi(env2);
+        if (const char* env = getenv("ARISTOS_EP_CHUNKS"))
+            if (atoi(env) >= 1) ep_row_windows(L->cap, atoi(env), 128, &L->chunk_rows, &L->chunks);
+        L->ffn_sm_limit = device_sm_count() - (nccl_ctas > 0 ? nccl_ctas : 16);
+        if (const char* env = getenv("ARISTOS_EP_FFN_SMS"))
+            if (atoi(env) >= 1) L->ffn_sm_limit = atoi(env);
         L->ev_in.resize(L->chunks);
         L->ev_out.resize(L->chunks);
         for (int c = 0; c < L->chunks && e == cudaSuccess; ++c) {
