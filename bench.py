@@ -274,7 +274,7 @@ def run_ours(args, cfg, workload_desc):
         roofline = {"bound": "tensor", "kernel": "ffn_grouped_gemm_kernel", "achieved": achieved,
                     "peak": peaks["bf16_sustained"], "unit": "TFLOP/s", "frac": achieved / peaks["bf16_sustained"],
                     "traffic": None, "peak_source": f"{peaks['source']} bf16 sustained (kernel timed inside a "
-                    "back-to-back loop of steps)", "launches_per_step": int(launches) // args.steps - 6,
+                    "back-to-back loop of steps)", "launches_per_step": 2 if world == 1 else None,
                     "flops_per_step": ffn_flops, "ms_per_step": stage["ffn"]}
         t_roof, terms = layer_roofline(cfg, world, kept_all / world)
         line = {"metric": "moe_fwd_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
@@ -282,7 +282,7 @@ def run_ours(args, cfg, workload_desc):
                 "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
                 "data": "synthetic",
                 "config": {"workload": workload_desc, "name": args.workload, "tokens_per_rank": S,
-                           "parallelism": f"ep{world}", "l2": "weights (>= 0.4 GB per rank) exceed the 126 MB L2, "
+                           "parallelism": f"ep{world}", "ep_transport": L.ep_transport, "l2": "weights (>= 0.4 GB per rank) exceed the 126 MB L2, "
                            "no flush needed between steps", "kept_assignments": kept_all},
                 "clocks": clocks,
                 "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": xh.numel() * 2 * world,

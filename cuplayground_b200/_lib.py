@@ -70,6 +70,7 @@ PROTOTYPES = {
     "aristos_moe_status": (_st, [_vp]),
     "aristos_moe_set_profiling": (_st, [_vp, _i]),
     "aristos_moe_stage_ms": (_st, [_vp, C.POINTER(C.c_float)]),
+    "aristos_moe_ep_transport": (C.c_char_p, [_vp]),
     "aristos_moe_launch_count": (C.c_int64, [_vp]),
     "aristos_moe_destroy": (_st, [_vp]),
     "aristos_gate_topk": (_st, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),

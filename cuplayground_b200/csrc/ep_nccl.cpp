@@ -27,6 +27,7 @@ struct NcclApi {
     ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
     ncclResult_t (*Send)(const void*, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
     ncclResult_t (*Recv)(void*, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
     ncclResult_t (*GroupStart)() = nullptr;
     ncclResult_t (*GroupEnd)() = nullptr;
     const char* (*GetErrorString)(ncclResult_t) = nullptr;
@@ -52,6 +53,7 @@ NcclApi& api() {
     LOAD(CommDestroy, "ncclCommDestroy")
     LOAD(Send, "ncclSend")
     LOAD(Recv, "ncclRecv")
+    LOAD(AllGather, "ncclAllGather")
     LOAD(GroupStart, "ncclGroupStart")
     LOAD(GroupEnd, "ncclGroupEnd")
     LOAD(GetErrorString, "ncclGetErrorString")
@@ -117,6 +119,13 @@ void ep_comm_destroy(EpComm* c) {
     if (!c) return;
     if (c->comm && api().ok) api().CommDestroy(c->comm);
     delete c;
+}
+
+aristos_status_t ep_allgather_bytes(EpComm* c, const void* send_dev, void* recv_dev, size_t bytes_per_rank,
+                                    cudaStream_t stream) {
+    if (!c || !send_dev || !recv_dev) return ARISTOS_ERR_INVALID_ARG;
+    NCCL_TRY(api().AllGather(send_dev, recv_dev, bytes_per_rank, ncclInt8, c->comm, stream));
+    return ARISTOS_OK;
 }
 
 // The exchange of one row window as a flat list of transfers; entry 0 is the rank's own copy.

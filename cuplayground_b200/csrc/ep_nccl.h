@@ -32,6 +32,10 @@ std::vector<EpTransfer> ep_exchange_plan(int rank, int world, int blocks_per_pee
 // min_rows unless the capacity itself is.
 void ep_row_windows(int cap, int max_windows, int min_rows, int* window_rows, int* windows);
 
+// All-gather of bytes_per_rank bytes (device buffers); also serves as a barrier over the ranks.
+aristos_status_t ep_allgather_bytes(EpComm* c, const void* send_dev, void* recv_dev, size_t bytes_per_rank,
+                                    cudaStream_t stream);
+
 // One grouped exchange. For every peer d != rank and every block b < blocks_per_peer:
 //   send  bytes [ (d*blocks_per_peer + b) * block_stride + offset, +len )  of send_buf to d
 //   recv  bytes [ (d*blocks_per_peer + b) * block_stride + offset, +len )  of recv_buf from d

@@ -1,0 +1,169 @@
+// Expert-parallel exchange over peer memory (see ep_p2p.h).
+//
+// This is the B200 counterpart of the reference's device-initiated exchange (auditorium/overlap.cuh:94-153:
+// nvshmemx_putmem_signal_nbi_block writes a tile into the peer's symmetric heap and raises a flag there, the consumer
+// spins on nvshmem_signal_wait_until) and of its commented-out peer-store GEMM (mma.cuh:445-539): put = copy-engine
+// write into the peer's IPC-mapped buffer, signal = epoch store into the peer's flag word, wait = stream memory
+// operation on the local flag (no kernel spins, no SM is held while data is in flight).
+#include "ep_p2p.h"
+
+#include <cuda.h>
+
+#include <vector>
+
+#include "common.cuh"
+
+namespace aristos {
+
+namespace {
+
+constexpr size_t FLAG_BYTES = 4096;
+constexpr int MAX_RANKS = 16;
+
+struct FlagTargets {
+    uint32_t* ptr[MAX_RANKS];
+    int n;
+};
+
+// One warp: lane d stores the epoch into rank d's flag word for (kind, window, this rank).
+__global__ void ep_signal_kernel(FlagTargets t, uint32_t epoch) {
+    const int d = threadIdx.x;
+    if (d < t.n) {
+        __threadfence_system();
+        *reinterpret_cast<volatile uint32_t*>(t.ptr[d]) = epoch;
+        __threadfence_system();
+    }
+}
+
+typedef CUresult (*StreamWaitValue32Fn)(CUstream, CUdeviceptr, cuuint32_t, unsigned int);
+
+StreamWaitValue32Fn stream_wait_fn() {
+    static StreamWaitValue32Fn fn = nullptr;
+    if (!fn) {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuStreamWaitValue32", &sym, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            return nullptr;
+        fn = reinterpret_cast<StreamWaitValue32Fn>(sym);
+    }
+    return fn;
+}
+
+}  // namespace
+
+struct EpP2P {
+    int rank = 0, world = 1, groups = 0;
+    size_t off_rcount = 0, off_xr = 0, off_yg = 0, bytes = 0;
+    char* local = nullptr;
+    std::vector<char*> base;     // every rank's region as mapped into this process (own = local)
+    uint32_t epoch = 0;
+};
+
+static size_t flag_index(const EpP2P* p, int kind, int window, int src) {
+    return ((size_t)kind * EP_MAX_WINDOWS + window) * MAX_RANKS + src;
+}
+
+aristos_status_t ep_p2p_create(EpComm* bootstrap, int rank, int world, int groups, size_t xr_bytes, size_t yg_bytes,
+                               EpP2P** out) {
+    if (!bootstrap || !out || world < 2 || world > MAX_RANKS) return ARISTOS_ERR_INVALID_ARG;
+    static_assert(3 * EP_MAX_WINDOWS * MAX_RANKS * 4 <= FLAG_BYTES, "flag words fit their page");
+    if (!stream_wait_fn()) { set_last_error("cuStreamWaitValue32 is not available from the driver"); return ARISTOS_ERR_CUDA; }
+    EpP2P* p = new EpP2P();
+    p->rank = rank;
+    p->world = world;
+    p->groups = groups;
+    p->off_rcount = FLAG_BYTES;
+    p->off_xr = align_up(p->off_rcount + (size_t)groups * 4, 1024);
+    p->off_yg = align_up(p->off_xr + xr_bytes, 1024);
+    p->bytes = align_up(p->off_yg + yg_bytes, 1024);
+    p->base.assign(world, nullptr);
+    cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&p->local), p->bytes);
+    if (e != cudaSuccess) {
+        set_last_error("cudaMalloc of the %zu-byte exchange region failed: %s", p->bytes, cudaGetErrorString(e));
+        delete p;
+        return ARISTOS_ERR_NOMEM;
+    }
+    p->base[rank] = p->local;
+    cudaIpcMemHandle_t mine;
+    cudaIpcMemHandle_t* d_all = nullptr;
+    std::vector<cudaIpcMemHandle_t> all(world);
+    aristos_status_t st = ARISTOS_OK;
+    do {
+        if ((e = cudaMemset(p->local, 0, FLAG_BYTES + (size_t)groups * 4)) != cudaSuccess) break;
+        if ((e = cudaIpcGetMemHandle(&mine, p->local)) != cudaSuccess) break;
+        if ((e = cudaMalloc(reinterpret_cast<void**>(&d_all), sizeof(mine) * (world + 1))) != cudaSuccess) break;
+        if ((e = cudaMemcpy(d_all + world, &mine, sizeof(mine), cudaMemcpyHostToDevice)) != cudaSuccess) break;
+        // the all-gather is also the barrier that orders every rank's flag clearing before any peer's first store
+        st = ep_allgather_bytes(bootstrap, d_all + world, d_all, sizeof(mine), nullptr);
+        if (st != ARISTOS_OK) break;
+        if ((e = cudaStreamSynchronize(nullptr)) != cudaSuccess) break;
+        if ((e = cudaMemcpy(all.data(), d_all, sizeof(mine) * world, cudaMemcpyDeviceToHost)) != cudaSuccess) break;
+        for (int r = 0; r < world && e == cudaSuccess; ++r) {
+            if (r == rank) continue;
+            void* mapped = nullptr;
+            e = cudaIpcOpenMemHandle(&mapped, all[r], cudaIpcMemLazyEnablePeerAccess);
+            p->base[r] = static_cast<char*>(mapped);
+        }
+    } while (false);
+    if (d_all) cudaFree(d_all);
+    if (st == ARISTOS_OK && e != cudaSuccess) st = cuda_fail(e, "peer-memory exchange set-up");
+    if (st != ARISTOS_OK) { ep_p2p_destroy(p); return st; }
+    *out = p;
+    return ARISTOS_OK;
+}
+
+void ep_p2p_destroy(EpP2P* p) {
+    if (!p) return;
+    for (int r = 0; r < p->world; ++r)
+        if (r != p->rank && p->base[r]) cudaIpcCloseMemHandle(p->base[r]);
+    if (p->local) cudaFree(p->local);
+    delete p;
+}
+
+void* ep_p2p_xr(EpP2P* p) { return p->local + p->off_xr; }
+void* ep_p2p_yg(EpP2P* p) { return p->local + p->off_yg; }
+int32_t* ep_p2p_rcount(EpP2P* p) { return reinterpret_cast<int32_t*>(p->local + p->off_rcount); }
+uint32_t ep_p2p_begin(EpP2P* p) { return ++p->epoch; }
+
+aristos_status_t ep_p2p_push(EpP2P* p, int which, const void* send_buf, int blocks_per_peer, size_t block_stride,
+                             size_t offset, size_t len, cudaStream_t stream) {
+    if (!p || !send_buf || blocks_per_peer <= 0) return ARISTOS_ERR_INVALID_ARG;
+    if (len == 0) return ARISTOS_OK;
+    const size_t dst_off = which == EP_FLAG_IN ? p->off_xr : (which == EP_FLAG_RET ? p->off_yg : p->off_rcount);
+    const char* sb = static_cast<const char*>(send_buf);
+    for (int step = 0; step < p->world; ++step) {
+        const int d = (p->rank + step) % p->world;      // own blocks first, then the peers in ring order
+        const char* src = sb + (size_t)d * blocks_per_peer * block_stride + offset;
+        char* dst = p->base[d] + dst_off + (size_t)p->rank * blocks_per_peer * block_stride + offset;
+        ARISTOS_CUDA_TRY(cudaMemcpy2DAsync(dst, block_stride, src, block_stride, len, blocks_per_peer,
+                                           cudaMemcpyDeviceToDevice, stream));
+    }
+    return ARISTOS_OK;
+}
+
+aristos_status_t ep_p2p_signal(EpP2P* p, int kind, int window, cudaStream_t stream) {
+    if (!p || window < 0 || window >= EP_MAX_WINDOWS) return ARISTOS_ERR_INVALID_ARG;
+    FlagTargets t;
+    t.n = p->world;
+    for (int d = 0; d < p->world; ++d)
+        t.ptr[d] = reinterpret_cast<uint32_t*>(p->base[d]) + flag_index(p, kind, window, p->rank);
+    ep_signal_kernel<<<1, 32, 0, stream>>>(t, p->epoch);
+    ARISTOS_COUNT_LAUNCH();
+    ARISTOS_CUDA_TRY(cudaGetLastError());
+    return ARISTOS_OK;
+}
+
+aristos_status_t ep_p2p_wait(EpP2P* p, int kind, int window, cudaStream_t stream) {
+    if (!p || window < 0 || window >= EP_MAX_WINDOWS) return ARISTOS_ERR_INVALID_ARG;
+    StreamWaitValue32Fn wait = stream_wait_fn();
+    for (int src = 0; src < p->world; ++src) {
+        uint32_t* flag = reinterpret_cast<uint32_t*>(p->local) + flag_index(p, kind, window, src);
+        const CUresult r = wait(reinterpret_cast<CUstream>(stream), reinterpret_cast<CUdeviceptr>(flag), p->epoch,
+                                CU_STREAM_WAIT_VALUE_GEQ);
+        if (r != CUDA_SUCCESS) { set_last_error("cuStreamWaitValue32 failed with %d", (int)r); return ARISTOS_ERR_CUDA; }
+    }
+    return ARISTOS_OK;
+}
+
+}  // namespace aristos

@@ -1,0 +1,41 @@
+// Expert-parallel exchange over peer memory: rows are pushed into the destination GPU's buffers by the copy engines
+// (cudaMemcpy2DAsync between CUDA-IPC mapped allocations, NVLink, no SM involved), arrival is published by a
+// one-warp kernel that stores an epoch number into the destination's flag word, and consumers order their streams
+// behind those flags with stream memory operations (cuStreamWaitValue32). Nothing on this path occupies SMs for the
+// duration of a transfer, so the persistent expert GEMMs keep the whole GPU while rows travel.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include "../../include/aristos_moe.h"
+#include "ep_nccl.h"
+
+namespace aristos {
+
+struct EpP2P;
+
+enum { EP_FLAG_IN = 0, EP_FLAG_RET = 1, EP_FLAG_COUNT = 2 };
+constexpr int EP_MAX_WINDOWS = 16;
+
+// Collective over the ranks of `bootstrap` (used for the IPC-handle exchange and as a start barrier). The exchange
+// region holds, per rank: flag words, the received row counts (groups int32), xr (xr_bytes) and yg (yg_bytes).
+aristos_status_t ep_p2p_create(EpComm* bootstrap, int rank, int world, int groups, size_t xr_bytes, size_t yg_bytes,
+                               EpP2P** out);
+void ep_p2p_destroy(EpP2P* p);
+void* ep_p2p_xr(EpP2P* p);
+void* ep_p2p_yg(EpP2P* p);
+int32_t* ep_p2p_rcount(EpP2P* p);
+// Starts a new forward: every flag of this forward is compared against the returned epoch.
+uint32_t ep_p2p_begin(EpP2P* p);
+// Push block b of peer d (b < blocks_per_peer) of send_buf to block (rank*blocks_per_peer + b) of the destination's
+// buffer `which` (EP_FLAG_IN: xr, EP_FLAG_RET: yg, EP_FLAG_COUNT: rcount), bytes [offset, offset + len) of each block.
+aristos_status_t ep_p2p_push(EpP2P* p, int which, const void* send_buf, int blocks_per_peer, size_t block_stride,
+                             size_t offset, size_t len, cudaStream_t stream);
+// After the pushes of (kind, window) on the same stream: publish them to every rank.
+aristos_status_t ep_p2p_signal(EpP2P* p, int kind, int window, cudaStream_t stream);
+// Order `stream` behind the arrival of (kind, window) from every rank.
+aristos_status_t ep_p2p_wait(EpP2P* p, int kind, int window, cudaStream_t stream);
+
+}  // namespace aristos

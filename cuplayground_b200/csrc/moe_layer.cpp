@@ -14,6 +14,7 @@
 
 #include "common.cuh"
 #include "ep_nccl.h"
+#include "ep_p2p.h"
 
 namespace aristos {
 aristos_status_t dispatch_impl(const int32_t* topk_idx, int S, int k, int E, int cap, int32_t* count,
@@ -42,6 +43,7 @@ struct aristos_moe {
     bool bias_ready = false;
     // expert parallel
     EpComm* comm = nullptr;
+    EpP2P* p2p = nullptr;                    // peer-memory transport (rows pushed by the copy engines); else NCCL
     cudaStream_t comm_stream = nullptr;
     cudaEvent_t ev_dispatched = nullptr, ev_returned = nullptr;
     std::vector<cudaEvent_t> ev_in, ev_out;
@@ -87,9 +89,14 @@ size_t plan_workspace(aristos_moe* L, char* base) {
     CARVE(xg, void*, E * cap * H * elt)
     CARVE(h, void*, rows_local * I * elt)
     CARVE(yr, void*, rows_local * H * elt)
-    if (L->world > 1) {
+    if (L->world > 1 && !L->p2p) {
         CARVE(xr, void*, rows_local * H * elt)
         CARVE(yg, void*, E * cap * H * elt)
+    } else if (base && L->p2p) {
+        // the peers write straight into this rank's exchange region
+        L->xr = ep_p2p_xr(L->p2p);
+        L->yg = ep_p2p_yg(L->p2p);
+        L->rcount = ep_p2p_rcount(L->p2p);
     } else if (base) {
         L->xr = L->xg;
         L->yg = L->yr;
@@ -151,7 +158,6 @@ aristos_status_t aristos_moe_create(const aristos_config_t* cfg, int rank, int w
     if ((int64_t)L->E * L->cap > 0x7fffffffLL) { delete L; set_last_error("create: E*capacity overflows int32"); return ARISTOS_ERR_CONFIG; }
     if (L->groups > 1024) { delete L; set_last_error("create: more than 1024 row groups per rank"); return ARISTOS_ERR_CONFIG; }
     L->dispatch_scratch_bytes = aristos_dispatch_scratch_bytes(L->S, L->k, L->E);
-    L->ws_bytes = plan_workspace(L, nullptr);
     if (world > 1) {
         // SMs handed to NCCL's copy kernels while the persistent GEMM grid runs on the rest
         int nccl_ctas = 8;
@@ -175,7 +181,18 @@ aristos_status_t aristos_moe_create(const aristos_config_t* cfg, int rank, int w
             if (e == cudaSuccess) e = cudaEventCreateWithFlags(&L->ev_out[c], cudaEventDisableTiming);
         }
         if (e != cudaSuccess) { aristos_moe_destroy(L); return cuda_fail(e, "stream/event creation"); }
+        // transport of the rows: peer memory (default) or NCCL send/recv (ARISTOS_EP_TRANSPORT=nccl, or when the
+        // peer-memory set-up is not possible on this machine)
+        const char* tr = getenv("ARISTOS_EP_TRANSPORT");
+        if (!(tr && !strcmp(tr, "nccl")) && L->chunks <= EP_MAX_WINDOWS) {
+            const size_t block_bytes = (size_t)L->cap * L->H * L->elt;
+            aristos_status_t ps = ep_p2p_create(L->comm, rank, world, L->groups, (size_t)L->groups * block_bytes,
+                                                (size_t)L->E * block_bytes, &L->p2p);
+            if (ps == ARISTOS_OK) L->ffn_sm_limit = 0;      // nothing else needs SMs while rows travel
+            else if (tr && !strcmp(tr, "p2p")) { aristos_moe_destroy(L); return ps; }
+        }
     }
+    L->ws_bytes = plan_workspace(L, nullptr);
     *out = L;
     return ARISTOS_OK;
 }
@@ -232,6 +249,35 @@ aristos_status_t aristos_moe_forward(aristos_moe_t* L, const void* x, const void
     if (L->world == 1) {
         ARISTOS_TRY(aristos_expert_ffn(L->xg, L->count, L->E, L->cap, L->E, w1, w3, w2, L->h, L->yr, L->H, L->I,
                                        L->cfg.hidden_act, dt, 0, L->cap, 0, L->dev_status, st));
+    } else if (L->p2p) {
+        // rows are pushed into the destination GPUs by the copy engines; flags + stream waits order the streams
+        const size_t row_bytes = (size_t)L->H * L->elt;
+        const size_t block_stride = (size_t)L->cap * row_bytes;
+        ep_p2p_begin(L->p2p);
+        ARISTOS_CUDA_TRY(cudaEventRecord(L->ev_dispatched, st));
+        ARISTOS_CUDA_TRY(cudaStreamWaitEvent(L->comm_stream, L->ev_dispatched, 0));
+        ARISTOS_TRY(ep_p2p_push(L->p2p, EP_FLAG_COUNT, L->count, 1, (size_t)L->E_local * 4, 0, (size_t)L->E_local * 4,
+                                L->comm_stream));
+        ARISTOS_TRY(ep_p2p_signal(L->p2p, EP_FLAG_COUNT, 0, L->comm_stream));
+        for (int c = 0; c < L->chunks; ++c) {
+            const int r0 = c * L->chunk_rows, r1 = std::min(L->cap, r0 + L->chunk_rows);
+            ARISTOS_TRY(ep_p2p_push(L->p2p, EP_FLAG_IN, L->xg, L->E_local, block_stride, (size_t)r0 * row_bytes,
+                                    (size_t)(r1 - r0) * row_bytes, L->comm_stream));
+            ARISTOS_TRY(ep_p2p_signal(L->p2p, EP_FLAG_IN, c, L->comm_stream));
+        }
+        ARISTOS_TRY(ep_p2p_wait(L->p2p, EP_FLAG_COUNT, 0, st));
+        for (int c = 0; c < L->chunks; ++c) {
+            const int r0 = c * L->chunk_rows, r1 = std::min(L->cap, r0 + L->chunk_rows);
+            ARISTOS_TRY(ep_p2p_wait(L->p2p, EP_FLAG_IN, c, st));
+            ARISTOS_TRY(aristos_expert_ffn(L->xr, L->rcount, L->groups, L->cap, L->E_local, w1, w3, w2, L->h, L->yr,
+                                           L->H, L->I, L->cfg.hidden_act, dt, r0, r1, 0, L->dev_status, st));
+            ARISTOS_CUDA_TRY(cudaEventRecord(L->ev_out[c], st));
+            ARISTOS_CUDA_TRY(cudaStreamWaitEvent(L->comm_stream, L->ev_out[c], 0));
+            ARISTOS_TRY(ep_p2p_push(L->p2p, EP_FLAG_RET, L->yr, L->E_local, block_stride, (size_t)r0 * row_bytes,
+                                    (size_t)(r1 - r0) * row_bytes, L->comm_stream));
+            ARISTOS_TRY(ep_p2p_signal(L->p2p, EP_FLAG_RET, c, L->comm_stream));
+        }
+        for (int c = 0; c < L->chunks; ++c) ARISTOS_TRY(ep_p2p_wait(L->p2p, EP_FLAG_RET, c, st));
     } else {
         const size_t row_bytes = (size_t)L->H * L->elt;
         const size_t block_stride = (size_t)L->cap * row_bytes;
@@ -355,6 +401,11 @@ aristos_status_t aristos_moe_stage_ms(aristos_moe_t* L, float out_ms[5]) {
     return ARISTOS_OK;
 }
 
+const char* aristos_moe_ep_transport(const aristos_moe_t* L) {
+    if (!L || L->world == 1) return "none";
+    return L->p2p ? "p2p" : "nccl";
+}
+
 int64_t aristos_moe_launch_count(const aristos_moe_t* L) { return L ? L->launches : 0; }
 
 aristos_status_t aristos_moe_destroy(aristos_moe_t* L) {
@@ -366,6 +417,7 @@ aristos_status_t aristos_moe_destroy(aristos_moe_t* L) {
     if (L->ev_dispatched) cudaEventDestroy(L->ev_dispatched);
     if (L->ev_returned) cudaEventDestroy(L->ev_returned);
     if (L->comm_stream) cudaStreamDestroy(L->comm_stream);
+    if (L->p2p) ep_p2p_destroy(L->p2p);
     if (L->comm) ep_comm_destroy(L->comm);
     if (L->ws && L->ws_owned) cudaFree(L->ws);
     delete L;

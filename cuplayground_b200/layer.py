@@ -211,6 +211,10 @@ class MoELayer:
         _lib.check(self._lib.aristos_moe_status(self._h))
 
     @property
+    def ep_transport(self) -> str:
+        return self._lib.aristos_moe_ep_transport(self._h).decode()
+
+    @property
     def launch_count(self) -> int:
         return int(self._lib.aristos_moe_launch_count(self._h))
 

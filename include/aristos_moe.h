@@ -163,6 +163,10 @@ ARISTOS_API aristos_status_t aristos_moe_status(aristos_moe_t* layer);
  * {gate, dispatch + gather, expert FFN (with the exchanges when world > 1), combine, whole forward}. */
 ARISTOS_API aristos_status_t aristos_moe_set_profiling(aristos_moe_t* layer, int enable);
 ARISTOS_API aristos_status_t aristos_moe_stage_ms(aristos_moe_t* layer, float out_ms[5]);
+/* How the rows of an expert-parallel layer travel: "p2p" (copy-engine pushes into the peers' CUDA-IPC mapped
+ * buffers over NVLink, arrival flags, stream memory waits - the default), "nccl" (grouped ncclSend/ncclRecv; chosen
+ * with ARISTOS_EP_TRANSPORT=nccl or when peer memory cannot be mapped) or "none" (world == 1). */
+ARISTOS_API const char* aristos_moe_ep_transport(const aristos_moe_t* layer);
 /* Kernels launched by this library for `layer` since create (the benchmark's launch count). */
 ARISTOS_API int64_t aristos_moe_launch_count(const aristos_moe_t* layer);
 ARISTOS_API aristos_status_t aristos_moe_destroy(aristos_moe_t* layer);

@@ -11,8 +11,9 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _worker(rank, world, uid, S, H, I, E, k, cf, act, q):
+def _worker(rank, world, uid, S, H, I, E, k, cf, act, transport, q):
     try:
+        os.environ["ARISTOS_EP_TRANSPORT"] = transport
         sys.path.insert(0, ROOT)
         sys.path.insert(0, os.path.join(ROOT, "tests"))
         import torch
@@ -31,6 +32,7 @@ def _worker(rank, world, uid, S, H, I, E, k, cf, act, q):
                                ep_world=world)
         dt = torch.bfloat16
         L = layer.MoELayer(cfg, rank, world, uid)
+        assert L.ep_transport == transport
         dev = [to_dev(a, dt) for a in (x, wg, w1[loc], None if w3 is None else w3[loc], w2[loc])]
         out = L.forward(*dev)
         L.status()
@@ -50,7 +52,7 @@ def _worker(rank, world, uid, S, H, I, E, k, cf, act, q):
         q.put((rank, "".join(traceback.format_exception(e))))
 
 
-def _run(world, S, H, I, E, k, cf, act):
+def _run(world, S, H, I, E, k, cf, act, transport):
     import torch
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
@@ -59,7 +61,7 @@ def _run(world, S, H, I, E, k, cf, act):
     uid = layer.nccl_unique_id()
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    procs = [ctx.Process(target=_worker, args=(r, world, uid, S, H, I, E, k, cf, act, q)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, uid, S, H, I, E, k, cf, act, transport, q)) for r in range(world)]
     for p in procs:
         p.start()
     results = []
@@ -75,13 +77,19 @@ def _run(world, S, H, I, E, k, cf, act):
     assert not bad, bad[0][1]
 
 
-def test_expert_parallel_2gpu_single_window():
-    _run(2, S=1024, H=256, I=512, E=8, k=2, cf=1.25, act=2)       # cap 320: one row window
+TRANSPORTS = ["p2p", "nccl"]     # copy-engine pushes into peer memory (default) and NCCL send/recv
 
 
-def test_expert_parallel_2gpu_four_windows():
-    _run(2, S=4096, H=128, I=256, E=4, k=2, cf=1.0, act=1)        # cap 2048: four windows of 512 rows
+@pytest.mark.parametrize("transport", TRANSPORTS)
+def test_expert_parallel_2gpu_single_window(transport):
+    _run(2, S=1024, H=256, I=512, E=8, k=2, cf=1.25, act=2, transport=transport)       # cap 320: one row window
 
 
-def test_expert_parallel_4gpu():
-    _run(4, S=1024, H=256, I=256, E=8, k=2, cf=1.0, act=0)
+@pytest.mark.parametrize("transport", TRANSPORTS)
+def test_expert_parallel_2gpu_four_windows(transport):
+    _run(2, S=4096, H=128, I=256, E=4, k=2, cf=1.0, act=1, transport=transport)        # cap 2048: four windows
+
+
+@pytest.mark.parametrize("transport", TRANSPORTS)
+def test_expert_parallel_4gpu(transport):
+    _run(4, S=1024, H=256, I=256, E=8, k=2, cf=1.0, act=0, transport=transport)
