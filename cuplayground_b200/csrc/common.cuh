@@ -80,7 +80,7 @@ __device__ __forceinline__ void store8(float* p, const float (&v)[8]) {
 
 __device__ __forceinline__ float act_relu(float v) { return v > 0.0f ? v : 0.0f; }
 __device__ __forceinline__ float act_gelu(float v) { return 0.5f * v * (1.0f + erff(v * 0.70710678118654752440f)); }
-__device__ __forceinline__ float act_silu(float v) { return v / (1.0f + __expf(-v)); }
+__device__ __forceinline__ float act_silu(float v) { return __fdividef(v, 1.0f + __expf(-v)); }
 #endif
 
 }  // namespace aristos

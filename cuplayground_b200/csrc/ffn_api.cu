@@ -31,6 +31,10 @@ extern "C" aristos_status_t aristos_expert_ffn(const void* xg, const int32_t* co
         set_last_error("expert_ffn: pointers must be 16-byte aligned");
         return ARISTOS_ERR_INVALID_ARG;
     }
+    if (row_end % 128 != 0 && row_end != rows_per_group) {
+        set_last_error("expert_ffn: row_end must be a multiple of 128 or equal to rows_per_group");
+        return ARISTOS_ERR_INVALID_ARG;
+    }
     if (groups == 0 || row_end == row_begin) return ARISTOS_OK;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     switch (dtype) {

@@ -50,7 +50,8 @@ constexpr int EPI_THREADS = 128;
 constexpr int TMEM_COLS = 512;   // two 256-column accumulators
 constexpr int MAX_GROUPS = 1024;
 constexpr int SMEM_AUX_BYTES = 256 + (MAX_GROUPS + 1) * 4;
-constexpr int SMEM_BYTES = 1024 /*alignment slack*/ + STAGES * STAGE_BYTES + SMEM_AUX_BYTES;
+constexpr int STAGING_BYTES = 128 * 128;   // 128 rows x 64 bf16 of epilogue output, 128-byte swizzled
+constexpr int SMEM_BYTES = 1024 /*alignment slack*/ + STAGES * STAGE_BYTES + STAGING_BYTES + SMEM_AUX_BYTES;
 
 struct FfnGemmParams {
     const int32_t* count;   // valid rows per group
@@ -71,86 +72,40 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
     return *reinterpret_cast<uint32_t*>(&t);
 }
 
-// Epilogue of one tile for one thread (= one accumulator row): TMEM -> registers -> activation -> bf16 -> global.
-// The accumulator buffer is handed back (arrive on `tempty`, a CTA-local or shared::cluster address) as soon as the
-// last TMEM load has landed, before the last stores.
-__device__ __forceinline__ void epilogue_tile(const FfnGemmParams& p, int g, int m0, int n0, int row_in_tile,
-                                              uint32_t taddr, uint32_t tempty, bool tempty_is_cluster_addr) {
-    const int row = m0 + row_in_tile;
+// Epilogue of one 128-row tile, run by the four epilogue warps of a CTA (thread = accumulator row): TMEM -> registers
+// -> activation -> bf16 -> 128-byte-swizzled shared staging (64 output columns at a time) -> TMA store. The
+// accumulator buffer is handed back as soon as the last TMEM load has landed. A tile that lies entirely at or past
+// the group's valid rows stores nothing; a partly valid tile stores all of its 128 rows (the extra rows hold
+// unspecified values, never past the group's row capacity: the tensor map clips them).
+template <bool PAIR>
+__device__ __forceinline__ void epilogue_tile(const FfnGemmParams& p, const CUtensorMap* tmOut, int g, int m0, int n0,
+                                              int row_in_tile, uint32_t taddr, uint32_t tempty, int lane,
+                                              int epi_tid, uint32_t staging) {
     const int row_limit = min(p.count[g], p.row_end);
-    const bool row_ok = row < row_limit;
-    __nv_bfloat16* orow = p.out + ((size_t)g * p.rows_per_group + row) * p.N + n0;
-    if (p.gated) {
+    const bool tile_live = m0 < row_limit;
+    const int nchunk = p.gated ? 2 : 4;              // 64-column chunks of the output tile
+    const uint32_t my_row = staging + row_in_tile * 128;
+    const int sw = row_in_tile & 7;
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-            uint32_t ga[32], up[32];
-            ptx::tmem_ld_32x32b_x32(taddr + c * 32, ga);
-            ptx::tmem_ld_32x32b_x32(taddr + 128 + c * 32, up);
+    for (int c = 0; c < nchunk; ++c) {
+        if (epi_tid == 0) ptx::bulk_wait_group_read0();      // the previous store has drained the staging buffer
+        ptx::named_barrier_sync(1, EPI_THREADS);
+#pragma unroll
+        for (int hlf = 0; hlf < 2; ++hlf) {
+            const int col = c * 64 + hlf * 32;
+            uint32_t a[32], b[32];
+            ptx::tmem_ld_32x32b_x32(taddr + col, a);
+            if (p.gated) ptx::tmem_ld_32x32b_x32(taddr + 128 + col, b);
             ptx::tmem_ld_wait();
-            if (c == 3) {
+            if (c == nchunk - 1 && hlf == 1) {
                 ptx::tcgen05_fence_before();
-                if (tempty_is_cluster_addr) ptx::mbar_arrive_cluster(tempty); else ptx::mbar_arrive(tempty);
-            }
-            if (row_ok && n0 + c * 32 < p.N) {
-                uint32_t o[16];
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const float h0 = act_silu(__uint_as_float(ga[2 * i])) * __uint_as_float(up[2 * i]);
-                    const float h1 = act_silu(__uint_as_float(ga[2 * i + 1])) * __uint_as_float(up[2 * i + 1]);
-                    o[i] = pack_bf16(h0, h1);
+                if (PAIR) {
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive_cluster(tempty);
+                } else {
+                    ptx::mbar_arrive(tempty);
                 }
-                uint4* dst = reinterpret_cast<uint4*>(orow + c * 32);
-#pragma unroll
-                for (int i = 0; i < 4; ++i) dst[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
             }
-        }
-    } else {
-#pragma unroll 1
-        for (int c = 0; c < 8; ++c) {
-            uint32_t acc[32];
-            ptx::tmem_ld_32x32b_x32(taddr + c * 32, acc);
-            ptx::tmem_ld_wait();
-            if (c == 7) {
-                ptx::tcgen05_fence_before();
-                if (tempty_is_cluster_addr) ptx::mbar_arrive_cluster(tempty); else ptx::mbar_arrive(tempty);
-            }
-            if (row_ok && n0 + c * 32 < p.N) {
-                uint32_t o[16];
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    float v0 = __uint_as_float(acc[2 * i]), v1 = __uint_as_float(acc[2 * i + 1]);
-                    if (p.act == ARISTOS_ACT_RELU) { v0 = act_relu(v0); v1 = act_relu(v1); }
-                    else if (p.act == ARISTOS_ACT_GELU) { v0 = act_gelu(v0); v1 = act_gelu(v1); }
-                    o[i] = pack_bf16(v0, v1);
-                }
-                uint4* dst = reinterpret_cast<uint4*>(orow + c * 32);
-#pragma unroll
-                for (int i = 0; i < 4; ++i) dst[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
-            }
-        }
-    }
-}
-
-// Pair variant: after the warp's last TMEM load one lane arrives on the first CTA's "accumulator free" barrier.
-__device__ __forceinline__ void epilogue_tile_pair(const FfnGemmParams& p, int g, int m0, int n0, int row_in_tile,
-                                                   uint32_t taddr, uint32_t tempty_cluster, int lane) {
-    const int row = m0 + row_in_tile;
-    const int row_limit = min(p.count[g], p.row_end);
-    const bool row_ok = row < row_limit;
-    __nv_bfloat16* orow = p.out + ((size_t)g * p.rows_per_group + row) * p.N + n0;
-    const int chunks = p.gated ? 4 : 8;
-#pragma unroll 1
-    for (int c = 0; c < chunks; ++c) {
-        uint32_t a[32], b[32];
-        ptx::tmem_ld_32x32b_x32(taddr + c * 32, a);
-        if (p.gated) ptx::tmem_ld_32x32b_x32(taddr + 128 + c * 32, b);
-        ptx::tmem_ld_wait();
-        if (c == chunks - 1) {
-            ptx::tcgen05_fence_before();
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive_cluster(tempty_cluster);
-        }
-        if (row_ok && n0 + c * 32 < p.N) {
             uint32_t o[16];
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
@@ -162,19 +117,29 @@ __device__ __forceinline__ void epilogue_tile_pair(const FfnGemmParams& p, int g
                 else if (p.act == ARISTOS_ACT_GELU) { v0 = act_gelu(v0); v1 = act_gelu(v1); }
                 o[i] = pack_bf16(v0, v1);
             }
-            uint4* dst = reinterpret_cast<uint4*>(orow + c * 32);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) dst[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+            for (int i = 0; i < 4; ++i) {
+                const int j = hlf * 4 + i;               // 16-byte chunk of the 128-byte staging row
+                ptx::st_shared_v4(my_row + ((j ^ sw) << 4), o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+            }
+        }
+        ptx::fence_proxy_async_shared();
+        ptx::named_barrier_sync(1, EPI_THREADS);
+        if (epi_tid == 0 && tile_live && n0 + c * 64 < p.N) {
+            ptx::tma_store_3d(tmOut, staging, n0 + c * 64, m0, g);
+            ptx::bulk_commit_group();
         }
     }
 }
 
 __global__ void __launch_bounds__(FFN_THREADS, 1)
 ffn_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB0,
-                        const __grid_constant__ CUtensorMap tmB1, const FfnGemmParams p) {
+                        const __grid_constant__ CUtensorMap tmB1, const __grid_constant__ CUtensorMap tmOut,
+                        const FfnGemmParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t* aux = smem + STAGES * STAGE_BYTES;
+    const uint32_t staging = ptx::smem_u32(smem + STAGES * STAGE_BYTES);
+    uint8_t* aux = smem + STAGES * STAGE_BYTES + STAGING_BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(aux);             // full[S], empty[S], tfull[2], tempty[2]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aux + 128);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(aux + 132);
@@ -303,6 +268,7 @@ ffn_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         // ------------------------------------------------------------------ epilogue (warps 2..5)
         const int quarter = warp & 3;                 // TMEM lanes this warp may read
         const int row_in_tile = quarter * 32 + lane;
+        const int epi_tid = threadIdx.x - 64;
         int g = 0;
         int it = 0;
         bool ok = true;
@@ -315,12 +281,15 @@ ffn_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
             const int buf = it & 1;
             const uint32_t aphase = (it >> 1) & 1u;
             ok = ptx::mbar_wait_bounded(bar_tfull + 8 * buf, aphase, abort_flag, p.dev_status);
-            ok = __all_sync(0xffffffffu, ok);   // the TMEM loads below need the whole warp
+            // the tile's epilogue synchronises the four warps: they must agree on leaving
+            ok = !ptx::named_barrier_or(2, EPI_THREADS, !ok);
             if (!ok) break;
             ptx::tcgen05_fence_after();
-            epilogue_tile(p, g, m0, n0, row_in_tile, tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN,
-                          bar_tempty + 8 * buf, false);
+            epilogue_tile<false>(p, &tmOut, g, m0, n0, row_in_tile,
+                                 tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN,
+                                 bar_tempty + 8 * buf, lane, epi_tid, staging);
         }
+        if (epi_tid == 0) ptx::bulk_wait_group0();
     }
 
     ptx::tcgen05_fence_before();
@@ -339,15 +308,17 @@ ffn_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
 // six stages instead of four). Used when the row groups are large; small groups keep the single-CTA tiles.
 constexpr int P_STAGES = 6;
 constexpr int P_STAGE_BYTES = A_STAGE_BYTES + B_HALF_BYTES;     // 32 KB per CTA and stage
-constexpr int P_SMEM_BYTES = 1024 + P_STAGES * P_STAGE_BYTES + SMEM_AUX_BYTES;
+constexpr int P_SMEM_BYTES = 1024 + P_STAGES * P_STAGE_BYTES + STAGING_BYTES + SMEM_AUX_BYTES;
 constexpr int PBM = 256;                                         // rows per pair tile
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(FFN_THREADS, 1)
 ffn_grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB0,
-                             const __grid_constant__ CUtensorMap tmB1, const FfnGemmParams p) {
+                             const __grid_constant__ CUtensorMap tmB1, const __grid_constant__ CUtensorMap tmOut,
+                             const FfnGemmParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t* aux = smem + P_STAGES * P_STAGE_BYTES;
+    const uint32_t staging = ptx::smem_u32(smem + P_STAGES * P_STAGE_BYTES);
+    uint8_t* aux = smem + P_STAGES * P_STAGE_BYTES + STAGING_BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(aux);             // full[S], empty[S], tfull[2], tempty[2]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aux + 128);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(aux + 132);
@@ -483,6 +454,7 @@ ffn_grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gr
         // ------------------------------------------------------------------ epilogue (warps 2..5 of both CTAs)
         const int quarter = warp & 3;
         const int row_in_tile = quarter * 32 + lane;
+        const int epi_tid = threadIdx.x - 64;
         const uint32_t tempty0 = ptx::mapa_shared(bar_tempty, 0);
         int g = 0;
         int it = 0;
@@ -496,12 +468,14 @@ ffn_grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gr
             const int buf = it & 1;
             const uint32_t aphase = (it >> 1) & 1u;
             ok = ptx::mbar_wait_bounded(bar_tfull + 8 * buf, aphase, abort_flag, p.dev_status);
-            ok = __all_sync(0xffffffffu, ok);
+            ok = !ptx::named_barrier_or(2, EPI_THREADS, !ok);
             if (!ok) break;
             ptx::tcgen05_fence_after();
-            epilogue_tile_pair(p, g, m0, n0, row_in_tile,
-                               tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN, tempty0 + 8 * buf, lane);
+            epilogue_tile<true>(p, &tmOut, g, m0, n0, row_in_tile,
+                                tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN, tempty0 + 8 * buf,
+                                lane, epi_tid, staging);
         }
+        if (epi_tid == 0) ptx::bulk_wait_group0();
     }
 
     ptx::tcgen05_fence_before();
@@ -564,10 +538,11 @@ bool use_pair_tiles(int window_rows) {
 
 aristos_status_t launch_gemm(const void* A, const void* B0, const void* B1, const FfnGemmParams& p, int grid_limit,
                              cudaStream_t st) {
-    CUtensorMap tmA, tmB0, tmB1;
+    CUtensorMap tmA, tmB0, tmB1, tmOut;
     ARISTOS_TRY(make_map_3d(&tmA, A, p.K, p.rows_per_group, p.groups));
     ARISTOS_TRY(make_map_3d(&tmB0, B0, p.K, p.N, p.experts));
     ARISTOS_TRY(make_map_3d(&tmB1, B1, p.K, p.N, p.experts));
+    ARISTOS_TRY(make_map_3d(&tmOut, p.out, p.N, p.rows_per_group, p.groups));
     const int out_w = p.gated ? 128 : 256;
     int sms = device_sm_count();
     if (sms <= 0) { set_last_error("no CUDA device"); return ARISTOS_ERR_CUDA; }
@@ -597,14 +572,14 @@ aristos_status_t launch_gemm(const void* A, const void* B0, const void* B1, cons
         int pairs = sms / 2 < max_clusters ? sms / 2 : max_clusters;
         if (bound < pairs) pairs = (int)bound;
         if (pairs <= 0) return ARISTOS_OK;
-        ffn_grouped_gemm_pair_kernel<<<2 * pairs, FFN_THREADS, P_SMEM_BYTES, st>>>(tmA, tmB0, tmB1, p);
+        ffn_grouped_gemm_pair_kernel<<<2 * pairs, FFN_THREADS, P_SMEM_BYTES, st>>>(tmA, tmB0, tmB1, tmOut, p);
     } else {
         ARISTOS_CUDA_TRY(cudaFuncSetAttribute(ffn_grouped_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                               SMEM_BYTES));
         const int64_t bound = (int64_t)p.groups * ceil_div(window, BM) * ceil_div(p.N, out_w);
         const int grid = (int)(bound < sms ? bound : sms);
         if (grid <= 0) return ARISTOS_OK;
-        ffn_grouped_gemm_kernel<<<grid, FFN_THREADS, SMEM_BYTES, st>>>(tmA, tmB0, tmB1, p);
+        ffn_grouped_gemm_kernel<<<grid, FFN_THREADS, SMEM_BYTES, st>>>(tmA, tmB0, tmB1, tmOut, p);
     }
     ARISTOS_COUNT_LAUNCH();
     ARISTOS_CUDA_TRY(cudaGetLastError());

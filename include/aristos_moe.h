@@ -204,7 +204,9 @@ ARISTOS_API aristos_status_t aristos_permute(const void* x, const int32_t* slot_
                                              void* xg, void* stream);
 /*
  * Expert FFN over `groups` row groups of `rows_per_group` rows each; group g uses expert (g % experts) and has
- * count[g] valid rows. Only rows in [row_begin, row_end) of every group are computed (row_begin % 128 == 0).
+ * count[g] valid rows. Only rows in [row_begin, row_end) of every group are computed (row_begin % 128 == 0; row_end a
+ * multiple of 128 or equal to rows_per_group). Rows of y and h_scratch between count[g] and the end of the 128-row
+ * tile that holds row count[g] - 1 may be overwritten with unspecified values; rows past that tile are not touched.
  *   h = act(xg * w1^T) or silu(xg * w1^T) * (xg * w3^T);   y = h * w2^T
  * Replaces fGET / deviceCollectiveMMA (mma.cuh:46-179, :198-369), BlockMM (processor/tiling.cuh:273-323) and the
  * in-kernel schedulers sK / wScheduler (auditorium/scheduling.cuh:202-265, warpScheduler.cuh:267-344).
