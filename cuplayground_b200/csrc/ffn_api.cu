@@ -1,5 +1,6 @@
 // aristos_expert_ffn: argument checks and the per-dtype kernels behind the C ABI.
 #include "common.cuh"
+#include "ptx_sm100.cuh"
 
 namespace aristos {
 aristos_status_t expert_ffn_bf16_sm100(const void* xg, const int32_t* count, int groups, int rows_per_group,
@@ -48,4 +49,49 @@ extern "C" aristos_status_t aristos_expert_ffn(const void* xg, const int32_t* co
             set_last_error("expert_ffn: dtype %d not implemented (f32 and bf16 are)", dtype);
             return ARISTOS_ERR_UNSUPPORTED;
     }
+}
+
+// ---- self-test of the bounded device-side wait ------------------------------------------------------------------------
+namespace aristos {
+namespace {
+// One warp waits on an mbarrier that nothing ever arrives on, with the same wait routine the GEMM roles use; the wait
+// must give up after limit_ns, report DEV_FAULT_TIMEOUT and let the kernel return normally.
+__global__ void bounded_wait_selftest_kernel(uint64_t limit_ns, int32_t* dev_status, uint64_t* waited_ns) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        ptx::mbar_init(ptx::smem_u32(&bar), 1);
+        abort_flag = 0;
+        ptx::fence_mbar_init();
+    }
+    __syncthreads();
+    const uint64_t t0 = ptx::globaltimer_ns();
+    const bool ok = ptx::mbar_wait_bounded(ptx::smem_u32(&bar), 0, &abort_flag, dev_status, limit_ns);
+    if (threadIdx.x == 0) *waited_ns = ok ? 0 : ptx::globaltimer_ns() - t0;
+}
+}  // namespace
+}  // namespace aristos
+
+extern "C" aristos_status_t aristos_selftest_bounded_wait(int limit_ms, int* waited_ms, void* stream) {
+    if (limit_ms < 1 || limit_ms > 5000) { set_last_error("selftest: limit_ms must be in 1..5000"); return ARISTOS_ERR_INVALID_ARG; }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int32_t* d_status = nullptr;
+    ARISTOS_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&d_status), 16));
+    uint64_t* d_waited = reinterpret_cast<uint64_t*>(d_status + 2);
+    cudaError_t e = cudaMemsetAsync(d_status, 0, 16, st);
+    if (e == cudaSuccess) {
+        bounded_wait_selftest_kernel<<<1, 32, 0, st>>>((uint64_t)limit_ms * 1000000ull, d_status, d_waited);
+        ARISTOS_COUNT_LAUNCH();
+        e = cudaGetLastError();
+    }
+    int32_t bits = 0;
+    uint64_t waited = 0;
+    if (e == cudaSuccess) e = cudaMemcpyAsync(&bits, d_status, 4, cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(&waited, d_waited, 8, cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    cudaFree(d_status);
+    if (e != cudaSuccess) return cuda_fail(e, "bounded-wait self-test");
+    if (waited_ms) *waited_ms = (int)(waited / 1000000ull);
+    if (bits & DEV_FAULT_TIMEOUT) { set_last_error("a bounded device-side wait expired (self-test)"); return ARISTOS_ERR_DEVICE_TIMEOUT; }
+    return ARISTOS_OK;
 }

@@ -54,14 +54,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // *dev_status) when the wall-clock limit passes or another thread of the CTA already gave up.
 constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;  // 2 s
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                                  int32_t* dev_status) {
+                                                  int32_t* dev_status, uint64_t limit_ns = WAIT_LIMIT_NS) {
     if (mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = globaltimer_ns();
     for (uint32_t it = 1;; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((it & 63u) == 0u) {
             if (*abort_flag) return false;
-            if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+            if (globaltimer_ns() - t0 > limit_ns) {
                 *abort_flag = 1;
                 if (dev_status) atomicOr(dev_status, DEV_FAULT_TIMEOUT);
                 return false;
@@ -189,7 +189,7 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 // 3-D tiled load issued by either CTA of a pair into its own shared memory; the byte count is credited to the
-// mbarrier at `bar_cluster_addr`, which may live in the other CTA of the pair. No multicast.
+// mbarrier at `bar_cluster_addr`, which may live in the other CTA of the pair; every CTA loads its own tile.
 __device__ __forceinline__ void tma_load_3d_pair(uint32_t smem_dst, const CUtensorMap* tm, int c0, int c1, int c2,
                                                  uint32_t bar_cluster_addr) {
     asm volatile(

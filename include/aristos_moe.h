@@ -222,6 +222,11 @@ ARISTOS_API aristos_status_t aristos_expert_ffn(const void* xg, const int32_t* c
  * nothing. Replaces Combine / VAA / deviceCombine (auditorium/combine.cuh:19-205). */
 ARISTOS_API aristos_status_t aristos_combine(const void* y, const int32_t* slot_of, const float* topk_w, int S,
                                              int k, int H, int dtype, void* out, void* stream);
+/* Self-test of the failure path of the device-side waits (the reference's waits spin without bound:
+ * auditorium/overlap.cuh:102-105, warpScheduler.cuh:339-341): one warp waits, with the routine the GEMM roles use, on a
+ * barrier that nothing signals; the wait gives up after limit_ms, the kernel returns normally and the call reports
+ * ARISTOS_ERR_DEVICE_TIMEOUT (that IS the expected result) with the time waited. The CUDA context stays usable. */
+ARISTOS_API aristos_status_t aristos_selftest_bounded_wait(int limit_ms, int* waited_ms, void* stream);
 /* Synthetic inputs: Philox4x32-10 + Box-Muller normal fill (the reference draws inputs from Philox,
  * main.cu:22-31). Element i uses counter (i/4, 0, stream_id, 0), key = seed, output word i%4. */
 ARISTOS_API aristos_status_t aristos_fill_normal(void* dst, int64_t n, float mean, float std, uint64_t seed,

@@ -161,3 +161,17 @@ def test_unsupported_dtype_fails_loudly():
     with pytest.raises(cp.AristosError) as e:
         layer.MoELayer(cfg)
     assert e.value.status == 6
+
+
+def test_bounded_device_wait_times_out_and_context_survives(oracle):
+    """Failure detection without a GPU fault: a wait that nothing satisfies gives up after its limit, the kernel
+    returns, the host reads the status, and the same context then runs a normal forward."""
+    import ctypes as C
+    torch, cp, layer = _mods()
+    lib = cp._lib.load()
+    waited = C.c_int(0)
+    st = lib.aristos_selftest_bounded_wait(200, C.byref(waited), None)
+    assert st == 8, "ARISTOS_ERR_DEVICE_TIMEOUT expected"
+    assert 200 <= waited.value < 1500, waited.value
+    got, r, ref = _run_layer(cp.baseline_config(1), 0, oracle)
+    _check_routing(r, ref)
