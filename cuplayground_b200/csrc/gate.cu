@@ -5,81 +5,158 @@
 // layout follows its expert-tile contract: x (S,H) row-major, Wg (E,H) row-major = the (N,K) B operand of
 // mma.cuh:396-397.
 //
-// Bit-exact contract (mirrored by the CPU oracle): for a token t and expert e, lane c of a warp accumulates
-//   p[c] = fmaf(x[t,h], Wg[e,h], p[c])   over the 8-element chunks q = h/8 with q % 32 == c, in increasing h,
-// then the 32 partial sums are combined by the xor butterfly 16, 8, 4, 2, 1 and the bias is added last.
-// Products of bf16 values are exact in fp32, every step is one IEEE operation, so the logits do not depend on
-// the launch geometry and the CPU reproduces them bit for bit. Top-k is taken on the logits (exp is monotone, so
-// the selected indices cannot depend on its rounding); ties go to the lower expert index.
+// Bit-exact contract (mirrored by the CPU oracle): for a token t and expert e there are 32 x 2 partial sums;
+//   p[c][h % 2] = fmaf(x[t,h], Wg[e,h], p[c][h % 2])   over the 8-element chunks q = h/8 with q % 32 == c, in
+// increasing h (even and odd elements accumulate separately: that is one packed two-lane FMA per bf16 pair), then
+// P[c] = p[c][0] + p[c][1], the 32 values P[c] are combined by the xor butterfly 16, 8, 4, 2, 1
+// (P[c] = P[c] + P[c ^ m]) and the bias is added last. Products of bf16 values are exact in fp32 and every step is
+// one IEEE operation, so the logits do not depend on the launch geometry and the CPU reproduces them bit for bit.
+// Top-k is taken on the logits (exp is monotone, so the selected indices cannot depend on its rounding); ties go to
+// the lower expert index.
+//
+// Kernel shape: a CTA of 16 warps owns a tile of tokens x experts; H is walked in slabs of 256 elements that are
+// staged in shared memory with cp.async (three stages), lane c of every warp reads chunk c of a slab row, so lane c
+// holds the partial sums c of its warp's 4-token x 8-expert register tile (packed fp32x2 FMAs: half the issue slots
+// of scalar FMAs, which is what bounds this kernel). The butterfly is done as a reduce-scatter
+// (each step keeps half of the tile, 31 shuffles instead of 160): adding the same two operands, it gives the same
+// bits as the full butterfly. With few experts the kernel streams x once from HBM; with many it is FMA-bound.
 #include "common.cuh"
 
 namespace aristos {
 
-constexpr int GATE_WARPS = 8;   // warps per CTA
-constexpr int GATE_TT = 4;      // tokens per warp pass
-constexpr int GATE_TE = 8;      // experts per register tile
+constexpr int GATE_THREADS = 512;
+constexpr int GATE_WARPS = GATE_THREADS / 32;
+constexpr int GATE_TT = 4;       // tokens per warp register tile
+constexpr int GATE_TE = 8;       // experts per warp register tile
+constexpr int GATE_SLAB = 256;   // elements of H per staged slab (one 8-element chunk per lane)
 constexpr int MAX_TOPK = 16;
 
-template <typename T>
-__global__ void __launch_bounds__(GATE_WARPS * 32)
+__device__ __forceinline__ void cp_async_16(uint32_t smem_dst, const void* gsrc, int src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_dst), "l"(gsrc), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// 8 consecutive elements as 4 (even, odd) pairs.
+__device__ __forceinline__ void load8_pairs(const __nv_bfloat16* p, float2 (&v)[4]) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = make_float2(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xFFFF0000u));
+}
+__device__ __forceinline__ void load8_pairs(const float* p, float2 (&v)[4]) {
+    const float4 a = *reinterpret_cast<const float4*>(p);
+    const float4 b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = make_float2(a.x, a.y); v[1] = make_float2(a.z, a.w);
+    v[2] = make_float2(b.x, b.y); v[3] = make_float2(b.z, b.w);
+}
+
+constexpr int GATE_STAGES = 3;
+
+// WT x WE warps: the CTA tile is (WT*4) tokens x (WE*8) experts; experts beyond that are walked in further tiles.
+template <typename T, int WT, int WE>
+__global__ void __launch_bounds__(GATE_THREADS)
 gate_topk_kernel(const T* __restrict__ x, const T* __restrict__ wg, const float* __restrict__ bias, int S, int H,
                  int E, int k, int gate_fn, int renorm, int32_t* __restrict__ topk_idx,
                  float* __restrict__ topk_w, float* __restrict__ logits_out) {
-    extern __shared__ float s_logits[];  // [GATE_WARPS][GATE_TT][E]
+    static_assert(WT * WE == GATE_WARPS, "warp grid");
+    constexpr int TOK = WT * GATE_TT, ET = WE * GATE_TE, ROWS = TOK + ET;
+    constexpr int ROW_BYTES = GATE_SLAB * (int)sizeof(T);
+    constexpr int CHUNKS16 = ROW_BYTES / 16 / 32;            // 16-byte pieces per lane and row (1 for bf16, 2 for fp32)
+    extern __shared__ __align__(16) uint8_t gate_smem[];
+    uint8_t* stage_mem = gate_smem;                          // [GATE_STAGES][ROWS][ROW_BYTES]
+    float* s_logits = reinterpret_cast<float*>(gate_smem + GATE_STAGES * ROWS * ROW_BYTES);   // [TOK][E]
+
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t0 = (blockIdx.x * GATE_WARPS + warp) * GATE_TT;
-    if (t0 >= S) return;
-    float* my_logits = s_logits + (size_t)warp * GATE_TT * E;
+    const int wt = warp / WE, we = warp % WE;
+    const int t0 = blockIdx.x * TOK;
     const int nchunk = H >> 3;
+    const int nslab = (nchunk + 31) >> 5;
+    const int etiles = (E + ET - 1) / ET;
+    const uint32_t stage_u32 = static_cast<uint32_t>(__cvta_generic_to_shared(stage_mem));
 
-    const T* xrow[GATE_TT];
+    // one slab of one expert tile: rows 0..TOK-1 = tokens, TOK..ROWS-1 = experts; invalid pieces are zero-filled
+    auto issue_slab = [&](int etile, int slab, int buf) {
+        for (int r = warp; r < ROWS; r += GATE_WARPS) {
+            const bool is_tok = r < TOK;
+            const int row = is_tok ? t0 + r : etile * ET + (r - TOK);
+            const bool row_ok = is_tok ? (row < S) : (row < E);
+            const T* base = (is_tok ? x : wg) + (size_t)(row_ok ? row : 0) * H;
 #pragma unroll
-    for (int tt = 0; tt < GATE_TT; ++tt) xrow[tt] = x + (size_t)min(t0 + tt, S - 1) * H;
+            for (int u = 0; u < CHUNKS16; ++u) {
+                // lane's 8-element chunk of this slab is q = slab*32 + lane; it spans CHUNKS16 16-byte pieces
+                const int q = slab * 32 + lane;
+                const bool ok = row_ok && q < nchunk;
+                const uint8_t* src = reinterpret_cast<const uint8_t*>(base + (size_t)(ok ? q : 0) * 8) + u * 16;
+                const uint32_t dst = stage_u32 + (buf * ROWS + r) * ROW_BYTES + lane * (16 * CHUNKS16) + u * 16;
+                cp_async_16(dst, src, ok ? 16 : 0);
+            }
+        }
+        cp_async_commit();
+    };
 
-    for (int e0 = 0; e0 < E; e0 += GATE_TE) {
-        float acc[GATE_TT][GATE_TE];
+    for (int etile = 0; etile < etiles; ++etile) {
+        float2 acc[GATE_TT][GATE_TE];      // (even, odd) partial sums
 #pragma unroll
         for (int tt = 0; tt < GATE_TT; ++tt)
 #pragma unroll
-            for (int ee = 0; ee < GATE_TE; ++ee) acc[tt][ee] = 0.0f;
-        const T* wrow[GATE_TE];
-#pragma unroll
-        for (int ee = 0; ee < GATE_TE; ++ee) wrow[ee] = wg + (size_t)min(e0 + ee, E - 1) * H;
+            for (int ee = 0; ee < GATE_TE; ++ee) acc[tt][ee] = make_float2(0.0f, 0.0f);
 
-        for (int q = lane; q < nchunk; q += 32) {
-            float xv[GATE_TT][8];
+        // three-stage pipeline, one barrier per slab: slab s lives in buffer s % 3
+        issue_slab(etile, 0, 0);
+        if (nslab > 1) issue_slab(etile, 1, 1); else cp_async_commit();
+        for (int slab = 0; slab < nslab; ++slab) {
+            cp_async_wait<1>();            // all groups but the newest have landed: slab `slab` is in shared memory
+            __syncthreads();               // ... for every thread, and buffer (slab + 2) % 3 is no longer being read
+            if (slab + 2 < nslab) issue_slab(etile, slab + 2, (slab + 2) % GATE_STAGES); else cp_async_commit();
+            const T* srow = reinterpret_cast<const T*>(stage_mem + (size_t)(slab % GATE_STAGES) * ROWS * ROW_BYTES);
+            float2 xv[GATE_TT][4];
 #pragma unroll
-            for (int tt = 0; tt < GATE_TT; ++tt) load8(xrow[tt] + q * 8, xv[tt]);
+            for (int tt = 0; tt < GATE_TT; ++tt) load8_pairs(srow + (wt * GATE_TT + tt) * GATE_SLAB + lane * 8, xv[tt]);
 #pragma unroll
             for (int ee = 0; ee < GATE_TE; ++ee) {
-                float wv[8];
-                load8(wrow[ee] + q * 8, wv);
+                float2 wv[4];
+                load8_pairs(srow + (TOK + we * GATE_TE + ee) * GATE_SLAB + lane * 8, wv);
 #pragma unroll
                 for (int tt = 0; tt < GATE_TT; ++tt)
 #pragma unroll
-                    for (int v = 0; v < 8; ++v) acc[tt][ee] = fmaf(xv[tt][v], wv[v], acc[tt][ee]);
+                    for (int i = 0; i < 4; ++i) acc[tt][ee] = __ffma2_rn(xv[tt][i], wv[i], acc[tt][ee]);
             }
         }
-#pragma unroll
-        for (int tt = 0; tt < GATE_TT; ++tt)
-#pragma unroll
-            for (int ee = 0; ee < GATE_TE; ++ee) {
-                float p = acc[tt][ee];
-#pragma unroll
-                for (int m = 16; m >= 1; m >>= 1) p = p + __shfl_xor_sync(0xffffffffu, p, m);
-                const int e = e0 + ee;
-                if (e < E) {
-                    if (bias) p = p + bias[e];
-                    if (lane == 0) my_logits[tt * E + e] = p;
-                }
-            }
-    }
-    __syncwarp();
+        __syncthreads();                   // the next expert tile restarts the pipeline in buffers 0 and 1
 
-    for (int tt = 0; tt < GATE_TT; ++tt) {
-        const int t = t0 + tt;
+        // xor butterfly 16, 8, 4, 2, 1 as a reduce-scatter: after the last step lane c holds tile element c
+        float a[GATE_TT * GATE_TE];
+#pragma unroll
+        for (int i = 0; i < GATE_TT * GATE_TE; ++i) a[i] = acc[i / GATE_TE][i % GATE_TE].x + acc[i / GATE_TE][i % GATE_TE].y;
+#pragma unroll
+        for (int half = 16; half >= 1; half >>= 1) {
+            const bool up = (lane & half) != 0;
+#pragma unroll
+            for (int i = 0; i < half; ++i) {
+                const float keep = up ? a[i + half] : a[i];
+                const float send = up ? a[i] : a[i + half];
+                a[i] = keep + __shfl_xor_sync(0xffffffffu, send, half);
+            }
+        }
+        {
+            const int tt = lane >> 3, ee = lane & 7;
+            const int e = etile * ET + we * GATE_TE + ee;
+            if (e < E) {
+                float p = a[0];
+                if (bias) p = p + bias[e];
+                s_logits[(wt * GATE_TT + tt) * E + e] = p;
+            }
+        }
+    }
+    __syncthreads();
+
+    // ---- top-k and weights: one warp per token -------------------------------------------------------------------
+    for (int tl = warp; tl < TOK; tl += GATE_WARPS) {
+        const int t = t0 + tl;
         if (t >= S) break;
-        const float* l = my_logits + tt * E;
+        const float* l = s_logits + tl * E;
         if (logits_out)
             for (int e = lane; e < E; e += 32) logits_out[(size_t)t * E + e] = l[e];
         int chosen[MAX_TOPK];
@@ -129,21 +206,36 @@ gate_topk_kernel(const T* __restrict__ x, const T* __restrict__ wg, const float*
     }
 }
 
+template <typename T, int WT, int WE>
+static aristos_status_t launch_gate_shape(const void* x, const void* wg, const float* bias, int S, int H, int E, int k,
+                                          int gate_fn, int renorm, int32_t* topk_idx, float* topk_w,
+                                          float* logits_out, cudaStream_t stream) {
+    constexpr int TOK = WT * GATE_TT, ET = WE * GATE_TE, ROWS = TOK + ET;
+    const size_t smem = GATE_STAGES * (size_t)ROWS * GATE_SLAB * sizeof(T) + sizeof(float) * (size_t)TOK * E;
+    auto kernel = gate_topk_kernel<T, WT, WE>;
+    if (smem > 48 * 1024)
+        ARISTOS_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const int grid = ceil_div(S, TOK);
+    kernel<<<grid, GATE_THREADS, smem, stream>>>(static_cast<const T*>(x), static_cast<const T*>(wg), bias, S, H, E, k,
+                                                 gate_fn, renorm, topk_idx, topk_w, logits_out);
+    ARISTOS_COUNT_LAUNCH();
+    ARISTOS_CUDA_TRY(cudaGetLastError());
+    return ARISTOS_OK;
+}
+
 template <typename T>
 static aristos_status_t launch_gate(const void* x, const void* wg, const float* bias, int S, int H, int E, int k,
                                     int gate_fn, int renorm, int32_t* topk_idx, float* topk_w, float* logits_out,
                                     cudaStream_t stream) {
-    const size_t smem = sizeof(float) * GATE_WARPS * GATE_TT * (size_t)E;
-    if (smem > 48 * 1024)
-        ARISTOS_CUDA_TRY(cudaFuncSetAttribute(gate_topk_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                              (int)smem));
-    const int grid = ceil_div(S, GATE_WARPS * GATE_TT);
-    gate_topk_kernel<T><<<grid, GATE_WARPS * 32, smem, stream>>>(
-        static_cast<const T*>(x), static_cast<const T*>(wg), bias, S, H, E, k, gate_fn, renorm, topk_idx, topk_w,
-        logits_out);
-    ARISTOS_COUNT_LAUNCH();
-    ARISTOS_CUDA_TRY(cudaGetLastError());
-    return ARISTOS_OK;
+    // few experts: wide token tiles (x streams once from HBM); many experts: 32-expert tiles walked per CTA
+    if (E <= 8)
+        return launch_gate_shape<T, 16, 1>(x, wg, bias, S, H, E, k, gate_fn, renorm, topk_idx, topk_w, logits_out, stream);
+    if (E <= 16)
+        return launch_gate_shape<T, 8, 2>(x, wg, bias, S, H, E, k, gate_fn, renorm, topk_idx, topk_w, logits_out, stream);
+    if (E <= 32)
+        return launch_gate_shape<T, 4, 4>(x, wg, bias, S, H, E, k, gate_fn, renorm, topk_idx, topk_w, logits_out, stream);
+    // 8 tokens x 64 experts per CTA: small token tiles keep the last wave of CTAs full
+    return launch_gate_shape<T, 2, 8>(x, wg, bias, S, H, E, k, gate_fn, renorm, topk_idx, topk_w, logits_out, stream);
 }
 
 }  // namespace aristos

@@ -109,22 +109,28 @@ ORC_API void orc_zipf_bias(float* bias, int E, double s) {
 
 /* ---------------------------------------------------------------------------------------------------------------
  * Gate logits, bit-exact contract.
- *   logit[t,e] = tree( p[0..31] ) (+ bias[e]),
- *   p[c] accumulates, in increasing h, fmaf(x[t,h], wg[e,h], p[c]) over the 8-element chunks q = h/8 with
- *   q % 32 == c; the tree is the xor butterfly 16, 8, 4, 2, 1 (p[c] = p[c] + p[c ^ m]).
- * This is the order a warp produces when lane c owns every 32nd 16-byte chunk of a bf16 row.
+ *   logit[t,e] = tree( P[0..31] ) (+ bias[e]),   P[c] = p[c][0] + p[c][1],
+ *   p[c][h % 2] accumulates, in increasing h, fmaf(x[t,h], wg[e,h], p[c][h % 2]) over the 8-element chunks
+ *   q = h/8 with q % 32 == c (even and odd elements separately); the tree is the xor butterfly 16, 8, 4, 2, 1
+ *   (P[c] = P[c] + P[c ^ m]).
+ * This is the order a warp produces when lane c owns every 32nd 16-byte chunk of a bf16 row and multiplies the
+ * (even, odd) element pairs with packed two-lane fused multiply-adds.
  * x is (S,H) row-major, wg is (E,H) row-major (the reference's B-operand convention, mma.cuh:396-397).
  * ------------------------------------------------------------------------------------------------------------- */
 static float gate_logit_one(const float* xr, const float* wr, int H) {
-    float p[32];
-    for (int c = 0; c < 32; ++c) p[c] = 0.0f;
+    float pe[32], po[32], p[32];
+    for (int c = 0; c < 32; ++c) pe[c] = po[c] = 0.0f;
     const int nchunk = H / 8;
     for (int q = 0; q < nchunk; ++q) {
         const int c = q & 31;
-        float acc = p[c];
-        for (int v = 0; v < 8; ++v) acc = fmaf(xr[q * 8 + v], wr[q * 8 + v], acc);
-        p[c] = acc;
+        float ae = pe[c], ao = po[c];
+        for (int v = 0; v < 8; v += 2) {
+            ae = fmaf(xr[q * 8 + v], wr[q * 8 + v], ae);
+            ao = fmaf(xr[q * 8 + v + 1], wr[q * 8 + v + 1], ao);
+        }
+        pe[c] = ae; po[c] = ao;
     }
+    for (int c = 0; c < 32; ++c) p[c] = pe[c] + po[c];
     for (int m = 16; m >= 1; m >>= 1) {
         float np[32];
         for (int c = 0; c < 32; ++c) np[c] = p[c] + p[c ^ m];

@@ -55,16 +55,19 @@ def test_gate_logits_order_and_value(oracle):
     x = rng.standard_normal((S, H)).astype(np.float32)
     wg = rng.standard_normal((E, H)).astype(np.float32)
     got = oracle.gate_logits(x, wg)
-    # independent restatement of the contract: 32 strided partial sums with fused multiply-add, xor butterfly
+    # independent restatement of the contract: 32 x (even, odd) strided partial sums with fused multiply-add,
+    # P[c] = even + odd, xor butterfly
     ref = np.zeros((S, E), np.float32)
     for t in range(S):
         for e in range(E):
-            p = [np.float32(0)] * 32
+            pp = [[np.float32(0), np.float32(0)] for _ in range(32)]
             for q in range(H // 8):
                 c = q % 32
                 for v in range(8):
                     h = q * 8 + v
-                    p[c] = np.float32(np.float64(x[t, h]) * np.float64(wg[e, h]) + np.float64(p[c]))  # exact product, one rounding
+                    # exact product (24-bit x 24-bit fits a double), one rounding
+                    pp[c][v % 2] = np.float32(np.float64(x[t, h]) * np.float64(wg[e, h]) + np.float64(pp[c][v % 2]))
+            p = [np.float32(a + b) for a, b in pp]
             for m in (16, 8, 4, 2, 1):
                 p = [np.float32(p[c] + p[c ^ m]) for c in range(32)]
             ref[t, e] = p[0]
