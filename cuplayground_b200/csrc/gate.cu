@@ -17,7 +17,7 @@
 // Kernel shape: a CTA of 16 warps owns a tile of tokens x experts; H is walked in slabs of 256 elements that are
 // staged in shared memory with cp.async (three stages), lane c of every warp reads chunk c of a slab row, so lane c
 // holds the partial sums c of its warp's 4-token x 8-expert register tile (packed fp32x2 FMAs: half the issue slots
-// of scalar FMAs, which is what bounds this kernel). The butterfly is done as a reduce-scatter
+// of scalar FMAs). The butterfly is done as a reduce-scatter
 // (each step keeps half of the tile, 31 shuffles instead of 160): adding the same two operands, it gives the same
 // bits as the full butterfly. With few experts the kernel streams x once from HBM; with many it is FMA-bound.
 #include "common.cuh"
@@ -53,6 +53,132 @@ __device__ __forceinline__ void load8_pairs(const float* p, float2 (&v)[4]) {
 }
 
 constexpr int GATE_STAGES = 3;
+
+// Top-k on one token's logits (in shared memory) by one warp, then the combine weights.
+__device__ __forceinline__ void topk_one_token(const float* l, int t, int E, int k, int gate_fn, int renorm, int lane,
+                                               int32_t* __restrict__ topk_idx, float* __restrict__ topk_w,
+                                               float* __restrict__ logits_out) {
+    if (logits_out)
+        for (int e = lane; e < E; e += 32) logits_out[(size_t)t * E + e] = l[e];
+    int chosen[MAX_TOPK];
+    float chosen_l[MAX_TOPK];
+#pragma unroll 1
+    for (int j = 0; j < k; ++j) {
+        float bv = 0.0f;
+        int bi = -1;
+        for (int e = lane; e < E; e += 32) {
+            bool taken = false;
+            for (int i = 0; i < j; ++i) taken |= (chosen[i] == e);
+            if (taken) continue;
+            const float v = l[e];
+            if (bi < 0 || v > bv) { bv = v; bi = e; }   // strict '>' keeps the lowest index within a lane
+        }
+#pragma unroll
+        for (int m = 16; m >= 1; m >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, m);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, m);
+            const bool take = (oi >= 0) && (bi < 0 || ov > bv || (ov == bv && oi < bi));
+            if (take) { bv = ov; bi = oi; }
+        }
+        chosen[j] = bi;
+        chosen_l[j] = bv;
+    }
+    float w_sel[MAX_TOPK];
+    if (gate_fn == ARISTOS_GATE_SOFTMAX) {
+        const float mx = chosen_l[0];
+        float den = 0.0f;
+        for (int e = lane; e < E; e += 32) den += expf(l[e] - mx);
+#pragma unroll
+        for (int m = 16; m >= 1; m >>= 1) den += __shfl_xor_sync(0xffffffffu, den, m);
+        for (int j = 0; j < k; ++j) w_sel[j] = expf(chosen_l[j] - mx) / den;
+    } else {
+        for (int j = 0; j < k; ++j) w_sel[j] = 1.0f / (1.0f + expf(-chosen_l[j]));
+    }
+    if (renorm) {
+        float s = 0.0f;
+        for (int j = 0; j < k; ++j) s += w_sel[j];
+        for (int j = 0; j < k; ++j) w_sel[j] = w_sel[j] / s;
+    }
+    for (int j = 0; j < k; ++j)
+        if (lane == j) {
+            topk_idx[(size_t)t * k + j] = chosen[j];
+            topk_w[(size_t)t * k + j] = w_sel[j];
+        }
+}
+
+// xor butterfly 16, 8, 4, 2, 1 over the lanes as a reduce-scatter of a 4 x 8 register tile: each step keeps half of
+// the tile; afterwards a[0] of lane c is the fully reduced tile element c (token c >> 3, expert c & 7).
+__device__ __forceinline__ float reduce_scatter_tile(float (&a)[GATE_TT * GATE_TE], int lane) {
+#pragma unroll
+    for (int half = 16; half >= 1; half >>= 1) {
+        const bool up = (lane & half) != 0;
+#pragma unroll
+        for (int i = 0; i < half; ++i) {
+            const float keep = up ? a[i + half] : a[i];
+            const float send = up ? a[i] : a[i + half];
+            a[i] = keep + __shfl_xor_sync(0xffffffffu, send, half);
+        }
+    }
+    return a[0];
+}
+
+// Few experts (E <= 8): every warp streams its own 4 token rows straight from global memory (Wg stays in L1), no
+// shared staging and no block-wide barrier; same arithmetic, same bits.
+constexpr int STREAM_WARPS = 8;
+template <typename T>
+__global__ void __launch_bounds__(STREAM_WARPS * 32)
+gate_topk_stream_kernel(const T* __restrict__ x, const T* __restrict__ wg, const float* __restrict__ bias, int S, int H,
+                        int E, int k, int gate_fn, int renorm, int32_t* __restrict__ topk_idx,
+                        float* __restrict__ topk_w, float* __restrict__ logits_out) {
+    __shared__ float s_logits[STREAM_WARPS][GATE_TT][GATE_TE];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t0 = (blockIdx.x * STREAM_WARPS + warp) * GATE_TT;
+    if (t0 >= S) return;
+    const int nchunk = H >> 3;
+    const T* xrow[GATE_TT];
+    const T* wrow[GATE_TE];
+#pragma unroll
+    for (int tt = 0; tt < GATE_TT; ++tt) xrow[tt] = x + (size_t)min(t0 + tt, S - 1) * H;
+#pragma unroll
+    for (int ee = 0; ee < GATE_TE; ++ee) wrow[ee] = wg + (size_t)min(ee, E - 1) * H;
+    float2 acc[GATE_TT][GATE_TE];
+#pragma unroll
+    for (int tt = 0; tt < GATE_TT; ++tt)
+#pragma unroll
+        for (int ee = 0; ee < GATE_TE; ++ee) acc[tt][ee] = make_float2(0.0f, 0.0f);
+    for (int q = lane; q < nchunk; q += 32) {
+        float2 xv[GATE_TT][4];
+#pragma unroll
+        for (int tt = 0; tt < GATE_TT; ++tt) load8_pairs(xrow[tt] + q * 8, xv[tt]);
+#pragma unroll
+        for (int ee = 0; ee < GATE_TE; ++ee) {
+            float2 wv[4];
+            load8_pairs(wrow[ee] + q * 8, wv);
+#pragma unroll
+            for (int tt = 0; tt < GATE_TT; ++tt)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc[tt][ee] = __ffma2_rn(xv[tt][i], wv[i], acc[tt][ee]);
+        }
+    }
+    float a[GATE_TT * GATE_TE];
+#pragma unroll
+    for (int i = 0; i < GATE_TT * GATE_TE; ++i) a[i] = acc[i / GATE_TE][i % GATE_TE].x + acc[i / GATE_TE][i % GATE_TE].y;
+    float p = reduce_scatter_tile(a, lane);
+    {
+        const int tt = lane >> 3, ee = lane & 7;
+        if (ee < E) {
+            if (bias) p = p + bias[ee];
+            s_logits[warp][tt][ee] = p;
+        }
+    }
+    __syncwarp();
+    for (int tt = 0; tt < GATE_TT; ++tt) {
+        const int t = t0 + tt;
+        if (t >= S) break;
+        topk_one_token(&s_logits[warp][tt][0], t, E, k, gate_fn, renorm, lane, topk_idx, topk_w, logits_out);
+    }
+}
+
 
 // WT x WE warps: the CTA tile is (WT*4) tokens x (WE*8) experts; experts beyond that are walked in further tiles.
 template <typename T, int WT, int WE>
@@ -126,25 +252,15 @@ gate_topk_kernel(const T* __restrict__ x, const T* __restrict__ wg, const float*
         }
         __syncthreads();                   // the next expert tile restarts the pipeline in buffers 0 and 1
 
-        // xor butterfly 16, 8, 4, 2, 1 as a reduce-scatter: after the last step lane c holds tile element c
         float a[GATE_TT * GATE_TE];
 #pragma unroll
         for (int i = 0; i < GATE_TT * GATE_TE; ++i) a[i] = acc[i / GATE_TE][i % GATE_TE].x + acc[i / GATE_TE][i % GATE_TE].y;
-#pragma unroll
-        for (int half = 16; half >= 1; half >>= 1) {
-            const bool up = (lane & half) != 0;
-#pragma unroll
-            for (int i = 0; i < half; ++i) {
-                const float keep = up ? a[i + half] : a[i];
-                const float send = up ? a[i] : a[i + half];
-                a[i] = keep + __shfl_xor_sync(0xffffffffu, send, half);
-            }
-        }
+        const float tile_elem = reduce_scatter_tile(a, lane);
         {
             const int tt = lane >> 3, ee = lane & 7;
             const int e = etile * ET + we * GATE_TE + ee;
             if (e < E) {
-                float p = a[0];
+                float p = tile_elem;
                 if (bias) p = p + bias[e];
                 s_logits[(wt * GATE_TT + tt) * E + e] = p;
             }
@@ -156,53 +272,7 @@ gate_topk_kernel(const T* __restrict__ x, const T* __restrict__ wg, const float*
     for (int tl = warp; tl < TOK; tl += GATE_WARPS) {
         const int t = t0 + tl;
         if (t >= S) break;
-        const float* l = s_logits + tl * E;
-        if (logits_out)
-            for (int e = lane; e < E; e += 32) logits_out[(size_t)t * E + e] = l[e];
-        int chosen[MAX_TOPK];
-        float chosen_l[MAX_TOPK];
-#pragma unroll 1
-        for (int j = 0; j < k; ++j) {
-            float bv = 0.0f;
-            int bi = -1;
-            for (int e = lane; e < E; e += 32) {
-                bool taken = false;
-                for (int i = 0; i < j; ++i) taken |= (chosen[i] == e);
-                if (taken) continue;
-                const float v = l[e];
-                if (bi < 0 || v > bv) { bv = v; bi = e; }   // strict '>' keeps the lowest index within a lane
-            }
-#pragma unroll
-            for (int m = 16; m >= 1; m >>= 1) {
-                const float ov = __shfl_xor_sync(0xffffffffu, bv, m);
-                const int oi = __shfl_xor_sync(0xffffffffu, bi, m);
-                const bool take = (oi >= 0) && (bi < 0 || ov > bv || (ov == bv && oi < bi));
-                if (take) { bv = ov; bi = oi; }
-            }
-            chosen[j] = bi;
-            chosen_l[j] = bv;
-        }
-        float w_sel[MAX_TOPK];
-        if (gate_fn == ARISTOS_GATE_SOFTMAX) {
-            const float mx = chosen_l[0];
-            float den = 0.0f;
-            for (int e = lane; e < E; e += 32) den += expf(l[e] - mx);
-#pragma unroll
-            for (int m = 16; m >= 1; m >>= 1) den += __shfl_xor_sync(0xffffffffu, den, m);
-            for (int j = 0; j < k; ++j) w_sel[j] = expf(chosen_l[j] - mx) / den;
-        } else {
-            for (int j = 0; j < k; ++j) w_sel[j] = 1.0f / (1.0f + expf(-chosen_l[j]));
-        }
-        if (renorm) {
-            float s = 0.0f;
-            for (int j = 0; j < k; ++j) s += w_sel[j];
-            for (int j = 0; j < k; ++j) w_sel[j] = w_sel[j] / s;
-        }
-        for (int j = 0; j < k; ++j)
-            if (lane == j) {
-                topk_idx[(size_t)t * k + j] = chosen[j];
-                topk_w[(size_t)t * k + j] = w_sel[j];
-            }
+        topk_one_token(s_logits + tl * E, t, E, k, gate_fn, renorm, lane, topk_idx, topk_w, logits_out);
     }
 }
 
@@ -228,8 +298,15 @@ static aristos_status_t launch_gate(const void* x, const void* wg, const float* 
                                     int gate_fn, int renorm, int32_t* topk_idx, float* topk_w, float* logits_out,
                                     cudaStream_t stream) {
     // few experts: wide token tiles (x streams once from HBM); many experts: 32-expert tiles walked per CTA
-    if (E <= 8)
-        return launch_gate_shape<T, 16, 1>(x, wg, bias, S, H, E, k, gate_fn, renorm, topk_idx, topk_w, logits_out, stream);
+    if (E <= 8) {
+        const int grid = ceil_div(S, STREAM_WARPS * GATE_TT);
+        gate_topk_stream_kernel<T><<<grid, STREAM_WARPS * 32, 0, stream>>>(
+            static_cast<const T*>(x), static_cast<const T*>(wg), bias, S, H, E, k, gate_fn, renorm, topk_idx, topk_w,
+            logits_out);
+        ARISTOS_COUNT_LAUNCH();
+        ARISTOS_CUDA_TRY(cudaGetLastError());
+        return ARISTOS_OK;
+    }
     if (E <= 16)
         return launch_gate_shape<T, 8, 2>(x, wg, bias, S, H, E, k, gate_fn, renorm, topk_idx, topk_w, logits_out, stream);
     if (E <= 32)
