@@ -65,6 +65,8 @@ PROTOTYPES = {
     "aristos_moe_set_workspace": (_st, [_vp, _vp, _sz]),
     "aristos_moe_forward": (_st, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "aristos_moe_forward_host": (_st, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "aristos_moe_submit_host": (_st, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "aristos_moe_wait_host": (_st, [_vp]),
     "aristos_moe_routing": (_st, [_vp, C.POINTER(AristosRoutingStruct)]),
     "aristos_moe_routing_to_host": (_st, [_vp, _vp, _vp, _vp, _vp, _vp]),
     "aristos_moe_status": (_st, [_vp]),

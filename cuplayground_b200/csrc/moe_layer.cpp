@@ -37,8 +37,15 @@ struct aristos_moe {
     int32_t *topk_idx = nullptr, *count = nullptr, *slot_of = nullptr, *token_of_slot = nullptr, *rcount = nullptr,
             *dev_status = nullptr;
     float *topk_w = nullptr, *gate_bias = nullptr;
-    void *dispatch_scratch = nullptr, *xg = nullptr, *xr = nullptr, *h = nullptr, *yr = nullptr, *yg = nullptr,
-         *x_stage = nullptr, *out_stage = nullptr;
+    void *dispatch_scratch = nullptr, *xg = nullptr, *xr = nullptr, *h = nullptr, *yr = nullptr, *yg = nullptr;
+    // host-activation path: two staging slots so that the copies of one call overlap the kernels of its neighbours
+    struct HostSlot {
+        void *x_dev = nullptr, *out_dev = nullptr;
+        cudaEvent_t h2d_done = nullptr, compute_done = nullptr, d2h_done = nullptr;
+        bool busy = false;
+    } slots[2];
+    int slot_next = 0;
+    cudaStream_t h2d_stream = nullptr, d2h_stream = nullptr;
     size_t dispatch_scratch_bytes = 0;
     bool bias_ready = false;
     // expert parallel
@@ -101,8 +108,10 @@ size_t plan_workspace(aristos_moe* L, char* base) {
         L->xr = L->xg;
         L->yg = L->yr;
     }
-    CARVE(x_stage, void*, S * H * elt)
-    CARVE(out_stage, void*, S * H * elt)
+    CARVE(slots[0].x_dev, void*, S * H * elt)
+    CARVE(slots[0].out_dev, void*, S * H * elt)
+    CARVE(slots[1].x_dev, void*, S * H * elt)
+    CARVE(slots[1].out_dev, void*, S * H * elt)
 #undef CARVE
     return c.off;
 }
@@ -315,18 +324,55 @@ aristos_status_t aristos_moe_forward(aristos_moe_t* L, const void* x, const void
     return ARISTOS_OK;
 }
 
+aristos_status_t aristos_moe_submit_host(aristos_moe_t* L, const void* x_host, const void* w_gate,
+                                         const float* gate_bias, const void* w1, const void* w3, const void* w2,
+                                         const void* scales, void* out_host, void* stream) {
+    if (!L || !x_host || !out_host) { set_last_error("submit_host: NULL pointer"); return ARISTOS_ERR_INVALID_ARG; }
+    ARISTOS_TRY(ensure_workspace(L));
+    if (!L->h2d_stream) {
+        ARISTOS_CUDA_TRY(cudaStreamCreateWithFlags(&L->h2d_stream, cudaStreamNonBlocking));
+        ARISTOS_CUDA_TRY(cudaStreamCreateWithFlags(&L->d2h_stream, cudaStreamNonBlocking));
+        for (auto& sl : L->slots) {
+            ARISTOS_CUDA_TRY(cudaEventCreateWithFlags(&sl.h2d_done, cudaEventDisableTiming));
+            ARISTOS_CUDA_TRY(cudaEventCreateWithFlags(&sl.compute_done, cudaEventDisableTiming));
+            ARISTOS_CUDA_TRY(cudaEventCreateWithFlags(&sl.d2h_done, cudaEventDisableTiming));
+        }
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    aristos_moe::HostSlot& sl = L->slots[L->slot_next];
+    L->slot_next ^= 1;
+    if (sl.busy) {                       // the call that used this slot two submissions ago must have drained
+        ARISTOS_CUDA_TRY(cudaEventSynchronize(sl.d2h_done));
+        sl.busy = false;
+    }
+    const size_t bytes = (size_t)L->S * L->H * L->elt;
+    ARISTOS_CUDA_TRY(cudaMemcpyAsync(sl.x_dev, x_host, bytes, cudaMemcpyHostToDevice, L->h2d_stream));
+    ARISTOS_CUDA_TRY(cudaEventRecord(sl.h2d_done, L->h2d_stream));
+    ARISTOS_CUDA_TRY(cudaStreamWaitEvent(st, sl.h2d_done, 0));
+    ARISTOS_TRY(aristos_moe_forward(L, sl.x_dev, w_gate, gate_bias, w1, w3, w2, scales, sl.out_dev, stream));
+    ARISTOS_CUDA_TRY(cudaEventRecord(sl.compute_done, st));
+    ARISTOS_CUDA_TRY(cudaStreamWaitEvent(L->d2h_stream, sl.compute_done, 0));
+    ARISTOS_CUDA_TRY(cudaMemcpyAsync(out_host, sl.out_dev, bytes, cudaMemcpyDeviceToHost, L->d2h_stream));
+    ARISTOS_CUDA_TRY(cudaEventRecord(sl.d2h_done, L->d2h_stream));
+    sl.busy = true;
+    return ARISTOS_OK;
+}
+
+aristos_status_t aristos_moe_wait_host(aristos_moe_t* L) {
+    if (!L) return ARISTOS_ERR_INVALID_ARG;
+    for (auto& sl : L->slots)
+        if (sl.busy) {
+            ARISTOS_CUDA_TRY(cudaEventSynchronize(sl.d2h_done));
+            sl.busy = false;
+        }
+    return ARISTOS_OK;
+}
+
 aristos_status_t aristos_moe_forward_host(aristos_moe_t* L, const void* x_host, const void* w_gate,
                                           const float* gate_bias, const void* w1, const void* w3, const void* w2,
                                           const void* scales, void* out_host, void* stream) {
-    if (!L || !x_host || !out_host) { set_last_error("forward_host: NULL pointer"); return ARISTOS_ERR_INVALID_ARG; }
-    ARISTOS_TRY(ensure_workspace(L));
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const size_t bytes = (size_t)L->S * L->H * L->elt;
-    ARISTOS_CUDA_TRY(cudaMemcpyAsync(L->x_stage, x_host, bytes, cudaMemcpyHostToDevice, st));
-    ARISTOS_TRY(aristos_moe_forward(L, L->x_stage, w_gate, gate_bias, w1, w3, w2, scales, L->out_stage, stream));
-    ARISTOS_CUDA_TRY(cudaMemcpyAsync(out_host, L->out_stage, bytes, cudaMemcpyDeviceToHost, st));
-    ARISTOS_CUDA_TRY(cudaStreamSynchronize(st));
-    return ARISTOS_OK;
+    ARISTOS_TRY(aristos_moe_submit_host(L, x_host, w_gate, gate_bias, w1, w3, w2, scales, out_host, stream));
+    return aristos_moe_wait_host(L);
 }
 
 aristos_status_t aristos_moe_routing(const aristos_moe_t* L, aristos_routing_t* out) {
@@ -417,6 +463,13 @@ aristos_status_t aristos_moe_destroy(aristos_moe_t* L) {
     if (L->ev_dispatched) cudaEventDestroy(L->ev_dispatched);
     if (L->ev_returned) cudaEventDestroy(L->ev_returned);
     if (L->comm_stream) cudaStreamDestroy(L->comm_stream);
+    for (auto& sl : L->slots) {
+        if (sl.h2d_done) cudaEventDestroy(sl.h2d_done);
+        if (sl.compute_done) cudaEventDestroy(sl.compute_done);
+        if (sl.d2h_done) cudaEventDestroy(sl.d2h_done);
+    }
+    if (L->h2d_stream) cudaStreamDestroy(L->h2d_stream);
+    if (L->d2h_stream) cudaStreamDestroy(L->d2h_stream);
     if (L->p2p) ep_p2p_destroy(L->p2p);
     if (L->comm) ep_comm_destroy(L->comm);
     if (L->ws && L->ws_owned) cudaFree(L->ws);

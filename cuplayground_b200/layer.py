@@ -186,6 +186,17 @@ class MoELayer:
                                                       _ptr(w3), _ptr(w2), None, _ptr(out_host), _stream_ptr(stream)))
         return out_host
 
+    def submit_host(self, x_host, w_gate, w1, w3, w2, out_host, gate_bias=None, stream=None):
+        """Asynchronous forward_host: returns once the copies and kernels are enqueued (two calls may be in flight);
+        the host tensors must stay alive and untouched until wait_host()."""
+        if x_host.is_cuda or out_host.is_cuda:
+            raise ValueError("submit_host takes host tensors")
+        _lib.check(self._lib.aristos_moe_submit_host(self._h, _ptr(x_host), _ptr(w_gate), _ptr(gate_bias), _ptr(w1),
+                                                     _ptr(w3), _ptr(w2), None, _ptr(out_host), _stream_ptr(stream)))
+
+    def wait_host(self) -> None:
+        _lib.check(self._lib.aristos_moe_wait_host(self._h))
+
     def routing(self) -> dict:
         """Host copies (CPU torch tensors) of the routing tensors of the last forward."""
         S, k, E, cap = self.S, self.k, self.E, self.cap
