@@ -68,8 +68,9 @@ extern "C" aristos_status_t aristos_combine(const void* y, const int32_t* slot_o
     switch (dtype) {
         case ARISTOS_DTYPE_F32: return launch_combine<float>(y, slot_of, topk_w, S, k, H, out, st);
         case ARISTOS_DTYPE_BF16: return launch_combine<__nv_bfloat16>(y, slot_of, topk_w, S, k, H, out, st);
+        case ARISTOS_DTYPE_F16: return launch_combine<__half>(y, slot_of, topk_w, S, k, H, out, st);
         default:
-            set_last_error("combine: dtype %d not implemented (f32 and bf16 are)", dtype);
+            set_last_error("combine: dtype %d not implemented (f32, bf16 and f16 are)", dtype);
             return ARISTOS_ERR_UNSUPPORTED;
     }
 }

@@ -2,6 +2,7 @@
 #pragma once
 
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -58,6 +59,16 @@ __device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&v)[8]) {
         v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
     }
 }
+__device__ __forceinline__ void load8(const __half* p, float (&v)[8]) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+        v[2 * i] = f.x;
+        v[2 * i + 1] = f.y;
+    }
+}
 __device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
     const float4 a = *reinterpret_cast<const float4*>(p);
     const float4 b = *reinterpret_cast<const float4*>(p + 4);
@@ -71,6 +82,15 @@ __device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&v)[8]) {
     t = __floats2bfloat162_rn(v[2], v[3]); u.y = *reinterpret_cast<uint32_t*>(&t);
     t = __floats2bfloat162_rn(v[4], v[5]); u.z = *reinterpret_cast<uint32_t*>(&t);
     t = __floats2bfloat162_rn(v[6], v[7]); u.w = *reinterpret_cast<uint32_t*>(&t);
+    *reinterpret_cast<uint4*>(p) = u;
+}
+__device__ __forceinline__ void store8(__half* p, const float (&v)[8]) {
+    uint4 u;
+    __half2 t;
+    t = __floats2half2_rn(v[0], v[1]); u.x = *reinterpret_cast<uint32_t*>(&t);
+    t = __floats2half2_rn(v[2], v[3]); u.y = *reinterpret_cast<uint32_t*>(&t);
+    t = __floats2half2_rn(v[4], v[5]); u.z = *reinterpret_cast<uint32_t*>(&t);
+    t = __floats2half2_rn(v[6], v[7]); u.w = *reinterpret_cast<uint32_t*>(&t);
     *reinterpret_cast<uint4*>(p) = u;
 }
 __device__ __forceinline__ void store8(float* p, const float (&v)[8]) {

@@ -3,10 +3,10 @@
 #include "ptx_sm100.cuh"
 
 namespace aristos {
-aristos_status_t expert_ffn_bf16_sm100(const void* xg, const int32_t* count, int groups, int rows_per_group,
-                                       int experts, const void* w1, const void* w3, const void* w2, void* h_scratch,
-                                       void* y, int H, int I, int hidden_act, int row_begin, int row_end,
-                                       int sm_limit, int32_t* dev_status, cudaStream_t st);
+aristos_status_t expert_ffn_16bit_sm100(const void* xg, const int32_t* count, int groups, int rows_per_group,
+                                        int experts, const void* w1, const void* w3, const void* w2, void* h_scratch,
+                                        void* y, int H, int I, int hidden_act, int is_f16, int row_begin,
+                                        int row_end, int sm_limit, int32_t* dev_status, cudaStream_t st);
 aristos_status_t expert_ffn_f32_simt(const void* xg, const int32_t* count, int groups, int rows_per_group, int experts,
                                      const void* w1, const void* w3, const void* w2, void* h_scratch, void* y, int H,
                                      int I, int hidden_act, int row_begin, int row_end, cudaStream_t st);
@@ -40,13 +40,15 @@ extern "C" aristos_status_t aristos_expert_ffn(const void* xg, const int32_t* co
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     switch (dtype) {
         case ARISTOS_DTYPE_BF16:
-            return expert_ffn_bf16_sm100(xg, count, groups, rows_per_group, experts, w1, w3, w2, h_scratch, y, H, I,
-                                         hidden_act, row_begin, row_end, sm_limit, dev_status, st);
+        case ARISTOS_DTYPE_F16:
+            return expert_ffn_16bit_sm100(xg, count, groups, rows_per_group, experts, w1, w3, w2, h_scratch, y, H, I,
+                                          hidden_act, dtype == ARISTOS_DTYPE_F16 ? 1 : 0, row_begin, row_end, sm_limit,
+                                          dev_status, st);
         case ARISTOS_DTYPE_F32:
             return expert_ffn_f32_simt(xg, count, groups, rows_per_group, experts, w1, w3, w2, h_scratch, y, H, I,
                                        hidden_act, row_begin, row_end, st);
         default:
-            set_last_error("expert_ffn: dtype %d not implemented (f32 and bf16 are)", dtype);
+            set_last_error("expert_ffn: dtype %d not implemented (f32, bf16 and f16 are)", dtype);
             return ARISTOS_ERR_UNSUPPORTED;
     }
 }

@@ -1,6 +1,6 @@
 // Expert FFN on the 5th-generation tensor cores: a persistent, warp-specialised grouped GEMM.
 //
-// Replaces, for bf16, the reference's fused expert tile fGET / deviceCollectiveMMA (mma.cuh:46-179, :198-369: one
+// Replaces, for bf16 and fp16, the reference's fused expert tile fGET / deviceCollectiveMMA (mma.cuh:46-179, :198-369: one
 // CTA per 128x64 tile, CUTLASS sm80 cp.async mainloop, mma.sync, accumulators transposed through shared memory,
 // epilogue act(acc + bias) from processor/tiling.cuh:29-57) and its software tile schedulers sK / wScheduler
 // (auditorium/scheduling.cuh:202-265, warpScheduler.cuh:267-344: doorbells and ready queues in global memory that
@@ -63,11 +63,16 @@ struct FfnGemmParams {
     int K;
     int gated;              // 1: B half 1 comes from the second weight tensor at the same rows (SwiGLU)
     int act;                // ARISTOS_ACT_* for the non-gated epilogue
-    __nv_bfloat16* out;     // (groups * rows_per_group, N)
+    void* out;              // (groups * rows_per_group, N), 16-bit elements
+    int is_f16;             // 0: bf16 operands and output, 1: f16
     int32_t* dev_status;
 };
 
-__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+__device__ __forceinline__ uint32_t pack_16bit(float a, float b, int is_f16) {
+    if (is_f16) {
+        __half2 t = __floats2half2_rn(a, b);
+        return *reinterpret_cast<uint32_t*>(&t);
+    }
     __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
     return *reinterpret_cast<uint32_t*>(&t);
 }
@@ -115,7 +120,7 @@ __device__ __forceinline__ void epilogue_tile(const FfnGemmParams& p, const CUte
                     v1 = act_silu(v1) * __uint_as_float(b[2 * i + 1]);
                 } else if (p.act == ARISTOS_ACT_RELU) { v0 = act_relu(v0); v1 = act_relu(v1); }
                 else if (p.act == ARISTOS_ACT_GELU) { v0 = act_gelu(v0); v1 = act_gelu(v1); }
-                o[i] = pack_bf16(v0, v1);
+                o[i] = pack_16bit(v0, v1, p.is_f16);
             }
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -233,7 +238,7 @@ ffn_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            constexpr uint32_t idesc = ptx::umma_idesc_bf16(BM, BN);
+            const uint32_t idesc = ptx::umma_idesc_16bit(BM, BN, p.is_f16 ? 0u : 1u);
             int stage = 0;
             uint32_t phase = 0;
             int it = 0;
@@ -414,7 +419,7 @@ ffn_grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gr
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer (CTA 0 only)
         if (lane == 0 && cta == 0) {
-            constexpr uint32_t idesc = ptx::umma_idesc_bf16(PBM, BN);
+            const uint32_t idesc = ptx::umma_idesc_16bit(PBM, BN, p.is_f16 ? 0u : 1u);
             const uint32_t empty_peer = ptx::mapa_shared(bar_empty, 1);
             const uint32_t tfull_peer = ptx::mapa_shared(bar_tfull, 1);
             int stage = 0;
@@ -506,14 +511,14 @@ EncodeTiledFn encode_tiled_fn() {
 }
 
 // (outer, rows, K) bf16 tensor, K contiguous; box = 64 x 128 x 1 with the 128-byte swizzle.
-aristos_status_t make_map_3d(CUtensorMap* tm, const void* base, int K, int rows, int outer) {
+aristos_status_t make_map_3d(CUtensorMap* tm, const void* base, int K, int rows, int outer, int is_f16) {
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) { set_last_error("cuTensorMapEncodeTiled is not available from the driver"); return ARISTOS_ERR_CUDA; }
     const cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)rows, (cuuint64_t)outer};
     const cuuint64_t strides[2] = {(cuuint64_t)K * 2, (cuuint64_t)K * 2 * (cuuint64_t)rows};
     const cuuint32_t box[3] = {BK, 128, 1};
     const cuuint32_t estr[3] = {1, 1, 1};
-    const CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+    const CUresult r = enc(tm, is_f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
@@ -539,10 +544,10 @@ bool use_pair_tiles(int window_rows) {
 aristos_status_t launch_gemm(const void* A, const void* B0, const void* B1, const FfnGemmParams& p, int grid_limit,
                              cudaStream_t st) {
     CUtensorMap tmA, tmB0, tmB1, tmOut;
-    ARISTOS_TRY(make_map_3d(&tmA, A, p.K, p.rows_per_group, p.groups));
-    ARISTOS_TRY(make_map_3d(&tmB0, B0, p.K, p.N, p.experts));
-    ARISTOS_TRY(make_map_3d(&tmB1, B1, p.K, p.N, p.experts));
-    ARISTOS_TRY(make_map_3d(&tmOut, p.out, p.N, p.rows_per_group, p.groups));
+    ARISTOS_TRY(make_map_3d(&tmA, A, p.K, p.rows_per_group, p.groups, p.is_f16));
+    ARISTOS_TRY(make_map_3d(&tmB0, B0, p.K, p.N, p.experts, p.is_f16));
+    ARISTOS_TRY(make_map_3d(&tmB1, B1, p.K, p.N, p.experts, p.is_f16));
+    ARISTOS_TRY(make_map_3d(&tmOut, p.out, p.N, p.rows_per_group, p.groups, p.is_f16));
     const int out_w = p.gated ? 128 : 256;
     int sms = device_sm_count();
     if (sms <= 0) { set_last_error("no CUDA device"); return ARISTOS_ERR_CUDA; }
@@ -588,10 +593,10 @@ aristos_status_t launch_gemm(const void* A, const void* B0, const void* B1, cons
 
 }  // namespace
 
-aristos_status_t expert_ffn_bf16_sm100(const void* xg, const int32_t* count, int groups, int rows_per_group,
-                                       int experts, const void* w1, const void* w3, const void* w2, void* h_scratch,
-                                       void* y, int H, int I, int hidden_act, int row_begin, int row_end,
-                                       int sm_limit, int32_t* dev_status, cudaStream_t st) {
+aristos_status_t expert_ffn_16bit_sm100(const void* xg, const int32_t* count, int groups, int rows_per_group,
+                                        int experts, const void* w1, const void* w3, const void* w2, void* h_scratch,
+                                        void* y, int H, int I, int hidden_act, int is_f16, int row_begin,
+                                        int row_end, int sm_limit, int32_t* dev_status, cudaStream_t st) {
     if (groups > MAX_GROUPS) { set_last_error("expert_ffn: more than %d row groups", MAX_GROUPS); return ARISTOS_ERR_CONFIG; }
     if (H % BK != 0 || I % BK != 0) { set_last_error("expert_ffn: H and I must be multiples of 64"); return ARISTOS_ERR_CONFIG; }
     if (row_begin % BM != 0) { set_last_error("expert_ffn: row_begin must be a multiple of 128"); return ARISTOS_ERR_INVALID_ARG; }
@@ -604,19 +609,20 @@ aristos_status_t expert_ffn_bf16_sm100(const void* xg, const int32_t* count, int
     p.row_begin = row_begin;
     p.row_end = row_end;
     p.dev_status = dev_status;
+    p.is_f16 = is_f16;
     // up-projection: h = epi(xg * W1^T [, xg * W3^T])
     p.N = I;
     p.K = H;
     p.gated = gated ? 1 : 0;
     p.act = hidden_act;
-    p.out = static_cast<__nv_bfloat16*>(h_scratch);
+    p.out = h_scratch;
     ARISTOS_TRY(launch_gemm(xg, w1, gated ? w3 : w1, p, sm_limit, st));
     // down-projection: y = h * W2^T
     p.N = H;
     p.K = I;
     p.gated = 0;
     p.act = ARISTOS_ACT_IDENTITY;
-    p.out = static_cast<__nv_bfloat16*>(y);
+    p.out = y;
     ARISTOS_TRY(launch_gemm(h_scratch, w2, w2, p, sm_limit, st));
     return ARISTOS_OK;
 }

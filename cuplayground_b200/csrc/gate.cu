@@ -45,6 +45,12 @@ __device__ __forceinline__ void load8_pairs(const __nv_bfloat16* p, float2 (&v)[
 #pragma unroll
     for (int i = 0; i < 4; ++i) v[i] = make_float2(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xFFFF0000u));
 }
+__device__ __forceinline__ void load8_pairs(const __half* p, float2 (&v)[4]) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+}
 __device__ __forceinline__ void load8_pairs(const float* p, float2 (&v)[4]) {
     const float4 a = *reinterpret_cast<const float4*>(p);
     const float4 b = *reinterpret_cast<const float4*>(p + 4);
@@ -337,8 +343,10 @@ extern "C" aristos_status_t aristos_gate_topk(const void* x, const void* w_gate,
             return launch_gate<float>(x, w_gate, gate_bias, S, H, E, k, gate_fn, renorm, topk_idx, topk_w, logits_out, st);
         case ARISTOS_DTYPE_BF16:
             return launch_gate<__nv_bfloat16>(x, w_gate, gate_bias, S, H, E, k, gate_fn, renorm, topk_idx, topk_w, logits_out, st);
+        case ARISTOS_DTYPE_F16:
+            return launch_gate<__half>(x, w_gate, gate_bias, S, H, E, k, gate_fn, renorm, topk_idx, topk_w, logits_out, st);
         default:
-            set_last_error("gate: dtype %d not implemented (f32 and bf16 are)", dtype);
+            set_last_error("gate: dtype %d not implemented (f32, bf16 and f16 are)", dtype);
             return ARISTOS_ERR_UNSUPPORTED;
     }
 }

@@ -236,9 +236,10 @@ __device__ __forceinline__ uint64_t umma_desc_k_sw128(uint32_t smem_addr) {
     d |= static_cast<uint64_t>(2) << 61;                      // layout: 128-byte swizzle
     return d;
 }
-// Instruction descriptor: bf16 x bf16 -> fp32, both operands K-major, tile M x N.
-__host__ __device__ constexpr uint32_t umma_idesc_bf16(int M, int N) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(N >> 3) << 17) |
+// Instruction descriptor of kind::f16: 16-bit inputs (ab_format 1 = bf16, 0 = f16) -> fp32, both operands K-major,
+// tile M x N.
+__host__ __device__ constexpr uint32_t umma_idesc_16bit(int M, int N, uint32_t ab_format) {
+    return (1u << 4) | (ab_format << 7) | (ab_format << 10) | (static_cast<uint32_t>(N >> 3) << 17) |
            (static_cast<uint32_t>(M >> 4) << 24);
 }
 

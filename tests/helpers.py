@@ -9,10 +9,14 @@ from oracle import moe_oracle as O
 STREAM_X, STREAM_WG, STREAM_W1, STREAM_W3, STREAM_W2 = 0, 1, 2, 3, 4
 
 
-def make_inputs(S, H, I, E, seed, *, swiglu=False, bf16=True, w_std=0.02):
+def round_f16(a):
+    return np.asarray(a, dtype=np.float32).astype(np.float16).astype(np.float32)
+
+
+def make_inputs(S, H, I, E, seed, *, swiglu=False, bf16=True, w_std=0.02, f16=False):
     """x ~ N(0,1), weights ~ N(0, w_std), in storage layout: x (S,H), wg (E,H), w1/w3 (E,I,H), w2 (E,H,I).
-    With bf16=True the fp32 arrays hold bf16-representable values (what the GPU stores)."""
-    rnd = O.round_bf16 if bf16 else (lambda a: a)
+    With bf16=True (f16=True) the fp32 arrays hold bf16- (fp16-) representable values (what the GPU stores)."""
+    rnd = round_f16 if f16 else (O.round_bf16 if bf16 else (lambda a: a))
     x = rnd(O.fill_normal(S * H, 0.0, 1.0, seed, STREAM_X)).reshape(S, H)
     wg = rnd(O.fill_normal(E * H, 0.0, w_std, seed, STREAM_WG)).reshape(E, H)
     w1 = rnd(O.fill_normal(E * I * H, 0.0, w_std, seed, STREAM_W1)).reshape(E, I, H)

@@ -24,11 +24,11 @@ def _check_routing(r, ref):
 
 def _run_layer(cfg, seed, oracle, w_std=0.02, only_rows=None):
     torch, cp, layer = _mods()
-    bf16 = cfg.torch_dtype == 2
-    dt = torch.bfloat16 if bf16 else torch.float32
+    bf16, f16 = cfg.torch_dtype == 2, cfg.torch_dtype == 3
+    dt = torch.bfloat16 if bf16 else (torch.float16 if f16 else torch.float32)
     swiglu = cfg.hidden_act == 2
     x, wg, w1, w3, w2 = make_inputs(cfg.S, cfg.hidden_size, cfg.intermediate_size, cfg.num_experts, seed,
-                                    swiglu=swiglu, bf16=bf16, w_std=w_std)
+                                    swiglu=swiglu, bf16=bf16, w_std=w_std, f16=f16)
     L = layer.MoELayer(cfg)
     out = L.forward(*(to_dev(a, dt) for a in (x, wg, w1, w3, w2)))
     L.status()
@@ -155,9 +155,22 @@ def test_forward_host_matches_device_forward(oracle):
     L.close()
 
 
+@pytest.mark.parametrize("act,k", [(1, 2), (2, 2), (0, 1)])
+def test_layer_fp16(oracle, act, k):
+    """torch_dtype 3 (fp16, aristos_config.schema.json:54-58): same kernels with f16 MMA inputs; fp16 keeps 11
+    significant bits, so the outputs sit well inside the 16-bit tolerance."""
+    torch, cp, layer = _mods()
+    cfg = cp.AristosConfig(capacity_factor=1.25, drop_tokens=1, expert_top_k=k, hidden_act=act, hidden_size=256,
+                           intermediate_size=512, num_experts=8, torch_dtype=3, tokens=512, renorm_topk=1)
+    got, r, ref = _run_layer(cfg, 13, oracle, w_std=0.05)
+    _check_routing(r, ref)
+    mx, mean = rel_errors(got, ref["out"])
+    assert mx < TOL_BF16_MAX / 4 and mean < TOL_BF16_MEAN / 4, (mx, mean)
+
+
 def test_unsupported_dtype_fails_loudly():
     torch, cp, layer = _mods()
-    cfg = cp.AristosConfig(hidden_size=128, intermediate_size=128, num_experts=4, torch_dtype=3, tokens=128)
+    cfg = cp.AristosConfig(hidden_size=128, intermediate_size=128, num_experts=4, torch_dtype=1, tokens=128)
     with pytest.raises(cp.AristosError) as e:
         layer.MoELayer(cfg)
     assert e.value.status == 6
