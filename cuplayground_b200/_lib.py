@@ -63,6 +63,7 @@ PROTOTYPES = {
     "aristos_ep_row_windows": (_st, [_i, C.POINTER(_i), C.POINTER(_i)]),
     "aristos_moe_workspace_bytes": (_sz, [_vp]),
     "aristos_moe_set_workspace": (_st, [_vp, _vp, _sz]),
+    "aristos_moe_set_bias": (_st, [_vp, _vp, _vp, _vp]),
     "aristos_moe_forward": (_st, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "aristos_moe_forward_host": (_st, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "aristos_moe_submit_host": (_st, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
@@ -81,6 +82,8 @@ PROTOTYPES = {
     "aristos_dispatch_static": (_st, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "aristos_permute": (_st, [_vp, _vp, _i, _i, _i, _i, _vp, _vp]),
     "aristos_expert_ffn": (_st, [_vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp]),
+    "aristos_expert_ffn_bias": (_st, [_vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
+                                      _i, _vp, _vp]),
     "aristos_combine": (_st, [_vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp]),
     "aristos_selftest_bounded_wait": (_st, [_i, C.POINTER(_i), _vp]),
     "aristos_fill_normal": (_st, [_vp, C.c_int64, C.c_float, C.c_float, C.c_uint64, C.c_uint32, _i, _vp]),

@@ -4,12 +4,14 @@
 
 namespace aristos {
 aristos_status_t expert_ffn_16bit_sm100(const void* xg, const int32_t* count, int groups, int rows_per_group,
-                                        int experts, const void* w1, const void* w3, const void* w2, void* h_scratch,
-                                        void* y, int H, int I, int hidden_act, int is_f16, int row_begin,
-                                        int row_end, int sm_limit, int32_t* dev_status, cudaStream_t st);
+                                        int experts, const void* w1, const void* w3, const void* w2, const void* b1,
+                                        const void* b3, const void* b2, void* h_scratch, void* y, int H, int I,
+                                        int hidden_act, int is_f16, int row_begin, int row_end, int sm_limit,
+                                        int32_t* dev_status, cudaStream_t st);
 aristos_status_t expert_ffn_f32_simt(const void* xg, const int32_t* count, int groups, int rows_per_group, int experts,
-                                     const void* w1, const void* w3, const void* w2, void* h_scratch, void* y, int H,
-                                     int I, int hidden_act, int row_begin, int row_end, cudaStream_t st);
+                                     const void* w1, const void* w3, const void* w2, const void* b1, const void* b3,
+                                     const void* b2, void* h_scratch, void* y, int H, int I, int hidden_act,
+                                     int row_begin, int row_end, cudaStream_t st);
 }  // namespace aristos
 
 using namespace aristos;
@@ -19,6 +21,17 @@ extern "C" aristos_status_t aristos_expert_ffn(const void* xg, const int32_t* co
                                                void* h_scratch, void* y, int H, int I, int hidden_act, int dtype,
                                                int row_begin, int row_end, int sm_limit, int32_t* dev_status,
                                                void* stream) {
+    return aristos_expert_ffn_bias(xg, count, groups, rows_per_group, experts, w1, w3, w2, nullptr, nullptr, nullptr,
+                                   h_scratch, y, H, I, hidden_act, dtype, row_begin, row_end, sm_limit, dev_status,
+                                   stream);
+}
+
+extern "C" aristos_status_t aristos_expert_ffn_bias(const void* xg, const int32_t* count, int groups,
+                                                    int rows_per_group, int experts, const void* w1, const void* w3,
+                                                    const void* w2, const void* b1, const void* b3, const void* b2,
+                                                    void* h_scratch, void* y, int H, int I, int hidden_act, int dtype,
+                                                    int row_begin, int row_end, int sm_limit, int32_t* dev_status,
+                                                    void* stream) {
     if (!xg || !count || !w1 || !w2 || !h_scratch || !y) { set_last_error("expert_ffn: NULL pointer"); return ARISTOS_ERR_INVALID_ARG; }
     if (hidden_act == ARISTOS_ACT_SWIGLU && !w3) { set_last_error("expert_ffn: SwiGLU needs w3"); return ARISTOS_ERR_INVALID_ARG; }
     if (hidden_act < 0 || hidden_act > 2) { set_last_error("expert_ffn: hidden_act must be 0, 1 or 2"); return ARISTOS_ERR_INVALID_ARG; }
@@ -28,7 +41,7 @@ extern "C" aristos_status_t aristos_expert_ffn(const void* xg, const int32_t* co
         return ARISTOS_ERR_INVALID_ARG;
     }
     if (!aligned16(xg) || !aligned16(w1) || !aligned16(w2) || !aligned16(h_scratch) || !aligned16(y) ||
-        (w3 && !aligned16(w3))) {
+        (w3 && !aligned16(w3)) || (b1 && !aligned16(b1)) || (b3 && !aligned16(b3)) || (b2 && !aligned16(b2))) {
         set_last_error("expert_ffn: pointers must be 16-byte aligned");
         return ARISTOS_ERR_INVALID_ARG;
     }
@@ -41,11 +54,11 @@ extern "C" aristos_status_t aristos_expert_ffn(const void* xg, const int32_t* co
     switch (dtype) {
         case ARISTOS_DTYPE_BF16:
         case ARISTOS_DTYPE_F16:
-            return expert_ffn_16bit_sm100(xg, count, groups, rows_per_group, experts, w1, w3, w2, h_scratch, y, H, I,
+            return expert_ffn_16bit_sm100(xg, count, groups, rows_per_group, experts, w1, w3, w2, b1, b3, b2, h_scratch, y, H, I,
                                           hidden_act, dtype == ARISTOS_DTYPE_F16 ? 1 : 0, row_begin, row_end, sm_limit,
                                           dev_status, st);
         case ARISTOS_DTYPE_F32:
-            return expert_ffn_f32_simt(xg, count, groups, rows_per_group, experts, w1, w3, w2, h_scratch, y, H, I,
+            return expert_ffn_f32_simt(xg, count, groups, rows_per_group, experts, w1, w3, w2, b1, b3, b2, h_scratch, y, H, I,
                                        hidden_act, row_begin, row_end, st);
         default:
             set_last_error("expert_ffn: dtype %d not implemented (f32, bf16 and f16 are)", dtype);

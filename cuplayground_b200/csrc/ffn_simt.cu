@@ -15,7 +15,7 @@ constexpr int TK = 16;   // K slab
 // out[g, r, n] = epi( sum_k A[g, r, k] * B0[e, n, k] [, sum_k A[g, r, k] * B1[e, n, k]] )
 __global__ void __launch_bounds__(256)
 ffn_simt_kernel(const float* __restrict__ A, const float* __restrict__ B0, const float* __restrict__ B1,
-                const int32_t* __restrict__ count, int experts, int rows_per_group, int row_begin, int row_end, int N,
+                const float* __restrict__ bias0, const float* __restrict__ bias1, const int32_t* __restrict__ count, int experts, int rows_per_group, int row_begin, int row_end, int N,
                 int K, int gated, int act, float* __restrict__ out) {
     const int g = blockIdx.z;
     const int m0 = row_begin + blockIdx.y * TS;
@@ -66,7 +66,12 @@ ffn_simt_kernel(const float* __restrict__ A, const float* __restrict__ B0, const
             const int col = n0 + tx * 4 + j;
             if (col >= N) continue;
             float v = acc0[i][j];
-            if (gated) v = (v / (1.0f + expf(-v))) * acc1[i][j];
+            if (bias0) v += bias0[(size_t)e * N + col];
+            if (gated) {
+                float u = acc1[i][j];
+                if (bias1) u += bias1[(size_t)e * N + col];
+                v = (v / (1.0f + expf(-v))) * u;
+            }
             else if (act == ARISTOS_ACT_RELU) v = act_relu(v);
             else if (act == ARISTOS_ACT_GELU) v = act_gelu(v);
             out[((size_t)g * rows_per_group + row) * N + col] = v;
@@ -77,19 +82,22 @@ ffn_simt_kernel(const float* __restrict__ A, const float* __restrict__ B0, const
 }  // namespace
 
 aristos_status_t expert_ffn_f32_simt(const void* xg, const int32_t* count, int groups, int rows_per_group, int experts,
-                                     const void* w1, const void* w3, const void* w2, void* h_scratch, void* y, int H,
-                                     int I, int hidden_act, int row_begin, int row_end, cudaStream_t st) {
+                                     const void* w1, const void* w3, const void* w2, const void* b1, const void* b3,
+                                     const void* b2, void* h_scratch, void* y, int H, int I, int hidden_act,
+                                     int row_begin, int row_end, cudaStream_t st) {
     if (groups > 65535) { set_last_error("expert_ffn(f32): too many groups"); return ARISTOS_ERR_CONFIG; }
     if (H % TK != 0 || I % TK != 0) { set_last_error("expert_ffn(f32): H and I must be multiples of 16"); return ARISTOS_ERR_CONFIG; }
     const int mt = ceil_div(row_end - row_begin, TS);
     if (mt <= 0 || groups <= 0) return ARISTOS_OK;
     const bool gated = hidden_act == ARISTOS_ACT_SWIGLU;
     dim3 g1(ceil_div(I, TS), mt, groups), g2(ceil_div(H, TS), mt, groups);
-    ffn_simt_kernel<<<g1, 256, 0, st>>>((const float*)xg, (const float*)w1, (const float*)w3, count, experts,
+    ffn_simt_kernel<<<g1, 256, 0, st>>>((const float*)xg, (const float*)w1, (const float*)w3, (const float*)b1,
+                                        gated ? (const float*)b3 : nullptr, count, experts,
                                         rows_per_group, row_begin, row_end, I, H, gated ? 1 : 0, hidden_act,
                                         (float*)h_scratch);
     ARISTOS_COUNT_LAUNCH();
-    ffn_simt_kernel<<<g2, 256, 0, st>>>((const float*)h_scratch, (const float*)w2, nullptr, count, experts,
+    ffn_simt_kernel<<<g2, 256, 0, st>>>((const float*)h_scratch, (const float*)w2, nullptr, (const float*)b2, nullptr,
+                                        count, experts,
                                         rows_per_group, row_begin, row_end, H, I, 0, ARISTOS_ACT_IDENTITY, (float*)y);
     ARISTOS_COUNT_LAUNCH();
     ARISTOS_CUDA_TRY(cudaGetLastError());

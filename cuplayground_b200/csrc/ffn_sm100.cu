@@ -65,6 +65,8 @@ struct FfnGemmParams {
     int act;                // ARISTOS_ACT_* for the non-gated epilogue
     void* out;              // (groups * rows_per_group, N), 16-bit elements
     int is_f16;             // 0: bf16 operands and output, 1: f16
+    const void* bias0;      // (experts, N) added to the accumulator before the activation, or nullptr
+    const void* bias1;      // SwiGLU: bias of the second (up) projection, or nullptr
     int32_t* dev_status;
 };
 
@@ -75,6 +77,29 @@ __device__ __forceinline__ uint32_t pack_16bit(float a, float b, int is_f16) {
     }
     __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
     return *reinterpret_cast<uint32_t*>(&t);
+}
+
+// acc[0..31] += bias[0..31] (16-bit elements, the same 64 bytes for every thread of the CTA: a broadcast load).
+__device__ __forceinline__ void add_bias32(uint32_t (&acc)[32], const void* bias, size_t elem_offset, int is_f16) {
+    const uint4* b = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(bias) + elem_offset);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const uint4 u = __ldg(b + q);
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float lo, hi;
+            if (is_f16) {
+                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+                lo = f.x; hi = f.y;
+            } else {
+                lo = __uint_as_float(w[i] << 16);
+                hi = __uint_as_float(w[i] & 0xFFFF0000u);
+            }
+            acc[q * 8 + 2 * i] = __float_as_uint(__uint_as_float(acc[q * 8 + 2 * i]) + lo);
+            acc[q * 8 + 2 * i + 1] = __float_as_uint(__uint_as_float(acc[q * 8 + 2 * i + 1]) + hi);
+        }
+    }
 }
 
 // Epilogue of one 128-row tile, run by the four epilogue warps of a CTA (thread = accumulator row): TMEM -> registers
@@ -110,6 +135,11 @@ __device__ __forceinline__ void epilogue_tile(const FfnGemmParams& p, const CUte
                 } else {
                     ptx::mbar_arrive(tempty);
                 }
+            }
+            if (n0 + col < p.N) {          // act(acc + bias), the reference's epilogue (processor/tiling.cuh:29-57)
+                const size_t boff = (size_t)(g % p.experts) * p.N + n0 + col;
+                if (p.bias0) add_bias32(a, p.bias0, boff, p.is_f16);
+                if (p.gated && p.bias1) add_bias32(b, p.bias1, boff, p.is_f16);
             }
             uint32_t o[16];
 #pragma unroll
@@ -594,9 +624,10 @@ aristos_status_t launch_gemm(const void* A, const void* B0, const void* B1, cons
 }  // namespace
 
 aristos_status_t expert_ffn_16bit_sm100(const void* xg, const int32_t* count, int groups, int rows_per_group,
-                                        int experts, const void* w1, const void* w3, const void* w2, void* h_scratch,
-                                        void* y, int H, int I, int hidden_act, int is_f16, int row_begin,
-                                        int row_end, int sm_limit, int32_t* dev_status, cudaStream_t st) {
+                                        int experts, const void* w1, const void* w3, const void* w2, const void* b1,
+                                        const void* b3, const void* b2, void* h_scratch, void* y, int H, int I,
+                                        int hidden_act, int is_f16, int row_begin, int row_end, int sm_limit,
+                                        int32_t* dev_status, cudaStream_t st) {
     if (groups > MAX_GROUPS) { set_last_error("expert_ffn: more than %d row groups", MAX_GROUPS); return ARISTOS_ERR_CONFIG; }
     if (H % BK != 0 || I % BK != 0) { set_last_error("expert_ffn: H and I must be multiples of 64"); return ARISTOS_ERR_CONFIG; }
     if (row_begin % BM != 0) { set_last_error("expert_ffn: row_begin must be a multiple of 128"); return ARISTOS_ERR_INVALID_ARG; }
@@ -616,6 +647,8 @@ aristos_status_t expert_ffn_16bit_sm100(const void* xg, const int32_t* count, in
     p.gated = gated ? 1 : 0;
     p.act = hidden_act;
     p.out = h_scratch;
+    p.bias0 = b1;
+    p.bias1 = gated ? b3 : nullptr;
     ARISTOS_TRY(launch_gemm(xg, w1, gated ? w3 : w1, p, sm_limit, st));
     // down-projection: y = h * W2^T
     p.N = H;
@@ -623,6 +656,8 @@ aristos_status_t expert_ffn_16bit_sm100(const void* xg, const int32_t* count, in
     p.gated = 0;
     p.act = ARISTOS_ACT_IDENTITY;
     p.out = y;
+    p.bias0 = b2;
+    p.bias1 = nullptr;
     ARISTOS_TRY(launch_gemm(h_scratch, w2, w2, p, sm_limit, st));
     return ARISTOS_OK;
 }

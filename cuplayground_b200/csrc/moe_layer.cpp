@@ -56,6 +56,7 @@ struct aristos_moe {
     std::vector<cudaEvent_t> ev_in, ev_out;
     int chunks = 1, chunk_rows = 0, ffn_sm_limit = 0;
     int64_t launches = 0;
+    const void *b1 = nullptr, *b3 = nullptr, *b2 = nullptr;   // optional expert biases (caller-owned, device)
     // stage stopwatch
     static constexpr int PROF_SETS = 64;      // ring of event sets: stage times average over the last 64 forwards
     bool profiling = false;
@@ -209,6 +210,18 @@ aristos_status_t aristos_moe_create(const aristos_config_t* cfg, int rank, int w
 
 size_t aristos_moe_workspace_bytes(const aristos_moe_t* L) { return L ? L->ws_bytes : 0; }
 
+aristos_status_t aristos_moe_set_bias(aristos_moe_t* L, const void* b1, const void* b3, const void* b2) {
+    if (!L) return ARISTOS_ERR_INVALID_ARG;
+    if ((b1 && !aligned16(b1)) || (b3 && !aligned16(b3)) || (b2 && !aligned16(b2))) {
+        set_last_error("set_bias: pointers must be 16-byte aligned");
+        return ARISTOS_ERR_INVALID_ARG;
+    }
+    L->b1 = b1;
+    L->b3 = b3;
+    L->b2 = b2;
+    return ARISTOS_OK;
+}
+
 aristos_status_t aristos_moe_set_workspace(aristos_moe_t* L, void* workspace, size_t bytes) {
     if (!L || !workspace) return ARISTOS_ERR_INVALID_ARG;
     if (bytes < L->ws_bytes) { set_last_error("workspace: %zu bytes given, %zu needed", bytes, L->ws_bytes); return ARISTOS_ERR_WORKSPACE; }
@@ -257,7 +270,7 @@ aristos_status_t aristos_moe_forward(aristos_moe_t* L, const void* x, const void
     PROF_MARK(2);
 
     if (L->world == 1) {
-        ARISTOS_TRY(aristos_expert_ffn(L->xg, L->count, L->E, L->cap, L->E, w1, w3, w2, L->h, L->yr, L->H, L->I,
+        ARISTOS_TRY(aristos_expert_ffn_bias(L->xg, L->count, L->E, L->cap, L->E, w1, w3, w2, L->b1, L->b3, L->b2, L->h, L->yr, L->H, L->I,
                                        L->cfg.hidden_act, dt, 0, L->cap, 0, L->dev_status, st));
     } else if (L->p2p) {
         // rows are pushed into the destination GPUs by the copy engines; flags + stream waits order the streams
@@ -279,7 +292,7 @@ aristos_status_t aristos_moe_forward(aristos_moe_t* L, const void* x, const void
         for (int c = 0; c < L->chunks; ++c) {
             const int r0 = c * L->chunk_rows, r1 = std::min(L->cap, r0 + L->chunk_rows);
             ARISTOS_TRY(ep_p2p_wait(L->p2p, EP_FLAG_IN, c, st));
-            ARISTOS_TRY(aristos_expert_ffn(L->xr, L->rcount, L->groups, L->cap, L->E_local, w1, w3, w2, L->h, L->yr,
+            ARISTOS_TRY(aristos_expert_ffn_bias(L->xr, L->rcount, L->groups, L->cap, L->E_local, w1, w3, w2, L->b1, L->b3, L->b2, L->h, L->yr,
                                            L->H, L->I, L->cfg.hidden_act, dt, r0, r1, 0, L->dev_status, st));
             ARISTOS_CUDA_TRY(cudaEventRecord(L->ev_out[c], st));
             ARISTOS_CUDA_TRY(cudaStreamWaitEvent(L->comm_stream, L->ev_out[c], 0));
@@ -305,7 +318,7 @@ aristos_status_t aristos_moe_forward(aristos_moe_t* L, const void* x, const void
         for (int c = 0; c < L->chunks; ++c) {
             const int r0 = c * L->chunk_rows, r1 = std::min(L->cap, r0 + L->chunk_rows);
             ARISTOS_CUDA_TRY(cudaStreamWaitEvent(st, L->ev_in[c], 0));
-            ARISTOS_TRY(aristos_expert_ffn(L->xr, L->rcount, L->groups, L->cap, L->E_local, w1, w3, w2, L->h, L->yr,
+            ARISTOS_TRY(aristos_expert_ffn_bias(L->xr, L->rcount, L->groups, L->cap, L->E_local, w1, w3, w2, L->b1, L->b3, L->b2, L->h, L->yr,
                                            L->H, L->I, L->cfg.hidden_act, dt, r0, r1, L->ffn_sm_limit, L->dev_status,
                                            st));
             ARISTOS_CUDA_TRY(cudaEventRecord(L->ev_out[c], st));

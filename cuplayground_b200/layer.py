@@ -116,8 +116,10 @@ def permute(x, slot_of, nslots: int, zero: bool = False):
 
 
 def expert_ffn(xg, count, w1, w3, w2, hidden_act: int, *, experts: Optional[int] = None, row_begin: int = 0,
-               row_end: Optional[int] = None, sm_limit: int = 0, dev_status=None, y=None, h=None):
-    """xg (groups, rows, H); w1/w3 (experts, I, H); w2 (experts, H, I) -> y (groups, rows, H)."""
+               row_end: Optional[int] = None, sm_limit: int = 0, dev_status=None, y=None, h=None, b1=None, b3=None,
+               b2=None):
+    """xg (groups, rows, H); w1/w3 (experts, I, H); w2 (experts, H, I); optional biases b1/b3 (experts, I),
+    b2 (experts, H) -> y (groups, rows, H)."""
     groups, rows, H = xg.shape
     I = w1.shape[1]
     experts = w1.shape[0] if experts is None else experts
@@ -126,9 +128,10 @@ def expert_ffn(xg, count, w1, w3, w2, hidden_act: int, *, experts: Optional[int]
         h = torch.empty((groups, rows, I), dtype=xg.dtype, device=xg.device)
     if y is None:
         y = torch.zeros((groups, rows, H), dtype=xg.dtype, device=xg.device)
-    _lib.check(_lib.load().aristos_expert_ffn(_ptr(xg), _ptr(count), groups, rows, experts, _ptr(w1), _ptr(w3),
-                                              _ptr(w2), _ptr(h), _ptr(y), H, I, hidden_act, _dt(xg), row_begin,
-                                              row_end, sm_limit, _ptr(dev_status), _stream_ptr()))
+    _lib.check(_lib.load().aristos_expert_ffn_bias(_ptr(xg), _ptr(count), groups, rows, experts, _ptr(w1), _ptr(w3),
+                                                   _ptr(w2), _ptr(b1), _ptr(b3), _ptr(b2), _ptr(h), _ptr(y), H, I,
+                                                   hidden_act, _dt(xg), row_begin, row_end, sm_limit,
+                                                   _ptr(dev_status), _stream_ptr()))
     return y
 
 
@@ -170,6 +173,11 @@ class MoELayer:
         self._ws = torch.empty(self.workspace_bytes + 1024, dtype=torch.uint8, device="cuda")
         base = (self._ws.data_ptr() + 1023) // 1024 * 1024
         _lib.check(self._lib.aristos_moe_set_workspace(self._h, C.c_void_p(base), self.workspace_bytes))
+
+    def set_bias(self, b1=None, b3=None, b2=None) -> None:
+        """Expert biases (E_local, I) / (E_local, I) / (E_local, H) for every later forward; kept alive here."""
+        self._bias = (b1, b3, b2)
+        _lib.check(self._lib.aristos_moe_set_bias(self._h, _ptr(b1), _ptr(b3), _ptr(b2)))
 
     def forward(self, x, w_gate, w1, w3, w2, gate_bias=None, out=None, stream=None):
         if out is None:

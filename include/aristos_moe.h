@@ -130,6 +130,10 @@ ARISTOS_API size_t aristos_moe_workspace_bytes(const aristos_moe_t* layer);
 /* Optional: hand the layer a caller-owned device workspace (>= aristos_moe_workspace_bytes, 1024-byte aligned).
  * Without it the first forward allocates one with cudaMalloc and keeps it until destroy. */
 ARISTOS_API aristos_status_t aristos_moe_set_workspace(aristos_moe_t* layer, void* workspace, size_t bytes);
+/* Optional expert biases used by every later forward (device pointers owned by the caller, NULL = none):
+ * b1 (E_local, I), b3 (E_local, I; SwiGLU only), b2 (E_local, H), in the activations' dtype. */
+ARISTOS_API aristos_status_t aristos_moe_set_bias(aristos_moe_t* layer, const void* b1, const void* b3,
+                                                  const void* b2);
 /*
  * One forward of the layer on this rank.
  *   x (S,H) activations          w_gate (E,H)        gate_bias (E) fp32 or NULL (NULL + gate_bias_zipf_s > 0 =
@@ -228,6 +232,15 @@ ARISTOS_API aristos_status_t aristos_expert_ffn(const void* xg, const int32_t* c
                                                 const void* w2, void* h_scratch, void* y, int H, int I,
                                                 int hidden_act, int dtype, int row_begin, int row_end,
                                                 int sm_limit, int32_t* dev_status, void* stream);
+/* The same with the reference's bias operand: the epilogue is act(acc + bias) (FAA, processor/tiling.cuh:29-57; bias
+ * tile (1,N), mma.cuh:87-95, :426-427). b1 (experts, I), b3 (experts, I; SwiGLU up projection), b2 (experts, H), in
+ * the activations' dtype; any of them may be NULL. */
+ARISTOS_API aristos_status_t aristos_expert_ffn_bias(const void* xg, const int32_t* count, int groups,
+                                                     int rows_per_group, int experts, const void* w1, const void* w3,
+                                                     const void* w2, const void* b1, const void* b3, const void* b2,
+                                                     void* h_scratch, void* y, int H, int I, int hidden_act,
+                                                     int dtype, int row_begin, int row_end, int sm_limit,
+                                                     int32_t* dev_status, void* stream);
 /* Combine: out[t] = sum_j topk_w[t,j] * y[slot_of[t,j]] in increasing j (fp32), dropped assignments add
  * nothing. Replaces Combine / VAA / deviceCombine (auditorium/combine.cuh:19-205). */
 ARISTOS_API aristos_status_t aristos_combine(const void* y, const int32_t* slot_of, const float* topk_w, int S,

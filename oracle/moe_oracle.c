@@ -249,11 +249,12 @@ ORC_API void orc_gemm_bias_act(const float* A, const float* B, const float* bias
 
 /* Expert FFN over the gathered rows of every expert.
  *   xg (E, cap, H); w1 (E, I, H); w3 (E, I, H) or NULL; w2 (E, H, I); y (E, cap, H)
+ *   optional biases b1 (E, I), b3 (E, I), b2 (E, H): every projection is act(acc + bias) (processor/tiling.cuh:29-57)
  *   hidden_act 0 relu, 1 gelu: h = act(xg w1^T); 2 swiglu: h = silu(xg w1^T) * (xg w3^T);  y = h w2^T
  * Rows at or past count[e] are left untouched. round_h != 0 rounds h to bf16 (what a bf16 pipeline stores). */
 ORC_API void orc_expert_ffn(const float* xg, const int32_t* count, const float* w1, const float* w3,
-                            const float* w2, float* y, int E, int cap, int H, int I, int hidden_act,
-                            int round_h) {
+                            const float* w2, const float* b1, const float* b3, const float* b2, float* y, int E,
+                            int cap, int H, int I, int hidden_act, int round_h) {
     int64_t total = 0;
     for (int e = 0; e < E; ++e) total += count[e];
     int32_t* row_e = (int32_t*)malloc(sizeof(int32_t) * (size_t)(total > 0 ? total : 1));
@@ -274,9 +275,15 @@ ORC_API void orc_expert_ffn(const float* xg, const int32_t* count, const float* 
             const float* W2 = w2 + (size_t)e * H * I;
             for (int n1 = 0; n1 < I; ++n1) {
                 float g = dotf(xr, W1 + (size_t)n1 * H, H);
+                if (b1) g += b1[(size_t)e * I + n1];
                 float v;
-                if (hidden_act == 2) v = silu(g) * dotf(xr, W3 + (size_t)n1 * H, H);
-                else v = act_apply(g, hidden_act);
+                if (hidden_act == 2) {
+                    float u = dotf(xr, W3 + (size_t)n1 * H, H);
+                    if (b3) u += b3[(size_t)e * I + n1];
+                    v = silu(g) * u;
+                } else {
+                    v = act_apply(g, hidden_act);
+                }
                 h[n1] = v;
             }
             if (round_h) {
@@ -288,7 +295,11 @@ ORC_API void orc_expert_ffn(const float* xg, const int32_t* count, const float* 
                 }
             }
             float* yr = y + row * H;
-            for (int n2 = 0; n2 < H; ++n2) yr[n2] = dotf(h, W2 + (size_t)n2 * I, I);
+            for (int n2 = 0; n2 < H; ++n2) {
+                float v = dotf(h, W2 + (size_t)n2 * I, I);
+                if (b2) v += b2[(size_t)e * H + n2];
+                yr[n2] = v;
+            }
         }
         free(h);
     }

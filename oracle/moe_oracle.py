@@ -127,15 +127,18 @@ def permute(x, token_of_slot) -> np.ndarray:
     return xg
 
 
-def expert_ffn(xg, count, w1, w3, w2, hidden_act: int, round_h: int = 0) -> np.ndarray:
-    """xg (E,cap,H), w1/w3 (E,I,H), w2 (E,H,I) -> y (E,cap,H); rows past count[e] stay zero."""
+def expert_ffn(xg, count, w1, w3, w2, hidden_act: int, round_h: int = 0, b1=None, b3=None, b2=None) -> np.ndarray:
+    """xg (E,cap,H), w1/w3 (E,I,H), w2 (E,H,I), optional biases b1/b3 (E,I), b2 (E,H) -> y (E,cap,H); rows past
+    count[e] stay zero."""
+    b1, b3, b2 = (None if b is None else _cf(b) for b in (b1, b3, b2))
     xg, w1, w2 = _cf(xg), _cf(w1), _cf(w2)
     w3 = None if w3 is None else _cf(w3)
     count = np.ascontiguousarray(count, dtype=np.int32)
     E, cap, H = xg.shape
     I = w1.shape[1]
     y = np.zeros((E, cap, H), dtype=np.float32)
-    lib().orc_expert_ffn(_f(xg), _i(count), _f(w1), _f(w3), _f(w2), _f(y), E, cap, H, I, hidden_act, round_h)
+    lib().orc_expert_ffn(_f(xg), _i(count), _f(w1), _f(w3), _f(w2), _f(b1), _f(b3), _f(b2), _f(y), E, cap, H, I,
+                         hidden_act, round_h)
     return y
 
 

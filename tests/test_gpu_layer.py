@@ -211,3 +211,27 @@ def test_submit_host_pipelines_consecutive_calls(oracle):
     for i in range(3):
         assert torch.equal(oh[i], expect[i]), i
     L.close()
+
+
+def test_layer_with_expert_biases(oracle):
+    """aristos_moe_set_bias: the layer equals gate -> dispatch -> gather -> biased expert FFN -> combine of the
+    oracle."""
+    torch, cp, layer = _mods()
+    S, H, I, E, k = 512, 128, 256, 4, 2
+    cfg = cp.AristosConfig(capacity_factor=1.25, drop_tokens=1, expert_top_k=k, hidden_act=2, hidden_size=H,
+                           intermediate_size=I, num_experts=E, torch_dtype=2, tokens=S)
+    x, wg, w1, w3, w2 = make_inputs(S, H, I, E, 17, swiglu=True, w_std=0.05)
+    rng = np.random.default_rng(3)
+    b1, b3, b2 = (oracle.round_bf16(rng.standard_normal(s).astype(np.float32) * 0.3) for s in ((E, I), (E, I), (E, H)))
+    dt = torch.bfloat16
+    L = layer.MoELayer(cfg)
+    L.set_bias(to_dev(b1, dt), to_dev(b3, dt), to_dev(b2, dt))
+    out = L.forward(*(to_dev(a, dt) for a in (x, wg, w1, w3, w2)))
+    L.status()
+    idx, w = oracle.gate_topk(oracle.gate_logits(x, wg), k, 0, 0)
+    count, slot_of, tos = oracle.dispatch(idx, E, cfg.capacity)
+    y = oracle.expert_ffn(oracle.permute(x, tos).reshape(E, cfg.capacity, H), count, w1, w3, w2, 2, b1=b1, b3=b3, b2=b2)
+    ref = oracle.combine(y, slot_of, w)
+    mx, mean = rel_errors(out.float().cpu().numpy(), ref)
+    assert mx < TOL_BF16_MAX and mean < TOL_BF16_MEAN, (mx, mean)
+    L.close()

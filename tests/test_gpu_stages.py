@@ -227,3 +227,48 @@ def test_fill_normal_matches_oracle_generator(cp, oracle):
     ref = oracle.fill_normal(n, 0.5, 2.0, 0x1234567890, 7)
     np.testing.assert_allclose(t.cpu().numpy(), ref, rtol=0, atol=2e-5)
     assert abs(float(t.mean()) - 0.5) < 0.05 and abs(float(t.std()) - 2.0) < 0.05
+
+
+def test_expert_tile_reference_fixture_with_bias(cp):
+    """The reference's testCollective fixture with its bias (mma.cuh:399-411): bias[0:2] = [1,2] ->
+    C[0:2,0:2] = [[6,9],[24,35]], and every other row shows ReLU(0 + bias) = [1,2] in its first two columns."""
+    torch = _torch()
+    M, K, N = 128, 64, 64
+    A = np.zeros((1, M, K), np.float32); A[0, :2, :2] = [[0, 1], [2, 3]]
+    B = np.zeros((1, N, K), np.float32); B[0, :2, :2] = [[4, 5], [6, 7]]
+    bias = np.zeros((1, N), np.float32); bias[0, :2] = [1, 2]
+    W2 = np.eye(N, dtype=np.float32)[None]
+    count = torch.tensor([M], dtype=torch.int32, device="cuda")
+    for dt in (torch.bfloat16, torch.float16, torch.float32):
+        y = cp.expert_ffn(to_dev(A, dt), count, to_dev(B, dt), None, to_dev(W2, dt), 0, b1=to_dev(bias, dt))
+        got = y.float().cpu().numpy()[0]
+        assert (got[:2, :2] == np.array([[6, 9], [24, 35]], np.float32)).all()
+        assert (got[2:, :2] == np.array([1, 2], np.float32)).all() and np.count_nonzero(got[:, 2:]) == 0
+
+
+@pytest.mark.parametrize("act,dtype", [(2, "bf16"), (1, "bf16"), (2, "f16"), (0, "f32"), (2, "f32")])
+def test_expert_ffn_bias_parity(cp, oracle, act, dtype):
+    """act(acc + bias) in both projections (and on the SwiGLU up branch) against the oracle."""
+    torch = _torch()
+    from helpers import round_f16
+    E, rows, H, I = 3, 200, 128, 384
+    bf16, f16 = dtype == "bf16", dtype == "f16"
+    x, _, w1, w3, w2 = make_inputs(E * rows, H, I, E, seed=31, swiglu=(act == 2), bf16=bf16, f16=f16, w_std=0.05)
+    rnd = oracle.round_bf16 if bf16 else (round_f16 if f16 else (lambda a: a))
+    rng = np.random.default_rng(7)
+    b1, b3, b2 = (rnd(rng.standard_normal(s).astype(np.float32) * 0.5) for s in ((E, I), (E, I), (E, H)))
+    if act != 2:
+        b3 = None
+    xg = x.reshape(E, rows, H)
+    count = np.array([200, 64, 129], np.int32)
+    dt = {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float32}[dtype]
+    y = cp.expert_ffn(to_dev(xg, dt), torch.from_numpy(count).cuda(), to_dev(w1, dt), to_dev(w3, dt), to_dev(w2, dt),
+                      act, b1=to_dev(b1, dt), b3=to_dev(b3, dt), b2=to_dev(b2, dt))
+    ref = oracle.expert_ffn(xg, count, w1, w3, w2, act, round_h=0 if dtype == "f32" else 1, b1=b1, b3=b3, b2=b2)
+    got = y.float().cpu().numpy()
+    for e in range(E):
+        mx, mean = rel_errors(got[e, :count[e]], ref[e, :count[e]])
+        if dtype == "f32":
+            assert mx < TOL_F32_MAX, (e, mx)
+        else:
+            assert mx < TOL_BF16_MAX and mean < TOL_BF16_MEAN, (e, mx, mean)
