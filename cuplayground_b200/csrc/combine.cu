@@ -66,7 +66,8 @@ extern "C" aristos_status_t aristos_combine(const void* y, const int32_t* slot_o
     if (S == 0) return ARISTOS_OK;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     switch (dtype) {
-        case ARISTOS_DTYPE_F32: return launch_combine<float>(y, slot_of, topk_w, S, k, H, out, st);
+        case ARISTOS_DTYPE_F32:
+        case ARISTOS_DTYPE_TF32: return launch_combine<float>(y, slot_of, topk_w, S, k, H, out, st);
         case ARISTOS_DTYPE_BF16: return launch_combine<__nv_bfloat16>(y, slot_of, topk_w, S, k, H, out, st);
         case ARISTOS_DTYPE_F16: return launch_combine<__half>(y, slot_of, topk_w, S, k, H, out, st);
         default:

@@ -1,6 +1,6 @@
 // Expert FFN on the 5th-generation tensor cores: a persistent, warp-specialised grouped GEMM.
 //
-// Replaces, for bf16 and fp16, the reference's fused expert tile fGET / deviceCollectiveMMA (mma.cuh:46-179, :198-369: one
+// Replaces, for bf16, fp16 and tf32 (fp32 storage), the reference's fused expert tile fGET / deviceCollectiveMMA (mma.cuh:46-179, :198-369: one
 // CTA per 128x64 tile, CUTLASS sm80 cp.async mainloop, mma.sync, accumulators transposed through shared memory,
 // epilogue act(acc + bias) from processor/tiling.cuh:29-57) and its software tile schedulers sK / wScheduler
 // (auditorium/scheduling.cuh:202-265, warpScheduler.cuh:267-344: doorbells and ready queues in global memory that
@@ -53,6 +53,8 @@ constexpr int SMEM_AUX_BYTES = 256 + (MAX_GROUPS + 1) * 4;
 constexpr int STAGING_BYTES = 128 * 128;   // 128 rows x 64 bf16 of epilogue output, 128-byte swizzled
 constexpr int SMEM_BYTES = 1024 /*alignment slack*/ + STAGES * STAGE_BYTES + STAGING_BYTES + SMEM_AUX_BYTES;
 
+enum { FMT_BF16 = 0, FMT_F16 = 1, FMT_TF32 = 2 };
+
 struct FfnGemmParams {
     const int32_t* count;   // valid rows per group
     int groups;
@@ -64,14 +66,14 @@ struct FfnGemmParams {
     int gated;              // 1: B half 1 comes from the second weight tensor at the same rows (SwiGLU)
     int act;                // ARISTOS_ACT_* for the non-gated epilogue
     void* out;              // (groups * rows_per_group, N), 16-bit elements
-    int is_f16;             // 0: bf16 operands and output, 1: f16
+    int fmt;                // FMT_BF16 / FMT_F16 (16-bit operands and output) or FMT_TF32 (fp32 storage, tf32 MMA)
     const void* bias0;      // (experts, N) added to the accumulator before the activation, or nullptr
     const void* bias1;      // SwiGLU: bias of the second (up) projection, or nullptr
     int32_t* dev_status;
 };
 
-__device__ __forceinline__ uint32_t pack_16bit(float a, float b, int is_f16) {
-    if (is_f16) {
+__device__ __forceinline__ uint32_t pack_16bit(float a, float b, int fmt) {
+    if (fmt == FMT_F16) {
         __half2 t = __floats2half2_rn(a, b);
         return *reinterpret_cast<uint32_t*>(&t);
     }
@@ -79,8 +81,20 @@ __device__ __forceinline__ uint32_t pack_16bit(float a, float b, int is_f16) {
     return *reinterpret_cast<uint32_t*>(&t);
 }
 
-// acc[0..31] += bias[0..31] (16-bit elements, the same 64 bytes for every thread of the CTA: a broadcast load).
-__device__ __forceinline__ void add_bias32(uint32_t (&acc)[32], const void* bias, size_t elem_offset, int is_f16) {
+// acc[0..31] += bias[0..31] (the same bytes for every thread of the CTA: a broadcast load).
+__device__ __forceinline__ void add_bias32(uint32_t (&acc)[32], const void* bias, size_t elem_offset, int fmt) {
+    if (fmt == FMT_TF32) {
+        const float4* b = reinterpret_cast<const float4*>(static_cast<const float*>(bias) + elem_offset);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            const float4 v = __ldg(b + q);
+            acc[4 * q] = __float_as_uint(__uint_as_float(acc[4 * q]) + v.x);
+            acc[4 * q + 1] = __float_as_uint(__uint_as_float(acc[4 * q + 1]) + v.y);
+            acc[4 * q + 2] = __float_as_uint(__uint_as_float(acc[4 * q + 2]) + v.z);
+            acc[4 * q + 3] = __float_as_uint(__uint_as_float(acc[4 * q + 3]) + v.w);
+        }
+        return;
+    }
     const uint4* b = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(bias) + elem_offset);
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
@@ -89,7 +103,7 @@ __device__ __forceinline__ void add_bias32(uint32_t (&acc)[32], const void* bias
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             float lo, hi;
-            if (is_f16) {
+            if (fmt == FMT_F16) {
                 const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
                 lo = f.x; hi = f.y;
             } else {
@@ -138,8 +152,8 @@ __device__ __forceinline__ void epilogue_tile(const FfnGemmParams& p, const CUte
             }
             if (n0 + col < p.N) {          // act(acc + bias), the reference's epilogue (processor/tiling.cuh:29-57)
                 const size_t boff = (size_t)(g % p.experts) * p.N + n0 + col;
-                if (p.bias0) add_bias32(a, p.bias0, boff, p.is_f16);
-                if (p.gated && p.bias1) add_bias32(b, p.bias1, boff, p.is_f16);
+                if (p.bias0) add_bias32(a, p.bias0, boff, p.fmt);
+                if (p.gated && p.bias1) add_bias32(b, p.bias1, boff, p.fmt);
             }
             uint32_t o[16];
 #pragma unroll
@@ -150,7 +164,7 @@ __device__ __forceinline__ void epilogue_tile(const FfnGemmParams& p, const CUte
                     v1 = act_silu(v1) * __uint_as_float(b[2 * i + 1]);
                 } else if (p.act == ARISTOS_ACT_RELU) { v0 = act_relu(v0); v1 = act_relu(v1); }
                 else if (p.act == ARISTOS_ACT_GELU) { v0 = act_gelu(v0); v1 = act_gelu(v1); }
-                o[i] = pack_16bit(v0, v1, p.is_f16);
+                o[i] = pack_16bit(v0, v1, p.fmt);
             }
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -162,6 +176,60 @@ __device__ __forceinline__ void epilogue_tile(const FfnGemmParams& p, const CUte
         ptx::named_barrier_sync(1, EPI_THREADS);
         if (epi_tid == 0 && tile_live && n0 + c * 64 < p.N) {
             ptx::tma_store_3d(tmOut, staging, n0 + c * 64, m0, g);
+            ptx::bulk_commit_group();
+        }
+    }
+}
+
+// The same for fp32 output (tf32 path): a 128-byte staging row holds 32 columns, so the tile leaves in 32-column
+// chunks.
+template <bool PAIR>
+__device__ __forceinline__ void epilogue_tile_f32(const FfnGemmParams& p, const CUtensorMap* tmOut, int g, int m0,
+                                                  int n0, int row_in_tile, uint32_t taddr, uint32_t tempty, int lane,
+                                                  int epi_tid, uint32_t staging) {
+    const int row_limit = min(p.count[g], p.row_end);
+    const bool tile_live = m0 < row_limit;
+    const int nchunk = p.gated ? 4 : 8;
+    const uint32_t my_row = staging + row_in_tile * 128;
+    const int sw = row_in_tile & 7;
+#pragma unroll 1
+    for (int c = 0; c < nchunk; ++c) {
+        if (epi_tid == 0) ptx::bulk_wait_group_read0();
+        ptx::named_barrier_sync(1, EPI_THREADS);
+        const int col = c * 32;
+        uint32_t a[32], b[32];
+        ptx::tmem_ld_32x32b_x32(taddr + col, a);
+        if (p.gated) ptx::tmem_ld_32x32b_x32(taddr + 128 + col, b);
+        ptx::tmem_ld_wait();
+        if (c == nchunk - 1) {
+            ptx::tcgen05_fence_before();
+            if (PAIR) {
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive_cluster(tempty);
+            } else {
+                ptx::mbar_arrive(tempty);
+            }
+        }
+        if (n0 + col < p.N) {
+            const size_t boff = (size_t)(g % p.experts) * p.N + n0 + col;
+            if (p.bias0) add_bias32(a, p.bias0, boff, p.fmt);
+            if (p.gated && p.bias1) add_bias32(b, p.bias1, boff, p.fmt);
+        }
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            float v = __uint_as_float(a[i]);
+            if (p.gated) v = act_silu(v) * __uint_as_float(b[i]);
+            else if (p.act == ARISTOS_ACT_RELU) v = act_relu(v);
+            else if (p.act == ARISTOS_ACT_GELU) v = act_gelu(v);
+            a[i] = __float_as_uint(v);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            ptx::st_shared_v4(my_row + ((j ^ sw) << 4), a[4 * j], a[4 * j + 1], a[4 * j + 2], a[4 * j + 3]);
+        ptx::fence_proxy_async_shared();
+        ptx::named_barrier_sync(1, EPI_THREADS);
+        if (epi_tid == 0 && tile_live && n0 + col < p.N) {
+            ptx::tma_store_3d(tmOut, staging, n0 + col, m0, g);
             ptx::bulk_commit_group();
         }
     }
@@ -231,7 +299,8 @@ ffn_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     ptx::tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const int total_tiles = prefix[p.groups];
-    const int kblocks = p.K / BK;
+    const int bke = p.fmt == FMT_TF32 ? BK / 2 : BK;   // elements of K per stage: 128 bytes
+    const int kblocks = p.K / bke;
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
@@ -257,9 +326,9 @@ ffn_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
                     const uint32_t full = bar_full + 8 * stage;
                     const uint32_t sa = smem_base + stage * STAGE_BYTES;
                     ptx::mbar_arrive_expect_tx(full, STAGE_BYTES);
-                    ptx::tma_load_3d(sa, &tmA, kb * BK, m0, g, full);
-                    ptx::tma_load_3d(sa + A_STAGE_BYTES, &tmB0, kb * BK, n0, e, full);
-                    ptx::tma_load_3d(sa + A_STAGE_BYTES + B_HALF_BYTES, &tmB1, kb * BK, n1, e, full);
+                    ptx::tma_load_3d(sa, &tmA, kb * bke, m0, g, full);
+                    ptx::tma_load_3d(sa + A_STAGE_BYTES, &tmB0, kb * bke, n0, e, full);
+                    ptx::tma_load_3d(sa + A_STAGE_BYTES + B_HALF_BYTES, &tmB1, kb * bke, n1, e, full);
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
             }
@@ -268,7 +337,7 @@ ffn_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            const uint32_t idesc = ptx::umma_idesc_16bit(BM, BN, p.is_f16 ? 0u : 1u);
+            const uint32_t idesc = ptx::umma_idesc_f32acc(BM, BN, p.fmt == FMT_BF16 ? 1u : (p.fmt == FMT_F16 ? 0u : 2u));
             int stage = 0;
             uint32_t phase = 0;
             int it = 0;
@@ -290,7 +359,8 @@ ffn_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k) {
                         // advance 32 bytes (16 bf16) along K inside the swizzled row: +2 in 16-byte units
-                        ptx::umma_f16(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                        if (p.fmt == FMT_TF32) ptx::umma_tf32(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                        else ptx::umma_f16(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
                     }
                     ptx::umma_commit(bar_empty + 8 * stage);
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -320,9 +390,11 @@ ffn_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
             ok = !ptx::named_barrier_or(2, EPI_THREADS, !ok);
             if (!ok) break;
             ptx::tcgen05_fence_after();
-            epilogue_tile<false>(p, &tmOut, g, m0, n0, row_in_tile,
-                                 tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN,
-                                 bar_tempty + 8 * buf, lane, epi_tid, staging);
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
+            if (p.fmt == FMT_TF32)
+                epilogue_tile_f32<false>(p, &tmOut, g, m0, n0, row_in_tile, taddr, bar_tempty + 8 * buf, lane, epi_tid, staging);
+            else
+                epilogue_tile<false>(p, &tmOut, g, m0, n0, row_in_tile, taddr, bar_tempty + 8 * buf, lane, epi_tid, staging);
         }
         if (epi_tid == 0) ptx::bulk_wait_group0();
     }
@@ -412,7 +484,8 @@ ffn_grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gr
     ptx::tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const int total_tiles = prefix[p.groups];
-    const int kblocks = p.K / BK;
+    const int bke = p.fmt == FMT_TF32 ? BK / 2 : BK;   // elements of K per stage: 128 bytes
+    const int kblocks = p.K / bke;
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer (both CTAs)
@@ -439,8 +512,8 @@ ffn_grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gr
                     if (!ok) break;
                     const uint32_t sa = smem_base + stage * P_STAGE_BYTES;
                     if (cta == 0) ptx::mbar_arrive_expect_tx(bar_full + 8 * stage, 2 * P_STAGE_BYTES);
-                    ptx::tma_load_3d_pair(sa, &tmA, kb * BK, m0, g, full0 + 8 * stage);
-                    ptx::tma_load_3d_pair(sa + A_STAGE_BYTES, tmB, kb * BK, nb, e, full0 + 8 * stage);
+                    ptx::tma_load_3d_pair(sa, &tmA, kb * bke, m0, g, full0 + 8 * stage);
+                    ptx::tma_load_3d_pair(sa + A_STAGE_BYTES, tmB, kb * bke, nb, e, full0 + 8 * stage);
                     if (++stage == P_STAGES) { stage = 0; phase ^= 1u; }
                 }
             }
@@ -449,7 +522,7 @@ ffn_grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gr
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer (CTA 0 only)
         if (lane == 0 && cta == 0) {
-            const uint32_t idesc = ptx::umma_idesc_16bit(PBM, BN, p.is_f16 ? 0u : 1u);
+            const uint32_t idesc = ptx::umma_idesc_f32acc(PBM, BN, p.fmt == FMT_BF16 ? 1u : (p.fmt == FMT_F16 ? 0u : 2u));
             const uint32_t empty_peer = ptx::mapa_shared(bar_empty, 1);
             const uint32_t tfull_peer = ptx::mapa_shared(bar_tfull, 1);
             int stage = 0;
@@ -472,7 +545,8 @@ ffn_grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gr
                     const uint64_t db = ptx::umma_desc_k_sw128(sa + A_STAGE_BYTES);
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k)
-                        ptx::umma_f16_pair(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                        if (p.fmt == FMT_TF32) ptx::umma_tf32_pair(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                        else ptx::umma_f16_pair(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
                     // release the stage in both CTAs
                     ptx::umma_commit_pair(bar_empty + 8 * stage);
                     ptx::umma_commit_pair(empty_peer + 8 * stage);
@@ -506,9 +580,11 @@ ffn_grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gr
             ok = !ptx::named_barrier_or(2, EPI_THREADS, !ok);
             if (!ok) break;
             ptx::tcgen05_fence_after();
-            epilogue_tile<true>(p, &tmOut, g, m0, n0, row_in_tile,
-                                tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN, tempty0 + 8 * buf,
-                                lane, epi_tid, staging);
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
+            if (p.fmt == FMT_TF32)
+                epilogue_tile_f32<true>(p, &tmOut, g, m0, n0, row_in_tile, taddr, tempty0 + 8 * buf, lane, epi_tid, staging);
+            else
+                epilogue_tile<true>(p, &tmOut, g, m0, n0, row_in_tile, taddr, tempty0 + 8 * buf, lane, epi_tid, staging);
         }
         if (epi_tid == 0) ptx::bulk_wait_group0();
     }
@@ -540,15 +616,18 @@ EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-// (outer, rows, K) bf16 tensor, K contiguous; box = 64 x 128 x 1 with the 128-byte swizzle.
-aristos_status_t make_map_3d(CUtensorMap* tm, const void* base, int K, int rows, int outer, int is_f16) {
+// (outer, rows, K) tensor, K contiguous; box = 128 bytes x 128 rows x 1 with the 128-byte swizzle.
+aristos_status_t make_map_3d(CUtensorMap* tm, const void* base, int K, int rows, int outer, int fmt) {
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) { set_last_error("cuTensorMapEncodeTiled is not available from the driver"); return ARISTOS_ERR_CUDA; }
     const cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)rows, (cuuint64_t)outer};
-    const cuuint64_t strides[2] = {(cuuint64_t)K * 2, (cuuint64_t)K * 2 * (cuuint64_t)rows};
-    const cuuint32_t box[3] = {BK, 128, 1};
+    const cuuint64_t elt = fmt == FMT_TF32 ? 4 : 2;
+    const cuuint64_t strides[2] = {(cuuint64_t)K * elt, (cuuint64_t)K * elt * (cuuint64_t)rows};
+    const cuuint32_t box[3] = {(cuuint32_t)(128 / elt), 128, 1};    // 128 bytes along K
     const cuuint32_t estr[3] = {1, 1, 1};
-    const CUresult r = enc(tm, is_f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+    const CUtensorMapDataType dt = fmt == FMT_TF32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                   : (fmt == FMT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16);
+    const CUresult r = enc(tm, dt, 3, const_cast<void*>(base), dims, strides, box, estr,
                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
@@ -574,10 +653,10 @@ bool use_pair_tiles(int window_rows) {
 aristos_status_t launch_gemm(const void* A, const void* B0, const void* B1, const FfnGemmParams& p, int grid_limit,
                              cudaStream_t st) {
     CUtensorMap tmA, tmB0, tmB1, tmOut;
-    ARISTOS_TRY(make_map_3d(&tmA, A, p.K, p.rows_per_group, p.groups, p.is_f16));
-    ARISTOS_TRY(make_map_3d(&tmB0, B0, p.K, p.N, p.experts, p.is_f16));
-    ARISTOS_TRY(make_map_3d(&tmB1, B1, p.K, p.N, p.experts, p.is_f16));
-    ARISTOS_TRY(make_map_3d(&tmOut, p.out, p.N, p.rows_per_group, p.groups, p.is_f16));
+    ARISTOS_TRY(make_map_3d(&tmA, A, p.K, p.rows_per_group, p.groups, p.fmt));
+    ARISTOS_TRY(make_map_3d(&tmB0, B0, p.K, p.N, p.experts, p.fmt));
+    ARISTOS_TRY(make_map_3d(&tmB1, B1, p.K, p.N, p.experts, p.fmt));
+    ARISTOS_TRY(make_map_3d(&tmOut, p.out, p.N, p.rows_per_group, p.groups, p.fmt));
     const int out_w = p.gated ? 128 : 256;
     int sms = device_sm_count();
     if (sms <= 0) { set_last_error("no CUDA device"); return ARISTOS_ERR_CUDA; }
@@ -623,10 +702,10 @@ aristos_status_t launch_gemm(const void* A, const void* B0, const void* B1, cons
 
 }  // namespace
 
-aristos_status_t expert_ffn_16bit_sm100(const void* xg, const int32_t* count, int groups, int rows_per_group,
+aristos_status_t expert_ffn_tc_sm100(const void* xg, const int32_t* count, int groups, int rows_per_group,
                                         int experts, const void* w1, const void* w3, const void* w2, const void* b1,
                                         const void* b3, const void* b2, void* h_scratch, void* y, int H, int I,
-                                        int hidden_act, int is_f16, int row_begin, int row_end, int sm_limit,
+                                        int hidden_act, int fmt, int row_begin, int row_end, int sm_limit,
                                         int32_t* dev_status, cudaStream_t st) {
     if (groups > MAX_GROUPS) { set_last_error("expert_ffn: more than %d row groups", MAX_GROUPS); return ARISTOS_ERR_CONFIG; }
     if (H % BK != 0 || I % BK != 0) { set_last_error("expert_ffn: H and I must be multiples of 64"); return ARISTOS_ERR_CONFIG; }
@@ -640,7 +719,7 @@ aristos_status_t expert_ffn_16bit_sm100(const void* xg, const int32_t* count, in
     p.row_begin = row_begin;
     p.row_end = row_end;
     p.dev_status = dev_status;
-    p.is_f16 = is_f16;
+    p.fmt = fmt;
     // up-projection: h = epi(xg * W1^T [, xg * W3^T])
     p.N = I;
     p.K = H;

@@ -57,7 +57,7 @@ extern "C" aristos_status_t aristos_fill_normal(void* dst, int64_t n, float mean
     const int grid = (int)((nblk + 255) / 256 < 148 * 16 ? (nblk + 255) / 256 : 148 * 16);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const uint32_t k0 = (uint32_t)seed, k1 = (uint32_t)(seed >> 32);
-    if (dtype == ARISTOS_DTYPE_F32) fill_normal_kernel<float><<<grid, 256, 0, st>>>((float*)dst, n, mean, std, k0, k1, stream_id);
+    if (dtype == ARISTOS_DTYPE_F32 || dtype == ARISTOS_DTYPE_TF32) fill_normal_kernel<float><<<grid, 256, 0, st>>>((float*)dst, n, mean, std, k0, k1, stream_id);
     else if (dtype == ARISTOS_DTYPE_BF16) fill_normal_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((__nv_bfloat16*)dst, n, mean, std, k0, k1, stream_id);
     else if (dtype == ARISTOS_DTYPE_F16) fill_normal_kernel<__half><<<grid, 256, 0, st>>>((__half*)dst, n, mean, std, k0, k1, stream_id);
     else { set_last_error("fill_normal: dtype %d not implemented", dtype); return ARISTOS_ERR_UNSUPPORTED; }

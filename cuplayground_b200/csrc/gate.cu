@@ -340,6 +340,7 @@ extern "C" aristos_status_t aristos_gate_topk(const void* x, const void* w_gate,
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     switch (dtype) {
         case ARISTOS_DTYPE_F32:
+        case ARISTOS_DTYPE_TF32:
             return launch_gate<float>(x, w_gate, gate_bias, S, H, E, k, gate_fn, renorm, topk_idx, topk_w, logits_out, st);
         case ARISTOS_DTYPE_BF16:
             return launch_gate<__nv_bfloat16>(x, w_gate, gate_bias, S, H, E, k, gate_fn, renorm, topk_idx, topk_w, logits_out, st);

@@ -144,9 +144,8 @@ aristos_status_t aristos_moe_create(const aristos_config_t* cfg, int rank, int w
     if (world < 1 || rank < 0 || rank >= world) { set_last_error("create: bad rank/world"); return ARISTOS_ERR_INVALID_ARG; }
     if (cfg->ep_world != world) { set_last_error("create: config ep_world (%d) != world (%d)", cfg->ep_world, world); return ARISTOS_ERR_CONFIG; }
     if (world > 1 && !nccl_unique_id) { set_last_error("create: world > 1 needs a NCCL unique id"); return ARISTOS_ERR_INVALID_ARG; }
-    if (cfg->torch_dtype != ARISTOS_DTYPE_F32 && cfg->torch_dtype != ARISTOS_DTYPE_BF16 &&
-        cfg->torch_dtype != ARISTOS_DTYPE_F16) {
-        set_last_error("create: torch_dtype %d not implemented (0 = fp32, 2 = bf16 and 3 = fp16 are)", cfg->torch_dtype);
+    if (cfg->torch_dtype == ARISTOS_DTYPE_FP8_E4M3) {
+        set_last_error("create: torch_dtype 4 (fp8 e4m3, block-scaled) is not implemented; 0 fp32, 1 tf32, 2 bf16, 3 fp16 are");
         return ARISTOS_ERR_UNSUPPORTED;
     }
     int dev = 0;

@@ -12,8 +12,10 @@ import torch
 from . import _lib
 from .config import AristosConfig
 
-_TORCH_DTYPE = {_lib.DTYPE_F32: torch.float32, _lib.DTYPE_BF16: torch.bfloat16, _lib.DTYPE_F16: torch.float16}
-_ARISTOS_DTYPE = {v: k for k, v in _TORCH_DTYPE.items()}
+_TORCH_DTYPE = {_lib.DTYPE_F32: torch.float32, _lib.DTYPE_TF32: torch.float32, _lib.DTYPE_BF16: torch.bfloat16,
+                _lib.DTYPE_F16: torch.float16}
+# storage type -> dtype code; fp32 tensors mean exact fp32 math unless a call asks for tf32 explicitly
+_ARISTOS_DTYPE = {torch.float32: _lib.DTYPE_F32, torch.bfloat16: _lib.DTYPE_BF16, torch.float16: _lib.DTYPE_F16}
 
 
 def _ptr(t: Optional[torch.Tensor]):
@@ -117,7 +119,7 @@ def permute(x, slot_of, nslots: int, zero: bool = False):
 
 def expert_ffn(xg, count, w1, w3, w2, hidden_act: int, *, experts: Optional[int] = None, row_begin: int = 0,
                row_end: Optional[int] = None, sm_limit: int = 0, dev_status=None, y=None, h=None, b1=None, b3=None,
-               b2=None):
+               b2=None, dtype: Optional[int] = None):
     """xg (groups, rows, H); w1/w3 (experts, I, H); w2 (experts, H, I); optional biases b1/b3 (experts, I),
     b2 (experts, H) -> y (groups, rows, H)."""
     groups, rows, H = xg.shape
@@ -130,7 +132,8 @@ def expert_ffn(xg, count, w1, w3, w2, hidden_act: int, *, experts: Optional[int]
         y = torch.zeros((groups, rows, H), dtype=xg.dtype, device=xg.device)
     _lib.check(_lib.load().aristos_expert_ffn_bias(_ptr(xg), _ptr(count), groups, rows, experts, _ptr(w1), _ptr(w3),
                                                    _ptr(w2), _ptr(b1), _ptr(b3), _ptr(b2), _ptr(h), _ptr(y), H, I,
-                                                   hidden_act, _dt(xg), row_begin, row_end, sm_limit,
+                                                   hidden_act, _dt(xg) if dtype is None else dtype, row_begin, row_end,
+                                                   sm_limit,
                                                    _ptr(dev_status), _stream_ptr()))
     return y
 

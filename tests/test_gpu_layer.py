@@ -168,9 +168,23 @@ def test_layer_fp16(oracle, act, k):
     assert mx < TOL_BF16_MAX / 4 and mean < TOL_BF16_MEAN / 4, (mx, mean)
 
 
+@pytest.mark.parametrize("act", [1, 2])
+def test_layer_tf32(oracle, act):
+    """torch_dtype 1 (tf32, aristos_config.schema.json:54-58): fp32 storage, exact fp32 gate, tf32 tensor-core expert
+    GEMMs (10-bit mantissa inputs): routing stays bit-exact, outputs within 5e-3 of the fp32 oracle."""
+    torch, cp, layer = _mods()
+    cfg = cp.AristosConfig(capacity_factor=1.25, drop_tokens=1, expert_top_k=2, hidden_act=act, hidden_size=256,
+                           intermediate_size=512, num_experts=8, torch_dtype=1, tokens=512)
+    got, r, ref = _run_layer(cfg, 23, oracle, w_std=0.05)
+    _check_routing(r, ref)
+    mx, mean = rel_errors(got, ref["out"])
+    assert mx < 5e-3 and mean < 5e-3, (mx, mean)
+    assert mx > 1e-6, "suspiciously exact: the tf32 path did not run"
+
+
 def test_unsupported_dtype_fails_loudly():
     torch, cp, layer = _mods()
-    cfg = cp.AristosConfig(hidden_size=128, intermediate_size=128, num_experts=4, torch_dtype=1, tokens=128)
+    cfg = cp.AristosConfig(hidden_size=128, intermediate_size=128, num_experts=4, torch_dtype=4, tokens=128)
     with pytest.raises(cp.AristosError) as e:
         layer.MoELayer(cfg)
     assert e.value.status == 6

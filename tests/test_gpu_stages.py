@@ -272,3 +272,25 @@ def test_expert_ffn_bias_parity(cp, oracle, act, dtype):
             assert mx < TOL_F32_MAX, (e, mx)
         else:
             assert mx < TOL_BF16_MAX and mean < TOL_BF16_MEAN, (e, mx, mean)
+
+
+@pytest.mark.parametrize("act,E,rows,H,I,counts", [(2, 2, 300, 128, 384, [300, 130]), (1, 3, 128, 256, 256, [128, 0, 7])])
+def test_expert_ffn_tf32_parity(cp, oracle, act, E, rows, H, I, counts):
+    """fp32 tensors through the tf32 tensor-core path (dtype code 1) against the fp32 oracle."""
+    torch = _torch()
+    x, _, w1, w3, w2 = make_inputs(E * rows, H, I, E, seed=41, swiglu=(act == 2), bf16=False, w_std=0.05)
+    xg = x.reshape(E, rows, H)
+    count = np.array(counts, np.int32)
+    dt = torch.float32
+    rng = np.random.default_rng(1)
+    b1, b2 = rng.standard_normal((E, I)).astype(np.float32) * 0.2, rng.standard_normal((E, H)).astype(np.float32) * 0.2
+    y = cp.expert_ffn(to_dev(xg, dt), torch.from_numpy(count).cuda(), to_dev(w1, dt), to_dev(w3, dt), to_dev(w2, dt),
+                      act, b1=to_dev(b1, dt), b2=to_dev(b2, dt), dtype=1)
+    ref = oracle.expert_ffn(xg, count, w1, w3, w2, act, b1=b1, b2=b2)
+    got = y.cpu().numpy()
+    for e in range(E):
+        n = counts[e]
+        assert (got[e, -(-n // 128) * 128:] == 0).all()
+        if n:
+            mx, mean = rel_errors(got[e, :n], ref[e, :n])
+            assert mx < 5e-3 and mean < 5e-3, (e, mx, mean)
