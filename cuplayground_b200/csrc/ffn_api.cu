@@ -12,9 +12,42 @@ aristos_status_t expert_ffn_f32_simt(const void* xg, const int32_t* count, int g
                                      const void* w1, const void* w3, const void* w2, const void* b1, const void* b3,
                                      const void* b2, void* h_scratch, void* y, int H, int I, int hidden_act,
                                      int row_begin, int row_end, cudaStream_t st);
+aristos_status_t expert_ffn_fp8_sm100(const void* xq, const float* sx, const int32_t* count, int groups,
+                                      int rows_per_group, int experts, const void* w1q, const float* s1,
+                                      const void* w3q, const float* s3, const void* w2q, const float* s2, void* h,
+                                      void* hq, float* sh, void* y, int H, int I, int hidden_act, int row_begin,
+                                      int row_end, int sm_limit, int32_t* dev_status, cudaStream_t st);
 }  // namespace aristos
 
 using namespace aristos;
+
+extern "C" aristos_status_t aristos_expert_ffn_fp8(const void* xq, const float* sx, const int32_t* count, int groups,
+                                                   int rows_per_group, int experts, const void* w1q, const float* s1,
+                                                   const void* w3q, const float* s3, const void* w2q, const float* s2,
+                                                   void* h_scratch, void* hq_scratch, float* sh_scratch, void* y,
+                                                   int H, int I, int hidden_act, int row_begin, int row_end,
+                                                   int sm_limit, int32_t* dev_status, void* stream) {
+    if (!xq || !sx || !count || !w1q || !s1 || !w2q || !s2 || !h_scratch || !hq_scratch || !sh_scratch || !y) {
+        set_last_error("expert_ffn_fp8: NULL pointer");
+        return ARISTOS_ERR_INVALID_ARG;
+    }
+    if (hidden_act == ARISTOS_ACT_SWIGLU && (!w3q || !s3)) { set_last_error("expert_ffn_fp8: SwiGLU needs w3 and its scales"); return ARISTOS_ERR_INVALID_ARG; }
+    if (hidden_act < 0 || hidden_act > 2) { set_last_error("expert_ffn_fp8: hidden_act must be 0, 1 or 2"); return ARISTOS_ERR_INVALID_ARG; }
+    if (groups < 0 || rows_per_group <= 0 || experts <= 0 || H <= 0 || I <= 0 || row_begin < 0 || row_end < row_begin ||
+        row_end > rows_per_group) {
+        set_last_error("expert_ffn_fp8: bad size");
+        return ARISTOS_ERR_INVALID_ARG;
+    }
+    if (!aligned16(xq) || !aligned16(w1q) || !aligned16(w2q) || !aligned16(h_scratch) || !aligned16(hq_scratch) ||
+        !aligned16(y) || (w3q && !aligned16(w3q))) {
+        set_last_error("expert_ffn_fp8: pointers must be 16-byte aligned");
+        return ARISTOS_ERR_INVALID_ARG;
+    }
+    if (groups == 0 || row_end == row_begin) return ARISTOS_OK;
+    return expert_ffn_fp8_sm100(xq, sx, count, groups, rows_per_group, experts, w1q, s1, w3q, s3, w2q, s2, h_scratch,
+                                hq_scratch, sh_scratch, y, H, I, hidden_act, row_begin, row_end, sm_limit, dev_status,
+                                static_cast<cudaStream_t>(stream));
+}
 
 extern "C" aristos_status_t aristos_expert_ffn(const void* xg, const int32_t* count, int groups, int rows_per_group,
                                                int experts, const void* w1, const void* w3, const void* w2,

@@ -1,0 +1,540 @@
+// Expert FFN with FP8 (e4m3) operands and fp32 block scales on the 5th-generation tensor cores.
+//
+// Operands: activations quantised per row and per 128 elements of K (scale sa[row][K/128]), weights quantised per
+// 128 x 128 block (scale sb[expert][N/128][K/128]); out = sum over K blocks kb of sa[row,kb] * sb[n/128,kb] *
+// (Aq[row, kb] . Bq[n, kb]). The hardware's own block scaling (power-of-two scales per 32 elements) cannot express
+// fp32 scales per 128, so the accumulation has two levels: one 128-wide K block is accumulated by four
+// tcgen05.mma kind::f8f6f4 (K = 32 each) into a fresh 128-column TMEM accumulator, the four epilogue warps drain it
+// (tcgen05.ld), multiply by the block's scale and add it to fp32 register accumulators (one row and 128 columns per
+// thread) while the tensor core works on the next block in the next of four TMEM buffers.
+//
+// Same tile contract as the 16-bit kernel (ffn_sm100.cu; reference: fGET, mma.cuh:46-179, A (M,K) and B (N,K)
+// row-major, epilogue act(acc)): persistent CTAs, warp 0 = TMA producer (a 128-byte K block is exactly one swizzled
+// row), warp 1 = MMA issuer, warps 2-5 = promotion + epilogue. SwiGLU tiles hold 64 gate and 64 up columns in one
+// N = 128 instruction. Output is bf16, written with 16-byte stores masked by the group's row count.
+#include <cuda.h>
+#include <cuda_fp8.h>
+
+#include "common.cuh"
+#include "ptx_sm100.cuh"
+
+namespace aristos {
+
+namespace {
+
+constexpr int F8_BM = 128;
+constexpr int F8_BN = 128;                       // MMA N = TMEM columns per accumulator buffer
+constexpr int F8_KB = 128;                       // elements (= bytes) of K per stage and per scale block
+constexpr int F8_STAGES = 6;
+constexpr int F8_A_BYTES = F8_BM * F8_KB;        // 16 KB
+constexpr int F8_B_BYTES = F8_BN * F8_KB;        // 16 KB
+constexpr int F8_STAGE_BYTES = F8_A_BYTES + F8_B_BYTES;
+constexpr int F8_TBUFS = 4;                      // TMEM accumulator buffers (4 x 128 columns)
+constexpr int F8_THREADS = 192;
+constexpr int F8_EPI_THREADS = 128;
+constexpr int F8_MAX_GROUPS = 1024;
+constexpr int F8_AUX_BYTES = 256 + (F8_MAX_GROUPS + 1) * 4;
+constexpr int F8_SMEM_BYTES = 1024 + F8_STAGES * F8_STAGE_BYTES + F8_AUX_BYTES;
+
+struct Fp8GemmParams {
+    const int32_t* count;
+    int groups, experts, rows_per_group, row_begin, row_end;
+    int N, K;
+    int gated, act;
+    const float* sa;      // [groups * rows_per_group][K / 128]
+    const float* sb0;     // [experts][ceil(N / 128)][K / 128]
+    const float* sb1;     // SwiGLU: scales of the up projection's weights
+    __nv_bfloat16* out;   // [groups * rows_per_group][N]
+    int32_t* dev_status;
+};
+
+__device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                        uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t"
+        "}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// e4m3 x e4m3 -> fp32, both operands K-major, tile M x N (formats 0 = e4m3 in bits 7-9 and 10-12).
+__host__ __device__ constexpr uint32_t umma_idesc_e4m3(int M, int N) {
+    return (1u << 4) | (static_cast<uint32_t>(N >> 3) << 17) | (static_cast<uint32_t>(M >> 4) << 24);
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
+    __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&t);
+}
+
+__global__ void __launch_bounds__(F8_THREADS, 1)
+ffn_fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB0,
+                            const __grid_constant__ CUtensorMap tmB1, const Fp8GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* aux = smem + F8_STAGES * F8_STAGE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(aux);     // full[S], empty[S], tfull[4], tempty[4]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aux + 192);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(aux + 196);
+    int* prefix = reinterpret_cast<int*>(aux + 256);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t bar_full = ptx::smem_u32(bars);
+    const uint32_t bar_empty = bar_full + 8 * F8_STAGES;
+    const uint32_t bar_tfull = bar_empty + 8 * F8_STAGES;
+    const uint32_t bar_tempty = bar_tfull + 8 * F8_TBUFS;
+    const uint32_t smem_base = ptx::smem_u32(smem);
+
+    const int out_w = p.gated ? 64 : 128;
+    const int n_tiles = (p.N + out_w - 1) / out_w;
+    const int window = p.row_end - p.row_begin;
+    const int kblocks = p.K / F8_KB;
+    const int nblk = (p.N + 127) / 128;                    // weight-scale blocks along N
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < F8_STAGES; ++s) {
+            ptx::mbar_init(bar_full + 8 * s, 1);
+            ptx::mbar_init(bar_empty + 8 * s, 1);
+        }
+        for (int b = 0; b < F8_TBUFS; ++b) {
+            ptx::mbar_init(bar_tfull + 8 * b, 1);
+            ptx::mbar_init(bar_tempty + 8 * b, F8_EPI_THREADS);
+        }
+        *abort_flag = 0;
+        ptx::fence_mbar_init();
+    }
+    if (warp == 0) {
+        int running = 0;
+        if (lane == 0) prefix[0] = 0;
+        for (int g0 = 0; g0 < p.groups; g0 += 32) {
+            const int g = g0 + lane;
+            int v = 0;
+            if (g < p.groups) {
+                int rows = p.count[g] - p.row_begin;
+                rows = max(0, min(rows, window));
+                v = ((rows + F8_BM - 1) / F8_BM) * n_tiles;
+            }
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const int o = __shfl_up_sync(0xffffffffu, v, d);
+                if (lane >= d) v += o;
+            }
+            if (g < p.groups) prefix[g + 1] = running + v;
+            running += __shfl_sync(0xffffffffu, v, 31);
+        }
+    } else if (warp == 1) {
+        ptx::tmem_alloc(ptx::smem_u32(tmem_slot), F8_TBUFS * F8_BN);
+    }
+    ptx::tcgen05_fence_before();
+    __syncthreads();
+    ptx::tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const int total_tiles = prefix[p.groups];
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            ptx::prefetch_tensormap(&tmA);
+            ptx::prefetch_tensormap(&tmB0);
+            ptx::prefetch_tensormap(&tmB1);
+            int stage = 0;
+            uint32_t phase = 0;
+            int g = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+                while (tile >= prefix[g + 1]) ++g;
+                const int local = tile - prefix[g];
+                const int mt = (prefix[g + 1] - prefix[g]) / n_tiles;
+                const int m0 = p.row_begin + (local % mt) * F8_BM;
+                const int n0 = (local / mt) * out_w;
+                const int e = g % p.experts;
+                const int n1 = p.gated ? n0 : n0 + 64;      // second 64-row box of B
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    ok = ptx::mbar_wait_bounded(bar_empty + 8 * stage, phase ^ 1u, abort_flag, p.dev_status);
+                    if (!ok) break;
+                    const uint32_t full = bar_full + 8 * stage;
+                    const uint32_t sa = smem_base + stage * F8_STAGE_BYTES;
+                    ptx::mbar_arrive_expect_tx(full, F8_STAGE_BYTES);
+                    ptx::tma_load_3d(sa, &tmA, kb * F8_KB, m0, g, full);
+                    ptx::tma_load_3d(sa + F8_A_BYTES, &tmB0, kb * F8_KB, n0, e, full);
+                    ptx::tma_load_3d(sa + F8_A_BYTES + F8_B_BYTES / 2, &tmB1, kb * F8_KB, n1, e, full);
+                    if (++stage == F8_STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer: one TMEM buffer per K block
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc_e4m3(F8_BM, F8_BN);
+            int stage = 0, tbuf = 0;
+            uint32_t phase = 0, tphase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    ok = ptx::mbar_wait_bounded(bar_tempty + 8 * tbuf, tphase ^ 1u, abort_flag, p.dev_status);
+                    if (!ok) break;
+                    ok = ptx::mbar_wait_bounded(bar_full + 8 * stage, phase, abort_flag, p.dev_status);
+                    if (!ok) break;
+                    ptx::tcgen05_fence_after();
+                    const uint32_t sa = smem_base + stage * F8_STAGE_BYTES;
+                    const uint64_t da = ptx::umma_desc_k_sw128(sa);
+                    const uint64_t db = ptx::umma_desc_k_sw128(sa + F8_A_BYTES);
+                    const uint32_t tmem_d = tmem_base + tbuf * F8_BN;
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)            // K = 32 elements = 32 bytes per instruction
+                        umma_f8(tmem_d, da + 2 * k, db + 2 * k, idesc, k != 0 ? 1u : 0u);
+                    ptx::umma_commit(bar_empty + 8 * stage);
+                    ptx::umma_commit(bar_tfull + 8 * tbuf);
+                    if (++stage == F8_STAGES) { stage = 0; phase ^= 1u; }
+                    if (++tbuf == F8_TBUFS) { tbuf = 0; tphase ^= 1u; }
+                }
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------------ promotion + epilogue (warps 2..5)
+        const int quarter = warp & 3;
+        const int row_in_tile = quarter * 32 + lane;
+        int g = 0, tbuf = 0;
+        uint32_t tphase = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+            while (tile >= prefix[g + 1]) ++g;
+            const int local = tile - prefix[g];
+            const int mt = (prefix[g + 1] - prefix[g]) / n_tiles;
+            const int m0 = p.row_begin + (local % mt) * F8_BM;
+            const int n0 = (local / mt) * out_w;
+            const int e = g % p.experts;
+            const int row = m0 + row_in_tile;
+            const int row_limit = min(p.count[g], p.row_end);
+            const bool row_ok = row < row_limit;
+            const float* sa_row = p.sa + ((size_t)g * p.rows_per_group + min(row, p.rows_per_group - 1)) * kblocks;
+            const float* sb0_row = p.sb0 + ((size_t)e * nblk + n0 / 128) * kblocks;
+            const float* sb1_row = p.gated ? p.sb1 + ((size_t)e * nblk + n0 / 128) * kblocks : sb0_row;
+            float acc[F8_BN];
+#pragma unroll
+            for (int i = 0; i < F8_BN; ++i) acc[i] = 0.0f;
+            for (int kb = 0; kb < kblocks; ++kb) {
+                ok = ptx::mbar_wait_bounded(bar_tfull + 8 * tbuf, tphase, abort_flag, p.dev_status);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                ptx::tcgen05_fence_after();
+                const float sa = __ldg(sa_row + kb);
+                const float w_lo = sa * __ldg(sb0_row + kb);       // columns 0..63 (gate, or the tile's first half)
+                const float w_hi = sa * __ldg(sb1_row + kb);       // columns 64..127 (up, or the second half)
+                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + tbuf * F8_BN;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t v[32];
+                    ptx::tmem_ld_32x32b_x32(taddr + c * 32, v);
+                    ptx::tmem_ld_wait();
+                    if (c == 3) {                                   // buffer drained: the tensor core may refill it
+                        ptx::tcgen05_fence_before();
+                        ptx::mbar_arrive(bar_tempty + 8 * tbuf);
+                    }
+                    const float w = c < 2 ? w_lo : w_hi;
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(w, __uint_as_float(v[i]), acc[c * 32 + i]);
+                }
+                if (++tbuf == F8_TBUFS) { tbuf = 0; tphase ^= 1u; }
+            }
+            if (!ok) break;
+            if (row_ok) {
+                __nv_bfloat16* orow = p.out + ((size_t)g * p.rows_per_group + row) * p.N + n0;
+                if (p.gated) {
+                    uint32_t o[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        o[i] = pack_bf16x2(act_silu(acc[2 * i]) * acc[64 + 2 * i],
+                                           act_silu(acc[2 * i + 1]) * acc[64 + 2 * i + 1]);
+                    if (n0 < p.N) {
+                        uint4* dst = reinterpret_cast<uint4*>(orow);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) dst[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+                    }
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        if (n0 + c * 32 >= p.N) break;
+                        uint32_t o[16];
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            float v0 = acc[c * 32 + 2 * i], v1 = acc[c * 32 + 2 * i + 1];
+                            if (p.act == ARISTOS_ACT_RELU) { v0 = act_relu(v0); v1 = act_relu(v1); }
+                            else if (p.act == ARISTOS_ACT_GELU) { v0 = act_gelu(v0); v1 = act_gelu(v1); }
+                            o[i] = pack_bf16x2(v0, v1);
+                        }
+                        uint4* dst = reinterpret_cast<uint4*>(orow + c * 32);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) dst[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+                    }
+                }
+            }
+        }
+    }
+
+    ptx::tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tcgen05_fence_after();
+        ptx::tmem_dealloc(tmem_base, F8_TBUFS * F8_BN);
+    }
+}
+
+// ---- quantisation ------------------------------------------------------------------------------------------------
+// Quantise 128 consecutive elements held 4 per lane by one warp: scale = amax / 448 (1 when all zero).
+template <typename T>
+__device__ __forceinline__ void quantize_group128(const T* __restrict__ s, uint8_t* __restrict__ d,
+                                                  float* __restrict__ scale_out, int lane) {
+    float v[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = static_cast<float>(s[lane * 4 + i]);
+    float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+#pragma unroll
+    for (int m = 16; m >= 1; m >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
+    const float scale = amax > 0.0f ? amax / 448.0f : 1.0f;
+    const float inv = 1.0f / scale;
+    uint32_t packed = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+        packed |= (uint32_t)__nv_cvt_float_to_fp8(v[i] * inv, __NV_SATFINITE, __NV_E4M3) << (8 * i);
+    *reinterpret_cast<uint32_t*>(d + lane * 4) = packed;
+    if (lane == 0) *scale_out = scale;
+}
+
+// Every row of a (rows, cols) tensor: one warp per (row, 128-column group).
+template <typename T>
+__global__ void __launch_bounds__(256)
+quantize_rows_fp8_kernel(const T* __restrict__ src, int64_t rows, int cols, uint8_t* __restrict__ dst,
+                         float* __restrict__ scales) {
+    const int ngroup = cols / 128;
+    const int lane = threadIdx.x & 31;
+    const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    for (int64_t task = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; task < rows * ngroup; task += nwarps) {
+        const int64_t row = task / ngroup;
+        const int cg = (int)(task % ngroup);
+        quantize_group128(src + row * cols + cg * 128, dst + row * cols + cg * 128, scales + row * ngroup + cg, lane);
+    }
+}
+
+// Only the valid rows of a (groups, rows_per_group, cols) tensor (row < count[group]): a persistent grid walks the
+// flattened list of valid (row, column group) pairs, found through a prefix over the groups' counts.
+template <typename T>
+__global__ void __launch_bounds__(256)
+quantize_group_rows_fp8_kernel(const T* __restrict__ src, const int32_t* __restrict__ count, int groups,
+                               int rows_per_group, int cols, uint8_t* __restrict__ dst, float* __restrict__ scales) {
+    __shared__ int s_prefix[F8_MAX_GROUPS + 1];
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        int running = 0;
+        if (lane == 0) s_prefix[0] = 0;
+        for (int g0 = 0; g0 < groups; g0 += 32) {
+            const int g = g0 + lane;
+            int v = g < groups ? min(max(count[g], 0), rows_per_group) : 0;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const int o = __shfl_up_sync(0xffffffffu, v, d);
+                if (lane >= d) v += o;
+            }
+            if (g < groups) s_prefix[g + 1] = running + v;
+            running += __shfl_sync(0xffffffffu, v, 31);
+        }
+    }
+    __syncthreads();
+    const int ngroup = cols / 128;
+    const int lane = threadIdx.x & 31;
+    const int64_t total = (int64_t)s_prefix[groups] * ngroup;
+    const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    for (int64_t task = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; task < total; task += nwarps) {
+        const int vrow = (int)(task / ngroup);
+        const int cg = (int)(task % ngroup);
+        int lo = 0, hi = groups;                       // largest g with s_prefix[g] <= vrow
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (s_prefix[mid] <= vrow) lo = mid; else hi = mid;
+        }
+        const int64_t row = (int64_t)lo * rows_per_group + (vrow - s_prefix[lo]);
+        quantize_group128(src + row * cols + cg * 128, dst + row * cols + cg * 128, scales + row * ngroup + cg, lane);
+    }
+}
+
+// One CTA per 128 x 128 block of a (mats, rows, cols) tensor: scale = amax / 448.
+template <typename T>
+__global__ void __launch_bounds__(256)
+quantize_blocks_fp8_kernel(const T* __restrict__ src, int rows, int cols, uint8_t* __restrict__ dst,
+                           float* __restrict__ scales) {
+    __shared__ float s_red[8];
+    const int cb = blockIdx.x, rb = blockIdx.y, mat = blockIdx.z;
+    const int ncb = cols / 128, nrb = (rows + 127) / 128;
+    const size_t base = (size_t)mat * rows * cols;
+    float amax = 0.0f;
+    for (int i = threadIdx.x; i < 128 * 32; i += 256) {
+        const int r = rb * 128 + i / 32, c = cb * 128 + (i % 32) * 4;
+        if (r < rows) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) amax = fmaxf(amax, fabsf(static_cast<float>(src[base + (size_t)r * cols + c + j])));
+        }
+    }
+#pragma unroll
+    for (int m = 16; m >= 1; m >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
+    if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    amax = s_red[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) amax = fmaxf(amax, s_red[w]);
+    const float scale = amax > 0.0f ? amax / 448.0f : 1.0f;
+    const float inv = 1.0f / scale;
+    for (int i = threadIdx.x; i < 128 * 32; i += 256) {
+        const int r = rb * 128 + i / 32, c = cb * 128 + (i % 32) * 4;
+        if (r < rows) {
+            uint32_t packed = 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                packed |= (uint32_t)__nv_cvt_float_to_fp8(static_cast<float>(src[base + (size_t)r * cols + c + j]) * inv,
+                                                          __NV_SATFINITE, __NV_E4M3) << (8 * j);
+            *reinterpret_cast<uint32_t*>(dst + base + (size_t)r * cols + c) = packed;
+        }
+    }
+    if (threadIdx.x == 0) scales[((size_t)mat * nrb + rb) * ncb + cb] = scale;
+}
+
+// ---- host side ------------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn8() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            return nullptr;
+        fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+    return fn;
+}
+
+// (outer, rows, K) byte tensor, K contiguous; box = 128 bytes x box_rows x 1 with the 128-byte swizzle.
+aristos_status_t make_map_u8(CUtensorMap* tm, const void* base, int K, int rows, int outer, int box_rows) {
+    EncodeTiledFn enc = encode_tiled_fn8();
+    if (!enc) { set_last_error("cuTensorMapEncodeTiled is not available from the driver"); return ARISTOS_ERR_CUDA; }
+    const cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)rows, (cuuint64_t)outer};
+    const cuuint64_t strides[2] = {(cuuint64_t)K, (cuuint64_t)K * (cuuint64_t)rows};
+    const cuuint32_t box[3] = {F8_KB, (cuuint32_t)box_rows, 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_last_error("cuTensorMapEncodeTiled (fp8) failed with %d (K=%d rows=%d outer=%d)", (int)r, K, rows, outer);
+        return ARISTOS_ERR_CUDA;
+    }
+    return ARISTOS_OK;
+}
+
+aristos_status_t launch_fp8_gemm(const void* A, const void* B0, const void* B1, const Fp8GemmParams& p, int grid_limit,
+                                 cudaStream_t st) {
+    CUtensorMap tmA, tmB0, tmB1;
+    ARISTOS_TRY(make_map_u8(&tmA, A, p.K, p.rows_per_group, p.groups, 128));
+    ARISTOS_TRY(make_map_u8(&tmB0, B0, p.K, p.N, p.experts, 64));
+    ARISTOS_TRY(make_map_u8(&tmB1, B1, p.K, p.N, p.experts, 64));
+    ARISTOS_CUDA_TRY(cudaFuncSetAttribute(ffn_fp8_grouped_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          F8_SMEM_BYTES));
+    const int out_w = p.gated ? 64 : 128;
+    int sms = device_sm_count();
+    if (sms <= 0) { set_last_error("no CUDA device"); return ARISTOS_ERR_CUDA; }
+    if (grid_limit > 0 && grid_limit < sms) sms = grid_limit;
+    const int64_t bound = (int64_t)p.groups * ceil_div(p.row_end - p.row_begin, F8_BM) * ceil_div(p.N, out_w);
+    const int grid = (int)(bound < sms ? bound : sms);
+    if (grid <= 0) return ARISTOS_OK;
+    ffn_fp8_grouped_gemm_kernel<<<grid, F8_THREADS, F8_SMEM_BYTES, st>>>(tmA, tmB0, tmB1, p);
+    ARISTOS_COUNT_LAUNCH();
+    ARISTOS_CUDA_TRY(cudaGetLastError());
+    return ARISTOS_OK;
+}
+
+}  // namespace
+
+// xq (groups, rows, H) e4m3 with sx (groups*rows, H/128); w1q/w3q (experts, I, H) with s1/s3 (experts, I/128, H/128);
+// w2q (experts, H, I) with s2 (experts, H/128, I/128); h (bf16), hq + sh: scratch; y (groups, rows, H) bf16.
+aristos_status_t expert_ffn_fp8_sm100(const void* xq, const float* sx, const int32_t* count, int groups,
+                                      int rows_per_group, int experts, const void* w1q, const float* s1,
+                                      const void* w3q, const float* s3, const void* w2q, const float* s2, void* h,
+                                      void* hq, float* sh, void* y, int H, int I, int hidden_act, int row_begin,
+                                      int row_end, int sm_limit, int32_t* dev_status, cudaStream_t st) {
+    if (groups > F8_MAX_GROUPS) { set_last_error("expert_ffn(fp8): more than %d row groups", F8_MAX_GROUPS); return ARISTOS_ERR_CONFIG; }
+    if (H % 128 != 0 || I % 128 != 0) { set_last_error("expert_ffn(fp8): H and I must be multiples of 128"); return ARISTOS_ERR_CONFIG; }
+    if (row_begin % F8_BM != 0) { set_last_error("expert_ffn(fp8): row_begin must be a multiple of 128"); return ARISTOS_ERR_INVALID_ARG; }
+    const bool gated = hidden_act == ARISTOS_ACT_SWIGLU;
+    Fp8GemmParams p{};
+    p.count = count;
+    p.groups = groups;
+    p.experts = experts;
+    p.rows_per_group = rows_per_group;
+    p.row_begin = row_begin;
+    p.row_end = row_end;
+    p.dev_status = dev_status;
+    p.N = I; p.K = H; p.gated = gated ? 1 : 0; p.act = hidden_act;
+    p.sa = sx; p.sb0 = s1; p.sb1 = gated ? s3 : s1;
+    p.out = static_cast<__nv_bfloat16*>(h);
+    ARISTOS_TRY(launch_fp8_gemm(xq, w1q, gated ? w3q : w1q, p, sm_limit, st));
+    // hidden activations: bf16 -> e4m3 per row and 128 columns (valid rows only)
+    quantize_group_rows_fp8_kernel<__nv_bfloat16><<<device_sm_count() * 4, 256, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(h), count, groups, rows_per_group, I, static_cast<uint8_t*>(hq), sh);
+    ARISTOS_COUNT_LAUNCH();
+    p.N = H; p.K = I; p.gated = 0; p.act = ARISTOS_ACT_IDENTITY;
+    p.sa = sh; p.sb0 = s2; p.sb1 = s2;
+    p.out = static_cast<__nv_bfloat16*>(y);
+    ARISTOS_TRY(launch_fp8_gemm(hq, w2q, w2q, p, sm_limit, st));
+    ARISTOS_CUDA_TRY(cudaGetLastError());
+    return ARISTOS_OK;
+}
+
+}  // namespace aristos
+
+using namespace aristos;
+
+extern "C" aristos_status_t aristos_quantize_fp8(const void* src, int64_t mats, int64_t rows, int cols, int block_rows,
+                                                 int src_dtype, void* dst_fp8, float* scales, void* stream) {
+    if (!src || !dst_fp8 || !scales) { set_last_error("quantize_fp8: NULL pointer"); return ARISTOS_ERR_INVALID_ARG; }
+    if (mats < 1 || rows < 0 || cols <= 0 || cols % 128 != 0 || (block_rows != 1 && block_rows != 128)) {
+        set_last_error("quantize_fp8: cols must be a multiple of 128 and block_rows 1 or 128");
+        return ARISTOS_ERR_INVALID_ARG;
+    }
+    if (src_dtype != ARISTOS_DTYPE_BF16 && src_dtype != ARISTOS_DTYPE_F32) {
+        set_last_error("quantize_fp8: source dtype must be bf16 or fp32");
+        return ARISTOS_ERR_UNSUPPORTED;
+    }
+    if (rows == 0) return ARISTOS_OK;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (block_rows == 1) {
+        const int64_t all = mats * rows;
+        int64_t blocks = (all * (cols / 128) * 32 + 255) / 256;
+        const int64_t cap_blocks = (int64_t)device_sm_count() * 8;
+        if (blocks > cap_blocks) blocks = cap_blocks;
+        if (src_dtype == ARISTOS_DTYPE_BF16)
+            quantize_rows_fp8_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, st>>>(
+                (const __nv_bfloat16*)src, all, cols, (uint8_t*)dst_fp8, scales);
+        else
+            quantize_rows_fp8_kernel<float><<<(unsigned)blocks, 256, 0, st>>>((const float*)src, all, cols,
+                                                                              (uint8_t*)dst_fp8, scales);
+    } else {
+        if (mats > 65535 || (rows + 127) / 128 > 65535) { set_last_error("quantize_fp8: tensor too large"); return ARISTOS_ERR_CONFIG; }
+        dim3 grid(cols / 128, (unsigned)((rows + 127) / 128), (unsigned)mats);
+        if (src_dtype == ARISTOS_DTYPE_BF16)
+            quantize_blocks_fp8_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)src, (int)rows, cols,
+                                                                            (uint8_t*)dst_fp8, scales);
+        else
+            quantize_blocks_fp8_kernel<float><<<grid, 256, 0, st>>>((const float*)src, (int)rows, cols, (uint8_t*)dst_fp8,
+                                                                    scales);
+    }
+    ARISTOS_COUNT_LAUNCH();
+    ARISTOS_CUDA_TRY(cudaGetLastError());
+    return ARISTOS_OK;
+}

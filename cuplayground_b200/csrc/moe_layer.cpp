@@ -37,6 +37,10 @@ struct aristos_moe {
     int32_t *topk_idx = nullptr, *count = nullptr, *slot_of = nullptr, *token_of_slot = nullptr, *rcount = nullptr,
             *dev_status = nullptr;
     float *topk_w = nullptr, *gate_bias = nullptr;
+    // fp8 path (torch_dtype 4): quantised activations, their scales, and the re-quantised hidden activations
+    bool fp8 = false;
+    void *xq = nullptr, *xgq = nullptr, *hq = nullptr;
+    float *sx = nullptr, *sxg = nullptr, *sh = nullptr;
     void *dispatch_scratch = nullptr, *xg = nullptr, *xr = nullptr, *h = nullptr, *yr = nullptr, *yg = nullptr;
     // host-activation path: two staging slots so that the copies of one call overlap the kernels of its neighbours
     struct HostSlot {
@@ -94,7 +98,16 @@ size_t plan_workspace(aristos_moe* L, char* base) {
     CARVE(token_of_slot, int32_t*, E * cap * 4)
     CARVE(gate_bias, float*, E * 4)
     CARVE(dispatch_scratch, void*, L->dispatch_scratch_bytes)
-    CARVE(xg, void*, E * cap * H * elt)
+    if (L->fp8) {
+        CARVE(xq, void*, S * H)
+        CARVE(sx, float*, S * (H / 128) * 4)
+        CARVE(xgq, void*, E * cap * H)
+        CARVE(sxg, float*, E * cap * (H / 128) * 4)
+        CARVE(hq, void*, rows_local * I)
+        CARVE(sh, float*, rows_local * (I / 128) * 4)
+    } else {
+        CARVE(xg, void*, E * cap * H * elt)
+    }
     CARVE(h, void*, rows_local * I * elt)
     CARVE(yr, void*, rows_local * H * elt)
     if (L->world > 1 && !L->p2p) {
@@ -145,8 +158,14 @@ aristos_status_t aristos_moe_create(const aristos_config_t* cfg, int rank, int w
     if (cfg->ep_world != world) { set_last_error("create: config ep_world (%d) != world (%d)", cfg->ep_world, world); return ARISTOS_ERR_CONFIG; }
     if (world > 1 && !nccl_unique_id) { set_last_error("create: world > 1 needs a NCCL unique id"); return ARISTOS_ERR_INVALID_ARG; }
     if (cfg->torch_dtype == ARISTOS_DTYPE_FP8_E4M3) {
-        set_last_error("create: torch_dtype 4 (fp8 e4m3, block-scaled) is not implemented; 0 fp32, 1 tf32, 2 bf16, 3 fp16 are");
-        return ARISTOS_ERR_UNSUPPORTED;
+        if (world > 1) {
+            set_last_error("create: torch_dtype 4 (fp8) is implemented for a single rank only");
+            return ARISTOS_ERR_UNSUPPORTED;
+        }
+        if (cfg->hidden_size % 512 != 0 || cfg->intermediate_size % 128 != 0) {
+            set_last_error("create: fp8 needs hidden_size %% 512 == 0 and intermediate_size %% 128 == 0");
+            return ARISTOS_ERR_CONFIG;
+        }
     }
     int dev = 0;
     ARISTOS_CUDA_TRY(cudaGetDevice(&dev));
@@ -164,7 +183,8 @@ aristos_status_t aristos_moe_create(const aristos_config_t* cfg, int rank, int w
     L->cap = aristos_config_capacity(cfg);
     L->E_local = L->E / world;
     L->groups = L->E_local * world;
-    L->elt = dtype_bytes(cfg->torch_dtype);
+    L->fp8 = cfg->torch_dtype == ARISTOS_DTYPE_FP8_E4M3;
+    L->elt = L->fp8 ? 2 : dtype_bytes(cfg->torch_dtype);     // fp8: activations and output are bf16
     if ((int64_t)L->E * L->cap > 0x7fffffffLL) { delete L; set_last_error("create: E*capacity overflows int32"); return ARISTOS_ERR_CONFIG; }
     if (L->groups > 1024) { delete L; set_last_error("create: more than 1024 row groups per rank"); return ARISTOS_ERR_CONFIG; }
     L->dispatch_scratch_bytes = aristos_dispatch_scratch_bytes(L->S, L->k, L->E);
@@ -237,13 +257,13 @@ aristos_status_t aristos_moe_set_workspace(aristos_moe_t* L, void* workspace, si
 aristos_status_t aristos_moe_forward(aristos_moe_t* L, const void* x, const void* w_gate, const float* gate_bias,
                                      const void* w1, const void* w3, const void* w2, const void* scales, void* out,
                                      void* stream) {
-    (void)scales;
     if (!L || !x || !w_gate || !w1 || !w2 || !out) { set_last_error("forward: NULL pointer"); return ARISTOS_ERR_INVALID_ARG; }
     if (L->cfg.hidden_act == ARISTOS_ACT_SWIGLU && !w3) { set_last_error("forward: SwiGLU needs w3"); return ARISTOS_ERR_INVALID_ARG; }
     ARISTOS_TRY(ensure_workspace(L));
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int64_t launches0 = launch_counter();
-    const int dt = L->cfg.torch_dtype;
+    const int dt = L->fp8 ? ARISTOS_DTYPE_BF16 : L->cfg.torch_dtype;     // dtype of x, out and the expert outputs
+    if (L->fp8 && !scales) { set_last_error("forward: fp8 needs the weight scales"); return ARISTOS_ERR_INVALID_ARG; }
 
     const float* bias = gate_bias;
     if (!bias && L->cfg.gate_bias_zipf_s > 0.0) {
@@ -265,10 +285,25 @@ aristos_status_t aristos_moe_forward(aristos_moe_t* L, const void* x, const void
     PROF_MARK(1);
     ARISTOS_TRY(dispatch_impl(L->topk_idx, L->S, L->k, L->E, L->cap, L->count, L->slot_of, L->token_of_slot,
                               L->dispatch_scratch, L->dispatch_scratch_bytes, L->dev_status, st));
-    ARISTOS_TRY(aristos_permute(x, L->slot_of, L->S, L->k, L->H, dt, L->xg, st));
+    if (L->fp8) {
+        // quantise the tokens per row and 128 elements, then gather codes and scales into expert-major order
+        ARISTOS_TRY(aristos_quantize_fp8(x, 1, L->S, L->H, 1, ARISTOS_DTYPE_BF16, L->xq, L->sx, stream));
+        ARISTOS_TRY(aristos_permute(L->xq, L->slot_of, L->S, L->k, L->H, ARISTOS_DTYPE_FP8_E4M3, L->xgq, st));
+        ARISTOS_TRY(aristos_permute(L->sx, L->slot_of, L->S, L->k, L->H / 128, ARISTOS_DTYPE_F32, L->sxg, st));
+    } else {
+        ARISTOS_TRY(aristos_permute(x, L->slot_of, L->S, L->k, L->H, dt, L->xg, st));
+    }
     PROF_MARK(2);
 
-    if (L->world == 1) {
+    if (L->fp8) {
+        const size_t nb1 = (size_t)L->E * (L->I / 128) * (L->H / 128);
+        const float* s1 = static_cast<const float*>(scales);
+        const float* s3 = L->cfg.hidden_act == ARISTOS_ACT_SWIGLU ? s1 + nb1 : nullptr;
+        const float* s2 = s1 + nb1 * (L->cfg.hidden_act == ARISTOS_ACT_SWIGLU ? 2 : 1);
+        ARISTOS_TRY(aristos_expert_ffn_fp8(L->xgq, L->sxg, L->count, L->E, L->cap, L->E, w1, s1, w3, s3, w2, s2, L->h,
+                                           L->hq, L->sh, L->yr, L->H, L->I, L->cfg.hidden_act, 0, L->cap, 0,
+                                           L->dev_status, st));
+    } else if (L->world == 1) {
         ARISTOS_TRY(aristos_expert_ffn_bias(L->xg, L->count, L->E, L->cap, L->E, w1, w3, w2, L->b1, L->b3, L->b2, L->h, L->yr, L->H, L->I,
                                        L->cfg.hidden_act, dt, 0, L->cap, 0, L->dev_status, st));
     } else if (L->p2p) {

@@ -13,7 +13,7 @@ from . import _lib
 from .config import AristosConfig
 
 _TORCH_DTYPE = {_lib.DTYPE_F32: torch.float32, _lib.DTYPE_TF32: torch.float32, _lib.DTYPE_BF16: torch.bfloat16,
-                _lib.DTYPE_F16: torch.float16}
+                _lib.DTYPE_F16: torch.float16, _lib.DTYPE_FP8_E4M3: torch.bfloat16}   # fp8: activations are bf16
 # storage type -> dtype code; fp32 tensors mean exact fp32 math unless a call asks for tf32 explicitly
 _ARISTOS_DTYPE = {torch.float32: _lib.DTYPE_F32, torch.bfloat16: _lib.DTYPE_BF16, torch.float16: _lib.DTYPE_F16}
 
@@ -138,6 +138,39 @@ def expert_ffn(xg, count, w1, w3, w2, hidden_act: int, *, experts: Optional[int]
     return y
 
 
+def quantize_fp8(src: torch.Tensor, block_rows: int):
+    """e4m3 codes (uint8, same shape) and fp32 scales of a bf16 / fp32 tensor (..., rows, cols): block_rows 1 = per
+    row and 128 columns (activations), 128 = per 128 x 128 block of every (rows, cols) matrix (weights)."""
+    rows, cols = src.shape[-2], src.shape[-1]
+    mats = src.numel() // (rows * cols)
+    q = torch.empty(src.shape, dtype=torch.uint8, device=src.device)
+    if block_rows == 1:
+        scales = torch.empty((*src.shape[:-1], cols // 128), dtype=torch.float32, device=src.device)
+    else:
+        scales = torch.empty((*src.shape[:-2], (rows + 127) // 128, cols // 128), dtype=torch.float32,
+                             device=src.device)
+    _lib.check(_lib.load().aristos_quantize_fp8(_ptr(src), mats, rows, cols, block_rows, _dt(src), _ptr(q),
+                                                _ptr(scales), _stream_ptr()))
+    return q, scales
+
+
+def expert_ffn_fp8(xq, sx, count, w1q, s1, w3q, s3, w2q, s2, hidden_act: int, dev_status=None):
+    """FP8 expert FFN: xq (groups, rows, H) uint8 + sx (groups, rows, H/128); weights uint8 + block scales ->
+    y (groups, rows, H) bf16."""
+    groups, rows, H = xq.shape
+    I = w1q.shape[1]
+    dev = xq.device
+    h = torch.empty((groups, rows, I), dtype=torch.bfloat16, device=dev)
+    hq = torch.empty((groups, rows, I), dtype=torch.uint8, device=dev)
+    sh = torch.empty((groups, rows, I // 128), dtype=torch.float32, device=dev)
+    y = torch.zeros((groups, rows, H), dtype=torch.bfloat16, device=dev)
+    _lib.check(_lib.load().aristos_expert_ffn_fp8(_ptr(xq), _ptr(sx), _ptr(count), groups, rows, w1q.shape[0],
+                                                  _ptr(w1q), _ptr(s1), _ptr(w3q), _ptr(s3), _ptr(w2q), _ptr(s2),
+                                                  _ptr(h), _ptr(hq), _ptr(sh), _ptr(y), H, I, hidden_act, 0, rows, 0,
+                                                  _ptr(dev_status), _stream_ptr()))
+    return y
+
+
 def combine(y, slot_of, topk_w):
     S, k = slot_of.shape
     H = y.shape[-1]
@@ -182,11 +215,12 @@ class MoELayer:
         self._bias = (b1, b3, b2)
         _lib.check(self._lib.aristos_moe_set_bias(self._h, _ptr(b1), _ptr(b3), _ptr(b2)))
 
-    def forward(self, x, w_gate, w1, w3, w2, gate_bias=None, out=None, stream=None):
+    def forward(self, x, w_gate, w1, w3, w2, gate_bias=None, out=None, stream=None, scales=None):
+        """scales: fp8 only - the weights' block scales [s1 | s3 | s2] as one contiguous fp32 tensor."""
         if out is None:
             out = torch.empty_like(x)
         _lib.check(self._lib.aristos_moe_forward(self._h, _ptr(x), _ptr(w_gate), _ptr(gate_bias), _ptr(w1), _ptr(w3),
-                                                 _ptr(w2), None, _ptr(out), _stream_ptr(stream)))
+                                                 _ptr(w2), _ptr(scales), _ptr(out), _stream_ptr(stream)))
         return out
 
     def forward_host(self, x_host, w_gate, w1, w3, w2, out_host, gate_bias=None, stream=None):

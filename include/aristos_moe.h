@@ -139,6 +139,9 @@ ARISTOS_API aristos_status_t aristos_moe_set_bias(aristos_moe_t* layer, const vo
  *   x (S,H) activations          w_gate (E,H)        gate_bias (E) fp32 or NULL (NULL + gate_bias_zipf_s > 0 =
  *   the layer's own Zipf prior)   w1 (E_local,I,H)    w3 (E_local,I,H), SwiGLU only, else NULL
  *   w2 (E_local,H,I)             scales: fp8 only, else NULL          out (S,H), same dtype as x
+ * torch_dtype 4 (fp8): x and out are bf16 (activations are quantised inside, per token and 128 elements); w1 / w3 /
+ * w2 are e4m3; scales = fp32 [s1 (E_local, I/128, H/128) | s3 (same, SwiGLU only) | s2 (E_local, H/128, I/128)],
+ * contiguous, as aristos_quantize_fp8(block_rows = 128) writes them. Single rank only in this build.
  * E_local = num_experts / world; rank r owns experts [r*E_local, (r+1)*E_local). Dropped tokens give zero rows.
  */
 ARISTOS_API aristos_status_t aristos_moe_forward(aristos_moe_t* layer, const void* x, const void* w_gate,
@@ -241,6 +244,28 @@ ARISTOS_API aristos_status_t aristos_expert_ffn_bias(const void* xg, const int32
                                                      void* h_scratch, void* y, int H, int I, int hidden_act,
                                                      int dtype, int row_begin, int row_end, int sm_limit,
                                                      int32_t* dev_status, void* stream);
+/*
+ * FP8 (e4m3) operands with fp32 block scales (torch_dtype 4, extension; the reference lists fp8 e4m3 among its
+ * tensor value types, util.cuh:70-76, but has no kernel for it).
+ * aristos_quantize_fp8: src (mats, rows, cols) in bf16 or fp32 -> dst e4m3 and scales = amax / 448 per
+ *   block_rows x 128 block: block_rows 1 = per row and 128 columns, scales (mats*rows, cols/128) - activations;
+ *   block_rows 128 = per 128 x 128 block, scales (mats, ceil(rows/128), cols/128) - weights.
+ * aristos_expert_ffn_fp8: like aristos_expert_ffn on quantised operands: xq (groups, rows, H) with sx
+ *   (groups*rows, H/128); w1q / w3q (experts, I, H) with s1 / s3 (experts, I/128, H/128); w2q (experts, H, I) with
+ *   s2 (experts, H/128, I/128). Every 128-wide K block is accumulated on the tensor cores and promoted with its
+ *   scale in fp32. h is produced in bf16 (h_scratch), re-quantised per row and 128 columns (hq_scratch, sh_scratch)
+ *   for the down projection; y is bf16. H and I must be multiples of 128.
+ */
+ARISTOS_API aristos_status_t aristos_quantize_fp8(const void* src, int64_t mats, int64_t rows, int cols,
+                                                  int block_rows, int src_dtype, void* dst_fp8, float* scales,
+                                                  void* stream);
+ARISTOS_API aristos_status_t aristos_expert_ffn_fp8(const void* xq, const float* sx, const int32_t* count, int groups,
+                                                    int rows_per_group, int experts, const void* w1q,
+                                                    const float* s1, const void* w3q, const float* s3,
+                                                    const void* w2q, const float* s2, void* h_scratch,
+                                                    void* hq_scratch, float* sh_scratch, void* y, int H, int I,
+                                                    int hidden_act, int row_begin, int row_end, int sm_limit,
+                                                    int32_t* dev_status, void* stream);
 /* Combine: out[t] = sum_j topk_w[t,j] * y[slot_of[t,j]] in increasing j (fp32), dropped assignments add
  * nothing. Replaces Combine / VAA / deviceCombine (auditorium/combine.cuh:19-205). */
 ARISTOS_API aristos_status_t aristos_combine(const void* y, const int32_t* slot_of, const float* topk_w, int S,

@@ -223,6 +223,43 @@ static inline float act_apply(float v, int act) {
 }
 static inline float silu(float v) { return v / (1.0f + expf(-v)); }
 
+static inline float round_bf16_one(float v) {
+    uint32_t u; memcpy(&u, &v, 4);
+    if ((u & 0x7F800000u) != 0x7F800000u) u += 0x7FFFu + ((u >> 16) & 1u);
+    u &= 0xFFFF0000u;
+    memcpy(&v, &u, 4);
+    return v;
+}
+
+/* Nearest fp8 e4m3 value (ties to even, saturating at +-448), returned as fp32. */
+static inline float e4m3_round(float f) {
+    float a = fabsf(f);
+    if (!(a < 448.0f)) a = 448.0f;
+    else if (a < 0.015625f) a = rintf(a * 512.0f) * (1.0f / 512.0f);             /* subnormals: step 2^-9 */
+    else {
+        int ex;
+        frexpf(a, &ex);                                                          /* a = m * 2^ex, m in [0.5, 1) */
+        const float step = ldexpf(1.0f, ex - 4);                                 /* 2^(E-3), E = ex - 1 */
+        a = rintf(a / step) * step;
+        if (a > 448.0f) a = 448.0f;
+    }
+    return copysignf(a, f);
+}
+
+/* What an fp8 pipeline stores for a row of hidden activations: bf16 rounding, then e4m3 with one scale
+ * (amax / 448) per 128 consecutive values; returned de-quantised. */
+static void quantize_row_fp8_inplace(float* h, int n) {
+    for (int i = 0; i < n; ++i) h[i] = round_bf16_one(h[i]);
+    for (int g0 = 0; g0 < n; g0 += 128) {
+        const int len = n - g0 < 128 ? n - g0 : 128;
+        float amax = 0.0f;
+        for (int i = 0; i < len; ++i) { const float a = fabsf(h[g0 + i]); if (a > amax) amax = a; }
+        const float scale = amax > 0.0f ? amax / 448.0f : 1.0f;
+        const float inv = 1.0f / scale;
+        for (int i = 0; i < len; ++i) h[g0 + i] = e4m3_round(h[g0 + i] * inv) * scale;
+    }
+}
+
 static inline float dotf(const float* a, const float* b, int K) {
     /* 16 independent partial sums so the compiler can vectorise without reassociation flags */
     float p[16];
@@ -251,7 +288,8 @@ ORC_API void orc_gemm_bias_act(const float* A, const float* B, const float* bias
  *   xg (E, cap, H); w1 (E, I, H); w3 (E, I, H) or NULL; w2 (E, H, I); y (E, cap, H)
  *   optional biases b1 (E, I), b3 (E, I), b2 (E, H): every projection is act(acc + bias) (processor/tiling.cuh:29-57)
  *   hidden_act 0 relu, 1 gelu: h = act(xg w1^T); 2 swiglu: h = silu(xg w1^T) * (xg w3^T);  y = h w2^T
- * Rows at or past count[e] are left untouched. round_h != 0 rounds h to bf16 (what a bf16 pipeline stores). */
+ * Rows at or past count[e] are left untouched. round_h 1 rounds h to bf16 (what a bf16 pipeline stores), 2 rounds it
+ * to bf16 and then to e4m3 with one scale per 128 values (what the fp8 pipeline feeds its down projection). */
 ORC_API void orc_expert_ffn(const float* xg, const int32_t* count, const float* w1, const float* w3,
                             const float* w2, const float* b1, const float* b3, const float* b2, float* y, int E,
                             int cap, int H, int I, int hidden_act, int round_h) {
@@ -286,13 +324,10 @@ ORC_API void orc_expert_ffn(const float* xg, const int32_t* count, const float* 
                 }
                 h[n1] = v;
             }
-            if (round_h) {
-                for (int n1 = 0; n1 < I; ++n1) {
-                    uint32_t u; memcpy(&u, &h[n1], 4);
-                    if ((u & 0x7F800000u) != 0x7F800000u) u += 0x7FFFu + ((u >> 16) & 1u);
-                    u &= 0xFFFF0000u;
-                    memcpy(&h[n1], &u, 4);
-                }
+            if (round_h == 1) {
+                for (int n1 = 0; n1 < I; ++n1) h[n1] = round_bf16_one(h[n1]);
+            } else if (round_h == 2) {
+                quantize_row_fp8_inplace(h, I);
             }
             float* yr = y + row * H;
             for (int n2 = 0; n2 < H; ++n2) {
@@ -339,12 +374,13 @@ ORC_API void orc_combine(const float* y, const int32_t* slot_of, const float* to
  * Optional outputs (may be NULL): topk_idx, topk_w (S*k), count (E), slot_of (S*k), token_of_slot (E*cap).
  * Token rows are computed directly from the routing (no (E,cap,H) staging buffers), so the full-size configs fit.
  * only_rows: if n_only > 0, only those tokens' output rows are computed (sampled parity at full size).
+ * x_ffn: if not NULL, the experts read these activations (e.g. de-quantised fp8) while the gate reads x.
  * ------------------------------------------------------------------------------------------------------------- */
 ORC_API int orc_moe_forward(const float* x, const float* wg, const float* gate_bias, const float* w1,
                             const float* w3, const float* w2, int S, int H, int I, int E, int k, int cap,
                             int gate_fn, int renorm, int hidden_act, int round_h, float* out,
                             int32_t* topk_idx_o, float* topk_w_o, int32_t* count_o, int32_t* slot_of_o,
-                            int32_t* token_of_slot_o, const int32_t* only_rows, int n_only) {
+                            int32_t* token_of_slot_o, const int32_t* only_rows, int n_only, const float* x_ffn) {
     float* logits = (float*)malloc(sizeof(float) * (size_t)S * E);
     int32_t* idx = (int32_t*)malloc(sizeof(int32_t) * (size_t)S * k);
     float* tw = (float*)malloc(sizeof(float) * (size_t)S * k);
@@ -366,7 +402,7 @@ ORC_API int orc_moe_forward(const float* x, const float* wg, const float* gate_b
                 const int t = n_only > 0 ? only_rows[r] : r;
                 float* o = out + (size_t)r * H;
                 for (int c = 0; c < H; ++c) o[c] = 0.0f;
-                const float* xr = x + (size_t)t * H;
+                const float* xr = (x_ffn ? x_ffn : x) + (size_t)t * H;   /* experts may see quantised activations */
                 for (int j = 0; j < k; ++j) {
                     if (slot_of[(size_t)t * k + j] < 0) continue;
                     const int e = idx[(size_t)t * k + j];
@@ -379,14 +415,10 @@ ORC_API int orc_moe_forward(const float* x, const float* wg, const float* gate_b
                         float v;
                         if (hidden_act == 2) v = silu(g) * dotf(xr, W3 + (size_t)n1 * H, H);
                         else v = act_apply(g, hidden_act);
-                        if (round_h) {
-                            uint32_t u; memcpy(&u, &v, 4);
-                            if ((u & 0x7F800000u) != 0x7F800000u) u += 0x7FFFu + ((u >> 16) & 1u);
-                            u &= 0xFFFF0000u;
-                            memcpy(&v, &u, 4);
-                        }
+                        if (round_h == 1) v = round_bf16_one(v);
                         h[n1] = v;
                     }
+                    if (round_h == 2) quantize_row_fp8_inplace(h, I);
                     for (int n2 = 0; n2 < H; ++n2) o[n2] = fmaf(w, dotf(h, W2 + (size_t)n2 * I, I), o[n2]);
                 }
             }

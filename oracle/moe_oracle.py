@@ -154,7 +154,7 @@ def combine(y, slot_of, topk_w) -> np.ndarray:
 
 
 def moe_forward(x, wg, w1, w3, w2, *, k: int, cap: int, gate_fn: int = 0, renorm: int = 0, hidden_act: int = 0,
-                gate_bias=None, round_h: int = 0, only_rows=None, want_out: bool = True):
+                gate_bias=None, round_h: int = 0, only_rows=None, want_out: bool = True, x_ffn=None):
     """Whole layer on one rank. Returns dict(out, topk_idx, topk_w, count, slot_of, token_of_slot)."""
     x, wg, w1, w2 = _cf(x), _cf(wg), _cf(w1), _cf(w2)
     w3 = None if w3 is None else _cf(w3)
@@ -162,6 +162,7 @@ def moe_forward(x, wg, w1, w3, w2, *, k: int, cap: int, gate_fn: int = 0, renorm
     S, H = x.shape
     E, I = w1.shape[0], w1.shape[1]
     assert wg.shape == (E, H) and w2.shape == (E, H, I)
+    x_ffn = None if x_ffn is None else _cf(x_ffn)
     only = None if only_rows is None else np.ascontiguousarray(only_rows, dtype=np.int32)
     n_only = 0 if only is None else int(only.size)
     out = np.empty((n_only if n_only else S, H), dtype=np.float32) if want_out else None
@@ -172,7 +173,7 @@ def moe_forward(x, wg, w1, w3, w2, *, k: int, cap: int, gate_fn: int = 0, renorm
     tos = np.empty(E * cap, dtype=np.int32)
     rc = lib().orc_moe_forward(_f(x), _f(wg), _f(gate_bias), _f(w1), _f(w3), _f(w2), S, H, I, E, k, cap, gate_fn,
                                renorm, hidden_act, round_h, _f(out), _i(idx), _f(tw), _i(count), _i(slot_of),
-                               _i(tos), _i(only), n_only)
+                               _i(tos), _i(only), n_only, _f(x_ffn))
     if rc != 0:
         raise MemoryError("oracle allocation failed")
     return dict(out=out, topk_idx=idx, topk_w=tw, count=count, slot_of=slot_of, token_of_slot=tos)
@@ -180,3 +181,47 @@ def moe_forward(x, wg, w1, w3, w2, *, k: int, cap: int, gate_fn: int = 0, renorm
 
 def num_threads() -> int:
     return int(lib().orc_num_threads())
+
+
+# ---- fp8 e4m3 (1 sign, 4 exponent bits with bias 7, 3 mantissa bits; no infinities, 0x7f / 0xff are NaN) -----------
+def _e4m3_table() -> np.ndarray:
+    t = np.zeros(256, dtype=np.float32)
+    for code in range(256):
+        s, e, m = code >> 7, (code >> 3) & 15, code & 7
+        if e == 15 and m == 7:
+            v = np.nan
+        elif e == 0:
+            v = m / 8.0 * 2.0 ** -6
+        else:
+            v = (1.0 + m / 8.0) * 2.0 ** (e - 7)
+        t[code] = -v if s else v
+    return t
+
+
+E4M3 = _e4m3_table()
+
+
+def e4m3_decode(codes: np.ndarray) -> np.ndarray:
+    return E4M3[np.asarray(codes, dtype=np.uint8)]
+
+
+def e4m3_encode(v: np.ndarray) -> np.ndarray:
+    """Round to nearest (ties to the even code), saturating at +-448."""
+    v = np.asarray(v, dtype=np.float32)
+    pos = E4M3[:127].astype(np.float64)                      # 0 .. 448, increasing with the code
+    a = np.minimum(np.abs(v).astype(np.float64), 448.0)
+    hi = np.clip(np.searchsorted(pos, a, side="left"), 0, 126)
+    lo = np.clip(hi - 1, 0, 126)
+    dlo, dhi = a - pos[lo], pos[hi] - a
+    pick_hi = (dhi < dlo) | ((dhi == dlo) & (hi % 2 == 0))
+    code = np.where(pick_hi, hi, lo).astype(np.uint8)
+    return (code | (np.signbit(v).astype(np.uint8) << 7)).astype(np.uint8)
+
+
+def dequantize_fp8(codes: np.ndarray, scales: np.ndarray, block_rows: int) -> np.ndarray:
+    """codes (..., rows, cols) with scales per block_rows x 128 block -> fp32."""
+    v = e4m3_decode(codes)
+    s = np.repeat(np.asarray(scales, dtype=np.float32), 128, axis=-1)[..., :codes.shape[-1]]
+    if block_rows > 1:
+        s = np.repeat(s, block_rows, axis=-2)[..., :codes.shape[-2], :]
+    return (v * s).astype(np.float32)
