@@ -30,6 +30,11 @@ WORKLOADS = {
     # enough for a multi-pass profiler capture
     "config3-profile": (3, "Mixtral-shaped, reduced for profiling: H=4096 I=14336 SwiGLU E=2 top-2 cf=1.25 bf16, "
                            "4096 tokens"),
+    "config4": (4, "DeepSeek-V3-shaped, one rank holding all experts: H=7168 I=2048 SwiGLU E=256 top-8 sigmoid gate "
+                   "normalised over the selected, no drops, FP8 e4m3 weights with 128x128-block fp32 scales, activations "
+                   "quantised per token per 128, bf16 output, 4096 tokens, seed 3"),
+    "config4-rank": (4, "DeepSeek-V3-shaped, the share of one of eight ranks: as config4 with the 32 experts a rank "
+                        "owns, 4096 tokens"),
     "config5": (5, "skewed routing: H=2048 I=1024 GELU E=128 top-4 Zipf(1.2) prior cf=1.0 bf16, 8192 tokens per "
                    "rank, seed 4"),
 }
@@ -203,7 +208,7 @@ def run_ours(args, cfg, workload_desc):
     S, H, I, E = cfg.S, cfg.hidden_size, cfg.intermediate_size, cfg.num_experts
     El = E // world
     dt = torch.bfloat16
-    x, wg, w1, w3, w2 = layer.synthetic_tensors(cfg, rank, world)
+    x, wg, w1, w3, w2, scales = layer.synthetic_tensors(cfg, rank, world)
     L = layer.MoELayer(cfg, rank, world, uid)
     out = torch.empty_like(x)
 
@@ -215,7 +220,7 @@ def run_ours(args, cfg, workload_desc):
 
     # ---- device-resident throughput ---------------------------------------------------------------------------------
     for _ in range(args.warmup):
-        L.forward(x, wg, w1, w3, w2, out=out)
+        L.forward(x, wg, w1, w3, w2, out=out, scales=scales)
     L.status()
     kept = int(L.routing()["count"].sum())
     L.set_profiling(True)      # stage stopwatch: events inside the timed region, averaged over its steps
@@ -225,7 +230,7 @@ def run_ours(args, cfg, workload_desc):
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record()
     for _ in range(args.steps):
-        L.forward(x, wg, w1, w3, w2, out=out)
+        L.forward(x, wg, w1, w3, w2, out=out, scales=scales)
     ev1.record()
     barrier()
     clocks = sampler.stop() if sampler else None
@@ -249,12 +254,12 @@ def run_ours(args, cfg, workload_desc):
     L.set_profiling(False)
     xh = [x.cpu().pin_memory(), x.cpu().pin_memory()]
     oh = [torch.empty_like(xh[0]).pin_memory(), torch.empty_like(xh[0]).pin_memory()]
-    L.forward_host(xh[0], wg, w1, w3, w2, oh[0])
+    L.forward_host(xh[0], wg, w1, w3, w2, oh[0], scales=scales)
     e2e_steps = max(4, min(args.steps, 20))
     barrier()
     t_start = time.perf_counter()
     for i in range(e2e_steps):
-        L.submit_host(xh[i & 1], wg, w1, w3, w2, oh[i & 1])
+        L.submit_host(xh[i & 1], wg, w1, w3, w2, oh[i & 1], scales=scales)
     L.wait_host()
     torch.cuda.synchronize()
     t_e2e = time.perf_counter() - t_start
@@ -267,7 +272,7 @@ def run_ours(args, cfg, workload_desc):
     barrier()
     t_start = time.perf_counter()
     for i in range(4):
-        L.forward_host(xh[i & 1], wg, w1, w3, w2, oh[i & 1])
+        L.forward_host(xh[i & 1], wg, w1, w3, w2, oh[i & 1], scales=scales)
     t_blk = time.perf_counter() - t_start
     tb = torch.tensor([t_blk * 1e3], dtype=torch.float64, device="cuda")
     if world > 1:
@@ -293,6 +298,16 @@ def run_ours(args, cfg, workload_desc):
                            "scaled by rows, average of the two launches of a forward")
         ffn_s = stage["ffn"] * 1e-3
         achieved = ffn_flops / ffn_s / 1e12
+        fp8 = cfg.torch_dtype == 4
+        if fp8:
+            # one rank holding many experts with ~128 rows each: the expert GEMMs stream every weight once
+            w_bytes = float((E // world) * m * H * I)                       # e4m3: one byte per weight
+            a_bytes = float(kept) * (H + 2 * I + I + 2 * H)                 # xq in, h out (bf16), hq in, y out (bf16)
+            hbm = (w_bytes + a_bytes) / ffn_s / 1e9
+            roofline_fp8 = {"bound": "hbm", "kernel": "ffn_fp8_grouped_gemm_kernel", "achieved": hbm,
+                            "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": hbm / peaks["hbm_gbs"], "traffic": None,
+                            "peak_source": f"{peaks['source']} copy bandwidth", "algorithmic_bytes": w_bytes + a_bytes,
+                            "tflops": achieved, "ms_per_step": stage["ffn"]}
         roofline = {"bound": "tensor", "kernel": "ffn_grouped_gemm_kernel", "achieved": achieved,
                     "peak": peaks["bf16_sustained"], "unit": "TFLOP/s", "frac": achieved / peaks["bf16_sustained"],
                     "traffic": traffic, "traffic_source": traffic_src, "peak_source": f"{peaks['source']} bf16 sustained (kernel timed inside a "
@@ -301,7 +316,7 @@ def run_ours(args, cfg, workload_desc):
         t_roof, terms = layer_roofline(cfg, world, kept_all / world)
         line = {"metric": "moe_fwd_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
-                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3" if cfg.torch_dtype == 4 else "bf16",
                 "data": "synthetic",
                 "config": {"workload": workload_desc, "name": args.workload, "tokens_per_rank": S,
                            "parallelism": f"ep{world}", "ep_transport": L.ep_transport, "l2": "weights (>= 0.4 GB per rank) exceed the 126 MB L2, "
@@ -314,7 +329,7 @@ def run_ours(args, cfg, workload_desc):
                         "device synchronised on both sides, max over ranks",
                         "blocking_call_value": e2e_blocking},
                 "gpu_launches": int(launches),
-                "roofline": roofline,
+                "roofline": roofline_fp8 if fp8 else roofline,
                 "layer_roofline": {"seconds": t_roof, **terms, "frac": t_roof / (ms / args.steps * 1e-3),
                                    "constants": "2250 TFLOP/s dense bf16, 8 TB/s HBM, 900 GB/s NVLink per direction"},
                 "stage_ms": stage}
@@ -353,6 +368,13 @@ def main():
     cfg = cp.baseline_config(n, world=args.gpus if args.impl == "ours" else 1)
     if args.workload == "config3-profile":
         cfg.num_experts, cfg.tokens = 2, 4096
+    if args.workload == "config4-rank":
+        cfg.num_experts = 32
+    if args.workload.startswith("config4"):
+        cfg.ep_world = 1
+        if args.gpus != 1 and args.impl == "ours":
+            raise SystemExit("the fp8 workloads run on one GPU in this build")
+        args.no_cpu_baseline = True      # the fp32 oracle would need the de-quantised weights of every expert on the host
     if args.impl == "reference":
         run_reference(args, cfg, desc)
     else:

@@ -52,22 +52,39 @@ def fill_normal(t: torch.Tensor, mean: float, std: float, seed: int, stream_id: 
 def synthetic_tensors(cfg: AristosConfig, rank: int = 0, world: int = 1):
     """Seeded synthetic inputs of one rank, generated on the device: x ~ N(0,1) (a different stream per rank),
     gate weights and this rank's expert weights ~ N(0, 0.02). Expert e draws from its own Philox streams, so the
-    shards of every world size are slices of the same global weights. Returns (x, w_gate, w1, w3, w2)."""
+    shards of every world size are slices of the same global weights. Returns (x, w_gate, w1, w3, w2, scales);
+    for torch_dtype 4 the expert weights are e4m3 codes (uint8) and scales holds their 128x128-block scales
+    [s1 | s3 | s2], otherwise scales is None."""
+    fp8 = cfg.torch_dtype == _lib.DTYPE_FP8_E4M3
     dt = _TORCH_DTYPE[cfg.torch_dtype]
     S, H, I, E = cfg.S, cfg.hidden_size, cfg.intermediate_size, cfg.num_experts
     El = E // world
+    swiglu = cfg.hidden_act == _lib.ACT_SWIGLU
     new = lambda *shape: torch.empty(shape, dtype=dt, device="cuda")
     x = fill_normal(new(S, H), 0.0, 1.0, cfg.seed, 0 if rank == 0 else 0x1000 + rank)
     wg = fill_normal(new(E, H), 0.0, 0.02, cfg.seed, 1)
-    w1, w2 = new(El, I, H), new(El, H, I)
-    w3 = new(El, I, H) if cfg.hidden_act == _lib.ACT_SWIGLU else None
-    for el in range(El):
-        e = rank * El + el
-        fill_normal(w1[el], 0.0, 0.02, cfg.seed, 16 * (e + 1) + 2)
-        if w3 is not None:
-            fill_normal(w3[el], 0.0, 0.02, cfg.seed, 16 * (e + 1) + 3)
-        fill_normal(w2[el], 0.0, 0.02, cfg.seed, 16 * (e + 1) + 4)
-    return x, wg, w1, w3, w2
+
+    def expert_tensor(rows, cols, which):
+        if not fp8:
+            w = new(El, rows, cols)
+            for el in range(El):
+                fill_normal(w[el], 0.0, 0.02, cfg.seed, 16 * (rank * El + el + 1) + which)
+            return w, None
+        q = torch.empty((El, rows, cols), dtype=torch.uint8, device="cuda")
+        sc = torch.empty((El, (rows + 127) // 128, cols // 128), dtype=torch.float32, device="cuda")
+        tmp = new(rows, cols)
+        for el in range(El):          # one expert at a time: the bf16 originals never exist all at once
+            fill_normal(tmp, 0.0, 0.02, cfg.seed, 16 * (rank * El + el + 1) + which)
+            qe, se = quantize_fp8(tmp, 128)
+            q[el].copy_(qe)
+            sc[el].copy_(se)
+        return q, sc
+
+    w1, s1 = expert_tensor(I, H, 2)
+    w3, s3 = expert_tensor(I, H, 3) if swiglu else (None, None)
+    w2, s2 = expert_tensor(H, I, 4)
+    scales = torch.cat([t.reshape(-1) for t in (s1, s3, s2) if t is not None]).contiguous() if fp8 else None
+    return x, wg, w1, w3, w2, scales
 
 
 # ---- stage entry points ---------------------------------------------------------------------------------------------
@@ -223,21 +240,23 @@ class MoELayer:
                                                  _ptr(w2), _ptr(scales), _ptr(out), _stream_ptr(stream)))
         return out
 
-    def forward_host(self, x_host, w_gate, w1, w3, w2, out_host, gate_bias=None, stream=None):
+    def forward_host(self, x_host, w_gate, w1, w3, w2, out_host, gate_bias=None, stream=None, scales=None):
         """x_host / out_host: CPU tensors (pinned for full speed); weights stay on the device. Synchronous."""
         if x_host.is_cuda or out_host.is_cuda:
             raise ValueError("forward_host takes host tensors")
         _lib.check(self._lib.aristos_moe_forward_host(self._h, _ptr(x_host), _ptr(w_gate), _ptr(gate_bias), _ptr(w1),
-                                                      _ptr(w3), _ptr(w2), None, _ptr(out_host), _stream_ptr(stream)))
+                                                      _ptr(w3), _ptr(w2), _ptr(scales), _ptr(out_host),
+                                                      _stream_ptr(stream)))
         return out_host
 
-    def submit_host(self, x_host, w_gate, w1, w3, w2, out_host, gate_bias=None, stream=None):
+    def submit_host(self, x_host, w_gate, w1, w3, w2, out_host, gate_bias=None, stream=None, scales=None):
         """Asynchronous forward_host: returns once the copies and kernels are enqueued (two calls may be in flight);
         the host tensors must stay alive and untouched until wait_host()."""
         if x_host.is_cuda or out_host.is_cuda:
             raise ValueError("submit_host takes host tensors")
         _lib.check(self._lib.aristos_moe_submit_host(self._h, _ptr(x_host), _ptr(w_gate), _ptr(gate_bias), _ptr(w1),
-                                                     _ptr(w3), _ptr(w2), None, _ptr(out_host), _stream_ptr(stream)))
+                                                     _ptr(w3), _ptr(w2), _ptr(scales), _ptr(out_host),
+                                                     _stream_ptr(stream)))
 
     def wait_host(self) -> None:
         _lib.check(self._lib.aristos_moe_wait_host(self._h))
