@@ -6,11 +6,13 @@
 // fp32 scales per 128, so the accumulation has two levels: one 128-wide K block is accumulated by four
 // tcgen05.mma kind::f8f6f4 (K = 32 each) into a fresh 128-column TMEM accumulator, the four epilogue warps drain it
 // (tcgen05.ld), multiply by the block's scale and add it to fp32 register accumulators (one row and 128 columns per
-// thread) while the tensor core works on the next block in the next of four TMEM buffers.
+// thread) while the tensor core works on the next block in the next of four TMEM buffers. Eight promotion warps
+// share the work: two per TMEM lane quarter, each owning 64 of the 128 columns (32-column chunks {0, 2} or {1, 3},
+// so a SwiGLU thread holds matching gate and up columns).
 //
 // Same tile contract as the 16-bit kernel (ffn_sm100.cu; reference: fGET, mma.cuh:46-179, A (M,K) and B (N,K)
 // row-major, epilogue act(acc)): persistent CTAs, warp 0 = TMA producer (a 128-byte K block is exactly one swizzled
-// row), warp 1 = MMA issuer, warps 2-5 = promotion + epilogue. SwiGLU tiles hold 64 gate and 64 up columns in one
+// row), warp 1 = MMA issuer, warps 2-9 = promotion + epilogue. SwiGLU tiles hold 64 gate and 64 up columns in one
 // N = 128 instruction. Output is bf16, written with 16-byte stores masked by the group's row count.
 #include <cuda.h>
 #include <cuda_fp8.h>
@@ -30,8 +32,8 @@ constexpr int F8_A_BYTES = F8_BM * F8_KB;        // 16 KB
 constexpr int F8_B_BYTES = F8_BN * F8_KB;        // 16 KB
 constexpr int F8_STAGE_BYTES = F8_A_BYTES + F8_B_BYTES;
 constexpr int F8_TBUFS = 4;                      // TMEM accumulator buffers (4 x 128 columns)
-constexpr int F8_THREADS = 192;
-constexpr int F8_EPI_THREADS = 128;
+constexpr int F8_THREADS = 320;                  // producer warp, MMA warp, 8 promotion warps
+constexpr int F8_EPI_THREADS = 256;
 constexpr int F8_MAX_GROUPS = 1024;
 constexpr int F8_AUX_BYTES = 256 + (F8_MAX_GROUPS + 1) * 4;
 constexpr int F8_SMEM_BYTES = 1024 + F8_STAGES * F8_STAGE_BYTES + F8_AUX_BYTES;
@@ -196,8 +198,9 @@ ffn_fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
         }
         __syncwarp();
     } else {
-        // ------------------------------------------------------------------ promotion + epilogue (warps 2..5)
-        const int quarter = warp & 3;
+        // ------------------------------------------------------------------ promotion + epilogue (warps 2..9)
+        const int quarter = warp & 3;                       // TMEM lanes this warp may read
+        const int half = (warp - 2) >> 2;                   // 0: column chunks {0, 2}, 1: chunks {1, 3}
         const int row_in_tile = quarter * 32 + lane;
         int g = 0, tbuf = 0;
         uint32_t tphase = 0;
@@ -215,30 +218,28 @@ ffn_fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
             const float* sa_row = p.sa + ((size_t)g * p.rows_per_group + min(row, p.rows_per_group - 1)) * kblocks;
             const float* sb0_row = p.sb0 + ((size_t)e * nblk + n0 / 128) * kblocks;
             const float* sb1_row = p.gated ? p.sb1 + ((size_t)e * nblk + n0 / 128) * kblocks : sb0_row;
-            float acc[F8_BN];
+            float acc_lo[32], acc_hi[32];                    // chunk `half` and chunk `half + 2` of this row
 #pragma unroll
-            for (int i = 0; i < F8_BN; ++i) acc[i] = 0.0f;
+            for (int i = 0; i < 32; ++i) { acc_lo[i] = 0.0f; acc_hi[i] = 0.0f; }
             for (int kb = 0; kb < kblocks; ++kb) {
                 ok = ptx::mbar_wait_bounded(bar_tfull + 8 * tbuf, tphase, abort_flag, p.dev_status);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 ptx::tcgen05_fence_after();
+                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + tbuf * F8_BN;
+                uint32_t v_lo[32], v_hi[32];
+                ptx::tmem_ld_32x32b_x32(taddr + half * 32, v_lo);
+                ptx::tmem_ld_32x32b_x32(taddr + (half + 2) * 32, v_hi);
                 const float sa = __ldg(sa_row + kb);
                 const float w_lo = sa * __ldg(sb0_row + kb);       // columns 0..63 (gate, or the tile's first half)
                 const float w_hi = sa * __ldg(sb1_row + kb);       // columns 64..127 (up, or the second half)
-                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + tbuf * F8_BN;
+                ptx::tmem_ld_wait();
+                ptx::tcgen05_fence_before();
+                ptx::mbar_arrive(bar_tempty + 8 * tbuf);           // drained: the tensor core may refill the buffer
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    uint32_t v[32];
-                    ptx::tmem_ld_32x32b_x32(taddr + c * 32, v);
-                    ptx::tmem_ld_wait();
-                    if (c == 3) {                                   // buffer drained: the tensor core may refill it
-                        ptx::tcgen05_fence_before();
-                        ptx::mbar_arrive(bar_tempty + 8 * tbuf);
-                    }
-                    const float w = c < 2 ? w_lo : w_hi;
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(w, __uint_as_float(v[i]), acc[c * 32 + i]);
+                for (int i = 0; i < 32; ++i) {
+                    acc_lo[i] = fmaf(w_lo, __uint_as_float(v_lo[i]), acc_lo[i]);
+                    acc_hi[i] = fmaf(w_hi, __uint_as_float(v_hi[i]), acc_hi[i]);
                 }
                 if (++tbuf == F8_TBUFS) { tbuf = 0; tphase ^= 1u; }
             }
@@ -246,29 +247,30 @@ ffn_fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
             if (row_ok) {
                 __nv_bfloat16* orow = p.out + ((size_t)g * p.rows_per_group + row) * p.N + n0;
                 if (p.gated) {
-                    uint32_t o[32];
+                    // gate columns [32*half, +32) pair with up columns [64 + 32*half, +32): 32 outputs
+                    uint32_t o[16];
 #pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        o[i] = pack_bf16x2(act_silu(acc[2 * i]) * acc[64 + 2 * i],
-                                           act_silu(acc[2 * i + 1]) * acc[64 + 2 * i + 1]);
-                    if (n0 < p.N) {
-                        uint4* dst = reinterpret_cast<uint4*>(orow);
+                    for (int i = 0; i < 16; ++i)
+                        o[i] = pack_bf16x2(act_silu(acc_lo[2 * i]) * acc_hi[2 * i],
+                                           act_silu(acc_lo[2 * i + 1]) * acc_hi[2 * i + 1]);
+                    uint4* dst = reinterpret_cast<uint4*>(orow + half * 32);
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) dst[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
-                    }
+                    for (int i = 0; i < 4; ++i) dst[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
                 } else {
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        if (n0 + c * 32 >= p.N) break;
+                    for (int c = 0; c < 2; ++c) {
+                        const int col = (half + 2 * c) * 32;
+                        if (n0 + col >= p.N) break;
                         uint32_t o[16];
 #pragma unroll
                         for (int i = 0; i < 16; ++i) {
-                            float v0 = acc[c * 32 + 2 * i], v1 = acc[c * 32 + 2 * i + 1];
+                            float v0 = c == 0 ? acc_lo[2 * i] : acc_hi[2 * i];
+                            float v1 = c == 0 ? acc_lo[2 * i + 1] : acc_hi[2 * i + 1];
                             if (p.act == ARISTOS_ACT_RELU) { v0 = act_relu(v0); v1 = act_relu(v1); }
                             else if (p.act == ARISTOS_ACT_GELU) { v0 = act_gelu(v0); v1 = act_gelu(v1); }
                             o[i] = pack_bf16x2(v0, v1);
                         }
-                        uint4* dst = reinterpret_cast<uint4*>(orow + c * 32);
+                        uint4* dst = reinterpret_cast<uint4*>(orow + col);
 #pragma unroll
                         for (int i = 0; i < 4; ++i) dst[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
                     }
