@@ -60,6 +60,50 @@ __device__ __forceinline__ void load8_pairs(const float* p, float2 (&v)[4]) {
 
 constexpr int GATE_STAGES = 3;
 
+// One 8-element chunk of a row in the form the FMA consumes: fp32 rows as four (even, odd) float2 pairs for the packed
+// fp32x2 FMA; 16-bit rows as their four raw 32-bit words, multiplied by the mixed-precision FMA
+// (fma.rn.f32.bf16 / .f16: 16-bit operands, fp32 accumulator, one rounding) so that nothing is unpacked on the
+// integer pipe. Both give acc.x = fmaf(x[2i], w[2i], acc.x), acc.y = fmaf(x[2i+1], w[2i+1], acc.y).
+template <typename T> struct GateChunk { uint32_t w[4]; };
+template <> struct GateChunk<float> { float2 v[4]; };
+
+__device__ __forceinline__ void load_chunk(const __nv_bfloat16* p, GateChunk<__nv_bfloat16>& c) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    c.w[0] = u.x; c.w[1] = u.y; c.w[2] = u.z; c.w[3] = u.w;
+}
+__device__ __forceinline__ void load_chunk(const __half* p, GateChunk<__half>& c) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    c.w[0] = u.x; c.w[1] = u.y; c.w[2] = u.z; c.w[3] = u.w;
+}
+__device__ __forceinline__ void load_chunk(const float* p, GateChunk<float>& c) { load8_pairs(p, c.v); }
+
+__device__ __forceinline__ void fma_pair(float2& acc, const GateChunk<__nv_bfloat16>& x,
+                                         const GateChunk<__nv_bfloat16>& w, int i) {
+    asm("{\n\t"
+        ".reg .b16 xl, xh, wl, wh;\n\t"
+        "mov.b32 {xl, xh}, %2;\n\t"
+        "mov.b32 {wl, wh}, %3;\n\t"
+        "fma.rn.f32.bf16 %0, xl, wl, %0;\n\t"
+        "fma.rn.f32.bf16 %1, xh, wh, %1;\n\t"
+        "}"
+        : "+f"(acc.x), "+f"(acc.y)
+        : "r"(x.w[i]), "r"(w.w[i]));
+}
+__device__ __forceinline__ void fma_pair(float2& acc, const GateChunk<__half>& x, const GateChunk<__half>& w, int i) {
+    asm("{\n\t"
+        ".reg .b16 xl, xh, wl, wh;\n\t"
+        "mov.b32 {xl, xh}, %2;\n\t"
+        "mov.b32 {wl, wh}, %3;\n\t"
+        "fma.rn.f32.f16 %0, xl, wl, %0;\n\t"
+        "fma.rn.f32.f16 %1, xh, wh, %1;\n\t"
+        "}"
+        : "+f"(acc.x), "+f"(acc.y)
+        : "r"(x.w[i]), "r"(w.w[i]));
+}
+__device__ __forceinline__ void fma_pair(float2& acc, const GateChunk<float>& x, const GateChunk<float>& w, int i) {
+    acc = __ffma2_rn(x.v[i], w.v[i], acc);
+}
+
 // Top-k on one token's logits (in shared memory) by one warp, then the combine weights.
 __device__ __forceinline__ void topk_one_token(const float* l, int t, int E, int k, int gate_fn, int renorm, int lane,
                                                int32_t* __restrict__ topk_idx, float* __restrict__ topk_w,
@@ -153,17 +197,17 @@ gate_topk_stream_kernel(const T* __restrict__ x, const T* __restrict__ wg, const
 #pragma unroll
         for (int ee = 0; ee < GATE_TE; ++ee) acc[tt][ee] = make_float2(0.0f, 0.0f);
     for (int q = lane; q < nchunk; q += 32) {
-        float2 xv[GATE_TT][4];
+        GateChunk<T> xv[GATE_TT];
 #pragma unroll
-        for (int tt = 0; tt < GATE_TT; ++tt) load8_pairs(xrow[tt] + q * 8, xv[tt]);
+        for (int tt = 0; tt < GATE_TT; ++tt) load_chunk(xrow[tt] + q * 8, xv[tt]);
 #pragma unroll
         for (int ee = 0; ee < GATE_TE; ++ee) {
-            float2 wv[4];
-            load8_pairs(wrow[ee] + q * 8, wv);
+            GateChunk<T> wv;
+            load_chunk(wrow[ee] + q * 8, wv);
 #pragma unroll
             for (int tt = 0; tt < GATE_TT; ++tt)
 #pragma unroll
-                for (int i = 0; i < 4; ++i) acc[tt][ee] = __ffma2_rn(xv[tt][i], wv[i], acc[tt][ee]);
+                for (int i = 0; i < 4; ++i) fma_pair(acc[tt][ee], xv[tt], wv, i);
         }
     }
     float a[GATE_TT * GATE_TE];
@@ -243,17 +287,17 @@ gate_topk_kernel(const T* __restrict__ x, const T* __restrict__ wg, const float*
             __syncthreads();               // ... for every thread, and buffer (slab + 2) % 3 is no longer being read
             if (slab + 2 < nslab) issue_slab(etile, slab + 2, (slab + 2) % GATE_STAGES); else cp_async_commit();
             const T* srow = reinterpret_cast<const T*>(stage_mem + (size_t)(slab % GATE_STAGES) * ROWS * ROW_BYTES);
-            float2 xv[GATE_TT][4];
+            GateChunk<T> xv[GATE_TT];
 #pragma unroll
-            for (int tt = 0; tt < GATE_TT; ++tt) load8_pairs(srow + (wt * GATE_TT + tt) * GATE_SLAB + lane * 8, xv[tt]);
+            for (int tt = 0; tt < GATE_TT; ++tt) load_chunk(srow + (wt * GATE_TT + tt) * GATE_SLAB + lane * 8, xv[tt]);
 #pragma unroll
             for (int ee = 0; ee < GATE_TE; ++ee) {
-                float2 wv[4];
-                load8_pairs(srow + (TOK + we * GATE_TE + ee) * GATE_SLAB + lane * 8, wv);
+                GateChunk<T> wv;
+                load_chunk(srow + (TOK + we * GATE_TE + ee) * GATE_SLAB + lane * 8, wv);
 #pragma unroll
                 for (int tt = 0; tt < GATE_TT; ++tt)
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) acc[tt][ee] = __ffma2_rn(xv[tt][i], wv[i], acc[tt][ee]);
+                    for (int i = 0; i < 4; ++i) fma_pair(acc[tt][ee], xv[tt], wv, i);
             }
         }
         __syncthreads();                   // the next expert tile restarts the pipeline in buffers 0 and 1

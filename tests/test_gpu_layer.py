@@ -182,11 +182,17 @@ def test_layer_tf32(oracle, act):
     assert mx > 1e-6, "suspiciously exact: the tf32 path did not run"
 
 
-def test_unsupported_dtype_fails_loudly():
+def test_unsupported_requests_fail_loudly():
     torch, cp, layer = _mods()
+    # fp8 needs H % 512 == 0: a configuration error, not a silent fallback
     cfg = cp.AristosConfig(hidden_size=128, intermediate_size=128, num_experts=4, torch_dtype=4, tokens=128)
     with pytest.raises(cp.AristosError) as e:
         layer.MoELayer(cfg)
+    assert e.value.status == 2
+    # fp8 across ranks is not built: refused before any communicator is created
+    cfg = cp.AristosConfig(hidden_size=512, intermediate_size=128, num_experts=4, torch_dtype=4, tokens=128, ep_world=2)
+    with pytest.raises(cp.AristosError) as e:
+        layer.MoELayer(cfg, rank=0, world=2, nccl_uid=bytes(128))
     assert e.value.status == 6
 
 
