@@ -30,7 +30,7 @@ WORKLOADS = {
     # enough for a multi-pass profiler capture
     "config3-profile": (3, "Mixtral-shaped, reduced for profiling: H=4096 I=14336 SwiGLU E=2 top-2 cf=1.25 bf16, "
                            "4096 tokens"),
-    "config4": (4, "DeepSeek-V3-shaped, one rank holding all experts: H=7168 I=2048 SwiGLU E=256 top-8 sigmoid gate "
+    "config4": (4, "DeepSeek-V3-shaped (experts sharded over the ranks; one rank holds all of them at --gpus 1): H=7168 I=2048 SwiGLU E=256 top-8 sigmoid gate "
                    "normalised over the selected, no drops, FP8 e4m3 weights with 128x128-block fp32 scales, activations "
                    "quantised per token per 128, bf16 output, 4096 tokens, seed 3"),
     "config4-rank": (4, "DeepSeek-V3-shaped, the share of one of eight ranks: as config4 with the 32 experts a rank "
@@ -371,9 +371,8 @@ def main():
     if args.workload == "config4-rank":
         cfg.num_experts = 32
     if args.workload.startswith("config4"):
-        cfg.ep_world = 1
-        if args.gpus != 1 and args.impl == "ours":
-            raise SystemExit("the fp8 workloads run on one GPU in this build")
+        if args.workload == "config4-rank" and args.gpus != 1 and args.impl == "ours":
+            raise SystemExit("config4-rank is the one-GPU share of config4: run config4 with --gpus N instead")
         args.no_cpu_baseline = True      # the fp32 oracle would need the de-quantised weights of every expert on the host
     if args.impl == "reference":
         run_reference(args, cfg, desc)

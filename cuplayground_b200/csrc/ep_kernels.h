@@ -1,0 +1,23 @@
+// Kernels that move rows between ranks by storing through peer pointers (see ep_kernels.cu).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include "../../include/aristos_moe.h"
+
+namespace aristos {
+
+struct PeerPtrs {
+    void* p[16];   // rank r's copy of one exchange buffer, as mapped into this process
+};
+
+// xg-less dispatch: token row t goes, for each kept assignment, into the buffer of the rank that owns the expert.
+aristos_status_t permute_rows_to_peers(const void* x, const int32_t* slot_of, int S, int k, size_t row_bytes,
+                                       int E_local, int cap, int src_rank, const PeerPtrs& dst, cudaStream_t st);
+// Valid rows of the local expert outputs (groups x cap rows, count[g] valid) back into their source ranks' buffers.
+aristos_status_t return_rows_to_peers(const void* y, const int32_t* count, int groups, int E_local, int cap,
+                                      size_t row_bytes, int this_rank, const PeerPtrs& dst, cudaStream_t st);
+
+}  // namespace aristos

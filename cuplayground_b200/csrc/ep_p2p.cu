@@ -54,7 +54,7 @@ StreamWaitValue32Fn stream_wait_fn() {
 
 struct EpP2P {
     int rank = 0, world = 1, groups = 0;
-    size_t off_rcount = 0, off_xr = 0, off_yg = 0, bytes = 0;
+    size_t off_rcount = 0, off_xr = 0, off_yg = 0, off_aux = 0, bytes = 0;
     char* local = nullptr;
     std::vector<char*> base;     // every rank's region as mapped into this process (own = local)
     uint32_t epoch = 0;
@@ -65,7 +65,7 @@ static size_t flag_index(const EpP2P* p, int kind, int window, int src) {
 }
 
 aristos_status_t ep_p2p_create(EpComm* bootstrap, int rank, int world, int groups, size_t xr_bytes, size_t yg_bytes,
-                               EpP2P** out) {
+                               size_t aux_bytes, EpP2P** out) {
     if (!bootstrap || !out || world < 2 || world > MAX_RANKS) return ARISTOS_ERR_INVALID_ARG;
     static_assert(3 * EP_MAX_WINDOWS * MAX_RANKS * 4 <= FLAG_BYTES, "flag words fit their page");
     if (!stream_wait_fn()) { set_last_error("cuStreamWaitValue32 is not available from the driver"); return ARISTOS_ERR_CUDA; }
@@ -76,7 +76,8 @@ aristos_status_t ep_p2p_create(EpComm* bootstrap, int rank, int world, int group
     p->off_rcount = FLAG_BYTES;
     p->off_xr = align_up(p->off_rcount + (size_t)groups * 4, 1024);
     p->off_yg = align_up(p->off_xr + xr_bytes, 1024);
-    p->bytes = align_up(p->off_yg + yg_bytes, 1024);
+    p->off_aux = align_up(p->off_yg + yg_bytes, 1024);
+    p->bytes = align_up(p->off_aux + aux_bytes, 1024);
     p->base.assign(world, nullptr);
     cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&p->local), p->bytes);
     if (e != cudaSuccess) {
@@ -123,6 +124,12 @@ void ep_p2p_destroy(EpP2P* p) {
 
 void* ep_p2p_xr(EpP2P* p) { return p->local + p->off_xr; }
 void* ep_p2p_yg(EpP2P* p) { return p->local + p->off_yg; }
+void* ep_p2p_aux(EpP2P* p) { return p->local + p->off_aux; }
+
+void ep_p2p_peer_ptrs(EpP2P* p, int which, void** out) {
+    const size_t off = which == EP_BUF_XR ? p->off_xr : (which == EP_BUF_YG ? p->off_yg : p->off_aux);
+    for (int r = 0; r < p->world; ++r) out[r] = p->base[r] + off;
+}
 int32_t* ep_p2p_rcount(EpP2P* p) { return reinterpret_cast<int32_t*>(p->local + p->off_rcount); }
 uint32_t ep_p2p_begin(EpP2P* p) { return ++p->epoch; }
 

@@ -22,10 +22,15 @@ constexpr int EP_MAX_WINDOWS = 16;
 // Collective over the ranks of `bootstrap` (used for the IPC-handle exchange and as a start barrier). The exchange
 // region holds, per rank: flag words, the received row counts (groups int32), xr (xr_bytes) and yg (yg_bytes).
 aristos_status_t ep_p2p_create(EpComm* bootstrap, int rank, int world, int groups, size_t xr_bytes, size_t yg_bytes,
-                               EpP2P** out);
+                               size_t aux_bytes, EpP2P** out);
 void ep_p2p_destroy(EpP2P* p);
 void* ep_p2p_xr(EpP2P* p);
 void* ep_p2p_yg(EpP2P* p);
+void* ep_p2p_aux(EpP2P* p);   // third exchange buffer (the fp8 path keeps the received activation scales there)
+// Every rank's copy of one exchange buffer as mapped into this process (out[world]); kernels store through them.
+enum { EP_BUF_XR = 0, EP_BUF_YG = 1, EP_BUF_AUX = 2 };
+constexpr int EP_MAX_RANKS = 16;
+void ep_p2p_peer_ptrs(EpP2P* p, int which, void** out);
 int32_t* ep_p2p_rcount(EpP2P* p);
 // Starts a new forward: every flag of this forward is compared against the returned epoch.
 uint32_t ep_p2p_begin(EpP2P* p);

@@ -15,6 +15,7 @@
 #include "common.cuh"
 #include "ep_nccl.h"
 #include "ep_p2p.h"
+#include "ep_kernels.h"
 
 namespace aristos {
 aristos_status_t dispatch_impl(const int32_t* topk_idx, int S, int k, int E, int cap, int32_t* count,
@@ -101,8 +102,10 @@ size_t plan_workspace(aristos_moe* L, char* base) {
     if (L->fp8) {
         CARVE(xq, void*, S * H)
         CARVE(sx, float*, S * (H / 128) * 4)
-        CARVE(xgq, void*, E * cap * H)
-        CARVE(sxg, float*, E * cap * (H / 128) * 4)
+        if (L->world == 1) {
+            CARVE(xgq, void*, E * cap * H)
+            CARVE(sxg, float*, E * cap * (H / 128) * 4)
+        }
         CARVE(hq, void*, rows_local * I)
         CARVE(sh, float*, rows_local * (I / 128) * 4)
     } else {
@@ -118,6 +121,10 @@ size_t plan_workspace(aristos_moe* L, char* base) {
         L->xr = ep_p2p_xr(L->p2p);
         L->yg = ep_p2p_yg(L->p2p);
         L->rcount = ep_p2p_rcount(L->p2p);
+        if (L->fp8) {      // the quantised rows and their scales arrive here from every rank
+            L->xgq = L->xr;
+            L->sxg = static_cast<float*>(ep_p2p_aux(L->p2p));
+        }
     } else if (base) {
         L->xr = L->xg;
         L->yg = L->yr;
@@ -158,8 +165,9 @@ aristos_status_t aristos_moe_create(const aristos_config_t* cfg, int rank, int w
     if (cfg->ep_world != world) { set_last_error("create: config ep_world (%d) != world (%d)", cfg->ep_world, world); return ARISTOS_ERR_CONFIG; }
     if (world > 1 && !nccl_unique_id) { set_last_error("create: world > 1 needs a NCCL unique id"); return ARISTOS_ERR_INVALID_ARG; }
     if (cfg->torch_dtype == ARISTOS_DTYPE_FP8_E4M3) {
-        if (world > 1) {
-            set_last_error("create: torch_dtype 4 (fp8) is implemented for a single rank only");
+        const char* tr = getenv("ARISTOS_EP_TRANSPORT");
+        if (world > 1 && tr && !strcmp(tr, "nccl")) {
+            set_last_error("create: torch_dtype 4 (fp8) across ranks needs the peer-memory transport");
             return ARISTOS_ERR_UNSUPPORTED;
         }
         if (cfg->hidden_size % 512 != 0 || cfg->intermediate_size % 128 != 0) {
@@ -216,10 +224,13 @@ aristos_status_t aristos_moe_create(const aristos_config_t* cfg, int rank, int w
         const char* tr = getenv("ARISTOS_EP_TRANSPORT");
         if (!(tr && !strcmp(tr, "nccl")) && L->chunks <= EP_MAX_WINDOWS) {
             const size_t block_bytes = (size_t)L->cap * L->H * L->elt;
-            aristos_status_t ps = ep_p2p_create(L->comm, rank, world, L->groups, (size_t)L->groups * block_bytes,
-                                                (size_t)L->E * block_bytes, &L->p2p);
+            // fp8: received rows are e4m3 codes (one byte) plus one fp32 scale per 128 elements; outputs stay bf16
+            const size_t in_bytes = L->fp8 ? (size_t)L->groups * L->cap * L->H : (size_t)L->groups * block_bytes;
+            const size_t aux_bytes = L->fp8 ? (size_t)L->groups * L->cap * (L->H / 128) * 4 : 0;
+            aristos_status_t ps = ep_p2p_create(L->comm, rank, world, L->groups, in_bytes, (size_t)L->E * block_bytes,
+                                                aux_bytes, &L->p2p);
             if (ps == ARISTOS_OK) L->ffn_sm_limit = 0;      // nothing else needs SMs while rows travel
-            else if (tr && !strcmp(tr, "p2p")) { aristos_moe_destroy(L); return ps; }
+            else if (L->fp8 || (tr && !strcmp(tr, "p2p"))) { aristos_moe_destroy(L); return ps; }
         }
     }
     L->ws_bytes = plan_workspace(L, nullptr);
@@ -285,21 +296,48 @@ aristos_status_t aristos_moe_forward(aristos_moe_t* L, const void* x, const void
     PROF_MARK(1);
     ARISTOS_TRY(dispatch_impl(L->topk_idx, L->S, L->k, L->E, L->cap, L->count, L->slot_of, L->token_of_slot,
                               L->dispatch_scratch, L->dispatch_scratch_bytes, L->dev_status, st));
-    if (L->fp8) {
+    const size_t nb1 = (size_t)L->E_local * (L->I / 128) * (L->H / 128);
+    const bool swiglu = L->cfg.hidden_act == ARISTOS_ACT_SWIGLU;
+    const float* s1 = static_cast<const float*>(scales);
+    const float* s3 = (L->fp8 && swiglu) ? s1 + nb1 : nullptr;
+    const float* s2 = L->fp8 ? s1 + nb1 * (swiglu ? 2 : 1) : nullptr;
+    if (L->fp8 && L->world == 1) {
         // quantise the tokens per row and 128 elements, then gather codes and scales into expert-major order
         ARISTOS_TRY(aristos_quantize_fp8(x, 1, L->S, L->H, 1, ARISTOS_DTYPE_BF16, L->xq, L->sx, stream));
         ARISTOS_TRY(aristos_permute(L->xq, L->slot_of, L->S, L->k, L->H, ARISTOS_DTYPE_FP8_E4M3, L->xgq, st));
         ARISTOS_TRY(aristos_permute(L->sx, L->slot_of, L->S, L->k, L->H / 128, ARISTOS_DTYPE_F32, L->sxg, st));
+    } else if (L->fp8) {
+        // expert parallel: the gather stores every kept row (codes and scales) straight into the owner's memory, so
+        // only rows that exist cross NVLink (capacity = tokens would make padded blocks enormous)
+        PeerPtrs rows_dst, scales_dst, y_dst;
+        ep_p2p_peer_ptrs(L->p2p, EP_BUF_XR, rows_dst.p);
+        ep_p2p_peer_ptrs(L->p2p, EP_BUF_AUX, scales_dst.p);
+        ep_p2p_peer_ptrs(L->p2p, EP_BUF_YG, y_dst.p);
+        ep_p2p_begin(L->p2p);
+        ARISTOS_TRY(aristos_quantize_fp8(x, 1, L->S, L->H, 1, ARISTOS_DTYPE_BF16, L->xq, L->sx, stream));
+        ARISTOS_TRY(permute_rows_to_peers(L->xq, L->slot_of, L->S, L->k, (size_t)L->H, L->E_local, L->cap, L->rank,
+                                          rows_dst, st));
+        ARISTOS_TRY(permute_rows_to_peers(L->sx, L->slot_of, L->S, L->k, (size_t)(L->H / 128) * 4, L->E_local, L->cap,
+                                          L->rank, scales_dst, st));
+        ARISTOS_TRY(ep_p2p_push(L->p2p, EP_FLAG_COUNT, L->count, 1, (size_t)L->E_local * 4, 0, (size_t)L->E_local * 4, st));
+        ARISTOS_TRY(ep_p2p_signal(L->p2p, EP_FLAG_IN, 0, st));
+        PROF_MARK(2);
+        ARISTOS_TRY(ep_p2p_wait(L->p2p, EP_FLAG_IN, 0, st));
+        ARISTOS_TRY(aristos_expert_ffn_fp8(L->xgq, L->sxg, L->rcount, L->groups, L->cap, L->E_local, w1, s1, w3, s3, w2,
+                                           s2, L->h, L->hq, L->sh, L->yr, L->H, L->I, L->cfg.hidden_act, 0, L->cap, 0,
+                                           L->dev_status, st));
+        ARISTOS_TRY(return_rows_to_peers(L->yr, L->rcount, L->groups, L->E_local, L->cap, (size_t)L->H * 2, L->rank,
+                                         y_dst, st));
+        ARISTOS_TRY(ep_p2p_signal(L->p2p, EP_FLAG_RET, 0, st));
+        ARISTOS_TRY(ep_p2p_wait(L->p2p, EP_FLAG_RET, 0, st));
     } else {
         ARISTOS_TRY(aristos_permute(x, L->slot_of, L->S, L->k, L->H, dt, L->xg, st));
     }
-    PROF_MARK(2);
+    if (!(L->fp8 && L->world > 1)) PROF_MARK(2);
 
-    if (L->fp8) {
-        const size_t nb1 = (size_t)L->E * (L->I / 128) * (L->H / 128);
-        const float* s1 = static_cast<const float*>(scales);
-        const float* s3 = L->cfg.hidden_act == ARISTOS_ACT_SWIGLU ? s1 + nb1 : nullptr;
-        const float* s2 = s1 + nb1 * (L->cfg.hidden_act == ARISTOS_ACT_SWIGLU ? 2 : 1);
+    if (L->fp8 && L->world > 1) {
+        // done above
+    } else if (L->fp8) {
         ARISTOS_TRY(aristos_expert_ffn_fp8(L->xgq, L->sxg, L->count, L->E, L->cap, L->E, w1, s1, w3, s3, w2, s2, L->h,
                                            L->hq, L->sh, L->yr, L->H, L->I, L->cfg.hidden_act, 0, L->cap, 0,
                                            L->dev_status, st));

@@ -141,7 +141,8 @@ ARISTOS_API aristos_status_t aristos_moe_set_bias(aristos_moe_t* layer, const vo
  *   w2 (E_local,H,I)             scales: fp8 only, else NULL          out (S,H), same dtype as x
  * torch_dtype 4 (fp8): x and out are bf16 (activations are quantised inside, per token and 128 elements); w1 / w3 /
  * w2 are e4m3; scales = fp32 [s1 (E_local, I/128, H/128) | s3 (same, SwiGLU only) | s2 (E_local, H/128, I/128)],
- * contiguous, as aristos_quantize_fp8(block_rows = 128) writes them. Single rank only in this build.
+ * contiguous, as aristos_quantize_fp8(block_rows = 128) writes them. Across ranks the fp8 layer needs the "p2p"
+ * transport (the gather stores quantised rows and scales straight into the owning rank's memory).
  * E_local = num_experts / world; rank r owns experts [r*E_local, (r+1)*E_local). Dropped tokens give zero rows.
  */
 ARISTOS_API aristos_status_t aristos_moe_forward(aristos_moe_t* layer, const void* x, const void* w_gate,

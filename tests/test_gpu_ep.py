@@ -93,3 +93,81 @@ def test_expert_parallel_2gpu_four_windows(transport):
 @pytest.mark.parametrize("transport", TRANSPORTS)
 def test_expert_parallel_4gpu(transport):
     _run(4, S=1024, H=256, I=256, E=8, k=2, cf=1.0, act=0, transport=transport)
+
+
+def _worker_fp8(rank, world, uid, S, H, I, E, k, q):
+    try:
+        os.environ["ARISTOS_EP_TRANSPORT"] = "p2p"
+        sys.path.insert(0, ROOT)
+        sys.path.insert(0, os.path.join(ROOT, "tests"))
+        import torch
+        from helpers import TOL_BF16_MAX, TOL_BF16_MEAN, make_inputs, rel_errors, to_dev
+        from oracle import moe_oracle as O
+        import cuplayground_b200 as cp
+        import cuplayground_b200.layer as layer
+
+        torch.cuda.set_device(rank)
+        El = E // world
+        dt = torch.bfloat16
+        _, wg, w1, w3, w2 = make_inputs(S, H, I, E, seed=100, swiglu=True, w_std=0.05)     # shared weights
+        x = make_inputs(S, H, I, E, seed=200 + rank, w_std=0.05)[0]                        # this rank's tokens
+        # every rank quantises the global weights the same way (per expert, per 128x128 block) and keeps its shard
+        q1, s1 = layer.quantize_fp8(to_dev(w1, dt), 128)
+        q3, s3 = layer.quantize_fp8(to_dev(w3, dt), 128)
+        q2, s2 = layer.quantize_fp8(to_dev(w2, dt), 128)
+        loc = slice(rank * El, (rank + 1) * El)
+        scales = torch.cat([t[loc].reshape(-1) for t in (s1, s3, s2)]).contiguous()
+        cfg = cp.AristosConfig(drop_tokens=0, expert_top_k=k, hidden_act=2, hidden_size=H, intermediate_size=I,
+                               num_experts=E, torch_dtype=4, tokens=S, gate_fn=1, renorm_topk=1, ep_world=world)
+        L = layer.MoELayer(cfg, rank, world, uid)
+        assert L.ep_transport == "p2p"
+        xd = to_dev(x, dt)
+        args = (xd, to_dev(wg, dt), q1[loc].contiguous(), q3[loc].contiguous(), q2[loc].contiguous())
+        out = L.forward(*args, scales=scales)
+        L.status()
+        out2 = L.forward(*args, scales=scales)
+        L.status()
+        assert torch.equal(out, out2)
+        r = L.routing()
+        xq, sx = layer.quantize_fp8(xd, 1)
+        host = lambda t: t.cpu().numpy()
+        dq = lambda qq, ss, b: O.dequantize_fp8(host(qq), host(ss), b)
+        ref = O.moe_forward(x, wg, dq(q1, s1, 128), dq(q3, s3, 128), dq(q2, s2, 128), k=k, cap=cfg.capacity, gate_fn=1,
+                            renorm=1, hidden_act=2, x_ffn=dq(xq, sx, 1), round_h=2)
+        for name in ("topk_idx", "count", "slot_of", "token_of_slot"):
+            assert np.array_equal(r[name].numpy(), ref[name]), name
+        mx, mean = rel_errors(out.float().cpu().numpy(), ref["out"])
+        assert mx < TOL_BF16_MAX and mean < TOL_BF16_MEAN, (mx, mean)
+        L.close()
+        q.put((rank, "ok"))
+    except Exception as e:      # pragma: no cover - reported to the parent
+        import traceback
+        q.put((rank, "".join(traceback.format_exception(e))))
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_expert_parallel_fp8(world):
+    """FP8 layer across ranks: the gather stores quantised rows and scales straight into the owning rank's memory,
+    outputs return row by row; drop-free routing (capacity = tokens), top-4 sigmoid gate."""
+    import torch
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    import torch.multiprocessing as mp
+    import cuplayground_b200.layer as layer
+    uid = layer.nccl_unique_id()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker_fp8, args=(r, world, uid, 640, 512, 256, 16, 4, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = []
+    try:
+        for _ in procs:
+            results.append(q.get(timeout=300))
+    finally:
+        for p in procs:
+            p.join(timeout=30)
+            if p.is_alive():
+                p.kill()
+    bad = [r for r in results if r[1] != "ok"]
+    assert not bad, bad[0][1]
