@@ -60,6 +60,7 @@ struct aristos_moe {
     cudaEvent_t ev_dispatched = nullptr, ev_returned = nullptr;
     std::vector<cudaEvent_t> ev_in, ev_out;
     int chunks = 1, chunk_rows = 0, ffn_sm_limit = 0;
+    bool ep_direct = false;                  // p2p: gather/return kernels store through peer pointers (no row windows)
     int64_t launches = 0;
     const void *b1 = nullptr, *b3 = nullptr, *b2 = nullptr;   // optional expert biases (caller-owned, device)
     // stage stopwatch
@@ -229,7 +230,13 @@ aristos_status_t aristos_moe_create(const aristos_config_t* cfg, int rank, int w
             const size_t aux_bytes = L->fp8 ? (size_t)L->groups * L->cap * (L->H / 128) * 4 : 0;
             aristos_status_t ps = ep_p2p_create(L->comm, rank, world, L->groups, in_bytes, (size_t)L->E * block_bytes,
                                                 aux_bytes, &L->p2p);
-            if (ps == ARISTOS_OK) L->ffn_sm_limit = 0;      // nothing else needs SMs while rows travel
+            if (ps == ARISTOS_OK) {
+                L->ffn_sm_limit = 0;      // nothing else needs SMs while rows travel
+                // default: the gather / return kernels store through peer pointers; ARISTOS_EP_MODE=windows selects
+                // the copy-engine pipeline over padded row windows instead
+                const char* mode = getenv("ARISTOS_EP_MODE");
+                L->ep_direct = !(mode && !strcmp(mode, "windows"));
+            }
             else if (L->fp8 || (tr && !strcmp(tr, "p2p"))) { aristos_moe_destroy(L); return ps; }
         }
     }
@@ -330,7 +337,7 @@ aristos_status_t aristos_moe_forward(aristos_moe_t* L, const void* x, const void
                                          y_dst, st));
         ARISTOS_TRY(ep_p2p_signal(L->p2p, EP_FLAG_RET, 0, st));
         ARISTOS_TRY(ep_p2p_wait(L->p2p, EP_FLAG_RET, 0, st));
-    } else {
+    } else if (!(L->p2p && L->ep_direct)) {
         ARISTOS_TRY(aristos_permute(x, L->slot_of, L->S, L->k, L->H, dt, L->xg, st));
     }
     if (!(L->fp8 && L->world > 1)) PROF_MARK(2);
@@ -344,6 +351,24 @@ aristos_status_t aristos_moe_forward(aristos_moe_t* L, const void* x, const void
     } else if (L->world == 1) {
         ARISTOS_TRY(aristos_expert_ffn_bias(L->xg, L->count, L->E, L->cap, L->E, w1, w3, w2, L->b1, L->b3, L->b2, L->h, L->yr, L->H, L->I,
                                        L->cfg.hidden_act, dt, 0, L->cap, 0, L->dev_status, st));
+    } else if (L->p2p && L->ep_direct) {
+        // the gather IS the dispatch all-to-all: every kept row is stored straight into its expert's rank, the expert
+        // outputs come back the same way; only rows that exist travel, one GEMM pair, no row windows
+        PeerPtrs rows_dst, y_dst;
+        ep_p2p_peer_ptrs(L->p2p, EP_BUF_XR, rows_dst.p);
+        ep_p2p_peer_ptrs(L->p2p, EP_BUF_YG, y_dst.p);
+        const size_t row_bytes = (size_t)L->H * L->elt;
+        ep_p2p_begin(L->p2p);
+        ARISTOS_TRY(permute_rows_to_peers(x, L->slot_of, L->S, L->k, row_bytes, L->E_local, L->cap, L->rank, rows_dst, st));
+        ARISTOS_TRY(ep_p2p_push(L->p2p, EP_FLAG_COUNT, L->count, 1, (size_t)L->E_local * 4, 0, (size_t)L->E_local * 4, st));
+        ARISTOS_TRY(ep_p2p_signal(L->p2p, EP_FLAG_IN, 0, st));
+        ARISTOS_TRY(ep_p2p_wait(L->p2p, EP_FLAG_IN, 0, st));
+        ARISTOS_TRY(aristos_expert_ffn_bias(L->xr, L->rcount, L->groups, L->cap, L->E_local, w1, w3, w2, L->b1, L->b3,
+                                            L->b2, L->h, L->yr, L->H, L->I, L->cfg.hidden_act, dt, 0, L->cap, 0,
+                                            L->dev_status, st));
+        ARISTOS_TRY(return_rows_to_peers(L->yr, L->rcount, L->groups, L->E_local, L->cap, row_bytes, L->rank, y_dst, st));
+        ARISTOS_TRY(ep_p2p_signal(L->p2p, EP_FLAG_RET, 0, st));
+        ARISTOS_TRY(ep_p2p_wait(L->p2p, EP_FLAG_RET, 0, st));
     } else if (L->p2p) {
         // rows are pushed into the destination GPUs by the copy engines; flags + stream waits order the streams
         const size_t row_bytes = (size_t)L->H * L->elt;

@@ -13,7 +13,9 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 def _worker(rank, world, uid, S, H, I, E, k, cf, act, transport, q):
     try:
-        os.environ["ARISTOS_EP_TRANSPORT"] = transport
+        os.environ["ARISTOS_EP_TRANSPORT"] = transport.split("-")[0]
+        os.environ["ARISTOS_EP_MODE"] = "windows" if transport.endswith("-windows") else "direct"
+        transport = transport.split("-")[0]
         sys.path.insert(0, ROOT)
         sys.path.insert(0, os.path.join(ROOT, "tests"))
         import torch
@@ -77,7 +79,9 @@ def _run(world, S, H, I, E, k, cf, act, transport):
     assert not bad, bad[0][1]
 
 
-TRANSPORTS = ["p2p", "nccl"]     # copy-engine pushes into peer memory (default) and NCCL send/recv
+# peer memory with gather/return kernels storing through peer pointers (default), peer memory with copy-engine
+# pushes of padded row windows, and NCCL send/recv
+TRANSPORTS = ["p2p", "p2p-windows", "nccl"]
 
 
 @pytest.mark.parametrize("transport", TRANSPORTS)
