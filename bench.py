@@ -109,7 +109,7 @@ def layer_flops(cfg, kept_assignments: int) -> float:
 
 
 def layer_roofline(cfg, world, kept, elt=2):
-    """The layer roofline of the build spec: the slowest of FLOPs at the dense tensor peak, minimum HBM bytes at
+    """The layer roofline: the slowest of FLOPs at the dense tensor peak, minimum HBM bytes at
     8 TB/s and all-to-all bytes at 900 GB/s per direction (dispatch and return summed). Seconds per rank."""
     m = 3 if cfg.hidden_act == 2 else 2
     H, I, E, S = cfg.hidden_size, cfg.intermediate_size, cfg.num_experts, cfg.S

@@ -73,7 +73,8 @@ class AristosConfig:
 
 
 def baseline_config(n: int, world: int = 1) -> AristosConfig:
-    """The five benchmark configurations (1-based, as listed in BASELINE.json)."""
+    """The five benchmark configurations (1-based): fp32 reference case, single-GPU GELU, Mixtral-shaped SwiGLU,
+    DeepSeek-V3-shaped FP8, skewed routing."""
     if n == 1:
         return AristosConfig(capacity_factor=1.0, drop_tokens=1, expert_top_k=1, hidden_act=0, hidden_size=256,
                              intermediate_size=512, num_experts=8, torch_dtype=0, tokens=128, seed=0, ep_world=world)

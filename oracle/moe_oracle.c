@@ -92,7 +92,7 @@ ORC_API void orc_round_bf16(float* v, int64_t n) {
 
 /* ---------------------------------------------------------------------------------------------------------------
  * Capacity. cap = ceil(cf*S*k/E) when tokens are dropped on overflow, else S (an expert can receive a token at
- * most once, so S rows always suffice). Config 1 of the build spec pins cap = S/E for k = 1, cf = 1.
+ * most once, so S rows always suffice). The fp32 reference case (S=128, E=8, k=1, cf=1) gives cap = S/E = 16.
  * ------------------------------------------------------------------------------------------------------------- */
 ORC_API int orc_capacity(int S, int E, int k, double cf, int drop_tokens) {
     if (!drop_tokens) return S;

@@ -36,6 +36,6 @@ def rel_errors(got: np.ndarray, ref: np.ndarray):
     return float(d.max() / max(np.abs(ref).max(), 1e-30)), float(d.mean() / max(np.abs(ref).mean(), 1e-30))
 
 
-# tolerances of the build spec
+# output tolerances: fp32 1e-4 relative; 16-bit and fp8 2e-2 max-relative, 1e-2 mean-relative
 TOL_F32_MAX = 1e-4
 TOL_BF16_MAX, TOL_BF16_MEAN = 2e-2, 1e-2
