@@ -14,11 +14,12 @@ namespace aristos {
 namespace {
 
 // Token-major gather into the owners' buffers: assignment (t, j) with slot e*cap + pos goes to rank e / E_local, row
-// ((src_rank*E_local + e % E_local)*cap + pos) of that rank's buffer. One warp per token, 16-byte lanes.
+// ((src_rank*E_local + e % E_local)*cap + pos) of that rank's buffer; only positions in [pos_lo, pos_hi) are handled
+// (one row window of the pipeline). One warp per token, 16-byte lanes.
 template <int MAXK>
 __global__ void __launch_bounds__(256)
 permute_rows_peer_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ slot_of, int S, int k, int row_vec,
-                         int E_local, int cap, int src_rank, PeerPtrs dst) {
+                         int E_local, int cap, int src_rank, int pos_lo, int pos_hi, PeerPtrs dst) {
     const int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (t >= S) return;
     uint4* rows[MAXK];
@@ -30,7 +31,8 @@ permute_rows_peer_kernel(const uint4* __restrict__ x, const int32_t* __restrict_
             if (slot >= 0) {
                 const int e = slot / cap, pos = slot - e * cap;
                 const int owner = e / E_local, el = e - owner * E_local;
-                rows[j] = static_cast<uint4*>(dst.p[owner]) + ((size_t)(src_rank * E_local + el) * cap + pos) * row_vec;
+                if (pos >= pos_lo && pos < pos_hi)
+                    rows[j] = static_cast<uint4*>(dst.p[owner]) + ((size_t)(src_rank * E_local + el) * cap + pos) * row_vec;
             }
         }
     }
@@ -45,10 +47,10 @@ permute_rows_peer_kernel(const uint4* __restrict__ x, const int32_t* __restrict_
 
 // Valid rows of y (groups = source rank x local expert, cap rows each, count[g] valid) back to their source ranks:
 // row (g, r) goes to rank g / E_local, row ((this_rank*E_local + g % E_local)*cap + r) of its buffer. A persistent
-// grid walks the flattened list of valid rows through a prefix over the counts.
+// grid walks the flattened list of valid rows (of the row window [row_lo, row_hi)) through a prefix over the counts.
 __global__ void __launch_bounds__(256)
 return_rows_peer_kernel(const uint4* __restrict__ y, const int32_t* __restrict__ count, int groups, int E_local,
-                        int cap, int row_vec, int this_rank, PeerPtrs dst) {
+                        int cap, int row_vec, int this_rank, int row_lo, int row_hi, PeerPtrs dst) {
     __shared__ int s_prefix[1025];
     if (threadIdx.x < 32) {
         const int lane = threadIdx.x;
@@ -56,7 +58,7 @@ return_rows_peer_kernel(const uint4* __restrict__ y, const int32_t* __restrict__
         if (lane == 0) s_prefix[0] = 0;
         for (int g0 = 0; g0 < groups; g0 += 32) {
             const int g = g0 + lane;
-            int v = g < groups ? min(max(count[g], 0), cap) : 0;
+            int v = g < groups ? min(max(min(count[g], cap) - row_lo, 0), row_hi - row_lo) : 0;
 #pragma unroll
             for (int d = 1; d < 32; d <<= 1) {
                 const int o = __shfl_up_sync(0xffffffffu, v, d);
@@ -76,7 +78,7 @@ return_rows_peer_kernel(const uint4* __restrict__ y, const int32_t* __restrict__
             const int mid = (lo + hi) >> 1;
             if (s_prefix[mid] <= vrow) lo = mid; else hi = mid;
         }
-        const int g = lo, r = vrow - s_prefix[lo];
+        const int g = lo, r = row_lo + vrow - s_prefix[lo];
         const int owner = g / E_local, el = g - owner * E_local;
         const uint4* src = y + ((size_t)g * cap + r) * row_vec;
         uint4* out = static_cast<uint4*>(dst.p[owner]) + ((size_t)(this_rank * E_local + el) * cap + r) * row_vec;
@@ -87,27 +89,29 @@ return_rows_peer_kernel(const uint4* __restrict__ y, const int32_t* __restrict__
 }  // namespace
 
 aristos_status_t permute_rows_to_peers(const void* x, const int32_t* slot_of, int S, int k, size_t row_bytes,
-                                       int E_local, int cap, int src_rank, const PeerPtrs& dst, cudaStream_t st) {
+                                       int E_local, int cap, int src_rank, int pos_lo, int pos_hi, const PeerPtrs& dst,
+                                       cudaStream_t st) {
     if (row_bytes % 16 != 0 || k > 16) { set_last_error("peer gather: row bytes must be a multiple of 16, k <= 16"); return ARISTOS_ERR_INVALID_ARG; }
     if (S == 0) return ARISTOS_OK;
     const int row_vec = (int)(row_bytes / 16);
     const int grid = ceil_div(S, 8);
     const uint4* xs = static_cast<const uint4*>(x);
-    if (k <= 2) permute_rows_peer_kernel<2><<<grid, 256, 0, st>>>(xs, slot_of, S, k, row_vec, E_local, cap, src_rank, dst);
-    else if (k <= 4) permute_rows_peer_kernel<4><<<grid, 256, 0, st>>>(xs, slot_of, S, k, row_vec, E_local, cap, src_rank, dst);
-    else if (k <= 8) permute_rows_peer_kernel<8><<<grid, 256, 0, st>>>(xs, slot_of, S, k, row_vec, E_local, cap, src_rank, dst);
-    else permute_rows_peer_kernel<16><<<grid, 256, 0, st>>>(xs, slot_of, S, k, row_vec, E_local, cap, src_rank, dst);
+    if (k <= 2) permute_rows_peer_kernel<2><<<grid, 256, 0, st>>>(xs, slot_of, S, k, row_vec, E_local, cap, src_rank, pos_lo, pos_hi, dst);
+    else if (k <= 4) permute_rows_peer_kernel<4><<<grid, 256, 0, st>>>(xs, slot_of, S, k, row_vec, E_local, cap, src_rank, pos_lo, pos_hi, dst);
+    else if (k <= 8) permute_rows_peer_kernel<8><<<grid, 256, 0, st>>>(xs, slot_of, S, k, row_vec, E_local, cap, src_rank, pos_lo, pos_hi, dst);
+    else permute_rows_peer_kernel<16><<<grid, 256, 0, st>>>(xs, slot_of, S, k, row_vec, E_local, cap, src_rank, pos_lo, pos_hi, dst);
     ARISTOS_COUNT_LAUNCH();
     ARISTOS_CUDA_TRY(cudaGetLastError());
     return ARISTOS_OK;
 }
 
 aristos_status_t return_rows_to_peers(const void* y, const int32_t* count, int groups, int E_local, int cap,
-                                      size_t row_bytes, int this_rank, const PeerPtrs& dst, cudaStream_t st) {
+                                      size_t row_bytes, int this_rank, int row_lo, int row_hi, const PeerPtrs& dst,
+                                      cudaStream_t st) {
     if (row_bytes % 16 != 0 || groups > 1024) { set_last_error("peer return: bad row size or too many groups"); return ARISTOS_ERR_INVALID_ARG; }
     if (groups == 0) return ARISTOS_OK;
     return_rows_peer_kernel<<<device_sm_count() * 2, 256, 0, st>>>(static_cast<const uint4*>(y), count, groups, E_local,
-                                                                   cap, (int)(row_bytes / 16), this_rank, dst);
+                                                                   cap, (int)(row_bytes / 16), this_rank, row_lo, row_hi, dst);
     ARISTOS_COUNT_LAUNCH();
     ARISTOS_CUDA_TRY(cudaGetLastError());
     return ARISTOS_OK;

@@ -13,11 +13,15 @@ struct PeerPtrs {
     void* p[16];   // rank r's copy of one exchange buffer, as mapped into this process
 };
 
-// xg-less dispatch: token row t goes, for each kept assignment, into the buffer of the rank that owns the expert.
+// Dispatch without a staging buffer: token row t goes, for each kept assignment whose position inside its expert lies
+// in [pos_lo, pos_hi), into the buffer of the rank that owns the expert.
 aristos_status_t permute_rows_to_peers(const void* x, const int32_t* slot_of, int S, int k, size_t row_bytes,
-                                       int E_local, int cap, int src_rank, const PeerPtrs& dst, cudaStream_t st);
-// Valid rows of the local expert outputs (groups x cap rows, count[g] valid) back into their source ranks' buffers.
+                                       int E_local, int cap, int src_rank, int pos_lo, int pos_hi, const PeerPtrs& dst,
+                                       cudaStream_t st);
+// Valid rows [row_lo, row_hi) of the local expert outputs (groups x cap rows, count[g] valid) back into their source
+// ranks' buffers.
 aristos_status_t return_rows_to_peers(const void* y, const int32_t* count, int groups, int E_local, int cap,
-                                      size_t row_bytes, int this_rank, const PeerPtrs& dst, cudaStream_t st);
+                                      size_t row_bytes, int this_rank, int row_lo, int row_hi, const PeerPtrs& dst,
+                                      cudaStream_t st);
 
 }  // namespace aristos

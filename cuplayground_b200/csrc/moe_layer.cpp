@@ -60,7 +60,8 @@ struct aristos_moe {
     cudaEvent_t ev_dispatched = nullptr, ev_returned = nullptr;
     std::vector<cudaEvent_t> ev_in, ev_out;
     int chunks = 1, chunk_rows = 0, ffn_sm_limit = 0;
-    bool ep_direct = false;                  // p2p: gather/return kernels store through peer pointers (no row windows)
+    bool ep_direct = false;                  // p2p: gather/return kernels store through peer pointers
+    int direct_windows = 1;                  // row windows of the direct mode (gather / GEMMs / return pipelined)
     int64_t launches = 0;
     const void *b1 = nullptr, *b3 = nullptr, *b2 = nullptr;   // optional expert biases (caller-owned, device)
     // stage stopwatch
@@ -236,6 +237,12 @@ aristos_status_t aristos_moe_create(const aristos_config_t* cfg, int rank, int w
                 // the copy-engine pipeline over padded row windows instead
                 const char* mode = getenv("ARISTOS_EP_MODE");
                 L->ep_direct = !(mode && !strcmp(mode, "windows"));
+                // one window by default: on two GPUs, splitting the GEMMs to hide the transfers behind them measured
+                // slower (10.5 ms, 10.5 ms, 10.8 ms of device time for 1, 2, 4 windows at 8192 tokens x 8 experts)
+                L->direct_windows = 1;
+                if (const char* env = getenv("ARISTOS_EP_DIRECT_WINDOWS"))
+                    if (atoi(env) >= 1) L->direct_windows = atoi(env);
+                L->direct_windows = std::min(L->direct_windows, (int)L->ev_out.size());
             }
             else if (L->fp8 || (tr && !strcmp(tr, "p2p"))) { aristos_moe_destroy(L); return ps; }
         }
@@ -322,10 +329,10 @@ aristos_status_t aristos_moe_forward(aristos_moe_t* L, const void* x, const void
         ep_p2p_peer_ptrs(L->p2p, EP_BUF_YG, y_dst.p);
         ep_p2p_begin(L->p2p);
         ARISTOS_TRY(aristos_quantize_fp8(x, 1, L->S, L->H, 1, ARISTOS_DTYPE_BF16, L->xq, L->sx, stream));
-        ARISTOS_TRY(permute_rows_to_peers(L->xq, L->slot_of, L->S, L->k, (size_t)L->H, L->E_local, L->cap, L->rank,
-                                          rows_dst, st));
+        ARISTOS_TRY(permute_rows_to_peers(L->xq, L->slot_of, L->S, L->k, (size_t)L->H, L->E_local, L->cap, L->rank, 0,
+                                          L->cap, rows_dst, st));
         ARISTOS_TRY(permute_rows_to_peers(L->sx, L->slot_of, L->S, L->k, (size_t)(L->H / 128) * 4, L->E_local, L->cap,
-                                          L->rank, scales_dst, st));
+                                          L->rank, 0, L->cap, scales_dst, st));
         ARISTOS_TRY(ep_p2p_push(L->p2p, EP_FLAG_COUNT, L->count, 1, (size_t)L->E_local * 4, 0, (size_t)L->E_local * 4, st));
         ARISTOS_TRY(ep_p2p_signal(L->p2p, EP_FLAG_IN, 0, st));
         PROF_MARK(2);
@@ -333,8 +340,8 @@ aristos_status_t aristos_moe_forward(aristos_moe_t* L, const void* x, const void
         ARISTOS_TRY(aristos_expert_ffn_fp8(L->xgq, L->sxg, L->rcount, L->groups, L->cap, L->E_local, w1, s1, w3, s3, w2,
                                            s2, L->h, L->hq, L->sh, L->yr, L->H, L->I, L->cfg.hidden_act, 0, L->cap, 0,
                                            L->dev_status, st));
-        ARISTOS_TRY(return_rows_to_peers(L->yr, L->rcount, L->groups, L->E_local, L->cap, (size_t)L->H * 2, L->rank,
-                                         y_dst, st));
+        ARISTOS_TRY(return_rows_to_peers(L->yr, L->rcount, L->groups, L->E_local, L->cap, (size_t)L->H * 2, L->rank, 0,
+                                         L->cap, y_dst, st));
         ARISTOS_TRY(ep_p2p_signal(L->p2p, EP_FLAG_RET, 0, st));
         ARISTOS_TRY(ep_p2p_wait(L->p2p, EP_FLAG_RET, 0, st));
     } else if (!(L->p2p && L->ep_direct)) {
@@ -353,22 +360,41 @@ aristos_status_t aristos_moe_forward(aristos_moe_t* L, const void* x, const void
                                        L->cfg.hidden_act, dt, 0, L->cap, 0, L->dev_status, st));
     } else if (L->p2p && L->ep_direct) {
         // the gather IS the dispatch all-to-all: every kept row is stored straight into its expert's rank, the expert
-        // outputs come back the same way; only rows that exist travel, one GEMM pair, no row windows
+        // outputs come back the same way; only rows that exist travel. The light gather / return kernels run on the
+        // communication stream and share the SMs with the persistent GEMM grid, window by window.
         PeerPtrs rows_dst, y_dst;
         ep_p2p_peer_ptrs(L->p2p, EP_BUF_XR, rows_dst.p);
         ep_p2p_peer_ptrs(L->p2p, EP_BUF_YG, y_dst.p);
         const size_t row_bytes = (size_t)L->H * L->elt;
+        const int nwin = L->direct_windows;
+        const int win_rows = ceil_div(ceil_div(L->cap, nwin), 256) * 256;
         ep_p2p_begin(L->p2p);
-        ARISTOS_TRY(permute_rows_to_peers(x, L->slot_of, L->S, L->k, row_bytes, L->E_local, L->cap, L->rank, rows_dst, st));
-        ARISTOS_TRY(ep_p2p_push(L->p2p, EP_FLAG_COUNT, L->count, 1, (size_t)L->E_local * 4, 0, (size_t)L->E_local * 4, st));
-        ARISTOS_TRY(ep_p2p_signal(L->p2p, EP_FLAG_IN, 0, st));
-        ARISTOS_TRY(ep_p2p_wait(L->p2p, EP_FLAG_IN, 0, st));
-        ARISTOS_TRY(aristos_expert_ffn_bias(L->xr, L->rcount, L->groups, L->cap, L->E_local, w1, w3, w2, L->b1, L->b3,
-                                            L->b2, L->h, L->yr, L->H, L->I, L->cfg.hidden_act, dt, 0, L->cap, 0,
-                                            L->dev_status, st));
-        ARISTOS_TRY(return_rows_to_peers(L->yr, L->rcount, L->groups, L->E_local, L->cap, row_bytes, L->rank, y_dst, st));
-        ARISTOS_TRY(ep_p2p_signal(L->p2p, EP_FLAG_RET, 0, st));
-        ARISTOS_TRY(ep_p2p_wait(L->p2p, EP_FLAG_RET, 0, st));
+        ARISTOS_CUDA_TRY(cudaEventRecord(L->ev_dispatched, st));
+        ARISTOS_CUDA_TRY(cudaStreamWaitEvent(L->comm_stream, L->ev_dispatched, 0));
+        ARISTOS_TRY(ep_p2p_push(L->p2p, EP_FLAG_COUNT, L->count, 1, (size_t)L->E_local * 4, 0, (size_t)L->E_local * 4,
+                                L->comm_stream));
+        for (int c = 0; c < nwin; ++c) {
+            const int r0 = c * win_rows, r1 = std::min(L->cap, r0 + win_rows);
+            if (r0 >= r1) break;
+            ARISTOS_TRY(permute_rows_to_peers(x, L->slot_of, L->S, L->k, row_bytes, L->E_local, L->cap, L->rank, r0, r1,
+                                              rows_dst, L->comm_stream));
+            ARISTOS_TRY(ep_p2p_signal(L->p2p, EP_FLAG_IN, c, L->comm_stream));
+        }
+        for (int c = 0; c < nwin; ++c) {
+            const int r0 = c * win_rows, r1 = std::min(L->cap, r0 + win_rows);
+            if (r0 >= r1) break;
+            ARISTOS_TRY(ep_p2p_wait(L->p2p, EP_FLAG_IN, c, st));
+            ARISTOS_TRY(aristos_expert_ffn_bias(L->xr, L->rcount, L->groups, L->cap, L->E_local, w1, w3, w2, L->b1,
+                                                L->b3, L->b2, L->h, L->yr, L->H, L->I, L->cfg.hidden_act, dt, r0, r1, 0,
+                                                L->dev_status, st));
+            ARISTOS_CUDA_TRY(cudaEventRecord(L->ev_out[c], st));
+            ARISTOS_CUDA_TRY(cudaStreamWaitEvent(L->comm_stream, L->ev_out[c], 0));
+            ARISTOS_TRY(return_rows_to_peers(L->yr, L->rcount, L->groups, L->E_local, L->cap, row_bytes, L->rank, r0, r1,
+                                             y_dst, L->comm_stream));
+            ARISTOS_TRY(ep_p2p_signal(L->p2p, EP_FLAG_RET, c, L->comm_stream));
+        }
+        for (int c = 0; c < nwin; ++c)
+            if (c * win_rows < L->cap) ARISTOS_TRY(ep_p2p_wait(L->p2p, EP_FLAG_RET, c, st));
     } else if (L->p2p) {
         // rows are pushed into the destination GPUs by the copy engines; flags + stream waits order the streams
         const size_t row_bytes = (size_t)L->H * L->elt;
