@@ -7,7 +7,7 @@
 //
 // Bit-exact contract (mirrored by the CPU oracle): for a token t and expert e there are 32 x 2 partial sums;
 //   p[c][h % 2] = fmaf(x[t,h], Wg[e,h], p[c][h % 2])   over the 8-element chunks q = h/8 with q % 32 == c, in
-// increasing h (even and odd elements accumulate separately: that is one packed two-lane FMA per bf16 pair), then
+// increasing h (even and odd elements accumulate separately, so fp32 rows take one packed two-lane FMA per pair), then
 // P[c] = p[c][0] + p[c][1], the 32 values P[c] are combined by the xor butterfly 16, 8, 4, 2, 1
 // (P[c] = P[c] + P[c ^ m]) and the bias is added last. Products of bf16 values are exact in fp32 and every step is
 // one IEEE operation, so the logits do not depend on the launch geometry and the CPU reproduces them bit for bit.
@@ -16,8 +16,10 @@
 //
 // Kernel shape: a CTA of 16 warps owns a tile of tokens x experts; H is walked in slabs of 256 elements that are
 // staged in shared memory with cp.async (three stages), lane c of every warp reads chunk c of a slab row, so lane c
-// holds the partial sums c of its warp's 4-token x 8-expert register tile (packed fp32x2 FMAs: half the issue slots
-// of scalar FMAs). The butterfly is done as a reduce-scatter
+// holds the partial sums c of its warp's 4-token x 8-expert register tile. fp32 rows use packed fp32x2 FMAs (half the
+// issue slots of scalar FMAs); bf16 / fp16 rows use the mixed-precision FMA on the raw 16-bit operands (fp32
+// accumulator, one rounding: the same bits as converting first), so nothing is unpacked on the integer pipe.
+// The butterfly is done as a reduce-scatter
 // (each step keeps half of the tile, 31 shuffles instead of 160): adding the same two operands, it gives the same
 // bits as the full butterfly. With few experts the kernel streams x once from HBM; with many it is FMA-bound.
 #include "common.cuh"
