@@ -12,8 +12,8 @@ __all__ = ["AristosConfig", "AristosError", "baseline_config", "_lib"]
 
 def __getattr__(name):
     # torch-dependent pieces are imported on first use so that config parsing works without importing torch
-    if name in ("MoELayer", "layer", "gate_topk", "dispatch", "permute", "expert_ffn", "combine", "fill_normal",
-                "nccl_unique_id"):
+    if name in ("MoELayer", "layer", "gate_topk", "gate_topk_screened", "dispatch", "permute", "expert_ffn", "combine",
+                "fill_normal", "nccl_unique_id"):
         from . import layer as _layer
         return _layer if name == "layer" else getattr(_layer, name)
     raise AttributeError(name)

@@ -14,7 +14,7 @@ OK = 0
 STATUS_NAMES = {0: "ARISTOS_OK", 1: "ARISTOS_ERR_INVALID_ARG", 2: "ARISTOS_ERR_CONFIG", 3: "ARISTOS_ERR_IO",
                 4: "ARISTOS_ERR_CUDA", 5: "ARISTOS_ERR_NCCL", 6: "ARISTOS_ERR_UNSUPPORTED",
                 7: "ARISTOS_ERR_WORKSPACE", 8: "ARISTOS_ERR_DEVICE_TIMEOUT", 9: "ARISTOS_ERR_DEVICE_BOUNDS",
-                10: "ARISTOS_ERR_NOMEM"}
+                10: "ARISTOS_ERR_NOMEM", 11: "ARISTOS_ERR_GATE_SCREEN"}
 
 DTYPE_F32, DTYPE_TF32, DTYPE_BF16, DTYPE_F16, DTYPE_FP8_E4M3 = 0, 1, 2, 3, 4
 ACT_RELU, ACT_GELU, ACT_SWIGLU, ACT_IDENTITY = 0, 1, 2, 3
@@ -77,6 +77,8 @@ PROTOTYPES = {
     "aristos_moe_launch_count": (C.c_int64, [_vp]),
     "aristos_moe_destroy": (_st, [_vp]),
     "aristos_gate_topk": (_st, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
+    "aristos_gate_scratch_bytes": (_sz, [_i, _i]),
+    "aristos_gate_topk_screened": (_st, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _sz, _vp, _vp]),
     "aristos_dispatch_scratch_bytes": (_sz, [_i, _i, _i]),
     "aristos_dispatch": (_st, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _sz, _vp]),
     "aristos_dispatch_static": (_st, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),

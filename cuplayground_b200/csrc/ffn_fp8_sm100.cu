@@ -19,6 +19,7 @@
 
 #include "common.cuh"
 #include "ptx_sm100.cuh"
+#include "tensor_map.cuh"
 
 namespace aristos {
 
@@ -405,39 +406,10 @@ quantize_blocks_fp8_kernel(const T* __restrict__ src, int rows, int cols, uint8_
 }
 
 // ---- host side ------------------------------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_tiled_fn8() {
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
-        void* sym = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess ||
-            q != cudaDriverEntryPointSuccess)
-            return nullptr;
-        fn = reinterpret_cast<EncodeTiledFn>(sym);
-    }
-    return fn;
-}
-
 // (outer, rows, K) byte tensor, K contiguous; box = 128 bytes x box_rows x 1 with the 128-byte swizzle.
 aristos_status_t make_map_u8(CUtensorMap* tm, const void* base, int K, int rows, int outer, int box_rows) {
-    EncodeTiledFn enc = encode_tiled_fn8();
-    if (!enc) { set_last_error("cuTensorMapEncodeTiled is not available from the driver"); return ARISTOS_ERR_CUDA; }
-    const cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)rows, (cuuint64_t)outer};
-    const cuuint64_t strides[2] = {(cuuint64_t)K, (cuuint64_t)K * (cuuint64_t)rows};
-    const cuuint32_t box[3] = {F8_KB, (cuuint32_t)box_rows, 1};
-    const cuuint32_t estr[3] = {1, 1, 1};
-    const CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
-                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) {
-        set_last_error("cuTensorMapEncodeTiled (fp8) failed with %d (K=%d rows=%d outer=%d)", (int)r, K, rows, outer);
-        return ARISTOS_ERR_CUDA;
-    }
-    return ARISTOS_OK;
+    static_assert(F8_KB == 128, "one swizzle row per box row");
+    return encode_map_3d(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, base, K, rows, outer, box_rows);
 }
 
 aristos_status_t launch_fp8_gemm(const void* A, const void* B0, const void* B1, const Fp8GemmParams& p, int grid_limit,

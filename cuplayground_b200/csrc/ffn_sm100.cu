@@ -31,6 +31,7 @@
 
 #include "common.cuh"
 #include "ptx_sm100.cuh"
+#include "tensor_map.cuh"
 
 namespace aristos {
 
@@ -599,42 +600,11 @@ ffn_grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gr
 }
 
 // ---- host side ------------------------------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_tiled_fn() {
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
-        void* sym = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess ||
-            q != cudaDriverEntryPointSuccess)
-            return nullptr;
-        fn = reinterpret_cast<EncodeTiledFn>(sym);
-    }
-    return fn;
-}
-
 // (outer, rows, K) tensor, K contiguous; box = 128 bytes x 128 rows x 1 with the 128-byte swizzle.
 aristos_status_t make_map_3d(CUtensorMap* tm, const void* base, int K, int rows, int outer, int fmt) {
-    EncodeTiledFn enc = encode_tiled_fn();
-    if (!enc) { set_last_error("cuTensorMapEncodeTiled is not available from the driver"); return ARISTOS_ERR_CUDA; }
-    const cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)rows, (cuuint64_t)outer};
-    const cuuint64_t elt = fmt == FMT_TF32 ? 4 : 2;
-    const cuuint64_t strides[2] = {(cuuint64_t)K * elt, (cuuint64_t)K * elt * (cuuint64_t)rows};
-    const cuuint32_t box[3] = {(cuuint32_t)(128 / elt), 128, 1};    // 128 bytes along K
-    const cuuint32_t estr[3] = {1, 1, 1};
     const CUtensorMapDataType dt = fmt == FMT_TF32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
                                    : (fmt == FMT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16);
-    const CUresult r = enc(tm, dt, 3, const_cast<void*>(base), dims, strides, box, estr,
-                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) {
-        set_last_error("cuTensorMapEncodeTiled failed with %d (K=%d rows=%d outer=%d)", (int)r, K, rows, outer);
-        return ARISTOS_ERR_CUDA;
-    }
-    return ARISTOS_OK;
+    return encode_map_3d(tm, dt, fmt == FMT_TF32 ? 4 : 2, base, K, rows, outer, 128);
 }
 
 // Tile shape: CTA pairs (256-row tiles) pay off when the row groups are long; short groups would mostly pad them.

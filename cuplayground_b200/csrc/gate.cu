@@ -23,6 +23,7 @@
 // (each step keeps half of the tile, 31 shuffles instead of 160): adding the same two operands, it gives the same
 // bits as the full butterfly. With few experts the kernel streams x once from HBM; with many it is FMA-bound.
 #include "common.cuh"
+#include "gate_contract.cuh"
 
 namespace aristos {
 
@@ -31,7 +32,6 @@ constexpr int GATE_WARPS = GATE_THREADS / 32;
 constexpr int GATE_TT = 4;       // tokens per warp register tile
 constexpr int GATE_TE = 8;       // experts per warp register tile
 constexpr int GATE_SLAB = 256;   // elements of H per staged slab (one 8-element chunk per lane)
-constexpr int MAX_TOPK = 16;
 
 __device__ __forceinline__ void cp_async_16(uint32_t smem_dst, const void* gsrc, int src_bytes) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_dst), "l"(gsrc), "r"(src_bytes) : "memory");
@@ -40,71 +40,7 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-// 8 consecutive elements as 4 (even, odd) pairs.
-__device__ __forceinline__ void load8_pairs(const __nv_bfloat16* p, float2 (&v)[4]) {
-    const uint4 u = *reinterpret_cast<const uint4*>(p);
-    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) v[i] = make_float2(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xFFFF0000u));
-}
-__device__ __forceinline__ void load8_pairs(const __half* p, float2 (&v)[4]) {
-    const uint4 u = *reinterpret_cast<const uint4*>(p);
-    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) v[i] = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
-}
-__device__ __forceinline__ void load8_pairs(const float* p, float2 (&v)[4]) {
-    const float4 a = *reinterpret_cast<const float4*>(p);
-    const float4 b = *reinterpret_cast<const float4*>(p + 4);
-    v[0] = make_float2(a.x, a.y); v[1] = make_float2(a.z, a.w);
-    v[2] = make_float2(b.x, b.y); v[3] = make_float2(b.z, b.w);
-}
-
 constexpr int GATE_STAGES = 3;
-
-// One 8-element chunk of a row in the form the FMA consumes: fp32 rows as four (even, odd) float2 pairs for the packed
-// fp32x2 FMA; 16-bit rows as their four raw 32-bit words, multiplied by the mixed-precision FMA
-// (fma.rn.f32.bf16 / .f16: 16-bit operands, fp32 accumulator, one rounding) so that nothing is unpacked on the
-// integer pipe. Both give acc.x = fmaf(x[2i], w[2i], acc.x), acc.y = fmaf(x[2i+1], w[2i+1], acc.y).
-template <typename T> struct GateChunk { uint32_t w[4]; };
-template <> struct GateChunk<float> { float2 v[4]; };
-
-__device__ __forceinline__ void load_chunk(const __nv_bfloat16* p, GateChunk<__nv_bfloat16>& c) {
-    const uint4 u = *reinterpret_cast<const uint4*>(p);
-    c.w[0] = u.x; c.w[1] = u.y; c.w[2] = u.z; c.w[3] = u.w;
-}
-__device__ __forceinline__ void load_chunk(const __half* p, GateChunk<__half>& c) {
-    const uint4 u = *reinterpret_cast<const uint4*>(p);
-    c.w[0] = u.x; c.w[1] = u.y; c.w[2] = u.z; c.w[3] = u.w;
-}
-__device__ __forceinline__ void load_chunk(const float* p, GateChunk<float>& c) { load8_pairs(p, c.v); }
-
-__device__ __forceinline__ void fma_pair(float2& acc, const GateChunk<__nv_bfloat16>& x,
-                                         const GateChunk<__nv_bfloat16>& w, int i) {
-    asm("{\n\t"
-        ".reg .b16 xl, xh, wl, wh;\n\t"
-        "mov.b32 {xl, xh}, %2;\n\t"
-        "mov.b32 {wl, wh}, %3;\n\t"
-        "fma.rn.f32.bf16 %0, xl, wl, %0;\n\t"
-        "fma.rn.f32.bf16 %1, xh, wh, %1;\n\t"
-        "}"
-        : "+f"(acc.x), "+f"(acc.y)
-        : "r"(x.w[i]), "r"(w.w[i]));
-}
-__device__ __forceinline__ void fma_pair(float2& acc, const GateChunk<__half>& x, const GateChunk<__half>& w, int i) {
-    asm("{\n\t"
-        ".reg .b16 xl, xh, wl, wh;\n\t"
-        "mov.b32 {xl, xh}, %2;\n\t"
-        "mov.b32 {wl, wh}, %3;\n\t"
-        "fma.rn.f32.f16 %0, xl, wl, %0;\n\t"
-        "fma.rn.f32.f16 %1, xh, wh, %1;\n\t"
-        "}"
-        : "+f"(acc.x), "+f"(acc.y)
-        : "r"(x.w[i]), "r"(w.w[i]));
-}
-__device__ __forceinline__ void fma_pair(float2& acc, const GateChunk<float>& x, const GateChunk<float>& w, int i) {
-    acc = __ffma2_rn(x.v[i], w.v[i], acc);
-}
 
 // Top-k on one token's logits (in shared memory) by one warp, then the combine weights.
 __device__ __forceinline__ void topk_one_token(const float* l, int t, int E, int k, int gate_fn, int renorm, int lane,

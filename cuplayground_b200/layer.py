@@ -99,6 +99,23 @@ def gate_topk(x, w_gate, k: int, gate_fn: int = 0, renorm: int = 0, gate_bias=No
     return (idx, w, logits) if want_logits else (idx, w)
 
 
+def gate_topk_screened(x, w_gate, k: int, gate_fn: int = 0, renorm: int = 0, gate_bias=None):
+    """aristos_gate_topk_screened: tensor-core screen + exact evaluation of the experts that can still reach the
+    top k (the layer's gate for 16-bit inputs and 32 <= E <= 256). Returns (topk_idx, topk_w, status word)."""
+    S, H = x.shape
+    E = w_gate.shape[0]
+    lib = _lib.load()
+    idx = torch.empty((S, k), dtype=torch.int32, device=x.device)
+    w = torch.empty((S, k), dtype=torch.float32, device=x.device)
+    nbytes = lib.aristos_gate_scratch_bytes(S, E)
+    scratch = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=x.device)
+    status = torch.zeros(1, dtype=torch.int32, device=x.device)
+    _lib.check(lib.aristos_gate_topk_screened(_ptr(x), _ptr(w_gate), _ptr(gate_bias), S, H, E, k, gate_fn, renorm,
+                                              _dt(x), _ptr(idx), _ptr(w), _ptr(scratch), nbytes, _ptr(status),
+                                              _stream_ptr()))
+    return idx, w, status
+
+
 def dispatch(topk_idx, E: int, cap: int):
     S, k = topk_idx.shape
     dev = topk_idx.device

@@ -45,7 +45,8 @@ typedef enum aristos_status {
     ARISTOS_ERR_WORKSPACE = 7,      /* caller-provided workspace too small */
     ARISTOS_ERR_DEVICE_TIMEOUT = 8, /* a bounded device-side wait expired (kernel returned early) */
     ARISTOS_ERR_DEVICE_BOUNDS = 9,  /* a routing-derived index was out of range (access skipped) */
-    ARISTOS_ERR_NOMEM = 10
+    ARISTOS_ERR_NOMEM = 10,
+    ARISTOS_ERR_GATE_SCREEN = 11    /* the screened gate met an accumulation error above its bound (token re-evaluated exactly) */
 } aristos_status_t;
 
 /* torch_dtype (aristos_config.schema.json:54-58) and hidden_act (:24-28), with the extension values. */
@@ -172,7 +173,7 @@ ARISTOS_API aristos_status_t aristos_moe_routing_to_host(const aristos_moe_t* la
                                                          float* topk_w_host, int32_t* count_host,
                                                          int32_t* slot_of_host, int32_t* token_of_slot_host);
 /* Synchronises the layer's streams and reports device-side faults of the forwards since the last call
- * (ARISTOS_ERR_DEVICE_TIMEOUT / ARISTOS_ERR_DEVICE_BOUNDS), then clears them. */
+ * (ARISTOS_ERR_DEVICE_TIMEOUT / ARISTOS_ERR_DEVICE_BOUNDS / ARISTOS_ERR_GATE_SCREEN), then clears them. */
 ARISTOS_API aristos_status_t aristos_moe_status(aristos_moe_t* layer);
 /* Stage stopwatch (the reference times its kernels with %globaltimer reads and cudaEvents, mma.cuh:56,163,
  * auditorium/overlap.cuh:207-224). With profiling on, every forward records CUDA events on its stream at the stage
@@ -197,6 +198,17 @@ ARISTOS_API aristos_status_t aristos_moe_destroy(aristos_moe_t* layer);
 ARISTOS_API aristos_status_t aristos_gate_topk(const void* x, const void* w_gate, const float* gate_bias, int S,
                                                int H, int E, int k, int gate_fn, int renorm, int dtype,
                                                int32_t* topk_idx, float* topk_w, float* logits_out, void* stream);
+/* The same gate for many experts (what the layer calls when it needs no logits): a tcgen05 screen computes
+ * approximate logits, the experts whose error interval reaches the k-th place are re-evaluated with the bit-exact
+ * contract, top-k runs on those. topk_idx is identical to aristos_gate_topk's; softmax weights agree to rounding
+ * (sigmoid weights exactly). Needs bf16/fp16 inputs and 32 <= E <= 256, E % 4 == 0; any other shape, or
+ * scratch == NULL, runs aristos_gate_topk. scratch: aristos_gate_scratch_bytes(S, E) bytes, 16-byte aligned.
+ * dev_status (device int32, may be NULL) receives fault bits of the bounded waits. */
+ARISTOS_API size_t aristos_gate_scratch_bytes(int S, int E);
+ARISTOS_API aristos_status_t aristos_gate_topk_screened(const void* x, const void* w_gate, const float* gate_bias,
+                                                        int S, int H, int E, int k, int gate_fn, int renorm,
+                                                        int dtype, int32_t* topk_idx, float* topk_w, void* scratch,
+                                                        size_t scratch_bytes, int32_t* dev_status, void* stream);
 /* Dispatch bookkeeping (capacity-bounded per-expert token lists, overflow dropped in token order). Replaces the
  * task-queue bookkeeping of auditorium/scheduling.cuh:218-252. scratch: aristos_dispatch_scratch_bytes(). */
 ARISTOS_API size_t aristos_dispatch_scratch_bytes(int S, int k, int E);

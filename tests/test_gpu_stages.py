@@ -56,6 +56,54 @@ def test_gate_ties_go_to_lower_index(cp, oracle):
     assert (idx5.cpu().numpy() == np.array([3, 7, 11, 0, 1])).all()
 
 
+@pytest.mark.parametrize("S,H,E,k,gate_fn,renorm,f16,bias", [
+    (512, 2048, 64, 2, 0, 1, False, False),    # gate of the single-GPU case
+    (777, 1024, 128, 4, 0, 0, False, True),    # skewed case (Zipf prior), ragged S
+    (96, 448, 256, 8, 1, 1, False, False),     # sigmoid gate, H not a multiple of the 64-element K block
+    (300, 7168, 256, 8, 1, 1, False, False),   # gate of the fine-grained case: long rows, H split over CTAs
+    (260, 512, 36, 3, 0, 0, True, False),      # fp16, E not a multiple of 16
+    (1, 64, 32, 1, 0, 0, False, False),        # one token
+])
+def test_gate_screened_parity(cp, oracle, S, H, E, k, gate_fn, renorm, f16, bias):
+    """Tensor-core screen + exact candidates: routing identical to the all-experts contract, weights to rounding,
+    and the screen's error bound holds on every candidate (status word stays 0)."""
+    torch = _torch()
+    x, wg, *_ = make_inputs(S, H, 64, E, seed=23, bf16=not f16, f16=f16)
+    wg = wg * 8.0
+    b = oracle.zipf_bias(E, 1.2) if bias else None
+    dt = torch.float16 if f16 else torch.bfloat16
+    idx, w, status = cp.gate_topk_screened(to_dev(x, dt), to_dev(wg, dt), k, gate_fn, renorm,
+                                           gate_bias=to_dev(b, torch.float32))
+    ref_idx, ref_w = oracle.gate_topk(oracle.gate_logits(x, wg, b), k, gate_fn, renorm)
+    assert int(status.item()) == 0
+    np.testing.assert_array_equal(idx.cpu().numpy(), ref_idx)
+    np.testing.assert_allclose(w.cpu().numpy(), ref_w, rtol=2e-5, atol=1e-7)
+    idx2, w2 = cp.gate_topk(to_dev(x, dt), to_dev(wg, dt), k, gate_fn, renorm, gate_bias=to_dev(b, torch.float32))
+    assert torch.equal(idx, idx2)
+    if gate_fn == 1:
+        assert torch.equal(w, w2)          # sigmoid weights depend on the selected (exact) logits only
+
+
+def test_gate_screened_ties_and_near_ties(cp, oracle):
+    """Experts that tie exactly (duplicated rows) or differ in one element by one bf16 step lie inside the screen's
+    error interval: all of them must become candidates and the exact logits decide, ties to the lower index."""
+    torch = _torch()
+    S, H, E, k = 256, 1024, 64, 4
+    x, wg, *_ = make_inputs(S, H, 64, E, seed=29, bf16=True)
+    wg = wg * 8.0
+    wg[32:] = wg[:32]                              # expert e + 32 ties with expert e on every token
+    wg = oracle.round_bf16(wg)
+    for e, h in ((41, 7), (50, 300), (63, 1023)):  # about one bf16 step away from rows 9, 18, 31 in one element
+        wg[e, h] = oracle.round_bf16(np.array([wg[e, h] * (1.0 + 2.0 ** -7)], np.float32))[0]
+    idx, w, status = cp.gate_topk_screened(to_dev(x, torch.bfloat16), to_dev(wg, torch.bfloat16), k)
+    ref_idx, ref_w = oracle.gate_topk(oracle.gate_logits(x, wg), k)
+    assert int(status.item()) == 0
+    np.testing.assert_array_equal(idx.cpu().numpy(), ref_idx)
+    np.testing.assert_allclose(w.cpu().numpy(), ref_w, rtol=2e-5, atol=1e-7)
+    first = idx.cpu().numpy()[:, 0]
+    assert ((first < 32) | np.isin(first, (41, 50, 63))).all()     # an exact tie goes to the lower index
+
+
 def _random_topk(rng, S, E, k, skew):
     p = 1.0 / np.arange(1, E + 1) ** skew
     p /= p.sum()
