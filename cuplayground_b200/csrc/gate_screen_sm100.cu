@@ -5,21 +5,24 @@
 // logits of experts close to the k-th place. So:
 //   1. gate_wnorm_kernel   : |Wg[e,:]|_2 per expert.
 //   2. gate_screen_kernel  : approximate logits A = x * Wg^T with tcgen05.mma (fp32 accumulators in TMEM, operands by
-//                            TMA), split along H over several CTAs per 128-token tile; the partial sums go to scratch.
+//                            TMA). H is cut into slices of 512 elements; each slice's partial sums start from zero
+//                            and go to scratch on their own, which keeps the accumulation chains short.
 //   3. gate_select_kernel  : one warp per token. With err[e] >= |A[e] - L[e]| (L = the contract's logit), every expert
 //                            whose upper bound A[e] + err[e] reaches the k-th largest lower bound A[e] - err[e] is a
 //                            candidate; no other expert can be among the top k. The candidates' logits are computed
 //                            exactly as in gate.cu, top-k (ties -> lower index) runs on those, and the softmax
 //                            denominator takes exact logits for candidates and screened ones for the rest.
-// err[e] = 4 H 2^-23 |x_t| |Wg_e| + 2^-20 max|A|: products of 16-bit inputs are exact, so both A and L differ from
-// the true dot product only by accumulation roundings; n accumulations that each lose at most one unit in the last
-// place of a partial sum bounded by sum|x_h w_h| <= |x||w| (Cauchy-Schwarz) give n 2^-23 |x||w|, and the factor 4
-// covers block-wise alignment and truncation inside the tensor core, the split over H and the bias addition. The
-// select kernel also checks the bound on every candidate (where it has both values); a token that violates it is
-// evaluated exactly over all experts and DEV_FAULT_SCREEN is raised in the status word.
+// err[e] = 4 n 2^-23 |x_t| |Wg_e| + (slices) 2^-24 sum|slice sums| + 2^-20 max|A|, n = elements per slice. Products of
+// 16-bit inputs are exact, so A and L differ from the true dot product only by accumulation roundings. Inside a slice,
+// n accumulations that each lose at most one unit in the last place of a partial sum bounded by sum|x_h w_h| give
+// n 2^-23 sum|x_h w_h|; over the slices, sum_s |x_s||w_s| <= |x||w| (Cauchy-Schwarz, twice). The factor 4 covers
+// block-wise alignment and truncation inside the tensor core and the contract's own roundings. The second term is the
+// fp32 sum over the slices (computed from the values added), the third the bias addition. The select kernel also
+// checks the bound on every candidate (where it has both values); a token that violates it is evaluated exactly over
+// all experts and DEV_FAULT_SCREEN is raised in the status word.
 // The routing is therefore identical to gate.cu's; only the weights of a softmax gate may differ in the last bits
 // (the screened logits of non-candidates enter the denominator). Used by the layer when no logits are requested,
-// for 16-bit inputs and 32 <= E <= 256.
+// for 16-bit inputs and many experts (up to 256).
 #include <cuda.h>
 
 #include <type_traits>
@@ -42,26 +45,30 @@ constexpr int GS_B_BOX_BYTES = 128 * GS_BK * 2; // one 128-expert box
 constexpr int GS_STAGE_BYTES = GS_A_BYTES + 2 * GS_B_BOX_BYTES;
 constexpr int GS_SMEM_BYTES = 1024 + GS_STAGES * GS_STAGE_BYTES + 256;
 constexpr int GS_MAX_E = 256;
-constexpr int GS_MAX_SPLIT = 4;
+constexpr int GS_MAX_SLICES = 16;             // slices of H whose partial logits are stored separately
+constexpr int GS_SLICE_KB = 8;                 // K blocks (of 64 elements) per slice, unless that needs more slices
 
 struct GateScreenParams {
     int S, H, E;
     int n_mma;          // E rounded up to a multiple of 16
-    int tmem_cols;      // power of two >= max(32, n_mma)
+    int buf_cols;       // TMEM columns per accumulator buffer: power of two >= max(32, n_mma)
     int kblocks;        // ceil(H / 64)
-    int kb_per_split;
+    int slice_kb;       // K blocks per slice; every slice restarts the accumulator and is stored on its own
+    int nslices;
     int bf16;           // 1: bf16 operands, 0: fp16
-    float* partial;     // (splits, S, E)
+    float* partial;     // (nslices, S, E)
     int32_t* dev_status;
 };
 
+// CTA (x, y) owns the 128-token tile x and the slices y, y + gridDim.y, ... of H. Accumulators alternate between two
+// TMEM buffers so that the stores of one slice run under the MMAs of the next.
 __global__ void __launch_bounds__(GS_THREADS, 1)
 gate_screen_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW,
                    const GateScreenParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* aux = smem + GS_STAGES * GS_STAGE_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(aux);             // full[S], empty[S], tfull
+    uint64_t* bars = reinterpret_cast<uint64_t*>(aux);             // full[S], empty[S], tfull[2], tempty[2]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aux + 128);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(aux + 132);
 
@@ -69,24 +76,26 @@ gate_screen_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
     const uint32_t bar_full = ptx::smem_u32(bars);
     const uint32_t bar_empty = bar_full + 8 * GS_STAGES;
     const uint32_t bar_tfull = bar_empty + 8 * GS_STAGES;
+    const uint32_t bar_tempty = bar_tfull + 16;
     const uint32_t smem_base = ptx::smem_u32(smem);
     const int m0 = blockIdx.x * GS_BM;
-    const int split = blockIdx.y;
-    const int kb0 = split * p.kb_per_split;
-    const int kb1 = min(p.kblocks, kb0 + p.kb_per_split);
     const int nbox = p.E > 128 ? 2 : 1;
     const uint32_t stage_tx = GS_A_BYTES + nbox * GS_B_BOX_BYTES;
+    const uint32_t tmem_cols = 2 * p.buf_cols;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < GS_STAGES; ++s) {
             ptx::mbar_init(bar_full + 8 * s, 1);
             ptx::mbar_init(bar_empty + 8 * s, 1);
         }
-        ptx::mbar_init(bar_tfull, 1);
+        for (int b = 0; b < 2; ++b) {
+            ptx::mbar_init(bar_tfull + 8 * b, 1);
+            ptx::mbar_init(bar_tempty + 8 * b, 128);
+        }
         *abort_flag = 0;
         ptx::fence_mbar_init();
     }
-    if (warp == 1) ptx::tmem_alloc(ptx::smem_u32(tmem_slot), p.tmem_cols);
+    if (warp == 1) ptx::tmem_alloc(ptx::smem_u32(tmem_slot), tmem_cols);
     ptx::tcgen05_fence_before();
     __syncthreads();
     ptx::tcgen05_fence_after();
@@ -98,15 +107,20 @@ gate_screen_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
             ptx::prefetch_tensormap(&tmW);
             int stage = 0;
             uint32_t phase = 0;
-            for (int kb = kb0; kb < kb1; ++kb) {
-                if (!ptx::mbar_wait_bounded(bar_empty + 8 * stage, phase ^ 1u, abort_flag, p.dev_status)) break;
-                const uint32_t full = bar_full + 8 * stage;
-                const uint32_t sa = smem_base + stage * GS_STAGE_BYTES;
-                ptx::mbar_arrive_expect_tx(full, stage_tx);
-                ptx::tma_load_3d(sa, &tmX, kb * GS_BK, m0, 0, full);
-                for (int b = 0; b < nbox; ++b)
-                    ptx::tma_load_3d(sa + GS_A_BYTES + b * GS_B_BOX_BYTES, &tmW, kb * GS_BK, b * 128, 0, full);
-                if (++stage == GS_STAGES) { stage = 0; phase ^= 1u; }
+            bool ok = true;
+            for (int sl = blockIdx.y; ok && sl < p.nslices; sl += gridDim.y) {
+                const int kb0 = sl * p.slice_kb, kb1 = min(p.kblocks, kb0 + p.slice_kb);
+                for (int kb = kb0; kb < kb1; ++kb) {
+                    ok = ptx::mbar_wait_bounded(bar_empty + 8 * stage, phase ^ 1u, abort_flag, p.dev_status);
+                    if (!ok) break;
+                    const uint32_t full = bar_full + 8 * stage;
+                    const uint32_t sa = smem_base + stage * GS_STAGE_BYTES;
+                    ptx::mbar_arrive_expect_tx(full, stage_tx);
+                    ptx::tma_load_3d(sa, &tmX, kb * GS_BK, m0, 0, full);
+                    for (int b = 0; b < nbox; ++b)
+                        ptx::tma_load_3d(sa + GS_A_BYTES + b * GS_B_BOX_BYTES, &tmW, kb * GS_BK, b * 128, 0, full);
+                    if (++stage == GS_STAGES) { stage = 0; phase ^= 1u; }
+                }
             }
         }
         __syncwarp();
@@ -115,35 +129,54 @@ gate_screen_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
             const uint32_t idesc = ptx::umma_idesc_f32acc(GS_BM, p.n_mma, p.bf16 ? 1u : 0u);
             int stage = 0;
             uint32_t phase = 0;
+            int it = 0;
             bool ok = true;
-            for (int kb = kb0; kb < kb1; ++kb) {
-                ok = ptx::mbar_wait_bounded(bar_full + 8 * stage, phase, abort_flag, p.dev_status);
+            for (int sl = blockIdx.y; ok && sl < p.nslices; sl += gridDim.y, ++it) {
+                const int buf = it & 1;
+                const uint32_t aphase = (it >> 1) & 1u;
+                ok = ptx::mbar_wait_bounded(bar_tempty + 8 * buf, aphase ^ 1u, abort_flag, p.dev_status);
                 if (!ok) break;
                 ptx::tcgen05_fence_after();
-                const uint32_t sa = smem_base + stage * GS_STAGE_BYTES;
-                const uint64_t da = ptx::umma_desc_k_sw128(sa);
-                const uint64_t db = ptx::umma_desc_k_sw128(sa + GS_A_BYTES);
+                const uint32_t tmem_d = tmem_base + buf * p.buf_cols;
+                const int kb0 = sl * p.slice_kb, kb1 = min(p.kblocks, kb0 + p.slice_kb);
+                for (int kb = kb0; kb < kb1; ++kb) {
+                    ok = ptx::mbar_wait_bounded(bar_full + 8 * stage, phase, abort_flag, p.dev_status);
+                    if (!ok) break;
+                    ptx::tcgen05_fence_after();
+                    const uint32_t sa = smem_base + stage * GS_STAGE_BYTES;
+                    const uint64_t da = ptx::umma_desc_k_sw128(sa);
+                    const uint64_t db = ptx::umma_desc_k_sw128(sa + GS_A_BYTES);
 #pragma unroll
-                for (int k = 0; k < GS_BK / 16; ++k)
-                    ptx::umma_f16(tmem_base, da + 2 * k, db + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
-                ptx::umma_commit(bar_empty + 8 * stage);
-                if (++stage == GS_STAGES) { stage = 0; phase ^= 1u; }
+                    for (int k = 0; k < GS_BK / 16; ++k)
+                        ptx::umma_f16(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+                    ptx::umma_commit(bar_empty + 8 * stage);
+                    if (++stage == GS_STAGES) { stage = 0; phase ^= 1u; }
+                }
+                if (ok) ptx::umma_commit(bar_tfull + 8 * buf);
             }
-            if (ok) ptx::umma_commit(bar_tfull);
         }
         __syncwarp();
     } else {
         const int quarter = warp & 3;                 // TMEM lanes this warp may read
         const int row = m0 + quarter * 32 + lane;
-        // tcgen05.ld is warp-collective: the warp leaves together
-        const bool ok = __all_sync(0xffffffffu, ptx::mbar_wait_bounded(bar_tfull, 0u, abort_flag, p.dev_status));
-        if (ok) {
+        int it = 0;
+        for (int sl = blockIdx.y; sl < p.nslices; sl += gridDim.y, ++it) {
+            const int buf = it & 1;
+            const uint32_t aphase = (it >> 1) & 1u;
+            // tcgen05.ld is warp-collective: the warp leaves together
+            if (!__all_sync(0xffffffffu, ptx::mbar_wait_bounded(bar_tfull + 8 * buf, aphase, abort_flag, p.dev_status)))
+                break;
             ptx::tcgen05_fence_after();
-            float* out = p.partial + ((size_t)split * p.S + (size_t)min(row, p.S - 1)) * p.E;
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * p.buf_cols;
+            float* out = p.partial + ((size_t)sl * p.S + (size_t)min(row, p.S - 1)) * p.E;
             for (int c0 = 0; c0 < p.n_mma; c0 += 32) {
                 uint32_t a[32];
-                ptx::tmem_ld_32x32b_x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + c0, a);
+                ptx::tmem_ld_32x32b_x32(taddr + c0, a);
                 ptx::tmem_ld_wait();
+                if (c0 + 32 >= p.n_mma) {             // the last load has landed: hand the buffer back
+                    ptx::tcgen05_fence_before();
+                    ptx::mbar_arrive(bar_tempty + 8 * buf);
+                }
                 if (row < p.S) {
 #pragma unroll
                     for (int q = 0; q < 8; ++q)
@@ -158,7 +191,7 @@ gate_screen_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
     __syncthreads();
     if (warp == 1) {
         ptx::tcgen05_fence_after();
-        ptx::tmem_dealloc(tmem_base, p.tmem_cols);
+        ptx::tmem_dealloc(tmem_base, tmem_cols);
     }
 }
 
@@ -228,7 +261,7 @@ __device__ __forceinline__ void exact_logits(const T* __restrict__ xrow, const T
 template <typename T>
 __global__ void __launch_bounds__(SEL_WARPS * 32)
 gate_select_kernel(const T* __restrict__ x, const T* __restrict__ wg, const float* __restrict__ bias,
-                   const float* __restrict__ partial, int splits, const float* __restrict__ wnorm, int S, int H, int E,
+                   const float* __restrict__ partial, int nslices, const float* __restrict__ wnorm, int S, int H, int E,
                    int k, int gate_fn, int renorm, float err_scale, int32_t* __restrict__ topk_idx,
                    float* __restrict__ topk_w, int32_t* dev_status) {
     __shared__ int s_cand[SEL_WARPS][GS_MAX_E];
@@ -248,11 +281,17 @@ gate_select_kernel(const T* __restrict__ x, const T* __restrict__ wg, const floa
     for (int i = 0; i < SEL_SLOTS; ++i) {
         const int e = lane + 32 * i;
         a[i] = NEG_INF;
+        err[i] = 0.0f;
         if (e < E) {
-            float v = 0.0f;
-            for (int s = 0; s < splits; ++s) v += partial[((size_t)s * S + t) * E + e];
+            float v = 0.0f, vabs = 0.0f;
+            for (int s = 0; s < nslices; ++s) {
+                const float ps = partial[((size_t)s * S + t) * E + e];
+                v += ps;
+                vabs += fabsf(ps);
+            }
             if (bias) v += bias[e];
             a[i] = v;
+            err[i] = (float)nslices * 5.9604644775390625e-8f * vabs * 1.0001f;   // the fp32 sum over the slices
             amax = fmaxf(amax, fabsf(v));
         }
     }
@@ -273,7 +312,7 @@ gate_select_kernel(const T* __restrict__ x, const T* __restrict__ wg, const floa
 #pragma unroll
     for (int i = 0; i < SEL_SLOTS; ++i) {
         const int e = lane + 32 * i;
-        err[i] = e < E ? err_scale * nx * wnorm[e] + 9.5367431640625e-7f * amax : 0.0f;
+        err[i] = e < E ? err[i] + err_scale * nx * wnorm[e] + 9.5367431640625e-7f * amax : 0.0f;
         lo[i] = e < E ? a[i] - err[i] : NEG_INF;
     }
 
@@ -403,15 +442,14 @@ aristos_status_t launch_screened(const void* x, const void* wg, const float* bia
     GateScreenParams p;
     p.S = S; p.H = H; p.E = E;
     p.n_mma = ceil_div(E, 16) * 16;
-    p.tmem_cols = 32;
-    while (p.tmem_cols < p.n_mma) p.tmem_cols *= 2;
+    p.buf_cols = 32;
+    while (p.buf_cols < p.n_mma) p.buf_cols *= 2;
     p.kblocks = ceil_div(H, GS_BK);
+    p.slice_kb = GS_SLICE_KB > ceil_div(p.kblocks, GS_MAX_SLICES) ? GS_SLICE_KB : ceil_div(p.kblocks, GS_MAX_SLICES);
+    p.nslices = ceil_div(p.kblocks, p.slice_kb);
     const int mtiles = ceil_div(S, GS_BM);
-    int splits = device_sm_count() / mtiles;
-    splits = splits < 1 ? 1 : (splits > GS_MAX_SPLIT ? GS_MAX_SPLIT : splits);
-    if (splits > p.kblocks) splits = p.kblocks;
-    p.kb_per_split = ceil_div(p.kblocks, splits);
-    splits = ceil_div(p.kblocks, p.kb_per_split);
+    int ysplit = device_sm_count() / mtiles;         // CTAs per token tile: fill the SMs, at most one per slice
+    ysplit = ysplit < 1 ? 1 : (ysplit > p.nslices ? p.nslices : ysplit);
     p.bf16 = is_bf16 ? 1 : 0;
     p.partial = partial;
     p.dev_status = dev_status;
@@ -424,11 +462,12 @@ aristos_status_t launch_screened(const void* x, const void* wg, const float* bia
 
     gate_wnorm_kernel<T><<<ceil_div(E, 8), 256, 0, st>>>(static_cast<const T*>(wg), E, H, wnorm);
     ARISTOS_COUNT_LAUNCH();
-    gate_screen_kernel<<<dim3(mtiles, splits), GS_THREADS, GS_SMEM_BYTES, st>>>(tmX, tmW, p);
+    gate_screen_kernel<<<dim3(mtiles, ysplit), GS_THREADS, GS_SMEM_BYTES, st>>>(tmX, tmW, p);
     ARISTOS_COUNT_LAUNCH();
-    const float err_scale = 4.0f * (float)H * 1.1920928955078125e-7f;
+    // 4 n 2^-23 with n = the elements of H one slice accumulates
+    const float err_scale = 4.0f * (float)(p.slice_kb * GS_BK) * 1.1920928955078125e-7f;
     gate_select_kernel<T><<<ceil_div(S, SEL_WARPS), SEL_WARPS * 32, 0, st>>>(
-        static_cast<const T*>(x), static_cast<const T*>(wg), bias, partial, splits, wnorm, S, H, E, k, gate_fn, renorm,
+        static_cast<const T*>(x), static_cast<const T*>(wg), bias, partial, p.nslices, wnorm, S, H, E, k, gate_fn, renorm,
         err_scale, topk_idx, topk_w, dev_status);
     ARISTOS_COUNT_LAUNCH();
     ARISTOS_CUDA_TRY(cudaGetLastError());
@@ -443,7 +482,7 @@ using namespace aristos;
 
 extern "C" size_t aristos_gate_scratch_bytes(int S, int E) {
     if (S <= 0 || E <= 0) return 0;
-    const size_t bytes = GS_MAX_E * sizeof(float) + (size_t)GS_MAX_SPLIT * S * E * sizeof(float);
+    const size_t bytes = GS_MAX_E * sizeof(float) + (size_t)GS_MAX_SLICES * S * E * sizeof(float);
     return (bytes + 255) / 256 * 256;
 }
 
