@@ -213,72 +213,87 @@ __global__ void __launch_bounds__(256) gate_wnorm_kernel(const T* __restrict__ w
 }
 
 constexpr int SEL_WARPS = 8;
-constexpr int SEL_SLOTS = GS_MAX_E / 32;   // experts per lane: e = lane + 32 * slot
-constexpr int SEL_GROUP = 4;               // candidates evaluated together (independent FMA chains)
 
-// The contract's logits of the experts cand[0..n) for one token, by one warp: lane c owns the chunks q % 32 == c,
+// fp32 -> unsigned key with the same order (-0 and +0 compare equal, as they do as floats); 0 marks "removed".
+__device__ __forceinline__ uint32_t order_key(float v) {
+    const uint32_t u = __float_as_uint(v + 0.0f);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+// The contract's logits of the experts cand[c0 .. c0+G) for one token, by one warp: lane c owns the chunks q % 32 == c,
 // (even, odd) partial sums, P = even + odd, xor butterfly 16..1 (both partners add the same two values, so every lane
-// ends with the same bits), bias last.
-template <typename T>
+// ends with the same bits), bias last. G independent FMA chains per lane.
+template <typename T, int G, int UNROLL>
 __device__ __forceinline__ void exact_logits(const T* __restrict__ xrow, const T* __restrict__ wg,
-                                             const float* __restrict__ bias, int H, const int* cand, int n,
+                                             const float* __restrict__ bias, int H, const int* cand, int c0,
                                              float* exact, int lane) {
     const int nchunk = H >> 3;
-    for (int c0 = 0; c0 < n; c0 += SEL_GROUP) {
-        const T* wr[SEL_GROUP];
-        int ex[SEL_GROUP];
-        float2 acc[SEL_GROUP];
+    const T* wr[G];
+    int ex[G];
+    float2 acc[G];
 #pragma unroll
-        for (int j = 0; j < SEL_GROUP; ++j) {
-            ex[j] = cand[min(c0 + j, n - 1)];
-            wr[j] = wg + (size_t)ex[j] * H;
-            acc[j] = make_float2(0.0f, 0.0f);
-        }
-#pragma unroll 2
-        for (int q = lane; q < nchunk; q += 32) {
-            GateChunk<T> xv;
-            load_chunk(xrow + q * 8, xv);
+    for (int j = 0; j < G; ++j) {
+        ex[j] = cand[c0 + j];
+        wr[j] = wg + (size_t)ex[j] * H;
+        acc[j] = make_float2(0.0f, 0.0f);
+    }
+#pragma unroll UNROLL
+    for (int q = lane; q < nchunk; q += 32) {
+        GateChunk<T> xv;
+        load_chunk(xrow + q * 8, xv);
 #pragma unroll
-            for (int j = 0; j < SEL_GROUP; ++j) {
-                GateChunk<T> wv;
-                load_chunk(wr[j] + q * 8, wv);
+        for (int j = 0; j < G; ++j) {
+            GateChunk<T> wv;
+            load_chunk(wr[j] + q * 8, wv);
 #pragma unroll
-                for (int i = 0; i < 4; ++i) fma_pair(acc[j], xv, wv, i);
-            }
-        }
-#pragma unroll
-        for (int j = 0; j < SEL_GROUP; ++j) {
-            float P = acc[j].x + acc[j].y;
-#pragma unroll
-            for (int m = 16; m >= 1; m >>= 1) P = P + __shfl_xor_sync(0xffffffffu, P, m);
-            if (bias) P = P + bias[ex[j]];
-            if (lane == j && c0 + j < n) exact[c0 + j] = P;
+            for (int i = 0; i < 4; ++i) fma_pair(acc[j], xv, wv, i);
         }
     }
-    __syncwarp();
+#pragma unroll
+    for (int j = 0; j < G; ++j) {
+        float P = acc[j].x + acc[j].y;
+#pragma unroll
+        for (int m = 16; m >= 1; m >>= 1) P = P + __shfl_xor_sync(0xffffffffu, P, m);
+        if (bias) P = P + bias[ex[j]];
+        if (lane == j) exact[c0 + j] = P;
+    }
 }
 
 template <typename T>
+__device__ __forceinline__ void exact_logits_all(const T* __restrict__ xrow, const T* __restrict__ wg,
+                                                 const float* __restrict__ bias, int H, const int* cand, int n,
+                                                 float* exact, int lane) {
+    int c0 = 0;
+    for (; c0 + 4 <= n; c0 += 4) exact_logits<T, 4, 2>(xrow, wg, bias, H, cand, c0, exact, lane);
+    if (n - c0 >= 2) { exact_logits<T, 2, 4>(xrow, wg, bias, H, cand, c0, exact, lane); c0 += 2; }
+    if (n - c0 >= 1) exact_logits<T, 1, 4>(xrow, wg, bias, H, cand, c0, exact, lane);
+    __syncwarp();
+}
+
+// SLOTS experts per lane: e = lane + 32 * slot.
+template <typename T, int SLOTS>
 __global__ void __launch_bounds__(SEL_WARPS * 32)
 gate_select_kernel(const T* __restrict__ x, const T* __restrict__ wg, const float* __restrict__ bias,
                    const float* __restrict__ partial, int nslices, const float* __restrict__ wnorm, int S, int H, int E,
                    int k, int gate_fn, int renorm, float err_scale, int32_t* __restrict__ topk_idx,
                    float* __restrict__ topk_w, int32_t* dev_status) {
-    __shared__ int s_cand[SEL_WARPS][GS_MAX_E];
-    __shared__ float s_exact[SEL_WARPS][GS_MAX_E];
+    __shared__ int s_cand[SEL_WARPS][SLOTS * 32];
+    __shared__ float s_exact[SEL_WARPS][SLOTS * 32];
+    __shared__ uint32_t s_key[SEL_WARPS][SLOTS * 32];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x * SEL_WARPS + warp;
     if (t >= S) return;
     int* cand = s_cand[warp];
     float* exact = s_exact[warp];
+    uint32_t* ekey = s_key[warp];
     const T* xrow = x + (size_t)t * H;
     const float NEG_INF = __int_as_float(0xff800000);
 
-    // screened logits (split partial sums added in a fixed order), |x_t|, error bounds
-    float a[SEL_SLOTS], err[SEL_SLOTS];
+    // screened logits (the slices' partial sums added in a fixed order), |x_t|, error bounds
+    float a[SLOTS], err[SLOTS];
     float amax = 0.0f;
 #pragma unroll
-    for (int i = 0; i < SEL_SLOTS; ++i) {
+    for (int i = 0; i < SLOTS; ++i) {
         const int e = lane + 32 * i;
         a[i] = NEG_INF;
         err[i] = 0.0f;
@@ -295,136 +310,128 @@ gate_select_kernel(const T* __restrict__ x, const T* __restrict__ wg, const floa
             amax = fmaxf(amax, fabsf(v));
         }
     }
-    float nx = 0.0f;
+    float2 nx2 = make_float2(0.0f, 0.0f);
     for (int q = lane; q < (H >> 3); q += 32) {
-        float2 v[4];
-        load8_pairs(xrow + q * 8, v);
+        GateChunk<T> xv;
+        load_chunk(xrow + q * 8, xv);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) nx = fmaf(v[i].y, v[i].y, fmaf(v[i].x, v[i].x, nx));
+        for (int i = 0; i < 4; ++i) fma_pair(nx2, xv, xv, i);
     }
+    float nx = nx2.x + nx2.y;
 #pragma unroll
     for (int m = 16; m >= 1; m >>= 1) {
         nx += __shfl_xor_sync(0xffffffffu, nx, m);
         amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
     }
     nx = sqrtf(nx) * 1.0001f;
-    float lo[SEL_SLOTS];
+
+    // k-th largest lower bound A - err, in key space
+    uint32_t lk[SLOTS];
 #pragma unroll
-    for (int i = 0; i < SEL_SLOTS; ++i) {
+    for (int i = 0; i < SLOTS; ++i) {
         const int e = lane + 32 * i;
         err[i] = e < E ? err[i] + err_scale * nx * wnorm[e] + 9.5367431640625e-7f * amax : 0.0f;
-        lo[i] = e < E ? a[i] - err[i] : NEG_INF;
+        lk[i] = e < E ? order_key(a[i] - err[i]) : 0u;
     }
-
-    // k-th largest lower bound
-    float kth = NEG_INF;
+    uint32_t kth = 0u;
 #pragma unroll 1
     for (int j = 0; j < k; ++j) {
-        float bv = NEG_INF;
-        int bs = 0;
+        uint32_t bk = 0u;
 #pragma unroll
-        for (int i = 0; i < SEL_SLOTS; ++i)
-            if (lo[i] > bv) { bv = lo[i]; bs = i; }
-        float wv = bv;
-        int wl = lane;
+        for (int i = 0; i < SLOTS; ++i) bk = max(bk, lk[i]);
+        kth = __reduce_max_sync(0xffffffffu, bk);
+        const uint32_t owners = __ballot_sync(0xffffffffu, bk == kth);
+        if (lane == __ffs(owners) - 1) {               // one holder of the maximum drops one instance of it
+            bool done = false;
 #pragma unroll
-        for (int m = 16; m >= 1; m >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, wv, m);
-            const int ol = __shfl_xor_sync(0xffffffffu, wl, m);
-            if (ov > wv || (ov == wv && ol < wl)) { wv = ov; wl = ol; }
+            for (int i = 0; i < SLOTS; ++i)
+                if (!done && lk[i] == kth) { lk[i] = 0u; done = true; }
         }
-        kth = wv;
-#pragma unroll
-        for (int i = 0; i < SEL_SLOTS; ++i)
-            if (lane == wl && i == bs) lo[i] = NEG_INF;
     }
 
-    // candidates: upper bound reaches the k-th lower bound
+    // candidates: upper bound reaches the k-th lower bound (ascending expert index along the list)
     int n = 0;
-    int pos[SEL_SLOTS];
+    int pos[SLOTS];
 #pragma unroll
-    for (int i = 0; i < SEL_SLOTS; ++i) {
+    for (int i = 0; i < SLOTS; ++i) {
         const int e = lane + 32 * i;
-        const bool pred = e < E && a[i] + err[i] >= kth;
+        const bool pred = e < E && order_key(a[i] + err[i]) >= kth;
         const uint32_t mask = __ballot_sync(0xffffffffu, pred);
         pos[i] = pred ? n + __popc(mask & ((1u << lane) - 1u)) : -1;
         if (pred) cand[pos[i]] = e;
         n += __popc(mask);
     }
     __syncwarp();
-    exact_logits<T>(xrow, wg, bias, H, cand, n, exact, lane);
+    exact_logits_all<T>(xrow, wg, bias, H, cand, n, exact, lane);
 
     // the error bound, checked wherever both values exist; a token that breaks it is evaluated over all experts
     bool bad = n == 0;      // only NaN logits leave no candidate
 #pragma unroll
-    for (int i = 0; i < SEL_SLOTS; ++i)
+    for (int i = 0; i < SLOTS; ++i)
         if (pos[i] >= 0) bad |= !(fabsf(exact[pos[i]] - a[i]) <= err[i]);
     if (__any_sync(0xffffffffu, bad)) {
         if (lane == 0 && dev_status) atomicOr(dev_status, DEV_FAULT_SCREEN);
         __syncwarp();
         n = E;
 #pragma unroll
-        for (int i = 0; i < SEL_SLOTS; ++i) {
+        for (int i = 0; i < SLOTS; ++i) {
             const int e = lane + 32 * i;
             pos[i] = e < E ? e : -1;
             if (e < E) cand[e] = e;
         }
         __syncwarp();
-        exact_logits<T>(xrow, wg, bias, H, cand, n, exact, lane);
+        exact_logits_all<T>(xrow, wg, bias, H, cand, n, exact, lane);
     }
 #pragma unroll
-    for (int i = 0; i < SEL_SLOTS; ++i)
-        if (pos[i] >= 0) a[i] = exact[pos[i]];
+    for (int i = 0; i < SLOTS; ++i)
+        if (pos[i] >= 0) {
+            a[i] = exact[pos[i]];
+            ekey[pos[i]] = order_key(a[i]);
+        }
+    __syncwarp();
 
-    // top-k over the candidates' exact logits, ties to the lower expert index
-    int chosen[MAX_TOPK];
-    float chosen_l[MAX_TOPK];
+    // top-k over the candidates' exact logits; the list ascends in expert index, so the lowest position among equal
+    // values is the lowest index. Lane j keeps the j-th choice.
+    int sel_e = 0;
+    float sel_l = 0.0f;
 #pragma unroll 1
     for (int j = 0; j < k; ++j) {
-        float bv = 0.0f;
-        int bi = -1;
+        uint32_t bk = 0u;
+        int bc = 0x7fffffff;
         for (int c = lane; c < n; c += 32) {
-            const int e = cand[c];
-            bool taken = false;
-            for (int i = 0; i < j; ++i) taken |= (chosen[i] == e);
-            if (taken) continue;
-            const float v = exact[c];
-            if (bi < 0 || v > bv || (v == bv && e < bi)) { bv = v; bi = e; }
+            const uint32_t key = ekey[c];
+            if (key > bk) { bk = key; bc = c; }
         }
-#pragma unroll
-        for (int m = 16; m >= 1; m >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, bv, m);
-            const int oi = __shfl_xor_sync(0xffffffffu, bi, m);
-            const bool take = (oi >= 0) && (bi < 0 || ov > bv || (ov == bv && oi < bi));
-            if (take) { bv = ov; bi = oi; }
-        }
-        chosen[j] = bi;
-        chosen_l[j] = bv;
+        const uint32_t wk = __reduce_max_sync(0xffffffffu, bk);
+        const int wc = min(__reduce_min_sync(0xffffffffu, bk == wk ? bc : 0x7fffffff), n - 1);
+        if (lane == j) { sel_e = cand[wc]; sel_l = exact[wc]; }
+        __syncwarp();
+        if (lane == 0) ekey[wc] = 0u;
+        __syncwarp();
     }
 
-    float w_sel[MAX_TOPK];
+    float w;
     if (gate_fn == ARISTOS_GATE_SOFTMAX) {
-        const float mx = chosen_l[0];
+        const float mx = __shfl_sync(0xffffffffu, sel_l, 0);
         float den = 0.0f;
 #pragma unroll
-        for (int i = 0; i < SEL_SLOTS; ++i)
+        for (int i = 0; i < SLOTS; ++i)
             if (lane + 32 * i < E) den += expf(a[i] - mx);
 #pragma unroll
         for (int m = 16; m >= 1; m >>= 1) den += __shfl_xor_sync(0xffffffffu, den, m);
-        for (int j = 0; j < k; ++j) w_sel[j] = expf(chosen_l[j] - mx) / den;
+        w = expf(sel_l - mx) / den;
     } else {
-        for (int j = 0; j < k; ++j) w_sel[j] = 1.0f / (1.0f + expf(-chosen_l[j]));
+        w = 1.0f / (1.0f + expf(-sel_l));
     }
     if (renorm) {
         float s = 0.0f;
-        for (int j = 0; j < k; ++j) s += w_sel[j];
-        for (int j = 0; j < k; ++j) w_sel[j] = w_sel[j] / s;
+        for (int j = 0; j < k; ++j) s += __shfl_sync(0xffffffffu, w, j);     // in choice order, like the other gate
+        w = w / s;
     }
-    for (int j = 0; j < k; ++j)
-        if (lane == j) {
-            topk_idx[(size_t)t * k + j] = chosen[j];
-            topk_w[(size_t)t * k + j] = w_sel[j];
-        }
+    if (lane < k) {
+        topk_idx[(size_t)t * k + lane] = sel_e;
+        topk_w[(size_t)t * k + lane] = w;
+    }
 }
 
 bool screen_supported(int dtype, int H, int E, int k) {
@@ -466,9 +473,15 @@ aristos_status_t launch_screened(const void* x, const void* wg, const float* bia
     ARISTOS_COUNT_LAUNCH();
     // 4 n 2^-23 with n = the elements of H one slice accumulates
     const float err_scale = 4.0f * (float)(p.slice_kb * GS_BK) * 1.1920928955078125e-7f;
-    gate_select_kernel<T><<<ceil_div(S, SEL_WARPS), SEL_WARPS * 32, 0, st>>>(
-        static_cast<const T*>(x), static_cast<const T*>(wg), bias, partial, p.nslices, wnorm, S, H, E, k, gate_fn, renorm,
-        err_scale, topk_idx, topk_w, dev_status);
+    const int sel_grid = ceil_div(S, SEL_WARPS);
+#define ARISTOS_LAUNCH_SELECT(SLOTS)                                                                                 \
+    gate_select_kernel<T, SLOTS><<<sel_grid, SEL_WARPS * 32, 0, st>>>(                                               \
+        static_cast<const T*>(x), static_cast<const T*>(wg), bias, partial, p.nslices, wnorm, S, H, E, k, gate_fn,   \
+        renorm, err_scale, topk_idx, topk_w, dev_status)
+    if (E <= 64) ARISTOS_LAUNCH_SELECT(2);
+    else if (E <= 128) ARISTOS_LAUNCH_SELECT(4);
+    else ARISTOS_LAUNCH_SELECT(8);
+#undef ARISTOS_LAUNCH_SELECT
     ARISTOS_COUNT_LAUNCH();
     ARISTOS_CUDA_TRY(cudaGetLastError());
     return ARISTOS_OK;
