@@ -110,42 +110,91 @@ __device__ __forceinline__ float reduce_scatter_tile(float (&a)[GATE_TT * GATE_T
     return a[0];
 }
 
-// Few experts (E <= 8): every warp streams its own 4 token rows straight from global memory (Wg stays in L1), no
-// shared staging and no block-wide barrier; same arithmetic, same bits.
+// Few experts (E <= 8): every warp streams its own 4 token rows (Wg stays in L1) with no block-wide barrier; same
+// arithmetic, same bits. The rows arrive through a per-lane ring in shared memory filled by cp.async three slabs
+// ahead: each lane reads back only the 16 bytes it copied itself, so the ring needs no synchronisation at all, and
+// the loads in flight do not cost registers (the 4 x 8 accumulator tile already takes 64).
 constexpr int STREAM_WARPS = 8;
+constexpr int STREAM_STAGES = 4;
+constexpr int STREAM_SMEM_BYTES = STREAM_WARPS * STREAM_STAGES * GATE_TT * 32 * 16;
 template <typename T>
 __global__ void __launch_bounds__(STREAM_WARPS * 32)
 gate_topk_stream_kernel(const T* __restrict__ x, const T* __restrict__ wg, const float* __restrict__ bias, int S, int H,
                         int E, int k, int gate_fn, int renorm, int32_t* __restrict__ topk_idx,
                         float* __restrict__ topk_w, float* __restrict__ logits_out) {
+    constexpr int PIECES = (int)sizeof(T) / 2;            // 16-byte pieces per 8-element chunk (fp32: 2)
+    extern __shared__ __align__(16) uint8_t stream_smem[];
     __shared__ float s_logits[STREAM_WARPS][GATE_TT][GATE_TE];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t0 = (blockIdx.x * STREAM_WARPS + warp) * GATE_TT;
     if (t0 >= S) return;
     const int nchunk = H >> 3;
+    const int nslab = (nchunk + 31) >> 5;
     const T* xrow[GATE_TT];
     const T* wrow[GATE_TE];
 #pragma unroll
     for (int tt = 0; tt < GATE_TT; ++tt) xrow[tt] = x + (size_t)min(t0 + tt, S - 1) * H;
 #pragma unroll
     for (int ee = 0; ee < GATE_TE; ++ee) wrow[ee] = wg + (size_t)min(ee, E - 1) * H;
+    // ring entry (stage, token, lane): 16 bytes
+    const uint32_t ring = static_cast<uint32_t>(__cvta_generic_to_shared(stream_smem)) +
+                          (uint32_t)warp * (STREAM_STAGES * GATE_TT * 512) + lane * 16;
+    const uint8_t* ring_ptr = stream_smem + warp * (STREAM_STAGES * GATE_TT * 512) + lane * 16;
+    auto issue = [&](int slab) {
+        // chunk slab*32 + lane of every row (16-bit rows: one 16-byte piece)
+        const int piece = slab * 32 + lane;
+        if (slab < nslab && piece < nchunk) {
+#pragma unroll
+            for (int tt = 0; tt < GATE_TT; ++tt)
+                cp_async_16(ring + ((slab % STREAM_STAGES) * GATE_TT + tt) * 512,
+                            reinterpret_cast<const uint8_t*>(xrow[tt]) + (size_t)piece * 16, 16);
+        }
+        cp_async_commit();
+    };
     float2 acc[GATE_TT][GATE_TE];
 #pragma unroll
     for (int tt = 0; tt < GATE_TT; ++tt)
 #pragma unroll
         for (int ee = 0; ee < GATE_TE; ++ee) acc[tt][ee] = make_float2(0.0f, 0.0f);
-    for (int q = lane; q < nchunk; q += 32) {
-        GateChunk<T> xv[GATE_TT];
+    if (PIECES == 1) {
+        // 16-bit rows: lane c owns the chunks q % 32 == c
 #pragma unroll
-        for (int tt = 0; tt < GATE_TT; ++tt) load_chunk(xrow[tt] + q * 8, xv[tt]);
+        for (int s = 0; s < STREAM_STAGES - 1; ++s) issue(s);
+        for (int slab = 0; slab < nslab; ++slab) {
+            cp_async_wait<STREAM_STAGES - 2>();
+            issue(slab + STREAM_STAGES - 1);
+            const int q = slab * 32 + lane;
+            if (q < nchunk) {
+                GateChunk<T> xv[GATE_TT];
 #pragma unroll
-        for (int ee = 0; ee < GATE_TE; ++ee) {
-            GateChunk<T> wv;
-            load_chunk(wrow[ee] + q * 8, wv);
+                for (int tt = 0; tt < GATE_TT; ++tt)
+                    load_chunk(reinterpret_cast<const T*>(ring_ptr + ((slab % STREAM_STAGES) * GATE_TT + tt) * 512), xv[tt]);
 #pragma unroll
-            for (int tt = 0; tt < GATE_TT; ++tt)
+                for (int ee = 0; ee < GATE_TE; ++ee) {
+                    GateChunk<T> wv;
+                    load_chunk(wrow[ee] + q * 8, wv);
 #pragma unroll
-                for (int i = 0; i < 4; ++i) fma_pair(acc[tt][ee], xv[tt], wv, i);
+                    for (int tt = 0; tt < GATE_TT; ++tt)
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) fma_pair(acc[tt][ee], xv[tt], wv, i);
+                }
+            }
+        }
+    } else {
+        // fp32 rows: straight from global memory (the fp32 gate is the small reference case)
+        for (int q = lane; q < nchunk; q += 32) {
+            GateChunk<T> xv[GATE_TT];
+#pragma unroll
+            for (int tt = 0; tt < GATE_TT; ++tt) load_chunk(xrow[tt] + q * 8, xv[tt]);
+#pragma unroll
+            for (int ee = 0; ee < GATE_TE; ++ee) {
+                GateChunk<T> wv;
+                load_chunk(wrow[ee] + q * 8, wv);
+#pragma unroll
+                for (int tt = 0; tt < GATE_TT; ++tt)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) fma_pair(acc[tt][ee], xv[tt], wv, i);
+            }
         }
     }
     float a[GATE_TT * GATE_TE];
@@ -288,7 +337,9 @@ static aristos_status_t launch_gate(const void* x, const void* wg, const float* 
     // few experts: wide token tiles (x streams once from HBM); many experts: 32-expert tiles walked per CTA
     if (E <= 8) {
         const int grid = ceil_div(S, STREAM_WARPS * GATE_TT);
-        gate_topk_stream_kernel<T><<<grid, STREAM_WARPS * 32, 0, stream>>>(
+        ARISTOS_CUDA_TRY(cudaFuncSetAttribute(gate_topk_stream_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                              STREAM_SMEM_BYTES));
+        gate_topk_stream_kernel<T><<<grid, STREAM_WARPS * 32, STREAM_SMEM_BYTES, stream>>>(
             static_cast<const T*>(x), static_cast<const T*>(wg), bias, S, H, E, k, gate_fn, renorm, topk_idx, topk_w,
             logits_out);
         ARISTOS_COUNT_LAUNCH();
