@@ -73,6 +73,10 @@ class ClockSampler:
         self.thread = threading.Thread(target=self._run, daemon=True)
         self.thread.start()
 
+    def begin_region(self):
+        """Drop what was sampled before the timed region."""
+        self.samples.clear()
+
     def _run(self):
         nv = self.nv
         while not self._stop.is_set():
@@ -224,13 +228,19 @@ def run_ours(args, cfg, workload_desc):
     L.status()
     kept = int(L.routing()["count"].sum())
     L.set_profiling(True)      # stage stopwatch: events inside the timed region, averaged over its steps
-    barrier()
+    # the sampler thread starts before the barrier: NVML start-up on rank 0 must not delay its first timed step
+    # (the other ranks would wait for it inside their timed region)
     sampler = ClockSampler(local_rank) if rank == 0 else None
+    barrier()
+    if sampler:
+        sampler.begin_region()
     launches0 = L.launch_count
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record()
+    t_host0 = time.perf_counter()
     for _ in range(args.steps):
         L.forward(x, wg, w1, w3, w2, out=out, scales=scales)
+    host_enqueue_ms = (time.perf_counter() - t_host0) * 1e3 / args.steps   # host time to enqueue one forward
     ev1.record()
     barrier()
     clocks = sampler.stop() if sampler else None
@@ -332,7 +342,7 @@ def run_ours(args, cfg, workload_desc):
                 "roofline": roofline_fp8 if fp8 else roofline,
                 "layer_roofline": {"seconds": t_roof, **terms, "frac": t_roof / (ms / args.steps * 1e-3),
                                    "constants": "2250 TFLOP/s dense bf16, 8 TB/s HBM, 900 GB/s NVLink per direction"},
-                "stage_ms": stage}
+                "stage_ms": stage, "host_enqueue_ms_per_step": host_enqueue_ms}
         if world == 1 and not args.no_cpu_baseline:
             from oracle import moe_oracle as oracle
             oracle.build()

@@ -1,23 +1,7 @@
 // aristos_expert_ffn: argument checks and the per-dtype kernels behind the C ABI.
 #include "common.cuh"
+#include "ffn_internal.h"
 #include "ptx_sm100.cuh"
-
-namespace aristos {
-aristos_status_t expert_ffn_tc_sm100(const void* xg, const int32_t* count, int groups, int rows_per_group,
-                                        int experts, const void* w1, const void* w3, const void* w2, const void* b1,
-                                        const void* b3, const void* b2, void* h_scratch, void* y, int H, int I,
-                                        int hidden_act, int fmt, int row_begin, int row_end, int sm_limit,
-                                        int32_t* dev_status, cudaStream_t st);
-aristos_status_t expert_ffn_f32_simt(const void* xg, const int32_t* count, int groups, int rows_per_group, int experts,
-                                     const void* w1, const void* w3, const void* w2, const void* b1, const void* b3,
-                                     const void* b2, void* h_scratch, void* y, int H, int I, int hidden_act,
-                                     int row_begin, int row_end, cudaStream_t st);
-aristos_status_t expert_ffn_fp8_sm100(const void* xq, const float* sx, const int32_t* count, int groups,
-                                      int rows_per_group, int experts, const void* w1q, const float* s1,
-                                      const void* w3q, const float* s3, const void* w2q, const float* s2, void* h,
-                                      void* hq, float* sh, void* y, int H, int I, int hidden_act, int row_begin,
-                                      int row_end, int sm_limit, int32_t* dev_status, cudaStream_t st);
-}  // namespace aristos
 
 using namespace aristos;
 

@@ -30,6 +30,7 @@
 #include <cstring>
 
 #include "common.cuh"
+#include "ffn_internal.h"
 #include "ptx_sm100.cuh"
 #include "tensor_map.cuh"
 
@@ -71,6 +72,15 @@ struct FfnGemmParams {
     const void* bias0;      // (experts, N) added to the accumulator before the activation, or nullptr
     const void* bias1;      // SwiGLU: bias of the second (up) projection, or nullptr
     int32_t* dev_status;
+    int peer_world;         // > 0: output tiles go straight to the rank that sent the rows (group g came from rank
+    int peer_rank;          //      g / experts) through PeerOutMaps, as group peer_rank * experts + g % experts
+};
+
+// One output tensor map per source rank: that rank's buffer for returned expert outputs, (all experts, rows, N),
+// mapped into this process. The epilogue's TMA store then IS the return all-to-all, tile by tile.
+constexpr int MAX_PEER_OUT = 8;
+struct PeerOutMaps {
+    CUtensorMap m[MAX_PEER_OUT];
 };
 
 __device__ __forceinline__ uint32_t pack_16bit(float a, float b, int fmt) {
@@ -123,8 +133,8 @@ __device__ __forceinline__ void add_bias32(uint32_t (&acc)[32], const void* bias
 // the group's valid rows stores nothing; a partly valid tile stores all of its 128 rows (the extra rows hold
 // unspecified values, never past the group's row capacity: the tensor map clips them).
 template <bool PAIR>
-__device__ __forceinline__ void epilogue_tile(const FfnGemmParams& p, const CUtensorMap* tmOut, int g, int m0, int n0,
-                                              int row_in_tile, uint32_t taddr, uint32_t tempty, int lane,
+__device__ __forceinline__ void epilogue_tile(const FfnGemmParams& p, const CUtensorMap* tmOut, int out_g, int g, int m0,
+                                              int n0, int row_in_tile, uint32_t taddr, uint32_t tempty, int lane,
                                               int epi_tid, uint32_t staging) {
     const int row_limit = min(p.count[g], p.row_end);
     const bool tile_live = m0 < row_limit;
@@ -176,7 +186,7 @@ __device__ __forceinline__ void epilogue_tile(const FfnGemmParams& p, const CUte
         ptx::fence_proxy_async_shared();
         ptx::named_barrier_sync(1, EPI_THREADS);
         if (epi_tid == 0 && tile_live && n0 + c * 64 < p.N) {
-            ptx::tma_store_3d(tmOut, staging, n0 + c * 64, m0, g);
+            ptx::tma_store_3d(tmOut, staging, n0 + c * 64, m0, out_g);
             ptx::bulk_commit_group();
         }
     }
@@ -185,9 +195,9 @@ __device__ __forceinline__ void epilogue_tile(const FfnGemmParams& p, const CUte
 // The same for fp32 output (tf32 path): a 128-byte staging row holds 32 columns, so the tile leaves in 32-column
 // chunks.
 template <bool PAIR>
-__device__ __forceinline__ void epilogue_tile_f32(const FfnGemmParams& p, const CUtensorMap* tmOut, int g, int m0,
-                                                  int n0, int row_in_tile, uint32_t taddr, uint32_t tempty, int lane,
-                                                  int epi_tid, uint32_t staging) {
+__device__ __forceinline__ void epilogue_tile_f32(const FfnGemmParams& p, const CUtensorMap* tmOut, int out_g, int g,
+                                                  int m0, int n0, int row_in_tile, uint32_t taddr, uint32_t tempty,
+                                                  int lane, int epi_tid, uint32_t staging) {
     const int row_limit = min(p.count[g], p.row_end);
     const bool tile_live = m0 < row_limit;
     const int nchunk = p.gated ? 4 : 8;
@@ -230,7 +240,7 @@ __device__ __forceinline__ void epilogue_tile_f32(const FfnGemmParams& p, const 
         ptx::fence_proxy_async_shared();
         ptx::named_barrier_sync(1, EPI_THREADS);
         if (epi_tid == 0 && tile_live && n0 + col < p.N) {
-            ptx::tma_store_3d(tmOut, staging, n0 + col, m0, g);
+            ptx::tma_store_3d(tmOut, staging, n0 + col, m0, out_g);
             ptx::bulk_commit_group();
         }
     }
@@ -239,7 +249,7 @@ __device__ __forceinline__ void epilogue_tile_f32(const FfnGemmParams& p, const 
 __global__ void __launch_bounds__(FFN_THREADS, 1)
 ffn_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB0,
                         const __grid_constant__ CUtensorMap tmB1, const __grid_constant__ CUtensorMap tmOut,
-                        const FfnGemmParams p) {
+                        const __grid_constant__ PeerOutMaps peers, const FfnGemmParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const uint32_t staging = ptx::smem_u32(smem + STAGES * STAGE_BYTES);
@@ -392,10 +402,17 @@ ffn_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
             if (!ok) break;
             ptx::tcgen05_fence_after();
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
+            const CUtensorMap* om = &tmOut;
+            int og = g;
+            if (p.peer_world > 0) {
+                const int src = g / p.experts;
+                om = &peers.m[src];
+                og = p.peer_rank * p.experts + (g - src * p.experts);
+            }
             if (p.fmt == FMT_TF32)
-                epilogue_tile_f32<false>(p, &tmOut, g, m0, n0, row_in_tile, taddr, bar_tempty + 8 * buf, lane, epi_tid, staging);
+                epilogue_tile_f32<false>(p, om, og, g, m0, n0, row_in_tile, taddr, bar_tempty + 8 * buf, lane, epi_tid, staging);
             else
-                epilogue_tile<false>(p, &tmOut, g, m0, n0, row_in_tile, taddr, bar_tempty + 8 * buf, lane, epi_tid, staging);
+                epilogue_tile<false>(p, om, og, g, m0, n0, row_in_tile, taddr, bar_tempty + 8 * buf, lane, epi_tid, staging);
         }
         if (epi_tid == 0) ptx::bulk_wait_group0();
     }
@@ -422,7 +439,7 @@ constexpr int PBM = 256;                                         // rows per pai
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(FFN_THREADS, 1)
 ffn_grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB0,
                              const __grid_constant__ CUtensorMap tmB1, const __grid_constant__ CUtensorMap tmOut,
-                             const FfnGemmParams p) {
+                             const __grid_constant__ PeerOutMaps peers, const FfnGemmParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const uint32_t staging = ptx::smem_u32(smem + P_STAGES * P_STAGE_BYTES);
@@ -582,10 +599,17 @@ ffn_grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gr
             if (!ok) break;
             ptx::tcgen05_fence_after();
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
+            const CUtensorMap* om = &tmOut;
+            int og = g;
+            if (p.peer_world > 0) {
+                const int src = g / p.experts;
+                om = &peers.m[src];
+                og = p.peer_rank * p.experts + (g - src * p.experts);
+            }
             if (p.fmt == FMT_TF32)
-                epilogue_tile_f32<true>(p, &tmOut, g, m0, n0, row_in_tile, taddr, tempty0 + 8 * buf, lane, epi_tid, staging);
+                epilogue_tile_f32<true>(p, om, og, g, m0, n0, row_in_tile, taddr, tempty0 + 8 * buf, lane, epi_tid, staging);
             else
-                epilogue_tile<true>(p, &tmOut, g, m0, n0, row_in_tile, taddr, tempty0 + 8 * buf, lane, epi_tid, staging);
+                epilogue_tile<true>(p, om, og, g, m0, n0, row_in_tile, taddr, tempty0 + 8 * buf, lane, epi_tid, staging);
         }
         if (epi_tid == 0) ptx::bulk_wait_group0();
     }
@@ -620,8 +644,8 @@ bool use_pair_tiles(int window_rows) {
     return window_rows >= 1024;
 }
 
-aristos_status_t launch_gemm(const void* A, const void* B0, const void* B1, const FfnGemmParams& p, int grid_limit,
-                             cudaStream_t st) {
+aristos_status_t launch_gemm(const void* A, const void* B0, const void* B1, const FfnGemmParams& p,
+                             const PeerOutMaps& peers, int grid_limit, cudaStream_t st) {
     CUtensorMap tmA, tmB0, tmB1, tmOut;
     ARISTOS_TRY(make_map_3d(&tmA, A, p.K, p.rows_per_group, p.groups, p.fmt));
     ARISTOS_TRY(make_map_3d(&tmB0, B0, p.K, p.N, p.experts, p.fmt));
@@ -656,14 +680,14 @@ aristos_status_t launch_gemm(const void* A, const void* B0, const void* B1, cons
         int pairs = sms / 2 < max_clusters ? sms / 2 : max_clusters;
         if (bound < pairs) pairs = (int)bound;
         if (pairs <= 0) return ARISTOS_OK;
-        ffn_grouped_gemm_pair_kernel<<<2 * pairs, FFN_THREADS, P_SMEM_BYTES, st>>>(tmA, tmB0, tmB1, tmOut, p);
+        ffn_grouped_gemm_pair_kernel<<<2 * pairs, FFN_THREADS, P_SMEM_BYTES, st>>>(tmA, tmB0, tmB1, tmOut, peers, p);
     } else {
         ARISTOS_CUDA_TRY(cudaFuncSetAttribute(ffn_grouped_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                               SMEM_BYTES));
         const int64_t bound = (int64_t)p.groups * ceil_div(window, BM) * ceil_div(p.N, out_w);
         const int grid = (int)(bound < sms ? bound : sms);
         if (grid <= 0) return ARISTOS_OK;
-        ffn_grouped_gemm_kernel<<<grid, FFN_THREADS, SMEM_BYTES, st>>>(tmA, tmB0, tmB1, tmOut, p);
+        ffn_grouped_gemm_kernel<<<grid, FFN_THREADS, SMEM_BYTES, st>>>(tmA, tmB0, tmB1, tmOut, peers, p);
     }
     ARISTOS_COUNT_LAUNCH();
     ARISTOS_CUDA_TRY(cudaGetLastError());
@@ -676,7 +700,12 @@ aristos_status_t expert_ffn_tc_sm100(const void* xg, const int32_t* count, int g
                                         int experts, const void* w1, const void* w3, const void* w2, const void* b1,
                                         const void* b3, const void* b2, void* h_scratch, void* y, int H, int I,
                                         int hidden_act, int fmt, int row_begin, int row_end, int sm_limit,
-                                        int32_t* dev_status, cudaStream_t st) {
+                                        int32_t* dev_status, cudaStream_t st, void* const* peer_y, int peer_world,
+                                        int peer_rank) {
+    if (peer_world > MAX_PEER_OUT || (peer_world > 0 && (!peer_y || groups != peer_world * experts))) {
+        set_last_error("expert_ffn: peer output needs world <= %d and groups == world * experts", MAX_PEER_OUT);
+        return ARISTOS_ERR_INVALID_ARG;
+    }
     if (groups > MAX_GROUPS) { set_last_error("expert_ffn: more than %d row groups", MAX_GROUPS); return ARISTOS_ERR_CONFIG; }
     if (H % BK != 0 || I % BK != 0) { set_last_error("expert_ffn: H and I must be multiples of 64"); return ARISTOS_ERR_CONFIG; }
     if (row_begin % BM != 0) { set_last_error("expert_ffn: row_begin must be a multiple of 128"); return ARISTOS_ERR_INVALID_ARG; }
@@ -698,7 +727,8 @@ aristos_status_t expert_ffn_tc_sm100(const void* xg, const int32_t* count, int g
     p.out = h_scratch;
     p.bias0 = b1;
     p.bias1 = gated ? b3 : nullptr;
-    ARISTOS_TRY(launch_gemm(xg, w1, gated ? w3 : w1, p, sm_limit, st));
+    static const PeerOutMaps no_peers{};
+    ARISTOS_TRY(launch_gemm(xg, w1, gated ? w3 : w1, p, no_peers, sm_limit, st));
     // down-projection: y = h * W2^T
     p.N = H;
     p.K = I;
@@ -707,7 +737,18 @@ aristos_status_t expert_ffn_tc_sm100(const void* xg, const int32_t* count, int g
     p.out = y;
     p.bias0 = b2;
     p.bias1 = nullptr;
-    ARISTOS_TRY(launch_gemm(h_scratch, w2, w2, p, sm_limit, st));
+    if (peer_world > 0) {
+        // every source rank's return buffer holds (all experts, rows_per_group, H); rows of group (src, e_local) land
+        // in rank src's block peer_rank * experts + e_local
+        PeerOutMaps peers{};
+        for (int d = 0; d < peer_world; ++d)
+            ARISTOS_TRY(make_map_3d(&peers.m[d], peer_y[d], H, rows_per_group, peer_world * experts, fmt));
+        p.peer_world = peer_world;
+        p.peer_rank = peer_rank;
+        ARISTOS_TRY(launch_gemm(h_scratch, w2, w2, p, peers, sm_limit, st));
+        return ARISTOS_OK;
+    }
+    ARISTOS_TRY(launch_gemm(h_scratch, w2, w2, p, no_peers, sm_limit, st));
     return ARISTOS_OK;
 }
 

@@ -16,6 +16,7 @@
 #include "ep_nccl.h"
 #include "ep_p2p.h"
 #include "ep_kernels.h"
+#include "ffn_internal.h"
 
 namespace aristos {
 aristos_status_t dispatch_impl(const int32_t* topk_idx, int S, int k, int E, int cap, int32_t* count,
@@ -64,6 +65,7 @@ struct aristos_moe {
     int chunks = 1, chunk_rows = 0, ffn_sm_limit = 0;
     bool ep_direct = false;                  // p2p: gather/return kernels store through peer pointers
     int direct_windows = 1;                  // row windows of the direct mode (gather / GEMMs / return pipelined)
+    bool fused_return = false;               // direct mode: the down projection's epilogue stores into the source ranks
     int64_t launches = 0;
     const void *b1 = nullptr, *b3 = nullptr, *b2 = nullptr;   // optional expert biases (caller-owned, device)
     // stage stopwatch
@@ -257,6 +259,12 @@ aristos_status_t aristos_moe_create(const aristos_config_t* cfg, int rank, int w
                 if (const char* env = getenv("ARISTOS_EP_DIRECT_WINDOWS"))
                     if (atoi(env) >= 1) L->direct_windows = atoi(env);
                 L->direct_windows = std::min(L->direct_windows, (int)L->ev_out.size());
+                // the tensor-core GEMM returns its output tiles itself (TMA stores through peer mappings);
+                // ARISTOS_EP_FUSED_RETURN=0 keeps the separate return kernel
+                const char* fr = getenv("ARISTOS_EP_FUSED_RETURN");
+                const int tdt = cfg->torch_dtype;
+                L->fused_return = L->ep_direct && world <= 8 && !(fr && !strcmp(fr, "0")) &&
+                                  (tdt == ARISTOS_DTYPE_BF16 || tdt == ARISTOS_DTYPE_F16 || tdt == ARISTOS_DTYPE_TF32);
             }
             else if (L->fp8 || (tr && !strcmp(tr, "p2p"))) { aristos_moe_destroy(L); return ps; }
         }
@@ -399,6 +407,17 @@ aristos_status_t aristos_moe_forward(aristos_moe_t* L, const void* x, const void
             const int r0 = c * win_rows, r1 = std::min(L->cap, r0 + win_rows);
             if (r0 >= r1) break;
             ARISTOS_TRY(ep_p2p_wait(L->p2p, EP_FLAG_IN, c, st));
+            if (L->fused_return) {
+                // the epilogue of the down projection IS the return all-to-all: each output tile is stored into the
+                // buffer of the rank its rows came from while the tensor cores work on the next tile
+                if (L->cfg.hidden_act == ARISTOS_ACT_SWIGLU && !w3) { set_last_error("forward: SwiGLU needs w3"); return ARISTOS_ERR_INVALID_ARG; }
+                const int fmt = dt == ARISTOS_DTYPE_BF16 ? 0 : (dt == ARISTOS_DTYPE_F16 ? 1 : 2);
+                ARISTOS_TRY(expert_ffn_tc_sm100(L->xr, L->rcount, L->groups, L->cap, L->E_local, w1, w3, w2, L->b1, L->b3,
+                                                L->b2, L->h, L->yr, L->H, L->I, L->cfg.hidden_act, fmt, r0, r1, 0,
+                                                L->dev_status, st, y_dst.p, L->world, L->rank));
+                ARISTOS_TRY(ep_p2p_signal(L->p2p, EP_FLAG_RET, c, st));
+                continue;
+            }
             ARISTOS_TRY(aristos_expert_ffn_bias(L->xr, L->rcount, L->groups, L->cap, L->E_local, w1, w3, w2, L->b1,
                                                 L->b3, L->b2, L->h, L->yr, L->H, L->I, L->cfg.hidden_act, dt, r0, r1, 0,
                                                 L->dev_status, st));
