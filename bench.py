@@ -51,7 +51,7 @@ def read_peaks():
 
 
 class ClockSampler:
-    """Samples SM clock, power and throttle reasons of one GPU every 10 ms during the timed region through NVML
+    """Samples SM clock, power and throttle reasons of one GPU every 2 ms during the timed region through NVML
     (read-only queries; nothing is set)."""
     REASONS = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20, "sw_power_cap": 0x4}
 
@@ -88,7 +88,7 @@ class ClockSampler:
             except Exception as e:
                 self.error = repr(e)
                 return
-            time.sleep(0.01)
+            time.sleep(0.002)
 
     def stop(self) -> dict:
         if self.thread is None:

@@ -49,6 +49,10 @@ struct Fp8GemmParams {
     const float* sb1;     // SwiGLU: scales of the up projection's weights
     __nv_bfloat16* out;   // [groups * rows_per_group][N]
     int32_t* dev_status;
+    // peer_world > 0: rows of group g = src * experts + e are stored into rank src's buffer peer_out[src]
+    // ((peer_world * experts, rows_per_group, N), mapped into this process) as group peer_rank * experts + e
+    int peer_world, peer_rank;
+    __nv_bfloat16* peer_out[8];
 };
 
 __device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
@@ -246,7 +250,14 @@ ffn_fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
             }
             if (!ok) break;
             if (row_ok) {
-                __nv_bfloat16* orow = p.out + ((size_t)g * p.rows_per_group + row) * p.N + n0;
+                __nv_bfloat16* obase = p.out;
+                int og = g;
+                if (p.peer_world > 0) {            // the store is the return all-to-all: straight into the source rank
+                    const int src = g / p.experts;
+                    obase = p.peer_out[src];
+                    og = p.peer_rank * p.experts + (g - src * p.experts);
+                }
+                __nv_bfloat16* orow = obase + ((size_t)og * p.rows_per_group + row) * p.N + n0;
                 if (p.gated) {
                     // gate columns [32*half, +32) pair with up columns [64 + 32*half, +32): 32 outputs
                     uint32_t o[16];
@@ -441,7 +452,12 @@ aristos_status_t expert_ffn_fp8_sm100(const void* xq, const float* sx, const int
                                       int rows_per_group, int experts, const void* w1q, const float* s1,
                                       const void* w3q, const float* s3, const void* w2q, const float* s2, void* h,
                                       void* hq, float* sh, void* y, int H, int I, int hidden_act, int row_begin,
-                                      int row_end, int sm_limit, int32_t* dev_status, cudaStream_t st) {
+                                      int row_end, int sm_limit, int32_t* dev_status, cudaStream_t st,
+                                      void* const* peer_y, int peer_world, int peer_rank) {
+    if (peer_world > 8 || (peer_world > 0 && (!peer_y || groups != peer_world * experts))) {
+        set_last_error("expert_ffn(fp8): peer output needs world <= 8 and groups == world * experts");
+        return ARISTOS_ERR_INVALID_ARG;
+    }
     if (groups > F8_MAX_GROUPS) { set_last_error("expert_ffn(fp8): more than %d row groups", F8_MAX_GROUPS); return ARISTOS_ERR_CONFIG; }
     if (H % 128 != 0 || I % 128 != 0) { set_last_error("expert_ffn(fp8): H and I must be multiples of 128"); return ARISTOS_ERR_CONFIG; }
     if (row_begin % F8_BM != 0) { set_last_error("expert_ffn(fp8): row_begin must be a multiple of 128"); return ARISTOS_ERR_INVALID_ARG; }
@@ -465,6 +481,9 @@ aristos_status_t expert_ffn_fp8_sm100(const void* xq, const float* sx, const int
     p.N = H; p.K = I; p.gated = 0; p.act = ARISTOS_ACT_IDENTITY;
     p.sa = sh; p.sb0 = s2; p.sb1 = s2;
     p.out = static_cast<__nv_bfloat16*>(y);
+    p.peer_world = peer_world;
+    p.peer_rank = peer_rank;
+    for (int d = 0; d < peer_world; ++d) p.peer_out[d] = static_cast<__nv_bfloat16*>(peer_y[d]);
     ARISTOS_TRY(launch_fp8_gemm(hq, w2q, w2q, p, sm_limit, st));
     ARISTOS_CUDA_TRY(cudaGetLastError());
     return ARISTOS_OK;

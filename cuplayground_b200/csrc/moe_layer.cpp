@@ -360,11 +360,19 @@ aristos_status_t aristos_moe_forward(aristos_moe_t* L, const void* x, const void
         ARISTOS_TRY(ep_p2p_signal(L->p2p, EP_FLAG_IN, 0, st));
         PROF_MARK(2);
         ARISTOS_TRY(ep_p2p_wait(L->p2p, EP_FLAG_IN, 0, st));
-        ARISTOS_TRY(aristos_expert_ffn_fp8(L->xgq, L->sxg, L->rcount, L->groups, L->cap, L->E_local, w1, s1, w3, s3, w2,
-                                           s2, L->h, L->hq, L->sh, L->yr, L->H, L->I, L->cfg.hidden_act, 0, L->cap, 0,
-                                           L->dev_status, st));
-        ARISTOS_TRY(return_rows_to_peers(L->yr, L->rcount, L->groups, L->E_local, L->cap, (size_t)L->H * 2, L->rank, 0,
-                                         L->cap, y_dst, st));
+        if (L->world <= 8 && !(getenv("ARISTOS_EP_FUSED_RETURN") && !strcmp(getenv("ARISTOS_EP_FUSED_RETURN"), "0"))) {
+            // the down projection stores its valid output rows straight into the ranks they came from
+            if (swiglu && !w3) { set_last_error("forward: SwiGLU needs w3"); return ARISTOS_ERR_INVALID_ARG; }
+            ARISTOS_TRY(expert_ffn_fp8_sm100(L->xgq, L->sxg, L->rcount, L->groups, L->cap, L->E_local, w1, s1, w3, s3, w2,
+                                             s2, L->h, L->hq, L->sh, L->yr, L->H, L->I, L->cfg.hidden_act, 0, L->cap, 0,
+                                             L->dev_status, st, y_dst.p, L->world, L->rank));
+        } else {
+            ARISTOS_TRY(aristos_expert_ffn_fp8(L->xgq, L->sxg, L->rcount, L->groups, L->cap, L->E_local, w1, s1, w3, s3,
+                                               w2, s2, L->h, L->hq, L->sh, L->yr, L->H, L->I, L->cfg.hidden_act, 0,
+                                               L->cap, 0, L->dev_status, st));
+            ARISTOS_TRY(return_rows_to_peers(L->yr, L->rcount, L->groups, L->E_local, L->cap, (size_t)L->H * 2, L->rank,
+                                             0, L->cap, y_dst, st));
+        }
         ARISTOS_TRY(ep_p2p_signal(L->p2p, EP_FLAG_RET, 0, st));
         ARISTOS_TRY(ep_p2p_wait(L->p2p, EP_FLAG_RET, 0, st));
     } else if (!(L->p2p && L->ep_direct)) {
