@@ -15,6 +15,7 @@ def _worker(rank, world, uid, S, H, I, E, k, cf, act, transport, q):
     try:
         os.environ["ARISTOS_EP_TRANSPORT"] = transport.split("-")[0]
         os.environ["ARISTOS_EP_MODE"] = "windows" if transport.endswith("-windows") else "direct"
+        os.environ["ARISTOS_EP_FUSED_RETURN"] = "0" if transport.endswith("-returnkernel") else "1"
         transport = transport.split("-")[0]
         sys.path.insert(0, ROOT)
         sys.path.insert(0, os.path.join(ROOT, "tests"))
@@ -79,9 +80,9 @@ def _run(world, S, H, I, E, k, cf, act, transport):
     assert not bad, bad[0][1]
 
 
-# peer memory with gather/return kernels storing through peer pointers (default), peer memory with copy-engine
-# pushes of padded row windows, and NCCL send/recv
-TRANSPORTS = ["p2p", "p2p-windows", "nccl"]
+# peer memory with the gather kernel and the down projection's epilogue storing through peer mappings (default),
+# the same with a separate return kernel, peer memory with copy-engine pushes of padded row windows, NCCL send/recv
+TRANSPORTS = ["p2p", "p2p-returnkernel", "p2p-windows", "nccl"]
 
 
 @pytest.mark.parametrize("transport", TRANSPORTS)
