@@ -15,7 +15,8 @@ def _worker(rank, world, uid, S, H, I, E, k, cf, act, transport, q):
     try:
         os.environ["ARISTOS_EP_TRANSPORT"] = transport.split("-")[0]
         os.environ["ARISTOS_EP_MODE"] = "windows" if transport.endswith("-windows") else "direct"
-        os.environ["ARISTOS_EP_FUSED_RETURN"] = "0" if transport.endswith("-returnkernel") else "1"
+        os.environ["ARISTOS_EP_FUSED_RETURN"] = "0" if "-returnkernel" in transport else "1"
+        os.environ["ARISTOS_EP_DIRECT_WINDOWS"] = "2" if "-2win" in transport else "1"
         transport = transport.split("-")[0]
         sys.path.insert(0, ROOT)
         sys.path.insert(0, os.path.join(ROOT, "tests"))
@@ -90,7 +91,7 @@ def test_expert_parallel_2gpu_single_window(transport):
     _run(2, S=1024, H=256, I=512, E=8, k=2, cf=1.25, act=2, transport=transport)       # cap 320: one row window
 
 
-@pytest.mark.parametrize("transport", TRANSPORTS)
+@pytest.mark.parametrize("transport", TRANSPORTS + ["p2p-2win", "p2p-returnkernel-2win"])
 def test_expert_parallel_2gpu_four_windows(transport):
     _run(2, S=4096, H=128, I=256, E=4, k=2, cf=1.0, act=1, transport=transport)        # cap 2048: four windows
 
