@@ -1,8 +1,9 @@
-// Expert-parallel exchange over peer memory: rows are pushed into the destination GPU's buffers by the copy engines
-// (cudaMemcpy2DAsync between CUDA-IPC mapped allocations, NVLink, no SM involved), arrival is published by a
-// one-warp kernel that stores an epoch number into the destination's flag word, and consumers order their streams
-// behind those flags with stream memory operations (cuStreamWaitValue32). Nothing on this path occupies SMs for the
-// duration of a transfer, so the persistent expert GEMMs keep the whole GPU while rows travel.
+// Expert-parallel exchange over peer memory: one exchange region per rank (flag words | received counts | received
+// rows | returned outputs | scales), mapped into every other rank through CUDA IPC. Rows reach it either by kernels
+// that store through the peer mappings (the gather kernel of ep_kernels.cu, the expert GEMM's output tiles) or by the
+// copy engines (cudaMemcpy2DAsync of row windows); arrival is published by a one-warp kernel that stores an epoch
+// number into the destination's flag word, and consumers order their streams behind those flags with stream memory
+// operations (cuStreamWaitValue32). No kernel spins on a peer.
 #pragma once
 
 #include <cuda_runtime.h>

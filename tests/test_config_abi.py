@@ -122,3 +122,19 @@ def test_compute_entry_points_fail_loudly_without_a_device(cp):
     h = C.c_void_p()
     st = cp._lib.load().aristos_moe_create(C.byref(s), 0, 1, None, C.byref(h))
     assert st == 4, "aristos_moe_create must report ARISTOS_ERR_CUDA without a device"
+
+
+def test_gate_scratch_bytes(cp):
+    """Scratch of the screened gate: the expert norms plus 16 slices of S x E partial logits, 256-byte granules."""
+    lib = cp._lib.load()
+    assert lib.aristos_gate_scratch_bytes(0, 128) == 0 and lib.aristos_gate_scratch_bytes(128, 0) == 0
+    n = lib.aristos_gate_scratch_bytes(8192, 128)
+    assert n % 256 == 0 and n >= 1024 + 16 * 8192 * 128 * 4
+    assert lib.aristos_gate_scratch_bytes(4096, 256) >= lib.aristos_gate_scratch_bytes(4096, 128)
+
+
+def test_status_strings_cover_every_code(cp):
+    lib = cp._lib.load()
+    names = {lib.aristos_status_str(i).decode() for i in range(12)}
+    assert len(names) == 12 and "unknown status" not in names
+    assert lib.aristos_status_str(99).decode() == "unknown status"
