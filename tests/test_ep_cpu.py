@@ -132,6 +132,65 @@ def test_expert_parallel_on_cpu_ranks(world, E, S, k, cf, act):
     assert not bad, bad[0][1]
 
 
+def _toy_worker(rank, world, port, q):
+    try:
+        sys.path.insert(0, ROOT)
+        import torch
+        import torch.distributed as dist
+        from oracle import moe_oracle as O
+        import cuplayground_b200 as cp
+
+        lib = cp._lib.load()
+        dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+        M = N = K = 2
+        blk = M * K
+        # the reference's fill (auditorium/overlap.cuh:197-204): world input blocks rank + i, one weight rank + j + 4
+        mk_a = lambda r: (r + np.arange(world * blk, dtype=np.float32)).reshape(world, M, K)
+        mk_b = lambda r: (r + 4 + np.arange(N * K, dtype=np.float32)).reshape(N, K)
+        a, b = mk_a(rank), mk_b(rank)
+        plan = _plan(lib, rank, world, 1, blk * 4, 0, blk * 4)
+        # dispatch: block d of every rank goes to rank d (put-with-signal of overlap.cuh:94-101)
+        recv = np.zeros_like(a)
+        _exchange(dist, torch, plan, a, recv, rank)
+        # first stage: GEMM of every received block with the local weight (overlap.cuh:110-115)
+        c1 = np.stack([O.gemm_bias_act(recv[s], b, None, 3) for s in range(world)])
+        # return (overlap.cuh:124-127), then the fused GEMM + ReLU of the second stage (overlap.cuh:138-146)
+        back = np.zeros_like(c1)
+        _exchange(dist, torch, plan, c1, back, rank)
+        c2 = np.stack([O.gemm_bias_act(back[s], b, None, 0) for s in range(world)])
+        # recomputed without any exchange: what rank d did to this rank's block d, then this rank's second stage
+        for d in range(world):
+            first = mk_a(rank)[d] @ mk_b(d).T
+            np.testing.assert_array_equal(back[d], first)
+            np.testing.assert_array_equal(c2[d], np.maximum(first @ b.T, 0.0))
+        dist.barrier()
+        dist.destroy_process_group()
+        q.put((rank, "ok"))
+    except Exception as e:      # pragma: no cover - reported to the parent
+        import traceback
+        q.put((rank, "".join(traceback.format_exception(e))))
+
+
+def test_reference_overlap_prototype_toy_on_two_ranks():
+    """The reference's two-stage exchange/GEMM toy (overlapPrototype: 2x2x2 blocks filled with rank + i and
+    rank + j + 4) replayed on CPU ranks through the product's exchange plan; the reference records no expected
+    values, so every rank checks against a recomputation that involves no exchange."""
+    import torch.multiprocessing as mp
+    from cuplayground_b200 import build
+    build.build_library()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_toy_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=120) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    bad = [r for r in results if r[1] != "ok"]
+    assert not bad, bad[0][1]
+
+
 def test_exchange_plan_is_a_permutation():
     """Every (destination rank, block) is written exactly once and sends pair up with receives."""
     import cuplayground_b200 as cp
