@@ -263,8 +263,9 @@ aristos_status_t aristos_moe_create(const aristos_config_t* cfg, int rank, int w
                 // ARISTOS_EP_FUSED_RETURN=0 keeps the separate return kernel
                 const char* fr = getenv("ARISTOS_EP_FUSED_RETURN");
                 const int tdt = cfg->torch_dtype;
-                L->fused_return = L->ep_direct && world <= 8 && !(fr && !strcmp(fr, "0")) &&
-                                  (tdt == ARISTOS_DTYPE_BF16 || tdt == ARISTOS_DTYPE_F16 || tdt == ARISTOS_DTYPE_TF32);
+                L->fused_return = world <= 8 && !(fr && !strcmp(fr, "0")) &&
+                                  (L->fp8 || (L->ep_direct && (tdt == ARISTOS_DTYPE_BF16 || tdt == ARISTOS_DTYPE_F16 ||
+                                                               tdt == ARISTOS_DTYPE_TF32)));
             }
             else if (L->fp8 || (tr && !strcmp(tr, "p2p"))) { aristos_moe_destroy(L); return ps; }
         }
@@ -360,7 +361,7 @@ aristos_status_t aristos_moe_forward(aristos_moe_t* L, const void* x, const void
         ARISTOS_TRY(ep_p2p_signal(L->p2p, EP_FLAG_IN, 0, st));
         PROF_MARK(2);
         ARISTOS_TRY(ep_p2p_wait(L->p2p, EP_FLAG_IN, 0, st));
-        if (L->world <= 8 && !(getenv("ARISTOS_EP_FUSED_RETURN") && !strcmp(getenv("ARISTOS_EP_FUSED_RETURN"), "0"))) {
+        if (L->fused_return) {
             // the down projection stores its valid output rows straight into the ranks they came from
             if (swiglu && !w3) { set_last_error("forward: SwiGLU needs w3"); return ARISTOS_ERR_INVALID_ARG; }
             ARISTOS_TRY(expert_ffn_fp8_sm100(L->xgq, L->sxg, L->rcount, L->groups, L->cap, L->E_local, w1, s1, w3, s3, w2,
