@@ -15,11 +15,19 @@ namespace {
 
 // Token-major gather into the owners' buffers: assignment (t, j) with slot e*cap + pos goes to rank e / E_local, row
 // ((src_rank*E_local + e % E_local)*cap + pos) of that rank's buffer; only positions in [pos_lo, pos_hi) are handled
-// (one row window of the pipeline). One warp per token, 16-byte lanes.
+// (one row window of the pipeline). One warp per token, 16-byte lanes. With count != nullptr the kernel also stores
+// the per-expert row counts into the owners' count lists (the same stream order publishes both).
 template <int MAXK>
 __global__ void __launch_bounds__(256)
 permute_rows_peer_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ slot_of, int S, int k, int row_vec,
-                         int E_local, int cap, int src_rank, int pos_lo, int pos_hi, PeerPtrs dst) {
+                         int E_local, int cap, int src_rank, int pos_lo, int pos_hi, PeerPtrs dst,
+                         const int32_t* __restrict__ count, int E, PeerPtrs count_dst) {
+    // the first CTA also delivers the row counts: count[e] becomes entry (src_rank, e % E_local) of the owner's list
+    if (count != nullptr && blockIdx.x == 0)
+        for (int e = threadIdx.x; e < E; e += blockDim.x) {
+            const int owner = e / E_local;
+            static_cast<int32_t*>(count_dst.p[owner])[src_rank * E_local + (e - owner * E_local)] = count[e];
+        }
     const int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (t >= S) return;
     uint4* rows[MAXK];
@@ -90,16 +98,18 @@ return_rows_peer_kernel(const uint4* __restrict__ y, const int32_t* __restrict__
 
 aristos_status_t permute_rows_to_peers(const void* x, const int32_t* slot_of, int S, int k, size_t row_bytes,
                                        int E_local, int cap, int src_rank, int pos_lo, int pos_hi, const PeerPtrs& dst,
-                                       cudaStream_t st) {
+                                       cudaStream_t st, const int32_t* count, int E, const PeerPtrs* count_dst) {
     if (row_bytes % 16 != 0 || k > 16) { set_last_error("peer gather: row bytes must be a multiple of 16, k <= 16"); return ARISTOS_ERR_INVALID_ARG; }
-    if (S == 0) return ARISTOS_OK;
+    if (count && !count_dst) { set_last_error("peer gather: counts without a destination"); return ARISTOS_ERR_INVALID_ARG; }
+    if (S == 0 && !count) return ARISTOS_OK;
     const int row_vec = (int)(row_bytes / 16);
-    const int grid = ceil_div(S, 8);
+    const int grid = S > 0 ? ceil_div(S, 8) : 1;
+    const PeerPtrs cd = count ? *count_dst : PeerPtrs{};
     const uint4* xs = static_cast<const uint4*>(x);
-    if (k <= 2) permute_rows_peer_kernel<2><<<grid, 256, 0, st>>>(xs, slot_of, S, k, row_vec, E_local, cap, src_rank, pos_lo, pos_hi, dst);
-    else if (k <= 4) permute_rows_peer_kernel<4><<<grid, 256, 0, st>>>(xs, slot_of, S, k, row_vec, E_local, cap, src_rank, pos_lo, pos_hi, dst);
-    else if (k <= 8) permute_rows_peer_kernel<8><<<grid, 256, 0, st>>>(xs, slot_of, S, k, row_vec, E_local, cap, src_rank, pos_lo, pos_hi, dst);
-    else permute_rows_peer_kernel<16><<<grid, 256, 0, st>>>(xs, slot_of, S, k, row_vec, E_local, cap, src_rank, pos_lo, pos_hi, dst);
+    if (k <= 2) permute_rows_peer_kernel<2><<<grid, 256, 0, st>>>(xs, slot_of, S, k, row_vec, E_local, cap, src_rank, pos_lo, pos_hi, dst, count, E, cd);
+    else if (k <= 4) permute_rows_peer_kernel<4><<<grid, 256, 0, st>>>(xs, slot_of, S, k, row_vec, E_local, cap, src_rank, pos_lo, pos_hi, dst, count, E, cd);
+    else if (k <= 8) permute_rows_peer_kernel<8><<<grid, 256, 0, st>>>(xs, slot_of, S, k, row_vec, E_local, cap, src_rank, pos_lo, pos_hi, dst, count, E, cd);
+    else permute_rows_peer_kernel<16><<<grid, 256, 0, st>>>(xs, slot_of, S, k, row_vec, E_local, cap, src_rank, pos_lo, pos_hi, dst, count, E, cd);
     ARISTOS_COUNT_LAUNCH();
     ARISTOS_CUDA_TRY(cudaGetLastError());
     return ARISTOS_OK;

@@ -14,10 +14,13 @@ struct PeerPtrs {
 };
 
 // Dispatch without a staging buffer: token row t goes, for each kept assignment whose position inside its expert lies
-// in [pos_lo, pos_hi), into the buffer of the rank that owns the expert.
+// in [pos_lo, pos_hi), into the buffer of the rank that owns the expert. With count != nullptr the same launch also
+// stores count[0 .. E) into the owners' received-count lists (count_dst: every rank's list), entry
+// src_rank * E_local + e % E_local.
 aristos_status_t permute_rows_to_peers(const void* x, const int32_t* slot_of, int S, int k, size_t row_bytes,
                                        int E_local, int cap, int src_rank, int pos_lo, int pos_hi, const PeerPtrs& dst,
-                                       cudaStream_t st);
+                                       cudaStream_t st, const int32_t* count = nullptr, int E = 0,
+                                       const PeerPtrs* count_dst = nullptr);
 // Valid rows [row_lo, row_hi) of the local expert outputs (groups x cap rows, count[g] valid) back into their source
 // ranks' buffers.
 aristos_status_t return_rows_to_peers(const void* y, const int32_t* count, int groups, int E_local, int cap,

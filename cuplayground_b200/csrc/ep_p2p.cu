@@ -127,7 +127,8 @@ void* ep_p2p_yg(EpP2P* p) { return p->local + p->off_yg; }
 void* ep_p2p_aux(EpP2P* p) { return p->local + p->off_aux; }
 
 void ep_p2p_peer_ptrs(EpP2P* p, int which, void** out) {
-    const size_t off = which == EP_BUF_XR ? p->off_xr : (which == EP_BUF_YG ? p->off_yg : p->off_aux);
+    const size_t off = which == EP_BUF_XR ? p->off_xr
+                       : (which == EP_BUF_YG ? p->off_yg : (which == EP_BUF_RCOUNT ? p->off_rcount : p->off_aux));
     for (int r = 0; r < p->world; ++r) out[r] = p->base[r] + off;
 }
 int32_t* ep_p2p_rcount(EpP2P* p) { return reinterpret_cast<int32_t*>(p->local + p->off_rcount); }

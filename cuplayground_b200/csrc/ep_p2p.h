@@ -29,7 +29,7 @@ void* ep_p2p_xr(EpP2P* p);
 void* ep_p2p_yg(EpP2P* p);
 void* ep_p2p_aux(EpP2P* p);   // third exchange buffer (the fp8 path keeps the received activation scales there)
 // Every rank's copy of one exchange buffer as mapped into this process (out[world]); kernels store through them.
-enum { EP_BUF_XR = 0, EP_BUF_YG = 1, EP_BUF_AUX = 2 };
+enum { EP_BUF_XR = 0, EP_BUF_YG = 1, EP_BUF_AUX = 2, EP_BUF_RCOUNT = 3 };
 constexpr int EP_MAX_RANKS = 16;
 void ep_p2p_peer_ptrs(EpP2P* p, int which, void** out);
 int32_t* ep_p2p_rcount(EpP2P* p);

@@ -353,11 +353,12 @@ aristos_status_t aristos_moe_forward(aristos_moe_t* L, const void* x, const void
         ep_p2p_peer_ptrs(L->p2p, EP_BUF_YG, y_dst.p);
         ep_p2p_begin(L->p2p);
         ARISTOS_TRY(aristos_quantize_fp8(x, 1, L->S, L->H, 1, ARISTOS_DTYPE_BF16, L->xq, L->sx, stream));
+        PeerPtrs count_dst;
+        ep_p2p_peer_ptrs(L->p2p, EP_BUF_RCOUNT, count_dst.p);
         ARISTOS_TRY(permute_rows_to_peers(L->xq, L->slot_of, L->S, L->k, (size_t)L->H, L->E_local, L->cap, L->rank, 0,
-                                          L->cap, rows_dst, st));
+                                          L->cap, rows_dst, st, L->count, L->E, &count_dst));
         ARISTOS_TRY(permute_rows_to_peers(L->sx, L->slot_of, L->S, L->k, (size_t)(L->H / 128) * 4, L->E_local, L->cap,
                                           L->rank, 0, L->cap, scales_dst, st));
-        ARISTOS_TRY(ep_p2p_push(L->p2p, EP_FLAG_COUNT, L->count, 1, (size_t)L->E_local * 4, 0, (size_t)L->E_local * 4, st));
         ARISTOS_TRY(ep_p2p_signal(L->p2p, EP_FLAG_IN, 0, st));
         PROF_MARK(2);
         ARISTOS_TRY(ep_p2p_wait(L->p2p, EP_FLAG_IN, 0, st));
@@ -391,26 +392,29 @@ aristos_status_t aristos_moe_forward(aristos_moe_t* L, const void* x, const void
         ARISTOS_TRY(aristos_expert_ffn_bias(L->xg, L->count, L->E, L->cap, L->E, w1, w3, w2, L->b1, L->b3, L->b2, L->h, L->yr, L->H, L->I,
                                        L->cfg.hidden_act, dt, 0, L->cap, 0, L->dev_status, st));
     } else if (L->p2p && L->ep_direct) {
-        // the gather IS the dispatch all-to-all: every kept row is stored straight into its expert's rank, the expert
-        // outputs come back the same way; only rows that exist travel. The light gather / return kernels run on the
-        // communication stream and share the SMs with the persistent GEMM grid, window by window.
-        PeerPtrs rows_dst, y_dst;
+        // the gather IS the dispatch all-to-all: every kept row is stored straight into its expert's rank (the row
+        // counts ride along in the same launch), the expert outputs come back the same way; only rows that exist
+        // travel. With one row window everything stays on the caller's stream; with more, the light gather / return
+        // kernels run on the communication stream and share the SMs with the persistent GEMM grid, window by window.
+        PeerPtrs rows_dst, y_dst, count_dst;
         ep_p2p_peer_ptrs(L->p2p, EP_BUF_XR, rows_dst.p);
         ep_p2p_peer_ptrs(L->p2p, EP_BUF_YG, y_dst.p);
+        ep_p2p_peer_ptrs(L->p2p, EP_BUF_RCOUNT, count_dst.p);
         const size_t row_bytes = (size_t)L->H * L->elt;
         const int nwin = L->direct_windows;
         const int win_rows = ceil_div(ceil_div(L->cap, nwin), 256) * 256;
+        cudaStream_t cs = nwin > 1 ? L->comm_stream : st;
         ep_p2p_begin(L->p2p);
-        ARISTOS_CUDA_TRY(cudaEventRecord(L->ev_dispatched, st));
-        ARISTOS_CUDA_TRY(cudaStreamWaitEvent(L->comm_stream, L->ev_dispatched, 0));
-        ARISTOS_TRY(ep_p2p_push(L->p2p, EP_FLAG_COUNT, L->count, 1, (size_t)L->E_local * 4, 0, (size_t)L->E_local * 4,
-                                L->comm_stream));
+        if (cs != st) {
+            ARISTOS_CUDA_TRY(cudaEventRecord(L->ev_dispatched, st));
+            ARISTOS_CUDA_TRY(cudaStreamWaitEvent(cs, L->ev_dispatched, 0));
+        }
         for (int c = 0; c < nwin; ++c) {
             const int r0 = c * win_rows, r1 = std::min(L->cap, r0 + win_rows);
             if (r0 >= r1) break;
             ARISTOS_TRY(permute_rows_to_peers(x, L->slot_of, L->S, L->k, row_bytes, L->E_local, L->cap, L->rank, r0, r1,
-                                              rows_dst, L->comm_stream));
-            ARISTOS_TRY(ep_p2p_signal(L->p2p, EP_FLAG_IN, c, L->comm_stream));
+                                              rows_dst, cs, c == 0 ? L->count : nullptr, L->E, &count_dst));
+            ARISTOS_TRY(ep_p2p_signal(L->p2p, EP_FLAG_IN, c, cs));
         }
         for (int c = 0; c < nwin; ++c) {
             const int r0 = c * win_rows, r1 = std::min(L->cap, r0 + win_rows);
@@ -430,11 +434,13 @@ aristos_status_t aristos_moe_forward(aristos_moe_t* L, const void* x, const void
             ARISTOS_TRY(aristos_expert_ffn_bias(L->xr, L->rcount, L->groups, L->cap, L->E_local, w1, w3, w2, L->b1,
                                                 L->b3, L->b2, L->h, L->yr, L->H, L->I, L->cfg.hidden_act, dt, r0, r1, 0,
                                                 L->dev_status, st));
-            ARISTOS_CUDA_TRY(cudaEventRecord(L->ev_out[c], st));
-            ARISTOS_CUDA_TRY(cudaStreamWaitEvent(L->comm_stream, L->ev_out[c], 0));
+            if (cs != st) {
+                ARISTOS_CUDA_TRY(cudaEventRecord(L->ev_out[c], st));
+                ARISTOS_CUDA_TRY(cudaStreamWaitEvent(cs, L->ev_out[c], 0));
+            }
             ARISTOS_TRY(return_rows_to_peers(L->yr, L->rcount, L->groups, L->E_local, L->cap, row_bytes, L->rank, r0, r1,
-                                             y_dst, L->comm_stream));
-            ARISTOS_TRY(ep_p2p_signal(L->p2p, EP_FLAG_RET, c, L->comm_stream));
+                                             y_dst, cs));
+            ARISTOS_TRY(ep_p2p_signal(L->p2p, EP_FLAG_RET, c, cs));
         }
         for (int c = 0; c < nwin; ++c)
             if (c * win_rows < L->cap) ARISTOS_TRY(ep_p2p_wait(L->p2p, EP_FLAG_RET, c, st));
