@@ -120,7 +120,7 @@ ffn_fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
             const int g = g0 + lane;
             int v = 0;
             if (g < p.groups) {
-                int rows = p.count[g] - p.row_begin;
+                int rows = p.count[ordered_group(g, p.groups, p.experts)] - p.row_begin;
                 rows = max(0, min(rows, window));
                 v = ((rows + F8_BM - 1) / F8_BM) * n_tiles;
             }
@@ -149,12 +149,13 @@ ffn_fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
             ptx::prefetch_tensormap(&tmB1);
             int stage = 0;
             uint32_t phase = 0;
-            int g = 0;
+            int vg = 0;
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-                while (tile >= prefix[g + 1]) ++g;
-                const int local = tile - prefix[g];
-                const int mt = (prefix[g + 1] - prefix[g]) / n_tiles;
+                while (tile >= prefix[vg + 1]) ++vg;
+                const int g = ordered_group(vg, p.groups, p.experts);
+                const int local = tile - prefix[vg];
+                const int mt = (prefix[vg + 1] - prefix[vg]) / n_tiles;
                 const int m0 = p.row_begin + (local % mt) * F8_BM;
                 const int n0 = (local / mt) * out_w;
                 const int e = g % p.experts;
@@ -207,13 +208,14 @@ ffn_fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
         const int quarter = warp & 3;                       // TMEM lanes this warp may read
         const int half = (warp - 2) >> 2;                   // 0: column chunks {0, 2}, 1: chunks {1, 3}
         const int row_in_tile = quarter * 32 + lane;
-        int g = 0, tbuf = 0;
+        int vg = 0, tbuf = 0;
         uint32_t tphase = 0;
         bool ok = true;
         for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-            while (tile >= prefix[g + 1]) ++g;
-            const int local = tile - prefix[g];
-            const int mt = (prefix[g + 1] - prefix[g]) / n_tiles;
+            while (tile >= prefix[vg + 1]) ++vg;
+            const int g = ordered_group(vg, p.groups, p.experts);
+            const int local = tile - prefix[vg];
+            const int mt = (prefix[vg + 1] - prefix[vg]) / n_tiles;
             const int m0 = p.row_begin + (local % mt) * F8_BM;
             const int n0 = (local / mt) * out_w;
             const int e = g % p.experts;

@@ -290,7 +290,7 @@ ffn_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
             const int g = g0 + lane;
             int v = 0;
             if (g < p.groups) {
-                int rows = p.count[g] - p.row_begin;
+                int rows = p.count[ordered_group(g, p.groups, p.experts)] - p.row_begin;
                 rows = max(0, min(rows, window));
                 v = ((rows + BM - 1) / BM) * n_tiles;
             }
@@ -321,12 +321,13 @@ ffn_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
             ptx::prefetch_tensormap(&tmB1);
             int stage = 0;
             uint32_t phase = 0;
-            int g = 0;
+            int vg = 0;
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-                while (tile >= prefix[g + 1]) ++g;
-                const int local = tile - prefix[g];
-                const int mt = (prefix[g + 1] - prefix[g]) / n_tiles;
+                while (tile >= prefix[vg + 1]) ++vg;
+                const int g = ordered_group(vg, p.groups, p.experts);
+                const int local = tile - prefix[vg];
+                const int mt = (prefix[vg + 1] - prefix[vg]) / n_tiles;
                 const int m0 = p.row_begin + (local % mt) * BM;
                 const int n0 = (local / mt) * out_w;
                 const int e = g % p.experts;
@@ -385,13 +386,14 @@ ffn_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         const int quarter = warp & 3;                 // TMEM lanes this warp may read
         const int row_in_tile = quarter * 32 + lane;
         const int epi_tid = threadIdx.x - 64;
-        int g = 0;
+        int vg = 0;
         int it = 0;
         bool ok = true;
         for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
-            while (tile >= prefix[g + 1]) ++g;
-            const int local = tile - prefix[g];
-            const int mt = (prefix[g + 1] - prefix[g]) / n_tiles;
+            while (tile >= prefix[vg + 1]) ++vg;
+            const int g = ordered_group(vg, p.groups, p.experts);
+            const int local = tile - prefix[vg];
+            const int mt = (prefix[vg + 1] - prefix[vg]) / n_tiles;
             const int m0 = p.row_begin + (local % mt) * BM;
             const int n0 = (local / mt) * out_w;
             const int buf = it & 1;
@@ -481,7 +483,7 @@ ffn_grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gr
             const int g = g0 + lane;
             int v = 0;
             if (g < p.groups) {
-                int rows = p.count[g] - p.row_begin;
+                int rows = p.count[ordered_group(g, p.groups, p.experts)] - p.row_begin;
                 rows = max(0, min(rows, window));
                 v = ((rows + PBM - 1) / PBM) * n_tiles;
             }
@@ -515,12 +517,13 @@ ffn_grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gr
             const uint32_t full0 = ptx::mapa_shared(bar_full, 0);   // the full barriers live in CTA 0
             int stage = 0;
             uint32_t phase = 0;
-            int g = 0;
+            int vg = 0;
             bool ok = true;
             for (int tile = pair; ok && tile < total_tiles; tile += num_pairs) {
-                while (tile >= prefix[g + 1]) ++g;
-                const int local = tile - prefix[g];
-                const int mt = (prefix[g + 1] - prefix[g]) / n_tiles;
+                while (tile >= prefix[vg + 1]) ++vg;
+                const int g = ordered_group(vg, p.groups, p.experts);
+                const int local = tile - prefix[vg];
+                const int mt = (prefix[vg + 1] - prefix[vg]) / n_tiles;
                 const int m0 = p.row_begin + (local % mt) * PBM + (int)cta * BM;
                 const int n0 = (local / mt) * out_w;
                 const int e = g % p.experts;
@@ -583,13 +586,14 @@ ffn_grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gr
         const int row_in_tile = quarter * 32 + lane;
         const int epi_tid = threadIdx.x - 64;
         const uint32_t tempty0 = ptx::mapa_shared(bar_tempty, 0);
-        int g = 0;
+        int vg = 0;
         int it = 0;
         bool ok = true;
         for (int tile = pair; ok && tile < total_tiles; tile += num_pairs, ++it) {
-            while (tile >= prefix[g + 1]) ++g;
-            const int local = tile - prefix[g];
-            const int mt = (prefix[g + 1] - prefix[g]) / n_tiles;
+            while (tile >= prefix[vg + 1]) ++vg;
+            const int g = ordered_group(vg, p.groups, p.experts);
+            const int local = tile - prefix[vg];
+            const int mt = (prefix[vg + 1] - prefix[vg]) / n_tiles;
             const int m0 = p.row_begin + (local % mt) * PBM + (int)cta * BM;
             const int n0 = (local / mt) * out_w;
             const int buf = it & 1;
