@@ -26,6 +26,21 @@ def test_e4m3_tables_roundtrip(oracle):
     assert oracle.e4m3_encode(np.array([1e9, -1e9, 0.0625 + 1e-9], np.float32)).tolist()[:2] == [0x7E, 0xFE]
 
 
+def test_quantize_fp8_matches_committed_golden_codes():
+    """A row whose largest magnitude is 448 gets scale 1, so its codes are the raw e4m3 encoding: compared with the
+    committed probe of rounding ties, subnormals and the saturation edge (tests/golden/case2_oracle.npz)."""
+    import os
+    import torch
+    import cuplayground_b200.layer as layer
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "case2_oracle.npz"))
+    keep = np.abs(g["e4m3_probe"]) <= 448.0
+    row = np.zeros((1, 128), np.float32)
+    row[0, :keep.sum()] = g["e4m3_probe"][keep]
+    q, s = layer.quantize_fp8(torch.from_numpy(row).cuda(), 1)
+    assert float(s[0, 0]) == 1.0
+    np.testing.assert_array_equal(q.cpu().numpy()[0, :keep.sum()], g["e4m3_codes"][keep])
+
+
 @pytest.mark.parametrize("block_rows,shape", [(1, (300, 512)), (128, (3, 200, 384)), (128, (2, 256, 256))])
 def test_quantize_fp8_matches_numpy(oracle, block_rows, shape):
     torch, cp, layer = _mods()

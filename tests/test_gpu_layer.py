@@ -73,6 +73,27 @@ def test_layer_bf16_small(oracle, S, H, I, E, k, act, cf, renorm, zipf):
     assert (got[dropped] == 0).all()
 
 
+def test_layer_matches_committed_golden_case2():
+    """The CUDA layer against the committed fixture tests/golden/case2_oracle.npz (no oracle call): routing bit-exact,
+    output within the bf16 tolerance."""
+    import os
+    torch, cp, layer = _mods()
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "case2_oracle.npz"))
+    S, H, I, E, k = 96, 128, 256, 16, 4
+    cfg = cp.AristosConfig(capacity_factor=1.0, drop_tokens=1, expert_top_k=k, hidden_act=2, hidden_size=H,
+                           intermediate_size=I, num_experts=E, torch_dtype=2, tokens=S, renorm_topk=1,
+                           gate_bias_zipf_s=1.2)
+    assert cfg.capacity == int(g["cap"])
+    x, wg, w1, w3, w2 = make_inputs(S, H, I, E, seed=7, swiglu=True, bf16=True, w_std=0.05)
+    L = layer.MoELayer(cfg)
+    out = L.forward(*(to_dev(a, torch.bfloat16) for a in (x, wg, w1, w3, w2)))
+    L.status()
+    _check_routing(L.routing(), g)
+    mx, mean = rel_errors(out.float().cpu().numpy(), g["out"])
+    assert mx < TOL_BF16_MAX and mean < TOL_BF16_MEAN, (mx, mean)
+    L.close()
+
+
 def test_layer_no_drop(oracle):
     torch, cp, layer = _mods()
     cfg = cp.AristosConfig(drop_tokens=0, expert_top_k=2, hidden_act=2, hidden_size=128, intermediate_size=256,

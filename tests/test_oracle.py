@@ -159,3 +159,23 @@ def test_golden_config1(oracle):
     np.testing.assert_allclose(r["topk_w"], g["topk_w"], rtol=1e-6)
     np.testing.assert_allclose(r["out"], g["out"], rtol=1e-5, atol=1e-8)
     assert g["count"].max() == 16 and g["count"].sum() == (g["slot_of"] >= 0).sum() < 128   # cap 16, some drops
+
+
+def test_golden_case2(oracle):
+    """bf16-representable inputs, top-4 of 16 with a Zipf prior and drops, renormalised softmax, SwiGLU, hidden
+    activations rounded to bf16; and the e4m3 tables."""
+    g = np.load(os.path.join(HERE, "golden", "case2_oracle.npz"))
+    S, H, I, E, k = 96, 128, 256, 16, 4
+    cap = oracle.capacity(S, E, k, 1.0)
+    assert cap == int(g["cap"]) == 24
+    x, wg, w1, w3, w2 = make_inputs(S, H, I, E, seed=7, swiglu=True, bf16=True, w_std=0.05)
+    bias = oracle.zipf_bias(E, 1.2)
+    np.testing.assert_array_equal(oracle.gate_logits(x, wg, bias).view(np.uint32), g["logits_bits"])
+    r = oracle.moe_forward(x, wg, w1, w3, w2, k=k, cap=cap, gate_fn=0, renorm=1, hidden_act=2, gate_bias=bias, round_h=1)
+    for name in ("topk_idx", "count", "slot_of", "token_of_slot"):
+        np.testing.assert_array_equal(r[name], g[name])
+    np.testing.assert_allclose(r["topk_w"], g["topk_w"], rtol=1e-6)
+    np.testing.assert_allclose(r["out"], g["out"], rtol=1e-5, atol=1e-8)
+    assert (g["count"] == cap).sum() >= 3 and (g["slot_of"] < 0).sum() > 0          # several experts overflow
+    np.testing.assert_array_equal(oracle.e4m3_decode(np.arange(256, dtype=np.uint8)).view(np.uint32), g["e4m3_table_bits"])
+    np.testing.assert_array_equal(oracle.e4m3_encode(g["e4m3_probe"]), g["e4m3_codes"])
