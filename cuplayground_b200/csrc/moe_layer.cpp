@@ -253,8 +253,9 @@ aristos_status_t aristos_moe_create(const aristos_config_t* cfg, int rank, int w
                 // the copy-engine pipeline over padded row windows instead
                 const char* mode = getenv("ARISTOS_EP_MODE");
                 L->ep_direct = !(mode && !strcmp(mode, "windows"));
-                // one window by default: on two GPUs, splitting the GEMMs to hide the transfers behind them measured
-                // slower (10.5 ms, 10.5 ms, 10.8 ms of device time for 1, 2, 4 windows at 8192 tokens x 8 experts)
+                // one window by default: on two GPUs, splitting the GEMMs to hide the transfers behind them was
+                // no faster (10.5, 10.5, 10.8 ms of device time for 1, 2, 4 windows: 16384 tokens per rank, 8 experts,
+                // H 4096, I 14336)
                 L->direct_windows = 1;
                 if (const char* env = getenv("ARISTOS_EP_DIRECT_WINDOWS"))
                     if (atoi(env) >= 1) L->direct_windows = atoi(env);
