@@ -39,17 +39,18 @@ inline size_t dtype_bytes(int dtype) {
 }
 inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
-#ifdef __CUDACC__
 // Row groups are numbered source-major (g = source * experts + expert). The GEMM kernels walk them expert-major
 // (position v -> expert v / sources, source v % sources), so that the tiles of all the groups that use one expert's
 // weights run back to back and the weights stay in L2 instead of being streamed once per source rank.
-__device__ __forceinline__ int ordered_group(int v, int groups, int experts) {
-    const int sources = groups / experts;
+#ifdef __CUDACC__
+__host__ __device__
+#endif
+inline int ordered_group(int v, int groups, int experts) {
+    const int sources = experts > 0 ? groups / experts : 0;
     if (sources <= 1 || sources * experts != groups) return v;
     const int e = v / sources;
     return (v - e * sources) * experts + e;
 }
-#endif
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 // Number of SMs of the current device (cached per device).

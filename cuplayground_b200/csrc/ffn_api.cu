@@ -106,6 +106,11 @@ __global__ void bounded_wait_selftest_kernel(uint64_t limit_ns, int32_t* dev_sta
 }  // namespace
 }  // namespace aristos
 
+extern "C" int aristos_ffn_group_order(int position, int groups, int experts) {
+    if (position < 0 || groups <= 0 || position >= groups) return -1;
+    return ordered_group(position, groups, experts);
+}
+
 extern "C" aristos_status_t aristos_selftest_bounded_wait(int limit_ms, int* waited_ms, void* stream) {
     if (limit_ms < 1 || limit_ms > 5000) { set_last_error("selftest: limit_ms must be in 1..5000"); return ARISTOS_ERR_INVALID_ARG; }
     cudaStream_t st = static_cast<cudaStream_t>(stream);

@@ -288,6 +288,9 @@ ARISTOS_API aristos_status_t aristos_combine(const void* y, const int32_t* slot_
  * barrier that nothing signals; the wait gives up after limit_ms, the kernel returns normally and the call reports
  * ARISTOS_ERR_DEVICE_TIMEOUT (that IS the expected result) with the time waited. The CUDA context stays usable. */
 ARISTOS_API aristos_status_t aristos_selftest_bounded_wait(int limit_ms, int* waited_ms, void* stream);
+/* The order in which the expert GEMMs walk `groups` row groups of `experts` experts (group g uses expert
+ * g % experts): position -> group, a permutation that keeps the groups of one expert adjacent. Host-only, for tests. */
+ARISTOS_API int aristos_ffn_group_order(int position, int groups, int experts);
 /* Synthetic inputs: Philox4x32-10 + Box-Muller normal fill (the reference draws inputs from Philox,
  * main.cu:22-31). Element i uses counter (i/4, 0, stream_id, 0), key = seed, output word i%4. */
 ARISTOS_API aristos_status_t aristos_fill_normal(void* dst, int64_t n, float mean, float std, uint64_t seed,

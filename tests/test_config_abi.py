@@ -138,3 +138,23 @@ def test_status_strings_cover_every_code(cp):
     names = {lib.aristos_status_str(i).decode() for i in range(12)}
     assert len(names) == 12 and "unknown status" not in names
     assert lib.aristos_status_str(99).decode() == "unknown status"
+
+
+def test_ffn_group_order_is_a_permutation_that_keeps_experts_adjacent(cp):
+    """The expert GEMMs walk the (source, expert) row groups expert-major: every group exactly once, the groups of one
+    expert next to each other, identity when a rank has one source or the group count is no multiple of the experts."""
+    lib = cp._lib.load()
+    for experts in (1, 2, 3, 8, 16, 32):
+        for sources in (1, 2, 4, 8, 16):
+            groups = experts * sources
+            order = [lib.aristos_ffn_group_order(v, groups, experts) for v in range(groups)]
+            assert sorted(order) == list(range(groups))
+            by_expert = [g % experts for g in order]
+            assert by_expert == sorted(by_expert)                       # expert-major
+            for e in range(experts):
+                srcs = [g // experts for g in order if g % experts == e]
+                assert srcs == list(range(sources))                     # sources ascending inside an expert
+            if sources == 1:
+                assert order == list(range(groups))
+    assert [lib.aristos_ffn_group_order(v, 10, 4) for v in range(10)] == list(range(10))
+    assert lib.aristos_ffn_group_order(10, 10, 4) == -1 and lib.aristos_ffn_group_order(-1, 8, 4) == -1
