@@ -26,13 +26,13 @@ namespace aristos {
 namespace {
 
 constexpr int F8_BM = 128;
-constexpr int F8_BN = 128;                       // MMA N = TMEM columns per accumulator buffer
+constexpr int F8_BN = 256;                       // MMA N = TMEM columns per accumulator buffer
 constexpr int F8_KB = 128;                       // elements (= bytes) of K per stage and per scale block
-constexpr int F8_STAGES = 6;
+constexpr int F8_STAGES = 4;
 constexpr int F8_A_BYTES = F8_BM * F8_KB;        // 16 KB
-constexpr int F8_B_BYTES = F8_BN * F8_KB;        // 16 KB
+constexpr int F8_B_BYTES = F8_BN * F8_KB;        // 32 KB: two boxes of 128 weight rows
 constexpr int F8_STAGE_BYTES = F8_A_BYTES + F8_B_BYTES;
-constexpr int F8_TBUFS = 4;                      // TMEM accumulator buffers (4 x 128 columns)
+constexpr int F8_TBUFS = 2;                      // TMEM accumulator buffers (2 x 256 columns)
 constexpr int F8_THREADS = 320;                  // producer warp, MMA warp, 8 promotion warps
 constexpr int F8_EPI_THREADS = 256;
 constexpr int F8_MAX_GROUPS = 1024;
@@ -95,7 +95,7 @@ ffn_fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
     const uint32_t bar_tempty = bar_tfull + 8 * F8_TBUFS;
     const uint32_t smem_base = ptx::smem_u32(smem);
 
-    const int out_w = p.gated ? 64 : 128;
+    const int out_w = p.gated ? 128 : 256;
     const int n_tiles = (p.N + out_w - 1) / out_w;
     const int window = p.row_end - p.row_begin;
     const int kblocks = p.K / F8_KB;
@@ -159,7 +159,7 @@ ffn_fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
                 const int m0 = p.row_begin + (local % mt) * F8_BM;
                 const int n0 = (local / mt) * out_w;
                 const int e = g % p.experts;
-                const int n1 = p.gated ? n0 : n0 + 64;      // second 64-row box of B
+                const int n1 = p.gated ? n0 : n0 + 128;     // second 128-row box of B
                 for (int kb = 0; kb < kblocks; ++kb) {
                     ok = ptx::mbar_wait_bounded(bar_empty + 8 * stage, phase ^ 1u, abort_flag, p.dev_status);
                     if (!ok) break;
@@ -205,8 +205,11 @@ ffn_fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
         __syncwarp();
     } else {
         // ------------------------------------------------------------------ promotion + epilogue (warps 2..9)
+        // A thread owns one accumulator row and the four 32-column chunks half, half + 2, half + 4, half + 6 of the
+        // 256-column tile: the first two lie in the tile's first 128 columns (gate, or weight-scale block n0 / 128),
+        // the last two in the second 128 (up, or the next scale block).
         const int quarter = warp & 3;                       // TMEM lanes this warp may read
-        const int half = (warp - 2) >> 2;                   // 0: column chunks {0, 2}, 1: chunks {1, 3}
+        const int half = (warp - 2) >> 2;
         const int row_in_tile = quarter * 32 + lane;
         int vg = 0, tbuf = 0;
         uint32_t tphase = 0;
@@ -223,30 +226,44 @@ ffn_fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
             const int row_limit = min(p.count[g], p.row_end);
             const bool row_ok = row < row_limit;
             const float* sa_row = p.sa + ((size_t)g * p.rows_per_group + min(row, p.rows_per_group - 1)) * kblocks;
-            const float* sb0_row = p.sb0 + ((size_t)e * nblk + n0 / 128) * kblocks;
-            const float* sb1_row = p.gated ? p.sb1 + ((size_t)e * nblk + n0 / 128) * kblocks : sb0_row;
-            float acc_lo[32], acc_hi[32];                    // chunk `half` and chunk `half + 2` of this row
+            const int blk = n0 / 128;
+            const float* sb0_row = p.sb0 + ((size_t)e * nblk + blk) * kblocks;
+            const float* sb1_row = p.gated ? p.sb1 + ((size_t)e * nblk + blk) * kblocks
+                                           : p.sb0 + ((size_t)e * nblk + min(blk + 1, nblk - 1)) * kblocks;
+            float2 acc[4][16];                               // chunk j = half + 2 j, 32 columns as 16 pairs
 #pragma unroll
-            for (int i = 0; i < 32; ++i) { acc_lo[i] = 0.0f; acc_hi[i] = 0.0f; }
+            for (int j = 0; j < 4; ++j)
+#pragma unroll
+                for (int i = 0; i < 16; ++i) acc[j][i] = make_float2(0.0f, 0.0f);
             for (int kb = 0; kb < kblocks; ++kb) {
+                const float sa = __ldg(sa_row + kb);
+                const float w_lo = sa * __ldg(sb0_row + kb);       // columns 0..127
+                const float w_hi = sa * __ldg(sb1_row + kb);       // columns 128..255
                 ok = ptx::mbar_wait_bounded(bar_tfull + 8 * tbuf, tphase, abort_flag, p.dev_status);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 ptx::tcgen05_fence_after();
-                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + tbuf * F8_BN;
-                uint32_t v_lo[32], v_hi[32];
-                ptx::tmem_ld_32x32b_x32(taddr + half * 32, v_lo);
-                ptx::tmem_ld_32x32b_x32(taddr + (half + 2) * 32, v_hi);
-                const float sa = __ldg(sa_row + kb);
-                const float w_lo = sa * __ldg(sb0_row + kb);       // columns 0..63 (gate, or the tile's first half)
-                const float w_hi = sa * __ldg(sb1_row + kb);       // columns 64..127 (up, or the second half)
+                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + tbuf * F8_BN + half * 32;
+                // eight 16-column loads, one in flight while the previous one is accumulated
+                uint32_t v[2][16];
+                ptx::tmem_ld_32x32b_x16(taddr, v[0]);
                 ptx::tmem_ld_wait();
-                ptx::tcgen05_fence_before();
-                ptx::mbar_arrive(bar_tempty + 8 * tbuf);           // drained: the tensor core may refill the buffer
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    acc_lo[i] = fmaf(w_lo, __uint_as_float(v_lo[i]), acc_lo[i]);
-                    acc_hi[i] = fmaf(w_hi, __uint_as_float(v_hi[i]), acc_hi[i]);
+                for (int s = 0; s < 8; ++s) {
+                    if (s + 1 < 8) ptx::tmem_ld_32x32b_x16(taddr + ((s + 1) >> 1) * 64 + ((s + 1) & 1) * 16, v[(s + 1) & 1]);
+                    const float w = s < 4 ? w_lo : w_hi;
+                    const float2 w2 = make_float2(w, w);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const float2 x2 = make_float2(__uint_as_float(v[s & 1][2 * i]), __uint_as_float(v[s & 1][2 * i + 1]));
+                        acc[s >> 1][(s & 1) * 8 + i] = __ffma2_rn(x2, w2, acc[s >> 1][(s & 1) * 8 + i]);
+                    }
+                    if (s + 1 < 8) {
+                        ptx::tmem_ld_wait();
+                    } else {
+                        ptx::tcgen05_fence_before();
+                        ptx::mbar_arrive(bar_tempty + 8 * tbuf);   // drained: the tensor core may refill the buffer
+                    }
                 }
                 if (++tbuf == F8_TBUFS) { tbuf = 0; tphase ^= 1u; }
             }
@@ -261,25 +278,28 @@ ffn_fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
                 }
                 __nv_bfloat16* orow = obase + ((size_t)og * p.rows_per_group + row) * p.N + n0;
                 if (p.gated) {
-                    // gate columns [32*half, +32) pair with up columns [64 + 32*half, +32): 32 outputs
-                    uint32_t o[16];
+                    // gate chunk half + 2 j pairs with up chunk half + 2 j + 4: 32 outputs each for j = 0, 1
 #pragma unroll
-                    for (int i = 0; i < 16; ++i)
-                        o[i] = pack_bf16x2(act_silu(acc_lo[2 * i]) * acc_hi[2 * i],
-                                           act_silu(acc_lo[2 * i + 1]) * acc_hi[2 * i + 1]);
-                    uint4* dst = reinterpret_cast<uint4*>(orow + half * 32);
+                    for (int j = 0; j < 2; ++j) {
+                        const int col = (half + 2 * j) * 32;
+                        if (n0 + col >= p.N) break;
+                        uint32_t o[16];
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) dst[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+                        for (int i = 0; i < 16; ++i)
+                            o[i] = pack_bf16x2(act_silu(acc[j][i].x) * acc[j + 2][i].x, act_silu(acc[j][i].y) * acc[j + 2][i].y);
+                        uint4* dst = reinterpret_cast<uint4*>(orow + col);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) dst[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+                    }
                 } else {
 #pragma unroll
-                    for (int c = 0; c < 2; ++c) {
-                        const int col = (half + 2 * c) * 32;
+                    for (int j = 0; j < 4; ++j) {
+                        const int col = (half + 2 * j) * 32;
                         if (n0 + col >= p.N) break;
                         uint32_t o[16];
 #pragma unroll
                         for (int i = 0; i < 16; ++i) {
-                            float v0 = c == 0 ? acc_lo[2 * i] : acc_hi[2 * i];
-                            float v1 = c == 0 ? acc_lo[2 * i + 1] : acc_hi[2 * i + 1];
+                            float v0 = acc[j][i].x, v1 = acc[j][i].y;
                             if (p.act == ARISTOS_ACT_RELU) { v0 = act_relu(v0); v1 = act_relu(v1); }
                             else if (p.act == ARISTOS_ACT_GELU) { v0 = act_gelu(v0); v1 = act_gelu(v1); }
                             o[i] = pack_bf16x2(v0, v1);
@@ -429,11 +449,11 @@ aristos_status_t launch_fp8_gemm(const void* A, const void* B0, const void* B1, 
                                  cudaStream_t st) {
     CUtensorMap tmA, tmB0, tmB1;
     ARISTOS_TRY(make_map_u8(&tmA, A, p.K, p.rows_per_group, p.groups, 128));
-    ARISTOS_TRY(make_map_u8(&tmB0, B0, p.K, p.N, p.experts, 64));
-    ARISTOS_TRY(make_map_u8(&tmB1, B1, p.K, p.N, p.experts, 64));
+    ARISTOS_TRY(make_map_u8(&tmB0, B0, p.K, p.N, p.experts, 128));
+    ARISTOS_TRY(make_map_u8(&tmB1, B1, p.K, p.N, p.experts, 128));
     ARISTOS_CUDA_TRY(cudaFuncSetAttribute(ffn_fp8_grouped_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           F8_SMEM_BYTES));
-    const int out_w = p.gated ? 64 : 128;
+    const int out_w = p.gated ? 128 : 256;
     int sms = device_sm_count();
     if (sms <= 0) { set_last_error("no CUDA device"); return ARISTOS_ERR_CUDA; }
     if (grid_limit > 0 && grid_limit < sms) sms = grid_limit;
