@@ -33,7 +33,7 @@ constexpr int F8_A_BYTES = F8_BM * F8_KB;        // 16 KB
 constexpr int F8_B_BYTES = F8_BN * F8_KB;        // 32 KB: two boxes of 128 weight rows
 constexpr int F8_STAGE_BYTES = F8_A_BYTES + F8_B_BYTES;
 constexpr int F8_TBUFS = 2;                      // TMEM accumulator buffers (2 x 256 columns)
-constexpr int F8_THREADS = 320;                  // producer warp, MMA warp, 8 promotion warps
+constexpr int F8_THREADS = 352;                  // producer warp, MMA warp, 8 promotion warps, second MMA warp
 constexpr int F8_EPI_THREADS = 256;
 constexpr int F8_MAX_GROUPS = 1024;
 constexpr int F8_AUX_BYTES = 256 + (F8_MAX_GROUPS + 1) * 4;
@@ -174,15 +174,21 @@ ffn_fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
             }
         }
         __syncwarp();
-    } else if (warp == 1) {
-        // ------------------------------------------------------------------ MMA issuer: one TMEM buffer per K block
+    } else if (warp == 1 || warp == 10) {
+        // ------------------------------------------------------------------ MMA issuers: one TMEM buffer per K block.
+        // Issuing the four MMAs and the commit of one K block costs the issuing thread more cycles than the tensor
+        // core needs to run them, so two warps take turns: K block number it goes to warp it % 2 and to TMEM buffer
+        // it % 2 (each thread's commit covers its own MMAs only).
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc_e4m3(F8_BM, F8_BN);
-            int stage = 0, tbuf = 0;
-            uint32_t phase = 0, tphase = 0;
+            const int me = warp == 1 ? 0 : 1;
+            int it = 0;
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-                for (int kb = 0; kb < kblocks; ++kb) {
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    if ((it & 1) != me) continue;
+                    const int tbuf = it & 1, stage = it % F8_STAGES;
+                    const uint32_t tphase = (it >> 1) & 1u, phase = (it / F8_STAGES) & 1u;
                     ok = ptx::mbar_wait_bounded(bar_tempty + 8 * tbuf, tphase ^ 1u, abort_flag, p.dev_status);
                     if (!ok) break;
                     ok = ptx::mbar_wait_bounded(bar_full + 8 * stage, phase, abort_flag, p.dev_status);
@@ -195,15 +201,13 @@ ffn_fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
 #pragma unroll
                     for (int k = 0; k < 4; ++k)            // K = 32 elements = 32 bytes per instruction
                         umma_f8(tmem_d, da + 2 * k, db + 2 * k, idesc, k != 0 ? 1u : 0u);
-                    ptx::umma_commit(bar_empty + 8 * stage);
+                    // one commit: the accumulator is ready; the promotion warps hand the stage back when they see it
                     ptx::umma_commit(bar_tfull + 8 * tbuf);
-                    if (++stage == F8_STAGES) { stage = 0; phase ^= 1u; }
-                    if (++tbuf == F8_TBUFS) { tbuf = 0; tphase ^= 1u; }
                 }
             }
         }
         __syncwarp();
-    } else {
+    } else if (warp >= 2 && warp < 10) {
         // ------------------------------------------------------------------ promotion + epilogue (warps 2..9)
         // A thread owns one accumulator row and the four 32-column chunks half, half + 2, half + 4, half + 6 of the
         // 256-column tile: the first two lie in the tile's first 128 columns (gate, or weight-scale block n0 / 128),
@@ -211,7 +215,7 @@ ffn_fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
         const int quarter = warp & 3;                       // TMEM lanes this warp may read
         const int half = (warp - 2) >> 2;
         const int row_in_tile = quarter * 32 + lane;
-        int vg = 0, tbuf = 0;
+        int vg = 0, tbuf = 0, rstage = 0;
         uint32_t tphase = 0;
         bool ok = true;
         for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
@@ -242,6 +246,9 @@ ffn_fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
                 ok = ptx::mbar_wait_bounded(bar_tfull + 8 * tbuf, tphase, abort_flag, p.dev_status);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
+                // the MMAs of this K block are complete, so their shared-memory stage is free again
+                if (threadIdx.x == 64) ptx::mbar_arrive(bar_empty + 8 * rstage);
+                if (++rstage == F8_STAGES) rstage = 0;
                 ptx::tcgen05_fence_after();
                 const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + tbuf * F8_BN + half * 32;
                 // eight 16-column loads, one in flight while the previous one is accumulated
