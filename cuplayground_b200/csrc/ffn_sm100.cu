@@ -635,17 +635,20 @@ aristos_status_t make_map_3d(CUtensorMap* tm, const void* base, int K, int rows,
     return encode_map_3d(tm, dt, fmt == FMT_TF32 ? 4 : 2, base, K, rows, outer, 128);
 }
 
-// Tile shape: CTA pairs (256-row tiles) pay off when the row groups are long; short groups would mostly pad them.
-// ARISTOS_FFN_TILES=single|pair overrides the choice (for measurements).
+// Tile shape: single-CTA 128 x 256 tiles by default. CTA pairs (256 x 256 tiles, cta_group::2) halve the B bytes each
+// SM stages and lower the power per FLOP, but their 256-row granularity pads the tail of every row group twice as
+// much and, measured back to back on one power-capped GPU (16384 tokens, 8 experts, H 4096, I 14336: 9.62 / 9.75 ms
+// against 10.01 / 10.06 ms for the two GEMMs), they were 3-4 % slower. ARISTOS_FFN_TILES=pair selects them where the
+// row window holds at least 1024 rows; ARISTOS_FFN_TILES=pair-always for every window.
 bool use_pair_tiles(int window_rows) {
     static int forced = -1;
     if (forced < 0) {
         const char* env = getenv("ARISTOS_FFN_TILES");
-        forced = !env ? 0 : (!strcmp(env, "pair") ? 2 : (!strcmp(env, "single") ? 1 : 0));
+        forced = !env ? 0 : (!strcmp(env, "pair") ? 2 : (!strcmp(env, "pair-always") ? 3 : 0));
     }
-    if (forced == 2) return true;
-    if (forced == 1) return false;
-    return window_rows >= 1024;
+    if (forced == 3) return true;
+    if (forced == 2) return window_rows >= 1024;
+    return false;
 }
 
 aristos_status_t launch_gemm(const void* A, const void* B0, const void* B1, const FfnGemmParams& p,

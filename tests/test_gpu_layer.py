@@ -159,6 +159,20 @@ def test_config3_full_size_mixtral_shaped(oracle):
     _full_size(3, 2, oracle, n_sample=64)
 
 
+def test_config3_with_cta_pair_tiles():
+    """The CTA-pair (cta_group::2, 256 x 256) variant of the expert GEMM is an option since the single-CTA tiles became
+    the default: the full-size Mixtral-shaped parity test once more in a process that selects it."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, ARISTOS_FFN_TILES="pair")
+    r = subprocess.run([sys.executable, "-m", "pytest", os.path.join(root, "tests", "test_gpu_layer.py"), "-q", "-x",
+                        "-k", "test_config3_full_size_mixtral_shaped", "-m", "gpu"], env=env, cwd=root,
+                       capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0 and "1 passed" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+
+
 def test_forward_host_matches_device_forward(oracle):
     torch, cp, layer = _mods()
     cfg = cp.AristosConfig(capacity_factor=1.25, drop_tokens=1, expert_top_k=2, hidden_act=1, hidden_size=256,
