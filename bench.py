@@ -299,12 +299,12 @@ def run_ours(args, cfg, workload_desc):
         if world > 1:
             ffn_flops = 2.0 * (kept_all / world) * H * I * m
         # DRAM bytes per GEMM launch: ncu dram__bytes_read+write of the up and down projections on config3-profile
-        # (8192 rows: 1010 MB + 1317 MB), scaled by the rows of this run; only valid for the config-3 shape
+        # (8192 rows: 810 MB + 1282 MB), scaled by the rows of this run; only valid for the config-3 shape
         traffic, traffic_src = None, None
         if args.workload.startswith("config3"):
             rows = kept if world == 1 else kept_all / world
-            traffic = (1010e6 + 1317e6) / 8192.0 * rows / 2.0
-            traffic_src = ("ncu capture on config3-profile (profiles/ffn_grouped_gemm_pair_config3_profile_ncu_full.md), "
+            traffic = (810e6 + 1282e6) / 8192.0 * rows / 2.0
+            traffic_src = ("ncu capture on config3-profile (profiles/ffn_grouped_gemm_single_config3_profile_ncu_full.md), "
                            "scaled by rows, average of the two launches of a forward")
         ffn_s = stage["ffn"] * 1e-3
         achieved = ffn_flops / ffn_s / 1e12
