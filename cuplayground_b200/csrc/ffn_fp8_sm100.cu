@@ -4,16 +4,20 @@
 // 128 x 128 block (scale sb[expert][N/128][K/128]); out = sum over K blocks kb of sa[row,kb] * sb[n/128,kb] *
 // (Aq[row, kb] . Bq[n, kb]). The hardware's own block scaling (power-of-two scales per 32 elements) cannot express
 // fp32 scales per 128, so the accumulation has two levels: one 128-wide K block is accumulated by four
-// tcgen05.mma kind::f8f6f4 (K = 32 each) into a fresh 128-column TMEM accumulator, the four epilogue warps drain it
-// (tcgen05.ld), multiply by the block's scale and add it to fp32 register accumulators (one row and 128 columns per
-// thread) while the tensor core works on the next block in the next of four TMEM buffers. Eight promotion warps
-// share the work: two per TMEM lane quarter, each owning 64 of the 128 columns (32-column chunks {0, 2} or {1, 3},
-// so a SwiGLU thread holds matching gate and up columns).
+// tcgen05.mma kind::f8f6f4 (M128 x N256 x K32 each) into a fresh 256-column TMEM accumulator, eight promotion warps
+// drain it (tcgen05.ld, 16 columns at a time, one load in flight while the previous one is used), multiply by the
+// block's scale and add it to fp32 register accumulators with packed FMAs while the tensor core fills the other of
+// the two TMEM buffers. Two promotion warps share a TMEM lane quarter, each owning four of the eight 32-column chunks
+// ({0, 2, 4, 6} or {1, 3, 5, 7}, so a SwiGLU thread holds matching gate and up columns): one row and 128 columns per
+// thread. The issue of four MMAs and a commit takes the issuing thread longer than the tensor core needs for them
+// whatever their width (about 150 cycles per instruction were measured), hence the N = 256 instructions and two
+// issuing warps that take turns per K block.
 //
 // Same tile contract as the 16-bit kernel (ffn_sm100.cu; reference: fGET, mma.cuh:46-179, A (M,K) and B (N,K)
 // row-major, epilogue act(acc)): persistent CTAs, warp 0 = TMA producer (a 128-byte K block is exactly one swizzled
-// row), warp 1 = MMA issuer, warps 2-9 = promotion + epilogue. SwiGLU tiles hold 64 gate and 64 up columns in one
-// N = 128 instruction. Output is bf16, written with 16-byte stores masked by the group's row count.
+// row; four 48 KB stages), warps 1 and 10 = MMA issuers, warps 2-9 = promotion + epilogue. SwiGLU tiles hold 128 gate
+// and 128 up columns in one N = 256 instruction. Output is bf16, written with 16-byte stores masked by the group's
+// row count (to this rank's buffer, or straight into the source ranks' buffers through peer pointers).
 #include <cuda.h>
 #include <cuda_fp8.h>
 
