@@ -137,10 +137,10 @@ def cpu_sample_forward(oracle, cfg, tensors, n_tokens):
 
 def cpu_calibrate(oracle, cfg, tensors, target_s):
     """Pick a sample size that takes about target_s seconds on this host."""
-    n0 = min(64, cfg.S)
+    n0 = min(64, tensors[0].shape[0])
     t = cpu_sample_forward(oracle, cfg, tensors, n0)
     rate = n0 / max(t, 1e-6)
-    n = int(max(64, min(cfg.S, rate * target_s)))
+    n = int(max(64, min(tensors[0].shape[0], rate * target_s)))
     return max(64, n // 64 * 64)
 
 
@@ -166,7 +166,10 @@ def run_reference(args, cfg, workload_desc):
         return
     from oracle import moe_oracle as oracle
     oracle.build()
-    n_probe = min(cfg.S, 4096)
+    # every core this process may use, whatever the launcher exported (torch.distributed.run sets OMP_NUM_THREADS=1)
+    oracle.use_all_cores()
+    S = cfg.tokens if cfg.tokens > 0 else cfg.micro_batch * cfg.sequence_len
+    n_probe = min(S, 4096)
     tensors = host_tensors_from_oracle(oracle, cfg, n_probe)
     n = min(n_probe, cpu_calibrate(oracle, cfg, tensors, target_s=4.0))
     for _ in range(args.warmup):
@@ -188,6 +191,61 @@ def run_reference(args, cfg, workload_desc):
 
 
 # ---------------------------------------------------------------------------------------------------------------------
+def time_ffn_variants(L, fwd, cfg, kept, local_rank, steps):
+    """Both tile shapes of the expert GEMM in this process, back to back: FFN-stage milliseconds (CUDA events inside
+    the forward), TFLOP/s and TFLOP/s per GHz of the median SM clock sampled while each ran."""
+    import cuplayground_b200._lib as _lib
+    lib = _lib.load()
+    m = 3 if cfg.hidden_act == 2 else 2
+    flops = 2.0 * kept * cfg.hidden_size * cfg.intermediate_size * m
+    res = {}
+    for name, mode in (("single", 1), ("pair", 2), ("single_again", 1), ("pair_again", 2)):
+        _lib.check(lib.aristos_ffn_set_tile_mode(mode))
+        for _ in range(2):
+            fwd()
+        L.status()
+        L.set_profiling(True)
+        sampler = ClockSampler(local_rank)
+        sampler.begin_region()
+        for _ in range(steps):
+            fwd()
+        L.status()
+        clocks = sampler.stop()
+        ms = L.stage_ms()["ffn"]
+        L.set_profiling(False)
+        tf = flops / (ms * 1e-3) / 1e12
+        res[name] = {"ffn_ms": ms, "tflops": tf, "sm_mhz": clocks.get("sm_mhz"),
+                     "tflops_per_ghz": tf / (clocks["sm_mhz"] / 1e3) if clocks.get("sm_mhz") else None,
+                     "power_w_max": clocks.get("power_w_max"), "reasons": clocks.get("reasons")}
+    _lib.check(lib.aristos_ffn_set_tile_mode(0))
+    return res
+
+
+def copy_only(torch, xh, oh, x_dev, out_dev, steps):
+    """The host copies of the end-to-end path alone (the same pinned buffers, no kernels): GB/s host-to-device,
+    device-to-host, and both at once on two streams as the pipelined path issues them."""
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+    nbytes = xh.numel() * xh.element_size()
+
+    def run(do_in, do_out):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            if do_in:
+                with torch.cuda.stream(s_in):
+                    x_dev.copy_(xh, non_blocking=True)
+            if do_out:
+                with torch.cuda.stream(s_out):
+                    oh.copy_(out_dev, non_blocking=True)
+        torch.cuda.synchronize()
+        return time.perf_counter() - t0
+
+    run(True, True)
+    t_in, t_out, t_both = run(True, False), run(False, True), run(True, True)
+    return {"h2d_gbs": nbytes * steps / t_in / 1e9, "d2h_gbs": nbytes * steps / t_out / 1e9,
+            "both_s_per_step": t_both / steps, "pinned": bool(xh.is_pinned() and oh.is_pinned())}
+
+
 def run_ours(args, cfg, workload_desc):
     import torch
     import torch.distributed as dist
@@ -202,6 +260,10 @@ def run_ours(args, cfg, workload_desc):
         raise SystemExit("bench.py needs a CUDA device: the library has no CPU fallback "
                          "(use --impl reference for the CPU baseline)")
     torch.cuda.set_device(local_rank)
+    # host threads and the pinned staging buffers go to the NUMA node of this rank's GPU (read from sysfs; nothing is
+    # set on the GPU)
+    from cuplayground_b200 import hostmem
+    numa = hostmem.bind_to_gpu_numa_node(local_rank)
     uid = None
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
@@ -290,6 +352,54 @@ def run_ours(args, cfg, workload_desc):
     e2e_blocking = S * world * 4 / (float(tb.item()) * 1e-3)
     L.status()
     assert torch.equal(oh[0], oh[1]) and torch.equal(oh[0], out.cpu()), "host path result differs from device path"
+    # the copies alone, all ranks at once (what the host side of this box allows)
+    barrier()
+    copies = copy_only(torch, xh[0], oh[0], torch.empty_like(x), out, e2e_steps)
+    barrier()
+    tc_ = torch.tensor([copies["both_s_per_step"], -copies["h2d_gbs"], -copies["d2h_gbs"]], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(tc_, op=dist.ReduceOp.MAX)
+    copies.update(both_s_per_step=float(tc_[0]), h2d_gbs=-float(tc_[1]), d2h_gbs=-float(tc_[2]))
+
+    # ---- parity of this run's last forward against the CPU oracle, on the first and the last rank: routing bit-exact
+    # on every token of the rank, sampled output rows within the 16-bit tolerance (checker only, not timed)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    parity = None
+    check_ranks = sorted({0, world - 1})
+    if not args.no_parity:
+        mine = None
+        if rank in check_ranks:
+            import parity as parity_mod
+            from oracle import moe_oracle as oracle
+            oracle.build()
+            oracle.use_all_cores()
+            try:
+                mine = parity_mod.check_rank(cfg, L, x, wg, out, n_rows=16 if cfg.torch_dtype == 4 else 64, seed=rank)
+            except AssertionError as e:
+                mine = {"ok": False, "routing": f"MISMATCH: {e}", "rows": 0, "max_rel": None, "mean_rel": None}
+            mine["rank"] = rank
+        if world > 1:
+            box = [None] * world
+            dist.all_gather_object(box, mine)
+            got = [b for b in box if b is not None]
+        else:
+            got = [mine]
+        parity = {"ranks": [g["rank"] for g in got],
+                  "routing": "bit-exact" if all(g["routing"] == "bit-exact" for g in got) else
+                  "; ".join(str(g["routing"]) for g in got),
+                  "rows": sum(g["rows"] for g in got),
+                  "max_rel": max((g["max_rel"] for g in got if g["max_rel"] is not None), default=None),
+                  "mean_rel": max((g["mean_rel"] for g in got if g["mean_rel"] is not None), default=None),
+                  "tolerance": "routing tensors bit-exact on every token of the rank; sampled output rows "
+                               "max|d|/max|ref| < 2e-2 and mean|d|/mean|ref| < 1e-2 against the fp32 oracle over the "
+                               "global weights",
+                  "ok": all(g["ok"] for g in got)}
+
+    # ---- both tile shapes of the expert GEMM, timed in this process (one GPU, 16-bit tensor-core workloads)
+    variants = None
+    if world == 1 and cfg.torch_dtype in (2, 3) and not args.no_variants:
+        variants = time_ffn_variants(L, lambda: L.forward(x, wg, w1, w3, w2, out=out, scales=scales), cfg, kept,
+                                     local_rank, max(3, min(args.steps, 10)))
 
     if rank == 0:
         peaks = read_peaks()
@@ -318,11 +428,14 @@ def run_ours(args, cfg, workload_desc):
                             "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": hbm / peaks["hbm_gbs"], "traffic": None,
                             "peak_source": f"{peaks['source']} copy bandwidth", "algorithmic_bytes": w_bytes + a_bytes,
                             "tflops": achieved, "ms_per_step": stage["ffn"]}
-        roofline = {"bound": "tensor", "kernel": "ffn_grouped_gemm_kernel", "achieved": achieved,
-                    "peak": peaks["bf16_sustained"], "unit": "TFLOP/s", "frac": achieved / peaks["bf16_sustained"],
-                    "traffic": traffic, "traffic_source": traffic_src, "peak_source": f"{peaks['source']} bf16 sustained (kernel timed inside a "
-                    "back-to-back loop of steps)", "launches_per_step": 2 if world == 1 else None,
-                    "flops_per_step": ffn_flops, "ms_per_step": stage["ffn"]}
+        # the timed loop is short (well under a second), so the burst cuBLAS figure is the denominator
+        roofline = {"bound": "tensor", "kernel": "ffn_grouped_gemm_pair_kernel + ffn_grouped_gemm_kernel (tail rows)",
+                    "achieved": achieved,
+                    "peak": peaks["bf16_burst"], "unit": "TFLOP/s", "frac": achieved / peaks["bf16_burst"],
+                    "frac_of_sustained_peak": achieved / peaks["bf16_sustained"],
+                    "traffic": traffic, "traffic_source": traffic_src,
+                    "peak_source": f"{peaks['source']} bf16 burst (cuBLAS 8192^3, best of 10)",
+                    "launches_per_step": 4, "flops_per_step": ffn_flops, "ms_per_step": stage["ffn"]}
         t_roof, terms = layer_roofline(cfg, world, kept_all / world)
         line = {"metric": "moe_fwd_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
@@ -337,12 +450,20 @@ def run_ours(args, cfg, workload_desc):
                         "api": "aristos_moe_submit_host per step + aristos_moe_wait_host (pinned host activations "
                                "in, host result out every step; two steps in flight)", "timing": "host wall clock, "
                         "device synchronised on both sides, max over ranks",
-                        "blocking_call_value": e2e_blocking},
+                        "blocking_call_value": e2e_blocking,
+                        "copy_only": {**copies, "tokens_per_s": S * world / copies["both_s_per_step"],
+                                      "what": "the same pinned buffers copied in and out per step with no kernels, "
+                                              "all ranks at once; GB/s are the slowest rank's"},
+                        "numa": numa},
                 "gpu_launches": int(launches),
                 "roofline": roofline_fp8 if fp8 else roofline,
                 "layer_roofline": {"seconds": t_roof, **terms, "frac": t_roof / (ms / args.steps * 1e-3),
                                    "constants": "2250 TFLOP/s dense bf16, 8 TB/s HBM, 900 GB/s NVLink per direction"},
                 "stage_ms": stage, "host_enqueue_ms_per_step": host_enqueue_ms}
+        if parity is not None:
+            line["parity"] = parity
+        if variants is not None:
+            line["ffn_variants"] = variants
         if world == 1 and not args.no_cpu_baseline:
             from oracle import moe_oracle as oracle
             oracle.build()
@@ -360,6 +481,8 @@ def run_ours(args, cfg, workload_desc):
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    if parity is not None and not parity["ok"]:
+        raise SystemExit("parity check against the CPU oracle failed: " + json.dumps(parity))
 
 
 def main():
@@ -370,6 +493,8 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="config3")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-parity", action="store_true", help="skip the oracle check of the last forward")
+    ap.add_argument("--no-variants", action="store_true", help="skip the timing of both GEMM tile shapes")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3     # timing rule: at least three warm-up steps

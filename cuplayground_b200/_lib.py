@@ -91,6 +91,11 @@ PROTOTYPES = {
                                      _i, _i, _i, _i, _vp, _vp]),
     "aristos_combine": (_st, [_vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp]),
     "aristos_selftest_bounded_wait": (_st, [_i, C.POINTER(_i), _vp]),
+    "aristos_selftest_bounded_flag_wait": (_st, [_i, C.POINTER(_i), _vp]),
+    "aristos_ffn_set_tile_mode": (_st, [_i]),
+    "aristos_ffn_tile_coord": (_i, [_i, _i, _i, _i, C.POINTER(_i), C.POINTER(_i)]),
+    "aristos_ep_transport_agreed": (_i, [C.POINTER(_i), _i]),
+    "aristos_moe_set_timeout_ms": (_st, [_vp, _i]),
     "aristos_ffn_group_order": (_i, [_i, _i, _i]),
     "aristos_fill_normal": (_st, [_vp, C.c_int64, C.c_float, C.c_float, C.c_uint64, C.c_uint32, _i, _vp]),
 }

@@ -45,11 +45,37 @@ inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 #ifdef __CUDACC__
 __host__ __device__
 #endif
-inline int ordered_group(int v, int groups, int experts) {
+// Within an expert the sources are taken in ring order starting at first_source: a rank starts with the rows it
+// gathered itself, which are in its memory before the kernel launches, while the peers' rows are still arriving.
+inline int ordered_group(int v, int groups, int experts, int first_source = 0) {
     const int sources = experts > 0 ? groups / experts : 0;
     if (sources <= 1 || sources * experts != groups) return v;
     const int e = v / sources;
-    return (v - e * sources) * experts + e;
+    int s = v - e * sources + first_source;
+    if (s >= sources) s -= sources;
+    return s * experts + e;
+}
+
+// Order of the tiles of one row group: mt row tiles x nt column tiles, `local` in [0, mt * nt). The row tiles are cut
+// into bands of `band` row tiles; inside a band the row tile runs fastest, then the column tile, then the next band.
+// The CTAs that run at the same time then share `band` A panels and about (CTAs / band) B panels, instead of all mt
+// A panels and few B panels. band >= mt gives the plain row-tile-fastest order.
+#ifdef __CUDACC__
+__host__ __device__
+#endif
+inline void band_tile_coord(int local, int mt, int nt, int band, int* m, int* n) {
+    if (band <= 0 || band >= mt) { *m = local % mt; *n = local / mt; return; }
+    const int per_band = band * nt;
+    const int full = mt / band;
+    if (local < full * per_band) {
+        const int b = local / per_band, r = local - b * per_band;
+        *n = r / band;
+        *m = b * band + (r - *n * band);
+    } else {
+        const int rem = mt - full * band, r = local - full * per_band;
+        *n = r / rem;
+        *m = full * band + (r - *n * rem);
+    }
 }
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 

@@ -9,6 +9,9 @@
 
 #include <cuda.h>
 
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
 #include <vector>
 
 #include "common.cuh"
@@ -31,6 +34,25 @@ __global__ void ep_signal_kernel(FlagTargets t, uint32_t epoch) {
     if (d < t.n) {
         __threadfence_system();
         *reinterpret_cast<volatile uint32_t*>(t.ptr[d]) = epoch;
+        __threadfence_system();
+    }
+}
+
+struct CountTargets {
+    int32_t* ptr[MAX_RANKS];
+};
+
+// Row counts to their owners, then this rank's count flag at every rank (one CTA).
+__global__ void ep_counts_kernel(const int32_t* __restrict__ count, int E, int E_local, int src_rank, CountTargets dst,
+                                 FlagTargets t, uint32_t epoch) {
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        const int owner = e / E_local;
+        dst.ptr[owner][src_rank * E_local + (e - owner * E_local)] = count[e];
+    }
+    __threadfence_system();
+    __syncthreads();
+    if ((int)threadIdx.x < t.n) {
+        *reinterpret_cast<volatile uint32_t*>(t.ptr[threadIdx.x]) = epoch;
         __threadfence_system();
     }
 }
@@ -64,11 +86,24 @@ static size_t flag_index(const EpP2P* p, int kind, int window, int src) {
     return ((size_t)kind * EP_MAX_WINDOWS + window) * MAX_RANKS + src;
 }
 
+bool ep_transport_agreed(const int* ok_flags, int world) {
+    for (int r = 0; r < world; ++r)
+        if (!ok_flags[r]) return false;
+    return world > 0;
+}
+
+// Every rank runs every collective step of the set-up, whatever happened to it locally: a rank whose allocation or
+// mapping failed still takes part in both all-gathers and reports "not ok", and all ranks then take the same
+// decision (peer memory only if it works everywhere). A rank that left early would leave the others in a collective.
 aristos_status_t ep_p2p_create(EpComm* bootstrap, int rank, int world, int groups, size_t xr_bytes, size_t yg_bytes,
                                size_t aux_bytes, EpP2P** out) {
     if (!bootstrap || !out || world < 2 || world > MAX_RANKS) return ARISTOS_ERR_INVALID_ARG;
     static_assert(3 * EP_MAX_WINDOWS * MAX_RANKS * 4 <= FLAG_BYTES, "flag words fit their page");
-    if (!stream_wait_fn()) { set_last_error("cuStreamWaitValue32 is not available from the driver"); return ARISTOS_ERR_CUDA; }
+    struct Hello {
+        cudaIpcMemHandle_t handle;
+        int ok;
+        int pad[3];
+    };
     EpP2P* p = new EpP2P();
     p->rank = rank;
     p->world = world;
@@ -79,37 +114,83 @@ aristos_status_t ep_p2p_create(EpComm* bootstrap, int rank, int world, int group
     p->off_aux = align_up(p->off_yg + yg_bytes, 1024);
     p->bytes = align_up(p->off_aux + aux_bytes, 1024);
     p->base.assign(world, nullptr);
-    cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&p->local), p->bytes);
-    if (e != cudaSuccess) {
-        set_last_error("cudaMalloc of the %zu-byte exchange region failed: %s", p->bytes, cudaGetErrorString(e));
-        delete p;
-        return ARISTOS_ERR_NOMEM;
+    char local_error[256] = "";
+    Hello mine;
+    memset(&mine, 0, sizeof(mine));
+    // ---- local part: may fail without leaving the protocol
+    int ok = stream_wait_fn() != nullptr;
+    if (!ok) snprintf(local_error, sizeof(local_error), "cuStreamWaitValue32 is not available from the driver");
+    // host-injected failure for the tests of the agreement (nothing on the GPU fails)
+    const char* inject = getenv("ARISTOS_EP_INJECT_P2P_FAIL");
+    const int inject_rank = inject ? atoi(inject) : -1;
+    const bool inject_alloc = inject_rank == rank && getenv("ARISTOS_EP_INJECT_STAGE") &&
+                              !strcmp(getenv("ARISTOS_EP_INJECT_STAGE"), "alloc");
+    if (ok) {
+        cudaError_t e = inject_alloc ? cudaErrorMemoryAllocation : cudaMalloc(reinterpret_cast<void**>(&p->local), p->bytes);
+        if (e == cudaSuccess) e = cudaMemset(p->local, 0, FLAG_BYTES + (size_t)groups * 4);
+        if (e == cudaSuccess) e = cudaIpcGetMemHandle(&mine.handle, p->local);
+        if (e != cudaSuccess) {
+            ok = 0;
+            snprintf(local_error, sizeof(local_error), "exchange region of %zu bytes: %s", p->bytes, cudaGetErrorString(e));
+            cudaGetLastError();
+        }
     }
+    mine.ok = ok;
     p->base[rank] = p->local;
-    cudaIpcMemHandle_t mine;
-    cudaIpcMemHandle_t* d_all = nullptr;
-    std::vector<cudaIpcMemHandle_t> all(world);
+    // ---- collective part 1: handles and "allocated" flags (also the barrier that orders every rank's flag clearing
+    // before any peer's first store)
+    Hello* d_all = nullptr;
+    std::vector<Hello> all(world);
+    cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&d_all), sizeof(Hello) * (world + 1));
+    if (e != cudaSuccess) { ep_p2p_destroy(p); return cuda_fail(e, "peer-memory exchange set-up (staging)"); }
     aristos_status_t st = ARISTOS_OK;
-    do {
-        if ((e = cudaMemset(p->local, 0, FLAG_BYTES + (size_t)groups * 4)) != cudaSuccess) break;
-        if ((e = cudaIpcGetMemHandle(&mine, p->local)) != cudaSuccess) break;
-        if ((e = cudaMalloc(reinterpret_cast<void**>(&d_all), sizeof(mine) * (world + 1))) != cudaSuccess) break;
-        if ((e = cudaMemcpy(d_all + world, &mine, sizeof(mine), cudaMemcpyHostToDevice)) != cudaSuccess) break;
-        // the all-gather is also the barrier that orders every rank's flag clearing before any peer's first store
-        st = ep_allgather_bytes(bootstrap, d_all + world, d_all, sizeof(mine), nullptr);
-        if (st != ARISTOS_OK) break;
-        if ((e = cudaStreamSynchronize(nullptr)) != cudaSuccess) break;
-        if ((e = cudaMemcpy(all.data(), d_all, sizeof(mine) * world, cudaMemcpyDeviceToHost)) != cudaSuccess) break;
-        for (int r = 0; r < world && e == cudaSuccess; ++r) {
+    e = cudaMemcpy(d_all + world, &mine, sizeof(mine), cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) st = ep_allgather_bytes(bootstrap, d_all + world, d_all, sizeof(Hello), nullptr);
+    if (e == cudaSuccess && st == ARISTOS_OK) e = cudaStreamSynchronize(nullptr);
+    if (e == cudaSuccess && st == ARISTOS_OK) e = cudaMemcpy(all.data(), d_all, sizeof(Hello) * world, cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess || st != ARISTOS_OK) {
+        cudaFree(d_all);
+        ep_p2p_destroy(p);
+        return st != ARISTOS_OK ? st : cuda_fail(e, "peer-memory exchange set-up (handle all-gather)");
+    }
+    std::vector<int> flags(world);
+    for (int r = 0; r < world; ++r) flags[r] = all[r].ok;
+    int mapped_ok = ep_transport_agreed(flags.data(), world) ? 1 : 0;
+    // ---- local part 2: map the peers' regions (only when every rank has one)
+    if (mapped_ok) {
+        for (int r = 0; r < world && mapped_ok; ++r) {
             if (r == rank) continue;
             void* mapped = nullptr;
-            e = cudaIpcOpenMemHandle(&mapped, all[r], cudaIpcMemLazyEnablePeerAccess);
+            cudaError_t me = (inject_rank == rank && !inject_alloc) ? cudaErrorInvalidResourceHandle
+                                 : cudaIpcOpenMemHandle(&mapped, all[r].handle, cudaIpcMemLazyEnablePeerAccess);
+            if (me != cudaSuccess) {
+                mapped_ok = 0;
+                snprintf(local_error, sizeof(local_error), "mapping rank %d's exchange region: %s", r, cudaGetErrorString(me));
+                cudaGetLastError();
+            }
             p->base[r] = static_cast<char*>(mapped);
         }
-    } while (false);
-    if (d_all) cudaFree(d_all);
-    if (st == ARISTOS_OK && e != cudaSuccess) st = cuda_fail(e, "peer-memory exchange set-up");
-    if (st != ARISTOS_OK) { ep_p2p_destroy(p); return st; }
+    }
+    // ---- collective part 2: did every rank map every peer?
+    mine.ok = mapped_ok;
+    e = cudaMemcpy(d_all + world, &mine, sizeof(mine), cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) st = ep_allgather_bytes(bootstrap, d_all + world, d_all, sizeof(Hello), nullptr);
+    if (e == cudaSuccess && st == ARISTOS_OK) e = cudaStreamSynchronize(nullptr);
+    if (e == cudaSuccess && st == ARISTOS_OK) e = cudaMemcpy(all.data(), d_all, sizeof(Hello) * world, cudaMemcpyDeviceToHost);
+    cudaFree(d_all);
+    if (e != cudaSuccess || st != ARISTOS_OK) {
+        ep_p2p_destroy(p);
+        return st != ARISTOS_OK ? st : cuda_fail(e, "peer-memory exchange set-up (agreement all-gather)");
+    }
+    for (int r = 0; r < world; ++r) flags[r] = all[r].ok;
+    if (!ep_transport_agreed(flags.data(), world)) {
+        int first_bad = 0;
+        while (first_bad < world && flags[first_bad]) ++first_bad;
+        ep_p2p_destroy(p);
+        if (local_error[0]) set_last_error("peer-memory transport unavailable on this rank: %s", local_error);
+        else set_last_error("peer-memory transport unavailable on rank %d; every rank falls back together", first_bad);
+        return ARISTOS_ERR_UNSUPPORTED;
+    }
     *out = p;
     return ARISTOS_OK;
 }
@@ -174,4 +255,42 @@ aristos_status_t ep_p2p_wait(EpP2P* p, int kind, int window, cudaStream_t stream
     return ARISTOS_OK;
 }
 
+const uint32_t* ep_p2p_flags(const EpP2P* p, int kind, int window) {
+    return reinterpret_cast<const uint32_t*>(p->local) + flag_index(p, kind, window, 0);
+}
+uint32_t ep_p2p_epoch(const EpP2P* p) { return p->epoch; }
+
+aristos_status_t ep_p2p_send_counts(EpP2P* p, const int32_t* count, int E, int E_local, cudaStream_t stream) {
+    if (!p || !count || E_local <= 0 || E != E_local * p->world) return ARISTOS_ERR_INVALID_ARG;
+    FlagTargets t;
+    CountTargets c;
+    t.n = p->world;
+    for (int d = 0; d < p->world; ++d) {
+        t.ptr[d] = reinterpret_cast<uint32_t*>(p->base[d]) + flag_index(p, EP_FLAG_COUNT, 0, p->rank);
+        c.ptr[d] = reinterpret_cast<int32_t*>(p->base[d] + p->off_rcount);
+    }
+    ep_counts_kernel<<<1, 256, 0, stream>>>(count, E, E_local, p->rank, c, t, p->epoch);
+    ARISTOS_COUNT_LAUNCH();
+    ARISTOS_CUDA_TRY(cudaGetLastError());
+    return ARISTOS_OK;
+}
+
+aristos_status_t ep_p2p_release_local_waits(EpP2P* p) {
+    if (!p) return ARISTOS_ERR_INVALID_ARG;
+    // a copy on the legacy stream would queue behind the stalled streams: use a non-blocking stream of its own
+    std::vector<uint32_t> words(3 * EP_MAX_WINDOWS * MAX_RANKS, p->epoch);
+    cudaStream_t s = nullptr;
+    ARISTOS_CUDA_TRY(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+    cudaError_t e = cudaMemcpyAsync(p->local, words.data(), words.size() * 4, cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    cudaStreamDestroy(s);
+    if (e != cudaSuccess) return cuda_fail(e, "release of the local exchange flags");
+    return ARISTOS_OK;
+}
+
 }  // namespace aristos
+
+extern "C" int aristos_ep_transport_agreed(const int* ok_flags, int world) {
+    if (!ok_flags || world < 1) return 0;
+    return aristos::ep_transport_agreed(ok_flags, world) ? 1 : 0;
+}

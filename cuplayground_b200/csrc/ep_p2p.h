@@ -22,9 +22,13 @@ constexpr int EP_MAX_WINDOWS = 16;
 
 // Collective over the ranks of `bootstrap` (used for the IPC-handle exchange and as a start barrier). The exchange
 // region holds, per rank: flag words, the received row counts (groups int32), xr (xr_bytes) and yg (yg_bytes).
+// Returns ARISTOS_ERR_UNSUPPORTED on EVERY rank when any rank could not allocate or map (all ranks then choose the
+// same fallback); other errors mean the bootstrap collective itself failed.
 aristos_status_t ep_p2p_create(EpComm* bootstrap, int rank, int world, int groups, size_t xr_bytes, size_t yg_bytes,
                                size_t aux_bytes, EpP2P** out);
 void ep_p2p_destroy(EpP2P* p);
+// The transport decision every rank takes from the all-gathered per-rank flags: peer memory only if it works on all.
+bool ep_transport_agreed(const int* ok_flags, int world);
 void* ep_p2p_xr(EpP2P* p);
 void* ep_p2p_yg(EpP2P* p);
 void* ep_p2p_aux(EpP2P* p);   // third exchange buffer (the fp8 path keeps the received activation scales there)
@@ -43,5 +47,16 @@ aristos_status_t ep_p2p_push(EpP2P* p, int which, const void* send_buf, int bloc
 aristos_status_t ep_p2p_signal(EpP2P* p, int kind, int window, cudaStream_t stream);
 // Order `stream` behind the arrival of (kind, window) from every rank.
 aristos_status_t ep_p2p_wait(EpP2P* p, int kind, int window, cudaStream_t stream);
+// This rank's flag words of (kind, window), indexed by source rank, and the epoch of the current forward: what a
+// kernel needs to wait for one source's rows itself instead of ordering the whole stream behind every rank.
+const uint32_t* ep_p2p_flags(const EpP2P* p, int kind, int window);
+uint32_t ep_p2p_epoch(const EpP2P* p);
+// One small kernel: count[e] of every expert goes into its owner's received-count list (entry rank * E_local +
+// e % E_local) and the EP_FLAG_COUNT flag (window 0) of this rank is raised at every rank.
+aristos_status_t ep_p2p_send_counts(EpP2P* p, const int32_t* count, int E, int E_local, cudaStream_t stream);
+// Host-side release: store the current epoch into every one of THIS rank's flag words, so that stream waits and
+// kernel waits of the current forward that a missing peer left unsatisfied complete (their data is then undefined;
+// the caller marks the forward failed).
+aristos_status_t ep_p2p_release_local_waits(EpP2P* p);
 
 }  // namespace aristos

@@ -103,6 +103,18 @@ __global__ void bounded_wait_selftest_kernel(uint64_t limit_ns, int32_t* dev_sta
     const bool ok = ptx::mbar_wait_bounded(ptx::smem_u32(&bar), 0, &abort_flag, dev_status, limit_ns);
     if (threadIdx.x == 0) *waited_ns = ok ? 0 : ptx::globaltimer_ns() - t0;
 }
+// The same for the wait on an arrival flag in global memory (what the up projection's producer does for every source
+// rank in the expert-parallel layer): a flag word that nothing raises to `epoch`.
+__global__ void bounded_flag_wait_selftest_kernel(const uint32_t* flag, uint32_t epoch, uint64_t limit_ns,
+                                                  int32_t* dev_status, uint64_t* waited_ns) {
+    __shared__ int abort_flag;
+    abort_flag = 0;
+    __syncwarp();
+    const uint64_t t0 = ptx::globaltimer_ns();
+    bool ok = true;
+    if (threadIdx.x == 0) ok = ptx::flag_wait_bounded(flag, epoch, &abort_flag, dev_status, limit_ns);
+    if (threadIdx.x == 0) *waited_ns = ok ? 0 : ptx::globaltimer_ns() - t0;
+}
 }  // namespace
 }  // namespace aristos
 
@@ -111,15 +123,42 @@ extern "C" int aristos_ffn_group_order(int position, int groups, int experts) {
     return ordered_group(position, groups, experts);
 }
 
+extern "C" aristos_status_t aristos_ffn_set_tile_mode(int mode) {
+    if (mode < -1 || mode > 3) { set_last_error("ffn_set_tile_mode: mode must be -1 .. 3"); return ARISTOS_ERR_INVALID_ARG; }
+    ffn_set_tile_mode(mode);
+    return ARISTOS_OK;
+}
+
+extern "C" int aristos_ffn_tile_coord(int local, int row_tiles, int col_tiles, int band, int* row_tile, int* col_tile) {
+    if (!row_tile || !col_tile || row_tiles < 1 || col_tiles < 1 || local < 0 || local >= row_tiles * col_tiles) return -1;
+    band_tile_coord(local, row_tiles, col_tiles, band, row_tile, col_tile);
+    return 0;
+}
+
+static aristos_status_t selftest_wait(int which, int limit_ms, int* waited_ms, void* stream);
+
 extern "C" aristos_status_t aristos_selftest_bounded_wait(int limit_ms, int* waited_ms, void* stream) {
+    return selftest_wait(0, limit_ms, waited_ms, stream);
+}
+
+extern "C" aristos_status_t aristos_selftest_bounded_flag_wait(int limit_ms, int* waited_ms, void* stream) {
+    return selftest_wait(1, limit_ms, waited_ms, stream);
+}
+
+static aristos_status_t selftest_wait(int which, int limit_ms, int* waited_ms, void* stream) {
     if (limit_ms < 1 || limit_ms > 5000) { set_last_error("selftest: limit_ms must be in 1..5000"); return ARISTOS_ERR_INVALID_ARG; }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     int32_t* d_status = nullptr;
-    ARISTOS_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&d_status), 16));
+    ARISTOS_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&d_status), 32));
     uint64_t* d_waited = reinterpret_cast<uint64_t*>(d_status + 2);
-    cudaError_t e = cudaMemsetAsync(d_status, 0, 16, st);
+    cudaError_t e = cudaMemsetAsync(d_status, 0, 32, st);
     if (e == cudaSuccess) {
-        bounded_wait_selftest_kernel<<<1, 32, 0, st>>>((uint64_t)limit_ms * 1000000ull, d_status, d_waited);
+        // the flag word (d_status + 4) stays 0; the wait asks for epoch 1
+        if (which == 1)
+            bounded_flag_wait_selftest_kernel<<<1, 32, 0, st>>>(reinterpret_cast<uint32_t*>(d_status + 4), 1u,
+                                                                (uint64_t)limit_ms * 1000000ull, d_status, d_waited);
+        else
+            bounded_wait_selftest_kernel<<<1, 32, 0, st>>>((uint64_t)limit_ms * 1000000ull, d_status, d_waited);
         ARISTOS_COUNT_LAUNCH();
         e = cudaGetLastError();
     }

@@ -74,7 +74,19 @@ struct FfnGemmParams {
     int32_t* dev_status;
     int peer_world;         // > 0: output tiles go straight to the rank that sent the rows (group g came from rank
     int peer_rank;          //      g / experts) through PeerOutMaps, as group peer_rank * experts + g % experts
+    int rows_mode;          // ROWS_ALL, ROWS_FULL_PAIRS (pair kernel: whole 256-row tiles only) or ROWS_TAIL (single-CTA
+                            // kernel: the < 256 rows per group that the pair kernel left)
+    int band;               // row tiles per band of the tile order (band_tile_coord); 0 = row tile fastest
+    int first_source;       // ring start of the source order inside an expert (this rank: its own rows come first)
+    // Arrival flags of the rows of each source rank (expert parallel, rows stored by the peers' gather kernels):
+    // the producer waits until src_flags[src] has reached flag_epoch before it loads the first tile of a group that
+    // came from rank src. nullptr: the rows are complete before the launch.
+    const uint32_t* src_flags;
+    uint32_t flag_epoch;
+    uint32_t flag_limit_ms;
 };
+
+enum { ROWS_ALL = 0, ROWS_FULL_PAIRS = 1, ROWS_TAIL = 2 };
 
 // One output tensor map per source rank: that rank's buffer for returned expert outputs, (all experts, rows, N),
 // mapped into this process. The epilogue's TMA store then IS the return all-to-all, tile by tile.
@@ -82,6 +94,69 @@ constexpr int MAX_PEER_OUT = 8;
 struct PeerOutMaps {
     CUtensorMap m[MAX_PEER_OUT];
 };
+
+// Rows of group g inside the row window of this launch.
+__device__ __forceinline__ int window_rows(const FfnGemmParams& p, int g) {
+    return max(0, min(p.count[g] - p.row_begin, p.row_end - p.row_begin));
+}
+// Row tiles this launch computes for a group with `rows` rows in the window (TILE_ROWS = 128 or 256).
+template <int TILE_ROWS>
+__device__ __forceinline__ int row_tiles_of(const FfnGemmParams& p, int rows) {
+    if (p.rows_mode == ROWS_FULL_PAIRS) return rows / 256;
+    if (p.rows_mode == ROWS_TAIL) return (rows % 256 + 127) / 128;
+    return (rows + TILE_ROWS - 1) / TILE_ROWS;
+}
+struct TileCoord {
+    int g, m0, n0;
+};
+// Tile number -> (group, first row, first output column); vg walks forward through the prefix.
+template <int TILE_ROWS>
+__device__ __forceinline__ TileCoord decode_tile(const FfnGemmParams& p, const int* prefix, int& vg, int tile,
+                                                 int n_tiles, int out_w) {
+    while (tile >= prefix[vg + 1]) ++vg;
+    TileCoord t;
+    t.g = ordered_group(vg, p.groups, p.experts, p.first_source);
+    const int local = tile - prefix[vg];
+    const int mt = (prefix[vg + 1] - prefix[vg]) / n_tiles;
+    int m, n;
+    band_tile_coord(local, mt, n_tiles, p.band, &m, &n);
+    const int start = p.rows_mode == ROWS_TAIL ? (window_rows(p, t.g) / 256) * 256 : 0;
+    t.m0 = p.row_begin + start + m * TILE_ROWS;
+    t.n0 = n * out_w;
+    return t;
+}
+// Every CTA builds the same prefix over the groups (in walking order) of tiles per group; one warp, 32 groups a step.
+template <int TILE_ROWS>
+__device__ __forceinline__ void build_tile_prefix(const FfnGemmParams& p, int* prefix, int n_tiles, int lane) {
+    int running = 0;
+    if (lane == 0) prefix[0] = 0;
+    for (int g0 = 0; g0 < p.groups; g0 += 32) {
+        const int g = g0 + lane;
+        int v = 0;
+        if (g < p.groups)
+            v = row_tiles_of<TILE_ROWS>(p, window_rows(p, ordered_group(g, p.groups, p.experts, p.first_source))) * n_tiles;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int o = __shfl_up_sync(0xffffffffu, v, d);
+            if (lane >= d) v += o;
+        }
+        if (g < p.groups) prefix[g + 1] = running + v;
+        running += __shfl_sync(0xffffffffu, v, 31);
+    }
+}
+// Producer side of the device-initiated exchange (the reference's nvshmem_signal_wait_until before each peer's GEMM,
+// auditorium/overlap.cuh:102-105, with a limit): before the first load of rows that came from rank src, wait until
+// that rank's arrival flag has reached this forward's epoch. `seen` caches the sources already observed.
+__device__ __forceinline__ bool wait_source_rows(const FfnGemmParams& p, int g, uint32_t& seen, volatile int* abort_flag) {
+    if (p.src_flags == nullptr) return true;
+    const int src = g / p.experts;
+    if ((seen >> src) & 1u) return true;
+    if (!ptx::flag_wait_bounded(p.src_flags + src, p.flag_epoch, abort_flag, p.dev_status,
+                                (uint64_t)p.flag_limit_ms * 1000000ull))
+        return false;
+    seen |= 1u << src;
+    return true;
+}
 
 __device__ __forceinline__ uint32_t pack_16bit(float a, float b, int fmt) {
     if (fmt == FMT_F16) {
@@ -268,7 +343,6 @@ ffn_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
 
     const int out_w = p.gated ? 128 : 256;             // output columns per tile
     const int n_tiles = (p.N + out_w - 1) / out_w;
-    const int window = p.row_end - p.row_begin;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -283,25 +357,7 @@ ffn_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         ptx::fence_mbar_init();
     }
     if (warp == 0) {
-        // inclusive warp scan over groups, 32 at a time
-        int running = 0;
-        if (lane == 0) prefix[0] = 0;
-        for (int g0 = 0; g0 < p.groups; g0 += 32) {
-            const int g = g0 + lane;
-            int v = 0;
-            if (g < p.groups) {
-                int rows = p.count[ordered_group(g, p.groups, p.experts)] - p.row_begin;
-                rows = max(0, min(rows, window));
-                v = ((rows + BM - 1) / BM) * n_tiles;
-            }
-#pragma unroll
-            for (int d = 1; d < 32; d <<= 1) {
-                const int o = __shfl_up_sync(0xffffffffu, v, d);
-                if (lane >= d) v += o;
-            }
-            if (g < p.groups) prefix[g + 1] = running + v;
-            running += __shfl_sync(0xffffffffu, v, 31);
-        }
+        build_tile_prefix<BM>(p, prefix, n_tiles, lane);
     } else if (warp == 1) {
         ptx::tmem_alloc(ptx::smem_u32(tmem_slot), TMEM_COLS);
     }
@@ -322,16 +378,15 @@ ffn_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
             int stage = 0;
             uint32_t phase = 0;
             int vg = 0;
+            uint32_t seen = 0;
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-                while (tile >= prefix[vg + 1]) ++vg;
-                const int g = ordered_group(vg, p.groups, p.experts);
-                const int local = tile - prefix[vg];
-                const int mt = (prefix[vg + 1] - prefix[vg]) / n_tiles;
-                const int m0 = p.row_begin + (local % mt) * BM;
-                const int n0 = (local / mt) * out_w;
+                const TileCoord t = decode_tile<BM>(p, prefix, vg, tile, n_tiles, out_w);
+                const int g = t.g, m0 = t.m0, n0 = t.n0;
                 const int e = g % p.experts;
                 const int n1 = p.gated ? n0 : n0 + 128;
+                ok = wait_source_rows(p, g, seen, abort_flag);
+                if (!ok) break;
                 for (int kb = 0; kb < kblocks; ++kb) {
                     ok = ptx::mbar_wait_bounded(bar_empty + 8 * stage, phase ^ 1u, abort_flag, p.dev_status);
                     if (!ok) break;
@@ -390,12 +445,8 @@ ffn_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         int it = 0;
         bool ok = true;
         for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
-            while (tile >= prefix[vg + 1]) ++vg;
-            const int g = ordered_group(vg, p.groups, p.experts);
-            const int local = tile - prefix[vg];
-            const int mt = (prefix[vg + 1] - prefix[vg]) / n_tiles;
-            const int m0 = p.row_begin + (local % mt) * BM;
-            const int n0 = (local / mt) * out_w;
+            const TileCoord t = decode_tile<BM>(p, prefix, vg, tile, n_tiles, out_w);
+            const int g = t.g, m0 = t.m0, n0 = t.n0;
             const int buf = it & 1;
             const uint32_t aphase = (it >> 1) & 1u;
             ok = ptx::mbar_wait_bounded(bar_tfull + 8 * buf, aphase, abort_flag, p.dev_status);
@@ -462,7 +513,6 @@ ffn_grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gr
 
     const int out_w = p.gated ? 128 : 256;
     const int n_tiles = (p.N + out_w - 1) / out_w;
-    const int window = p.row_end - p.row_begin;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < P_STAGES; ++s) {
@@ -477,24 +527,7 @@ ffn_grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gr
         ptx::fence_mbar_init();
     }
     if (warp == 0) {
-        int running = 0;
-        if (lane == 0) prefix[0] = 0;
-        for (int g0 = 0; g0 < p.groups; g0 += 32) {
-            const int g = g0 + lane;
-            int v = 0;
-            if (g < p.groups) {
-                int rows = p.count[ordered_group(g, p.groups, p.experts)] - p.row_begin;
-                rows = max(0, min(rows, window));
-                v = ((rows + PBM - 1) / PBM) * n_tiles;
-            }
-#pragma unroll
-            for (int d = 1; d < 32; d <<= 1) {
-                const int o = __shfl_up_sync(0xffffffffu, v, d);
-                if (lane >= d) v += o;
-            }
-            if (g < p.groups) prefix[g + 1] = running + v;
-            running += __shfl_sync(0xffffffffu, v, 31);
-        }
+        build_tile_prefix<PBM>(p, prefix, n_tiles, lane);
     } else if (warp == 1) {
         ptx::tmem_alloc_pair(ptx::smem_u32(tmem_slot), TMEM_COLS);
     }
@@ -518,16 +551,15 @@ ffn_grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gr
             int stage = 0;
             uint32_t phase = 0;
             int vg = 0;
+            uint32_t seen = 0;
             bool ok = true;
             for (int tile = pair; ok && tile < total_tiles; tile += num_pairs) {
-                while (tile >= prefix[vg + 1]) ++vg;
-                const int g = ordered_group(vg, p.groups, p.experts);
-                const int local = tile - prefix[vg];
-                const int mt = (prefix[vg + 1] - prefix[vg]) / n_tiles;
-                const int m0 = p.row_begin + (local % mt) * PBM + (int)cta * BM;
-                const int n0 = (local / mt) * out_w;
+                const TileCoord t = decode_tile<PBM>(p, prefix, vg, tile, n_tiles, out_w);
+                const int g = t.g, m0 = t.m0 + (int)cta * BM, n0 = t.n0;
                 const int e = g % p.experts;
                 const int nb = p.gated ? n0 : n0 + (int)cta * 128;
+                ok = wait_source_rows(p, g, seen, abort_flag);
+                if (!ok) break;
                 for (int kb = 0; kb < kblocks; ++kb) {
                     ok = ptx::mbar_wait_bounded(bar_empty + 8 * stage, phase ^ 1u, abort_flag, p.dev_status);
                     if (!ok) break;
@@ -590,12 +622,8 @@ ffn_grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gr
         int it = 0;
         bool ok = true;
         for (int tile = pair; ok && tile < total_tiles; tile += num_pairs, ++it) {
-            while (tile >= prefix[vg + 1]) ++vg;
-            const int g = ordered_group(vg, p.groups, p.experts);
-            const int local = tile - prefix[vg];
-            const int mt = (prefix[vg + 1] - prefix[vg]) / n_tiles;
-            const int m0 = p.row_begin + (local % mt) * PBM + (int)cta * BM;
-            const int n0 = (local / mt) * out_w;
+            const TileCoord t = decode_tile<PBM>(p, prefix, vg, tile, n_tiles, out_w);
+            const int g = t.g, m0 = t.m0 + (int)cta * BM, n0 = t.n0;
             const int buf = it & 1;
             const uint32_t aphase = (it >> 1) & 1u;
             ok = ptx::mbar_wait_bounded(bar_tfull + 8 * buf, aphase, abort_flag, p.dev_status);
@@ -635,24 +663,69 @@ aristos_status_t make_map_3d(CUtensorMap* tm, const void* base, int K, int rows,
     return encode_map_3d(tm, dt, fmt == FMT_TF32 ? 4 : 2, base, K, rows, outer, 128);
 }
 
-// Tile shape: single-CTA 128 x 256 tiles by default. CTA pairs (256 x 256 tiles, cta_group::2) halve the B bytes each
-// SM stages and lower the power per FLOP, but their 256-row granularity pads the tail of every row group twice as
-// much and, measured back to back on one power-capped GPU (16384 tokens, 8 experts, H 4096, I 14336: 9.62 / 9.75 ms
-// against 10.01 / 10.06 ms for the two GEMMs), they were 3-4 % slower. ARISTOS_FFN_TILES=pair selects them where the
-// row window holds at least 1024 rows; ARISTOS_FFN_TILES=pair-always for every window.
-bool use_pair_tiles(int window_rows) {
-    static int forced = -1;
-    if (forced < 0) {
+// Tile shapes. A single-CTA 128 x 256 tile stages 48 KB per 64-wide K block and is bound by the bandwidth that feeds
+// the operands to the SM; a CTA pair (cta_group::2, 256 x 256 tile) stages 32 KB per SM for the same work. The pair
+// kernel computes whole 256-row tiles only and the single-CTA kernel finishes the < 256 remaining rows of every
+// group in a second launch, so pairing never pads a group by more than the 128-row tile does.
+//   TILES_AUTO    pairs (+ single-CTA tail) where the row window holds at least 1024 rows, else single-CTA tiles
+//   TILES_SINGLE  single-CTA tiles only
+//   TILES_PAIR    pairs (+ tail) for every window
+//   TILES_PAIR_PADDED  pairs only, every group padded to whole 256-row tiles
+enum { TILES_AUTO = 0, TILES_SINGLE = 1, TILES_PAIR = 2, TILES_PAIR_PADDED = 3 };
+int g_tile_mode = -1;      // -1: not yet read from the environment
+int g_band_rows = -1;
+
+int tile_mode() {
+    if (g_tile_mode < 0) {
         const char* env = getenv("ARISTOS_FFN_TILES");
-        forced = !env ? 0 : (!strcmp(env, "pair") ? 2 : (!strcmp(env, "pair-always") ? 3 : 0));
+        g_tile_mode = !env ? TILES_AUTO
+                           : (!strcmp(env, "single") ? TILES_SINGLE
+                              : (!strcmp(env, "pair") ? TILES_PAIR
+                                 : (!strcmp(env, "pair-padded") ? TILES_PAIR_PADDED : TILES_AUTO)));
     }
-    if (forced == 3) return true;
-    if (forced == 2) return window_rows >= 1024;
-    return false;
+    return g_tile_mode;
 }
 
-aristos_status_t launch_gemm(const void* A, const void* B0, const void* B1, const FfnGemmParams& p,
-                             const PeerOutMaps& peers, int grid_limit, cudaStream_t st) {
+// Rows per band of the tile order. A group whose A panel (rows x K) stays in L2 keeps the row-tile-fastest order
+// (every B panel is then read from HBM once); a larger panel is walked in bands of 2048 rows, so that the CTAs of a
+// wave share 2048 rows of A and about 8 B panels instead of re-reading the whole A panel for every few B panels.
+// ARISTOS_FFN_BAND_ROWS overrides (0 = never band).
+int band_rows_for(int window_rows, int K, int elt) {
+    if (g_band_rows < 0) {
+        const char* env = getenv("ARISTOS_FFN_BAND_ROWS");
+        g_band_rows = env ? atoi(env) : 1;      // 1: automatic
+        if (g_band_rows < 0) g_band_rows = 1;
+    }
+    if (g_band_rows != 1) return g_band_rows / 256 * 256;
+    return (int64_t)window_rows * K * elt > (48ll << 20) ? 2048 : 0;
+}
+
+aristos_status_t max_pair_clusters(int* out) {
+    // a persistent grid must be fully co-resident: ask how many 2-CTA clusters the device can hold at once
+    static int max_clusters = -1;
+    if (max_clusters < 0) {
+        ARISTOS_CUDA_TRY(cudaFuncSetAttribute(ffn_grouped_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                              P_SMEM_BYTES));
+        cudaLaunchConfig_t lc = {};
+        lc.gridDim = dim3(2 * (device_sm_count() / 2));
+        lc.blockDim = dim3(FFN_THREADS);
+        lc.dynamicSmemBytes = P_SMEM_BYTES;
+        cudaLaunchAttribute at;
+        at.id = cudaLaunchAttributeClusterDimension;
+        at.val.clusterDim.x = 2; at.val.clusterDim.y = 1; at.val.clusterDim.z = 1;
+        lc.attrs = &at;
+        lc.numAttrs = 1;
+        int n = 0;
+        ARISTOS_CUDA_TRY(cudaOccupancyMaxActiveClusters(&n, ffn_grouped_gemm_pair_kernel, &lc));
+        max_clusters = n;
+        if (getenv("ARISTOS_DEBUG")) fprintf(stderr, "[aristos] co-resident 2-CTA clusters: %d\n", n);
+    }
+    *out = max_clusters;
+    return ARISTOS_OK;
+}
+
+aristos_status_t launch_gemm(const void* A, const void* B0, const void* B1, FfnGemmParams p, const PeerOutMaps& peers,
+                             int grid_limit, cudaStream_t st) {
     CUtensorMap tmA, tmB0, tmB1, tmOut;
     ARISTOS_TRY(make_map_3d(&tmA, A, p.K, p.rows_per_group, p.groups, p.fmt));
     ARISTOS_TRY(make_map_3d(&tmB0, B0, p.K, p.N, p.experts, p.fmt));
@@ -663,39 +736,32 @@ aristos_status_t launch_gemm(const void* A, const void* B0, const void* B1, cons
     if (sms <= 0) { set_last_error("no CUDA device"); return ARISTOS_ERR_CUDA; }
     if (grid_limit > 0 && grid_limit < sms) sms = grid_limit;
     const int window = p.row_end - p.row_begin;
-    if (use_pair_tiles(window)) {
-        ARISTOS_CUDA_TRY(cudaFuncSetAttribute(ffn_grouped_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                              P_SMEM_BYTES));
+    const int band_rows = band_rows_for(window, p.K, p.fmt == FMT_TF32 ? 4 : 2);
+    const int mode = tile_mode();
+    const bool pairs = mode == TILES_PAIR || mode == TILES_PAIR_PADDED || (mode == TILES_AUTO && window >= 1024);
+    if (pairs) {
+        int max_clusters = 0;
+        ARISTOS_TRY(max_pair_clusters(&max_clusters));
         const int64_t bound = (int64_t)p.groups * ceil_div(window, PBM) * ceil_div(p.N, out_w);
-        // a persistent grid must be fully co-resident: ask how many 2-CTA clusters the device can hold at once
-        static int max_clusters = -1;
-        if (max_clusters < 0) {
-            cudaLaunchConfig_t lc = {};
-            lc.gridDim = dim3(2 * (device_sm_count() / 2));
-            lc.blockDim = dim3(FFN_THREADS);
-            lc.dynamicSmemBytes = P_SMEM_BYTES;
-            cudaLaunchAttribute at;
-            at.id = cudaLaunchAttributeClusterDimension;
-            at.val.clusterDim.x = 2; at.val.clusterDim.y = 1; at.val.clusterDim.z = 1;
-            lc.attrs = &at;
-            lc.numAttrs = 1;
-            int n = 0;
-            ARISTOS_CUDA_TRY(cudaOccupancyMaxActiveClusters(&n, ffn_grouped_gemm_pair_kernel, &lc));
-            max_clusters = n;
-            if (getenv("ARISTOS_DEBUG")) fprintf(stderr, "[aristos] co-resident 2-CTA clusters: %d\n", n);
+        int npairs = sms / 2 < max_clusters ? sms / 2 : max_clusters;
+        if (bound < npairs) npairs = (int)bound;
+        p.rows_mode = mode == TILES_PAIR_PADDED ? ROWS_ALL : ROWS_FULL_PAIRS;
+        p.band = band_rows / PBM;
+        if (npairs > 0 && (mode == TILES_PAIR_PADDED || window >= PBM)) {
+            ffn_grouped_gemm_pair_kernel<<<2 * npairs, FFN_THREADS, P_SMEM_BYTES, st>>>(tmA, tmB0, tmB1, tmOut, peers, p);
+            ARISTOS_COUNT_LAUNCH();
+            ARISTOS_CUDA_TRY(cudaGetLastError());
         }
-        int pairs = sms / 2 < max_clusters ? sms / 2 : max_clusters;
-        if (bound < pairs) pairs = (int)bound;
-        if (pairs <= 0) return ARISTOS_OK;
-        ffn_grouped_gemm_pair_kernel<<<2 * pairs, FFN_THREADS, P_SMEM_BYTES, st>>>(tmA, tmB0, tmB1, tmOut, peers, p);
-    } else {
-        ARISTOS_CUDA_TRY(cudaFuncSetAttribute(ffn_grouped_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                              SMEM_BYTES));
-        const int64_t bound = (int64_t)p.groups * ceil_div(window, BM) * ceil_div(p.N, out_w);
-        const int grid = (int)(bound < sms ? bound : sms);
-        if (grid <= 0) return ARISTOS_OK;
-        ffn_grouped_gemm_kernel<<<grid, FFN_THREADS, SMEM_BYTES, st>>>(tmA, tmB0, tmB1, tmOut, peers, p);
+        if (mode == TILES_PAIR_PADDED) return ARISTOS_OK;
+        p.rows_mode = ROWS_TAIL;     // the single-CTA kernel below finishes every group's last < 256 rows
     }
+    ARISTOS_CUDA_TRY(cudaFuncSetAttribute(ffn_grouped_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          SMEM_BYTES));
+    p.band = band_rows / BM;
+    const int64_t bound = (int64_t)p.groups * (pairs ? 2 : ceil_div(window, BM)) * ceil_div(p.N, out_w);
+    const int grid = (int)(bound < sms ? bound : sms);
+    if (grid <= 0) return ARISTOS_OK;
+    ffn_grouped_gemm_kernel<<<grid, FFN_THREADS, SMEM_BYTES, st>>>(tmA, tmB0, tmB1, tmOut, peers, p);
     ARISTOS_COUNT_LAUNCH();
     ARISTOS_CUDA_TRY(cudaGetLastError());
     return ARISTOS_OK;
@@ -703,14 +769,21 @@ aristos_status_t launch_gemm(const void* A, const void* B0, const void* B1, cons
 
 }  // namespace
 
+void ffn_set_tile_mode(int mode) { g_tile_mode = (mode >= TILES_AUTO && mode <= TILES_PAIR_PADDED) ? mode : -1; }
+int ffn_tile_mode() { return tile_mode(); }
+
 aristos_status_t expert_ffn_tc_sm100(const void* xg, const int32_t* count, int groups, int rows_per_group,
                                         int experts, const void* w1, const void* w3, const void* w2, const void* b1,
                                         const void* b3, const void* b2, void* h_scratch, void* y, int H, int I,
                                         int hidden_act, int fmt, int row_begin, int row_end, int sm_limit,
-                                        int32_t* dev_status, cudaStream_t st, void* const* peer_y, int peer_world,
-                                        int peer_rank) {
-    if (peer_world > MAX_PEER_OUT || (peer_world > 0 && (!peer_y || groups != peer_world * experts))) {
+                                        int32_t* dev_status, cudaStream_t st, const FfnEpArgs* ep) {
+    const int peer_world = ep ? ep->peer_world : 0;
+    if (peer_world > MAX_PEER_OUT || (peer_world > 0 && (!ep->peer_y || groups != peer_world * experts))) {
         set_last_error("expert_ffn: peer output needs world <= %d and groups == world * experts", MAX_PEER_OUT);
+        return ARISTOS_ERR_INVALID_ARG;
+    }
+    if (ep && ep->src_flags && (experts <= 0 || groups / experts > 32)) {
+        set_last_error("expert_ffn: arrival flags need at most 32 source ranks");
         return ARISTOS_ERR_INVALID_ARG;
     }
     if (groups > MAX_GROUPS) { set_last_error("expert_ffn: more than %d row groups", MAX_GROUPS); return ARISTOS_ERR_CONFIG; }
@@ -726,6 +799,12 @@ aristos_status_t expert_ffn_tc_sm100(const void* xg, const int32_t* count, int g
     p.row_end = row_end;
     p.dev_status = dev_status;
     p.fmt = fmt;
+    if (ep) {
+        p.first_source = ep->first_source;
+        p.src_flags = ep->src_flags;
+        p.flag_epoch = ep->flag_epoch;
+        p.flag_limit_ms = ep->flag_limit_ms > 0 ? ep->flag_limit_ms : 2000;
+    }
     // up-projection: h = epi(xg * W1^T [, xg * W3^T])
     p.N = I;
     p.K = H;
@@ -736,7 +815,8 @@ aristos_status_t expert_ffn_tc_sm100(const void* xg, const int32_t* count, int g
     p.bias1 = gated ? b3 : nullptr;
     static const PeerOutMaps no_peers{};
     ARISTOS_TRY(launch_gemm(xg, w1, gated ? w3 : w1, p, no_peers, sm_limit, st));
-    // down-projection: y = h * W2^T
+    // down-projection: y = h * W2^T (h was written by the launch above: nothing left to wait for)
+    p.src_flags = nullptr;
     p.N = H;
     p.K = I;
     p.gated = 0;
@@ -749,9 +829,9 @@ aristos_status_t expert_ffn_tc_sm100(const void* xg, const int32_t* count, int g
         // in rank src's block peer_rank * experts + e_local
         PeerOutMaps peers{};
         for (int d = 0; d < peer_world; ++d)
-            ARISTOS_TRY(make_map_3d(&peers.m[d], peer_y[d], H, rows_per_group, peer_world * experts, fmt));
+            ARISTOS_TRY(make_map_3d(&peers.m[d], ep->peer_y[d], H, rows_per_group, peer_world * experts, fmt));
         p.peer_world = peer_world;
-        p.peer_rank = peer_rank;
+        p.peer_rank = ep->peer_rank;
         ARISTOS_TRY(launch_gemm(h_scratch, w2, w2, p, peers, sm_limit, st));
         return ARISTOS_OK;
     }

@@ -6,10 +6,14 @@
 // per-peer pipeline "put tile -> wait flag -> GEMM -> put result -> wait flag" (:94-153) becomes the chunked
 // exchange below: rows travel in row windows of every expert block, the GEMMs of window c run while window c+1 is
 // still in flight, and the results of window c return while window c+1 is being computed).
+#include <nvtx3/nvToolsExt.h>
+
+#include <chrono>
 #include <cmath>
 #include <cstdlib>
 #include <cstring>
 #include <new>
+#include <thread>
 #include <vector>
 
 #include "common.cuh"
@@ -66,8 +70,18 @@ struct aristos_moe {
     bool ep_direct = false;                  // p2p: gather/return kernels store through peer pointers
     int direct_windows = 1;                  // row windows of the direct mode (gather / GEMMs / return pipelined)
     bool fused_return = false;               // direct mode: the down projection's epilogue stores into the source ranks
+    bool kernel_wait = false;                // direct mode: the up projection waits for each source's rows itself
     int64_t launches = 0;
     const void *b1 = nullptr, *b3 = nullptr, *b2 = nullptr;   // optional expert biases (caller-owned, device)
+    // failure handling of the exchange: every wait for a forward's completion has a wall-clock limit; on expiry the
+    // rank releases its own flag waits, and the handle refuses further forwards (its epochs no longer match the peers')
+    int timeout_ms = 30000;
+    bool failed = false;
+    cudaEvent_t ev_last = nullptr;           // end of the last forward on its stream
+    bool ev_last_valid = false;
+    // training mode (is_training = 1): routing of the last forward kept for a backward pass + load-balance statistics
+    int32_t *saved_topk_idx = nullptr, *saved_slot_of = nullptr;
+    float *saved_topk_w = nullptr, *lb_stats = nullptr;
     // stage stopwatch
     static constexpr int PROF_SETS = 64;      // ring of event sets: stage times average over the last 64 forwards
     bool profiling = false;
@@ -104,6 +118,12 @@ size_t plan_workspace(aristos_moe* L, char* base) {
     CARVE(slot_of, int32_t*, S * k * 4)
     CARVE(token_of_slot, int32_t*, E * cap * 4)
     CARVE(gate_bias, float*, E * 4)
+    if (L->cfg.is_training) {
+        CARVE(saved_topk_idx, int32_t*, S * k * 4)
+        CARVE(saved_topk_w, float*, S * k * 4)
+        CARVE(saved_slot_of, int32_t*, S * k * 4)
+        CARVE(lb_stats, float*, (2 * E + 2) * 4)
+    }
     CARVE(dispatch_scratch, void*, L->dispatch_scratch_bytes)
     if (L->gate_scratch_bytes) CARVE(gate_scratch, void*, L->gate_scratch_bytes)
     if (L->fp8) {
@@ -142,6 +162,39 @@ size_t plan_workspace(aristos_moe* L, char* base) {
     CARVE(slots[1].out_dev, void*, S * H * elt)
 #undef CARVE
     return c.off;
+}
+
+// Waits for `ev` with the layer's wall-clock limit when the layer takes part in an exchange (a peer that stops leaves
+// stream waits and flag waits unsatisfied; cudaEventSynchronize / cudaDeviceSynchronize would then never return).
+// On expiry this rank's own flag words are set to the current epoch from the host, which completes every wait of
+// the forward in flight; the forward's result is then undefined, the handle is marked failed and
+// ARISTOS_ERR_DEVICE_TIMEOUT returned. The NCCL transport has no flags to release: the handle is marked failed and
+// the caller has to end the process group.
+aristos_status_t wait_event_bounded(aristos_moe* L, cudaEvent_t ev) {
+    if (L->world == 1 || !ev) {
+        if (ev) ARISTOS_CUDA_TRY(cudaEventSynchronize(ev));
+        return ARISTOS_OK;
+    }
+    const auto t0 = std::chrono::steady_clock::now();
+    for (int spins = 0;; ++spins) {
+        const cudaError_t q = cudaEventQuery(ev);
+        if (q == cudaSuccess) return ARISTOS_OK;
+        if (q != cudaErrorNotReady) return cuda_fail(q, "cudaEventQuery");
+        const auto ms = std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0).count();
+        if (ms > L->timeout_ms) break;
+        if (spins > 2000) std::this_thread::sleep_for(std::chrono::microseconds(200));
+    }
+    L->failed = true;
+    if (L->p2p) {
+        ARISTOS_TRY(ep_p2p_release_local_waits(L->p2p));
+        // the released forward now runs to its end on whatever rows are there; its bounded kernels cannot hang
+        ARISTOS_CUDA_TRY(cudaEventSynchronize(ev));
+        set_last_error("a peer did not take part in the exchange within %d ms: this rank's waits were released, the "
+                       "forward's result is undefined", L->timeout_ms);
+    } else {
+        set_last_error("the NCCL exchange did not complete within %d ms", L->timeout_ms);
+    }
+    return ARISTOS_ERR_DEVICE_TIMEOUT;
 }
 
 aristos_status_t ensure_workspace(aristos_moe* L) {
@@ -226,7 +279,9 @@ aristos_status_t aristos_moe_create(const aristos_config_t* cfg, int rank, int w
         // row windows of the overlapped exchange
         ep_row_windows(L->cap, 4, 512, &L->chunk_rows, &L->chunks);
         if (const char* env = getenv("ARISTOS_EP_CHUNKS"))
-            if (atoi(env) >= 1) ep_row_windows(L->cap, atoi(env), 128, &L->chunk_rows, &L->chunks);
+            if (atoi(env) >= 1) ep_row_windows(L->cap, std::min(atoi(env), EP_MAX_WINDOWS), 128, &L->chunk_rows, &L->chunks);
+        if (const char* env = getenv("ARISTOS_EP_TIMEOUT_MS"))
+            if (atoi(env) >= 1) L->timeout_ms = atoi(env);
         L->ffn_sm_limit = device_sm_count() - (nccl_ctas > 0 ? nccl_ctas : 16);
         if (const char* env = getenv("ARISTOS_EP_FFN_SMS"))
             if (atoi(env) >= 1) L->ffn_sm_limit = atoi(env);
@@ -236,6 +291,7 @@ aristos_status_t aristos_moe_create(const aristos_config_t* cfg, int rank, int w
             e = cudaEventCreateWithFlags(&L->ev_in[c], cudaEventDisableTiming);
             if (e == cudaSuccess) e = cudaEventCreateWithFlags(&L->ev_out[c], cudaEventDisableTiming);
         }
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&L->ev_last, cudaEventDisableTiming);
         if (e != cudaSuccess) { aristos_moe_destroy(L); return cuda_fail(e, "stream/event creation"); }
         // transport of the rows: peer memory (default) or NCCL send/recv (ARISTOS_EP_TRANSPORT=nccl, or when the
         // peer-memory set-up is not possible on this machine)
@@ -264,11 +320,20 @@ aristos_status_t aristos_moe_create(const aristos_config_t* cfg, int rank, int w
                 // ARISTOS_EP_FUSED_RETURN=0 keeps the separate return kernel
                 const char* fr = getenv("ARISTOS_EP_FUSED_RETURN");
                 const int tdt = cfg->torch_dtype;
-                L->fused_return = world <= 8 && !(fr && !strcmp(fr, "0")) &&
-                                  (L->fp8 || (L->ep_direct && (tdt == ARISTOS_DTYPE_BF16 || tdt == ARISTOS_DTYPE_F16 ||
-                                                               tdt == ARISTOS_DTYPE_TF32)));
+                const bool tc = tdt == ARISTOS_DTYPE_BF16 || tdt == ARISTOS_DTYPE_F16 || tdt == ARISTOS_DTYPE_TF32;
+                L->fused_return = world <= 8 && !(fr && !strcmp(fr, "0")) && (L->fp8 || (L->ep_direct && tc));
+                // the tensor-core up projection waits for each source rank's rows itself (own rows first) instead
+                // of the stream waiting for every rank before the first tile; ARISTOS_EP_KERNEL_WAIT=0 keeps the
+                // stream waits
+                const char* kw = getenv("ARISTOS_EP_KERNEL_WAIT");
+                L->kernel_wait = L->ep_direct && tc && !(kw && !strcmp(kw, "0"));
             }
-            else if (L->fp8 || (tr && !strcmp(tr, "p2p"))) { aristos_moe_destroy(L); return ps; }
+            else if (L->fp8 || (tr && !strcmp(tr, "p2p")) || ps != ARISTOS_ERR_UNSUPPORTED) {
+                // ARISTOS_ERR_UNSUPPORTED is the agreed answer of every rank (all fall back to NCCL together); any
+                // other status means the bootstrap itself failed
+                aristos_moe_destroy(L);
+                return ps;
+            }
         }
     }
     L->ws_bytes = plan_workspace(L, nullptr);
@@ -280,6 +345,10 @@ size_t aristos_moe_workspace_bytes(const aristos_moe_t* L) { return L ? L->ws_by
 
 aristos_status_t aristos_moe_set_bias(aristos_moe_t* L, const void* b1, const void* b3, const void* b2) {
     if (!L) return ARISTOS_ERR_INVALID_ARG;
+    if (L->fp8 && (b1 || b3 || b2)) {
+        set_last_error("set_bias: the fp8 expert FFN has no bias epilogue");
+        return ARISTOS_ERR_UNSUPPORTED;
+    }
     if ((b1 && !aligned16(b1)) || (b3 && !aligned16(b3)) || (b2 && !aligned16(b2))) {
         set_last_error("set_bias: pointers must be 16-byte aligned");
         return ARISTOS_ERR_INVALID_ARG;
@@ -303,16 +372,38 @@ aristos_status_t aristos_moe_set_workspace(aristos_moe_t* L, void* workspace, si
     return ARISTOS_OK;
 }
 
+static aristos_status_t forward_impl(aristos_moe_t* L, const void* x, const void* w_gate, const float* gate_bias,
+                                     const void* w1, const void* w3, const void* w2, const void* scales, void* out,
+                                     void* stream, bool* exchange_started);
+
 aristos_status_t aristos_moe_forward(aristos_moe_t* L, const void* x, const void* w_gate, const float* gate_bias,
                                      const void* w1, const void* w3, const void* w2, const void* scales, void* out,
                                      void* stream) {
     if (!L || !x || !w_gate || !w1 || !w2 || !out) { set_last_error("forward: NULL pointer"); return ARISTOS_ERR_INVALID_ARG; }
     if (L->cfg.hidden_act == ARISTOS_ACT_SWIGLU && !w3) { set_last_error("forward: SwiGLU needs w3"); return ARISTOS_ERR_INVALID_ARG; }
+    if (L->fp8 && !scales) { set_last_error("forward: fp8 needs the weight scales"); return ARISTOS_ERR_INVALID_ARG; }
+    if (L->failed) {
+        set_last_error("forward: an earlier forward of this expert-parallel layer failed or timed out; its exchange "
+                       "epochs no longer match the peers' - destroy the layer on every rank and create it again");
+        return ARISTOS_ERR_DEVICE_TIMEOUT;
+    }
     ARISTOS_TRY(ensure_workspace(L));
+    bool exchange_started = false;
+    const aristos_status_t s = forward_impl(L, x, w_gate, gate_bias, w1, w3, w2, scales, out, stream, &exchange_started);
+    // a forward that stopped after it announced a new epoch leaves this rank out of step with its peers
+    if (s != ARISTOS_OK && exchange_started) L->failed = true;
+    if (s == ARISTOS_OK && L->ev_last) {
+        if (cudaEventRecord(L->ev_last, static_cast<cudaStream_t>(stream)) == cudaSuccess) L->ev_last_valid = true;
+    }
+    return s;
+}
+
+static aristos_status_t forward_impl(aristos_moe_t* L, const void* x, const void* w_gate, const float* gate_bias,
+                                     const void* w1, const void* w3, const void* w2, const void* scales, void* out,
+                                     void* stream, bool* exchange_started) {
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int64_t launches0 = launch_counter();
     const int dt = L->fp8 ? ARISTOS_DTYPE_BF16 : L->cfg.torch_dtype;     // dtype of x, out and the expert outputs
-    if (L->fp8 && !scales) { set_last_error("forward: fp8 needs the weight scales"); return ARISTOS_ERR_INVALID_ARG; }
 
     const float* bias = gate_bias;
     if (!bias && L->cfg.gate_bias_zipf_s > 0.0) {
@@ -328,11 +419,26 @@ aristos_status_t aristos_moe_forward(aristos_moe_t* L, const void* x, const void
 
     const int prof_set = (int)(L->prof_n % aristos_moe::PROF_SETS) * 5;
 #define PROF_MARK(i) do { if (L->profiling) ARISTOS_CUDA_TRY(cudaEventRecord(L->ev_prof[prof_set + i], st)); } while (0)
+    // NVTX ranges (host side: they bracket the enqueue of each stage, so a profiler timeline groups the stage's
+    // launches; the reference links NVTX without calling it, CMakeLists.txt:104-118)
+    struct StageRange {
+        bool open = false;
+        void next(const char* name) {
+            if (open) nvtxRangePop();
+            nvtxRangePushA(name);
+            open = true;
+        }
+        ~StageRange() { if (open) nvtxRangePop(); }
+    };
+    StageRange whole, stage;
+    whole.next("aristos_moe_forward");
     PROF_MARK(0);
+    stage.next("gate");
     ARISTOS_TRY(aristos_gate_topk_screened(x, w_gate, bias, L->S, L->H, L->E, L->k, L->cfg.gate_fn, L->cfg.renorm_topk,
                                            dt, L->topk_idx, L->topk_w, L->gate_scratch_bytes ? L->gate_scratch : nullptr,
                                            L->gate_scratch_bytes, L->dev_status, st));
     PROF_MARK(1);
+    stage.next("dispatch");
     ARISTOS_TRY(dispatch_impl(L->topk_idx, L->S, L->k, L->E, L->cap, L->count, L->slot_of, L->token_of_slot,
                               L->dispatch_scratch, L->dispatch_scratch_bytes, L->dev_status, st));
     const size_t nb1 = (size_t)L->E_local * (L->I / 128) * (L->H / 128);
@@ -353,6 +459,8 @@ aristos_status_t aristos_moe_forward(aristos_moe_t* L, const void* x, const void
         ep_p2p_peer_ptrs(L->p2p, EP_BUF_AUX, scales_dst.p);
         ep_p2p_peer_ptrs(L->p2p, EP_BUF_YG, y_dst.p);
         ep_p2p_begin(L->p2p);
+        *exchange_started = true;
+        stage.next("exchange");
         ARISTOS_TRY(aristos_quantize_fp8(x, 1, L->S, L->H, 1, ARISTOS_DTYPE_BF16, L->xq, L->sx, stream));
         PeerPtrs count_dst;
         ep_p2p_peer_ptrs(L->p2p, EP_BUF_RCOUNT, count_dst.p);
@@ -363,6 +471,7 @@ aristos_status_t aristos_moe_forward(aristos_moe_t* L, const void* x, const void
         ARISTOS_TRY(ep_p2p_signal(L->p2p, EP_FLAG_IN, 0, st));
         PROF_MARK(2);
         ARISTOS_TRY(ep_p2p_wait(L->p2p, EP_FLAG_IN, 0, st));
+        stage.next("expert_ffn");
         if (L->fused_return) {
             // the down projection stores its valid output rows straight into the ranks they came from
             if (swiglu && !w3) { set_last_error("forward: SwiGLU needs w3"); return ARISTOS_ERR_INVALID_ARG; }
@@ -382,6 +491,7 @@ aristos_status_t aristos_moe_forward(aristos_moe_t* L, const void* x, const void
         ARISTOS_TRY(aristos_permute(x, L->slot_of, L->S, L->k, L->H, dt, L->xg, st));
     }
     if (!(L->fp8 && L->world > 1)) PROF_MARK(2);
+    if (!(L->fp8 && L->world > 1)) stage.next(L->world > 1 ? "exchange+expert_ffn" : "expert_ffn");
 
     if (L->fp8 && L->world > 1) {
         // done above
@@ -393,48 +503,68 @@ aristos_status_t aristos_moe_forward(aristos_moe_t* L, const void* x, const void
         ARISTOS_TRY(aristos_expert_ffn_bias(L->xg, L->count, L->E, L->cap, L->E, w1, w3, w2, L->b1, L->b3, L->b2, L->h, L->yr, L->H, L->I,
                                        L->cfg.hidden_act, dt, 0, L->cap, 0, L->dev_status, st));
     } else if (L->p2p && L->ep_direct) {
-        // the gather IS the dispatch all-to-all: every kept row is stored straight into its expert's rank (the row
-        // counts ride along in the same launch), the expert outputs come back the same way; only rows that exist
-        // travel. With one row window everything stays on the caller's stream; with more, the light gather / return
+        // the gather IS the dispatch all-to-all: every kept row is stored straight into its expert's rank, the expert
+        // outputs come back the same way; only rows that exist travel. With one row window everything stays on the caller's stream; with more, the light gather / return
         // kernels run on the communication stream and share the SMs with the persistent GEMM grid, window by window.
-        PeerPtrs rows_dst, y_dst, count_dst;
+        PeerPtrs rows_dst, y_dst;
         ep_p2p_peer_ptrs(L->p2p, EP_BUF_XR, rows_dst.p);
         ep_p2p_peer_ptrs(L->p2p, EP_BUF_YG, y_dst.p);
-        ep_p2p_peer_ptrs(L->p2p, EP_BUF_RCOUNT, count_dst.p);
         const size_t row_bytes = (size_t)L->H * L->elt;
         const int nwin = L->direct_windows;
         const int win_rows = ceil_div(ceil_div(L->cap, nwin), 256) * 256;
         cudaStream_t cs = nwin > 1 ? L->comm_stream : st;
         ep_p2p_begin(L->p2p);
+        *exchange_started = true;
         if (cs != st) {
             ARISTOS_CUDA_TRY(cudaEventRecord(L->ev_dispatched, st));
             ARISTOS_CUDA_TRY(cudaStreamWaitEvent(cs, L->ev_dispatched, 0));
         }
+        // the row counts go first, with a flag of their own: every rank can build its tile list as soon as its peers
+        // have routed their tokens, long before their rows have all arrived
+        ARISTOS_TRY(ep_p2p_send_counts(L->p2p, L->count, L->E, L->E_local, cs));
         for (int c = 0; c < nwin; ++c) {
             const int r0 = c * win_rows, r1 = std::min(L->cap, r0 + win_rows);
             if (r0 >= r1) break;
             ARISTOS_TRY(permute_rows_to_peers(x, L->slot_of, L->S, L->k, row_bytes, L->E_local, L->cap, L->rank, r0, r1,
-                                              rows_dst, cs, c == 0 ? L->count : nullptr, L->E, &count_dst));
+                                              rows_dst, cs));
             ARISTOS_TRY(ep_p2p_signal(L->p2p, EP_FLAG_IN, c, cs));
         }
+        ARISTOS_TRY(ep_p2p_wait(L->p2p, EP_FLAG_COUNT, 0, st));
+        const bool tc = dt == ARISTOS_DTYPE_BF16 || dt == ARISTOS_DTYPE_F16 || dt == ARISTOS_DTYPE_TF32;
         for (int c = 0; c < nwin; ++c) {
             const int r0 = c * win_rows, r1 = std::min(L->cap, r0 + win_rows);
             if (r0 >= r1) break;
-            ARISTOS_TRY(ep_p2p_wait(L->p2p, EP_FLAG_IN, c, st));
-            if (L->fused_return) {
-                // the epilogue of the down projection IS the return all-to-all: each output tile is stored into the
-                // buffer of the rank its rows came from while the tensor cores work on the next tile
-                if (L->cfg.hidden_act == ARISTOS_ACT_SWIGLU && !w3) { set_last_error("forward: SwiGLU needs w3"); return ARISTOS_ERR_INVALID_ARG; }
+            // either the stream waits for the rows of every rank, or the up projection waits per source rank while
+            // it already works on the rows that are there (its own first)
+            if (!(L->kernel_wait && tc)) ARISTOS_TRY(ep_p2p_wait(L->p2p, EP_FLAG_IN, c, st));
+            if (tc) {
+                FfnEpArgs ep;
+                ep.first_source = L->rank;
+                if (L->kernel_wait) {
+                    ep.src_flags = ep_p2p_flags(L->p2p, EP_FLAG_IN, c);
+                    ep.flag_epoch = ep_p2p_epoch(L->p2p);
+                    ep.flag_limit_ms = 2000;
+                }
+                if (L->fused_return) {
+                    // the epilogue of the down projection IS the return all-to-all: each output tile is stored into
+                    // the buffer of the rank its rows came from while the tensor cores work on the next tile
+                    ep.peer_y = y_dst.p;
+                    ep.peer_world = L->world;
+                    ep.peer_rank = L->rank;
+                }
                 const int fmt = dt == ARISTOS_DTYPE_BF16 ? 0 : (dt == ARISTOS_DTYPE_F16 ? 1 : 2);
                 ARISTOS_TRY(expert_ffn_tc_sm100(L->xr, L->rcount, L->groups, L->cap, L->E_local, w1, w3, w2, L->b1, L->b3,
                                                 L->b2, L->h, L->yr, L->H, L->I, L->cfg.hidden_act, fmt, r0, r1, 0,
-                                                L->dev_status, st, y_dst.p, L->world, L->rank));
-                ARISTOS_TRY(ep_p2p_signal(L->p2p, EP_FLAG_RET, c, st));
-                continue;
+                                                L->dev_status, st, &ep));
+                if (L->fused_return) {
+                    ARISTOS_TRY(ep_p2p_signal(L->p2p, EP_FLAG_RET, c, st));
+                    continue;
+                }
+            } else {
+                ARISTOS_TRY(aristos_expert_ffn_bias(L->xr, L->rcount, L->groups, L->cap, L->E_local, w1, w3, w2, L->b1,
+                                                    L->b3, L->b2, L->h, L->yr, L->H, L->I, L->cfg.hidden_act, dt, r0, r1,
+                                                    0, L->dev_status, st));
             }
-            ARISTOS_TRY(aristos_expert_ffn_bias(L->xr, L->rcount, L->groups, L->cap, L->E_local, w1, w3, w2, L->b1,
-                                                L->b3, L->b2, L->h, L->yr, L->H, L->I, L->cfg.hidden_act, dt, r0, r1, 0,
-                                                L->dev_status, st));
             if (cs != st) {
                 ARISTOS_CUDA_TRY(cudaEventRecord(L->ev_out[c], st));
                 ARISTOS_CUDA_TRY(cudaStreamWaitEvent(cs, L->ev_out[c], 0));
@@ -450,6 +580,7 @@ aristos_status_t aristos_moe_forward(aristos_moe_t* L, const void* x, const void
         const size_t row_bytes = (size_t)L->H * L->elt;
         const size_t block_stride = (size_t)L->cap * row_bytes;
         ep_p2p_begin(L->p2p);
+        *exchange_started = true;
         ARISTOS_CUDA_TRY(cudaEventRecord(L->ev_dispatched, st));
         ARISTOS_CUDA_TRY(cudaStreamWaitEvent(L->comm_stream, L->ev_dispatched, 0));
         ARISTOS_TRY(ep_p2p_push(L->p2p, EP_FLAG_COUNT, L->count, 1, (size_t)L->E_local * 4, 0, (size_t)L->E_local * 4,
@@ -477,6 +608,7 @@ aristos_status_t aristos_moe_forward(aristos_moe_t* L, const void* x, const void
     } else {
         const size_t row_bytes = (size_t)L->H * L->elt;
         const size_t block_stride = (size_t)L->cap * row_bytes;
+        *exchange_started = true;
         ARISTOS_CUDA_TRY(cudaEventRecord(L->ev_dispatched, st));
         ARISTOS_CUDA_TRY(cudaStreamWaitEvent(L->comm_stream, L->ev_dispatched, 0));
         // per-(source, local expert) row counts
@@ -503,6 +635,7 @@ aristos_status_t aristos_moe_forward(aristos_moe_t* L, const void* x, const void
         ARISTOS_CUDA_TRY(cudaStreamWaitEvent(st, L->ev_returned, 0));
     }
     PROF_MARK(3);
+    stage.next("combine");
     ARISTOS_TRY(aristos_combine(L->yg, L->slot_of, L->topk_w, L->S, L->k, L->H, dt, out, st));
     PROF_MARK(4);
 #undef PROF_MARK
@@ -529,8 +662,8 @@ aristos_status_t aristos_moe_submit_host(aristos_moe_t* L, const void* x_host, c
     aristos_moe::HostSlot& sl = L->slots[L->slot_next];
     L->slot_next ^= 1;
     if (sl.busy) {                       // the call that used this slot two submissions ago must have drained
-        ARISTOS_CUDA_TRY(cudaEventSynchronize(sl.d2h_done));
         sl.busy = false;
+        ARISTOS_TRY(wait_event_bounded(L, sl.d2h_done));
     }
     const size_t bytes = (size_t)L->S * L->H * L->elt;
     ARISTOS_CUDA_TRY(cudaMemcpyAsync(sl.x_dev, x_host, bytes, cudaMemcpyHostToDevice, L->h2d_stream));
@@ -547,12 +680,14 @@ aristos_status_t aristos_moe_submit_host(aristos_moe_t* L, const void* x_host, c
 
 aristos_status_t aristos_moe_wait_host(aristos_moe_t* L) {
     if (!L) return ARISTOS_ERR_INVALID_ARG;
+    aristos_status_t first = ARISTOS_OK;
     for (auto& sl : L->slots)
         if (sl.busy) {
-            ARISTOS_CUDA_TRY(cudaEventSynchronize(sl.d2h_done));
             sl.busy = false;
+            const aristos_status_t s = wait_event_bounded(L, sl.d2h_done);
+            if (first == ARISTOS_OK) first = s;
         }
-    return ARISTOS_OK;
+    return first;
 }
 
 aristos_status_t aristos_moe_forward_host(aristos_moe_t* L, const void* x_host, const void* w_gate,
@@ -582,6 +717,7 @@ aristos_status_t aristos_moe_routing_to_host(const aristos_moe_t* L, int32_t* to
                                              int32_t* token_of_slot_host) {
     if (!L) return ARISTOS_ERR_INVALID_ARG;
     if (!L->ws) { set_last_error("routing: no forward has run yet"); return ARISTOS_ERR_INVALID_ARG; }
+    if (L->world > 1 && L->ev_last_valid) ARISTOS_TRY(wait_event_bounded(const_cast<aristos_moe_t*>(L), L->ev_last));
     ARISTOS_CUDA_TRY(cudaDeviceSynchronize());
     const size_t sk = (size_t)L->S * L->k;
     if (topk_idx_host) ARISTOS_CUDA_TRY(cudaMemcpy(topk_idx_host, L->topk_idx, sk * 4, cudaMemcpyDeviceToHost));
@@ -595,6 +731,7 @@ aristos_status_t aristos_moe_routing_to_host(const aristos_moe_t* L, int32_t* to
 
 aristos_status_t aristos_moe_status(aristos_moe_t* L) {
     if (!L) return ARISTOS_ERR_INVALID_ARG;
+    if (L->world > 1 && L->ev_last_valid) ARISTOS_TRY(wait_event_bounded(L, L->ev_last));
     ARISTOS_CUDA_TRY(cudaDeviceSynchronize());
     if (!L->ws) return ARISTOS_OK;
     int32_t bits = 0;
@@ -638,6 +775,12 @@ aristos_status_t aristos_moe_stage_ms(aristos_moe_t* L, float out_ms[5]) {
     return ARISTOS_OK;
 }
 
+aristos_status_t aristos_moe_set_timeout_ms(aristos_moe_t* L, int timeout_ms) {
+    if (!L || timeout_ms < 1) { set_last_error("set_timeout_ms: the limit must be at least 1 ms"); return ARISTOS_ERR_INVALID_ARG; }
+    L->timeout_ms = timeout_ms;
+    return ARISTOS_OK;
+}
+
 const char* aristos_moe_ep_transport(const aristos_moe_t* L) {
     if (!L || L->world == 1) return "none";
     return L->p2p ? "p2p" : "nccl";
@@ -647,7 +790,15 @@ int64_t aristos_moe_launch_count(const aristos_moe_t* L) { return L ? L->launche
 
 aristos_status_t aristos_moe_destroy(aristos_moe_t* L) {
     if (!L) return ARISTOS_OK;
-    cudaDeviceSynchronize();
+    // a forward still waiting for a peer that will never come must not keep destroy from returning
+    if (L->world > 1 && L->ev_last_valid && !L->failed) {
+        const int keep = L->timeout_ms;
+        L->timeout_ms = std::min(keep, 5000);
+        wait_event_bounded(L, L->ev_last);
+        L->timeout_ms = keep;
+    }
+    if (!(L->failed && !L->p2p)) cudaDeviceSynchronize();   // a stuck NCCL kernel cannot be waited for
+    if (L->ev_last) cudaEventDestroy(L->ev_last);
     for (cudaEvent_t e : L->ev_in) if (e) cudaEventDestroy(e);
     for (cudaEvent_t e : L->ev_out) if (e) cudaEventDestroy(e);
     for (cudaEvent_t e : L->ev_prof) if (e) cudaEventDestroy(e);

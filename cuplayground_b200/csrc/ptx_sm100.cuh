@@ -70,6 +70,32 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
     }
 }
 
+// Wait until a 32-bit flag word in global memory, stored by another GPU (or an earlier kernel) with system scope, has
+// reached `epoch` (cyclic comparison, like the stream memory operation CU_STREAM_WAIT_VALUE_GEQ). The acquire load
+// orders the later reads of the data that the flag publishes; the proxy fence extends that to TMA loads. Bounded like
+// mbar_wait_bounded: on expiry the CTA's abort flag is raised, DEV_FAULT_TIMEOUT reported and false returned.
+__device__ __forceinline__ bool flag_wait_bounded(const uint32_t* flag, uint32_t epoch, volatile int* abort_flag,
+                                                  int32_t* dev_status, uint64_t limit_ns = WAIT_LIMIT_NS) {
+    uint64_t t0 = 0;
+    for (uint32_t it = 0;; ++it) {
+        uint32_t v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+        if (static_cast<int32_t>(v - epoch) >= 0) break;
+        if (it == 0) t0 = globaltimer_ns();
+        if ((it & 15u) == 15u) {
+            if (*abort_flag) return false;
+            if (globaltimer_ns() - t0 > limit_ns) {
+                *abort_flag = 1;
+                if (dev_status) atomicOr(dev_status, DEV_FAULT_TIMEOUT);
+                return false;
+            }
+        }
+        __nanosleep(200);
+    }
+    asm volatile("fence.proxy.async;" ::: "memory");
+    return true;
+}
+
 // ---- TMA ----------------------------------------------------------------------------------------------------------
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* tm) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tm)) : "memory");

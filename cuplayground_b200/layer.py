@@ -214,6 +214,12 @@ def combine(y, slot_of, topk_w):
     return out
 
 
+def ffn_set_tile_mode(mode: int) -> None:
+    """aristos_ffn_set_tile_mode: 0 automatic, 1 single-CTA tiles, 2 CTA pairs + single-CTA tail, 3 CTA pairs padded,
+    -1 re-read ARISTOS_FFN_TILES."""
+    _lib.check(_lib.load().aristos_ffn_set_tile_mode(int(mode)))
+
+
 # ---- layer ----------------------------------------------------------------------------------------------------------
 class MoELayer:
     """One MoE layer on the current CUDA device (aristos_moe_create ... aristos_moe_destroy)."""
@@ -301,6 +307,10 @@ class MoELayer:
 
     def status(self) -> None:
         _lib.check(self._lib.aristos_moe_status(self._h))
+
+    def set_timeout_ms(self, timeout_ms: int) -> None:
+        """Wall-clock limit of the waits for an expert-parallel forward (status, wait_host, routing, close)."""
+        _lib.check(self._lib.aristos_moe_set_timeout_ms(self._h, int(timeout_ms)))
 
     @property
     def ep_transport(self) -> str:

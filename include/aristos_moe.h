@@ -173,8 +173,18 @@ ARISTOS_API aristos_status_t aristos_moe_routing_to_host(const aristos_moe_t* la
                                                          float* topk_w_host, int32_t* count_host,
                                                          int32_t* slot_of_host, int32_t* token_of_slot_host);
 /* Synchronises the layer's streams and reports device-side faults of the forwards since the last call
- * (ARISTOS_ERR_DEVICE_TIMEOUT / ARISTOS_ERR_DEVICE_BOUNDS / ARISTOS_ERR_GATE_SCREEN), then clears them. */
+ * (ARISTOS_ERR_DEVICE_TIMEOUT / ARISTOS_ERR_DEVICE_BOUNDS / ARISTOS_ERR_GATE_SCREEN), then clears them.
+ * Expert-parallel layers wait with a wall-clock limit (aristos_moe_set_timeout_ms): the reference's exchange spins
+ * without bound on its peers' flags (auditorium/overlap.cuh:102-105, :133-136), so one stopped rank hangs all. Here,
+ * when the last forward has not completed within the limit (a peer never sent its rows or its results), the rank
+ * stores the current epoch into its own arrival flags from the host - every stream wait and kernel wait of that
+ * forward then completes on whatever data is there -, marks the handle failed and returns
+ * ARISTOS_ERR_DEVICE_TIMEOUT. A failed handle refuses further forwards (its epochs no longer match its peers');
+ * aristos_moe_destroy still returns. aristos_moe_wait_host, aristos_moe_routing_to_host and aristos_moe_destroy
+ * wait the same way. */
 ARISTOS_API aristos_status_t aristos_moe_status(aristos_moe_t* layer);
+/* Wall-clock limit of those waits in milliseconds (default 30000, or ARISTOS_EP_TIMEOUT_MS at create). */
+ARISTOS_API aristos_status_t aristos_moe_set_timeout_ms(aristos_moe_t* layer, int timeout_ms);
 /* Stage stopwatch (the reference times its kernels with %globaltimer reads and cudaEvents, mma.cuh:56,163,
  * auditorium/overlap.cuh:207-224). With profiling on, every forward records CUDA events on its stream at the stage
  * boundaries; aristos_moe_stage_ms waits for the last forward and returns milliseconds, averaged over the forwards
@@ -182,9 +192,13 @@ ARISTOS_API aristos_status_t aristos_moe_status(aristos_moe_t* layer);
  * {gate, dispatch + gather, expert FFN (with the exchanges when world > 1), combine, whole forward}. */
 ARISTOS_API aristos_status_t aristos_moe_set_profiling(aristos_moe_t* layer, int enable);
 ARISTOS_API aristos_status_t aristos_moe_stage_ms(aristos_moe_t* layer, float out_ms[5]);
-/* How the rows of an expert-parallel layer travel: "p2p" (copy-engine pushes into the peers' CUDA-IPC mapped
- * buffers over NVLink, arrival flags, stream memory waits - the default), "nccl" (grouped ncclSend/ncclRecv; chosen
- * with ARISTOS_EP_TRANSPORT=nccl or when peer memory cannot be mapped) or "none" (world == 1). */
+/* How the rows of an expert-parallel layer travel: "p2p" (the default: kernels store through the peers' CUDA-IPC
+ * mapped exchange buffers over NVLink - the gather kernel writes every kept token row into the rank that owns its
+ * expert, the down projection's epilogue writes every output tile into the rank the rows came from -, arrival is
+ * published by epoch flags; the up projection waits per source rank inside the kernel, the combine behind a stream
+ * memory wait. ARISTOS_EP_MODE=windows selects copy-engine pushes of padded row windows instead), "nccl" (grouped
+ * ncclSend/ncclRecv; chosen with ARISTOS_EP_TRANSPORT=nccl, or by every rank together when any rank cannot allocate
+ * or map the peer memory) or "none" (world == 1). */
 ARISTOS_API const char* aristos_moe_ep_transport(const aristos_moe_t* layer);
 /* Kernels launched by this library for `layer` since create (the benchmark's launch count). */
 ARISTOS_API int64_t aristos_moe_launch_count(const aristos_moe_t* layer);
@@ -288,6 +302,23 @@ ARISTOS_API aristos_status_t aristos_combine(const void* y, const int32_t* slot_
  * barrier that nothing signals; the wait gives up after limit_ms, the kernel returns normally and the call reports
  * ARISTOS_ERR_DEVICE_TIMEOUT (that IS the expected result) with the time waited. The CUDA context stays usable. */
 ARISTOS_API aristos_status_t aristos_selftest_bounded_wait(int limit_ms, int* waited_ms, void* stream);
+/* The same for the wait on an arrival flag in global memory - what the up projection does before it loads the rows of
+ * a source rank in the expert-parallel layer (the bounded successor of nvshmem_signal_wait_until,
+ * auditorium/overlap.cuh:102-105): a flag word that nothing raises; ARISTOS_ERR_DEVICE_TIMEOUT is the expected
+ * result. */
+ARISTOS_API aristos_status_t aristos_selftest_bounded_flag_wait(int limit_ms, int* waited_ms, void* stream);
+/* Tile shape of the tensor-core expert GEMM for later calls of this process (replaces the compile-time BLOCK_M /
+ * BLOCK_N of processor/tiling.cuh:19-26): 0 automatic (CTA pairs, tcgen05 cta_group::2 with 256 x 256 tiles, where a
+ * row window holds >= 1024 rows, each group's last < 256 rows on single-CTA 128 x 256 tiles), 1 single-CTA tiles only,
+ * 2 pairs + single-CTA tail for every window, 3 pairs only (groups padded to 256 rows), -1 re-read ARISTOS_FFN_TILES
+ * (single | pair | pair-padded). Results are bit-identical across the modes. */
+ARISTOS_API aristos_status_t aristos_ffn_set_tile_mode(int mode);
+/* Order in which the GEMM walks the row_tiles x col_tiles tiles of one row group (`band` row tiles per band; 0 = row
+ * tile fastest): position `local` -> (row tile, column tile). Host-only, for tests. Returns 0, or -1 on bad input. */
+ARISTOS_API int aristos_ffn_tile_coord(int local, int row_tiles, int col_tiles, int band, int* row_tile, int* col_tile);
+/* Whether peer memory is the transport, given every rank's "works here" flag (all-gathered at create): only if it
+ * works on all ranks; otherwise all ranks fall back together. Host-only, for tests of the agreement. */
+ARISTOS_API int aristos_ep_transport_agreed(const int* ok_flags, int world);
 /* The order in which the expert GEMMs walk `groups` row groups of `experts` experts (group g uses expert
  * g % experts): position -> group, a permutation that keeps the groups of one expert adjacent. Host-only, for tests. */
 ARISTOS_API int aristos_ffn_group_order(int position, int groups, int experts);

@@ -441,3 +441,13 @@ ORC_API int orc_num_threads(void) {
     return 1;
 #endif
 }
+
+/* Number of OpenMP threads for the later calls of this process. A launcher may have exported OMP_NUM_THREADS=1
+ * (torch.distributed.run does); the benchmark's CPU arm sets the count from the cores it may use instead. */
+ORC_API void orc_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n >= 1) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}

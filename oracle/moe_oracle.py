@@ -183,6 +183,44 @@ def num_threads() -> int:
     return int(lib().orc_num_threads())
 
 
+def set_num_threads(n: int) -> None:
+    lib().orc_set_num_threads(C.c_int(int(n)))
+
+
+def use_all_cores() -> int:
+    """Run the later calls on every core this process may use (sched_getaffinity), whatever OMP_NUM_THREADS says:
+    launchers such as torch.distributed.run export OMP_NUM_THREADS=1. Returns the thread count."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    set_num_threads(n)
+    return num_threads()
+
+
+def gate_logits_f64(x, wg, bias=None) -> np.ndarray:
+    """Order-independent recomputation of the gate logits in float64 (products of 16-bit inputs are exact in
+    float64 and the sum of H of them is accurate to about 1e-13 relative): the yardstick for the fixed-order fp32
+    contract of gate_logits, not a contract itself."""
+    l = np.asarray(x, dtype=np.float64) @ np.asarray(wg, dtype=np.float64).T
+    if bias is not None:
+        l = l + np.asarray(bias, dtype=np.float64)[None, :]
+    return l
+
+
+def load_balance_stats(topk_idx, topk_w, slot_of, E: int):
+    """Per-expert routing statistics of one forward, the ingredients of the usual auxiliary load-balance loss:
+    frac[e] = share of the S*k assignments routed to expert e (before capacity drops), prob[e] = sum of the gate
+    weights assigned to e divided by S, aux = E * sum(frac * prob), dropped = share of assignments dropped."""
+    idx = np.asarray(topk_idx).reshape(-1)
+    w = np.asarray(topk_w, dtype=np.float64).reshape(-1)
+    S = np.asarray(topk_idx).shape[0]
+    frac = np.bincount(idx, minlength=E).astype(np.float64) / idx.size
+    prob = np.bincount(idx, weights=w, minlength=E) / S
+    dropped = float((np.asarray(slot_of) < 0).sum()) / idx.size
+    return frac, prob, float(E * (frac * prob).sum()), dropped
+
+
 # ---- fp8 e4m3 (1 sign, 4 exponent bits with bias 7, 3 mantissa bits; no infinities, 0x7f / 0xff are NaN) -----------
 def _e4m3_table() -> np.ndarray:
     t = np.zeros(256, dtype=np.float32)

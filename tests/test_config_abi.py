@@ -158,3 +158,64 @@ def test_ffn_group_order_is_a_permutation_that_keeps_experts_adjacent(cp):
                 assert order == list(range(groups))
     assert [lib.aristos_ffn_group_order(v, 10, 4) for v in range(10)] == list(range(10))
     assert lib.aristos_ffn_group_order(10, 10, 4) == -1 and lib.aristos_ffn_group_order(-1, 8, 4) == -1
+
+
+@pytest.mark.parametrize("mt,nt,band", [(33, 16, 16), (17, 112, 8), (5, 3, 0), (4, 7, 9), (1, 1, 4), (40, 2, 16)])
+def test_ffn_tile_order_is_a_bijection(cp, mt, nt, band):
+    """The banded tile order of the expert GEMM visits every (row tile, column tile) of a group exactly once, and
+    inside a band walks the row tiles fastest."""
+    import ctypes as C
+    lib = cp._lib.load()
+    seen = []
+    for local in range(mt * nt):
+        m, n = C.c_int(-1), C.c_int(-1)
+        assert lib.aristos_ffn_tile_coord(local, mt, nt, band, C.byref(m), C.byref(n)) == 0
+        seen.append((m.value, n.value))
+    assert sorted(seen) == [(m, n) for m in range(mt) for n in range(nt)]
+    if 0 < band < mt:
+        assert seen[:band] == [(m, 0) for m in range(band)]          # row tile fastest inside the first band
+        assert seen[band][1] == 1 or nt == 1
+        first_of_band1 = seen.index((band, 0))
+        assert first_of_band1 == band * nt                            # a band finishes all its column tiles first
+    else:
+        assert seen[:mt] == [(m, 0) for m in range(mt)]
+    m, n = C.c_int(), C.c_int()
+    assert lib.aristos_ffn_tile_coord(mt * nt, mt, nt, band, C.byref(m), C.byref(n)) == -1
+
+
+def test_source_order_starts_with_the_own_rank():
+    """Host check of the walking order of the row groups in the expert-parallel layer: expert-major, and inside an
+    expert the sources in ring order from the rank itself (mirrors ordered_group of csrc/common.cuh)."""
+    def ordered(v, groups, experts, first):
+        sources = groups // experts
+        e, i = divmod(v, sources)
+        return ((i + first) % sources) * experts + e
+    groups, experts = 8, 2
+    for first in range(4):
+        order = [ordered(v, groups, experts, first) for v in range(groups)]
+        assert sorted(order) == list(range(groups))
+        assert order[0] == first * experts and order[4] == first * experts + 1
+
+
+def test_transport_agreement(cp):
+    import ctypes as C
+    lib = cp._lib.load()
+    arr = lambda v: (C.c_int * len(v))(*v)
+    assert lib.aristos_ep_transport_agreed(arr([1, 1, 1, 1]), 4) == 1
+    assert lib.aristos_ep_transport_agreed(arr([1, 0, 1, 1]), 4) == 0
+    assert lib.aristos_ep_transport_agreed(arr([0]), 1) == 0
+
+
+def test_numa_binding_plan(tmp_path):
+    """hostmem: the CPU set a rank binds to comes from the GPU's NUMA node as sysfs reports it (here: a fake tree)."""
+    from cuplayground_b200 import hostmem
+    node = tmp_path / "devices/system/node/node1"
+    node.mkdir(parents=True)
+    (node / "cpulist").write_text("8-15,24-27\n")
+    cpus = hostmem.node_cpus(1, sysfs=str(tmp_path))
+    assert cpus == set(range(8, 16)) | set(range(24, 28))
+    assert hostmem.plan_binding(set(range(0, 32)), 1, cpus) == cpus
+    assert hostmem.plan_binding(set(range(8, 16)), 1, cpus) is None          # already local
+    assert hostmem.plan_binding(set(range(0, 8)), 1, cpus) is None           # none of the node's CPUs allowed
+    assert hostmem.plan_binding(set(range(0, 32)), None, set()) is None      # unknown node
+    assert hostmem.node_cpus(7, sysfs=str(tmp_path)) == set()

@@ -160,3 +160,25 @@ def test_config4_rank_shape(oracle):
     cfg = cp.baseline_config(4)
     cfg.num_experts = 32
     _fp8_layer_case(oracle, cfg, seed=3, n_sample=64)
+
+
+def test_config4_full_layer_on_one_gpu(oracle):
+    """The whole DeepSeek-V3-shaped layer on one GPU: all 256 experts, 4096 tokens, H 7168, top-8 sigmoid gate
+    normalised over the selected experts, no drops, FP8 operands. With E = 256 the layer's gate is the tensor-core
+    screen + exact candidates, so this is the screened gate checked through the layer at the shape with the longest
+    accumulation chains: routing bit-exact on every token, 8 sampled output rows (up to 64 experts' weights
+    regenerated and de-quantised on the host) against the oracle."""
+    torch, cp, layer = _mods()
+    import parity
+    cfg = cp.baseline_config(4, world=1)
+    assert cfg.num_experts == 256 and cfg.S == 4096
+    x, wg, w1, w3, w2, scales = layer.synthetic_tensors(cfg, 0, 1)
+    L = layer.MoELayer(cfg)
+    out = L.forward(x, wg, w1, w3, w2, scales=scales)
+    L.status()
+    out2 = L.forward(x, wg, w1, w3, w2, scales=scales)
+    L.status()
+    assert torch.equal(out, out2)
+    res = parity.check_rank(cfg, L, x, wg, out, n_rows=8, seed=4)
+    assert res["ok"], res
+    L.close()

@@ -159,14 +159,16 @@ def test_config3_full_size_mixtral_shaped(oracle):
     _full_size(3, 2, oracle, n_sample=64)
 
 
-def test_config3_with_cta_pair_tiles():
-    """The CTA-pair (cta_group::2, 256 x 256) variant of the expert GEMM is an option since the single-CTA tiles became
-    the default: the full-size Mixtral-shaped parity test once more in a process that selects it."""
+@pytest.mark.parametrize("tiles", ["single", "pair-padded"])
+def test_config3_with_other_tile_shapes(tiles):
+    """CTA pairs (cta_group::2, 256 x 256 tiles) with a single-CTA tail are the default where a row group is large;
+    the full-size Mixtral-shaped parity test once more in processes that select single-CTA tiles only and padded
+    pairs only."""
     import os
     import subprocess
     import sys
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    env = dict(os.environ, ARISTOS_FFN_TILES="pair")
+    env = dict(os.environ, ARISTOS_FFN_TILES=tiles)
     r = subprocess.run([sys.executable, "-m", "pytest", os.path.join(root, "tests", "test_gpu_layer.py"), "-q", "-x",
                         "-k", "test_config3_full_size_mixtral_shaped", "-m", "gpu"], env=env, cwd=root,
                        capture_output=True, text=True, timeout=900)

@@ -342,3 +342,56 @@ def test_expert_ffn_tf32_parity(cp, oracle, act, E, rows, H, I, counts):
         if n:
             mx, mean = rel_errors(got[e, :n], ref[e, :n])
             assert mx < 5e-3 and mean < 5e-3, (e, mx, mean)
+
+
+@pytest.mark.parametrize("act", [2, 1])
+def test_expert_ffn_tile_shapes_agree(cp, oracle, act):
+    """The expert GEMM with single-CTA tiles, CTA pairs + single-CTA tail (the pair kernel computes whole 256-row
+    tiles, the single-CTA kernel every group's last < 256 rows) and padded CTA pairs: ragged row counts around the
+    128- and 256-row boundaries; every shape must match the oracle and leave rows past the last valid tile alone."""
+    torch = _torch()
+    import cuplayground_b200.layer as layer
+    experts, rows, H, I = 4, 1152, 128, 256
+    counts = [0, 1, 255, 256, 257, 384, 1000, 1152]
+    groups = len(counts)
+    x, _, w1, w3, w2 = make_inputs(groups * rows, H, I, experts, seed=31, swiglu=(act == 2), w_std=0.05)
+    xg = x.reshape(groups, rows, H)
+    count = np.array(counts, np.int32)
+    dt = torch.bfloat16
+    dev = [to_dev(a, dt) for a in (xg, w1, w3, w2)]
+    cnt = torch.from_numpy(count).cuda()
+    rep = lambda w: None if w is None else np.concatenate([w] * (groups // experts))     # expert of group g: g % 4
+    ref = oracle.expert_ffn(xg, count, rep(w1), rep(w3), rep(w2), act, round_h=1)
+    outs = {}
+    try:
+        for mode in (1, 2, 3):
+            layer.ffn_set_tile_mode(mode)
+            y = cp.expert_ffn(dev[0], cnt, dev[1], dev[2], dev[3], act, experts=experts)
+            torch.cuda.synchronize()
+            outs[mode] = y.float().cpu().numpy()
+    finally:
+        layer.ffn_set_tile_mode(-1)
+    for mode, got in outs.items():
+        pad = 256 if mode == 3 else 128
+        for g in range(groups):
+            n = counts[g]
+            assert (got[g, min(rows, -(-n // pad) * pad):] == 0).all(), (mode, g)
+            if n:
+                mx, mean = rel_errors(got[g, :n], ref[g, :n])
+                assert mx < TOL_BF16_MAX and mean < TOL_BF16_MEAN, (mode, g, mx, mean)
+    for g in range(groups):
+        n = counts[g]
+        assert np.array_equal(outs[1][g, :n], outs[2][g, :n]) and np.array_equal(outs[1][g, :n], outs[3][g, :n]), \
+            f"group {g}: the tile shapes must give the same bits"
+
+
+def test_bounded_flag_wait_gives_up(cp):
+    """The wait of the up projection for a source rank's arrival flag, on a flag that nothing raises: it expires after
+    its limit, the kernel returns, the status says so and the context still works."""
+    import ctypes as C
+    torch = _torch()
+    lib = cp._lib.load()
+    waited = C.c_int(0)
+    assert lib.aristos_selftest_bounded_flag_wait(150, C.byref(waited), None) == 8     # ARISTOS_ERR_DEVICE_TIMEOUT
+    assert 150 <= waited.value < 1500, waited.value
+    assert int(torch.ones(4, device="cuda").sum().item()) == 4
