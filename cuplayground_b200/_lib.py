@@ -14,7 +14,7 @@ OK = 0
 STATUS_NAMES = {0: "ARISTOS_OK", 1: "ARISTOS_ERR_INVALID_ARG", 2: "ARISTOS_ERR_CONFIG", 3: "ARISTOS_ERR_IO",
                 4: "ARISTOS_ERR_CUDA", 5: "ARISTOS_ERR_NCCL", 6: "ARISTOS_ERR_UNSUPPORTED",
                 7: "ARISTOS_ERR_WORKSPACE", 8: "ARISTOS_ERR_DEVICE_TIMEOUT", 9: "ARISTOS_ERR_DEVICE_BOUNDS",
-                10: "ARISTOS_ERR_NOMEM", 11: "ARISTOS_ERR_GATE_SCREEN"}
+                10: "ARISTOS_ERR_NOMEM", 11: "ARISTOS_ERR_GATE_SCREEN", 12: "ARISTOS_ERR_NONFINITE"}
 
 DTYPE_F32, DTYPE_TF32, DTYPE_BF16, DTYPE_F16, DTYPE_FP8_E4M3 = 0, 1, 2, 3, 4
 ACT_RELU, ACT_GELU, ACT_SWIGLU, ACT_IDENTITY = 0, 1, 2, 3
@@ -36,6 +36,12 @@ class AristosRoutingStruct(C.Structure):
     _fields_ = [("topk_idx", C.c_void_p), ("topk_w", C.c_void_p), ("count", C.c_void_p), ("slot_of", C.c_void_p),
                 ("token_of_slot", C.c_void_p), ("tokens", C.c_int), ("top_k", C.c_int), ("num_experts", C.c_int),
                 ("capacity", C.c_int)]
+
+
+class AristosTrainingStateStruct(C.Structure):
+    """Mirror of aristos_training_state_t."""
+    _fields_ = [("topk_idx", C.c_void_p), ("topk_w", C.c_void_p), ("slot_of", C.c_void_p),
+                ("load_balance", C.c_void_p), ("tokens", C.c_int), ("top_k", C.c_int), ("num_experts", C.c_int)]
 
 
 class AristosError(RuntimeError):
@@ -95,7 +101,16 @@ PROTOTYPES = {
     "aristos_ffn_set_tile_mode": (_st, [_i]),
     "aristos_ffn_tile_coord": (_i, [_i, _i, _i, _i, C.POINTER(_i), C.POINTER(_i)]),
     "aristos_ep_transport_agreed": (_i, [C.POINTER(_i), _i]),
+    "aristos_ep_flag_words": (_i, []),
+    "aristos_ep_flag_word_index": (_i, [_i, _i, _i]),
+    "aristos_ep_flags_pending": (C.c_uint32, [_vp, C.c_uint32, _i, _i, _i]),
+    "aristos_ep_flags_release": (None, [_vp, C.c_uint32]),
     "aristos_moe_set_timeout_ms": (_st, [_vp, _i]),
+    "aristos_moe_training_bytes": (_sz, [_vp]),
+    "aristos_moe_set_training_buffer": (_st, [_vp, _vp, _sz]),
+    "aristos_moe_training_state": (_st, [_vp, C.POINTER(AristosTrainingStateStruct)]),
+    "aristos_load_balance_stats_bytes": (_sz, [_i]),
+    "aristos_load_balance_stats": (_st, [_vp, _vp, _vp, _i, _i, _i, _vp, _vp]),
     "aristos_ffn_group_order": (_i, [_i, _i, _i]),
     "aristos_fill_normal": (_st, [_vp, C.c_int64, C.c_float, C.c_float, C.c_uint64, C.c_uint32, _i, _vp]),
 }

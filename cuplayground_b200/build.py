@@ -18,7 +18,7 @@ CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "_obj")
 LIB = os.path.join(HERE, "libaristos_moe.so")
 
-SOURCES = ["runtime.cpp", "config.cpp", "gate.cu", "gate_screen_sm100.cu", "dispatch.cu", "combine.cu", "ffn_sm100.cu", "ffn_simt.cu",
+SOURCES = ["runtime.cpp", "config.cpp", "gate.cu", "gate_screen_sm100.cu", "dispatch.cu", "train_stats.cu", "combine.cu", "ffn_sm100.cu", "ffn_simt.cu",
            "ffn_fp8_sm100.cu", "ffn_api.cu", "fill.cu", "ep_nccl.cpp", "ep_p2p.cu", "ep_kernels.cu", "moe_layer.cpp"]
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

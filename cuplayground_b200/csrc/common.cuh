@@ -11,7 +11,7 @@
 namespace aristos {
 
 // Bits OR-ed into the device status word by kernels; mapped to aristos_status_t by the host.
-enum : int32_t { DEV_FAULT_TIMEOUT = 1, DEV_FAULT_BOUNDS = 2, DEV_FAULT_SCREEN = 4 };
+enum : int32_t { DEV_FAULT_TIMEOUT = 1, DEV_FAULT_BOUNDS = 2, DEV_FAULT_SCREEN = 4, DEV_FAULT_NONFINITE = 8 };
 
 void set_last_error(const char* fmt, ...);
 aristos_status_t cuda_fail(cudaError_t e, const char* what);

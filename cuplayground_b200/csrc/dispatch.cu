@@ -11,6 +11,7 @@
 //   3. assign: every warp owns a contiguous sub-chunk; per-warp histograms + an in-CTA prefix give each warp its
 //              base, __match_any_sync groups lanes that picked the same expert and the lane's rank inside its
 //              group is its offset, so positions follow token order exactly.
+#include <atomic>
 #include "common.cuh"
 
 namespace aristos {
@@ -209,17 +210,21 @@ extern "C" aristos_status_t aristos_dispatch_static(const int32_t* topk_idx, int
     }
     // The array's name is only a host-side handle: the kernels need its device address, looked up once per device
     // with that device current.
+    // Two host threads that make the first call on one device at the same time both look the address up and store the
+    // same value; the atomic makes that store and the later loads well defined.
     constexpr int MAX_DEVICES = 64;
-    static int32_t* scratch_of_device[MAX_DEVICES] = {nullptr};
+    static std::atomic<int32_t*> scratch_of_device[MAX_DEVICES];
     int dev = 0;
     ARISTOS_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= MAX_DEVICES) { set_last_error("dispatch_static: device index %d not supported", dev); return ARISTOS_ERR_UNSUPPORTED; }
-    if (!scratch_of_device[dev]) {
+    int32_t* scratch = scratch_of_device[dev].load(std::memory_order_acquire);
+    if (!scratch) {
         void* p = nullptr;
         ARISTOS_CUDA_TRY(cudaGetSymbolAddress(&p, g_dispatch_static_scratch));
-        scratch_of_device[dev] = static_cast<int32_t*>(p);
+        scratch = static_cast<int32_t*>(p);
+        scratch_of_device[dev].store(scratch, std::memory_order_release);
     }
-    return dispatch_impl(topk_idx, S, k, E, cap, count, slot_of, token_of_slot, scratch_of_device[dev],
+    return dispatch_impl(topk_idx, S, k, E, cap, count, slot_of, token_of_slot, scratch,
                          sizeof(int32_t) * STATIC_MAX_CHUNKS * STATIC_MAX_EXPERTS, nullptr,
                          static_cast<cudaStream_t>(stream));
 }

@@ -82,8 +82,9 @@ struct EpP2P {
     uint32_t epoch = 0;
 };
 
-static size_t flag_index(const EpP2P* p, int kind, int window, int src) {
-    return ((size_t)kind * EP_MAX_WINDOWS + window) * MAX_RANKS + src;
+int ep_flag_word_index(int kind, int window, int src);
+static size_t flag_index(const EpP2P*, int kind, int window, int src) {
+    return (size_t)ep_flag_word_index(kind, window, src);
 }
 
 bool ep_transport_agreed(const int* ok_flags, int world) {
@@ -275,13 +276,41 @@ aristos_status_t ep_p2p_send_counts(EpP2P* p, const int32_t* count, int E, int E
     return ARISTOS_OK;
 }
 
+// ---- the flag protocol as host-side functions (the device-side stores and waits follow the same layout and the same
+// cyclic comparison; exported for tests that run the protocol among CPU ranks) ------------------------------------
+int ep_flag_words() { return 3 * EP_MAX_WINDOWS * MAX_RANKS; }
+int ep_flag_word_index(int kind, int window, int src) {
+    if (kind < 0 || kind > 2 || window < 0 || window >= EP_MAX_WINDOWS || src < 0 || src >= MAX_RANKS) return -1;
+    return (kind * EP_MAX_WINDOWS + window) * MAX_RANKS + src;
+}
+// Bit s set: source rank s has not yet raised its (kind, window) flag to `epoch` (cyclic comparison: a flag that is
+// ahead of the epoch counts as arrived).
+uint32_t ep_flags_pending(const uint32_t* words, uint32_t epoch, int world, int kind, int window) {
+    uint32_t pending = 0;
+    for (int s = 0; s < world && s < MAX_RANKS; ++s)
+        if (static_cast<int32_t>(words[ep_flag_word_index(kind, window, s)] - epoch) < 0) pending |= 1u << s;
+    return pending;
+}
+// Release: every flag word of this rank takes the current epoch, so nothing of the current forward is pending.
+void ep_flags_release(uint32_t* words, uint32_t epoch) {
+    for (int i = 0; i < ep_flag_words(); ++i)
+        if (static_cast<int32_t>(words[i] - epoch) < 0) words[i] = epoch;
+}
+
 aristos_status_t ep_p2p_release_local_waits(EpP2P* p) {
     if (!p) return ARISTOS_ERR_INVALID_ARG;
-    // a copy on the legacy stream would queue behind the stalled streams: use a non-blocking stream of its own
-    std::vector<uint32_t> words(3 * EP_MAX_WINDOWS * MAX_RANKS, p->epoch);
+    // copies on the legacy stream would queue behind the stalled streams: use a non-blocking stream of its own.
+    // Peers cannot be ahead of this rank's epoch (they need its flags to get there), so raising the lagging words
+    // to the epoch never undoes a store of theirs.
+    std::vector<uint32_t> words(ep_flag_words(), 0u);
     cudaStream_t s = nullptr;
     ARISTOS_CUDA_TRY(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
-    cudaError_t e = cudaMemcpyAsync(p->local, words.data(), words.size() * 4, cudaMemcpyHostToDevice, s);
+    cudaError_t e = cudaMemcpyAsync(words.data(), p->local, words.size() * 4, cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    if (e == cudaSuccess) {
+        ep_flags_release(words.data(), p->epoch);
+        e = cudaMemcpyAsync(p->local, words.data(), words.size() * 4, cudaMemcpyHostToDevice, s);
+    }
     if (e == cudaSuccess) e = cudaStreamSynchronize(s);
     cudaStreamDestroy(s);
     if (e != cudaSuccess) return cuda_fail(e, "release of the local exchange flags");
@@ -293,4 +322,16 @@ aristos_status_t ep_p2p_release_local_waits(EpP2P* p) {
 extern "C" int aristos_ep_transport_agreed(const int* ok_flags, int world) {
     if (!ok_flags || world < 1) return 0;
     return aristos::ep_transport_agreed(ok_flags, world) ? 1 : 0;
+}
+
+extern "C" int aristos_ep_flag_words(void) { return aristos::ep_flag_words(); }
+extern "C" int aristos_ep_flag_word_index(int kind, int window, int src) {
+    return aristos::ep_flag_word_index(kind, window, src);
+}
+extern "C" uint32_t aristos_ep_flags_pending(const uint32_t* words, uint32_t epoch, int world, int kind, int window) {
+    if (!words || world < 1 || aristos::ep_flag_word_index(kind, window, 0) < 0) return 0xffffffffu;
+    return aristos::ep_flags_pending(words, epoch, world, kind, window);
+}
+extern "C" void aristos_ep_flags_release(uint32_t* words, uint32_t epoch) {
+    if (words) aristos::ep_flags_release(words, epoch);
 }

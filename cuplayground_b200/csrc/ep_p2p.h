@@ -54,6 +54,12 @@ uint32_t ep_p2p_epoch(const EpP2P* p);
 // One small kernel: count[e] of every expert goes into its owner's received-count list (entry rank * E_local +
 // e % E_local) and the EP_FLAG_COUNT flag (window 0) of this rank is raised at every rank.
 aristos_status_t ep_p2p_send_counts(EpP2P* p, const int32_t* count, int E, int E_local, cudaStream_t stream);
+// The flag page as plain words (host-side mirror of what the kernels and stream waits do; used by the release below
+// and by tests that run the protocol among CPU ranks).
+int ep_flag_words();
+int ep_flag_word_index(int kind, int window, int src);
+uint32_t ep_flags_pending(const uint32_t* words, uint32_t epoch, int world, int kind, int window);
+void ep_flags_release(uint32_t* words, uint32_t epoch);
 // Host-side release: store the current epoch into every one of THIS rank's flag words, so that stream waits and
 // kernel waits of the current forward that a missing peer left unsatisfied complete (their data is then undefined;
 // the caller marks the forward failed).

@@ -94,6 +94,17 @@ constexpr int MAX_PEER_OUT = 8;
 struct PeerOutMaps {
     CUtensorMap m[MAX_PEER_OUT];
 };
+// Kernel argument: the maps for the instantiations that return tiles to peers, one word for those that do not (the
+// kernels are specialised on the operand format, on bias and on peer output at compile time, so the common case -
+// bf16, no bias, local output - carries none of the other cases' instructions, registers or arguments).
+template <bool PEERS>
+struct PeerMapsArg {
+    CUtensorMap m[MAX_PEER_OUT];
+};
+template <>
+struct PeerMapsArg<false> {
+    int unused;
+};
 
 // Rows of group g inside the row window of this launch.
 __device__ __forceinline__ int window_rows(const FfnGemmParams& p, int g) {
@@ -207,7 +218,7 @@ __device__ __forceinline__ void add_bias32(uint32_t (&acc)[32], const void* bias
 // accumulator buffer is handed back as soon as the last TMEM load has landed. A tile that lies entirely at or past
 // the group's valid rows stores nothing; a partly valid tile stores all of its 128 rows (the extra rows hold
 // unspecified values, never past the group's row capacity: the tensor map clips them).
-template <bool PAIR>
+template <bool PAIR, int FMT, bool BIAS>
 __device__ __forceinline__ void epilogue_tile(const FfnGemmParams& p, const CUtensorMap* tmOut, int out_g, int g, int m0,
                                               int n0, int row_in_tile, uint32_t taddr, uint32_t tempty, int lane,
                                               int epi_tid, uint32_t staging) {
@@ -236,10 +247,10 @@ __device__ __forceinline__ void epilogue_tile(const FfnGemmParams& p, const CUte
                     ptx::mbar_arrive(tempty);
                 }
             }
-            if (n0 + col < p.N) {          // act(acc + bias), the reference's epilogue (processor/tiling.cuh:29-57)
+            if (BIAS && n0 + col < p.N) {  // act(acc + bias), the reference's epilogue (processor/tiling.cuh:29-57)
                 const size_t boff = (size_t)(g % p.experts) * p.N + n0 + col;
-                if (p.bias0) add_bias32(a, p.bias0, boff, p.fmt);
-                if (p.gated && p.bias1) add_bias32(b, p.bias1, boff, p.fmt);
+                if (p.bias0) add_bias32(a, p.bias0, boff, FMT);
+                if (p.gated && p.bias1) add_bias32(b, p.bias1, boff, FMT);
             }
             uint32_t o[16];
 #pragma unroll
@@ -250,7 +261,7 @@ __device__ __forceinline__ void epilogue_tile(const FfnGemmParams& p, const CUte
                     v1 = act_silu(v1) * __uint_as_float(b[2 * i + 1]);
                 } else if (p.act == ARISTOS_ACT_RELU) { v0 = act_relu(v0); v1 = act_relu(v1); }
                 else if (p.act == ARISTOS_ACT_GELU) { v0 = act_gelu(v0); v1 = act_gelu(v1); }
-                o[i] = pack_16bit(v0, v1, p.fmt);
+                o[i] = pack_16bit(v0, v1, FMT);
             }
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -269,7 +280,7 @@ __device__ __forceinline__ void epilogue_tile(const FfnGemmParams& p, const CUte
 
 // The same for fp32 output (tf32 path): a 128-byte staging row holds 32 columns, so the tile leaves in 32-column
 // chunks.
-template <bool PAIR>
+template <bool PAIR, bool BIAS>
 __device__ __forceinline__ void epilogue_tile_f32(const FfnGemmParams& p, const CUtensorMap* tmOut, int out_g, int g,
                                                   int m0, int n0, int row_in_tile, uint32_t taddr, uint32_t tempty,
                                                   int lane, int epi_tid, uint32_t staging) {
@@ -296,10 +307,10 @@ __device__ __forceinline__ void epilogue_tile_f32(const FfnGemmParams& p, const 
                 ptx::mbar_arrive(tempty);
             }
         }
-        if (n0 + col < p.N) {
+        if (BIAS && n0 + col < p.N) {
             const size_t boff = (size_t)(g % p.experts) * p.N + n0 + col;
-            if (p.bias0) add_bias32(a, p.bias0, boff, p.fmt);
-            if (p.gated && p.bias1) add_bias32(b, p.bias1, boff, p.fmt);
+            if (p.bias0) add_bias32(a, p.bias0, boff, FMT_TF32);
+            if (p.gated && p.bias1) add_bias32(b, p.bias1, boff, FMT_TF32);
         }
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
@@ -321,10 +332,11 @@ __device__ __forceinline__ void epilogue_tile_f32(const FfnGemmParams& p, const 
     }
 }
 
+template <int FMT, bool BIAS, bool PEERS>
 __global__ void __launch_bounds__(FFN_THREADS, 1)
 ffn_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB0,
                         const __grid_constant__ CUtensorMap tmB1, const __grid_constant__ CUtensorMap tmOut,
-                        const __grid_constant__ PeerOutMaps peers, const FfnGemmParams p) {
+                        const __grid_constant__ PeerMapsArg<PEERS> peers, const FfnGemmParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const uint32_t staging = ptx::smem_u32(smem + STAGES * STAGE_BYTES);
@@ -366,7 +378,7 @@ ffn_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     ptx::tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const int total_tiles = prefix[p.groups];
-    const int bke = p.fmt == FMT_TF32 ? BK / 2 : BK;   // elements of K per stage: 128 bytes
+    constexpr int bke = FMT == FMT_TF32 ? BK / 2 : BK;   // elements of K per stage: 128 bytes
     const int kblocks = p.K / bke;
 
     if (warp == 0) {
@@ -404,7 +416,7 @@ ffn_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            const uint32_t idesc = ptx::umma_idesc_f32acc(BM, BN, p.fmt == FMT_BF16 ? 1u : (p.fmt == FMT_F16 ? 0u : 2u));
+            constexpr uint32_t idesc = ptx::umma_idesc_f32acc(BM, BN, FMT == FMT_BF16 ? 1u : (FMT == FMT_F16 ? 0u : 2u));
             int stage = 0;
             uint32_t phase = 0;
             int it = 0;
@@ -426,7 +438,7 @@ ffn_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k) {
                         // advance 32 bytes (16 bf16) along K inside the swizzled row: +2 in 16-byte units
-                        if (p.fmt == FMT_TF32) ptx::umma_tf32(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                        if constexpr (FMT == FMT_TF32) ptx::umma_tf32(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
                         else ptx::umma_f16(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
                     }
                     ptx::umma_commit(bar_empty + 8 * stage);
@@ -457,15 +469,15 @@ ffn_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
             const CUtensorMap* om = &tmOut;
             int og = g;
-            if (p.peer_world > 0) {
+            if constexpr (PEERS) {
                 const int src = g / p.experts;
                 om = &peers.m[src];
                 og = p.peer_rank * p.experts + (g - src * p.experts);
             }
-            if (p.fmt == FMT_TF32)
-                epilogue_tile_f32<false>(p, om, og, g, m0, n0, row_in_tile, taddr, bar_tempty + 8 * buf, lane, epi_tid, staging);
+            if constexpr (FMT == FMT_TF32)
+                epilogue_tile_f32<false, BIAS>(p, om, og, g, m0, n0, row_in_tile, taddr, bar_tempty + 8 * buf, lane, epi_tid, staging);
             else
-                epilogue_tile<false>(p, om, og, g, m0, n0, row_in_tile, taddr, bar_tempty + 8 * buf, lane, epi_tid, staging);
+                epilogue_tile<false, FMT, BIAS>(p, om, og, g, m0, n0, row_in_tile, taddr, bar_tempty + 8 * buf, lane, epi_tid, staging);
         }
         if (epi_tid == 0) ptx::bulk_wait_group0();
     }
@@ -489,10 +501,11 @@ constexpr int P_STAGE_BYTES = A_STAGE_BYTES + B_HALF_BYTES;     // 32 KB per CTA
 constexpr int P_SMEM_BYTES = 1024 + P_STAGES * P_STAGE_BYTES + STAGING_BYTES + SMEM_AUX_BYTES;
 constexpr int PBM = 256;                                         // rows per pair tile
 
+template <int FMT, bool BIAS, bool PEERS>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(FFN_THREADS, 1)
 ffn_grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB0,
                              const __grid_constant__ CUtensorMap tmB1, const __grid_constant__ CUtensorMap tmOut,
-                             const __grid_constant__ PeerOutMaps peers, const FfnGemmParams p) {
+                             const __grid_constant__ PeerMapsArg<PEERS> peers, const FfnGemmParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const uint32_t staging = ptx::smem_u32(smem + P_STAGES * P_STAGE_BYTES);
@@ -537,7 +550,7 @@ ffn_grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gr
     ptx::tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const int total_tiles = prefix[p.groups];
-    const int bke = p.fmt == FMT_TF32 ? BK / 2 : BK;   // elements of K per stage: 128 bytes
+    constexpr int bke = FMT == FMT_TF32 ? BK / 2 : BK;   // elements of K per stage: 128 bytes
     const int kblocks = p.K / bke;
 
     if (warp == 0) {
@@ -575,7 +588,7 @@ ffn_grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gr
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer (CTA 0 only)
         if (lane == 0 && cta == 0) {
-            const uint32_t idesc = ptx::umma_idesc_f32acc(PBM, BN, p.fmt == FMT_BF16 ? 1u : (p.fmt == FMT_F16 ? 0u : 2u));
+            constexpr uint32_t idesc = ptx::umma_idesc_f32acc(PBM, BN, FMT == FMT_BF16 ? 1u : (FMT == FMT_F16 ? 0u : 2u));
             const uint32_t empty_peer = ptx::mapa_shared(bar_empty, 1);
             const uint32_t tfull_peer = ptx::mapa_shared(bar_tfull, 1);
             int stage = 0;
@@ -598,7 +611,7 @@ ffn_grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gr
                     const uint64_t db = ptx::umma_desc_k_sw128(sa + A_STAGE_BYTES);
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k)
-                        if (p.fmt == FMT_TF32) ptx::umma_tf32_pair(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                        if constexpr (FMT == FMT_TF32) ptx::umma_tf32_pair(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
                         else ptx::umma_f16_pair(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
                     // release the stage in both CTAs
                     ptx::umma_commit_pair(bar_empty + 8 * stage);
@@ -633,15 +646,15 @@ ffn_grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gr
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
             const CUtensorMap* om = &tmOut;
             int og = g;
-            if (p.peer_world > 0) {
+            if constexpr (PEERS) {
                 const int src = g / p.experts;
                 om = &peers.m[src];
                 og = p.peer_rank * p.experts + (g - src * p.experts);
             }
-            if (p.fmt == FMT_TF32)
-                epilogue_tile_f32<true>(p, om, og, g, m0, n0, row_in_tile, taddr, tempty0 + 8 * buf, lane, epi_tid, staging);
+            if constexpr (FMT == FMT_TF32)
+                epilogue_tile_f32<true, BIAS>(p, om, og, g, m0, n0, row_in_tile, taddr, tempty0 + 8 * buf, lane, epi_tid, staging);
             else
-                epilogue_tile<true>(p, om, og, g, m0, n0, row_in_tile, taddr, tempty0 + 8 * buf, lane, epi_tid, staging);
+                epilogue_tile<true, FMT, BIAS>(p, om, og, g, m0, n0, row_in_tile, taddr, tempty0 + 8 * buf, lane, epi_tid, staging);
         }
         if (epi_tid == 0) ptx::bulk_wait_group0();
     }
@@ -700,12 +713,13 @@ int band_rows_for(int window_rows, int K, int elt) {
     return (int64_t)window_rows * K * elt > (48ll << 20) ? 2048 : 0;
 }
 
+template <int FMT, bool BIAS, bool PEERS>
 aristos_status_t max_pair_clusters(int* out) {
     // a persistent grid must be fully co-resident: ask how many 2-CTA clusters the device can hold at once
     static int max_clusters = -1;
     if (max_clusters < 0) {
-        ARISTOS_CUDA_TRY(cudaFuncSetAttribute(ffn_grouped_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                              P_SMEM_BYTES));
+        auto kernel = ffn_grouped_gemm_pair_kernel<FMT, BIAS, PEERS>;
+        ARISTOS_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES));
         cudaLaunchConfig_t lc = {};
         lc.gridDim = dim3(2 * (device_sm_count() / 2));
         lc.blockDim = dim3(FFN_THREADS);
@@ -716,7 +730,7 @@ aristos_status_t max_pair_clusters(int* out) {
         lc.attrs = &at;
         lc.numAttrs = 1;
         int n = 0;
-        ARISTOS_CUDA_TRY(cudaOccupancyMaxActiveClusters(&n, ffn_grouped_gemm_pair_kernel, &lc));
+        ARISTOS_CUDA_TRY(cudaOccupancyMaxActiveClusters(&n, kernel, &lc));
         max_clusters = n;
         if (getenv("ARISTOS_DEBUG")) fprintf(stderr, "[aristos] co-resident 2-CTA clusters: %d\n", n);
     }
@@ -724,47 +738,76 @@ aristos_status_t max_pair_clusters(int* out) {
     return ARISTOS_OK;
 }
 
-aristos_status_t launch_gemm(const void* A, const void* B0, const void* B1, FfnGemmParams p, const PeerOutMaps& peers,
-                             int grid_limit, cudaStream_t st) {
+template <int FMT, bool BIAS, bool PEERS>
+aristos_status_t launch_gemm_t(const void* A, const void* B0, const void* B1, FfnGemmParams p, const PeerOutMaps& peers,
+                               int grid_limit, cudaStream_t st) {
     CUtensorMap tmA, tmB0, tmB1, tmOut;
-    ARISTOS_TRY(make_map_3d(&tmA, A, p.K, p.rows_per_group, p.groups, p.fmt));
-    ARISTOS_TRY(make_map_3d(&tmB0, B0, p.K, p.N, p.experts, p.fmt));
-    ARISTOS_TRY(make_map_3d(&tmB1, B1, p.K, p.N, p.experts, p.fmt));
-    ARISTOS_TRY(make_map_3d(&tmOut, p.out, p.N, p.rows_per_group, p.groups, p.fmt));
+    ARISTOS_TRY(make_map_3d(&tmA, A, p.K, p.rows_per_group, p.groups, FMT));
+    ARISTOS_TRY(make_map_3d(&tmB0, B0, p.K, p.N, p.experts, FMT));
+    ARISTOS_TRY(make_map_3d(&tmB1, B1, p.K, p.N, p.experts, FMT));
+    ARISTOS_TRY(make_map_3d(&tmOut, p.out, p.N, p.rows_per_group, p.groups, FMT));
+    PeerMapsArg<PEERS> pm;
+    if constexpr (PEERS) memcpy(pm.m, peers.m, sizeof(pm.m));
+    else pm.unused = 0;
     const int out_w = p.gated ? 128 : 256;
     int sms = device_sm_count();
     if (sms <= 0) { set_last_error("no CUDA device"); return ARISTOS_ERR_CUDA; }
     if (grid_limit > 0 && grid_limit < sms) sms = grid_limit;
     const int window = p.row_end - p.row_begin;
-    const int band_rows = band_rows_for(window, p.K, p.fmt == FMT_TF32 ? 4 : 2);
+    const int band_rows = band_rows_for(window, p.K, FMT == FMT_TF32 ? 4 : 2);
     const int mode = tile_mode();
     const bool pairs = mode == TILES_PAIR || mode == TILES_PAIR_PADDED || (mode == TILES_AUTO && window >= 1024);
     if (pairs) {
         int max_clusters = 0;
-        ARISTOS_TRY(max_pair_clusters(&max_clusters));
+        ARISTOS_TRY((max_pair_clusters<FMT, BIAS, PEERS>(&max_clusters)));
         const int64_t bound = (int64_t)p.groups * ceil_div(window, PBM) * ceil_div(p.N, out_w);
         int npairs = sms / 2 < max_clusters ? sms / 2 : max_clusters;
         if (bound < npairs) npairs = (int)bound;
         p.rows_mode = mode == TILES_PAIR_PADDED ? ROWS_ALL : ROWS_FULL_PAIRS;
         p.band = band_rows / PBM;
         if (npairs > 0 && (mode == TILES_PAIR_PADDED || window >= PBM)) {
-            ffn_grouped_gemm_pair_kernel<<<2 * npairs, FFN_THREADS, P_SMEM_BYTES, st>>>(tmA, tmB0, tmB1, tmOut, peers, p);
+            ffn_grouped_gemm_pair_kernel<FMT, BIAS, PEERS><<<2 * npairs, FFN_THREADS, P_SMEM_BYTES, st>>>(
+                tmA, tmB0, tmB1, tmOut, pm, p);
             ARISTOS_COUNT_LAUNCH();
             ARISTOS_CUDA_TRY(cudaGetLastError());
         }
         if (mode == TILES_PAIR_PADDED) return ARISTOS_OK;
         p.rows_mode = ROWS_TAIL;     // the single-CTA kernel below finishes every group's last < 256 rows
     }
-    ARISTOS_CUDA_TRY(cudaFuncSetAttribute(ffn_grouped_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          SMEM_BYTES));
+    auto kernel = ffn_grouped_gemm_kernel<FMT, BIAS, PEERS>;
+    static bool attr_set = false;    // per instantiation
+    if (!attr_set) {
+        ARISTOS_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        attr_set = true;
+    }
     p.band = band_rows / BM;
     const int64_t bound = (int64_t)p.groups * (pairs ? 2 : ceil_div(window, BM)) * ceil_div(p.N, out_w);
     const int grid = (int)(bound < sms ? bound : sms);
     if (grid <= 0) return ARISTOS_OK;
-    ffn_grouped_gemm_kernel<<<grid, FFN_THREADS, SMEM_BYTES, st>>>(tmA, tmB0, tmB1, tmOut, peers, p);
+    kernel<<<grid, FFN_THREADS, SMEM_BYTES, st>>>(tmA, tmB0, tmB1, tmOut, pm, p);
     ARISTOS_COUNT_LAUNCH();
     ARISTOS_CUDA_TRY(cudaGetLastError());
     return ARISTOS_OK;
+}
+
+template <int FMT>
+aristos_status_t launch_gemm_f(const void* A, const void* B0, const void* B1, const FfnGemmParams& p,
+                               const PeerOutMaps& peers, int grid_limit, cudaStream_t st) {
+    const bool bias = p.bias0 != nullptr || p.bias1 != nullptr;
+    const bool to_peers = p.peer_world > 0;
+    if (bias) return to_peers ? launch_gemm_t<FMT, true, true>(A, B0, B1, p, peers, grid_limit, st)
+                              : launch_gemm_t<FMT, true, false>(A, B0, B1, p, peers, grid_limit, st);
+    return to_peers ? launch_gemm_t<FMT, false, true>(A, B0, B1, p, peers, grid_limit, st)
+                    : launch_gemm_t<FMT, false, false>(A, B0, B1, p, peers, grid_limit, st);
+}
+
+aristos_status_t launch_gemm(const void* A, const void* B0, const void* B1, const FfnGemmParams& p,
+                             const PeerOutMaps& peers, int grid_limit, cudaStream_t st) {
+    switch (p.fmt) {
+        case FMT_BF16: return launch_gemm_f<FMT_BF16>(A, B0, B1, p, peers, grid_limit, st);
+        case FMT_F16: return launch_gemm_f<FMT_F16>(A, B0, B1, p, peers, grid_limit, st);
+        default: return launch_gemm_f<FMT_TF32>(A, B0, B1, p, peers, grid_limit, st);
+    }
 }
 
 }  // namespace

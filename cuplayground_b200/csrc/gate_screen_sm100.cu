@@ -18,8 +18,11 @@
 // n 2^-23 sum|x_h w_h|; over the slices, sum_s |x_s||w_s| <= |x||w| (Cauchy-Schwarz, twice). The factor 4 covers
 // block-wise alignment and truncation inside the tensor core and the contract's own roundings. The second term is the
 // fp32 sum over the slices (computed from the values added), the third the bias addition. The select kernel also
-// checks the bound on every candidate (where it has both values); a token that violates it is evaluated exactly over
-// all experts and DEV_FAULT_SCREEN is raised in the status word.
+// checks the bound on every candidate (where it has both values) and on one expert that the screen ruled out (the one
+// whose upper bound came closest to the k-th place: what a bound that is too small would drop first); a token that
+// violates it is evaluated exactly over all experts and DEV_FAULT_SCREEN is raised in the status word - an error, not
+// a warning, because a bound that fails where it is checked cannot be trusted where it is not. Tokens whose logits are
+// NaN leave no candidate: they raise DEV_FAULT_NONFINITE instead.
 // The routing is therefore identical to gate.cu's; only the weights of a softmax gate may differ in the last bits
 // (the screened logits of non-candidates enter the denominator). Used by the layer when no logits are requested,
 // for 16-bit inputs and many experts (up to 256).
@@ -361,16 +364,44 @@ gate_select_kernel(const T* __restrict__ x, const T* __restrict__ wg, const floa
         if (pred) cand[pos[i]] = e;
         n += __popc(mask);
     }
-    __syncwarp();
-    exact_logits_all<T>(xrow, wg, bias, H, cand, n, exact, lane);
+    // One expert that the screen ruled out is evaluated exactly all the same: the one whose upper bound came closest
+    // to the k-th place. It is the likeliest victim of an error bound that does not hold, and no candidate check
+    // would ever see it. It sits behind the candidates in the list (entry n) and takes no part in the top-k.
+    int probe_slot = -1;         // slot of the probed expert in the lane that owns it
+    {
+        uint32_t bk = 0u;
+        int bs = -1;
+#pragma unroll
+        for (int i = 0; i < SLOTS; ++i) {
+            const int e = lane + 32 * i;
+            if (e < E && pos[i] < 0) {
+                const uint32_t key = order_key(a[i] + err[i]);
+                if (key > bk) { bk = key; bs = i; }
+            }
+        }
+        const uint32_t wk = __reduce_max_sync(0xffffffffu, bk);
+        const uint32_t owners = __ballot_sync(0xffffffffu, wk != 0u && bk == wk);
+        if (owners != 0u && lane == __ffs(owners) - 1) {
+            probe_slot = bs;
+            cand[n] = lane + 32 * bs;
+        }
+        __syncwarp();
+        const int n_eval = n + (owners != 0u ? 1 : 0);
+        exact_logits_all<T>(xrow, wg, bias, H, cand, n_eval, exact, lane);
+    }
 
     // the error bound, checked wherever both values exist; a token that breaks it is evaluated over all experts
-    bool bad = n == 0;      // only NaN logits leave no candidate
+    bool nonfinite = n == 0;    // only NaN logits leave no candidate
+    bool bad = false;
 #pragma unroll
-    for (int i = 0; i < SLOTS; ++i)
+    for (int i = 0; i < SLOTS; ++i) {
         if (pos[i] >= 0) bad |= !(fabsf(exact[pos[i]] - a[i]) <= err[i]);
-    if (__any_sync(0xffffffffu, bad)) {
-        if (lane == 0 && dev_status) atomicOr(dev_status, DEV_FAULT_SCREEN);
+        if (i == probe_slot) bad |= !(fabsf(exact[n] - a[i]) <= err[i]);
+    }
+    nonfinite = __any_sync(0xffffffffu, nonfinite);
+    bad = __any_sync(0xffffffffu, bad);
+    if (nonfinite || bad) {
+        if (lane == 0 && dev_status) atomicOr(dev_status, nonfinite ? DEV_FAULT_NONFINITE : DEV_FAULT_SCREEN);
         __syncwarp();
         n = E;
 #pragma unroll

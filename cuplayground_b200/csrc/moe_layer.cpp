@@ -80,8 +80,9 @@ struct aristos_moe {
     cudaEvent_t ev_last = nullptr;           // end of the last forward on its stream
     bool ev_last_valid = false;
     // training mode (is_training = 1): routing of the last forward kept for a backward pass + load-balance statistics
-    int32_t *saved_topk_idx = nullptr, *saved_slot_of = nullptr;
-    float *saved_topk_w = nullptr, *lb_stats = nullptr;
+    void* train_own = nullptr;               // layer-owned buffer (in the workspace)
+    void* train_buf = nullptr;               // where the next forward saves: caller's buffer, or train_own
+    aristos_training_state_t train_last = {};   // what the last forward saved
     // stage stopwatch
     static constexpr int PROF_SETS = 64;      // ring of event sets: stage times average over the last 64 forwards
     bool profiling = false;
@@ -99,6 +100,12 @@ struct Carver {
         return o;
     }
 };
+
+// Saved routing of one forward: [topk_idx | topk_w | slot_of | load-balance statistics], each part 256-byte aligned.
+size_t training_bytes(const aristos_moe* L) {
+    const size_t sk = align_up((size_t)L->S * L->k * 4, 256);
+    return 3 * sk + aristos_load_balance_stats_bytes(L->E);
+}
 
 // Lays the buffers out; with base == nullptr only the total size is computed.
 size_t plan_workspace(aristos_moe* L, char* base) {
@@ -118,12 +125,7 @@ size_t plan_workspace(aristos_moe* L, char* base) {
     CARVE(slot_of, int32_t*, S * k * 4)
     CARVE(token_of_slot, int32_t*, E * cap * 4)
     CARVE(gate_bias, float*, E * 4)
-    if (L->cfg.is_training) {
-        CARVE(saved_topk_idx, int32_t*, S * k * 4)
-        CARVE(saved_topk_w, float*, S * k * 4)
-        CARVE(saved_slot_of, int32_t*, S * k * 4)
-        CARVE(lb_stats, float*, (2 * E + 2) * 4)
-    }
+    if (L->cfg.is_training) CARVE(train_own, void*, training_bytes(L))
     CARVE(dispatch_scratch, void*, L->dispatch_scratch_bytes)
     if (L->gate_scratch_bytes) CARVE(gate_scratch, void*, L->gate_scratch_bytes)
     if (L->fp8) {
@@ -441,6 +443,26 @@ static aristos_status_t forward_impl(aristos_moe_t* L, const void* x, const void
     stage.next("dispatch");
     ARISTOS_TRY(dispatch_impl(L->topk_idx, L->S, L->k, L->E, L->cap, L->count, L->slot_of, L->token_of_slot,
                               L->dispatch_scratch, L->dispatch_scratch_bytes, L->dev_status, st));
+    if (L->cfg.is_training) {
+        // training mode: the routing of this forward is copied out of the working buffers (which the next forward
+        // overwrites) together with its load-balance statistics
+        char* tb = static_cast<char*>(L->train_buf ? L->train_buf : L->train_own);
+        const size_t skb = (size_t)L->S * L->k * 4, sk = align_up(skb, 256);
+        aristos_training_state_t ts;
+        ts.topk_idx = reinterpret_cast<int32_t*>(tb);
+        ts.topk_w = reinterpret_cast<float*>(tb + sk);
+        ts.slot_of = reinterpret_cast<int32_t*>(tb + 2 * sk);
+        ts.load_balance = reinterpret_cast<float*>(tb + 3 * sk);
+        ts.tokens = L->S;
+        ts.top_k = L->k;
+        ts.num_experts = L->E;
+        ARISTOS_CUDA_TRY(cudaMemcpyAsync(const_cast<int32_t*>(ts.topk_idx), L->topk_idx, skb, cudaMemcpyDeviceToDevice, st));
+        ARISTOS_CUDA_TRY(cudaMemcpyAsync(const_cast<float*>(ts.topk_w), L->topk_w, skb, cudaMemcpyDeviceToDevice, st));
+        ARISTOS_CUDA_TRY(cudaMemcpyAsync(const_cast<int32_t*>(ts.slot_of), L->slot_of, skb, cudaMemcpyDeviceToDevice, st));
+        ARISTOS_TRY(aristos_load_balance_stats(L->topk_idx, L->topk_w, L->slot_of, L->S, L->k, L->E,
+                                               const_cast<float*>(ts.load_balance), stream));
+        L->train_last = ts;
+    }
     const size_t nb1 = (size_t)L->E_local * (L->I / 128) * (L->H / 128);
     const bool swiglu = L->cfg.hidden_act == ARISTOS_ACT_SWIGLU;
     const float* s1 = static_cast<const float*>(scales);
@@ -740,9 +762,11 @@ aristos_status_t aristos_moe_status(aristos_moe_t* L) {
     if (bits & DEV_FAULT_TIMEOUT) { set_last_error("a bounded device-side wait expired"); return ARISTOS_ERR_DEVICE_TIMEOUT; }
     if (bits & DEV_FAULT_BOUNDS) { set_last_error("a routing index was out of range"); return ARISTOS_ERR_DEVICE_BOUNDS; }
     if (bits & DEV_FAULT_SCREEN) {
-        set_last_error("the gate's tensor-core screen exceeded its error bound (affected tokens were re-evaluated exactly)");
+        set_last_error("the gate's tensor-core screen exceeded its error bound (affected tokens were re-evaluated "
+                       "exactly; ARISTOS_GATE=exact selects the all-experts gate)");
         return ARISTOS_ERR_GATE_SCREEN;
     }
+    if (bits & DEV_FAULT_NONFINITE) { set_last_error("a token's gate logits were NaN"); return ARISTOS_ERR_NONFINITE; }
     return ARISTOS_OK;
 }
 
@@ -772,6 +796,27 @@ aristos_status_t aristos_moe_stage_ms(aristos_moe_t* L, float out_ms[5]) {
         }
     }
     for (int i = 0; i < 5; ++i) out_ms[i] = (float)(acc[i] / n);
+    return ARISTOS_OK;
+}
+
+size_t aristos_moe_training_bytes(const aristos_moe_t* L) { return (L && L->cfg.is_training) ? training_bytes(L) : 0; }
+
+aristos_status_t aristos_moe_set_training_buffer(aristos_moe_t* L, void* device_buffer, size_t bytes) {
+    if (!L) return ARISTOS_ERR_INVALID_ARG;
+    if (!L->cfg.is_training) { set_last_error("set_training_buffer: the layer was created with is_training = 0"); return ARISTOS_ERR_CONFIG; }
+    if (device_buffer && (bytes < training_bytes(L) || reinterpret_cast<uintptr_t>(device_buffer) % 256 != 0)) {
+        set_last_error("set_training_buffer: %zu bytes given, %zu needed, 256-byte aligned", bytes, training_bytes(L));
+        return ARISTOS_ERR_WORKSPACE;
+    }
+    L->train_buf = device_buffer;
+    return ARISTOS_OK;
+}
+
+aristos_status_t aristos_moe_training_state(const aristos_moe_t* L, aristos_training_state_t* out) {
+    if (!L || !out) return ARISTOS_ERR_INVALID_ARG;
+    if (!L->cfg.is_training) { set_last_error("training_state: the layer was created with is_training = 0"); return ARISTOS_ERR_CONFIG; }
+    if (!L->train_last.topk_idx) { set_last_error("training_state: no forward has run yet"); return ARISTOS_ERR_INVALID_ARG; }
+    *out = L->train_last;
     return ARISTOS_OK;
 }
 

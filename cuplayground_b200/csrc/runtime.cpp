@@ -57,6 +57,7 @@ const char* aristos_status_str(aristos_status_t s) {
         case ARISTOS_ERR_DEVICE_BOUNDS: return "device-side index out of range";
         case ARISTOS_ERR_NOMEM: return "out of memory";
         case ARISTOS_ERR_GATE_SCREEN: return "gate screen error bound exceeded";
+        case ARISTOS_ERR_NONFINITE: return "non-finite gate logits";
     }
     return "unknown status";
 }

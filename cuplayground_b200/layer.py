@@ -308,6 +308,41 @@ class MoELayer:
     def status(self) -> None:
         _lib.check(self._lib.aristos_moe_status(self._h))
 
+    def training_state(self) -> dict:
+        """is_training = 1: what the last forward saved for a backward pass - host copies of the routing and the
+        load-balance statistics (frac, prob per expert; aux loss; dropped share)."""
+        ts = _lib.AristosTrainingStateStruct()
+        _lib.check(self._lib.aristos_moe_training_state(self._h, C.byref(ts)))
+        torch.cuda.synchronize()
+        S, k, E = ts.tokens, ts.top_k, ts.num_experts
+
+        def host(ptr, n, dtype):
+            t = torch.empty(n, dtype=dtype)
+            torch.cuda.current_stream().synchronize()
+            rc = torch.cuda.cudart().cudaMemcpy(t.data_ptr(), ptr, n * 4, 2)      # cudaMemcpyDeviceToHost
+            if int(rc) != 0:
+                raise RuntimeError(f"cudaMemcpy failed with {int(rc)}")
+            return t
+        lb = host(ts.load_balance, 2 * E + 2, torch.float32)
+        return dict(topk_idx=host(ts.topk_idx, S * k, torch.int32).view(S, k),
+                    topk_w=host(ts.topk_w, S * k, torch.float32).view(S, k),
+                    slot_of=host(ts.slot_of, S * k, torch.int32).view(S, k),
+                    frac=lb[:E], prob=lb[E:2 * E], aux=float(lb[2 * E]), dropped=float(lb[2 * E + 1]),
+                    device_ptrs=(ts.topk_idx, ts.topk_w, ts.slot_of, ts.load_balance))
+
+    def set_training_buffer(self, buf: Optional[torch.Tensor]) -> None:
+        """Point the next forwards' saved training state at a caller-owned device buffer (uint8, at least
+        training_bytes, 256-byte aligned); None returns to the layer's own buffer."""
+        self._train_buf = buf
+        if buf is None:
+            _lib.check(self._lib.aristos_moe_set_training_buffer(self._h, None, 0))
+        else:
+            _lib.check(self._lib.aristos_moe_set_training_buffer(self._h, C.c_void_p(buf.data_ptr()), buf.numel()))
+
+    @property
+    def training_bytes(self) -> int:
+        return int(self._lib.aristos_moe_training_bytes(self._h))
+
     def set_timeout_ms(self, timeout_ms: int) -> None:
         """Wall-clock limit of the waits for an expert-parallel forward (status, wait_host, routing, close)."""
         _lib.check(self._lib.aristos_moe_set_timeout_ms(self._h, int(timeout_ms)))

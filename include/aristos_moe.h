@@ -46,7 +46,10 @@ typedef enum aristos_status {
     ARISTOS_ERR_DEVICE_TIMEOUT = 8, /* a bounded device-side wait expired (kernel returned early) */
     ARISTOS_ERR_DEVICE_BOUNDS = 9,  /* a routing-derived index was out of range (access skipped) */
     ARISTOS_ERR_NOMEM = 10,
-    ARISTOS_ERR_GATE_SCREEN = 11    /* the screened gate met an accumulation error above its bound (token re-evaluated exactly) */
+    ARISTOS_ERR_GATE_SCREEN = 11,   /* the screened gate met an accumulation error above its bound: the affected token was
+                                       re-evaluated exactly, but the bound cannot be trusted for these inputs
+                                       (ARISTOS_GATE=exact selects the all-experts gate) */
+    ARISTOS_ERR_NONFINITE = 12      /* a token's gate logits were NaN (non-finite activations or gate weights) */
 } aristos_status_t;
 
 /* torch_dtype (aristos_config.schema.json:54-58) and hidden_act (:24-28), with the extension values. */
@@ -183,6 +186,33 @@ ARISTOS_API aristos_status_t aristos_moe_routing_to_host(const aristos_moe_t* la
  * aristos_moe_destroy still returns. aristos_moe_wait_host, aristos_moe_routing_to_host and aristos_moe_destroy
  * wait the same way. */
 ARISTOS_API aristos_status_t aristos_moe_status(aristos_moe_t* layer);
+/*
+ * Training mode (is_training = 1; the reference's schema has the flag, aristos_config.schema.json:20-23, and nothing
+ * behind it). Every forward of such a layer saves what a backward pass and the auxiliary load-balance loss need,
+ * outside the working buffers that the next forward overwrites: the routing (topk_idx, topk_w, slot_of) and
+ * load_balance = [frac (E) | prob (E) | aux | dropped]: frac[e] = share of the S*k assignments that chose expert e
+ * (before drops), prob[e] = sum of the gate weights given to e / S, aux = E * sum frac*prob, dropped = share of
+ * assignments that capacity dropped. By default the state lives in one layer-owned buffer (overwritten by the next
+ * forward); aristos_moe_set_training_buffer points the NEXT forwards at a caller-owned device buffer of
+ * aristos_moe_training_bytes() bytes (256-byte aligned; NULL = back to the layer's), so a caller keeps as many
+ * micro-batches alive as it has buffers. aristos_moe_training_state returns the device pointers the LAST forward
+ * wrote (valid in stream order after that forward). aristos_load_balance_stats is the stage on its own
+ * (stats: aristos_load_balance_stats_bytes(E) bytes on the device).
+ */
+typedef struct aristos_training_state {
+    const int32_t* topk_idx;      /* (tokens, top_k) */
+    const float* topk_w;          /* (tokens, top_k) */
+    const int32_t* slot_of;       /* (tokens, top_k), -1 = dropped */
+    const float* load_balance;    /* 2 * num_experts + 2 floats */
+    int tokens, top_k, num_experts;
+} aristos_training_state_t;
+ARISTOS_API size_t aristos_moe_training_bytes(const aristos_moe_t* layer);
+ARISTOS_API aristos_status_t aristos_moe_set_training_buffer(aristos_moe_t* layer, void* device_buffer, size_t bytes);
+ARISTOS_API aristos_status_t aristos_moe_training_state(const aristos_moe_t* layer, aristos_training_state_t* out);
+ARISTOS_API size_t aristos_load_balance_stats_bytes(int E);
+ARISTOS_API aristos_status_t aristos_load_balance_stats(const int32_t* topk_idx, const float* topk_w,
+                                                        const int32_t* slot_of, int S, int k, int E, float* stats,
+                                                        void* stream);
 /* Wall-clock limit of those waits in milliseconds (default 30000, or ARISTOS_EP_TIMEOUT_MS at create). */
 ARISTOS_API aristos_status_t aristos_moe_set_timeout_ms(aristos_moe_t* layer, int timeout_ms);
 /* Stage stopwatch (the reference times its kernels with %globaltimer reads and cudaEvents, mma.cuh:56,163,
@@ -319,6 +349,17 @@ ARISTOS_API int aristos_ffn_tile_coord(int local, int row_tiles, int col_tiles, 
 /* Whether peer memory is the transport, given every rank's "works here" flag (all-gathered at create): only if it
  * works on all ranks; otherwise all ranks fall back together. Host-only, for tests of the agreement. */
 ARISTOS_API int aristos_ep_transport_agreed(const int* ok_flags, int world);
+/* The arrival-flag protocol of the peer-memory transport on plain host words, as the kernels and stream waits apply it
+ * to a rank's flag page (successor of the reference's signal values, auditorium/overlap.cuh:20-24, :100-105): a page
+ * of aristos_ep_flag_words() 32-bit words; word aristos_ep_flag_word_index(kind, window, src) (kind 0 rows in, 1
+ * results back, 2 counts) holds the last epoch rank src published; aristos_ep_flags_pending returns the set of source
+ * ranks (bit s) whose flag has not reached `epoch` (cyclic comparison); aristos_ep_flags_release is what a rank does
+ * to its OWN page when its time limit expires: every lagging word takes the epoch, nothing stays pending. Host-only;
+ * the tests run the protocol among CPU ranks with them. */
+ARISTOS_API int aristos_ep_flag_words(void);
+ARISTOS_API int aristos_ep_flag_word_index(int kind, int window, int src);
+ARISTOS_API uint32_t aristos_ep_flags_pending(const uint32_t* words, uint32_t epoch, int world, int kind, int window);
+ARISTOS_API void aristos_ep_flags_release(uint32_t* words, uint32_t epoch);
 /* The order in which the expert GEMMs walk `groups` row groups of `experts` experts (group g uses expert
  * g % experts): position -> group, a permutation that keeps the groups of one expert adjacent. Host-only, for tests. */
 ARISTOS_API int aristos_ffn_group_order(int position, int groups, int experts);

@@ -135,8 +135,8 @@ def test_gate_scratch_bytes(cp):
 
 def test_status_strings_cover_every_code(cp):
     lib = cp._lib.load()
-    names = {lib.aristos_status_str(i).decode() for i in range(12)}
-    assert len(names) == 12 and "unknown status" not in names
+    names = {lib.aristos_status_str(i).decode() for i in range(13)}
+    assert len(names) == 13 and "unknown status" not in names
     assert lib.aristos_status_str(99).decode() == "unknown status"
 
 

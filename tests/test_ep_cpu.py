@@ -222,3 +222,103 @@ def test_row_windows():
         wr, nw = C.c_int(), C.c_int()
         cp._lib.check(lib.aristos_ep_row_windows(cap, C.byref(wr), C.byref(nw)))
         assert (wr.value, nw.value) == (exp_rows, exp_n), (cap, wr.value, nw.value)
+
+
+# ---- the arrival-flag protocol and its time limit, among CPU ranks ----------------------------------------------------
+def _flag_worker(rank, world, port, q):
+    """Two forwards. In the first every rank publishes its flags to every rank; in the second rank 1 never sends.
+    Rank 0 must see rank 1 pending until its time limit, release its own page, and end with nothing pending."""
+    try:
+        sys.path.insert(0, ROOT)
+        import time
+        import torch.distributed as dist
+        import cuplayground_b200 as cp
+        lib = cp._lib.load()
+        dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+        page = np.zeros(lib.aristos_ep_flag_words(), dtype=np.uint32)
+        ptr = page.ctypes.data_as(C.c_void_p)
+        KIND_IN, KIND_COUNT = 0, 2
+        pending = lambda epoch, kind: lib.aristos_ep_flags_pending(ptr, epoch, world, kind, 0)
+
+        store = dist.distributed_c10d._get_default_store()
+
+        def publish(epoch, kind):          # "store my epoch into my word of every rank's page"
+            page[lib.aristos_ep_flag_word_index(kind, 0, rank)] = epoch
+            for d in range(world):
+                if d != rank:
+                    store.set(f"flag/{d}/{kind}/{rank}/{epoch}", "1")
+
+        def poll_arrivals(srcs, epoch, kind, limit_s):
+            """Take in the peers' flag stores until nothing is pending or the limit passes; True when complete."""
+            t0 = time.time()
+            while pending(epoch, kind):
+                for s in srcs:
+                    if store.check([f"flag/{rank}/{kind}/{s}/{epoch}"]):
+                        page[lib.aristos_ep_flag_word_index(kind, 0, s)] = epoch
+                if time.time() - t0 > limit_s:
+                    return False
+                time.sleep(0.005)
+            return True
+
+        others = [r for r in range(world) if r != rank]
+        # forward 1: everyone takes part (counts, then rows)
+        for kind in (KIND_COUNT, KIND_IN):
+            publish(1, kind)
+            assert poll_arrivals(others, 1, kind, 20.0), f"rank {rank}: forward 1 did not complete"
+            assert pending(1, kind) == 0
+        assert pending(2, KIND_COUNT) == (1 << world) - 1          # nothing of forward 2 has arrived yet
+        result = "ok"
+        if rank == 0:
+            # forward 2: rank 1 never sends. Rank 0 publishes, waits with a limit, then releases its own page.
+            publish(2, KIND_COUNT)
+            t0 = time.time()
+            done = poll_arrivals(others, 2, KIND_COUNT, 1.0)
+            waited = time.time() - t0
+            if done or not (0.9 < waited < 10.0):
+                result = f"expected a timeout after about 1 s, got done={done} after {waited:.2f} s"
+            elif pending(2, KIND_COUNT) != 0b10:
+                result = f"pending set {pending(2, KIND_COUNT):b}, expected rank 1 only"
+            else:
+                lib.aristos_ep_flags_release(ptr, 2)
+                if pending(2, KIND_COUNT) or pending(2, KIND_IN) or lib.aristos_ep_flags_pending(ptr, 2, world, 1, 3):
+                    result = "flags still pending after the release"
+                elif pending(3, KIND_COUNT) != (1 << world) - 1:
+                    result = "the release must not satisfy a later epoch"
+        # rank 1 simply does not take part in forward 2 (it keeps its process alive until rank 0 is done)
+        dist.barrier()
+        dist.destroy_process_group()
+        q.put((rank, result))
+    except Exception as e:      # pragma: no cover
+        import traceback
+        q.put((rank, "".join(traceback.format_exception(e))))
+
+
+def test_missing_peer_and_release_among_cpu_ranks():
+    """Host-side failure handling of the exchange, without a GPU: the product's flag-page functions
+    (aristos_ep_flags_pending / aristos_ep_flags_release, the same comparison and layout the stream waits and kernels
+    use) driven by two gloo ranks, one of which stops sending."""
+    import multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_flag_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=120) for _ in procs]
+    for p in procs:
+        p.join(timeout=30)
+    bad = [r for r in results if r[1] != "ok"]
+    assert not bad, bad[0][1]
+
+
+def test_flag_comparison_is_cyclic():
+    import cuplayground_b200 as cp
+    lib = cp._lib.load()
+    page = np.zeros(lib.aristos_ep_flag_words(), dtype=np.uint32)
+    ptr = page.ctypes.data_as(C.c_void_p)
+    i0, i1 = lib.aristos_ep_flag_word_index(0, 2, 0), lib.aristos_ep_flag_word_index(0, 2, 1)
+    assert i0 >= 0 and i1 == i0 + 1 and lib.aristos_ep_flag_word_index(3, 0, 0) == -1
+    page[i0], page[i1] = 0xFFFFFFFF, 2                      # epochs wrap around: 2 is AFTER 0xFFFFFFFF
+    assert lib.aristos_ep_flags_pending(ptr, 0xFFFFFFFF, 2, 0, 2) == 0
+    assert lib.aristos_ep_flags_pending(ptr, 1, 2, 0, 2) == 0b01
+    assert lib.aristos_ep_flags_pending(ptr, 3, 2, 0, 2) == 0b11

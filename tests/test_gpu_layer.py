@@ -287,3 +287,52 @@ def test_layer_with_expert_biases(oracle):
     mx, mean = rel_errors(out.float().cpu().numpy(), ref)
     assert mx < TOL_BF16_MAX and mean < TOL_BF16_MEAN, (mx, mean)
     L.close()
+
+
+def test_training_mode_keeps_routing_and_load_balance_statistics(oracle):
+    """is_training = 1 (aristos_config.schema.json:20-23): every forward saves its routing and the load-balance
+    statistics outside the working buffers; a caller-owned buffer keeps a micro-batch alive across the next forward.
+    Routing bit-exact and statistics within fp32 rounding of the oracle's float64 recomputation."""
+    torch, cp, layer = _mods()
+    S, H, I, E, k = 1024, 256, 256, 16, 2
+    cfg = cp.AristosConfig(capacity_factor=1.0, drop_tokens=1, expert_top_k=k, hidden_act=1, hidden_size=H,
+                           intermediate_size=I, num_experts=E, torch_dtype=2, tokens=S, is_training=1,
+                           gate_bias_zipf_s=1.0)
+    dt = torch.bfloat16
+    _, wg, w1, w3, w2 = make_inputs(S, H, I, E, 41, w_std=0.05)
+    xa, xb = (make_inputs(S, H, I, E, 42 + i, w_std=0.05)[0] for i in range(2))
+    dev_w = [to_dev(a, dt) for a in (wg, w1, w3, w2)]
+    bias = oracle.zipf_bias(E, 1.0)
+    L = layer.MoELayer(cfg)
+    assert L.training_bytes > 0
+    keep = torch.empty(L.training_bytes + 256, dtype=torch.uint8, device="cuda")
+    off = (-keep.data_ptr()) % 256
+    L.set_training_buffer(keep[off:off + L.training_bytes])
+    L.forward(to_dev(xa, dt), *dev_w)            # micro-batch A goes to the caller's buffer
+    state_a = L.training_state()
+    L.set_training_buffer(None)
+    L.forward(to_dev(xb, dt), *dev_w)            # micro-batch B goes to the layer's own buffer
+    L.status()
+    state_b = L.training_state()
+    assert state_a["device_ptrs"] != state_b["device_ptrs"]
+    # A's saved state survived B's forward: read it again through the pointers of the kept buffer
+    L.set_training_buffer(keep[off:off + L.training_bytes])
+    for x, st in ((xa, state_a), (xb, state_b)):
+        ref = oracle.moe_forward(x, wg, w1, w3, w2, k=k, cap=cfg.capacity, hidden_act=1, gate_bias=bias, want_out=False)
+        assert np.array_equal(st["topk_idx"].numpy(), ref["topk_idx"])
+        assert np.array_equal(st["slot_of"].numpy(), ref["slot_of"])
+        assert np.allclose(st["topk_w"].numpy(), ref["topk_w"], rtol=1e-5, atol=1e-7)
+        frac, prob, aux, dropped = oracle.load_balance_stats(ref["topk_idx"], ref["topk_w"], ref["slot_of"], E)
+        assert np.allclose(st["frac"].numpy(), frac, rtol=1e-6, atol=1e-7)
+        assert np.allclose(st["prob"].numpy(), prob, rtol=1e-5, atol=1e-7)
+        assert abs(st["aux"] - aux) < 1e-5 * max(1.0, aux) and abs(st["dropped"] - dropped) < 1e-6
+    assert state_a["dropped"] > 0, "the Zipf prior with capacity factor 1 must overflow some experts"
+    idx_a = torch.empty((S, k), dtype=torch.int32)
+    torch.cuda.cudart().cudaMemcpy(idx_a.data_ptr(), state_a["device_ptrs"][0], S * k * 4, 2)
+    assert torch.equal(idx_a, state_a["topk_idx"]), "the kept buffer was overwritten by the next forward"
+    # a layer without is_training has no training state
+    L2 = layer.MoELayer(cp.AristosConfig(expert_top_k=k, hidden_size=H, intermediate_size=I, num_experts=E,
+                                         torch_dtype=2, tokens=S))
+    with pytest.raises(cp.AristosError):
+        L2.training_state()
+    L.close(); L2.close()

@@ -395,3 +395,37 @@ def test_bounded_flag_wait_gives_up(cp):
     assert lib.aristos_selftest_bounded_flag_wait(150, C.byref(waited), None) == 8     # ARISTOS_ERR_DEVICE_TIMEOUT
     assert 150 <= waited.value < 1500, waited.value
     assert int(torch.ones(4, device="cuda").sum().item()) == 4
+
+
+@pytest.mark.parametrize("f16", [False, True])
+def test_gate_screen_stress_equals_exact_gate(cp, f16):
+    """The screened gate against the all-experts gate on inputs built to strain the screen's error bound: 102400
+    tokens at H = 7168, E = 256, k = 8 (the longest accumulation chains in use); heavy-tailed magnitudes with random
+    signs, so that sum |x w| is far above |logit| (large cancellation, mixed magnitudes); and the experts in 16
+    clusters of 16 whose weight rows differ from each other in a handful of elements by one unit in the last place,
+    so that the k-th place (8 < 16) always falls inside a cluster of near-ties. Both gates must select the same
+    experts in the same order for every token, and the screen must not report a violated bound."""
+    torch = _torch()
+    S, H, E, k = 102400, 7168, 256, 8
+    dt = torch.float16 if f16 else torch.bfloat16
+    g = torch.Generator(device="cuda").manual_seed(1234 + int(f16))
+    heavy = lambda *shape: torch.randn(*shape, generator=g, device="cuda") * torch.exp(
+        1.5 * torch.randn(*shape, generator=g, device="cuda"))
+    x = heavy(S, H).clamp_(-6e4, 6e4).to(dt)
+    base = (heavy(16, H) * 0.02).to(dt)
+    wg = base.repeat_interleave(16, dim=0).contiguous()              # expert 16 c + i = cluster c
+    # one unit in the last place on 1 + i elements of member i (bit pattern + 1 moves a positive value up by one ulp)
+    bits = wg.view(torch.int16)
+    for i in range(1, 16):
+        cols = torch.randint(0, H, (16, i), generator=g, device="cuda")
+        rows = (torch.arange(16, device="cuda") * 16 + i)[:, None].expand(16, i)
+        bits[rows, cols] += 1
+    x, wg = x.contiguous(), wg.contiguous()
+    idx_s, w_s, status = cp.gate_topk_screened(x, wg, k, gate_fn=1, renorm=1)
+    idx_e, w_e = cp.gate_topk(x, wg, k, gate_fn=1, renorm=1)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0, "the screen reported a violated error bound or a non-finite logit"
+    assert torch.equal(idx_s, idx_e), f"{int((idx_s != idx_e).any(dim=1).sum())} tokens routed differently"
+    assert torch.allclose(w_s, w_e, rtol=1e-5, atol=1e-7)            # sigmoid weights of the same exact logits
+    # the clusters really are near-ties: most tokens take their 8 experts from one or two clusters
+    assert (idx_e // 16).to(torch.float32).std(dim=1).median() < 16
