@@ -35,6 +35,12 @@ WORKLOADS = {
                    "quantised per token per 128, bf16 output, 4096 tokens, seed 3"),
     "config4-rank": (4, "DeepSeek-V3-shaped, the share of one of eight ranks: as config4 with the 32 experts a rank "
                         "owns, 4096 tokens"),
+    # a quarter of config4-rank (8 of its 32 experts, 1024 tokens that all select the 8: the same ~1024 rows per
+    # expert), small enough for a multi-pass profiler capture
+    "config4-profile": (4, "DeepSeek-V3-shaped, reduced for profiling: as config4-rank with 8 experts and 1024 tokens "
+                           "(top-8 of 8: 1024 rows per expert)"),
+    "config1": (1, "the fp32 reference case: S=128 H=256 I=512 E=8 top-1 softmax ReLU cf=1.0 fp32, seed 0 (exact FFMA "
+                   "expert GEMM)"),
     "config5": (5, "skewed routing: H=2048 I=1024 GELU E=128 top-4 Zipf(1.2) prior cf=1.0 bf16, 8192 tokens per "
                    "rank, seed 4"),
 }
@@ -311,6 +317,7 @@ def run_ours(args, cfg, workload_desc):
     ms = ev0.elapsed_time(ev1)
     # stage times averaged over the timed steps (events recorded inside the timed region, at most the last 64)
     stage = L.stage_ms()
+    exchange_out_ms = L.exchange_ms() if world > 1 else 0.0
     t = torch.tensor([ms], dtype=torch.float64, device="cuda")
     kept_t = torch.tensor([kept], dtype=torch.float64, device="cuda")
     if world > 1:
@@ -397,7 +404,7 @@ def run_ours(args, cfg, workload_desc):
 
     # ---- both tile shapes of the expert GEMM, timed in this process (one GPU, 16-bit tensor-core workloads)
     variants = None
-    if world == 1 and cfg.torch_dtype in (2, 3) and not args.no_variants:
+    if world == 1 and cfg.torch_dtype in (2, 3) and cfg.capacity >= 1024 and not args.no_variants:
         variants = time_ffn_variants(L, lambda: L.forward(x, wg, w1, w3, w2, out=out, scales=scales), cfg, kept,
                                      local_rank, max(3, min(args.steps, 10)))
 
@@ -439,14 +446,14 @@ def run_ours(args, cfg, workload_desc):
         t_roof, terms = layer_roofline(cfg, world, kept_all / world)
         line = {"metric": "moe_fwd_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
-                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3" if cfg.torch_dtype == 4 else "bf16",
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": {0: "f32", 1: "tf32", 2: "bf16", 3: "f16", 4: "fp8_e4m3"}[cfg.torch_dtype],
                 "data": "synthetic",
                 "config": {"workload": workload_desc, "name": args.workload, "tokens_per_rank": S,
                            "parallelism": f"ep{world}", "ep_transport": L.ep_transport, "l2": "weights (>= 0.4 GB per rank) exceed the 126 MB L2, "
                            "no flush needed between steps", "kept_assignments": kept_all},
                 "clocks": clocks,
-                "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": xh[0].numel() * 2 * world,
-                        "d2h_bytes_per_step": oh[0].numel() * 2 * world, "steps": e2e_steps,
+                "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": xh[0].numel() * xh[0].element_size() * world,
+                        "d2h_bytes_per_step": oh[0].numel() * oh[0].element_size() * world, "steps": e2e_steps,
                         "api": "aristos_moe_submit_host per step + aristos_moe_wait_host (pinned host activations "
                                "in, host result out every step; two steps in flight)", "timing": "host wall clock, "
                         "device synchronised on both sides, max over ranks",
@@ -460,6 +467,14 @@ def run_ours(args, cfg, workload_desc):
                 "layer_roofline": {"seconds": t_roof, **terms, "frac": t_roof / (ms / args.steps * 1e-3),
                                    "constants": "2250 TFLOP/s dense bf16, 8 TB/s HBM, 900 GB/s NVLink per direction"},
                 "stage_ms": stage, "host_enqueue_ms_per_step": host_enqueue_ms}
+        if world > 1:
+            # the outgoing exchange of rank 0: rows that leave the rank x row bytes over the time of its count + gather
+            # kernels (part of stage_ms["ffn"]); the rest of that stage is the GEMMs with the return fused in
+            sent_bytes = kept_all / world * (world - 1) / world * H * 2
+            line["exchange"] = {"gather_ms": exchange_out_ms, "rows_to_peers_bytes": sent_bytes,
+                                "gather_gbs": sent_bytes / (exchange_out_ms * 1e-3) / 1e9 if exchange_out_ms > 0 else None,
+                                "what": "rank 0: count + gather kernels storing kept rows into the owning ranks over "
+                                        "NVLink, CUDA events inside the forward"}
         if parity is not None:
             line["parity"] = parity
         if variants is not None:
@@ -505,9 +520,11 @@ def main():
         cfg.num_experts, cfg.tokens = 2, 4096
     if args.workload == "config4-rank":
         cfg.num_experts = 32
+    if args.workload == "config4-profile":
+        cfg.num_experts, cfg.tokens = 8, 1024
     if args.workload.startswith("config4"):
-        if args.workload == "config4-rank" and args.gpus != 1 and args.impl == "ours":
-            raise SystemExit("config4-rank is the one-GPU share of config4: run config4 with --gpus N instead")
+        if args.workload != "config4" and args.gpus != 1 and args.impl == "ours":
+            raise SystemExit(f"{args.workload} is a one-GPU share of config4: run config4 with --gpus N instead")
         args.no_cpu_baseline = True      # the fp32 oracle would need the de-quantised weights of every expert on the host
     if args.impl == "reference":
         run_reference(args, cfg, desc)

@@ -79,6 +79,7 @@ PROTOTYPES = {
     "aristos_moe_status": (_st, [_vp]),
     "aristos_moe_set_profiling": (_st, [_vp, _i]),
     "aristos_moe_stage_ms": (_st, [_vp, C.POINTER(C.c_float)]),
+    "aristos_moe_exchange_ms": (_st, [_vp, C.POINTER(C.c_float)]),
     "aristos_moe_ep_transport": (C.c_char_p, [_vp]),
     "aristos_moe_launch_count": (C.c_int64, [_vp]),
     "aristos_moe_destroy": (_st, [_vp]),
@@ -109,6 +110,7 @@ PROTOTYPES = {
     "aristos_moe_training_bytes": (_sz, [_vp]),
     "aristos_moe_set_training_buffer": (_st, [_vp, _vp, _sz]),
     "aristos_moe_training_state": (_st, [_vp, C.POINTER(AristosTrainingStateStruct)]),
+    "aristos_moe_training_state_to_host": (_st, [_vp, _vp, _vp, _vp, _vp]),
     "aristos_load_balance_stats_bytes": (_sz, [_i]),
     "aristos_load_balance_stats": (_st, [_vp, _vp, _vp, _i, _i, _i, _vp, _vp]),
     "aristos_ffn_group_order": (_i, [_i, _i, _i]),

@@ -17,11 +17,15 @@ namespace {
 // ((src_rank*E_local + e % E_local)*cap + pos) of that rank's buffer; only positions in [pos_lo, pos_hi) are handled
 // (one row window of the pipeline). One warp per token, 16-byte lanes. With count != nullptr the kernel also stores
 // the per-expert row counts into the owners' count lists (the same stream order publishes both).
+// With send_base != nullptr the destination is densely packed per expert: all sources' rows of expert e follow each
+// other in one group of group_rows rows, this rank's rows starting at row send_base[e] (the rows of the lower ranks
+// come first), so the owner computes whole tiles of one expert instead of one padded group per (source, expert).
 template <int MAXK>
 __global__ void __launch_bounds__(256)
 permute_rows_peer_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ slot_of, int S, int k, int row_vec,
                          int E_local, int cap, int src_rank, int pos_lo, int pos_hi, PeerPtrs dst,
-                         const int32_t* __restrict__ count, int E, PeerPtrs count_dst) {
+                         const int32_t* __restrict__ count, int E, PeerPtrs count_dst,
+                         const int32_t* __restrict__ send_base, int group_rows) {
     // the first CTA also delivers the row counts: count[e] becomes entry (src_rank, e % E_local) of the owner's list
     if (count != nullptr && blockIdx.x == 0)
         for (int e = threadIdx.x; e < E; e += blockDim.x) {
@@ -39,8 +43,11 @@ permute_rows_peer_kernel(const uint4* __restrict__ x, const int32_t* __restrict_
             if (slot >= 0) {
                 const int e = slot / cap, pos = slot - e * cap;
                 const int owner = e / E_local, el = e - owner * E_local;
-                if (pos >= pos_lo && pos < pos_hi)
-                    rows[j] = static_cast<uint4*>(dst.p[owner]) + ((size_t)(src_rank * E_local + el) * cap + pos) * row_vec;
+                if (pos >= pos_lo && pos < pos_hi) {
+                    const size_t row = send_base ? (size_t)el * group_rows + send_base[e] + pos
+                                                 : (size_t)(src_rank * E_local + el) * cap + pos;
+                    rows[j] = static_cast<uint4*>(dst.p[owner]) + row * row_vec;
+                }
             }
         }
     }
@@ -94,11 +101,47 @@ return_rows_peer_kernel(const uint4* __restrict__ y, const int32_t* __restrict__
     }
 }
 
+// From the counts of every expert at every rank (allcount[src * E + e]): where this rank's rows start inside each
+// expert's dense group at the owner (send_base[e] = rows of the lower ranks), how many rows each local expert receives
+// in all (dense_count[el]) and where each source's rows start in it (src_off[el * (world + 1) + s], s = 0 .. world).
+__global__ void dense_plan_kernel(const int32_t* __restrict__ allcount, int world, int E, int E_local, int rank,
+                                  int32_t* __restrict__ send_base, int32_t* __restrict__ dense_count,
+                                  int32_t* __restrict__ src_off) {
+    for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < E; e += gridDim.x * blockDim.x) {
+        int before = 0, total = 0;
+        const int el = e - rank * E_local;
+        const bool mine = el >= 0 && el < E_local;
+        for (int s = 0; s < world; ++s) {
+            if (s == rank) before = total;
+            if (mine) src_off[el * (world + 1) + s] = total;
+            total += allcount[s * E + e];
+        }
+        send_base[e] = before;
+        if (mine) {
+            src_off[el * (world + 1) + world] = total;
+            dense_count[el] = total;
+        }
+    }
+}
+
 }  // namespace
+
+aristos_status_t dense_exchange_plan(const int32_t* allcount, int world, int E, int E_local, int rank,
+                                     int32_t* send_base, int32_t* dense_count, int32_t* src_off, cudaStream_t st) {
+    if (!allcount || !send_base || !dense_count || !src_off || world < 1 || E_local < 1 || E != world * E_local) {
+        set_last_error("dense exchange plan: bad arguments");
+        return ARISTOS_ERR_INVALID_ARG;
+    }
+    dense_plan_kernel<<<ceil_div(E, 128), 128, 0, st>>>(allcount, world, E, E_local, rank, send_base, dense_count, src_off);
+    ARISTOS_COUNT_LAUNCH();
+    ARISTOS_CUDA_TRY(cudaGetLastError());
+    return ARISTOS_OK;
+}
 
 aristos_status_t permute_rows_to_peers(const void* x, const int32_t* slot_of, int S, int k, size_t row_bytes,
                                        int E_local, int cap, int src_rank, int pos_lo, int pos_hi, const PeerPtrs& dst,
-                                       cudaStream_t st, const int32_t* count, int E, const PeerPtrs* count_dst) {
+                                       cudaStream_t st, const int32_t* count, int E, const PeerPtrs* count_dst,
+                                       const int32_t* send_base, int group_rows) {
     if (row_bytes % 16 != 0 || k > 16) { set_last_error("peer gather: row bytes must be a multiple of 16, k <= 16"); return ARISTOS_ERR_INVALID_ARG; }
     if (count && !count_dst) { set_last_error("peer gather: counts without a destination"); return ARISTOS_ERR_INVALID_ARG; }
     if (S == 0 && !count) return ARISTOS_OK;
@@ -106,10 +149,10 @@ aristos_status_t permute_rows_to_peers(const void* x, const int32_t* slot_of, in
     const int grid = S > 0 ? ceil_div(S, 8) : 1;
     const PeerPtrs cd = count ? *count_dst : PeerPtrs{};
     const uint4* xs = static_cast<const uint4*>(x);
-    if (k <= 2) permute_rows_peer_kernel<2><<<grid, 256, 0, st>>>(xs, slot_of, S, k, row_vec, E_local, cap, src_rank, pos_lo, pos_hi, dst, count, E, cd);
-    else if (k <= 4) permute_rows_peer_kernel<4><<<grid, 256, 0, st>>>(xs, slot_of, S, k, row_vec, E_local, cap, src_rank, pos_lo, pos_hi, dst, count, E, cd);
-    else if (k <= 8) permute_rows_peer_kernel<8><<<grid, 256, 0, st>>>(xs, slot_of, S, k, row_vec, E_local, cap, src_rank, pos_lo, pos_hi, dst, count, E, cd);
-    else permute_rows_peer_kernel<16><<<grid, 256, 0, st>>>(xs, slot_of, S, k, row_vec, E_local, cap, src_rank, pos_lo, pos_hi, dst, count, E, cd);
+    if (k <= 2) permute_rows_peer_kernel<2><<<grid, 256, 0, st>>>(xs, slot_of, S, k, row_vec, E_local, cap, src_rank, pos_lo, pos_hi, dst, count, E, cd, send_base, group_rows);
+    else if (k <= 4) permute_rows_peer_kernel<4><<<grid, 256, 0, st>>>(xs, slot_of, S, k, row_vec, E_local, cap, src_rank, pos_lo, pos_hi, dst, count, E, cd, send_base, group_rows);
+    else if (k <= 8) permute_rows_peer_kernel<8><<<grid, 256, 0, st>>>(xs, slot_of, S, k, row_vec, E_local, cap, src_rank, pos_lo, pos_hi, dst, count, E, cd, send_base, group_rows);
+    else permute_rows_peer_kernel<16><<<grid, 256, 0, st>>>(xs, slot_of, S, k, row_vec, E_local, cap, src_rank, pos_lo, pos_hi, dst, count, E, cd, send_base, group_rows);
     ARISTOS_COUNT_LAUNCH();
     ARISTOS_CUDA_TRY(cudaGetLastError());
     return ARISTOS_OK;

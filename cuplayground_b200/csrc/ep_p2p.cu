@@ -42,12 +42,16 @@ struct CountTargets {
     int32_t* ptr[MAX_RANKS];
 };
 
-// Row counts to their owners, then this rank's count flag at every rank (one CTA).
+// Row counts to their owners, then this rank's count flag at every rank (one CTA). With all.ptr[0] != nullptr every
+// rank also gets the whole list (entry src_rank * E + e of its all-counts table).
 __global__ void ep_counts_kernel(const int32_t* __restrict__ count, int E, int E_local, int src_rank, CountTargets dst,
-                                 FlagTargets t, uint32_t epoch) {
+                                 CountTargets all, FlagTargets t, uint32_t epoch) {
     for (int e = threadIdx.x; e < E; e += blockDim.x) {
         const int owner = e / E_local;
-        dst.ptr[owner][src_rank * E_local + (e - owner * E_local)] = count[e];
+        const int c = count[e];
+        dst.ptr[owner][src_rank * E_local + (e - owner * E_local)] = c;
+        if (all.ptr[0] != nullptr)
+            for (int d = 0; d < t.n; ++d) all.ptr[d][src_rank * E + e] = c;
     }
     __threadfence_system();
     __syncthreads();
@@ -76,7 +80,7 @@ StreamWaitValue32Fn stream_wait_fn() {
 
 struct EpP2P {
     int rank = 0, world = 1, groups = 0;
-    size_t off_rcount = 0, off_xr = 0, off_yg = 0, off_aux = 0, bytes = 0;
+    size_t off_rcount = 0, off_allcount = 0, off_xr = 0, off_yg = 0, off_aux = 0, bytes = 0;
     char* local = nullptr;
     std::vector<char*> base;     // every rank's region as mapped into this process (own = local)
     uint32_t epoch = 0;
@@ -110,7 +114,10 @@ aristos_status_t ep_p2p_create(EpComm* bootstrap, int rank, int world, int group
     p->world = world;
     p->groups = groups;
     p->off_rcount = FLAG_BYTES;
-    p->off_xr = align_up(p->off_rcount + (size_t)groups * 4, 1024);
+    // the counts of every expert from every rank (world x E ints, E = groups): what dense packing of the received rows
+    // needs at every sender before it gathers
+    p->off_allcount = align_up(p->off_rcount + (size_t)groups * 4, 256);
+    p->off_xr = align_up(p->off_allcount + (size_t)world * groups * 4, 1024);
     p->off_yg = align_up(p->off_xr + xr_bytes, 1024);
     p->off_aux = align_up(p->off_yg + yg_bytes, 1024);
     p->bytes = align_up(p->off_aux + aux_bytes, 1024);
@@ -128,7 +135,7 @@ aristos_status_t ep_p2p_create(EpComm* bootstrap, int rank, int world, int group
                               !strcmp(getenv("ARISTOS_EP_INJECT_STAGE"), "alloc");
     if (ok) {
         cudaError_t e = inject_alloc ? cudaErrorMemoryAllocation : cudaMalloc(reinterpret_cast<void**>(&p->local), p->bytes);
-        if (e == cudaSuccess) e = cudaMemset(p->local, 0, FLAG_BYTES + (size_t)groups * 4);
+        if (e == cudaSuccess) e = cudaMemset(p->local, 0, p->off_xr);
         if (e == cudaSuccess) e = cudaIpcGetMemHandle(&mine.handle, p->local);
         if (e != cudaSuccess) {
             ok = 0;
@@ -214,6 +221,7 @@ void ep_p2p_peer_ptrs(EpP2P* p, int which, void** out) {
     for (int r = 0; r < p->world; ++r) out[r] = p->base[r] + off;
 }
 int32_t* ep_p2p_rcount(EpP2P* p) { return reinterpret_cast<int32_t*>(p->local + p->off_rcount); }
+int32_t* ep_p2p_allcount(EpP2P* p) { return reinterpret_cast<int32_t*>(p->local + p->off_allcount); }
 uint32_t ep_p2p_begin(EpP2P* p) { return ++p->epoch; }
 
 aristos_status_t ep_p2p_push(EpP2P* p, int which, const void* send_buf, int blocks_per_peer, size_t block_stride,
@@ -261,16 +269,19 @@ const uint32_t* ep_p2p_flags(const EpP2P* p, int kind, int window) {
 }
 uint32_t ep_p2p_epoch(const EpP2P* p) { return p->epoch; }
 
-aristos_status_t ep_p2p_send_counts(EpP2P* p, const int32_t* count, int E, int E_local, cudaStream_t stream) {
-    if (!p || !count || E_local <= 0 || E != E_local * p->world) return ARISTOS_ERR_INVALID_ARG;
+aristos_status_t ep_p2p_send_counts(EpP2P* p, const int32_t* count, int E, int E_local, cudaStream_t stream,
+                                    bool to_all) {
+    if (!p || !count || E_local <= 0 || E != E_local * p->world || E != p->groups) return ARISTOS_ERR_INVALID_ARG;
     FlagTargets t;
-    CountTargets c;
+    CountTargets c, all;
     t.n = p->world;
+    for (int d = 0; d < MAX_RANKS; ++d) all.ptr[d] = nullptr;
     for (int d = 0; d < p->world; ++d) {
         t.ptr[d] = reinterpret_cast<uint32_t*>(p->base[d]) + flag_index(p, EP_FLAG_COUNT, 0, p->rank);
         c.ptr[d] = reinterpret_cast<int32_t*>(p->base[d] + p->off_rcount);
+        if (to_all) all.ptr[d] = reinterpret_cast<int32_t*>(p->base[d] + p->off_allcount);
     }
-    ep_counts_kernel<<<1, 256, 0, stream>>>(count, E, E_local, p->rank, c, t, p->epoch);
+    ep_counts_kernel<<<1, 256, 0, stream>>>(count, E, E_local, p->rank, c, all, t, p->epoch);
     ARISTOS_COUNT_LAUNCH();
     ARISTOS_CUDA_TRY(cudaGetLastError());
     return ARISTOS_OK;

@@ -53,7 +53,10 @@ const uint32_t* ep_p2p_flags(const EpP2P* p, int kind, int window);
 uint32_t ep_p2p_epoch(const EpP2P* p);
 // One small kernel: count[e] of every expert goes into its owner's received-count list (entry rank * E_local +
 // e % E_local) and the EP_FLAG_COUNT flag (window 0) of this rank is raised at every rank.
-aristos_status_t ep_p2p_send_counts(EpP2P* p, const int32_t* count, int E, int E_local, cudaStream_t stream);
+// With to_all every rank also receives the whole list in its all-counts table (ep_p2p_allcount: entry src * E + e).
+aristos_status_t ep_p2p_send_counts(EpP2P* p, const int32_t* count, int E, int E_local, cudaStream_t stream,
+                                    bool to_all = false);
+int32_t* ep_p2p_allcount(EpP2P* p);
 // The flag page as plain words (host-side mirror of what the kernels and stream waits do; used by the release below
 // and by tests that run the protocol among CPU ranks).
 int ep_flag_words();

@@ -57,6 +57,11 @@ struct Fp8GemmParams {
     // ((peer_world * experts, rows_per_group, N), mapped into this process) as group peer_rank * experts + e
     int peer_world, peer_rank;
     __nv_bfloat16* peer_out[8];
+    // Dense groups (src_off != nullptr; groups == experts): group e holds the rows of every source rank back to back,
+    // source s in rows [src_off[e * (peer_world + 1) + s], src_off[... + s + 1]); row r of source s returns to rank s
+    // as row r - src_off[..s] of its group peer_rank * experts + e, whose groups have ret_rows rows.
+    const int32_t* src_off;
+    int ret_rows;
 };
 
 __device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
@@ -282,12 +287,22 @@ ffn_fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
             if (row_ok) {
                 __nv_bfloat16* obase = p.out;
                 int og = g;
-                if (p.peer_world > 0) {            // the store is the return all-to-all: straight into the source rank
+                int orows = p.rows_per_group, orow_idx = row;
+                if (p.peer_world > 0 && p.src_off != nullptr) {
+                    // dense group: find the source rank of this row, return it to that rank's own numbering
+                    const int32_t* off = p.src_off + g * (p.peer_world + 1);
+                    int src = 0;
+                    while (src + 1 < p.peer_world && row >= __ldg(off + src + 1)) ++src;
+                    obase = p.peer_out[src];
+                    og = p.peer_rank * p.experts + g;
+                    orows = p.ret_rows;
+                    orow_idx = row - __ldg(off + src);
+                } else if (p.peer_world > 0) {     // the store is the return all-to-all: straight into the source rank
                     const int src = g / p.experts;
                     obase = p.peer_out[src];
                     og = p.peer_rank * p.experts + (g - src * p.experts);
                 }
-                __nv_bfloat16* orow = obase + ((size_t)og * p.rows_per_group + row) * p.N + n0;
+                __nv_bfloat16* orow = obase + ((size_t)og * orows + orow_idx) * p.N + n0;
                 if (p.gated) {
                     // gate chunk half + 2 j pairs with up chunk half + 2 j + 4: 32 outputs each for j = 0, 1
 #pragma unroll
@@ -486,9 +501,11 @@ aristos_status_t expert_ffn_fp8_sm100(const void* xq, const float* sx, const int
                                       const void* w3q, const float* s3, const void* w2q, const float* s2, void* h,
                                       void* hq, float* sh, void* y, int H, int I, int hidden_act, int row_begin,
                                       int row_end, int sm_limit, int32_t* dev_status, cudaStream_t st,
-                                      void* const* peer_y, int peer_world, int peer_rank) {
-    if (peer_world > 8 || (peer_world > 0 && (!peer_y || groups != peer_world * experts))) {
-        set_last_error("expert_ffn(fp8): peer output needs world <= 8 and groups == world * experts");
+                                      void* const* peer_y, int peer_world, int peer_rank, const int32_t* dense_src_off,
+                                      int dense_ret_rows) {
+    const int want_groups = dense_src_off ? experts : peer_world * experts;
+    if (peer_world > 8 || (peer_world > 0 && (!peer_y || groups != want_groups)) || (dense_src_off && peer_world == 0)) {
+        set_last_error("expert_ffn(fp8): peer output needs world <= 8 and groups == world * experts (experts when dense)");
         return ARISTOS_ERR_INVALID_ARG;
     }
     if (groups > F8_MAX_GROUPS) { set_last_error("expert_ffn(fp8): more than %d row groups", F8_MAX_GROUPS); return ARISTOS_ERR_CONFIG; }
@@ -516,6 +533,8 @@ aristos_status_t expert_ffn_fp8_sm100(const void* xq, const float* sx, const int
     p.out = static_cast<__nv_bfloat16*>(y);
     p.peer_world = peer_world;
     p.peer_rank = peer_rank;
+    p.src_off = dense_src_off;
+    p.ret_rows = dense_ret_rows;
     for (int d = 0; d < peer_world; ++d) p.peer_out[d] = static_cast<__nv_bfloat16*>(peer_y[d]);
     ARISTOS_TRY(launch_fp8_gemm(hq, w2q, w2q, p, sm_limit, st));
     ARISTOS_CUDA_TRY(cudaGetLastError());

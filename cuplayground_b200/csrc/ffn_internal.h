@@ -40,7 +40,9 @@ aristos_status_t expert_ffn_fp8_sm100(const void* xq, const float* sx, const int
                                       const void* w3q, const float* s3, const void* w2q, const float* s2, void* h,
                                       void* hq, float* sh, void* y, int H, int I, int hidden_act, int row_begin,
                                       int row_end, int sm_limit, int32_t* dev_status, cudaStream_t st,
-                                      void* const* peer_y = nullptr, int peer_world = 0, int peer_rank = 0);
-// (the fp8 variant takes the peer output arguments directly)
+                                      void* const* peer_y = nullptr, int peer_world = 0, int peer_rank = 0,
+                                      const int32_t* dense_src_off = nullptr, int dense_ret_rows = 0);
+// (the fp8 variant takes the peer output arguments directly; dense_src_off != nullptr: one dense group per expert that
+// holds every source rank's rows, see dense_exchange_plan in ep_kernels.h)
 
 }  // namespace aristos

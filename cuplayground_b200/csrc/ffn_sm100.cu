@@ -383,7 +383,7 @@ ffn_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
-        if (lane == 0) {
+        if (ptx::elect_one()) {
             ptx::prefetch_tensormap(&tmA);
             ptx::prefetch_tensormap(&tmB0);
             ptx::prefetch_tensormap(&tmB1);
@@ -415,7 +415,7 @@ ffn_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         __syncwarp();
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
+        if (ptx::elect_one()) {
             constexpr uint32_t idesc = ptx::umma_idesc_f32acc(BM, BN, FMT == FMT_BF16 ? 1u : (FMT == FMT_F16 ? 0u : 2u));
             int stage = 0;
             uint32_t phase = 0;
@@ -555,7 +555,7 @@ ffn_grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gr
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer (both CTAs)
-        if (lane == 0) {
+        if (ptx::elect_one()) {
             ptx::prefetch_tensormap(&tmA);
             ptx::prefetch_tensormap(&tmB0);
             ptx::prefetch_tensormap(&tmB1);
@@ -587,7 +587,7 @@ ffn_grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gr
         __syncwarp();
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer (CTA 0 only)
-        if (lane == 0 && cta == 0) {
+        if (cta == 0 && ptx::elect_one()) {
             constexpr uint32_t idesc = ptx::umma_idesc_f32acc(PBM, BN, FMT == FMT_BF16 ? 1u : (FMT == FMT_F16 ? 0u : 2u));
             const uint32_t empty_peer = ptx::mapa_shared(bar_empty, 1);
             const uint32_t tfull_peer = ptx::mapa_shared(bar_tfull, 1);

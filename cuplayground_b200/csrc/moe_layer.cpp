@@ -71,6 +71,8 @@ struct aristos_moe {
     int direct_windows = 1;                  // row windows of the direct mode (gather / GEMMs / return pipelined)
     bool fused_return = false;               // direct mode: the down projection's epilogue stores into the source ranks
     bool kernel_wait = false;                // direct mode: the up projection waits for each source's rows itself
+    bool dense = false;                      // fp8 across ranks: received rows packed per expert across the sources
+    int32_t *send_base = nullptr, *dense_count = nullptr, *src_off = nullptr;
     int64_t launches = 0;
     const void *b1 = nullptr, *b3 = nullptr, *b2 = nullptr;   // optional expert biases (caller-owned, device)
     // failure handling of the exchange: every wait for a forward's completion has a wall-clock limit; on expiry the
@@ -87,7 +89,8 @@ struct aristos_moe {
     static constexpr int PROF_SETS = 64;      // ring of event sets: stage times average over the last 64 forwards
     bool profiling = false;
     int64_t prof_n = 0;
-    std::vector<cudaEvent_t> ev_prof;         // [PROF_SETS][5]
+    std::vector<cudaEvent_t> ev_prof;         // [PROF_SETS][6]: 5 stage boundaries + "rows sent" of the direct exchange
+    bool prof_sent = false;                   // this forward recorded event 5
 };
 
 namespace {
@@ -122,6 +125,11 @@ size_t plan_workspace(aristos_moe* L, char* base) {
     CARVE(topk_w, float*, S * k * 4)
     CARVE(count, int32_t*, E * 4)
     CARVE(rcount, int32_t*, (size_t)L->groups * 4)
+    if (L->dense) {
+        CARVE(send_base, int32_t*, E * 4)
+        CARVE(dense_count, int32_t*, (size_t)L->E_local * 4)
+        CARVE(src_off, int32_t*, (size_t)L->E_local * (L->world + 1) * 4)
+    }
     CARVE(slot_of, int32_t*, S * k * 4)
     CARVE(token_of_slot, int32_t*, E * cap * 4)
     CARVE(gate_bias, float*, E * 4)
@@ -327,6 +335,10 @@ aristos_status_t aristos_moe_create(const aristos_config_t* cfg, int rank, int w
                 // the tensor-core up projection waits for each source rank's rows itself (own rows first) instead
                 // of the stream waiting for every rank before the first tile; ARISTOS_EP_KERNEL_WAIT=0 keeps the
                 // stream waits
+                // fp8: the rows an expert receives from all ranks are packed into one group (whole tiles of one
+                // expert instead of one padded group per (source, expert)); ARISTOS_EP_DENSE=0 keeps the groups apart
+                const char* dn = getenv("ARISTOS_EP_DENSE");
+                L->dense = L->fp8 && L->fused_return && !(dn && !strcmp(dn, "0"));
                 const char* kw = getenv("ARISTOS_EP_KERNEL_WAIT");
                 L->kernel_wait = L->ep_direct && tc && !(kw && !strcmp(kw, "0"));
             }
@@ -419,7 +431,8 @@ static aristos_status_t forward_impl(aristos_moe_t* L, const void* x, const void
         bias = L->gate_bias;
     }
 
-    const int prof_set = (int)(L->prof_n % aristos_moe::PROF_SETS) * 5;
+    const int prof_set = (int)(L->prof_n % aristos_moe::PROF_SETS) * 6;
+    L->prof_sent = false;
 #define PROF_MARK(i) do { if (L->profiling) ARISTOS_CUDA_TRY(cudaEventRecord(L->ev_prof[prof_set + i], st)); } while (0)
     // NVTX ranges (host side: they bracket the enqueue of each stage, so a profiler timeline groups the stage's
     // launches; the reference links NVTX without calling it, CMakeLists.txt:104-118)
@@ -483,7 +496,32 @@ static aristos_status_t forward_impl(aristos_moe_t* L, const void* x, const void
         ep_p2p_begin(L->p2p);
         *exchange_started = true;
         stage.next("exchange");
+        if (L->dense) {
+            // every rank learns every rank's counts first (one small kernel + flag), then knows where its rows start
+            // inside each expert's dense group at the owner
+            ARISTOS_TRY(ep_p2p_send_counts(L->p2p, L->count, L->E, L->E_local, st, /*to_all=*/true));
+        }
         ARISTOS_TRY(aristos_quantize_fp8(x, 1, L->S, L->H, 1, ARISTOS_DTYPE_BF16, L->xq, L->sx, stream));
+        if (L->dense) {
+            const int dense_rows = L->world * L->cap;          // rows of one expert's group: all sources, worst case
+            ARISTOS_TRY(ep_p2p_wait(L->p2p, EP_FLAG_COUNT, 0, st));
+            ARISTOS_TRY(dense_exchange_plan(ep_p2p_allcount(L->p2p), L->world, L->E, L->E_local, L->rank, L->send_base,
+                                            L->dense_count, L->src_off, st));
+            ARISTOS_TRY(permute_rows_to_peers(L->xq, L->slot_of, L->S, L->k, (size_t)L->H, L->E_local, L->cap, L->rank, 0,
+                                              L->cap, rows_dst, st, nullptr, 0, nullptr, L->send_base, dense_rows));
+            ARISTOS_TRY(permute_rows_to_peers(L->sx, L->slot_of, L->S, L->k, (size_t)(L->H / 128) * 4, L->E_local, L->cap,
+                                              L->rank, 0, L->cap, scales_dst, st, nullptr, 0, nullptr, L->send_base,
+                                              dense_rows));
+            ARISTOS_TRY(ep_p2p_signal(L->p2p, EP_FLAG_IN, 0, st));
+            PROF_MARK(2);
+            ARISTOS_TRY(ep_p2p_wait(L->p2p, EP_FLAG_IN, 0, st));
+            stage.next("expert_ffn");
+            if (swiglu && !w3) { set_last_error("forward: SwiGLU needs w3"); return ARISTOS_ERR_INVALID_ARG; }
+            ARISTOS_TRY(expert_ffn_fp8_sm100(L->xgq, L->sxg, L->dense_count, L->E_local, dense_rows, L->E_local, w1, s1, w3,
+                                             s3, w2, s2, L->h, L->hq, L->sh, L->yr, L->H, L->I, L->cfg.hidden_act, 0,
+                                             dense_rows, 0, L->dev_status, st, y_dst.p, L->world, L->rank, L->src_off,
+                                             L->cap));
+        } else {
         PeerPtrs count_dst;
         ep_p2p_peer_ptrs(L->p2p, EP_BUF_RCOUNT, count_dst.p);
         ARISTOS_TRY(permute_rows_to_peers(L->xq, L->slot_of, L->S, L->k, (size_t)L->H, L->E_local, L->cap, L->rank, 0,
@@ -506,6 +544,7 @@ static aristos_status_t forward_impl(aristos_moe_t* L, const void* x, const void
                                                L->cap, 0, L->dev_status, st));
             ARISTOS_TRY(return_rows_to_peers(L->yr, L->rcount, L->groups, L->E_local, L->cap, (size_t)L->H * 2, L->rank,
                                              0, L->cap, y_dst, st));
+        }
         }
         ARISTOS_TRY(ep_p2p_signal(L->p2p, EP_FLAG_RET, 0, st));
         ARISTOS_TRY(ep_p2p_wait(L->p2p, EP_FLAG_RET, 0, st));
@@ -550,6 +589,10 @@ static aristos_status_t forward_impl(aristos_moe_t* L, const void* x, const void
             ARISTOS_TRY(permute_rows_to_peers(x, L->slot_of, L->S, L->k, row_bytes, L->E_local, L->cap, L->rank, r0, r1,
                                               rows_dst, cs));
             ARISTOS_TRY(ep_p2p_signal(L->p2p, EP_FLAG_IN, c, cs));
+        }
+        if (L->profiling) {          // "rows sent": the gather kernels and their flags are behind this event
+            ARISTOS_CUDA_TRY(cudaEventRecord(L->ev_prof[prof_set + 5], cs));
+            L->prof_sent = true;
         }
         ARISTOS_TRY(ep_p2p_wait(L->p2p, EP_FLAG_COUNT, 0, st));
         const bool tc = dt == ARISTOS_DTYPE_BF16 || dt == ARISTOS_DTYPE_F16 || dt == ARISTOS_DTYPE_TF32;
@@ -660,6 +703,7 @@ static aristos_status_t forward_impl(aristos_moe_t* L, const void* x, const void
     stage.next("combine");
     ARISTOS_TRY(aristos_combine(L->yg, L->slot_of, L->topk_w, L->S, L->k, L->H, dt, out, st));
     PROF_MARK(4);
+    if (L->profiling && !L->prof_sent) ARISTOS_CUDA_TRY(cudaEventRecord(L->ev_prof[prof_set + 5], st));
 #undef PROF_MARK
     if (L->profiling) L->prof_n += 1;
     L->launches += launch_counter() - launches0;
@@ -773,7 +817,7 @@ aristos_status_t aristos_moe_status(aristos_moe_t* L) {
 aristos_status_t aristos_moe_set_profiling(aristos_moe_t* L, int enable) {
     if (!L) return ARISTOS_ERR_INVALID_ARG;
     if (enable && L->ev_prof.empty()) {
-        L->ev_prof.assign(aristos_moe::PROF_SETS * 5, nullptr);
+        L->ev_prof.assign(aristos_moe::PROF_SETS * 6, nullptr);
         for (cudaEvent_t& e : L->ev_prof) ARISTOS_CUDA_TRY(cudaEventCreate(&e));
     }
     L->profiling = enable != 0;
@@ -787,7 +831,7 @@ aristos_status_t aristos_moe_stage_ms(aristos_moe_t* L, float out_ms[5]) {
     const int n = (int)std::min<int64_t>(L->prof_n, aristos_moe::PROF_SETS);
     double acc[5] = {0, 0, 0, 0, 0};
     for (int j = 0; j < n; ++j) {
-        const int set = (int)((L->prof_n - 1 - j) % aristos_moe::PROF_SETS) * 5;
+        const int set = (int)((L->prof_n - 1 - j) % aristos_moe::PROF_SETS) * 6;
         ARISTOS_CUDA_TRY(cudaEventSynchronize(L->ev_prof[set + 4]));
         for (int i = 0; i < 5; ++i) {
             float ms = 0.0f;
@@ -796,6 +840,25 @@ aristos_status_t aristos_moe_stage_ms(aristos_moe_t* L, float out_ms[5]) {
         }
     }
     for (int i = 0; i < 5; ++i) out_ms[i] = (float)(acc[i] / n);
+    return ARISTOS_OK;
+}
+
+aristos_status_t aristos_moe_exchange_ms(aristos_moe_t* L, float* sent_ms) {
+    if (!L || !sent_ms) return ARISTOS_ERR_INVALID_ARG;
+    if (L->prof_n == 0) { set_last_error("exchange_ms: no forward has run since profiling was switched on"); return ARISTOS_ERR_INVALID_ARG; }
+    *sent_ms = 0.0f;
+    if (!(L->p2p && L->ep_direct) || L->fp8) return ARISTOS_OK;      // only the direct bf16 / fp16 / tf32 exchange marks it
+    const int n = (int)std::min<int64_t>(L->prof_n, aristos_moe::PROF_SETS);
+    double acc = 0;
+    for (int j = 0; j < n; ++j) {
+        const int set = (int)((L->prof_n - 1 - j) % aristos_moe::PROF_SETS) * 6;
+        ARISTOS_CUDA_TRY(cudaEventSynchronize(L->ev_prof[set + 4]));
+        ARISTOS_CUDA_TRY(cudaEventSynchronize(L->ev_prof[set + 5]));
+        float ms = 0.0f;
+        ARISTOS_CUDA_TRY(cudaEventElapsedTime(&ms, L->ev_prof[set + 2], L->ev_prof[set + 5]));
+        acc += ms;
+    }
+    *sent_ms = (float)(acc / n);
     return ARISTOS_OK;
 }
 
@@ -817,6 +880,21 @@ aristos_status_t aristos_moe_training_state(const aristos_moe_t* L, aristos_trai
     if (!L->cfg.is_training) { set_last_error("training_state: the layer was created with is_training = 0"); return ARISTOS_ERR_CONFIG; }
     if (!L->train_last.topk_idx) { set_last_error("training_state: no forward has run yet"); return ARISTOS_ERR_INVALID_ARG; }
     *out = L->train_last;
+    return ARISTOS_OK;
+}
+
+aristos_status_t aristos_moe_training_state_to_host(const aristos_moe_t* L, int32_t* topk_idx_host, float* topk_w_host,
+                                                    int32_t* slot_of_host, float* load_balance_host) {
+    aristos_training_state_t ts;
+    ARISTOS_TRY(aristos_moe_training_state(L, &ts));
+    if (L->world > 1 && L->ev_last_valid) ARISTOS_TRY(wait_event_bounded(const_cast<aristos_moe_t*>(L), L->ev_last));
+    ARISTOS_CUDA_TRY(cudaDeviceSynchronize());
+    const size_t sk = (size_t)ts.tokens * ts.top_k * 4;
+    if (topk_idx_host) ARISTOS_CUDA_TRY(cudaMemcpy(topk_idx_host, ts.topk_idx, sk, cudaMemcpyDeviceToHost));
+    if (topk_w_host) ARISTOS_CUDA_TRY(cudaMemcpy(topk_w_host, ts.topk_w, sk, cudaMemcpyDeviceToHost));
+    if (slot_of_host) ARISTOS_CUDA_TRY(cudaMemcpy(slot_of_host, ts.slot_of, sk, cudaMemcpyDeviceToHost));
+    if (load_balance_host)
+        ARISTOS_CUDA_TRY(cudaMemcpy(load_balance_host, ts.load_balance, (size_t)(2 * ts.num_experts + 2) * 4, cudaMemcpyDeviceToHost));
     return ARISTOS_OK;
 }
 

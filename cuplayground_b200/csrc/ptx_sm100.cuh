@@ -23,6 +23,22 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
     return t;
 }
 
+// One lane of the (converged) warp, chosen by the hardware. Unlike `lane == 0`, the compiler knows that exactly one
+// lane takes the branch and that everything computed from warp-uniform values stays uniform inside it, so the
+// descriptors of the TMA and MMA instructions issued there are built on the uniform datapath instead of being moved
+// over from per-thread registers before every instruction.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred P;\n\t"
+        "elect.sync _|P, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, P;\n\t"
+        "}"
+        : "=r"(pred));
+    return pred != 0;
+}
+
 // ---- mbarrier ---------------------------------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");

@@ -305,6 +305,12 @@ class MoELayer:
         _lib.check(self._lib.aristos_moe_stage_ms(self._h, ms))
         return dict(gate=ms[0], dispatch=ms[1], ffn=ms[2], combine=ms[3], total=ms[4])
 
+    def exchange_ms(self) -> float:
+        """Milliseconds of the outgoing exchange (counts + gather into the peers + flags) of the last forwards."""
+        ms = C.c_float(0.0)
+        _lib.check(self._lib.aristos_moe_exchange_ms(self._h, C.byref(ms)))
+        return float(ms.value)
+
     def status(self) -> None:
         _lib.check(self._lib.aristos_moe_status(self._h))
 
@@ -313,21 +319,14 @@ class MoELayer:
         load-balance statistics (frac, prob per expert; aux loss; dropped share)."""
         ts = _lib.AristosTrainingStateStruct()
         _lib.check(self._lib.aristos_moe_training_state(self._h, C.byref(ts)))
-        torch.cuda.synchronize()
         S, k, E = ts.tokens, ts.top_k, ts.num_experts
-
-        def host(ptr, n, dtype):
-            t = torch.empty(n, dtype=dtype)
-            torch.cuda.current_stream().synchronize()
-            rc = torch.cuda.cudart().cudaMemcpy(t.data_ptr(), ptr, n * 4, 2)      # cudaMemcpyDeviceToHost
-            if int(rc) != 0:
-                raise RuntimeError(f"cudaMemcpy failed with {int(rc)}")
-            return t
-        lb = host(ts.load_balance, 2 * E + 2, torch.float32)
-        return dict(topk_idx=host(ts.topk_idx, S * k, torch.int32).view(S, k),
-                    topk_w=host(ts.topk_w, S * k, torch.float32).view(S, k),
-                    slot_of=host(ts.slot_of, S * k, torch.int32).view(S, k),
-                    frac=lb[:E], prob=lb[E:2 * E], aux=float(lb[2 * E]), dropped=float(lb[2 * E + 1]),
+        idx = torch.empty((S, k), dtype=torch.int32)
+        w = torch.empty((S, k), dtype=torch.float32)
+        slot = torch.empty((S, k), dtype=torch.int32)
+        lb = torch.empty(2 * E + 2, dtype=torch.float32)
+        _lib.check(self._lib.aristos_moe_training_state_to_host(self._h, _ptr(idx), _ptr(w), _ptr(slot), _ptr(lb)))
+        return dict(topk_idx=idx, topk_w=w, slot_of=slot, frac=lb[:E], prob=lb[E:2 * E], aux=float(lb[2 * E]),
+                    dropped=float(lb[2 * E + 1]),
                     device_ptrs=(ts.topk_idx, ts.topk_w, ts.slot_of, ts.load_balance))
 
     def set_training_buffer(self, buf: Optional[torch.Tensor]) -> None:

@@ -95,6 +95,16 @@ public:
         check(aristos_moe_stage_ms(h_, ms));
         return StageMs{ms[0], ms[1], ms[2], ms[3], ms[4]};
     }
+    // Expert-parallel layers: wall-clock limit of status() / destruction when a peer stops taking part.
+    void set_timeout_ms(int ms) { check(aristos_moe_set_timeout_ms(h_, ms)); }
+    // is_training = 1: what the last forward saved (device pointers), and where the next forwards save.
+    aristos_training_state_t training_state() const {
+        aristos_training_state_t t;
+        check(aristos_moe_training_state(h_, &t));
+        return t;
+    }
+    size_t training_bytes() const { return aristos_moe_training_bytes(h_); }
+    void set_training_buffer(void* device_ptr, size_t bytes) { check(aristos_moe_set_training_buffer(h_, device_ptr, bytes)); }
     const char* ep_transport() const { return aristos_moe_ep_transport(h_); }
     long long launch_count() const { return aristos_moe_launch_count(h_); }
     aristos_moe_t* raw() noexcept { return h_; }

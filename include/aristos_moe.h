@@ -209,6 +209,10 @@ typedef struct aristos_training_state {
 ARISTOS_API size_t aristos_moe_training_bytes(const aristos_moe_t* layer);
 ARISTOS_API aristos_status_t aristos_moe_set_training_buffer(aristos_moe_t* layer, void* device_buffer, size_t bytes);
 ARISTOS_API aristos_status_t aristos_moe_training_state(const aristos_moe_t* layer, aristos_training_state_t* out);
+/* Host copies of that state (any pointer may be NULL; load_balance_host: 2 * num_experts + 2 floats); synchronises. */
+ARISTOS_API aristos_status_t aristos_moe_training_state_to_host(const aristos_moe_t* layer, int32_t* topk_idx_host,
+                                                                float* topk_w_host, int32_t* slot_of_host,
+                                                                float* load_balance_host);
 ARISTOS_API size_t aristos_load_balance_stats_bytes(int E);
 ARISTOS_API aristos_status_t aristos_load_balance_stats(const int32_t* topk_idx, const float* topk_w,
                                                         const int32_t* slot_of, int S, int k, int E, float* stats,
@@ -222,6 +226,10 @@ ARISTOS_API aristos_status_t aristos_moe_set_timeout_ms(aristos_moe_t* layer, in
  * {gate, dispatch + gather, expert FFN (with the exchanges when world > 1), combine, whole forward}. */
 ARISTOS_API aristos_status_t aristos_moe_set_profiling(aristos_moe_t* layer, int enable);
 ARISTOS_API aristos_status_t aristos_moe_stage_ms(aristos_moe_t* layer, float out_ms[5]);
+/* Expert-parallel peer-memory layers (16-bit / tf32): milliseconds from the end of the dispatch bookkeeping until this
+ * rank's count and gather kernels have stored its rows into the owning ranks and raised their flags (the part of the
+ * "expert FFN" stage that is the outgoing exchange), averaged like aristos_moe_stage_ms; 0 for other layers. */
+ARISTOS_API aristos_status_t aristos_moe_exchange_ms(aristos_moe_t* layer, float* sent_ms);
 /* How the rows of an expert-parallel layer travel: "p2p" (the default: kernels store through the peers' CUDA-IPC
  * mapped exchange buffers over NVLink - the gather kernel writes every kept token row into the rank that owns its
  * expert, the down projection's epilogue writes every output tile into the rank the rows came from -, arrival is

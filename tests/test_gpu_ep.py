@@ -104,9 +104,10 @@ def test_expert_parallel_4gpu(transport):
     _run(4, S=1024, H=256, I=256, E=8, k=2, cf=1.0, act=0, transport=transport)
 
 
-def _worker_fp8(rank, world, uid, S, H, I, E, k, q):
+def _worker_fp8(rank, world, uid, S, H, I, E, k, q, dense="1"):
     try:
         os.environ["ARISTOS_EP_TRANSPORT"] = "p2p"
+        os.environ["ARISTOS_EP_DENSE"] = dense
         sys.path.insert(0, ROOT)
         sys.path.insert(0, os.path.join(ROOT, "tests"))
         import torch
@@ -154,10 +155,11 @@ def _worker_fp8(rank, world, uid, S, H, I, E, k, q):
         q.put((rank, "".join(traceback.format_exception(e))))
 
 
-@pytest.mark.parametrize("world", [2, 4])
-def test_expert_parallel_fp8(world):
+@pytest.mark.parametrize("world,dense", [(2, "1"), (2, "0"), (4, "1")])
+def test_expert_parallel_fp8(world, dense):
     """FP8 layer across ranks: the gather stores quantised rows and scales straight into the owning rank's memory,
-    outputs return row by row; drop-free routing (capacity = tokens), top-4 sigmoid gate."""
+    outputs return row by row; drop-free routing (capacity = tokens), top-4 sigmoid gate. dense = "1": the rows an
+    expert receives from all ranks are packed into one row group (the default); "0": one group per (source, expert)."""
     import torch
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
@@ -166,7 +168,7 @@ def test_expert_parallel_fp8(world):
     uid = layer.nccl_unique_id()
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    procs = [ctx.Process(target=_worker_fp8, args=(r, world, uid, 640, 512, 256, 16, 4, q)) for r in range(world)]
+    procs = [ctx.Process(target=_worker_fp8, args=(r, world, uid, 640, 512, 256, 16, 4, q, dense)) for r in range(world)]
     for p in procs:
         p.start()
     results = []
