@@ -152,7 +152,7 @@ ffn_fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
-        if (lane == 0) {
+        if (ptx::elect_one()) {
             ptx::prefetch_tensormap(&tmA);
             ptx::prefetch_tensormap(&tmB0);
             ptx::prefetch_tensormap(&tmB1);
@@ -188,7 +188,7 @@ ffn_fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
         // Issuing the four MMAs and the commit of one K block costs the issuing thread more cycles than the tensor
         // core needs to run them, so two warps take turns: K block number it goes to warp it % 2 and to TMEM buffer
         // it % 2 (each thread's commit covers its own MMAs only).
-        if (lane == 0) {
+        if (ptx::elect_one()) {
             constexpr uint32_t idesc = umma_idesc_e4m3(F8_BM, F8_BN);
             const int me = warp == 1 ? 0 : 1;
             int it = 0;

@@ -19,6 +19,10 @@ struct FfnEpArgs {
     const uint32_t* src_flags = nullptr;
     uint32_t flag_epoch = 0;
     uint32_t flag_limit_ms = 0;
+    // Counter scratch (device, groups * ceil(rows / 128) int32): with it, small row groups run the up and the down
+    // projection as ONE persistent launch whose down tiles wait for the up tiles of their row tile.
+    int32_t* updown_scratch = nullptr;
+    size_t updown_scratch_ints = 0;
 };
 
 // bf16 / fp16 / tf32 on the tensor cores (fmt 0 / 1 / 2).

@@ -490,6 +490,222 @@ ffn_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     }
 }
 
+// ---- up and down projection in one persistent launch ------------------------------------------------------------------
+// For small row groups (many experts, a few row tiles each) the two projections of a layer are one launch: the tile list
+// is every up-projection tile followed by every down-projection tile, and a down tile of (group, row tile) becomes
+// ready when all the up-projection column tiles of that row tile have stored their part of h - the dependency the
+// reference's schedulers model with per-row-tile queues of second-GEMM tasks (auditorium/scheduling.cuh:212-216,
+// warpScheduler.cuh:280-285: "sTB" tasks appear when a row of "fTB" tiles is complete). Here the epilogue of an up tile
+// counts itself into done[group][row tile] once its TMA stores have completed, and the producer of a down tile waits
+// (bounded) until the count has reached the number of up column tiles. Every CTA walks its tiles in order and all up
+// tiles precede all down tiles, so no up tile ever waits behind a down tile: the wait cannot deadlock. There is no
+// drain between the projections, the tail of the up projection overlaps the head of the down projection, and h is
+// read back while it is still in L2.
+__device__ __forceinline__ TileCoord decode_phase_tile(const FfnGemmParams& p, const int* rt_prefix, int& vg, int t,
+                                                       int n_tiles, int out_w) {
+    // t counts the tiles of one projection: groups in walking order, inside a group the row tile runs fastest
+    while (t >= rt_prefix[vg + 1] * n_tiles) ++vg;
+    TileCoord c;
+    c.g = ordered_group(vg, p.groups, p.experts, p.first_source);
+    const int local = t - rt_prefix[vg] * n_tiles;
+    const int mt = rt_prefix[vg + 1] - rt_prefix[vg];
+    c.m0 = p.row_begin + (local % mt) * BM;
+    c.n0 = (local / mt) * out_w;
+    return c;
+}
+
+template <int FMT, bool BIAS, bool PEERS>
+__global__ void __launch_bounds__(FFN_THREADS, 1)
+ffn_updown_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmB00,
+                  const __grid_constant__ CUtensorMap tmB01, const __grid_constant__ CUtensorMap tmOut0,
+                  const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmB1,
+                  const __grid_constant__ CUtensorMap tmOut1, const __grid_constant__ PeerMapsArg<PEERS> peers,
+                  const FfnGemmParams p0, const FfnGemmParams p1, int32_t* __restrict__ done, int max_row_tiles) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const uint32_t staging = ptx::smem_u32(smem + STAGES * STAGE_BYTES);
+    uint8_t* aux = smem + STAGES * STAGE_BYTES + STAGING_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(aux);             // full[S], empty[S], tfull[2], tempty[2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aux + 128);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(aux + 132);
+    int* rt_prefix = reinterpret_cast<int*>(aux + 256);            // [groups + 1] row tiles before group g
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t bar_full = ptx::smem_u32(bars);
+    const uint32_t bar_empty = bar_full + 8 * STAGES;
+    const uint32_t bar_tfull = bar_empty + 8 * STAGES;
+    const uint32_t bar_tempty = bar_tfull + 16;
+    const uint32_t smem_base = ptx::smem_u32(smem);
+
+    const int out_w0 = p0.gated ? 128 : 256;
+    const int nt0 = (p0.N + out_w0 - 1) / out_w0;
+    const int nt1 = (p1.N + 255) / 256;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            ptx::mbar_init(bar_full + 8 * s, 1);
+            ptx::mbar_init(bar_empty + 8 * s, 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            ptx::mbar_init(bar_tfull + 8 * b, 1);
+            ptx::mbar_init(bar_tempty + 8 * b, EPI_THREADS);
+        }
+        *abort_flag = 0;
+        ptx::fence_mbar_init();
+    }
+    if (warp == 0) {
+        build_tile_prefix<BM>(p0, rt_prefix, 1, lane);          // n_tiles = 1: a prefix over row tiles
+    } else if (warp == 1) {
+        ptx::tmem_alloc(ptx::smem_u32(tmem_slot), TMEM_COLS);
+    }
+    ptx::tcgen05_fence_before();
+    __syncthreads();
+    ptx::tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const int row_tiles = rt_prefix[p0.groups];
+    const int T0 = row_tiles * nt0, total_tiles = T0 + row_tiles * nt1;
+    constexpr int bke = FMT == FMT_TF32 ? BK / 2 : BK;
+    const int kblocks0 = p0.K / bke, kblocks1 = p1.K / bke;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (ptx::elect_one()) {
+            ptx::prefetch_tensormap(&tmA0);
+            ptx::prefetch_tensormap(&tmB00);
+            ptx::prefetch_tensormap(&tmB01);
+            ptx::prefetch_tensormap(&tmA1);
+            ptx::prefetch_tensormap(&tmB1);
+            int stage = 0;
+            uint32_t phase = 0;
+            int vg0 = 0, vg1 = 0;
+            uint32_t seen = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+                const bool down = tile >= T0;
+                const TileCoord t = down ? decode_phase_tile(p1, rt_prefix, vg1, tile - T0, nt1, 256)
+                                         : decode_phase_tile(p0, rt_prefix, vg0, tile, nt0, out_w0);
+                const int g = t.g, m0 = t.m0, n0 = t.n0;
+                const int e = g % p0.experts;
+                const CUtensorMap *mA, *mB0, *mB1;
+                int n1, kblocks;
+                if (down) {
+                    // every up-projection column tile of this row tile must have stored its part of h
+                    const int rt = (m0 - p1.row_begin) / BM;
+                    ok = ptx::flag_wait_bounded(reinterpret_cast<const uint32_t*>(done + g * max_row_tiles + rt),
+                                                (uint32_t)nt0, abort_flag, p1.dev_status);
+                    if (!ok) break;
+                    mA = &tmA1; mB0 = &tmB1; mB1 = &tmB1; n1 = n0 + 128; kblocks = kblocks1;
+                } else {
+                    ok = wait_source_rows(p0, g, seen, abort_flag);
+                    if (!ok) break;
+                    mA = &tmA0; mB0 = &tmB00; mB1 = &tmB01; n1 = p0.gated ? n0 : n0 + 128; kblocks = kblocks0;
+                }
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    ok = ptx::mbar_wait_bounded(bar_empty + 8 * stage, phase ^ 1u, abort_flag, p0.dev_status);
+                    if (!ok) break;
+                    const uint32_t full = bar_full + 8 * stage;
+                    const uint32_t sa = smem_base + stage * STAGE_BYTES;
+                    ptx::mbar_arrive_expect_tx(full, STAGE_BYTES);
+                    ptx::tma_load_3d(sa, mA, kb * bke, m0, g, full);
+                    ptx::tma_load_3d(sa + A_STAGE_BYTES, mB0, kb * bke, n0, e, full);
+                    ptx::tma_load_3d(sa + A_STAGE_BYTES + B_HALF_BYTES, mB1, kb * bke, n1, e, full);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (ptx::elect_one()) {
+            constexpr uint32_t idesc = ptx::umma_idesc_f32acc(BM, BN, FMT == FMT_BF16 ? 1u : (FMT == FMT_F16 ? 0u : 2u));
+            int stage = 0;
+            uint32_t phase = 0;
+            int it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
+                const int kblocks = tile >= T0 ? kblocks1 : kblocks0;
+                const int buf = it & 1;
+                const uint32_t aphase = (it >> 1) & 1u;
+                ok = ptx::mbar_wait_bounded(bar_tempty + 8 * buf, aphase ^ 1u, abort_flag, p0.dev_status);
+                if (!ok) break;
+                ptx::tcgen05_fence_after();
+                const uint32_t tmem_d = tmem_base + buf * BN;
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    ok = ptx::mbar_wait_bounded(bar_full + 8 * stage, phase, abort_flag, p0.dev_status);
+                    if (!ok) break;
+                    ptx::tcgen05_fence_after();
+                    const uint32_t sa = smem_base + stage * STAGE_BYTES;
+                    const uint64_t da = ptx::umma_desc_k_sw128(sa);
+                    const uint64_t db = ptx::umma_desc_k_sw128(sa + A_STAGE_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        if constexpr (FMT == FMT_TF32) ptx::umma_tf32(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                        else ptx::umma_f16(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                    }
+                    ptx::umma_commit(bar_empty + 8 * stage);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+                if (ok) ptx::umma_commit(bar_tfull + 8 * buf);
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------------ epilogue (warps 2..5)
+        const int quarter = warp & 3;
+        const int row_in_tile = quarter * 32 + lane;
+        const int epi_tid = threadIdx.x - 64;
+        int vg0 = 0, vg1 = 0;
+        int it = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
+            const bool down = tile >= T0;
+            const TileCoord t = down ? decode_phase_tile(p1, rt_prefix, vg1, tile - T0, nt1, 256)
+                                     : decode_phase_tile(p0, rt_prefix, vg0, tile, nt0, out_w0);
+            const int g = t.g, m0 = t.m0, n0 = t.n0;
+            const int buf = it & 1;
+            const uint32_t aphase = (it >> 1) & 1u;
+            ok = ptx::mbar_wait_bounded(bar_tfull + 8 * buf, aphase, abort_flag, p0.dev_status);
+            ok = !ptx::named_barrier_or(2, EPI_THREADS, !ok);
+            if (!ok) break;
+            ptx::tcgen05_fence_after();
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
+            if (!down) {
+                if constexpr (FMT == FMT_TF32)
+                    epilogue_tile_f32<false, BIAS>(p0, &tmOut0, g, g, m0, n0, row_in_tile, taddr, bar_tempty + 8 * buf, lane, epi_tid, staging);
+                else
+                    epilogue_tile<false, FMT, BIAS>(p0, &tmOut0, g, g, m0, n0, row_in_tile, taddr, bar_tempty + 8 * buf, lane, epi_tid, staging);
+                // this tile's part of h is complete in global memory: count it for the down projection's producers
+                if (epi_tid == 0) {
+                    ptx::bulk_wait_group0();
+                    asm volatile("fence.proxy.async;" ::: "memory");
+                    __threadfence();
+                    atomicAdd(done + g * max_row_tiles + (m0 - p0.row_begin) / BM, 1);
+                }
+            } else {
+                const CUtensorMap* om = &tmOut1;
+                int og = g;
+                if constexpr (PEERS) {
+                    const int src = g / p1.experts;
+                    om = &peers.m[src];
+                    og = p1.peer_rank * p1.experts + (g - src * p1.experts);
+                }
+                if constexpr (FMT == FMT_TF32)
+                    epilogue_tile_f32<false, BIAS>(p1, om, og, g, m0, n0, row_in_tile, taddr, bar_tempty + 8 * buf, lane, epi_tid, staging);
+                else
+                    epilogue_tile<false, FMT, BIAS>(p1, om, og, g, m0, n0, row_in_tile, taddr, bar_tempty + 8 * buf, lane, epi_tid, staging);
+            }
+        }
+        if (epi_tid == 0) ptx::bulk_wait_group0();
+    }
+
+    ptx::tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tcgen05_fence_after();
+        ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
 // ---- CTA-pair variant --------------------------------------------------------------------------------------------------
 // Two CTAs on the two SMs of a TPC work on one 256 x 256 tile with tcgen05 cta_group::2: each CTA stages its own 128
 // rows of A and its own 128 rows of B (for SwiGLU: CTA 0 the W1 rows, CTA 1 the W3 rows), the first CTA's MMA thread
@@ -677,13 +893,15 @@ aristos_status_t make_map_3d(CUtensorMap* tm, const void* base, int K, int rows,
 }
 
 // Tile shapes. A single-CTA 128 x 256 tile stages 48 KB per 64-wide K block and is bound by the bandwidth that feeds
-// the operands to the SM; a CTA pair (cta_group::2, 256 x 256 tile) stages 32 KB per SM for the same work. The pair
-// kernel computes whole 256-row tiles only and the single-CTA kernel finishes the < 256 remaining rows of every
-// group in a second launch, so pairing never pads a group by more than the 128-row tile does.
-//   TILES_AUTO    pairs (+ single-CTA tail) where the row window holds at least 1024 rows, else single-CTA tiles
+// the operands to the SM (tensor pipe 86-91 % active); a CTA pair (cta_group::2, 256 x 256 tile) stages 32 KB per SM
+// for the same work (98-99 %). Pairs pad every group to whole 256-row tiles (128 wasted rows per group on average).
+// The alternative - the pair kernel computes whole tiles only and a second, single-CTA launch finishes the < 256
+// remaining rows of every group - wastes half as many rows but its few tiles fill their waves poorly: measured on
+// 8 groups of about 4096 rows, the tail launches took 0.55 ms for 3 % of the rows where padding costs 0.25 ms.
+//   TILES_AUTO    padded pairs where the row window holds at least 1024 rows, else single-CTA tiles
 //   TILES_SINGLE  single-CTA tiles only
-//   TILES_PAIR    pairs (+ tail) for every window
-//   TILES_PAIR_PADDED  pairs only, every group padded to whole 256-row tiles
+//   TILES_PAIR    pairs + single-CTA tail launch, for every window
+//   TILES_PAIR_PADDED  padded pairs for every window
 enum { TILES_AUTO = 0, TILES_SINGLE = 1, TILES_PAIR = 2, TILES_PAIR_PADDED = 3 };
 int g_tile_mode = -1;      // -1: not yet read from the environment
 int g_band_rows = -1;
@@ -757,21 +975,22 @@ aristos_status_t launch_gemm_t(const void* A, const void* B0, const void* B1, Ff
     const int band_rows = band_rows_for(window, p.K, FMT == FMT_TF32 ? 4 : 2);
     const int mode = tile_mode();
     const bool pairs = mode == TILES_PAIR || mode == TILES_PAIR_PADDED || (mode == TILES_AUTO && window >= 1024);
+    const bool padded = mode != TILES_PAIR;
     if (pairs) {
         int max_clusters = 0;
         ARISTOS_TRY((max_pair_clusters<FMT, BIAS, PEERS>(&max_clusters)));
         const int64_t bound = (int64_t)p.groups * ceil_div(window, PBM) * ceil_div(p.N, out_w);
         int npairs = sms / 2 < max_clusters ? sms / 2 : max_clusters;
         if (bound < npairs) npairs = (int)bound;
-        p.rows_mode = mode == TILES_PAIR_PADDED ? ROWS_ALL : ROWS_FULL_PAIRS;
+        p.rows_mode = padded ? ROWS_ALL : ROWS_FULL_PAIRS;
         p.band = band_rows / PBM;
-        if (npairs > 0 && (mode == TILES_PAIR_PADDED || window >= PBM)) {
+        if (npairs > 0 && (padded || window >= PBM)) {
             ffn_grouped_gemm_pair_kernel<FMT, BIAS, PEERS><<<2 * npairs, FFN_THREADS, P_SMEM_BYTES, st>>>(
                 tmA, tmB0, tmB1, tmOut, pm, p);
             ARISTOS_COUNT_LAUNCH();
             ARISTOS_CUDA_TRY(cudaGetLastError());
         }
-        if (mode == TILES_PAIR_PADDED) return ARISTOS_OK;
+        if (padded) return ARISTOS_OK;
         p.rows_mode = ROWS_TAIL;     // the single-CTA kernel below finishes every group's last < 256 rows
     }
     auto kernel = ffn_grouped_gemm_kernel<FMT, BIAS, PEERS>;
@@ -788,6 +1007,56 @@ aristos_status_t launch_gemm_t(const void* A, const void* B0, const void* B1, Ff
     ARISTOS_COUNT_LAUNCH();
     ARISTOS_CUDA_TRY(cudaGetLastError());
     return ARISTOS_OK;
+}
+
+// Both projections in one launch (ffn_updown_kernel). `done` holds groups * max_row_tiles counters.
+template <int FMT, bool BIAS, bool PEERS>
+aristos_status_t launch_updown_t(const void* xg, const void* w1, const void* w3, const void* h, const void* w2,
+                                 const FfnGemmParams& p0, const FfnGemmParams& p1, const PeerOutMaps& peers,
+                                 int32_t* done, int grid_limit, cudaStream_t st) {
+    CUtensorMap tmA0, tmB00, tmB01, tmOut0, tmA1, tmB1, tmOut1;
+    ARISTOS_TRY(make_map_3d(&tmA0, xg, p0.K, p0.rows_per_group, p0.groups, FMT));
+    ARISTOS_TRY(make_map_3d(&tmB00, w1, p0.K, p0.N, p0.experts, FMT));
+    ARISTOS_TRY(make_map_3d(&tmB01, w3, p0.K, p0.N, p0.experts, FMT));
+    ARISTOS_TRY(make_map_3d(&tmOut0, p0.out, p0.N, p0.rows_per_group, p0.groups, FMT));
+    ARISTOS_TRY(make_map_3d(&tmA1, h, p1.K, p1.rows_per_group, p1.groups, FMT));
+    ARISTOS_TRY(make_map_3d(&tmB1, w2, p1.K, p1.N, p1.experts, FMT));
+    ARISTOS_TRY(make_map_3d(&tmOut1, p1.out, p1.N, p1.rows_per_group, p1.groups, FMT));
+    PeerMapsArg<PEERS> pm;
+    if constexpr (PEERS) memcpy(pm.m, peers.m, sizeof(pm.m));
+    else pm.unused = 0;
+    int sms = device_sm_count();
+    if (sms <= 0) { set_last_error("no CUDA device"); return ARISTOS_ERR_CUDA; }
+    if (grid_limit > 0 && grid_limit < sms) sms = grid_limit;
+    const int window = p0.row_end - p0.row_begin;
+    const int max_row_tiles = ceil_div(window, BM);
+    auto kernel = ffn_updown_kernel<FMT, BIAS, PEERS>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        ARISTOS_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        attr_set = true;
+    }
+    ARISTOS_CUDA_TRY(cudaMemsetAsync(done, 0, sizeof(int32_t) * (size_t)p0.groups * max_row_tiles, st));
+    const int64_t bound = (int64_t)p0.groups * max_row_tiles * (ceil_div(p0.N, p0.gated ? 128 : 256) + ceil_div(p1.N, 256));
+    const int grid = (int)(bound < sms ? bound : sms);
+    if (grid <= 0) return ARISTOS_OK;
+    kernel<<<grid, FFN_THREADS, SMEM_BYTES, st>>>(tmA0, tmB00, tmB01, tmOut0, tmA1, tmB1, tmOut1, pm, p0, p1, done,
+                                                  max_row_tiles);
+    ARISTOS_COUNT_LAUNCH();
+    ARISTOS_CUDA_TRY(cudaGetLastError());
+    return ARISTOS_OK;
+}
+
+template <int FMT>
+aristos_status_t launch_updown_f(const void* xg, const void* w1, const void* w3, const void* h, const void* w2,
+                                 const FfnGemmParams& p0, const FfnGemmParams& p1, const PeerOutMaps& peers,
+                                 int32_t* done, int grid_limit, cudaStream_t st) {
+    const bool bias = p0.bias0 || p0.bias1 || p1.bias0;
+    const bool to_peers = p1.peer_world > 0;
+    if (bias) return to_peers ? launch_updown_t<FMT, true, true>(xg, w1, w3, h, w2, p0, p1, peers, done, grid_limit, st)
+                              : launch_updown_t<FMT, true, false>(xg, w1, w3, h, w2, p0, p1, peers, done, grid_limit, st);
+    return to_peers ? launch_updown_t<FMT, false, true>(xg, w1, w3, h, w2, p0, p1, peers, done, grid_limit, st)
+                    : launch_updown_t<FMT, false, false>(xg, w1, w3, h, w2, p0, p1, peers, done, grid_limit, st);
 }
 
 template <int FMT>
@@ -857,7 +1126,16 @@ aristos_status_t expert_ffn_tc_sm100(const void* xg, const int32_t* count, int g
     p.bias0 = b1;
     p.bias1 = gated ? b3 : nullptr;
     static const PeerOutMaps no_peers{};
-    ARISTOS_TRY(launch_gemm(xg, w1, gated ? w3 : w1, p, no_peers, sm_limit, st));
+    // small row groups: both projections in one persistent launch (needs the caller's counter scratch)
+    const int window = row_end - row_begin;
+    const int mode = tile_mode();
+    const bool small_groups = mode == TILES_SINGLE || (mode == TILES_AUTO && window < 1024);
+    const char* fz = getenv("ARISTOS_FFN_FUSED");
+    const bool one_launch = small_groups && ep && ep->updown_scratch &&
+                            ep->updown_scratch_ints >= (size_t)groups * ceil_div(window, BM) && !(fz && !strcmp(fz, "0")) &&
+                            !(mode == TILES_SINGLE && !(fz && !strcmp(fz, "1")));
+    const FfnGemmParams p_up = p;
+    if (!one_launch) ARISTOS_TRY(launch_gemm(xg, w1, gated ? w3 : w1, p, no_peers, sm_limit, st));
     // down-projection: y = h * W2^T (h was written by the launch above: nothing left to wait for)
     p.src_flags = nullptr;
     p.N = H;
@@ -867,6 +1145,21 @@ aristos_status_t expert_ffn_tc_sm100(const void* xg, const int32_t* count, int g
     p.out = y;
     p.bias0 = b2;
     p.bias1 = nullptr;
+    if (one_launch) {
+        PeerOutMaps peers{};
+        if (peer_world > 0) {
+            for (int d = 0; d < peer_world; ++d)
+                ARISTOS_TRY(make_map_3d(&peers.m[d], ep->peer_y[d], H, rows_per_group, peer_world * experts, fmt));
+            p.peer_world = peer_world;
+            p.peer_rank = ep->peer_rank;
+        }
+        const void* w3x = gated ? w3 : w1;
+        switch (fmt) {
+            case FMT_BF16: return launch_updown_f<FMT_BF16>(xg, w1, w3x, h_scratch, w2, p_up, p, peers, ep->updown_scratch, sm_limit, st);
+            case FMT_F16: return launch_updown_f<FMT_F16>(xg, w1, w3x, h_scratch, w2, p_up, p, peers, ep->updown_scratch, sm_limit, st);
+            default: return launch_updown_f<FMT_TF32>(xg, w1, w3x, h_scratch, w2, p_up, p, peers, ep->updown_scratch, sm_limit, st);
+        }
+    }
     if (peer_world > 0) {
         // every source rank's return buffer holds (all experts, rows_per_group, H); rows of group (src, e_local) land
         // in rank src's block peer_rank * experts + e_local

@@ -105,7 +105,7 @@ gate_screen_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0) {
-        if (lane == 0) {
+        if (ptx::elect_one()) {
             ptx::prefetch_tensormap(&tmX);
             ptx::prefetch_tensormap(&tmW);
             int stage = 0;
@@ -128,7 +128,7 @@ gate_screen_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
         }
         __syncwarp();
     } else if (warp == 1) {
-        if (lane == 0) {
+        if (ptx::elect_one()) {
             const uint32_t idesc = ptx::umma_idesc_f32acc(GS_BM, p.n_mma, p.bf16 ? 1u : 0u);
             int stage = 0;
             uint32_t phase = 0;

@@ -73,6 +73,8 @@ struct aristos_moe {
     bool kernel_wait = false;                // direct mode: the up projection waits for each source's rows itself
     bool dense = false;                      // fp8 across ranks: received rows packed per expert across the sources
     int32_t *send_base = nullptr, *dense_count = nullptr, *src_off = nullptr;
+    int32_t* ffn_done = nullptr;             // counters of the one-launch expert FFN (groups x row tiles)
+    size_t ffn_done_ints = 0;
     int64_t launches = 0;
     const void *b1 = nullptr, *b3 = nullptr, *b2 = nullptr;   // optional expert biases (caller-owned, device)
     // failure handling of the exchange: every wait for a forward's completion has a wall-clock limit; on expiry the
@@ -125,6 +127,7 @@ size_t plan_workspace(aristos_moe* L, char* base) {
     CARVE(topk_w, float*, S * k * 4)
     CARVE(count, int32_t*, E * 4)
     CARVE(rcount, int32_t*, (size_t)L->groups * 4)
+    CARVE(ffn_done, int32_t*, L->ffn_done_ints * 4)
     if (L->dense) {
         CARVE(send_base, int32_t*, E * 4)
         CARVE(dense_count, int32_t*, (size_t)L->E_local * 4)
@@ -266,6 +269,7 @@ aristos_status_t aristos_moe_create(const aristos_config_t* cfg, int rank, int w
     if ((int64_t)L->E * L->cap > 0x7fffffffLL) { delete L; set_last_error("create: E*capacity overflows int32"); return ARISTOS_ERR_CONFIG; }
     if (L->groups > 1024) { delete L; set_last_error("create: more than 1024 row groups per rank"); return ARISTOS_ERR_CONFIG; }
     L->dispatch_scratch_bytes = aristos_dispatch_scratch_bytes(L->S, L->k, L->E);
+    L->ffn_done_ints = (size_t)L->groups * ((L->cap + 127) / 128);
     {
         // many experts, 16-bit inputs: the gate screens on the tensor cores (ARISTOS_GATE=exact keeps the
         // all-experts kernel)
@@ -560,6 +564,13 @@ static aristos_status_t forward_impl(aristos_moe_t* L, const void* x, const void
         ARISTOS_TRY(aristos_expert_ffn_fp8(L->xgq, L->sxg, L->count, L->E, L->cap, L->E, w1, s1, w3, s3, w2, s2, L->h,
                                            L->hq, L->sh, L->yr, L->H, L->I, L->cfg.hidden_act, 0, L->cap, 0,
                                            L->dev_status, st));
+    } else if (L->world == 1 && (dt == ARISTOS_DTYPE_BF16 || dt == ARISTOS_DTYPE_F16 || dt == ARISTOS_DTYPE_TF32)) {
+        FfnEpArgs extra;                     // no exchange; the scratch lets small row groups run as one launch
+        extra.updown_scratch = L->ffn_done;
+        extra.updown_scratch_ints = L->ffn_done_ints;
+        const int fmt = dt == ARISTOS_DTYPE_BF16 ? 0 : (dt == ARISTOS_DTYPE_F16 ? 1 : 2);
+        ARISTOS_TRY(expert_ffn_tc_sm100(L->xg, L->count, L->E, L->cap, L->E, w1, w3, w2, L->b1, L->b3, L->b2, L->h, L->yr,
+                                        L->H, L->I, L->cfg.hidden_act, fmt, 0, L->cap, 0, L->dev_status, st, &extra));
     } else if (L->world == 1) {
         ARISTOS_TRY(aristos_expert_ffn_bias(L->xg, L->count, L->E, L->cap, L->E, w1, w3, w2, L->b1, L->b3, L->b2, L->h, L->yr, L->H, L->I,
                                        L->cfg.hidden_act, dt, 0, L->cap, 0, L->dev_status, st));
@@ -605,6 +616,10 @@ static aristos_status_t forward_impl(aristos_moe_t* L, const void* x, const void
             if (tc) {
                 FfnEpArgs ep;
                 ep.first_source = L->rank;
+                if (nwin == 1) {             // one row window: small row groups run both projections as one launch
+                    ep.updown_scratch = L->ffn_done;
+                    ep.updown_scratch_ints = L->ffn_done_ints;
+                }
                 if (L->kernel_wait) {
                     ep.src_flags = ep_p2p_flags(L->p2p, EP_FLAG_IN, c);
                     ep.flag_epoch = ep_p2p_epoch(L->p2p);

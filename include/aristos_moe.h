@@ -346,10 +346,11 @@ ARISTOS_API aristos_status_t aristos_selftest_bounded_wait(int limit_ms, int* wa
  * result. */
 ARISTOS_API aristos_status_t aristos_selftest_bounded_flag_wait(int limit_ms, int* waited_ms, void* stream);
 /* Tile shape of the tensor-core expert GEMM for later calls of this process (replaces the compile-time BLOCK_M /
- * BLOCK_N of processor/tiling.cuh:19-26): 0 automatic (CTA pairs, tcgen05 cta_group::2 with 256 x 256 tiles, where a
- * row window holds >= 1024 rows, each group's last < 256 rows on single-CTA 128 x 256 tiles), 1 single-CTA tiles only,
- * 2 pairs + single-CTA tail for every window, 3 pairs only (groups padded to 256 rows), -1 re-read ARISTOS_FFN_TILES
- * (single | pair | pair-padded). Results are bit-identical across the modes. */
+ * BLOCK_N of processor/tiling.cuh:19-26): 0 automatic (CTA pairs, tcgen05 cta_group::2 with 256 x 256 tiles and groups
+ * padded to whole tiles, where a row window holds >= 1024 rows; single-CTA 128 x 256 tiles otherwise), 1 single-CTA
+ * tiles only, 2 pairs over each group's whole 256-row tiles + a single-CTA launch for its last < 256 rows, 3 padded
+ * pairs for every window, -1 re-read ARISTOS_FFN_TILES (single | pair | pair-padded). Results are bit-identical
+ * across the modes. */
 ARISTOS_API aristos_status_t aristos_ffn_set_tile_mode(int mode);
 /* Order in which the GEMM walks the row_tiles x col_tiles tiles of one row group (`band` row tiles per band; 0 = row
  * tile fastest): position `local` -> (row tile, column tile). Host-only, for tests. Returns 0, or -1 on bad input. */

@@ -159,11 +159,11 @@ def test_config3_full_size_mixtral_shaped(oracle):
     _full_size(3, 2, oracle, n_sample=64)
 
 
-@pytest.mark.parametrize("tiles", ["single", "pair-padded"])
+@pytest.mark.parametrize("tiles", ["single", "pair"])
 def test_config3_with_other_tile_shapes(tiles):
-    """CTA pairs (cta_group::2, 256 x 256 tiles) with a single-CTA tail are the default where a row group is large;
-    the full-size Mixtral-shaped parity test once more in processes that select single-CTA tiles only and padded
-    pairs only."""
+    """Padded CTA pairs (cta_group::2, 256 x 256 tiles) are the default where a row group is large; the full-size
+    Mixtral-shaped parity test once more in processes that select single-CTA tiles only, and pairs over the whole
+    256-row tiles with a single-CTA launch for every group's remaining rows."""
     import os
     import subprocess
     import sys
