@@ -118,15 +118,19 @@ def layer_flops(cfg, kept_assignments: int) -> float:
         2.0 * cfg.S * cfg.hidden_size * cfg.num_experts
 
 
-def layer_roofline(cfg, world, kept, elt=2):
-    """The layer roofline: the slowest of FLOPs at the dense tensor peak, minimum HBM bytes at
-    8 TB/s and all-to-all bytes at 900 GB/s per direction (dispatch and return summed). Seconds per rank."""
+def layer_roofline(cfg, world, kept):
+    """The layer roofline: the slowest of FLOPs at the dense tensor peak (2250 TFLOP/s bf16, 4500 TFLOP/s fp8), minimum
+    HBM bytes at 8 TB/s and all-to-all bytes at 900 GB/s per direction (dispatch and return summed). Seconds per rank."""
     m = 3 if cfg.hidden_act == 2 else 2
     H, I, E, S = cfg.hidden_size, cfg.intermediate_size, cfg.num_experts, cfg.S
-    t_tc = layer_flops(cfg, kept) / 2250e12
-    hbm = (E // world) * m * H * I * elt + S * H * elt + S * H * elt + E * H * elt
+    fp8 = cfg.torch_dtype == 4
+    b_w = 1 if fp8 else 2                      # bytes per weight; activations and outputs are 16-bit either way
+    t_tc = layer_flops(cfg, kept) / (4500e12 if fp8 else 2250e12)
+    hbm = (E // world) * m * H * I * b_w + S * H * 2 + S * H * 2 + E * H * 2
     t_hbm = hbm / 8e12
-    t_a2a = 2.0 * kept * (world - 1) / world * H * elt / 900e9 if world > 1 else 0.0
+    # dispatch moves the rows as the experts read them (fp8: codes + one fp32 scale per 128), the return is 16-bit
+    b_out = (1 + 4.0 / 128) if fp8 else 2
+    t_a2a = kept * (world - 1) / world * H * (b_out + 2) / 900e9 if world > 1 else 0.0
     return max(t_tc, t_hbm, t_a2a), dict(t_tensor_ms=t_tc * 1e3, t_hbm_ms=t_hbm * 1e3, t_a2a_ms=t_a2a * 1e3)
 
 
@@ -466,7 +470,8 @@ def run_ours(args, cfg, workload_desc):
                 "gpu_launches": int(launches),
                 "roofline": roofline_fp8 if fp8 else roofline,
                 "layer_roofline": {"seconds": t_roof, **terms, "frac": t_roof / (ms / args.steps * 1e-3),
-                                   "constants": "2250 TFLOP/s dense bf16, 8 TB/s HBM, 900 GB/s NVLink per direction"},
+                                   "constants": "2250 TFLOP/s dense bf16 (4500 fp8), 8 TB/s HBM, 900 GB/s NVLink per "
+                                                "direction"},
                 "stage_ms": stage, "host_enqueue_ms_per_step": host_enqueue_ms}
         if world > 1:
             # the outgoing exchange of rank 0: rows that leave the rank x row bytes over the time of its count + gather

@@ -25,7 +25,7 @@ __global__ void __launch_bounds__(256)
 permute_rows_peer_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ slot_of, int S, int k, int row_vec,
                          int E_local, int cap, int src_rank, int pos_lo, int pos_hi, PeerPtrs dst,
                          const int32_t* __restrict__ count, int E, PeerPtrs count_dst,
-                         const int32_t* __restrict__ send_base, int group_rows) {
+                         const int32_t* __restrict__ send_base, int group_rows, int dest_filter) {
     // the first CTA also delivers the row counts: count[e] becomes entry (src_rank, e % E_local) of the owner's list
     if (count != nullptr && blockIdx.x == 0)
         for (int e = threadIdx.x; e < E; e += blockDim.x) {
@@ -43,7 +43,9 @@ permute_rows_peer_kernel(const uint4* __restrict__ x, const int32_t* __restrict_
             if (slot >= 0) {
                 const int e = slot / cap, pos = slot - e * cap;
                 const int owner = e / E_local, el = e - owner * E_local;
-                if (pos >= pos_lo && pos < pos_hi) {
+                // dest_filter 1: only the rows this rank keeps; 2: only the rows that go to other ranks
+                const bool wanted = dest_filter == 0 || (dest_filter == 1) == (owner == src_rank);
+                if (wanted && pos >= pos_lo && pos < pos_hi) {
                     const size_t row = send_base ? (size_t)el * group_rows + send_base[e] + pos
                                                  : (size_t)(src_rank * E_local + el) * cap + pos;
                     rows[j] = static_cast<uint4*>(dst.p[owner]) + row * row_vec;
@@ -141,7 +143,7 @@ aristos_status_t dense_exchange_plan(const int32_t* allcount, int world, int E, 
 aristos_status_t permute_rows_to_peers(const void* x, const int32_t* slot_of, int S, int k, size_t row_bytes,
                                        int E_local, int cap, int src_rank, int pos_lo, int pos_hi, const PeerPtrs& dst,
                                        cudaStream_t st, const int32_t* count, int E, const PeerPtrs* count_dst,
-                                       const int32_t* send_base, int group_rows) {
+                                       const int32_t* send_base, int group_rows, int dest_filter) {
     if (row_bytes % 16 != 0 || k > 16) { set_last_error("peer gather: row bytes must be a multiple of 16, k <= 16"); return ARISTOS_ERR_INVALID_ARG; }
     if (count && !count_dst) { set_last_error("peer gather: counts without a destination"); return ARISTOS_ERR_INVALID_ARG; }
     if (S == 0 && !count) return ARISTOS_OK;
@@ -149,10 +151,10 @@ aristos_status_t permute_rows_to_peers(const void* x, const int32_t* slot_of, in
     const int grid = S > 0 ? ceil_div(S, 8) : 1;
     const PeerPtrs cd = count ? *count_dst : PeerPtrs{};
     const uint4* xs = static_cast<const uint4*>(x);
-    if (k <= 2) permute_rows_peer_kernel<2><<<grid, 256, 0, st>>>(xs, slot_of, S, k, row_vec, E_local, cap, src_rank, pos_lo, pos_hi, dst, count, E, cd, send_base, group_rows);
-    else if (k <= 4) permute_rows_peer_kernel<4><<<grid, 256, 0, st>>>(xs, slot_of, S, k, row_vec, E_local, cap, src_rank, pos_lo, pos_hi, dst, count, E, cd, send_base, group_rows);
-    else if (k <= 8) permute_rows_peer_kernel<8><<<grid, 256, 0, st>>>(xs, slot_of, S, k, row_vec, E_local, cap, src_rank, pos_lo, pos_hi, dst, count, E, cd, send_base, group_rows);
-    else permute_rows_peer_kernel<16><<<grid, 256, 0, st>>>(xs, slot_of, S, k, row_vec, E_local, cap, src_rank, pos_lo, pos_hi, dst, count, E, cd, send_base, group_rows);
+    if (k <= 2) permute_rows_peer_kernel<2><<<grid, 256, 0, st>>>(xs, slot_of, S, k, row_vec, E_local, cap, src_rank, pos_lo, pos_hi, dst, count, E, cd, send_base, group_rows, dest_filter);
+    else if (k <= 4) permute_rows_peer_kernel<4><<<grid, 256, 0, st>>>(xs, slot_of, S, k, row_vec, E_local, cap, src_rank, pos_lo, pos_hi, dst, count, E, cd, send_base, group_rows, dest_filter);
+    else if (k <= 8) permute_rows_peer_kernel<8><<<grid, 256, 0, st>>>(xs, slot_of, S, k, row_vec, E_local, cap, src_rank, pos_lo, pos_hi, dst, count, E, cd, send_base, group_rows, dest_filter);
+    else permute_rows_peer_kernel<16><<<grid, 256, 0, st>>>(xs, slot_of, S, k, row_vec, E_local, cap, src_rank, pos_lo, pos_hi, dst, count, E, cd, send_base, group_rows, dest_filter);
     ARISTOS_COUNT_LAUNCH();
     ARISTOS_CUDA_TRY(cudaGetLastError());
     return ARISTOS_OK;

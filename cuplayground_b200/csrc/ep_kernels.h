@@ -21,7 +21,9 @@ aristos_status_t permute_rows_to_peers(const void* x, const int32_t* slot_of, in
                                        int E_local, int cap, int src_rank, int pos_lo, int pos_hi, const PeerPtrs& dst,
                                        cudaStream_t st, const int32_t* count = nullptr, int E = 0,
                                        const PeerPtrs* count_dst = nullptr, const int32_t* send_base = nullptr,
-                                       int group_rows = 0);
+                                       int group_rows = 0, int dest_filter = 0);
+// dest_filter: 0 every kept row, 1 only the rows whose expert this rank owns (a local copy), 2 only the rows that go
+// to other ranks (what can run beside the expert GEMM while it works on the local rows).
 // Dense packing of the received rows per expert across source ranks. From allcount[src * E + e] (every rank's counts
 // of every expert): send_base[e] = where this rank's rows start in expert e's group at its owner (the lower ranks'
 // rows come first); for this rank's experts dense_count[el] = rows received in all and src_off[el * (world + 1) + s]

@@ -19,6 +19,7 @@ struct FfnEpArgs {
     const uint32_t* src_flags = nullptr;
     uint32_t flag_epoch = 0;
     uint32_t flag_limit_ms = 0;
+    int self_source = -1;     // rows of this source rank are complete before the launch: no flag wait for them
     // Counter scratch (device, groups * ceil(rows / 128) int32): with it, small row groups run the up and the down
     // projection as ONE persistent launch whose down tiles wait for the up tiles of their row tile.
     int32_t* updown_scratch = nullptr;

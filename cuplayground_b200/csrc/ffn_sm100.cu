@@ -74,6 +74,7 @@ struct FfnGemmParams {
     int32_t* dev_status;
     int peer_world;         // > 0: output tiles go straight to the rank that sent the rows (group g came from rank
     int peer_rank;          //      g / experts) through PeerOutMaps, as group peer_rank * experts + g % experts
+    void* peer_base[8];     // the same buffers as raw pointers (row-masked stores of partly valid tiles)
     int rows_mode;          // ROWS_ALL, ROWS_FULL_PAIRS (pair kernel: whole 256-row tiles only) or ROWS_TAIL (single-CTA
                             // kernel: the < 256 rows per group that the pair kernel left)
     int band;               // row tiles per band of the tile order (band_tile_coord); 0 = row tile fastest
@@ -84,6 +85,7 @@ struct FfnGemmParams {
     const uint32_t* src_flags;
     uint32_t flag_epoch;
     uint32_t flag_limit_ms;
+    int self_source;        // rows of this source need no flag (gathered on the launching stream); -1: none
 };
 
 enum { ROWS_ALL = 0, ROWS_FULL_PAIRS = 1, ROWS_TAIL = 2 };
@@ -161,12 +163,39 @@ __device__ __forceinline__ void build_tile_prefix(const FfnGemmParams& p, int* p
 __device__ __forceinline__ bool wait_source_rows(const FfnGemmParams& p, int g, uint32_t& seen, volatile int* abort_flag) {
     if (p.src_flags == nullptr) return true;
     const int src = g / p.experts;
-    if ((seen >> src) & 1u) return true;
+    if (src == p.self_source || ((seen >> src) & 1u)) return true;
     if (!ptx::flag_wait_bounded(p.src_flags + src, p.flag_epoch, abort_flag, p.dev_status,
                                 (uint64_t)p.flag_limit_ms * 1000000ull))
         return false;
     seen |= 1u << src;
     return true;
+}
+
+// The first `valid` rows of the 128 x 128-byte swizzled staging tile to global memory (row pitch `pitch` bytes), by
+// the 128 epilogue threads: 8 threads per row, 16 rows per step, 16-byte stores that together fill whole 128-byte lines.
+__device__ __forceinline__ void copy_valid_rows(uint32_t staging, uint8_t* dst, size_t pitch, int valid, int epi_tid) {
+    const int ch = epi_tid & 7;
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+        const int r = it * 16 + (epi_tid >> 3);
+        if (r < valid) {
+            uint4 v;
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                         : "r"(staging + r * 128 + ((ch ^ (r & 7)) << 4)));
+            *reinterpret_cast<uint4*>(dst + (size_t)r * pitch + ch * 16) = v;
+        }
+    }
+}
+
+// Destination of a partly valid 128-row tile whose output goes to rank src: row m0 of group og in that rank's buffer,
+// or nullptr for a whole tile (which leaves by TMA store). Partly valid tiles are stored row by row, valid rows only.
+template <int FMT>
+__device__ __forceinline__ uint8_t* masked_peer_rows(const FfnGemmParams& p, int src, int og, int g, int m0, int rows) {
+    const int row_limit = min(p.count[g], p.row_end);
+    if (p.peer_base[src] == nullptr || m0 >= row_limit || m0 + rows <= row_limit) return nullptr;
+    constexpr size_t elt = FMT == FMT_TF32 ? 4 : 2;
+    return static_cast<uint8_t*>(p.peer_base[src]) + ((size_t)og * p.rows_per_group + m0) * p.N * elt;
 }
 
 __device__ __forceinline__ uint32_t pack_16bit(float a, float b, int fmt) {
@@ -217,13 +246,16 @@ __device__ __forceinline__ void add_bias32(uint32_t (&acc)[32], const void* bias
 // -> activation -> bf16 -> 128-byte-swizzled shared staging (64 output columns at a time) -> TMA store. The
 // accumulator buffer is handed back as soon as the last TMEM load has landed. A tile that lies entirely at or past
 // the group's valid rows stores nothing; a partly valid tile stores all of its 128 rows (the extra rows hold
-// unspecified values, never past the group's row capacity: the tensor map clips them).
+// unspecified values, never past the group's row capacity: the tensor map clips them). With masked_dst != nullptr
+// (a partly valid tile whose rows go to another rank: masked_dst = row m0 of the destination group there) every thread
+// stores its own row with 16-byte stores if the row is valid, so that only rows that exist cross NVLink.
 template <bool PAIR, int FMT, bool BIAS>
 __device__ __forceinline__ void epilogue_tile(const FfnGemmParams& p, const CUtensorMap* tmOut, int out_g, int g, int m0,
                                               int n0, int row_in_tile, uint32_t taddr, uint32_t tempty, int lane,
-                                              int epi_tid, uint32_t staging) {
+                                              int epi_tid, uint32_t staging, uint8_t* masked_dst = nullptr) {
     const int row_limit = min(p.count[g], p.row_end);
     const bool tile_live = m0 < row_limit;
+    const bool masked = masked_dst != nullptr;       // the same for all epilogue threads of the tile
     const int nchunk = p.gated ? 2 : 4;              // 64-column chunks of the output tile
     const uint32_t my_row = staging + row_in_tile * 128;
     const int sw = row_in_tile & 7;
@@ -271,7 +303,11 @@ __device__ __forceinline__ void epilogue_tile(const FfnGemmParams& p, const CUte
         }
         ptx::fence_proxy_async_shared();
         ptx::named_barrier_sync(1, EPI_THREADS);
-        if (epi_tid == 0 && tile_live && n0 + c * 64 < p.N) {
+        if (masked) {
+            // the valid rows only, 8 threads per 128-byte row: whole lines leave for the other rank
+            if (n0 + c * 64 < p.N) copy_valid_rows(staging, masked_dst + (size_t)(n0 + c * 64) * 2, (size_t)p.N * 2,
+                                                   row_limit - m0, epi_tid);
+        } else if (epi_tid == 0 && tile_live && n0 + c * 64 < p.N) {
             ptx::tma_store_3d(tmOut, staging, n0 + c * 64, m0, out_g);
             ptx::bulk_commit_group();
         }
@@ -283,9 +319,10 @@ __device__ __forceinline__ void epilogue_tile(const FfnGemmParams& p, const CUte
 template <bool PAIR, bool BIAS>
 __device__ __forceinline__ void epilogue_tile_f32(const FfnGemmParams& p, const CUtensorMap* tmOut, int out_g, int g,
                                                   int m0, int n0, int row_in_tile, uint32_t taddr, uint32_t tempty,
-                                                  int lane, int epi_tid, uint32_t staging) {
+                                                  int lane, int epi_tid, uint32_t staging, uint8_t* masked_dst = nullptr) {
     const int row_limit = min(p.count[g], p.row_end);
     const bool tile_live = m0 < row_limit;
+    const bool masked = masked_dst != nullptr;
     const int nchunk = p.gated ? 4 : 8;
     const uint32_t my_row = staging + row_in_tile * 128;
     const int sw = row_in_tile & 7;
@@ -325,7 +362,10 @@ __device__ __forceinline__ void epilogue_tile_f32(const FfnGemmParams& p, const 
             ptx::st_shared_v4(my_row + ((j ^ sw) << 4), a[4 * j], a[4 * j + 1], a[4 * j + 2], a[4 * j + 3]);
         ptx::fence_proxy_async_shared();
         ptx::named_barrier_sync(1, EPI_THREADS);
-        if (epi_tid == 0 && tile_live && n0 + col < p.N) {
+        if (masked) {
+            if (n0 + col < p.N) copy_valid_rows(staging, masked_dst + (size_t)(n0 + col) * 4, (size_t)p.N * 4, row_limit - m0,
+                                                epi_tid);
+        } else if (epi_tid == 0 && tile_live && n0 + col < p.N) {
             ptx::tma_store_3d(tmOut, staging, n0 + col, m0, out_g);
             ptx::bulk_commit_group();
         }
@@ -469,15 +509,17 @@ ffn_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
             const CUtensorMap* om = &tmOut;
             int og = g;
+            uint8_t* md = nullptr;
             if constexpr (PEERS) {
                 const int src = g / p.experts;
                 om = &peers.m[src];
                 og = p.peer_rank * p.experts + (g - src * p.experts);
+                md = masked_peer_rows<FMT>(p, src, og, g, m0, BM);
             }
             if constexpr (FMT == FMT_TF32)
-                epilogue_tile_f32<false, BIAS>(p, om, og, g, m0, n0, row_in_tile, taddr, bar_tempty + 8 * buf, lane, epi_tid, staging);
+                epilogue_tile_f32<false, BIAS>(p, om, og, g, m0, n0, row_in_tile, taddr, bar_tempty + 8 * buf, lane, epi_tid, staging, md);
             else
-                epilogue_tile<false, FMT, BIAS>(p, om, og, g, m0, n0, row_in_tile, taddr, bar_tempty + 8 * buf, lane, epi_tid, staging);
+                epilogue_tile<false, FMT, BIAS>(p, om, og, g, m0, n0, row_in_tile, taddr, bar_tempty + 8 * buf, lane, epi_tid, staging, md);
         }
         if (epi_tid == 0) ptx::bulk_wait_group0();
     }
@@ -684,15 +726,17 @@ ffn_updown_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constan
             } else {
                 const CUtensorMap* om = &tmOut1;
                 int og = g;
+                uint8_t* md = nullptr;
                 if constexpr (PEERS) {
                     const int src = g / p1.experts;
                     om = &peers.m[src];
                     og = p1.peer_rank * p1.experts + (g - src * p1.experts);
+                    md = masked_peer_rows<FMT>(p1, src, og, g, m0, BM);
                 }
                 if constexpr (FMT == FMT_TF32)
-                    epilogue_tile_f32<false, BIAS>(p1, om, og, g, m0, n0, row_in_tile, taddr, bar_tempty + 8 * buf, lane, epi_tid, staging);
+                    epilogue_tile_f32<false, BIAS>(p1, om, og, g, m0, n0, row_in_tile, taddr, bar_tempty + 8 * buf, lane, epi_tid, staging, md);
                 else
-                    epilogue_tile<false, FMT, BIAS>(p1, om, og, g, m0, n0, row_in_tile, taddr, bar_tempty + 8 * buf, lane, epi_tid, staging);
+                    epilogue_tile<false, FMT, BIAS>(p1, om, og, g, m0, n0, row_in_tile, taddr, bar_tempty + 8 * buf, lane, epi_tid, staging, md);
             }
         }
         if (epi_tid == 0) ptx::bulk_wait_group0();
@@ -862,15 +906,17 @@ ffn_grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gr
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
             const CUtensorMap* om = &tmOut;
             int og = g;
+            uint8_t* md = nullptr;
             if constexpr (PEERS) {
                 const int src = g / p.experts;
                 om = &peers.m[src];
                 og = p.peer_rank * p.experts + (g - src * p.experts);
+                md = masked_peer_rows<FMT>(p, src, og, g, m0, BM);
             }
             if constexpr (FMT == FMT_TF32)
-                epilogue_tile_f32<true, BIAS>(p, om, og, g, m0, n0, row_in_tile, taddr, tempty0 + 8 * buf, lane, epi_tid, staging);
+                epilogue_tile_f32<true, BIAS>(p, om, og, g, m0, n0, row_in_tile, taddr, tempty0 + 8 * buf, lane, epi_tid, staging, md);
             else
-                epilogue_tile<true, FMT, BIAS>(p, om, og, g, m0, n0, row_in_tile, taddr, tempty0 + 8 * buf, lane, epi_tid, staging);
+                epilogue_tile<true, FMT, BIAS>(p, om, og, g, m0, n0, row_in_tile, taddr, tempty0 + 8 * buf, lane, epi_tid, staging, md);
         }
         if (epi_tid == 0) ptx::bulk_wait_group0();
     }
@@ -1081,6 +1127,17 @@ aristos_status_t launch_gemm(const void* A, const void* B0, const void* B1, cons
 
 }  // namespace
 
+// Partly valid tiles of the fused return leave row by row, valid rows only (ARISTOS_EP_MASKED_RETURN=0: whole tiles
+// by TMA store, padding rows included).
+bool masked_return() {
+    static int v = -1;
+    if (v < 0) {
+        const char* env = getenv("ARISTOS_EP_MASKED_RETURN");
+        v = (env && !strcmp(env, "0")) ? 0 : 1;
+    }
+    return v == 1;
+}
+
 void ffn_set_tile_mode(int mode) { g_tile_mode = (mode >= TILES_AUTO && mode <= TILES_PAIR_PADDED) ? mode : -1; }
 int ffn_tile_mode() { return tile_mode(); }
 
@@ -1111,11 +1168,13 @@ aristos_status_t expert_ffn_tc_sm100(const void* xg, const int32_t* count, int g
     p.row_end = row_end;
     p.dev_status = dev_status;
     p.fmt = fmt;
+    p.self_source = -1;
     if (ep) {
         p.first_source = ep->first_source;
         p.src_flags = ep->src_flags;
         p.flag_epoch = ep->flag_epoch;
         p.flag_limit_ms = ep->flag_limit_ms > 0 ? ep->flag_limit_ms : 2000;
+        p.self_source = ep->self_source;
     }
     // up-projection: h = epi(xg * W1^T [, xg * W3^T])
     p.N = I;
@@ -1148,8 +1207,10 @@ aristos_status_t expert_ffn_tc_sm100(const void* xg, const int32_t* count, int g
     if (one_launch) {
         PeerOutMaps peers{};
         if (peer_world > 0) {
-            for (int d = 0; d < peer_world; ++d)
+            for (int d = 0; d < peer_world; ++d) {
                 ARISTOS_TRY(make_map_3d(&peers.m[d], ep->peer_y[d], H, rows_per_group, peer_world * experts, fmt));
+                p.peer_base[d] = masked_return() ? ep->peer_y[d] : nullptr;
+            }
             p.peer_world = peer_world;
             p.peer_rank = ep->peer_rank;
         }
@@ -1164,8 +1225,10 @@ aristos_status_t expert_ffn_tc_sm100(const void* xg, const int32_t* count, int g
         // every source rank's return buffer holds (all experts, rows_per_group, H); rows of group (src, e_local) land
         // in rank src's block peer_rank * experts + e_local
         PeerOutMaps peers{};
-        for (int d = 0; d < peer_world; ++d)
+        for (int d = 0; d < peer_world; ++d) {
             ARISTOS_TRY(make_map_3d(&peers.m[d], ep->peer_y[d], H, rows_per_group, peer_world * experts, fmt));
+            p.peer_base[d] = masked_return() ? ep->peer_y[d] : nullptr;
+        }
         p.peer_world = peer_world;
         p.peer_rank = ep->peer_rank;
         ARISTOS_TRY(launch_gemm(h_scratch, w2, w2, p, peers, sm_limit, st));

@@ -71,6 +71,7 @@ struct aristos_moe {
     int direct_windows = 1;                  // row windows of the direct mode (gather / GEMMs / return pipelined)
     bool fused_return = false;               // direct mode: the down projection's epilogue stores into the source ranks
     bool kernel_wait = false;                // direct mode: the up projection waits for each source's rows itself
+    bool overlap_gather = false;             // direct mode: rows for other ranks are gathered beside the up projection
     bool dense = false;                      // fp8 across ranks: received rows packed per expert across the sources
     int32_t *send_base = nullptr, *dense_count = nullptr, *src_off = nullptr;
     int32_t* ffn_done = nullptr;             // counters of the one-launch expert FFN (groups x row tiles)
@@ -345,6 +346,11 @@ aristos_status_t aristos_moe_create(const aristos_config_t* cfg, int rank, int w
                 L->dense = L->fp8 && L->fused_return && !(dn && !strcmp(dn, "0"));
                 const char* kw = getenv("ARISTOS_EP_KERNEL_WAIT");
                 L->kernel_wait = L->ep_direct && tc && !(kw && !strcmp(kw, "0"));
+                // ... and then only the rows a rank keeps are gathered before its up projection starts; the rows for
+                // the other ranks leave on the communication stream while the tensor cores work on the local rows
+                // (ARISTOS_EP_OVERLAP_GATHER=0: the whole gather runs first)
+                const char* og = getenv("ARISTOS_EP_OVERLAP_GATHER");
+                L->overlap_gather = L->kernel_wait && L->direct_windows == 1 && !(og && !strcmp(og, "0"));
             }
             else if (L->fp8 || (tr && !strcmp(tr, "p2p")) || ps != ARISTOS_ERR_UNSUPPORTED) {
                 // ARISTOS_ERR_UNSUPPORTED is the agreed answer of every rank (all fall back to NCCL together); any
@@ -584,27 +590,32 @@ static aristos_status_t forward_impl(aristos_moe_t* L, const void* x, const void
         const size_t row_bytes = (size_t)L->H * L->elt;
         const int nwin = L->direct_windows;
         const int win_rows = ceil_div(ceil_div(L->cap, nwin), 256) * 256;
-        cudaStream_t cs = nwin > 1 ? L->comm_stream : st;
+        const bool overlap = L->overlap_gather && nwin == 1;
+        cudaStream_t cs = (nwin > 1 || overlap) ? L->comm_stream : st;
         ep_p2p_begin(L->p2p);
         *exchange_started = true;
+        // the row counts go first, with a flag of their own: every rank can build its tile list as soon as its peers
+        // have routed their tokens, long before their rows have all arrived
+        ARISTOS_TRY(ep_p2p_send_counts(L->p2p, L->count, L->E, L->E_local, st));
+        if (overlap)      // the rows this rank keeps: a local copy, complete before the up projection is launched
+            ARISTOS_TRY(permute_rows_to_peers(x, L->slot_of, L->S, L->k, row_bytes, L->E_local, L->cap, L->rank, 0, L->cap,
+                                              rows_dst, st, nullptr, 0, nullptr, nullptr, 0, /*dest_filter=*/1));
         if (cs != st) {
             ARISTOS_CUDA_TRY(cudaEventRecord(L->ev_dispatched, st));
             ARISTOS_CUDA_TRY(cudaStreamWaitEvent(cs, L->ev_dispatched, 0));
         }
-        // the row counts go first, with a flag of their own: every rank can build its tile list as soon as its peers
-        // have routed their tokens, long before their rows have all arrived
-        ARISTOS_TRY(ep_p2p_send_counts(L->p2p, L->count, L->E, L->E_local, cs));
         for (int c = 0; c < nwin; ++c) {
             const int r0 = c * win_rows, r1 = std::min(L->cap, r0 + win_rows);
             if (r0 >= r1) break;
             ARISTOS_TRY(permute_rows_to_peers(x, L->slot_of, L->S, L->k, row_bytes, L->E_local, L->cap, L->rank, r0, r1,
-                                              rows_dst, cs));
+                                              rows_dst, cs, nullptr, 0, nullptr, nullptr, 0, overlap ? 2 : 0));
             ARISTOS_TRY(ep_p2p_signal(L->p2p, EP_FLAG_IN, c, cs));
         }
         if (L->profiling) {          // "rows sent": the gather kernels and their flags are behind this event
             ARISTOS_CUDA_TRY(cudaEventRecord(L->ev_prof[prof_set + 5], cs));
             L->prof_sent = true;
         }
+        if (overlap) ARISTOS_CUDA_TRY(cudaEventRecord(L->ev_in[0], cs));      // joined before the combine
         ARISTOS_TRY(ep_p2p_wait(L->p2p, EP_FLAG_COUNT, 0, st));
         const bool tc = dt == ARISTOS_DTYPE_BF16 || dt == ARISTOS_DTYPE_F16 || dt == ARISTOS_DTYPE_TF32;
         for (int c = 0; c < nwin; ++c) {
@@ -616,6 +627,7 @@ static aristos_status_t forward_impl(aristos_moe_t* L, const void* x, const void
             if (tc) {
                 FfnEpArgs ep;
                 ep.first_source = L->rank;
+                if (overlap) ep.self_source = L->rank;
                 if (nwin == 1) {             // one row window: small row groups run both projections as one launch
                     ep.updown_scratch = L->ffn_done;
                     ep.updown_scratch_ints = L->ffn_done_ints;
@@ -655,6 +667,8 @@ static aristos_status_t forward_impl(aristos_moe_t* L, const void* x, const void
         }
         for (int c = 0; c < nwin; ++c)
             if (c * win_rows < L->cap) ARISTOS_TRY(ep_p2p_wait(L->p2p, EP_FLAG_RET, c, st));
+        // the gather for the other ranks still reads x and the routing tensors: the caller's stream joins it
+        if (overlap) ARISTOS_CUDA_TRY(cudaStreamWaitEvent(st, L->ev_in[0], 0));
     } else if (L->p2p) {
         // rows are pushed into the destination GPUs by the copy engines; flags + stream waits order the streams
         const size_t row_bytes = (size_t)L->H * L->elt;
