@@ -68,13 +68,14 @@ struct FfnGemmParams {
     int gated;              // 1: B half 1 comes from the second weight tensor at the same rows (SwiGLU)
     int act;                // ARISTOS_ACT_* for the non-gated epilogue
     void* out;              // (groups * rows_per_group, N), 16-bit elements
-    int fmt;                // FMT_BF16 / FMT_F16 (16-bit operands and output) or FMT_TF32 (fp32 storage, tf32 MMA)
+    int self_source;        // expert parallel: rows of this source rank need no arrival flag (gathered on the launching
+                            // stream); -1: none. (The struct is kept at 128 bytes: one more member changes how the
+                            // compiler treats the kernel argument and cost the small-K configurations 30 %.)
     const void* bias0;      // (experts, N) added to the accumulator before the activation, or nullptr
     const void* bias1;      // SwiGLU: bias of the second (up) projection, or nullptr
     int32_t* dev_status;
     int peer_world;         // > 0: output tiles go straight to the rank that sent the rows (group g came from rank
     int peer_rank;          //      g / experts) through PeerOutMaps, as group peer_rank * experts + g % experts
-    void* peer_base[8];     // the same buffers as raw pointers (row-masked stores of partly valid tiles)
     int rows_mode;          // ROWS_ALL, ROWS_FULL_PAIRS (pair kernel: whole 256-row tiles only) or ROWS_TAIL (single-CTA
                             // kernel: the < 256 rows per group that the pair kernel left)
     int band;               // row tiles per band of the tile order (band_tile_coord); 0 = row tile fastest
@@ -85,8 +86,8 @@ struct FfnGemmParams {
     const uint32_t* src_flags;
     uint32_t flag_epoch;
     uint32_t flag_limit_ms;
-    int self_source;        // rows of this source need no flag (gathered on the launching stream); -1: none
 };
+static_assert(sizeof(FfnGemmParams) == 128, "FfnGemmParams: keep the kernel argument at 128 bytes");
 
 enum { ROWS_ALL = 0, ROWS_FULL_PAIRS = 1, ROWS_TAIL = 2 };
 
@@ -95,6 +96,7 @@ enum { ROWS_ALL = 0, ROWS_FULL_PAIRS = 1, ROWS_TAIL = 2 };
 constexpr int MAX_PEER_OUT = 8;
 struct PeerOutMaps {
     CUtensorMap m[MAX_PEER_OUT];
+    void* base[MAX_PEER_OUT];
 };
 // Kernel argument: the maps for the instantiations that return tiles to peers, one word for those that do not (the
 // kernels are specialised on the operand format, on bias and on peer output at compile time, so the common case -
@@ -102,6 +104,7 @@ struct PeerOutMaps {
 template <bool PEERS>
 struct PeerMapsArg {
     CUtensorMap m[MAX_PEER_OUT];
+    void* base[MAX_PEER_OUT];     // the same buffers as raw pointers (row-masked stores of partly valid tiles), or null
 };
 template <>
 struct PeerMapsArg<false> {
@@ -191,11 +194,11 @@ __device__ __forceinline__ void copy_valid_rows(uint32_t staging, uint8_t* dst, 
 // Destination of a partly valid 128-row tile whose output goes to rank src: row m0 of group og in that rank's buffer,
 // or nullptr for a whole tile (which leaves by TMA store). Partly valid tiles are stored row by row, valid rows only.
 template <int FMT>
-__device__ __forceinline__ uint8_t* masked_peer_rows(const FfnGemmParams& p, int src, int og, int g, int m0, int rows) {
+__device__ __forceinline__ uint8_t* masked_peer_rows(const FfnGemmParams& p, void* base, int og, int g, int m0, int rows) {
     const int row_limit = min(p.count[g], p.row_end);
-    if (p.peer_base[src] == nullptr || m0 >= row_limit || m0 + rows <= row_limit) return nullptr;
+    if (base == nullptr || m0 >= row_limit || m0 + rows <= row_limit) return nullptr;
     constexpr size_t elt = FMT == FMT_TF32 ? 4 : 2;
-    return static_cast<uint8_t*>(p.peer_base[src]) + ((size_t)og * p.rows_per_group + m0) * p.N * elt;
+    return static_cast<uint8_t*>(base) + ((size_t)og * p.rows_per_group + m0) * p.N * elt;
 }
 
 __device__ __forceinline__ uint32_t pack_16bit(float a, float b, int fmt) {
@@ -249,13 +252,13 @@ __device__ __forceinline__ void add_bias32(uint32_t (&acc)[32], const void* bias
 // unspecified values, never past the group's row capacity: the tensor map clips them). With masked_dst != nullptr
 // (a partly valid tile whose rows go to another rank: masked_dst = row m0 of the destination group there) every thread
 // stores its own row with 16-byte stores if the row is valid, so that only rows that exist cross NVLink.
-template <bool PAIR, int FMT, bool BIAS>
+template <bool PAIR, int FMT, bool BIAS, bool MASKABLE>
 __device__ __forceinline__ void epilogue_tile(const FfnGemmParams& p, const CUtensorMap* tmOut, int out_g, int g, int m0,
                                               int n0, int row_in_tile, uint32_t taddr, uint32_t tempty, int lane,
                                               int epi_tid, uint32_t staging, uint8_t* masked_dst = nullptr) {
     const int row_limit = min(p.count[g], p.row_end);
     const bool tile_live = m0 < row_limit;
-    const bool masked = masked_dst != nullptr;       // the same for all epilogue threads of the tile
+    const bool masked = MASKABLE && masked_dst != nullptr;       // the same for all epilogue threads of the tile
     const int nchunk = p.gated ? 2 : 4;              // 64-column chunks of the output tile
     const uint32_t my_row = staging + row_in_tile * 128;
     const int sw = row_in_tile & 7;
@@ -303,7 +306,7 @@ __device__ __forceinline__ void epilogue_tile(const FfnGemmParams& p, const CUte
         }
         ptx::fence_proxy_async_shared();
         ptx::named_barrier_sync(1, EPI_THREADS);
-        if (masked) {
+        if (MASKABLE && masked) {
             // the valid rows only, 8 threads per 128-byte row: whole lines leave for the other rank
             if (n0 + c * 64 < p.N) copy_valid_rows(staging, masked_dst + (size_t)(n0 + c * 64) * 2, (size_t)p.N * 2,
                                                    row_limit - m0, epi_tid);
@@ -316,13 +319,13 @@ __device__ __forceinline__ void epilogue_tile(const FfnGemmParams& p, const CUte
 
 // The same for fp32 output (tf32 path): a 128-byte staging row holds 32 columns, so the tile leaves in 32-column
 // chunks.
-template <bool PAIR, bool BIAS>
+template <bool PAIR, bool BIAS, bool MASKABLE>
 __device__ __forceinline__ void epilogue_tile_f32(const FfnGemmParams& p, const CUtensorMap* tmOut, int out_g, int g,
                                                   int m0, int n0, int row_in_tile, uint32_t taddr, uint32_t tempty,
                                                   int lane, int epi_tid, uint32_t staging, uint8_t* masked_dst = nullptr) {
     const int row_limit = min(p.count[g], p.row_end);
     const bool tile_live = m0 < row_limit;
-    const bool masked = masked_dst != nullptr;
+    const bool masked = MASKABLE && masked_dst != nullptr;
     const int nchunk = p.gated ? 4 : 8;
     const uint32_t my_row = staging + row_in_tile * 128;
     const int sw = row_in_tile & 7;
@@ -362,7 +365,7 @@ __device__ __forceinline__ void epilogue_tile_f32(const FfnGemmParams& p, const 
             ptx::st_shared_v4(my_row + ((j ^ sw) << 4), a[4 * j], a[4 * j + 1], a[4 * j + 2], a[4 * j + 3]);
         ptx::fence_proxy_async_shared();
         ptx::named_barrier_sync(1, EPI_THREADS);
-        if (masked) {
+        if (MASKABLE && masked) {
             if (n0 + col < p.N) copy_valid_rows(staging, masked_dst + (size_t)(n0 + col) * 4, (size_t)p.N * 4, row_limit - m0,
                                                 epi_tid);
         } else if (epi_tid == 0 && tile_live && n0 + col < p.N) {
@@ -514,12 +517,12 @@ ffn_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
                 const int src = g / p.experts;
                 om = &peers.m[src];
                 og = p.peer_rank * p.experts + (g - src * p.experts);
-                md = masked_peer_rows<FMT>(p, src, og, g, m0, BM);
+                md = masked_peer_rows<FMT>(p, peers.base[src], og, g, m0, BM);
             }
             if constexpr (FMT == FMT_TF32)
-                epilogue_tile_f32<false, BIAS>(p, om, og, g, m0, n0, row_in_tile, taddr, bar_tempty + 8 * buf, lane, epi_tid, staging, md);
+                epilogue_tile_f32<false, BIAS, PEERS>(p, om, og, g, m0, n0, row_in_tile, taddr, bar_tempty + 8 * buf, lane, epi_tid, staging, md);
             else
-                epilogue_tile<false, FMT, BIAS>(p, om, og, g, m0, n0, row_in_tile, taddr, bar_tempty + 8 * buf, lane, epi_tid, staging, md);
+                epilogue_tile<false, FMT, BIAS, PEERS>(p, om, og, g, m0, n0, row_in_tile, taddr, bar_tempty + 8 * buf, lane, epi_tid, staging, md);
         }
         if (epi_tid == 0) ptx::bulk_wait_group0();
     }
@@ -713,9 +716,9 @@ ffn_updown_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constan
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
             if (!down) {
                 if constexpr (FMT == FMT_TF32)
-                    epilogue_tile_f32<false, BIAS>(p0, &tmOut0, g, g, m0, n0, row_in_tile, taddr, bar_tempty + 8 * buf, lane, epi_tid, staging);
+                    epilogue_tile_f32<false, BIAS, false>(p0, &tmOut0, g, g, m0, n0, row_in_tile, taddr, bar_tempty + 8 * buf, lane, epi_tid, staging);
                 else
-                    epilogue_tile<false, FMT, BIAS>(p0, &tmOut0, g, g, m0, n0, row_in_tile, taddr, bar_tempty + 8 * buf, lane, epi_tid, staging);
+                    epilogue_tile<false, FMT, BIAS, false>(p0, &tmOut0, g, g, m0, n0, row_in_tile, taddr, bar_tempty + 8 * buf, lane, epi_tid, staging);
                 // this tile's part of h is complete in global memory: count it for the down projection's producers
                 if (epi_tid == 0) {
                     ptx::bulk_wait_group0();
@@ -731,12 +734,12 @@ ffn_updown_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constan
                     const int src = g / p1.experts;
                     om = &peers.m[src];
                     og = p1.peer_rank * p1.experts + (g - src * p1.experts);
-                    md = masked_peer_rows<FMT>(p1, src, og, g, m0, BM);
+                    md = masked_peer_rows<FMT>(p1, peers.base[src], og, g, m0, BM);
                 }
                 if constexpr (FMT == FMT_TF32)
-                    epilogue_tile_f32<false, BIAS>(p1, om, og, g, m0, n0, row_in_tile, taddr, bar_tempty + 8 * buf, lane, epi_tid, staging, md);
+                    epilogue_tile_f32<false, BIAS, PEERS>(p1, om, og, g, m0, n0, row_in_tile, taddr, bar_tempty + 8 * buf, lane, epi_tid, staging, md);
                 else
-                    epilogue_tile<false, FMT, BIAS>(p1, om, og, g, m0, n0, row_in_tile, taddr, bar_tempty + 8 * buf, lane, epi_tid, staging, md);
+                    epilogue_tile<false, FMT, BIAS, PEERS>(p1, om, og, g, m0, n0, row_in_tile, taddr, bar_tempty + 8 * buf, lane, epi_tid, staging, md);
             }
         }
         if (epi_tid == 0) ptx::bulk_wait_group0();
@@ -911,12 +914,12 @@ ffn_grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gr
                 const int src = g / p.experts;
                 om = &peers.m[src];
                 og = p.peer_rank * p.experts + (g - src * p.experts);
-                md = masked_peer_rows<FMT>(p, src, og, g, m0, BM);
+                md = masked_peer_rows<FMT>(p, peers.base[src], og, g, m0, BM);
             }
             if constexpr (FMT == FMT_TF32)
-                epilogue_tile_f32<true, BIAS>(p, om, og, g, m0, n0, row_in_tile, taddr, tempty0 + 8 * buf, lane, epi_tid, staging, md);
+                epilogue_tile_f32<true, BIAS, PEERS>(p, om, og, g, m0, n0, row_in_tile, taddr, tempty0 + 8 * buf, lane, epi_tid, staging, md);
             else
-                epilogue_tile<true, FMT, BIAS>(p, om, og, g, m0, n0, row_in_tile, taddr, tempty0 + 8 * buf, lane, epi_tid, staging, md);
+                epilogue_tile<true, FMT, BIAS, PEERS>(p, om, og, g, m0, n0, row_in_tile, taddr, tempty0 + 8 * buf, lane, epi_tid, staging, md);
         }
         if (epi_tid == 0) ptx::bulk_wait_group0();
     }
@@ -1011,8 +1014,12 @@ aristos_status_t launch_gemm_t(const void* A, const void* B0, const void* B1, Ff
     ARISTOS_TRY(make_map_3d(&tmB1, B1, p.K, p.N, p.experts, FMT));
     ARISTOS_TRY(make_map_3d(&tmOut, p.out, p.N, p.rows_per_group, p.groups, FMT));
     PeerMapsArg<PEERS> pm;
-    if constexpr (PEERS) memcpy(pm.m, peers.m, sizeof(pm.m));
-    else pm.unused = 0;
+    if constexpr (PEERS) {
+        memcpy(pm.m, peers.m, sizeof(pm.m));
+        memcpy(pm.base, peers.base, sizeof(pm.base));
+    } else {
+        pm.unused = 0;
+    }
     const int out_w = p.gated ? 128 : 256;
     int sms = device_sm_count();
     if (sms <= 0) { set_last_error("no CUDA device"); return ARISTOS_ERR_CUDA; }
@@ -1069,8 +1076,12 @@ aristos_status_t launch_updown_t(const void* xg, const void* w1, const void* w3,
     ARISTOS_TRY(make_map_3d(&tmB1, w2, p1.K, p1.N, p1.experts, FMT));
     ARISTOS_TRY(make_map_3d(&tmOut1, p1.out, p1.N, p1.rows_per_group, p1.groups, FMT));
     PeerMapsArg<PEERS> pm;
-    if constexpr (PEERS) memcpy(pm.m, peers.m, sizeof(pm.m));
-    else pm.unused = 0;
+    if constexpr (PEERS) {
+        memcpy(pm.m, peers.m, sizeof(pm.m));
+        memcpy(pm.base, peers.base, sizeof(pm.base));
+    } else {
+        pm.unused = 0;
+    }
     int sms = device_sm_count();
     if (sms <= 0) { set_last_error("no CUDA device"); return ARISTOS_ERR_CUDA; }
     if (grid_limit > 0 && grid_limit < sms) sms = grid_limit;
@@ -1117,8 +1128,8 @@ aristos_status_t launch_gemm_f(const void* A, const void* B0, const void* B1, co
 }
 
 aristos_status_t launch_gemm(const void* A, const void* B0, const void* B1, const FfnGemmParams& p,
-                             const PeerOutMaps& peers, int grid_limit, cudaStream_t st) {
-    switch (p.fmt) {
+                             const PeerOutMaps& peers, int grid_limit, cudaStream_t st, int fmt) {
+    switch (fmt) {
         case FMT_BF16: return launch_gemm_f<FMT_BF16>(A, B0, B1, p, peers, grid_limit, st);
         case FMT_F16: return launch_gemm_f<FMT_F16>(A, B0, B1, p, peers, grid_limit, st);
         default: return launch_gemm_f<FMT_TF32>(A, B0, B1, p, peers, grid_limit, st);
@@ -1167,7 +1178,6 @@ aristos_status_t expert_ffn_tc_sm100(const void* xg, const int32_t* count, int g
     p.row_begin = row_begin;
     p.row_end = row_end;
     p.dev_status = dev_status;
-    p.fmt = fmt;
     p.self_source = -1;
     if (ep) {
         p.first_source = ep->first_source;
@@ -1194,7 +1204,7 @@ aristos_status_t expert_ffn_tc_sm100(const void* xg, const int32_t* count, int g
                             ep->updown_scratch_ints >= (size_t)groups * ceil_div(window, BM) && !(fz && !strcmp(fz, "0")) &&
                             !(mode == TILES_SINGLE && !(fz && !strcmp(fz, "1")));
     const FfnGemmParams p_up = p;
-    if (!one_launch) ARISTOS_TRY(launch_gemm(xg, w1, gated ? w3 : w1, p, no_peers, sm_limit, st));
+    if (!one_launch) ARISTOS_TRY(launch_gemm(xg, w1, gated ? w3 : w1, p, no_peers, sm_limit, st, fmt));
     // down-projection: y = h * W2^T (h was written by the launch above: nothing left to wait for)
     p.src_flags = nullptr;
     p.N = H;
@@ -1209,7 +1219,7 @@ aristos_status_t expert_ffn_tc_sm100(const void* xg, const int32_t* count, int g
         if (peer_world > 0) {
             for (int d = 0; d < peer_world; ++d) {
                 ARISTOS_TRY(make_map_3d(&peers.m[d], ep->peer_y[d], H, rows_per_group, peer_world * experts, fmt));
-                p.peer_base[d] = masked_return() ? ep->peer_y[d] : nullptr;
+                peers.base[d] = masked_return() ? ep->peer_y[d] : nullptr;
             }
             p.peer_world = peer_world;
             p.peer_rank = ep->peer_rank;
@@ -1227,14 +1237,14 @@ aristos_status_t expert_ffn_tc_sm100(const void* xg, const int32_t* count, int g
         PeerOutMaps peers{};
         for (int d = 0; d < peer_world; ++d) {
             ARISTOS_TRY(make_map_3d(&peers.m[d], ep->peer_y[d], H, rows_per_group, peer_world * experts, fmt));
-            p.peer_base[d] = masked_return() ? ep->peer_y[d] : nullptr;
+            peers.base[d] = masked_return() ? ep->peer_y[d] : nullptr;
         }
         p.peer_world = peer_world;
         p.peer_rank = ep->peer_rank;
-        ARISTOS_TRY(launch_gemm(h_scratch, w2, w2, p, peers, sm_limit, st));
+        ARISTOS_TRY(launch_gemm(h_scratch, w2, w2, p, peers, sm_limit, st, fmt));
         return ARISTOS_OK;
     }
-    ARISTOS_TRY(launch_gemm(h_scratch, w2, w2, p, no_peers, sm_limit, st));
+    ARISTOS_TRY(launch_gemm(h_scratch, w2, w2, p, no_peers, sm_limit, st, fmt));
     return ARISTOS_OK;
 }
 
