@@ -114,6 +114,8 @@ PROTOTYPES = {
     "aristos_load_balance_stats_bytes": (_sz, [_i]),
     "aristos_load_balance_stats": (_st, [_vp, _vp, _vp, _i, _i, _i, _vp, _vp]),
     "aristos_ffn_group_order": (_i, [_i, _i, _i]),
+    "aristos_ffn_group_order_from": (_i, [_i, _i, _i, _i]),
+    "aristos_ep_dense_plan_host": (_st, [_vp, _i, _i, _i, _i, _vp, _vp, _vp]),
     "aristos_fill_normal": (_st, [_vp, C.c_int64, C.c_float, C.c_float, C.c_uint64, C.c_uint32, _i, _vp]),
 }
 

@@ -106,24 +106,28 @@ return_rows_peer_kernel(const uint4* __restrict__ y, const int32_t* __restrict__
 // From the counts of every expert at every rank (allcount[src * E + e]): where this rank's rows start inside each
 // expert's dense group at the owner (send_base[e] = rows of the lower ranks), how many rows each local expert receives
 // in all (dense_count[el]) and where each source's rows start in it (src_off[el * (world + 1) + s], s = 0 .. world).
+__host__ __device__ inline void dense_plan_expert(const int32_t* allcount, int world, int E, int E_local, int rank, int e,
+                                                  int32_t* send_base, int32_t* dense_count, int32_t* src_off) {
+    int before = 0, total = 0;
+    const int el = e - rank * E_local;
+    const bool mine = el >= 0 && el < E_local;
+    for (int s = 0; s < world; ++s) {
+        if (s == rank) before = total;
+        if (mine) src_off[el * (world + 1) + s] = total;
+        total += allcount[s * E + e];
+    }
+    send_base[e] = before;
+    if (mine) {
+        src_off[el * (world + 1) + world] = total;
+        dense_count[el] = total;
+    }
+}
+
 __global__ void dense_plan_kernel(const int32_t* __restrict__ allcount, int world, int E, int E_local, int rank,
                                   int32_t* __restrict__ send_base, int32_t* __restrict__ dense_count,
                                   int32_t* __restrict__ src_off) {
-    for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < E; e += gridDim.x * blockDim.x) {
-        int before = 0, total = 0;
-        const int el = e - rank * E_local;
-        const bool mine = el >= 0 && el < E_local;
-        for (int s = 0; s < world; ++s) {
-            if (s == rank) before = total;
-            if (mine) src_off[el * (world + 1) + s] = total;
-            total += allcount[s * E + e];
-        }
-        send_base[e] = before;
-        if (mine) {
-            src_off[el * (world + 1) + world] = total;
-            dense_count[el] = total;
-        }
-    }
+    for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < E; e += gridDim.x * blockDim.x)
+        dense_plan_expert(allcount, world, E, E_local, rank, e, send_base, dense_count, src_off);
 }
 
 }  // namespace
@@ -173,3 +177,15 @@ aristos_status_t return_rows_to_peers(const void* y, const int32_t* count, int g
 }
 
 }  // namespace aristos
+
+// Host-side run of the same plan (tests of the expert-parallel logic on CPU ranks).
+extern "C" aristos_status_t aristos_ep_dense_plan_host(const int32_t* allcount, int world, int E, int E_local, int rank,
+                                                       int32_t* send_base, int32_t* dense_count, int32_t* src_off) {
+    if (!allcount || !send_base || !dense_count || !src_off || world < 1 || E_local < 1 || E != world * E_local || rank < 0 ||
+        rank >= world) {
+        aristos::set_last_error("dense exchange plan: bad arguments");
+        return ARISTOS_ERR_INVALID_ARG;
+    }
+    for (int e = 0; e < E; ++e) aristos::dense_plan_expert(allcount, world, E, E_local, rank, e, send_base, dense_count, src_off);
+    return ARISTOS_OK;
+}

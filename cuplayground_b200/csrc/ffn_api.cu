@@ -123,6 +123,13 @@ extern "C" int aristos_ffn_group_order(int position, int groups, int experts) {
     return ordered_group(position, groups, experts);
 }
 
+extern "C" int aristos_ffn_group_order_from(int position, int groups, int experts, int first_source) {
+    if (position < 0 || groups <= 0 || position >= groups || experts <= 0 || first_source < 0 ||
+        first_source >= (groups / experts > 0 ? groups / experts : 1))
+        return -1;
+    return ordered_group(position, groups, experts, first_source);
+}
+
 extern "C" aristos_status_t aristos_ffn_set_tile_mode(int mode) {
     if (mode < -1 || mode > 3) { set_last_error("ffn_set_tile_mode: mode must be -1 .. 3"); return ARISTOS_ERR_INVALID_ARG; }
     ffn_set_tile_mode(mode);

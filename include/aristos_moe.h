@@ -372,6 +372,16 @@ ARISTOS_API void aristos_ep_flags_release(uint32_t* words, uint32_t epoch);
 /* The order in which the expert GEMMs walk `groups` row groups of `experts` experts (group g uses expert
  * g % experts): position -> group, a permutation that keeps the groups of one expert adjacent. Host-only, for tests. */
 ARISTOS_API int aristos_ffn_group_order(int position, int groups, int experts);
+/* The same order on a rank of an expert-parallel layer: inside an expert the source ranks are taken in ring order
+ * starting at first_source (the rank itself: its own rows are in its memory before the kernel starts). */
+ARISTOS_API int aristos_ffn_group_order_from(int position, int groups, int experts, int first_source);
+/* Dense packing of the rows an expert receives from all source ranks (the fp8 expert-parallel layer), host-side run of
+ * what the layer computes on the device from the all-gathered counts allcount[src * E + e]: send_base[e] (E entries) =
+ * first row of THIS rank's rows inside expert e's group at its owner (the lower ranks' rows come first); for the
+ * experts this rank owns, dense_count[el] (E_local entries) = rows received in all and src_off[el * (world + 1) + s] =
+ * first row of source s (entry `world` = the total). Host-only, for tests. */
+ARISTOS_API aristos_status_t aristos_ep_dense_plan_host(const int32_t* allcount, int world, int E, int E_local, int rank,
+                                                        int32_t* send_base, int32_t* dense_count, int32_t* src_off);
 /* Synthetic inputs: Philox4x32-10 + Box-Muller normal fill (the reference draws inputs from Philox,
  * main.cu:22-31). Element i uses counter (i/4, 0, stream_id, 0), key = seed, output word i%4. */
 ARISTOS_API aristos_status_t aristos_fill_normal(void* dst, int64_t n, float mean, float std, uint64_t seed,

@@ -183,18 +183,18 @@ def test_ffn_tile_order_is_a_bijection(cp, mt, nt, band):
     assert lib.aristos_ffn_tile_coord(mt * nt, mt, nt, band, C.byref(m), C.byref(n)) == -1
 
 
-def test_source_order_starts_with_the_own_rank():
-    """Host check of the walking order of the row groups in the expert-parallel layer: expert-major, and inside an
-    expert the sources in ring order from the rank itself (mirrors ordered_group of csrc/common.cuh)."""
-    def ordered(v, groups, experts, first):
-        sources = groups // experts
-        e, i = divmod(v, sources)
-        return ((i + first) % sources) * experts + e
+def test_source_order_starts_with_the_own_rank(cp):
+    """The walking order of the row groups on a rank of the expert-parallel layer: expert-major, and inside an expert
+    the sources in ring order from the rank itself."""
+    lib = cp._lib.load()
     groups, experts = 8, 2
     for first in range(4):
-        order = [ordered(v, groups, experts, first) for v in range(groups)]
+        order = [lib.aristos_ffn_group_order_from(v, groups, experts, first) for v in range(groups)]
         assert sorted(order) == list(range(groups))
-        assert order[0] == first * experts and order[4] == first * experts + 1
+        assert order[0] == first * experts and order[4] == first * experts + 1          # own rows first, per expert
+        assert [g % experts for g in order] == [0, 0, 0, 0, 1, 1, 1, 1]               # experts stay adjacent
+        assert [g // experts for g in order[:4]] == [(first + i) % 4 for i in range(4)]
+    assert lib.aristos_ffn_group_order_from(0, 8, 2, 4) == -1
 
 
 def test_transport_agreement(cp):

@@ -322,3 +322,38 @@ def test_flag_comparison_is_cyclic():
     assert lib.aristos_ep_flags_pending(ptr, 0xFFFFFFFF, 2, 0, 2) == 0
     assert lib.aristos_ep_flags_pending(ptr, 1, 2, 0, 2) == 0b01
     assert lib.aristos_ep_flags_pending(ptr, 3, 2, 0, 2) == 0b11
+
+
+def test_dense_packing_plan_is_consistent_across_ranks():
+    """fp8 expert parallel: from the all-gathered counts every rank computes where its rows start inside each expert's
+    dense group at the owner, and every owner where each source's rows start. The senders' start rows must tile the
+    owners' groups exactly (no gap, no overlap), whatever the counts."""
+    import cuplayground_b200 as cp
+    lib = cp._lib.load()
+    rng = np.random.default_rng(5)
+    for world, E_local in ((2, 3), (4, 2), (8, 4)):
+        E = world * E_local
+        allcount = rng.integers(0, 300, size=(world, E)).astype(np.int32)
+        allcount[rng.integers(0, world), rng.integers(0, E)] = 0
+        plans = []
+        for rank in range(world):
+            send_base = np.full(E, -1, np.int32)
+            dense_count = np.full(E_local, -1, np.int32)
+            src_off = np.full(E_local * (world + 1), -1, np.int32)
+            st = lib.aristos_ep_dense_plan_host(allcount.ctypes.data_as(C.c_void_p), world, E, E_local, rank,
+                                                send_base.ctypes.data_as(C.c_void_p),
+                                                dense_count.ctypes.data_as(C.c_void_p),
+                                                src_off.ctypes.data_as(C.c_void_p))
+            assert st == 0
+            plans.append((send_base, dense_count, src_off.reshape(E_local, world + 1)))
+        for e in range(E):
+            owner, el = divmod(e, E_local)
+            _, dense_count, src_off = plans[owner]
+            assert dense_count[el] == allcount[:, e].sum()
+            for s in range(world):
+                # sender s starts where the owner expects source s, and the next source starts right behind its rows
+                assert plans[s][0][e] == src_off[el, s]
+                assert src_off[el, s + 1] == src_off[el, s] + allcount[s, e]
+    bad = np.zeros(4, np.int32)
+    assert lib.aristos_ep_dense_plan_host(bad.ctypes.data_as(C.c_void_p), 2, 5, 2, 0, bad.ctypes.data_as(C.c_void_p),
+                                          bad.ctypes.data_as(C.c_void_p), bad.ctypes.data_as(C.c_void_p)) == 1
