@@ -37,8 +37,10 @@ constexpr int F8_A_BYTES = F8_BM * F8_KB;        // 16 KB
 constexpr int F8_B_BYTES = F8_BN * F8_KB;        // 32 KB: two boxes of 128 weight rows
 constexpr int F8_STAGE_BYTES = F8_A_BYTES + F8_B_BYTES;
 constexpr int F8_TBUFS = 2;                      // TMEM accumulator buffers (2 x 256 columns)
-constexpr int F8_THREADS = 352;                  // producer warp, MMA warp, 8 promotion warps, second MMA warp
-constexpr int F8_EPI_THREADS = 256;
+// Promotion warps per TMEM lane quarter: each owns 8 / SUBS of the eight 32-column chunks of the 256-column tile
+// (chunks sub, sub + SUBS, ...). Roles: warp 0 producer, warp 1 MMA, warps 2 .. 2 + 4 SUBS promotion, then the second MMA
+// warp. Two per quarter is the measured optimum: with four, 608 threads leave 96 registers each and the kernel slows down.
+constexpr int f8_threads(int subs) { return 32 * (3 + 4 * subs); }
 constexpr int F8_MAX_GROUPS = 1024;
 constexpr int F8_AUX_BYTES = 256 + (F8_MAX_GROUPS + 1) * 4;
 constexpr int F8_SMEM_BYTES = 1024 + F8_STAGES * F8_STAGE_BYTES + F8_AUX_BYTES;
@@ -53,6 +55,12 @@ struct Fp8GemmParams {
     const float* sb1;     // SwiGLU: scales of the up projection's weights
     __nv_bfloat16* out;   // [groups * rows_per_group][N]
     int32_t* dev_status;
+};
+static_assert(sizeof(Fp8GemmParams) <= 128, "Fp8GemmParams: keep the kernel argument within 128 bytes");
+
+// Expert-parallel output, a kernel argument of its own (the hot parameters above stay within 128 bytes: a larger
+// struct changes how the compiler treats the argument).
+struct Fp8PeerArgs {
     // peer_world > 0: rows of group g = src * experts + e are stored into rank src's buffer peer_out[src]
     // ((peer_world * experts, rows_per_group, N), mapped into this process) as group peer_rank * experts + e
     int peer_world, peer_rank;
@@ -86,9 +94,14 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
     return *reinterpret_cast<uint32_t*>(&t);
 }
 
-__global__ void __launch_bounds__(F8_THREADS, 1)
+template <int SUBS>
+__global__ void __launch_bounds__(f8_threads(SUBS), 1)
 ffn_fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB0,
-                            const __grid_constant__ CUtensorMap tmB1, const Fp8GemmParams p) {
+                            const __grid_constant__ CUtensorMap tmB1, const Fp8GemmParams p,
+                            const __grid_constant__ Fp8PeerArgs pa) {
+    constexpr int F8_EPI_THREADS = 128 * SUBS;
+    constexpr int CH = 8 / SUBS;                           // 32-column chunks per promotion thread
+    constexpr int MMA2_WARP = 2 + 4 * SUBS;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* aux = smem + F8_STAGES * F8_STAGE_BYTES;
@@ -183,7 +196,7 @@ ffn_fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
             }
         }
         __syncwarp();
-    } else if (warp == 1 || warp == 10) {
+    } else if (warp == 1 || warp == MMA2_WARP) {
         // ------------------------------------------------------------------ MMA issuers: one TMEM buffer per K block.
         // Issuing the four MMAs and the commit of one K block costs the issuing thread more cycles than the tensor
         // core needs to run them, so two warps take turns: K block number it goes to warp it % 2 and to TMEM buffer
@@ -216,13 +229,13 @@ ffn_fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
             }
         }
         __syncwarp();
-    } else if (warp >= 2 && warp < 10) {
-        // ------------------------------------------------------------------ promotion + epilogue (warps 2..9)
-        // A thread owns one accumulator row and the four 32-column chunks half, half + 2, half + 4, half + 6 of the
-        // 256-column tile: the first two lie in the tile's first 128 columns (gate, or weight-scale block n0 / 128),
-        // the last two in the second 128 (up, or the next scale block).
+    } else if (warp >= 2 && warp < MMA2_WARP) {
+        // ------------------------------------------------------------------ promotion + epilogue
+        // A thread owns one accumulator row and the CH 32-column chunks half, half + SUBS, ... of the 256-column tile:
+        // the first CH / 2 lie in the tile's first 128 columns (gate, or weight-scale block n0 / 128), the others in
+        // the second 128 (up, or the next scale block).
         const int quarter = warp & 3;                       // TMEM lanes this warp may read
-        const int half = (warp - 2) >> 2;
+        const int half = (warp - 2) >> 2;                   // 0 .. SUBS - 1
         const int row_in_tile = quarter * 32 + lane;
         int vg = 0, tbuf = 0, rstage = 0;
         uint32_t tphase = 0;
@@ -243,9 +256,9 @@ ffn_fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
             const float* sb0_row = p.sb0 + ((size_t)e * nblk + blk) * kblocks;
             const float* sb1_row = p.gated ? p.sb1 + ((size_t)e * nblk + blk) * kblocks
                                            : p.sb0 + ((size_t)e * nblk + min(blk + 1, nblk - 1)) * kblocks;
-            float2 acc[4][16];                               // chunk j = half + 2 j, 32 columns as 16 pairs
+            float2 acc[CH][16];                              // chunk j = half + SUBS j, 32 columns as 16 pairs
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
+            for (int j = 0; j < CH; ++j)
 #pragma unroll
                 for (int i = 0; i < 16; ++i) acc[j][i] = make_float2(0.0f, 0.0f);
             for (int kb = 0; kb < kblocks; ++kb) {
@@ -260,21 +273,22 @@ ffn_fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
                 if (++rstage == F8_STAGES) rstage = 0;
                 ptx::tcgen05_fence_after();
                 const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + tbuf * F8_BN + half * 32;
-                // eight 16-column loads, one in flight while the previous one is accumulated
+                // 2 CH 16-column loads, one in flight while the previous one is accumulated
                 uint32_t v[2][16];
                 ptx::tmem_ld_32x32b_x16(taddr, v[0]);
                 ptx::tmem_ld_wait();
 #pragma unroll
-                for (int s = 0; s < 8; ++s) {
-                    if (s + 1 < 8) ptx::tmem_ld_32x32b_x16(taddr + ((s + 1) >> 1) * 64 + ((s + 1) & 1) * 16, v[(s + 1) & 1]);
-                    const float w = s < 4 ? w_lo : w_hi;
+                for (int s = 0; s < 2 * CH; ++s) {
+                    if (s + 1 < 2 * CH)
+                        ptx::tmem_ld_32x32b_x16(taddr + ((s + 1) >> 1) * (32 * SUBS) + ((s + 1) & 1) * 16, v[(s + 1) & 1]);
+                    const float w = s < CH ? w_lo : w_hi;
                     const float2 w2 = make_float2(w, w);
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
                         const float2 x2 = make_float2(__uint_as_float(v[s & 1][2 * i]), __uint_as_float(v[s & 1][2 * i + 1]));
                         acc[s >> 1][(s & 1) * 8 + i] = __ffma2_rn(x2, w2, acc[s >> 1][(s & 1) * 8 + i]);
                     }
-                    if (s + 1 < 8) {
+                    if (s + 1 < 2 * CH) {
                         ptx::tmem_ld_wait();
                     } else {
                         ptx::tcgen05_fence_before();
@@ -288,39 +302,40 @@ ffn_fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
                 __nv_bfloat16* obase = p.out;
                 int og = g;
                 int orows = p.rows_per_group, orow_idx = row;
-                if (p.peer_world > 0 && p.src_off != nullptr) {
+                if (pa.peer_world > 0 && pa.src_off != nullptr) {
                     // dense group: find the source rank of this row, return it to that rank's own numbering
-                    const int32_t* off = p.src_off + g * (p.peer_world + 1);
+                    const int32_t* off = pa.src_off + g * (pa.peer_world + 1);
                     int src = 0;
-                    while (src + 1 < p.peer_world && row >= __ldg(off + src + 1)) ++src;
-                    obase = p.peer_out[src];
-                    og = p.peer_rank * p.experts + g;
-                    orows = p.ret_rows;
+                    while (src + 1 < pa.peer_world && row >= __ldg(off + src + 1)) ++src;
+                    obase = pa.peer_out[src];
+                    og = pa.peer_rank * p.experts + g;
+                    orows = pa.ret_rows;
                     orow_idx = row - __ldg(off + src);
-                } else if (p.peer_world > 0) {     // the store is the return all-to-all: straight into the source rank
+                } else if (pa.peer_world > 0) {    // the store is the return all-to-all: straight into the source rank
                     const int src = g / p.experts;
-                    obase = p.peer_out[src];
-                    og = p.peer_rank * p.experts + (g - src * p.experts);
+                    obase = pa.peer_out[src];
+                    og = pa.peer_rank * p.experts + (g - src * p.experts);
                 }
                 __nv_bfloat16* orow = obase + ((size_t)og * orows + orow_idx) * p.N + n0;
                 if (p.gated) {
-                    // gate chunk half + 2 j pairs with up chunk half + 2 j + 4: 32 outputs each for j = 0, 1
+                    // gate chunk half + SUBS j pairs with up chunk half + SUBS j + 4: 32 outputs each
 #pragma unroll
-                    for (int j = 0; j < 2; ++j) {
-                        const int col = (half + 2 * j) * 32;
+                    for (int j = 0; j < CH / 2; ++j) {
+                        const int col = (half + SUBS * j) * 32;
                         if (n0 + col >= p.N) break;
                         uint32_t o[16];
 #pragma unroll
                         for (int i = 0; i < 16; ++i)
-                            o[i] = pack_bf16x2(act_silu(acc[j][i].x) * acc[j + 2][i].x, act_silu(acc[j][i].y) * acc[j + 2][i].y);
+                            o[i] = pack_bf16x2(act_silu(acc[j][i].x) * acc[j + CH / 2][i].x,
+                                               act_silu(acc[j][i].y) * acc[j + CH / 2][i].y);
                         uint4* dst = reinterpret_cast<uint4*>(orow + col);
 #pragma unroll
                         for (int i = 0; i < 4; ++i) dst[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
                     }
                 } else {
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const int col = (half + 2 * j) * 32;
+                    for (int j = 0; j < CH; ++j) {
+                        const int col = (half + SUBS * j) * 32;
                         if (n0 + col >= p.N) break;
                         uint32_t o[16];
 #pragma unroll
@@ -471,13 +486,22 @@ aristos_status_t make_map_u8(CUtensorMap* tm, const void* base, int K, int rows,
     return encode_map_3d(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, base, K, rows, outer, box_rows);
 }
 
-aristos_status_t launch_fp8_gemm(const void* A, const void* B0, const void* B1, const Fp8GemmParams& p, int grid_limit,
-                                 cudaStream_t st) {
+aristos_status_t launch_fp8_gemm(const void* A, const void* B0, const void* B1, const Fp8GemmParams& p,
+                                 const Fp8PeerArgs& pa, int grid_limit, cudaStream_t st) {
     CUtensorMap tmA, tmB0, tmB1;
     ARISTOS_TRY(make_map_u8(&tmA, A, p.K, p.rows_per_group, p.groups, 128));
     ARISTOS_TRY(make_map_u8(&tmB0, B0, p.K, p.N, p.experts, 128));
     ARISTOS_TRY(make_map_u8(&tmB1, B1, p.K, p.N, p.experts, 128));
-    ARISTOS_CUDA_TRY(cudaFuncSetAttribute(ffn_fp8_grouped_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    // promotion warps per lane quarter: 2 (ARISTOS_FP8_PROMOTION_WARPS=4 selects four: measured slower, 2.31 ms
+    // against 1.92 ms for 32 experts x 1024 rows, H 7168, I 2048 - 608 threads leave each 96 registers)
+    static int subs = 0;
+    if (subs == 0) {
+        const char* env = getenv("ARISTOS_FP8_PROMOTION_WARPS");
+        subs = (env && atoi(env) == 4) ? 4 : 2;
+    }
+    ARISTOS_CUDA_TRY(cudaFuncSetAttribute(ffn_fp8_grouped_gemm_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          F8_SMEM_BYTES));
+    ARISTOS_CUDA_TRY(cudaFuncSetAttribute(ffn_fp8_grouped_gemm_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           F8_SMEM_BYTES));
     const int out_w = p.gated ? 128 : 256;
     int sms = device_sm_count();
@@ -486,7 +510,8 @@ aristos_status_t launch_fp8_gemm(const void* A, const void* B0, const void* B1, 
     const int64_t bound = (int64_t)p.groups * ceil_div(p.row_end - p.row_begin, F8_BM) * ceil_div(p.N, out_w);
     const int grid = (int)(bound < sms ? bound : sms);
     if (grid <= 0) return ARISTOS_OK;
-    ffn_fp8_grouped_gemm_kernel<<<grid, F8_THREADS, F8_SMEM_BYTES, st>>>(tmA, tmB0, tmB1, p);
+    if (subs == 2) ffn_fp8_grouped_gemm_kernel<2><<<grid, f8_threads(2), F8_SMEM_BYTES, st>>>(tmA, tmB0, tmB1, p, pa);
+    else ffn_fp8_grouped_gemm_kernel<4><<<grid, f8_threads(4), F8_SMEM_BYTES, st>>>(tmA, tmB0, tmB1, p, pa);
     ARISTOS_COUNT_LAUNCH();
     ARISTOS_CUDA_TRY(cudaGetLastError());
     return ARISTOS_OK;
@@ -523,7 +548,8 @@ aristos_status_t expert_ffn_fp8_sm100(const void* xq, const float* sx, const int
     p.N = I; p.K = H; p.gated = gated ? 1 : 0; p.act = hidden_act;
     p.sa = sx; p.sb0 = s1; p.sb1 = gated ? s3 : s1;
     p.out = static_cast<__nv_bfloat16*>(h);
-    ARISTOS_TRY(launch_fp8_gemm(xq, w1q, gated ? w3q : w1q, p, sm_limit, st));
+    Fp8PeerArgs pa{};
+    ARISTOS_TRY(launch_fp8_gemm(xq, w1q, gated ? w3q : w1q, p, pa, sm_limit, st));
     // hidden activations: bf16 -> e4m3 per row and 128 columns (valid rows only)
     quantize_group_rows_fp8_kernel<__nv_bfloat16><<<device_sm_count() * 4, 256, 0, st>>>(
         static_cast<const __nv_bfloat16*>(h), count, groups, rows_per_group, I, static_cast<uint8_t*>(hq), sh);
@@ -531,12 +557,12 @@ aristos_status_t expert_ffn_fp8_sm100(const void* xq, const float* sx, const int
     p.N = H; p.K = I; p.gated = 0; p.act = ARISTOS_ACT_IDENTITY;
     p.sa = sh; p.sb0 = s2; p.sb1 = s2;
     p.out = static_cast<__nv_bfloat16*>(y);
-    p.peer_world = peer_world;
-    p.peer_rank = peer_rank;
-    p.src_off = dense_src_off;
-    p.ret_rows = dense_ret_rows;
-    for (int d = 0; d < peer_world; ++d) p.peer_out[d] = static_cast<__nv_bfloat16*>(peer_y[d]);
-    ARISTOS_TRY(launch_fp8_gemm(hq, w2q, w2q, p, sm_limit, st));
+    pa.peer_world = peer_world;
+    pa.peer_rank = peer_rank;
+    pa.src_off = dense_src_off;
+    pa.ret_rows = dense_ret_rows;
+    for (int d = 0; d < peer_world; ++d) pa.peer_out[d] = static_cast<__nv_bfloat16*>(peer_y[d]);
+    ARISTOS_TRY(launch_fp8_gemm(hq, w2q, w2q, p, pa, sm_limit, st));
     ARISTOS_CUDA_TRY(cudaGetLastError());
     return ARISTOS_OK;
 }
