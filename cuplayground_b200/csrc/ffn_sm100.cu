@@ -946,7 +946,8 @@ aristos_status_t make_map_3d(CUtensorMap* tm, const void* base, int K, int rows,
 // for the same work (98-99 %). Pairs pad every group to whole 256-row tiles (128 wasted rows per group on average).
 // The alternative - the pair kernel computes whole tiles only and a second, single-CTA launch finishes the < 256
 // remaining rows of every group - wastes half as many rows but its few tiles fill their waves poorly: measured on
-// 8 groups of about 4096 rows, the tail launches took 0.55 ms for 3 % of the rows where padding costs 0.25 ms.
+// 8 groups of about 4096 rows, the tail launches took 0.55 ms for 3 % of the rows and the two forms came out equal
+// (8.04 against 8.08 ms of GEMM time per forward); the padded form needs half the launches.
 //   TILES_AUTO    padded pairs where the row window holds at least 1024 rows, else single-CTA tiles
 //   TILES_SINGLE  single-CTA tiles only
 //   TILES_PAIR    pairs + single-CTA tail launch, for every window
