@@ -21,6 +21,9 @@
 #include <cuda.h>
 #include <cuda_fp8.h>
 
+#include <cstdlib>
+#include <cstring>
+
 #include "common.cuh"
 #include "ptx_sm100.cuh"
 #include "tensor_map.cuh"
@@ -362,6 +365,322 @@ ffn_fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
     }
 }
 
+// ---- the same GEMM with warpgroup roles -----------------------------------------------------------------------------
+// 384 threads: warpgroup 0 = TMA producer (warp 0), the two MMA issuers (warps 1, 2) and an idle warp; warpgroups 1-2
+// = the eight promotion warps. Warpgroup 0 gives registers back (setmaxnreg) and the promotion warps take them, which
+// pays for 64 staging registers beside the 128 accumulators: a K block is drained by four 32-column tcgen05.ld per
+// thread with one always in flight behind the packed FMAs of the previous one, and the first load of the next K
+// block is issued before the last FMAs of this one. (With 16-column loads and 168 registers the promotion of a block
+// took about twice the tensor core's time for it: eight exposed TMEM round trips per block.)
+// The output leaves through a small per-warp staging area so that a store instruction covers 8 rows x 64 bytes of
+// full 32-byte sectors instead of 32 rows x 16 bytes.
+constexpr int F8W_THREADS = 384;
+constexpr int F8W_PROMO_THREADS = 256;
+constexpr int F8W_AUX_BYTES = (F8_AUX_BYTES + 127) & ~127;
+constexpr int F8W_OUT_BYTES_PER_WARP = 32 * 64;              // 32 rows x 32 bf16
+constexpr int F8W_SMEM_BYTES = 1024 + F8_STAGES * F8_STAGE_BYTES + F8W_AUX_BYTES + 8 * F8W_OUT_BYTES_PER_WARP;
+static_assert(F8W_SMEM_BYTES <= 227 * 1024, "fp8 GEMM: shared memory");
+
+__global__ void __launch_bounds__(F8W_THREADS, 1)
+ffn_fp8_grouped_gemm_wg_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB0,
+                               const __grid_constant__ CUtensorMap tmB1, const Fp8GemmParams p,
+                               const __grid_constant__ Fp8PeerArgs pa) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* aux = smem + F8_STAGES * F8_STAGE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(aux);     // full[S], empty[S], tfull[2], tempty[2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aux + 192);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(aux + 196);
+    int* prefix = reinterpret_cast<int*>(aux + 256);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t bar_full = ptx::smem_u32(bars);
+    const uint32_t bar_empty = bar_full + 8 * F8_STAGES;
+    const uint32_t bar_tfull = bar_empty + 8 * F8_STAGES;
+    const uint32_t bar_tempty = bar_tfull + 8 * F8_TBUFS;
+    const uint32_t smem_base = ptx::smem_u32(smem);
+
+    const int out_w = p.gated ? 128 : 256;
+    const int n_tiles = (p.N + out_w - 1) / out_w;
+    const int window = p.row_end - p.row_begin;
+    const int kblocks = p.K / F8_KB;
+    const int nblk = (p.N + 127) / 128;                    // weight-scale blocks along N
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < F8_STAGES; ++s) {
+            ptx::mbar_init(bar_full + 8 * s, 1);
+            ptx::mbar_init(bar_empty + 8 * s, 1);
+        }
+        for (int b = 0; b < F8_TBUFS; ++b) {
+            ptx::mbar_init(bar_tfull + 8 * b, 1);
+            ptx::mbar_init(bar_tempty + 8 * b, F8W_PROMO_THREADS);
+        }
+        *abort_flag = 0;
+        ptx::fence_mbar_init();
+    }
+    if (warp == 0) {
+        int running = 0;
+        if (lane == 0) prefix[0] = 0;
+        for (int g0 = 0; g0 < p.groups; g0 += 32) {
+            const int g = g0 + lane;
+            int v = 0;
+            if (g < p.groups) {
+                int rows = p.count[ordered_group(g, p.groups, p.experts)] - p.row_begin;
+                rows = max(0, min(rows, window));
+                v = ((rows + F8_BM - 1) / F8_BM) * n_tiles;
+            }
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const int o = __shfl_up_sync(0xffffffffu, v, d);
+                if (lane >= d) v += o;
+            }
+            if (g < p.groups) prefix[g + 1] = running + v;
+            running += __shfl_sync(0xffffffffu, v, 31);
+        }
+    } else if (warp == 1) {
+        ptx::tmem_alloc(ptx::smem_u32(tmem_slot), F8_TBUFS * F8_BN);
+    }
+    ptx::tcgen05_fence_before();
+    __syncthreads();
+    ptx::tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const int total_tiles = prefix[p.groups];
+
+    if (warp < 4) {
+        ptx::warpgroup_reg_release<40>();
+        if (warp == 0) {
+            // -------------------------------------------------------------------------------------- TMA producer
+            if (ptx::elect_one()) {
+                ptx::prefetch_tensormap(&tmA);
+                ptx::prefetch_tensormap(&tmB0);
+                ptx::prefetch_tensormap(&tmB1);
+                int stage = 0;
+                uint32_t phase = 0;
+                int vg = 0;
+                bool ok = true;
+                for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+                    while (tile >= prefix[vg + 1]) ++vg;
+                    const int g = ordered_group(vg, p.groups, p.experts);
+                    const int local = tile - prefix[vg];
+                    const int mt = (prefix[vg + 1] - prefix[vg]) / n_tiles;
+                    const int m0 = p.row_begin + (local % mt) * F8_BM;
+                    const int n0 = (local / mt) * out_w;
+                    const int e = g % p.experts;
+                    const int n1 = p.gated ? n0 : n0 + 128;     // second 128-row box of B
+                    for (int kb = 0; kb < kblocks; ++kb) {
+                        ok = ptx::mbar_wait_bounded(bar_empty + 8 * stage, phase ^ 1u, abort_flag, p.dev_status);
+                        if (!ok) break;
+                        const uint32_t full = bar_full + 8 * stage;
+                        const uint32_t sa = smem_base + stage * F8_STAGE_BYTES;
+                        ptx::mbar_arrive_expect_tx(full, F8_STAGE_BYTES);
+                        ptx::tma_load_3d(sa, &tmA, kb * F8_KB, m0, g, full);
+                        ptx::tma_load_3d(sa + F8_A_BYTES, &tmB0, kb * F8_KB, n0, e, full);
+                        ptx::tma_load_3d(sa + F8_A_BYTES + F8_B_BYTES / 2, &tmB1, kb * F8_KB, n1, e, full);
+                        if (++stage == F8_STAGES) { stage = 0; phase ^= 1u; }
+                    }
+                }
+            }
+            __syncwarp();
+        } else if (warp <= 2) {
+            // ------------------------------------------------------------- MMA issuers: one TMEM buffer per K block,
+            // K block number it goes to warp 1 + it % 2 and to TMEM buffer it % 2 (a commit covers its own thread's MMAs)
+            if (ptx::elect_one()) {
+                constexpr uint32_t idesc = umma_idesc_e4m3(F8_BM, F8_BN);
+                const int me = warp - 1;
+                int it = 0;
+                bool ok = true;
+                for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+                    for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                        if ((it & 1) != me) continue;
+                        const int tbuf = it & 1, stage = it % F8_STAGES;
+                        const uint32_t tphase = (it >> 1) & 1u, phase = (it / F8_STAGES) & 1u;
+                        ok = ptx::mbar_wait_bounded(bar_tempty + 8 * tbuf, tphase ^ 1u, abort_flag, p.dev_status);
+                        if (!ok) break;
+                        ok = ptx::mbar_wait_bounded(bar_full + 8 * stage, phase, abort_flag, p.dev_status);
+                        if (!ok) break;
+                        ptx::tcgen05_fence_after();
+                        const uint32_t sa = smem_base + stage * F8_STAGE_BYTES;
+                        const uint64_t da = ptx::umma_desc_k_sw128(sa);
+                        const uint64_t db = ptx::umma_desc_k_sw128(sa + F8_A_BYTES);
+                        const uint32_t tmem_d = tmem_base + tbuf * F8_BN;
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)            // K = 32 elements = 32 bytes per instruction
+                            umma_f8(tmem_d, da + 2 * k, db + 2 * k, idesc, k != 0 ? 1u : 0u);
+                        ptx::umma_commit(bar_tfull + 8 * tbuf);
+                    }
+                }
+            }
+            __syncwarp();
+        }
+    } else {
+        ptx::warpgroup_reg_acquire<232>();
+        // ------------------------------------------------------------------------------ promotion + epilogue
+        // A thread owns one accumulator row and the 32-column chunks half, half + 2, half + 4, half + 6 of the
+        // 256-column tile: two in the tile's first 128 columns (gate, or weight-scale block n0 / 128), two in the
+        // second 128 (up, or the next scale block).
+        const int pw = warp - 4;
+        const int quarter = warp & 3;                       // TMEM lanes this warp may read
+        const int half = pw >> 2;
+        const int row_in_tile = quarter * 32 + lane;
+        const uint32_t out_stage = smem_base + F8_STAGES * F8_STAGE_BYTES + F8W_AUX_BYTES + pw * F8W_OUT_BYTES_PER_WARP;
+        const uint32_t lane_taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + half * 32;
+        int vg = 0, tbuf = 0, rstage = 0;
+        uint32_t tphase = 0;
+        bool ok = true;
+        uint32_t v[2][32];
+        for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+            while (tile >= prefix[vg + 1]) ++vg;
+            const int g = ordered_group(vg, p.groups, p.experts);
+            const int local = tile - prefix[vg];
+            const int mt = (prefix[vg + 1] - prefix[vg]) / n_tiles;
+            const int m0 = p.row_begin + (local % mt) * F8_BM;
+            const int n0 = (local / mt) * out_w;
+            const int e = g % p.experts;
+            const int row = m0 + row_in_tile;
+            const int row_limit = min(p.count[g], p.row_end);
+            const bool row_ok = row < row_limit;
+            const float* sa_row = p.sa + ((size_t)g * p.rows_per_group + min(row, p.rows_per_group - 1)) * kblocks;
+            const int blk = n0 / 128;
+            const float* sb0_row = p.sb0 + ((size_t)e * nblk + blk) * kblocks;
+            const float* sb1_row = p.gated ? p.sb1 + ((size_t)e * nblk + blk) * kblocks
+                                           : p.sb0 + ((size_t)e * nblk + min(blk + 1, nblk - 1)) * kblocks;
+            float2 acc[4][16];                               // chunk j = half + 2 j, 32 columns as 16 pairs
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+#pragma unroll
+                for (int i = 0; i < 16; ++i) acc[j][i] = make_float2(0.0f, 0.0f);
+            float w_lo, w_hi;
+            {
+                const float sa = __ldg(sa_row);
+                w_lo = sa * __ldg(sb0_row);                  // columns 0..127
+                w_hi = sa * __ldg(sb1_row);                  // columns 128..255
+            }
+            // first K block of the tile: wait for its MMAs, hand its shared-memory stage back, start the first load
+            ok = ptx::mbar_wait_bounded(bar_tfull + 8 * tbuf, tphase, abort_flag, p.dev_status);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            if (threadIdx.x == 128) ptx::mbar_arrive(bar_empty + 8 * rstage);
+            if (++rstage == F8_STAGES) rstage = 0;
+            ptx::tcgen05_fence_after();
+            ptx::tmem_ld_32x32b_x32(lane_taddr + tbuf * F8_BN, v[0]);
+            for (int kb = 0; kb < kblocks; ++kb) {
+                float nw_lo = 0.0f, nw_hi = 0.0f;
+                if (kb + 1 < kblocks) {
+                    const float sa = __ldg(sa_row + kb + 1);
+                    nw_lo = sa * __ldg(sb0_row + kb + 1);
+                    nw_hi = sa * __ldg(sb1_row + kb + 1);
+                }
+#pragma unroll
+                for (int s = 0; s < 4; ++s) {
+                    ptx::tmem_ld_wait();                      // chunk s of this block is in v[s & 1]
+                    if (s < 3) {
+                        ptx::tmem_ld_32x32b_x32(lane_taddr + tbuf * F8_BN + (s + 1) * 64, v[(s + 1) & 1]);
+                    } else {
+                        // every read of this buffer is complete: the tensor core may refill it; then on to the next
+                        // block's buffer, whose first chunk travels while the last chunk of this one is accumulated
+                        ptx::tcgen05_fence_before();
+                        ptx::mbar_arrive(bar_tempty + 8 * tbuf);
+                        if (++tbuf == F8_TBUFS) { tbuf = 0; tphase ^= 1u; }
+                        if (kb + 1 < kblocks) {
+                            ok = ptx::mbar_wait_bounded(bar_tfull + 8 * tbuf, tphase, abort_flag, p.dev_status);
+                            ok = __all_sync(0xffffffffu, ok);
+                            if (ok) {
+                                if (threadIdx.x == 128) ptx::mbar_arrive(bar_empty + 8 * rstage);
+                                if (++rstage == F8_STAGES) rstage = 0;
+                                ptx::tcgen05_fence_after();
+                                ptx::tmem_ld_32x32b_x32(lane_taddr + tbuf * F8_BN, v[0]);
+                            }
+                        }
+                    }
+                    const float w = s < 2 ? w_lo : w_hi;
+                    const float2 w2 = make_float2(w, w);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const float2 x2 = make_float2(__uint_as_float(v[s & 1][2 * i]), __uint_as_float(v[s & 1][2 * i + 1]));
+                        acc[s][i] = __ffma2_rn(x2, w2, acc[s][i]);
+                    }
+                }
+                if (!ok) break;
+                w_lo = nw_lo;
+                w_hi = nw_hi;
+            }
+            if (!ok) break;
+            // ---- epilogue: every lane knows where its own row goes; rows leave 8 at a time, 64 bytes each
+            __nv_bfloat16* my_dst = nullptr;
+            if (row_ok) {
+                __nv_bfloat16* obase = p.out;
+                int og = g;
+                int orows = p.rows_per_group, orow_idx = row;
+                if (pa.peer_world > 0 && pa.src_off != nullptr) {
+                    // dense group: find the source rank of this row, return it to that rank's own numbering
+                    const int32_t* off = pa.src_off + g * (pa.peer_world + 1);
+                    int src = 0;
+                    while (src + 1 < pa.peer_world && row >= __ldg(off + src + 1)) ++src;
+                    obase = pa.peer_out[src];
+                    og = pa.peer_rank * p.experts + g;
+                    orows = pa.ret_rows;
+                    orow_idx = row - __ldg(off + src);
+                } else if (pa.peer_world > 0) {    // the store is the return all-to-all: straight into the source rank
+                    const int src = g / p.experts;
+                    obase = pa.peer_out[src];
+                    og = pa.peer_rank * p.experts + (g - src * p.experts);
+                }
+                my_dst = obase + ((size_t)og * orows + orow_idx) * p.N + n0;
+            }
+            __nv_bfloat16* dst4[4];                          // rows it * 8 + lane / 4 of this warp's 32
+#pragma unroll
+            for (int it = 0; it < 4; ++it)
+                dst4[it] = reinterpret_cast<__nv_bfloat16*>(
+                    __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(my_dst), it * 8 + (lane >> 2)));
+            const int unit = lane & 3;
+            const int nchunks = p.gated ? 2 : 4;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if (j >= nchunks) break;
+                const int col = (half + 2 * j) * 32;
+                if (n0 + col >= p.N) break;
+                uint32_t o[16];
+                if (p.gated) {
+                    // gate chunk half + 2 j pairs with up chunk half + 2 j + 4
+                    const int ju = (j + 2) & 3;
+#pragma unroll
+                    for (int i = 0; i < 16; ++i)
+                        o[i] = pack_bf16x2(act_silu(acc[j][i].x) * acc[ju][i].x, act_silu(acc[j][i].y) * acc[ju][i].y);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        float v0 = acc[j][i].x, v1 = acc[j][i].y;
+                        if (p.act == ARISTOS_ACT_RELU) { v0 = act_relu(v0); v1 = act_relu(v1); }
+                        else if (p.act == ARISTOS_ACT_GELU) { v0 = act_gelu(v0); v1 = act_gelu(v1); }
+                        o[i] = pack_bf16x2(v0, v1);
+                    }
+                }
+                // row `lane`, 16-byte unit u lands at unit u ^ ((lane / 2) % 4): neither side has bank conflicts
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    ptx::st_shared_v4(out_stage + lane * 64 + ((u ^ ((lane >> 1) & 3)) << 4), o[4 * u], o[4 * u + 1],
+                                      o[4 * u + 2], o[4 * u + 3]);
+                __syncwarp();
+#pragma unroll
+                for (int it = 0; it < 4; ++it) {
+                    const int r = it * 8 + (lane >> 2);
+                    const uint4 val = ptx::ld_shared_v4(out_stage + r * 64 + ((unit ^ ((r >> 1) & 3)) << 4));
+                    if (dst4[it] != nullptr) *reinterpret_cast<uint4*>(dst4[it] + col + unit * 8) = val;
+                }
+                __syncwarp();
+            }
+        }
+        ptx::tmem_ld_wait();                                 // nothing of this thread's stays in flight on any path
+    }
+
+    ptx::tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tcgen05_fence_after();
+        ptx::tmem_dealloc(tmem_base, F8_TBUFS * F8_BN);
+    }
+}
+
 // ---- quantisation ------------------------------------------------------------------------------------------------
 // Quantise 128 consecutive elements held 4 per lane by one warp: scale = amax / 448 (1 when all zero).
 template <typename T>
@@ -492,17 +811,15 @@ aristos_status_t launch_fp8_gemm(const void* A, const void* B0, const void* B1, 
     ARISTOS_TRY(make_map_u8(&tmA, A, p.K, p.rows_per_group, p.groups, 128));
     ARISTOS_TRY(make_map_u8(&tmB0, B0, p.K, p.N, p.experts, 128));
     ARISTOS_TRY(make_map_u8(&tmB1, B1, p.K, p.N, p.experts, 128));
-    // promotion warps per lane quarter: 2 (ARISTOS_FP8_PROMOTION_WARPS=4 selects four: measured slower, 2.31 ms
-    // against 1.92 ms for 32 experts x 1024 rows, H 7168, I 2048 - 608 threads leave each 96 registers)
-    static int subs = 0;
-    if (subs == 0) {
-        const char* env = getenv("ARISTOS_FP8_PROMOTION_WARPS");
-        subs = (env && atoi(env) == 4) ? 4 : 2;
+    static int legacy = -1;
+    if (legacy < 0) {
+        const char* env = getenv("ARISTOS_FP8_KERNEL");
+        legacy = (env && strcmp(env, "wg") == 0) ? 0 : 1;
     }
     ARISTOS_CUDA_TRY(cudaFuncSetAttribute(ffn_fp8_grouped_gemm_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           F8_SMEM_BYTES));
-    ARISTOS_CUDA_TRY(cudaFuncSetAttribute(ffn_fp8_grouped_gemm_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          F8_SMEM_BYTES));
+    ARISTOS_CUDA_TRY(cudaFuncSetAttribute(ffn_fp8_grouped_gemm_wg_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          F8W_SMEM_BYTES));
     const int out_w = p.gated ? 128 : 256;
     int sms = device_sm_count();
     if (sms <= 0) { set_last_error("no CUDA device"); return ARISTOS_ERR_CUDA; }
@@ -510,8 +827,8 @@ aristos_status_t launch_fp8_gemm(const void* A, const void* B0, const void* B1, 
     const int64_t bound = (int64_t)p.groups * ceil_div(p.row_end - p.row_begin, F8_BM) * ceil_div(p.N, out_w);
     const int grid = (int)(bound < sms ? bound : sms);
     if (grid <= 0) return ARISTOS_OK;
-    if (subs == 2) ffn_fp8_grouped_gemm_kernel<2><<<grid, f8_threads(2), F8_SMEM_BYTES, st>>>(tmA, tmB0, tmB1, p, pa);
-    else ffn_fp8_grouped_gemm_kernel<4><<<grid, f8_threads(4), F8_SMEM_BYTES, st>>>(tmA, tmB0, tmB1, p, pa);
+    if (legacy) ffn_fp8_grouped_gemm_kernel<2><<<grid, f8_threads(2), F8_SMEM_BYTES, st>>>(tmA, tmB0, tmB1, p, pa);
+    else ffn_fp8_grouped_gemm_wg_kernel<<<grid, F8W_THREADS, F8W_SMEM_BYTES, st>>>(tmA, tmB0, tmB1, p, pa);
     ARISTOS_COUNT_LAUNCH();
     ARISTOS_CUDA_TRY(cudaGetLastError());
     return ARISTOS_OK;
