@@ -14,6 +14,8 @@ def __getattr__(name):
     # torch-dependent pieces are imported on first use so that config parsing works without importing torch
     if name in ("MoELayer", "layer", "gate_topk", "gate_topk_screened", "dispatch", "permute", "expert_ffn", "combine",
                 "fill_normal", "nccl_unique_id"):
-        from . import layer as _layer
+        import importlib
+
+        _layer = importlib.import_module(".layer", __name__)   # `from . import layer` would re-enter __getattr__
         return _layer if name == "layer" else getattr(_layer, name)
     raise AttributeError(name)

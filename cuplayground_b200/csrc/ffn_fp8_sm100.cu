@@ -58,6 +58,10 @@ struct Fp8GemmParams {
     const float* sb1;     // SwiGLU: scales of the up projection's weights
     __nv_bfloat16* out;   // [groups * rows_per_group][N]
     int32_t* dev_status;
+    // quantised output (the up projection of the warpgroup kernel): e4m3 codes [groups * rows_per_group][N] and one
+    // fp32 scale per row and 128 columns, exactly what quantising the bf16 output would give
+    uint8_t* outq;
+    float* out_scales;
 };
 static_assert(sizeof(Fp8GemmParams) <= 128, "Fp8GemmParams: keep the kernel argument within 128 bytes");
 
@@ -378,9 +382,12 @@ constexpr int F8W_THREADS = 384;
 constexpr int F8W_PROMO_THREADS = 256;
 constexpr int F8W_AUX_BYTES = (F8_AUX_BYTES + 127) & ~127;
 constexpr int F8W_OUT_BYTES_PER_WARP = 32 * 64;              // 32 rows x 32 bf16
-constexpr int F8W_SMEM_BYTES = 1024 + F8_STAGES * F8_STAGE_BYTES + F8W_AUX_BYTES + 8 * F8W_OUT_BYTES_PER_WARP;
+constexpr int F8W_AMAX_BYTES = 2 * 2 * 128 * 2 * 4;           // [tile parity][scale block][row][warp of the pair]
+constexpr int F8W_SMEM_BYTES = 1024 + F8_STAGES * F8_STAGE_BYTES + F8W_AUX_BYTES + 8 * F8W_OUT_BYTES_PER_WARP +
+                               F8W_AMAX_BYTES;
 static_assert(F8W_SMEM_BYTES <= 227 * 1024, "fp8 GEMM: shared memory");
 
+template <bool QUANT>
 __global__ void __launch_bounds__(F8W_THREADS, 1)
 ffn_fp8_grouped_gemm_wg_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB0,
                                const __grid_constant__ CUtensorMap tmB1, const Fp8GemmParams p,
@@ -388,7 +395,7 @@ ffn_fp8_grouped_gemm_wg_kernel(const __grid_constant__ CUtensorMap tmA, const __
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* aux = smem + F8_STAGES * F8_STAGE_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(aux);     // full[S], empty[S], tfull[2], tempty[2]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(aux);     // full[S], empty[S], tfull[2], tempty[2], amax[4]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aux + 192);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(aux + 196);
     int* prefix = reinterpret_cast<int*>(aux + 256);
@@ -398,6 +405,7 @@ ffn_fp8_grouped_gemm_wg_kernel(const __grid_constant__ CUtensorMap tmA, const __
     const uint32_t bar_empty = bar_full + 8 * F8_STAGES;
     const uint32_t bar_tfull = bar_empty + 8 * F8_STAGES;
     const uint32_t bar_tempty = bar_tfull + 8 * F8_TBUFS;
+    const uint32_t bar_amax = bar_tempty + 8 * F8_TBUFS;   // [4]: the two promotion warps of a lane quarter meet here
     const uint32_t smem_base = ptx::smem_u32(smem);
 
     const int out_w = p.gated ? 128 : 256;
@@ -415,6 +423,7 @@ ffn_fp8_grouped_gemm_wg_kernel(const __grid_constant__ CUtensorMap tmA, const __
             ptx::mbar_init(bar_tfull + 8 * b, 1);
             ptx::mbar_init(bar_tempty + 8 * b, F8W_PROMO_THREADS);
         }
+        for (int q = 0; q < 4; ++q) ptx::mbar_init(bar_amax + 8 * q, 64);
         *abort_flag = 0;
         ptx::fence_mbar_init();
     }
@@ -525,6 +534,7 @@ ffn_fp8_grouped_gemm_wg_kernel(const __grid_constant__ CUtensorMap tmA, const __
         const uint32_t out_stage = smem_base + F8_STAGES * F8_STAGE_BYTES + F8W_AUX_BYTES + pw * F8W_OUT_BYTES_PER_WARP;
         const uint32_t lane_taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + half * 32;
         int vg = 0, tbuf = 0, rstage = 0;
+        int qtile = 0;                                      // tiles this thread has quantised (amax buffer parity)
         uint32_t tphase = 0;
         bool ok = true;
         uint32_t v[2][32];
@@ -605,6 +615,90 @@ ffn_fp8_grouped_gemm_wg_kernel(const __grid_constant__ CUtensorMap tmA, const __
                 w_hi = nw_hi;
             }
             if (!ok) break;
+            if constexpr (QUANT) {
+                // ---- epilogue, quantised: the tile's 128 (SwiGLU) or 2 x 128 output columns of a row are one or two
+                // scale groups, split between the two warps of the lane quarter: amax through shared memory
+                float amax[2] = {0.0f, 0.0f};              // the activated bf16 values replace acc[j] in place
+                const int nchunks = p.gated ? 2 : 4;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    if (j >= nchunks) break;
+                    const int ju = (j + 2) & 3;
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        float v0, v1;
+                        if (p.gated) {
+                            v0 = act_silu(acc[j][i].x) * acc[ju][i].x;
+                            v1 = act_silu(acc[j][i].y) * acc[ju][i].y;
+                        } else {
+                            v0 = acc[j][i].x;
+                            v1 = acc[j][i].y;
+                            if (p.act == ARISTOS_ACT_RELU) { v0 = act_relu(v0); v1 = act_relu(v1); }
+                            else if (p.act == ARISTOS_ACT_GELU) { v0 = act_gelu(v0); v1 = act_gelu(v1); }
+                        }
+                        const __nv_bfloat162 r = __floats2bfloat162_rn(v0, v1);     // the bf16 value is what is quantised
+                        acc[j][i] = make_float2(__low2float(r), __high2float(r));
+                        const int b = p.gated ? 0 : (j >> 1);
+                        amax[b] = fmaxf(amax[b], fmaxf(fabsf(acc[j][i].x), fabsf(acc[j][i].y)));
+                    }
+                }
+                float* ex = reinterpret_cast<float*>(smem + F8_STAGES * F8_STAGE_BYTES + F8W_AUX_BYTES +
+                                                     8 * F8W_OUT_BYTES_PER_WARP) + (qtile & 1) * 512;
+                ex[row_in_tile * 2 + half] = amax[0];
+                ex[256 + row_in_tile * 2 + half] = amax[1];
+                ptx::mbar_arrive(bar_amax + 8 * quarter);
+                ok = ptx::mbar_wait_bounded(bar_amax + 8 * quarter, qtile & 1, abort_flag, p.dev_status);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                amax[0] = fmaxf(amax[0], ex[row_in_tile * 2 + (half ^ 1)]);
+                amax[1] = fmaxf(amax[1], ex[256 + row_in_tile * 2 + (half ^ 1)]);
+                ++qtile;
+                const size_t grow = (size_t)g * p.rows_per_group + row;
+                uint8_t* my_q = row_ok ? p.outq + grow * p.N + n0 : nullptr;
+                uint8_t* q2[2];                              // rows it * 16 + lane / 2 of this warp's 32
+#pragma unroll
+                for (int it = 0; it < 2; ++it)
+                    q2[it] = reinterpret_cast<uint8_t*>(
+                        __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(my_q), it * 16 + (lane >> 1)));
+                const int unit = lane & 1;
+#pragma unroll
+                for (int b = 0; b < 2; ++b) {
+                    if (b == 1 && p.gated) break;
+                    if (n0 + b * 128 >= p.N) break;
+                    const float scale = amax[b] > 0.0f ? amax[b] / 448.0f : 1.0f;
+                    const float inv = 1.0f / scale;
+                    if (row_ok && half == 0) p.out_scales[grow * nblk + blk + b] = scale;
+#pragma unroll
+                    for (int jj = 0; jj < 2; ++jj) {
+                        const int j = p.gated ? jj : 2 * b + jj;
+                        if (j >= 4) break;
+                        const int col = (half + 2 * j) * 32;
+                        uint32_t o[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            o[i] = 0;
+#pragma unroll
+                            for (int c = 0; c < 4; ++c) {
+                                const float2 pr = acc[j][2 * i + (c >> 1)];
+                                o[i] |= (uint32_t)__nv_cvt_float_to_fp8(((c & 1) ? pr.y : pr.x) * inv, __NV_SATFINITE, __NV_E4M3) << (8 * c);
+                            }
+                        }
+                        // row `lane`, 16-byte unit u lands at unit u ^ ((lane / 4) % 2): no bank conflicts either way
+#pragma unroll
+                        for (int u = 0; u < 2; ++u)
+                            ptx::st_shared_v4(out_stage + lane * 32 + ((u ^ ((lane >> 2) & 1)) << 4), o[4 * u], o[4 * u + 1],
+                                              o[4 * u + 2], o[4 * u + 3]);
+                        __syncwarp();
+#pragma unroll
+                        for (int it = 0; it < 2; ++it) {
+                            const int r = it * 16 + (lane >> 1);
+                            const uint4 val = ptx::ld_shared_v4(out_stage + r * 32 + ((unit ^ ((r >> 2) & 1)) << 4));
+                            if (q2[it] != nullptr) *reinterpret_cast<uint4*>(q2[it] + col + unit * 16) = val;
+                        }
+                        __syncwarp();
+                    }
+                }
+            } else {
             // ---- epilogue: every lane knows where its own row goes; rows leave 8 at a time, 64 bytes each
             __nv_bfloat16* my_dst = nullptr;
             if (row_ok) {
@@ -668,6 +762,7 @@ ffn_fp8_grouped_gemm_wg_kernel(const __grid_constant__ CUtensorMap tmA, const __
                     if (dst4[it] != nullptr) *reinterpret_cast<uint4*>(dst4[it] + col + unit * 8) = val;
                 }
                 __syncwarp();
+            }
             }
         }
         ptx::tmem_ld_wait();                                 // nothing of this thread's stays in flight on any path
@@ -805,21 +900,38 @@ aristos_status_t make_map_u8(CUtensorMap* tm, const void* base, int K, int rows,
     return encode_map_3d(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, base, K, rows, outer, box_rows);
 }
 
+// Kernel selection (read once): ARISTOS_FP8_KERNEL=wg selects the warpgroup kernel; with it the up projection writes
+// the quantised hidden activations itself unless ARISTOS_FP8_FUSED_QUANT=0.
+bool fp8_warpgroup_kernel() {
+    static int wg = -1;
+    if (wg < 0) {
+        const char* env = getenv("ARISTOS_FP8_KERNEL");
+        wg = (env && strcmp(env, "wg") == 0) ? 1 : 0;
+    }
+    return wg == 1;
+}
+bool fp8_fused_quant() {
+    static int fq = -1;
+    if (fq < 0) {
+        const char* env = getenv("ARISTOS_FP8_FUSED_QUANT");
+        fq = (env && strcmp(env, "0") == 0) ? 0 : 1;
+    }
+    return fq == 1 && fp8_warpgroup_kernel();
+}
+
 aristos_status_t launch_fp8_gemm(const void* A, const void* B0, const void* B1, const Fp8GemmParams& p,
                                  const Fp8PeerArgs& pa, int grid_limit, cudaStream_t st) {
     CUtensorMap tmA, tmB0, tmB1;
     ARISTOS_TRY(make_map_u8(&tmA, A, p.K, p.rows_per_group, p.groups, 128));
     ARISTOS_TRY(make_map_u8(&tmB0, B0, p.K, p.N, p.experts, 128));
     ARISTOS_TRY(make_map_u8(&tmB1, B1, p.K, p.N, p.experts, 128));
-    static int legacy = -1;
-    if (legacy < 0) {
-        const char* env = getenv("ARISTOS_FP8_KERNEL");
-        legacy = (env && strcmp(env, "wg") == 0) ? 0 : 1;
-    }
+    const bool legacy = !fp8_warpgroup_kernel();
     ARISTOS_CUDA_TRY(cudaFuncSetAttribute(ffn_fp8_grouped_gemm_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           F8_SMEM_BYTES));
-    ARISTOS_CUDA_TRY(cudaFuncSetAttribute(ffn_fp8_grouped_gemm_wg_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          F8W_SMEM_BYTES));
+    ARISTOS_CUDA_TRY(cudaFuncSetAttribute(ffn_fp8_grouped_gemm_wg_kernel<false>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, F8W_SMEM_BYTES));
+    ARISTOS_CUDA_TRY(cudaFuncSetAttribute(ffn_fp8_grouped_gemm_wg_kernel<true>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, F8W_SMEM_BYTES));
     const int out_w = p.gated ? 128 : 256;
     int sms = device_sm_count();
     if (sms <= 0) { set_last_error("no CUDA device"); return ARISTOS_ERR_CUDA; }
@@ -828,7 +940,8 @@ aristos_status_t launch_fp8_gemm(const void* A, const void* B0, const void* B1, 
     const int grid = (int)(bound < sms ? bound : sms);
     if (grid <= 0) return ARISTOS_OK;
     if (legacy) ffn_fp8_grouped_gemm_kernel<2><<<grid, f8_threads(2), F8_SMEM_BYTES, st>>>(tmA, tmB0, tmB1, p, pa);
-    else ffn_fp8_grouped_gemm_wg_kernel<<<grid, F8W_THREADS, F8W_SMEM_BYTES, st>>>(tmA, tmB0, tmB1, p, pa);
+    else if (p.outq) ffn_fp8_grouped_gemm_wg_kernel<true><<<grid, F8W_THREADS, F8W_SMEM_BYTES, st>>>(tmA, tmB0, tmB1, p, pa);
+    else ffn_fp8_grouped_gemm_wg_kernel<false><<<grid, F8W_THREADS, F8W_SMEM_BYTES, st>>>(tmA, tmB0, tmB1, p, pa);
     ARISTOS_COUNT_LAUNCH();
     ARISTOS_CUDA_TRY(cudaGetLastError());
     return ARISTOS_OK;
@@ -866,11 +979,20 @@ aristos_status_t expert_ffn_fp8_sm100(const void* xq, const float* sx, const int
     p.sa = sx; p.sb0 = s1; p.sb1 = gated ? s3 : s1;
     p.out = static_cast<__nv_bfloat16*>(h);
     Fp8PeerArgs pa{};
-    ARISTOS_TRY(launch_fp8_gemm(xq, w1q, gated ? w3q : w1q, p, pa, sm_limit, st));
-    // hidden activations: bf16 -> e4m3 per row and 128 columns (valid rows only)
-    quantize_group_rows_fp8_kernel<__nv_bfloat16><<<device_sm_count() * 4, 256, 0, st>>>(
-        static_cast<const __nv_bfloat16*>(h), count, groups, rows_per_group, I, static_cast<uint8_t*>(hq), sh);
-    ARISTOS_COUNT_LAUNCH();
+    if (fp8_fused_quant()) {
+        // the up projection's epilogue quantises its own output rows: no bf16 copy of the hidden activations
+        p.outq = static_cast<uint8_t*>(hq);
+        p.out_scales = sh;
+        ARISTOS_TRY(launch_fp8_gemm(xq, w1q, gated ? w3q : w1q, p, pa, sm_limit, st));
+        p.outq = nullptr;
+        p.out_scales = nullptr;
+    } else {
+        ARISTOS_TRY(launch_fp8_gemm(xq, w1q, gated ? w3q : w1q, p, pa, sm_limit, st));
+        // hidden activations: bf16 -> e4m3 per row and 128 columns (valid rows only)
+        quantize_group_rows_fp8_kernel<__nv_bfloat16><<<device_sm_count() * 4, 256, 0, st>>>(
+            static_cast<const __nv_bfloat16*>(h), count, groups, rows_per_group, I, static_cast<uint8_t*>(hq), sh);
+        ARISTOS_COUNT_LAUNCH();
+    }
     p.N = H; p.K = I; p.gated = 0; p.act = ARISTOS_ACT_IDENTITY;
     p.sa = sh; p.sb0 = s2; p.sb1 = s2;
     p.out = static_cast<__nv_bfloat16*>(y);

@@ -219,3 +219,16 @@ def test_numa_binding_plan(tmp_path):
     assert hostmem.plan_binding(set(range(0, 8)), 1, cpus) is None           # none of the node's CPUs allowed
     assert hostmem.plan_binding(set(range(0, 32)), None, set()) is None      # unknown node
     assert hostmem.node_cpus(7, sysfs=str(tmp_path)) == set()
+
+
+def test_lazy_package_attributes_resolve_in_a_fresh_interpreter():
+    """The torch-dependent names of the package are imported on first use: from a fresh interpreter, where the
+    submodule has not been imported yet, both spellings must resolve (and not recurse)."""
+    import subprocess
+    import sys
+
+    code = ("import cuplayground_b200 as c; assert c.MoELayer.__name__ == 'MoELayer'; "
+            "from cuplayground_b200 import layer, gate_topk; assert layer.gate_topk is gate_topk")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-c", code], cwd=root, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
