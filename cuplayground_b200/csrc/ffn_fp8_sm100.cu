@@ -9,9 +9,18 @@
 // block's scale and add it to fp32 register accumulators with packed FMAs while the tensor core fills the other of
 // the two TMEM buffers. Two promotion warps share a TMEM lane quarter, each owning four of the eight 32-column chunks
 // ({0, 2, 4, 6} or {1, 3, 5, 7}, so a SwiGLU thread holds matching gate and up columns): one row and 128 columns per
-// thread. The issue of four MMAs and a commit takes the issuing thread longer than the tensor core needs for them
-// whatever their width (about 150 cycles per instruction were measured), hence the N = 256 instructions and two
-// issuing warps that take turns per K block.
+// thread. Two issuing warps take turns per K block (a commit covers its own thread's MMAs only).
+//
+// What bounds the kernel: every K block's 128 x 256 fp32 partial sums (128 KB) have to leave TMEM through tcgen05.ld.
+// Clock stamps inside the kernel (per K block, CTA 0) showed a promotion warp needing about 1050 cycles for its share
+// of a block (~260 per 32 columns with the two warps of a lane quarter loading at once, i.e. roughly 32 bytes per
+// clock and lane quarter, 128 per SM), the same whether the tensor core was running beside it or idle, with 16- or
+// 32-column loads, one or two loads in flight, and with the registers of the other warps handed to the promotion
+// warps; issuing a block's MMAs cost 85 cycles and the operands were never late (75 cycles waiting for TMA). The
+// tensor core needs 542 cycles for the block, so it can be busy about half of the time (measured: 51 % in the up
+// projection): the format's fp32 scale per 128 elements of K, not the MMA rate, sets the speed of this kernel.
+// (A variant with four promotion warps per lane quarter that took their registers from the other warps with
+// setmaxnreg did not finish on the GPU and was not run again; with two per quarter the hand-over changed nothing.)
 //
 // Same tile contract as the 16-bit kernel (ffn_sm100.cu; reference: fGET, mma.cuh:46-179, A (M,K) and B (N,K)
 // row-major, epilogue act(acc)): persistent CTAs, warp 0 = TMA producer (a 128-byte K block is exactly one swizzled
@@ -20,9 +29,6 @@
 // row count (to this rank's buffer, or straight into the source ranks' buffers through peer pointers).
 #include <cuda.h>
 #include <cuda_fp8.h>
-
-#include <cstdlib>
-#include <cstring>
 
 #include "common.cuh"
 #include "ptx_sm100.cuh"
@@ -58,10 +64,6 @@ struct Fp8GemmParams {
     const float* sb1;     // SwiGLU: scales of the up projection's weights
     __nv_bfloat16* out;   // [groups * rows_per_group][N]
     int32_t* dev_status;
-    // quantised output (the up projection of the warpgroup kernel): e4m3 codes [groups * rows_per_group][N] and one
-    // fp32 scale per row and 128 columns, exactly what quantising the bf16 output would give
-    uint8_t* outq;
-    float* out_scales;
 };
 static_assert(sizeof(Fp8GemmParams) <= 128, "Fp8GemmParams: keep the kernel argument within 128 bytes");
 
@@ -369,413 +371,6 @@ ffn_fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
     }
 }
 
-// ---- the same GEMM with warpgroup roles -----------------------------------------------------------------------------
-// 384 threads: warpgroup 0 = TMA producer (warp 0), the two MMA issuers (warps 1, 2) and an idle warp; warpgroups 1-2
-// = the eight promotion warps. Warpgroup 0 gives registers back (setmaxnreg) and the promotion warps take them, which
-// pays for 64 staging registers beside the 128 accumulators: a K block is drained by four 32-column tcgen05.ld per
-// thread with one always in flight behind the packed FMAs of the previous one, and the first load of the next K
-// block is issued before the last FMAs of this one. (With 16-column loads and 168 registers the promotion of a block
-// took about twice the tensor core's time for it: eight exposed TMEM round trips per block.)
-// The output leaves through a small per-warp staging area so that a store instruction covers 8 rows x 64 bytes of
-// full 32-byte sectors instead of 32 rows x 16 bytes.
-constexpr int F8W_THREADS = 384;
-constexpr int F8W_PROMO_THREADS = 256;
-constexpr int F8W_AUX_BYTES = (F8_AUX_BYTES + 127) & ~127;
-constexpr int F8W_OUT_BYTES_PER_WARP = 32 * 64;              // 32 rows x 32 bf16
-constexpr int F8W_AMAX_BYTES = 2 * 2 * 128 * 2 * 4;           // [tile parity][scale block][row][warp of the pair]
-constexpr int F8W_SMEM_BYTES = 1024 + F8_STAGES * F8_STAGE_BYTES + F8W_AUX_BYTES + 8 * F8W_OUT_BYTES_PER_WARP +
-                               F8W_AMAX_BYTES;
-static_assert(F8W_SMEM_BYTES <= 227 * 1024, "fp8 GEMM: shared memory");
-
-template <bool QUANT>
-__global__ void __launch_bounds__(F8W_THREADS, 1)
-ffn_fp8_grouped_gemm_wg_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB0,
-                               const __grid_constant__ CUtensorMap tmB1, const Fp8GemmParams p,
-                               const __grid_constant__ Fp8PeerArgs pa) {
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t* aux = smem + F8_STAGES * F8_STAGE_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(aux);     // full[S], empty[S], tfull[2], tempty[2], amax[4]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aux + 192);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(aux + 196);
-    int* prefix = reinterpret_cast<int*>(aux + 256);
-
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t bar_full = ptx::smem_u32(bars);
-    const uint32_t bar_empty = bar_full + 8 * F8_STAGES;
-    const uint32_t bar_tfull = bar_empty + 8 * F8_STAGES;
-    const uint32_t bar_tempty = bar_tfull + 8 * F8_TBUFS;
-    const uint32_t bar_amax = bar_tempty + 8 * F8_TBUFS;   // [4]: the two promotion warps of a lane quarter meet here
-    const uint32_t smem_base = ptx::smem_u32(smem);
-
-    const int out_w = p.gated ? 128 : 256;
-    const int n_tiles = (p.N + out_w - 1) / out_w;
-    const int window = p.row_end - p.row_begin;
-    const int kblocks = p.K / F8_KB;
-    const int nblk = (p.N + 127) / 128;                    // weight-scale blocks along N
-
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < F8_STAGES; ++s) {
-            ptx::mbar_init(bar_full + 8 * s, 1);
-            ptx::mbar_init(bar_empty + 8 * s, 1);
-        }
-        for (int b = 0; b < F8_TBUFS; ++b) {
-            ptx::mbar_init(bar_tfull + 8 * b, 1);
-            ptx::mbar_init(bar_tempty + 8 * b, F8W_PROMO_THREADS);
-        }
-        for (int q = 0; q < 4; ++q) ptx::mbar_init(bar_amax + 8 * q, 64);
-        *abort_flag = 0;
-        ptx::fence_mbar_init();
-    }
-    if (warp == 0) {
-        int running = 0;
-        if (lane == 0) prefix[0] = 0;
-        for (int g0 = 0; g0 < p.groups; g0 += 32) {
-            const int g = g0 + lane;
-            int v = 0;
-            if (g < p.groups) {
-                int rows = p.count[ordered_group(g, p.groups, p.experts)] - p.row_begin;
-                rows = max(0, min(rows, window));
-                v = ((rows + F8_BM - 1) / F8_BM) * n_tiles;
-            }
-#pragma unroll
-            for (int d = 1; d < 32; d <<= 1) {
-                const int o = __shfl_up_sync(0xffffffffu, v, d);
-                if (lane >= d) v += o;
-            }
-            if (g < p.groups) prefix[g + 1] = running + v;
-            running += __shfl_sync(0xffffffffu, v, 31);
-        }
-    } else if (warp == 1) {
-        ptx::tmem_alloc(ptx::smem_u32(tmem_slot), F8_TBUFS * F8_BN);
-    }
-    ptx::tcgen05_fence_before();
-    __syncthreads();
-    ptx::tcgen05_fence_after();
-    const uint32_t tmem_base = *tmem_slot;
-    const int total_tiles = prefix[p.groups];
-
-    if (warp < 4) {
-        ptx::warpgroup_reg_release<40>();
-        if (warp == 0) {
-            // -------------------------------------------------------------------------------------- TMA producer
-            if (ptx::elect_one()) {
-                ptx::prefetch_tensormap(&tmA);
-                ptx::prefetch_tensormap(&tmB0);
-                ptx::prefetch_tensormap(&tmB1);
-                int stage = 0;
-                uint32_t phase = 0;
-                int vg = 0;
-                bool ok = true;
-                for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-                    while (tile >= prefix[vg + 1]) ++vg;
-                    const int g = ordered_group(vg, p.groups, p.experts);
-                    const int local = tile - prefix[vg];
-                    const int mt = (prefix[vg + 1] - prefix[vg]) / n_tiles;
-                    const int m0 = p.row_begin + (local % mt) * F8_BM;
-                    const int n0 = (local / mt) * out_w;
-                    const int e = g % p.experts;
-                    const int n1 = p.gated ? n0 : n0 + 128;     // second 128-row box of B
-                    for (int kb = 0; kb < kblocks; ++kb) {
-                        ok = ptx::mbar_wait_bounded(bar_empty + 8 * stage, phase ^ 1u, abort_flag, p.dev_status);
-                        if (!ok) break;
-                        const uint32_t full = bar_full + 8 * stage;
-                        const uint32_t sa = smem_base + stage * F8_STAGE_BYTES;
-                        ptx::mbar_arrive_expect_tx(full, F8_STAGE_BYTES);
-                        ptx::tma_load_3d(sa, &tmA, kb * F8_KB, m0, g, full);
-                        ptx::tma_load_3d(sa + F8_A_BYTES, &tmB0, kb * F8_KB, n0, e, full);
-                        ptx::tma_load_3d(sa + F8_A_BYTES + F8_B_BYTES / 2, &tmB1, kb * F8_KB, n1, e, full);
-                        if (++stage == F8_STAGES) { stage = 0; phase ^= 1u; }
-                    }
-                }
-            }
-            __syncwarp();
-        } else if (warp <= 2) {
-            // ------------------------------------------------------------- MMA issuers: one TMEM buffer per K block,
-            // K block number it goes to warp 1 + it % 2 and to TMEM buffer it % 2 (a commit covers its own thread's MMAs)
-            if (ptx::elect_one()) {
-                constexpr uint32_t idesc = umma_idesc_e4m3(F8_BM, F8_BN);
-                const int me = warp - 1;
-                int it = 0;
-                bool ok = true;
-                for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-                    for (int kb = 0; kb < kblocks; ++kb, ++it) {
-                        if ((it & 1) != me) continue;
-                        const int tbuf = it & 1, stage = it % F8_STAGES;
-                        const uint32_t tphase = (it >> 1) & 1u, phase = (it / F8_STAGES) & 1u;
-                        ok = ptx::mbar_wait_bounded(bar_tempty + 8 * tbuf, tphase ^ 1u, abort_flag, p.dev_status);
-                        if (!ok) break;
-                        ok = ptx::mbar_wait_bounded(bar_full + 8 * stage, phase, abort_flag, p.dev_status);
-                        if (!ok) break;
-                        ptx::tcgen05_fence_after();
-                        const uint32_t sa = smem_base + stage * F8_STAGE_BYTES;
-                        const uint64_t da = ptx::umma_desc_k_sw128(sa);
-                        const uint64_t db = ptx::umma_desc_k_sw128(sa + F8_A_BYTES);
-                        const uint32_t tmem_d = tmem_base + tbuf * F8_BN;
-#pragma unroll
-                        for (int k = 0; k < 4; ++k)            // K = 32 elements = 32 bytes per instruction
-                            umma_f8(tmem_d, da + 2 * k, db + 2 * k, idesc, k != 0 ? 1u : 0u);
-                        ptx::umma_commit(bar_tfull + 8 * tbuf);
-                    }
-                }
-            }
-            __syncwarp();
-        }
-    } else {
-        ptx::warpgroup_reg_acquire<232>();
-        // ------------------------------------------------------------------------------ promotion + epilogue
-        // A thread owns one accumulator row and the 32-column chunks half, half + 2, half + 4, half + 6 of the
-        // 256-column tile: two in the tile's first 128 columns (gate, or weight-scale block n0 / 128), two in the
-        // second 128 (up, or the next scale block).
-        const int pw = warp - 4;
-        const int quarter = warp & 3;                       // TMEM lanes this warp may read
-        const int half = pw >> 2;
-        const int row_in_tile = quarter * 32 + lane;
-        const uint32_t out_stage = smem_base + F8_STAGES * F8_STAGE_BYTES + F8W_AUX_BYTES + pw * F8W_OUT_BYTES_PER_WARP;
-        const uint32_t lane_taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + half * 32;
-        int vg = 0, tbuf = 0, rstage = 0;
-        int qtile = 0;                                      // tiles this thread has quantised (amax buffer parity)
-        uint32_t tphase = 0;
-        bool ok = true;
-        uint32_t v[2][32];
-        for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-            while (tile >= prefix[vg + 1]) ++vg;
-            const int g = ordered_group(vg, p.groups, p.experts);
-            const int local = tile - prefix[vg];
-            const int mt = (prefix[vg + 1] - prefix[vg]) / n_tiles;
-            const int m0 = p.row_begin + (local % mt) * F8_BM;
-            const int n0 = (local / mt) * out_w;
-            const int e = g % p.experts;
-            const int row = m0 + row_in_tile;
-            const int row_limit = min(p.count[g], p.row_end);
-            const bool row_ok = row < row_limit;
-            const float* sa_row = p.sa + ((size_t)g * p.rows_per_group + min(row, p.rows_per_group - 1)) * kblocks;
-            const int blk = n0 / 128;
-            const float* sb0_row = p.sb0 + ((size_t)e * nblk + blk) * kblocks;
-            const float* sb1_row = p.gated ? p.sb1 + ((size_t)e * nblk + blk) * kblocks
-                                           : p.sb0 + ((size_t)e * nblk + min(blk + 1, nblk - 1)) * kblocks;
-            float2 acc[4][16];                               // chunk j = half + 2 j, 32 columns as 16 pairs
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-#pragma unroll
-                for (int i = 0; i < 16; ++i) acc[j][i] = make_float2(0.0f, 0.0f);
-            float w_lo, w_hi;
-            {
-                const float sa = __ldg(sa_row);
-                w_lo = sa * __ldg(sb0_row);                  // columns 0..127
-                w_hi = sa * __ldg(sb1_row);                  // columns 128..255
-            }
-            // first K block of the tile: wait for its MMAs, hand its shared-memory stage back, start the first load
-            ok = ptx::mbar_wait_bounded(bar_tfull + 8 * tbuf, tphase, abort_flag, p.dev_status);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            if (threadIdx.x == 128) ptx::mbar_arrive(bar_empty + 8 * rstage);
-            if (++rstage == F8_STAGES) rstage = 0;
-            ptx::tcgen05_fence_after();
-            ptx::tmem_ld_32x32b_x32(lane_taddr + tbuf * F8_BN, v[0]);
-            for (int kb = 0; kb < kblocks; ++kb) {
-                float nw_lo = 0.0f, nw_hi = 0.0f;
-                if (kb + 1 < kblocks) {
-                    const float sa = __ldg(sa_row + kb + 1);
-                    nw_lo = sa * __ldg(sb0_row + kb + 1);
-                    nw_hi = sa * __ldg(sb1_row + kb + 1);
-                }
-#pragma unroll
-                for (int s = 0; s < 4; ++s) {
-                    ptx::tmem_ld_wait();                      // chunk s of this block is in v[s & 1]
-                    if (s < 3) {
-                        ptx::tmem_ld_32x32b_x32(lane_taddr + tbuf * F8_BN + (s + 1) * 64, v[(s + 1) & 1]);
-                    } else {
-                        // every read of this buffer is complete: the tensor core may refill it; then on to the next
-                        // block's buffer, whose first chunk travels while the last chunk of this one is accumulated
-                        ptx::tcgen05_fence_before();
-                        ptx::mbar_arrive(bar_tempty + 8 * tbuf);
-                        if (++tbuf == F8_TBUFS) { tbuf = 0; tphase ^= 1u; }
-                        if (kb + 1 < kblocks) {
-                            ok = ptx::mbar_wait_bounded(bar_tfull + 8 * tbuf, tphase, abort_flag, p.dev_status);
-                            ok = __all_sync(0xffffffffu, ok);
-                            if (ok) {
-                                if (threadIdx.x == 128) ptx::mbar_arrive(bar_empty + 8 * rstage);
-                                if (++rstage == F8_STAGES) rstage = 0;
-                                ptx::tcgen05_fence_after();
-                                ptx::tmem_ld_32x32b_x32(lane_taddr + tbuf * F8_BN, v[0]);
-                            }
-                        }
-                    }
-                    const float w = s < 2 ? w_lo : w_hi;
-                    const float2 w2 = make_float2(w, w);
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        const float2 x2 = make_float2(__uint_as_float(v[s & 1][2 * i]), __uint_as_float(v[s & 1][2 * i + 1]));
-                        acc[s][i] = __ffma2_rn(x2, w2, acc[s][i]);
-                    }
-                }
-                if (!ok) break;
-                w_lo = nw_lo;
-                w_hi = nw_hi;
-            }
-            if (!ok) break;
-            if constexpr (QUANT) {
-                // ---- epilogue, quantised: the tile's 128 (SwiGLU) or 2 x 128 output columns of a row are one or two
-                // scale groups, split between the two warps of the lane quarter: amax through shared memory
-                float amax[2] = {0.0f, 0.0f};              // the activated bf16 values replace acc[j] in place
-                const int nchunks = p.gated ? 2 : 4;
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    if (j >= nchunks) break;
-                    const int ju = (j + 2) & 3;
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        float v0, v1;
-                        if (p.gated) {
-                            v0 = act_silu(acc[j][i].x) * acc[ju][i].x;
-                            v1 = act_silu(acc[j][i].y) * acc[ju][i].y;
-                        } else {
-                            v0 = acc[j][i].x;
-                            v1 = acc[j][i].y;
-                            if (p.act == ARISTOS_ACT_RELU) { v0 = act_relu(v0); v1 = act_relu(v1); }
-                            else if (p.act == ARISTOS_ACT_GELU) { v0 = act_gelu(v0); v1 = act_gelu(v1); }
-                        }
-                        const __nv_bfloat162 r = __floats2bfloat162_rn(v0, v1);     // the bf16 value is what is quantised
-                        acc[j][i] = make_float2(__low2float(r), __high2float(r));
-                        const int b = p.gated ? 0 : (j >> 1);
-                        amax[b] = fmaxf(amax[b], fmaxf(fabsf(acc[j][i].x), fabsf(acc[j][i].y)));
-                    }
-                }
-                float* ex = reinterpret_cast<float*>(smem + F8_STAGES * F8_STAGE_BYTES + F8W_AUX_BYTES +
-                                                     8 * F8W_OUT_BYTES_PER_WARP) + (qtile & 1) * 512;
-                ex[row_in_tile * 2 + half] = amax[0];
-                ex[256 + row_in_tile * 2 + half] = amax[1];
-                ptx::mbar_arrive(bar_amax + 8 * quarter);
-                ok = ptx::mbar_wait_bounded(bar_amax + 8 * quarter, qtile & 1, abort_flag, p.dev_status);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                amax[0] = fmaxf(amax[0], ex[row_in_tile * 2 + (half ^ 1)]);
-                amax[1] = fmaxf(amax[1], ex[256 + row_in_tile * 2 + (half ^ 1)]);
-                ++qtile;
-                const size_t grow = (size_t)g * p.rows_per_group + row;
-                uint8_t* my_q = row_ok ? p.outq + grow * p.N + n0 : nullptr;
-                uint8_t* q2[2];                              // rows it * 16 + lane / 2 of this warp's 32
-#pragma unroll
-                for (int it = 0; it < 2; ++it)
-                    q2[it] = reinterpret_cast<uint8_t*>(
-                        __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(my_q), it * 16 + (lane >> 1)));
-                const int unit = lane & 1;
-#pragma unroll
-                for (int b = 0; b < 2; ++b) {
-                    if (b == 1 && p.gated) break;
-                    if (n0 + b * 128 >= p.N) break;
-                    const float scale = amax[b] > 0.0f ? amax[b] / 448.0f : 1.0f;
-                    const float inv = 1.0f / scale;
-                    if (row_ok && half == 0) p.out_scales[grow * nblk + blk + b] = scale;
-#pragma unroll
-                    for (int jj = 0; jj < 2; ++jj) {
-                        const int j = p.gated ? jj : 2 * b + jj;
-                        if (j >= 4) break;
-                        const int col = (half + 2 * j) * 32;
-                        uint32_t o[8];
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            o[i] = 0;
-#pragma unroll
-                            for (int c = 0; c < 4; ++c) {
-                                const float2 pr = acc[j][2 * i + (c >> 1)];
-                                o[i] |= (uint32_t)__nv_cvt_float_to_fp8(((c & 1) ? pr.y : pr.x) * inv, __NV_SATFINITE, __NV_E4M3) << (8 * c);
-                            }
-                        }
-                        // row `lane`, 16-byte unit u lands at unit u ^ ((lane / 4) % 2): no bank conflicts either way
-#pragma unroll
-                        for (int u = 0; u < 2; ++u)
-                            ptx::st_shared_v4(out_stage + lane * 32 + ((u ^ ((lane >> 2) & 1)) << 4), o[4 * u], o[4 * u + 1],
-                                              o[4 * u + 2], o[4 * u + 3]);
-                        __syncwarp();
-#pragma unroll
-                        for (int it = 0; it < 2; ++it) {
-                            const int r = it * 16 + (lane >> 1);
-                            const uint4 val = ptx::ld_shared_v4(out_stage + r * 32 + ((unit ^ ((r >> 2) & 1)) << 4));
-                            if (q2[it] != nullptr) *reinterpret_cast<uint4*>(q2[it] + col + unit * 16) = val;
-                        }
-                        __syncwarp();
-                    }
-                }
-            } else {
-            // ---- epilogue: every lane knows where its own row goes; rows leave 8 at a time, 64 bytes each
-            __nv_bfloat16* my_dst = nullptr;
-            if (row_ok) {
-                __nv_bfloat16* obase = p.out;
-                int og = g;
-                int orows = p.rows_per_group, orow_idx = row;
-                if (pa.peer_world > 0 && pa.src_off != nullptr) {
-                    // dense group: find the source rank of this row, return it to that rank's own numbering
-                    const int32_t* off = pa.src_off + g * (pa.peer_world + 1);
-                    int src = 0;
-                    while (src + 1 < pa.peer_world && row >= __ldg(off + src + 1)) ++src;
-                    obase = pa.peer_out[src];
-                    og = pa.peer_rank * p.experts + g;
-                    orows = pa.ret_rows;
-                    orow_idx = row - __ldg(off + src);
-                } else if (pa.peer_world > 0) {    // the store is the return all-to-all: straight into the source rank
-                    const int src = g / p.experts;
-                    obase = pa.peer_out[src];
-                    og = pa.peer_rank * p.experts + (g - src * p.experts);
-                }
-                my_dst = obase + ((size_t)og * orows + orow_idx) * p.N + n0;
-            }
-            __nv_bfloat16* dst4[4];                          // rows it * 8 + lane / 4 of this warp's 32
-#pragma unroll
-            for (int it = 0; it < 4; ++it)
-                dst4[it] = reinterpret_cast<__nv_bfloat16*>(
-                    __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(my_dst), it * 8 + (lane >> 2)));
-            const int unit = lane & 3;
-            const int nchunks = p.gated ? 2 : 4;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                if (j >= nchunks) break;
-                const int col = (half + 2 * j) * 32;
-                if (n0 + col >= p.N) break;
-                uint32_t o[16];
-                if (p.gated) {
-                    // gate chunk half + 2 j pairs with up chunk half + 2 j + 4
-                    const int ju = (j + 2) & 3;
-#pragma unroll
-                    for (int i = 0; i < 16; ++i)
-                        o[i] = pack_bf16x2(act_silu(acc[j][i].x) * acc[ju][i].x, act_silu(acc[j][i].y) * acc[ju][i].y);
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        float v0 = acc[j][i].x, v1 = acc[j][i].y;
-                        if (p.act == ARISTOS_ACT_RELU) { v0 = act_relu(v0); v1 = act_relu(v1); }
-                        else if (p.act == ARISTOS_ACT_GELU) { v0 = act_gelu(v0); v1 = act_gelu(v1); }
-                        o[i] = pack_bf16x2(v0, v1);
-                    }
-                }
-                // row `lane`, 16-byte unit u lands at unit u ^ ((lane / 2) % 4): neither side has bank conflicts
-#pragma unroll
-                for (int u = 0; u < 4; ++u)
-                    ptx::st_shared_v4(out_stage + lane * 64 + ((u ^ ((lane >> 1) & 3)) << 4), o[4 * u], o[4 * u + 1],
-                                      o[4 * u + 2], o[4 * u + 3]);
-                __syncwarp();
-#pragma unroll
-                for (int it = 0; it < 4; ++it) {
-                    const int r = it * 8 + (lane >> 2);
-                    const uint4 val = ptx::ld_shared_v4(out_stage + r * 64 + ((unit ^ ((r >> 1) & 3)) << 4));
-                    if (dst4[it] != nullptr) *reinterpret_cast<uint4*>(dst4[it] + col + unit * 8) = val;
-                }
-                __syncwarp();
-            }
-            }
-        }
-        ptx::tmem_ld_wait();                                 // nothing of this thread's stays in flight on any path
-    }
-
-    ptx::tcgen05_fence_before();
-    __syncthreads();
-    if (warp == 1) {
-        ptx::tcgen05_fence_after();
-        ptx::tmem_dealloc(tmem_base, F8_TBUFS * F8_BN);
-    }
-}
-
 // ---- quantisation ------------------------------------------------------------------------------------------------
 // Quantise 128 consecutive elements held 4 per lane by one warp: scale = amax / 448 (1 when all zero).
 template <typename T>
@@ -900,38 +495,23 @@ aristos_status_t make_map_u8(CUtensorMap* tm, const void* base, int K, int rows,
     return encode_map_3d(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, base, K, rows, outer, box_rows);
 }
 
-// Kernel selection (read once): ARISTOS_FP8_KERNEL=wg selects the warpgroup kernel; with it the up projection writes
-// the quantised hidden activations itself unless ARISTOS_FP8_FUSED_QUANT=0.
-bool fp8_warpgroup_kernel() {
-    static int wg = -1;
-    if (wg < 0) {
-        const char* env = getenv("ARISTOS_FP8_KERNEL");
-        wg = (env && strcmp(env, "wg") == 0) ? 1 : 0;
-    }
-    return wg == 1;
-}
-bool fp8_fused_quant() {
-    static int fq = -1;
-    if (fq < 0) {
-        const char* env = getenv("ARISTOS_FP8_FUSED_QUANT");
-        fq = (env && strcmp(env, "0") == 0) ? 0 : 1;
-    }
-    return fq == 1 && fp8_warpgroup_kernel();
-}
-
 aristos_status_t launch_fp8_gemm(const void* A, const void* B0, const void* B1, const Fp8GemmParams& p,
                                  const Fp8PeerArgs& pa, int grid_limit, cudaStream_t st) {
     CUtensorMap tmA, tmB0, tmB1;
     ARISTOS_TRY(make_map_u8(&tmA, A, p.K, p.rows_per_group, p.groups, 128));
     ARISTOS_TRY(make_map_u8(&tmB0, B0, p.K, p.N, p.experts, 128));
     ARISTOS_TRY(make_map_u8(&tmB1, B1, p.K, p.N, p.experts, 128));
-    const bool legacy = !fp8_warpgroup_kernel();
+    // promotion warps per lane quarter: 2 (ARISTOS_FP8_PROMOTION_WARPS=4 selects four: measured slower, 2.31 ms
+    // against 1.92 ms for 32 experts x 1024 rows, H 7168, I 2048 - 608 threads leave each 96 registers)
+    static int subs = 0;
+    if (subs == 0) {
+        const char* env = getenv("ARISTOS_FP8_PROMOTION_WARPS");
+        subs = (env && atoi(env) == 4) ? 4 : 2;
+    }
     ARISTOS_CUDA_TRY(cudaFuncSetAttribute(ffn_fp8_grouped_gemm_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           F8_SMEM_BYTES));
-    ARISTOS_CUDA_TRY(cudaFuncSetAttribute(ffn_fp8_grouped_gemm_wg_kernel<false>,
-                                          cudaFuncAttributeMaxDynamicSharedMemorySize, F8W_SMEM_BYTES));
-    ARISTOS_CUDA_TRY(cudaFuncSetAttribute(ffn_fp8_grouped_gemm_wg_kernel<true>,
-                                          cudaFuncAttributeMaxDynamicSharedMemorySize, F8W_SMEM_BYTES));
+    ARISTOS_CUDA_TRY(cudaFuncSetAttribute(ffn_fp8_grouped_gemm_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          F8_SMEM_BYTES));
     const int out_w = p.gated ? 128 : 256;
     int sms = device_sm_count();
     if (sms <= 0) { set_last_error("no CUDA device"); return ARISTOS_ERR_CUDA; }
@@ -939,9 +519,8 @@ aristos_status_t launch_fp8_gemm(const void* A, const void* B0, const void* B1, 
     const int64_t bound = (int64_t)p.groups * ceil_div(p.row_end - p.row_begin, F8_BM) * ceil_div(p.N, out_w);
     const int grid = (int)(bound < sms ? bound : sms);
     if (grid <= 0) return ARISTOS_OK;
-    if (legacy) ffn_fp8_grouped_gemm_kernel<2><<<grid, f8_threads(2), F8_SMEM_BYTES, st>>>(tmA, tmB0, tmB1, p, pa);
-    else if (p.outq) ffn_fp8_grouped_gemm_wg_kernel<true><<<grid, F8W_THREADS, F8W_SMEM_BYTES, st>>>(tmA, tmB0, tmB1, p, pa);
-    else ffn_fp8_grouped_gemm_wg_kernel<false><<<grid, F8W_THREADS, F8W_SMEM_BYTES, st>>>(tmA, tmB0, tmB1, p, pa);
+    if (subs == 2) ffn_fp8_grouped_gemm_kernel<2><<<grid, f8_threads(2), F8_SMEM_BYTES, st>>>(tmA, tmB0, tmB1, p, pa);
+    else ffn_fp8_grouped_gemm_kernel<4><<<grid, f8_threads(4), F8_SMEM_BYTES, st>>>(tmA, tmB0, tmB1, p, pa);
     ARISTOS_COUNT_LAUNCH();
     ARISTOS_CUDA_TRY(cudaGetLastError());
     return ARISTOS_OK;
@@ -979,20 +558,11 @@ aristos_status_t expert_ffn_fp8_sm100(const void* xq, const float* sx, const int
     p.sa = sx; p.sb0 = s1; p.sb1 = gated ? s3 : s1;
     p.out = static_cast<__nv_bfloat16*>(h);
     Fp8PeerArgs pa{};
-    if (fp8_fused_quant()) {
-        // the up projection's epilogue quantises its own output rows: no bf16 copy of the hidden activations
-        p.outq = static_cast<uint8_t*>(hq);
-        p.out_scales = sh;
-        ARISTOS_TRY(launch_fp8_gemm(xq, w1q, gated ? w3q : w1q, p, pa, sm_limit, st));
-        p.outq = nullptr;
-        p.out_scales = nullptr;
-    } else {
-        ARISTOS_TRY(launch_fp8_gemm(xq, w1q, gated ? w3q : w1q, p, pa, sm_limit, st));
-        // hidden activations: bf16 -> e4m3 per row and 128 columns (valid rows only)
-        quantize_group_rows_fp8_kernel<__nv_bfloat16><<<device_sm_count() * 4, 256, 0, st>>>(
-            static_cast<const __nv_bfloat16*>(h), count, groups, rows_per_group, I, static_cast<uint8_t*>(hq), sh);
-        ARISTOS_COUNT_LAUNCH();
-    }
+    ARISTOS_TRY(launch_fp8_gemm(xq, w1q, gated ? w3q : w1q, p, pa, sm_limit, st));
+    // hidden activations: bf16 -> e4m3 per row and 128 columns (valid rows only)
+    quantize_group_rows_fp8_kernel<__nv_bfloat16><<<device_sm_count() * 4, 256, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(h), count, groups, rows_per_group, I, static_cast<uint8_t*>(hq), sh);
+    ARISTOS_COUNT_LAUNCH();
     p.N = H; p.K = I; p.gated = 0; p.act = ARISTOS_ACT_IDENTITY;
     p.sa = sh; p.sb0 = s2; p.sb1 = s2;
     p.out = static_cast<__nv_bfloat16*>(y);
