@@ -30,6 +30,9 @@
 #include <cuda.h>
 #include <cuda_fp8.h>
 
+#include <cstdlib>
+#include <cstring>
+
 #include "common.cuh"
 #include "ptx_sm100.cuh"
 #include "tensor_map.cuh"
@@ -52,7 +55,12 @@ constexpr int F8_TBUFS = 2;                      // TMEM accumulator buffers (2 
 constexpr int f8_threads(int subs) { return 32 * (3 + 4 * subs); }
 constexpr int F8_MAX_GROUPS = 1024;
 constexpr int F8_AUX_BYTES = 256 + (F8_MAX_GROUPS + 1) * 4;
-constexpr int F8_SMEM_BYTES = 1024 + F8_STAGES * F8_STAGE_BYTES + F8_AUX_BYTES;
+constexpr int F8_AUX_ALIGNED = (F8_AUX_BYTES + 127) & ~127;
+constexpr int F8_QSTAGE_BYTES_PER_WARP = 32 * 32;            // quantised output: 32 rows x 32 codes per promotion warp
+constexpr int F8_AMAX_BYTES = 2 * 2 * 128 * 2 * 4;           // [tile parity][scale group][row][warp of the pair]
+constexpr int F8_SMEM_BYTES = 1024 + F8_STAGES * F8_STAGE_BYTES + F8_AUX_ALIGNED + 8 * F8_QSTAGE_BYTES_PER_WARP +
+                              F8_AMAX_BYTES;
+static_assert(F8_SMEM_BYTES <= 227 * 1024, "fp8 GEMM: shared memory");
 
 struct Fp8GemmParams {
     const int32_t* count;
@@ -64,6 +72,10 @@ struct Fp8GemmParams {
     const float* sb1;     // SwiGLU: scales of the up projection's weights
     __nv_bfloat16* out;   // [groups * rows_per_group][N]
     int32_t* dev_status;
+    // quantised output (up projection): e4m3 codes [groups * rows_per_group][N] and one fp32 scale per row and 128
+    // columns, bit for bit what quantising the bf16 output afterwards would give; `out` is not written then
+    uint8_t* outq;
+    float* out_scales;
 };
 static_assert(sizeof(Fp8GemmParams) <= 128, "Fp8GemmParams: keep the kernel argument within 128 bytes");
 
@@ -103,7 +115,7 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
     return *reinterpret_cast<uint32_t*>(&t);
 }
 
-template <int SUBS>
+template <int SUBS, bool QUANT>
 __global__ void __launch_bounds__(f8_threads(SUBS), 1)
 ffn_fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB0,
                             const __grid_constant__ CUtensorMap tmB1, const Fp8GemmParams p,
@@ -111,10 +123,11 @@ ffn_fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
     constexpr int F8_EPI_THREADS = 128 * SUBS;
     constexpr int CH = 8 / SUBS;                           // 32-column chunks per promotion thread
     constexpr int MMA2_WARP = 2 + 4 * SUBS;
+    static_assert(!QUANT || SUBS == 2, "the quantising epilogue pairs the two promotion warps of a lane quarter");
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* aux = smem + F8_STAGES * F8_STAGE_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(aux);     // full[S], empty[S], tfull[4], tempty[4]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(aux);     // full[S], empty[S], tfull[2], tempty[2], amax[4]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aux + 192);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(aux + 196);
     int* prefix = reinterpret_cast<int*>(aux + 256);
@@ -124,6 +137,7 @@ ffn_fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
     const uint32_t bar_empty = bar_full + 8 * F8_STAGES;
     const uint32_t bar_tfull = bar_empty + 8 * F8_STAGES;
     const uint32_t bar_tempty = bar_tfull + 8 * F8_TBUFS;
+    const uint32_t bar_amax = bar_tempty + 8 * F8_TBUFS;   // where the two promotion warps of a lane quarter meet
     const uint32_t smem_base = ptx::smem_u32(smem);
 
     const int out_w = p.gated ? 128 : 256;
@@ -141,6 +155,7 @@ ffn_fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
             ptx::mbar_init(bar_tfull + 8 * b, 1);
             ptx::mbar_init(bar_tempty + 8 * b, F8_EPI_THREADS);
         }
+        for (int q = 0; q < 4; ++q) ptx::mbar_init(bar_amax + 8 * q, 64);
         *abort_flag = 0;
         ptx::fence_mbar_init();
     }
@@ -247,6 +262,7 @@ ffn_fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
         const int half = (warp - 2) >> 2;                   // 0 .. SUBS - 1
         const int row_in_tile = quarter * 32 + lane;
         int vg = 0, tbuf = 0, rstage = 0;
+        int qtile = 0;                                      // tiles quantised so far (parity of the amax buffer)
         uint32_t tphase = 0;
         bool ok = true;
         for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
@@ -307,6 +323,90 @@ ffn_fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
                 if (++tbuf == F8_TBUFS) { tbuf = 0; tphase ^= 1u; }
             }
             if (!ok) break;
+            if constexpr (QUANT) {
+                // ---- epilogue, quantised: the tile's 128 (SwiGLU) or 2 x 128 output columns of a row are one or two
+                // scale groups, split between the two warps of the lane quarter: amax through shared memory
+                float amax[2] = {0.0f, 0.0f};              // the activated bf16 values replace acc[j] in place
+                const int nchunks = p.gated ? 2 : 4;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    if (j >= nchunks) break;
+                    const int ju = (j + 2) & 3;
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        float v0, v1;
+                        if (p.gated) {
+                            v0 = act_silu(acc[j][i].x) * acc[ju][i].x;
+                            v1 = act_silu(acc[j][i].y) * acc[ju][i].y;
+                        } else {
+                            v0 = acc[j][i].x;
+                            v1 = acc[j][i].y;
+                            if (p.act == ARISTOS_ACT_RELU) { v0 = act_relu(v0); v1 = act_relu(v1); }
+                            else if (p.act == ARISTOS_ACT_GELU) { v0 = act_gelu(v0); v1 = act_gelu(v1); }
+                        }
+                        const __nv_bfloat162 r = __floats2bfloat162_rn(v0, v1);     // the bf16 value is what is quantised
+                        acc[j][i] = make_float2(__low2float(r), __high2float(r));
+                        const int b = p.gated ? 0 : (j >> 1);
+                        amax[b] = fmaxf(amax[b], fmaxf(fabsf(acc[j][i].x), fabsf(acc[j][i].y)));
+                    }
+                }
+                float* ex = reinterpret_cast<float*>(aux + F8_AUX_ALIGNED + 8 * F8_QSTAGE_BYTES_PER_WARP) + (qtile & 1) * 512;
+                const uint32_t out_stage = ptx::smem_u32(aux + F8_AUX_ALIGNED) + (warp - 2) * F8_QSTAGE_BYTES_PER_WARP;
+                ex[row_in_tile * 2 + half] = amax[0];
+                ex[256 + row_in_tile * 2 + half] = amax[1];
+                ptx::mbar_arrive(bar_amax + 8 * quarter);
+                ok = ptx::mbar_wait_bounded(bar_amax + 8 * quarter, qtile & 1, abort_flag, p.dev_status);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                amax[0] = fmaxf(amax[0], ex[row_in_tile * 2 + (half ^ 1)]);
+                amax[1] = fmaxf(amax[1], ex[256 + row_in_tile * 2 + (half ^ 1)]);
+                ++qtile;
+                const size_t grow = (size_t)g * p.rows_per_group + row;
+                uint8_t* my_q = row_ok ? p.outq + grow * p.N + n0 : nullptr;
+                uint8_t* q2[2];                              // rows it * 16 + lane / 2 of this warp's 32
+#pragma unroll
+                for (int it = 0; it < 2; ++it)
+                    q2[it] = reinterpret_cast<uint8_t*>(
+                        __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(my_q), it * 16 + (lane >> 1)));
+                const int unit = lane & 1;
+#pragma unroll
+                for (int b = 0; b < 2; ++b) {
+                    if (b == 1 && p.gated) break;
+                    if (n0 + b * 128 >= p.N) break;
+                    const float scale = amax[b] > 0.0f ? amax[b] / 448.0f : 1.0f;
+                    const float inv = 1.0f / scale;
+                    if (row_ok && half == 0) p.out_scales[grow * nblk + blk + b] = scale;
+#pragma unroll
+                    for (int jj = 0; jj < 2; ++jj) {
+                        const int j = p.gated ? jj : 2 * b + jj;
+                        if (j >= 4) break;
+                        const int col = (half + 2 * j) * 32;
+                        uint32_t o[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            o[i] = 0;
+#pragma unroll
+                            for (int c = 0; c < 4; ++c) {
+                                const float2 pr = acc[j][2 * i + (c >> 1)];
+                                o[i] |= (uint32_t)__nv_cvt_float_to_fp8(((c & 1) ? pr.y : pr.x) * inv, __NV_SATFINITE, __NV_E4M3) << (8 * c);
+                            }
+                        }
+                        // row `lane`, 16-byte unit u lands at unit u ^ ((lane / 4) % 2): no bank conflicts either way
+#pragma unroll
+                        for (int u = 0; u < 2; ++u)
+                            ptx::st_shared_v4(out_stage + lane * 32 + ((u ^ ((lane >> 2) & 1)) << 4), o[4 * u], o[4 * u + 1],
+                                              o[4 * u + 2], o[4 * u + 3]);
+                        __syncwarp();
+#pragma unroll
+                        for (int it = 0; it < 2; ++it) {
+                            const int r = it * 16 + (lane >> 1);
+                            const uint4 val = ptx::ld_shared_v4(out_stage + r * 32 + ((unit ^ ((r >> 2) & 1)) << 4));
+                            if (q2[it] != nullptr) *reinterpret_cast<uint4*>(q2[it] + col + unit * 16) = val;
+                        }
+                        __syncwarp();
+                    }
+                }
+            } else {
             if (row_ok) {
                 __nv_bfloat16* obase = p.out;
                 int og = g;
@@ -359,6 +459,7 @@ ffn_fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
                         for (int i = 0; i < 4; ++i) dst[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
                     }
                 }
+            }
             }
         }
     }
@@ -508,10 +609,12 @@ aristos_status_t launch_fp8_gemm(const void* A, const void* B0, const void* B1, 
         const char* env = getenv("ARISTOS_FP8_PROMOTION_WARPS");
         subs = (env && atoi(env) == 4) ? 4 : 2;
     }
-    ARISTOS_CUDA_TRY(cudaFuncSetAttribute(ffn_fp8_grouped_gemm_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          F8_SMEM_BYTES));
-    ARISTOS_CUDA_TRY(cudaFuncSetAttribute(ffn_fp8_grouped_gemm_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          F8_SMEM_BYTES));
+    ARISTOS_CUDA_TRY(cudaFuncSetAttribute(ffn_fp8_grouped_gemm_kernel<2, false>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, F8_SMEM_BYTES));
+    ARISTOS_CUDA_TRY(cudaFuncSetAttribute(ffn_fp8_grouped_gemm_kernel<2, true>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, F8_SMEM_BYTES));
+    ARISTOS_CUDA_TRY(cudaFuncSetAttribute(ffn_fp8_grouped_gemm_kernel<4, false>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, F8_SMEM_BYTES));
     const int out_w = p.gated ? 128 : 256;
     int sms = device_sm_count();
     if (sms <= 0) { set_last_error("no CUDA device"); return ARISTOS_ERR_CUDA; }
@@ -519,8 +622,9 @@ aristos_status_t launch_fp8_gemm(const void* A, const void* B0, const void* B1, 
     const int64_t bound = (int64_t)p.groups * ceil_div(p.row_end - p.row_begin, F8_BM) * ceil_div(p.N, out_w);
     const int grid = (int)(bound < sms ? bound : sms);
     if (grid <= 0) return ARISTOS_OK;
-    if (subs == 2) ffn_fp8_grouped_gemm_kernel<2><<<grid, f8_threads(2), F8_SMEM_BYTES, st>>>(tmA, tmB0, tmB1, p, pa);
-    else ffn_fp8_grouped_gemm_kernel<4><<<grid, f8_threads(4), F8_SMEM_BYTES, st>>>(tmA, tmB0, tmB1, p, pa);
+    if (p.outq) ffn_fp8_grouped_gemm_kernel<2, true><<<grid, f8_threads(2), F8_SMEM_BYTES, st>>>(tmA, tmB0, tmB1, p, pa);
+    else if (subs == 2) ffn_fp8_grouped_gemm_kernel<2, false><<<grid, f8_threads(2), F8_SMEM_BYTES, st>>>(tmA, tmB0, tmB1, p, pa);
+    else ffn_fp8_grouped_gemm_kernel<4, false><<<grid, f8_threads(4), F8_SMEM_BYTES, st>>>(tmA, tmB0, tmB1, p, pa);
     ARISTOS_COUNT_LAUNCH();
     ARISTOS_CUDA_TRY(cudaGetLastError());
     return ARISTOS_OK;
@@ -558,11 +662,26 @@ aristos_status_t expert_ffn_fp8_sm100(const void* xq, const float* sx, const int
     p.sa = sx; p.sb0 = s1; p.sb1 = gated ? s3 : s1;
     p.out = static_cast<__nv_bfloat16*>(h);
     Fp8PeerArgs pa{};
-    ARISTOS_TRY(launch_fp8_gemm(xq, w1q, gated ? w3q : w1q, p, pa, sm_limit, st));
-    // hidden activations: bf16 -> e4m3 per row and 128 columns (valid rows only)
-    quantize_group_rows_fp8_kernel<__nv_bfloat16><<<device_sm_count() * 4, 256, 0, st>>>(
-        static_cast<const __nv_bfloat16*>(h), count, groups, rows_per_group, I, static_cast<uint8_t*>(hq), sh);
-    ARISTOS_COUNT_LAUNCH();
+    // ARISTOS_FP8_FUSED_QUANT=0: the up projection writes bf16 and a kernel of its own quantises it (the same bits)
+    static int fused_quant = -1;
+    if (fused_quant < 0) {
+        const char* env = getenv("ARISTOS_FP8_FUSED_QUANT");
+        fused_quant = (env && strcmp(env, "0") == 0) ? 0 : 1;
+    }
+    if (fused_quant) {
+        // the up projection's epilogue quantises its own output rows: no bf16 copy of the hidden activations
+        p.outq = static_cast<uint8_t*>(hq);
+        p.out_scales = sh;
+        ARISTOS_TRY(launch_fp8_gemm(xq, w1q, gated ? w3q : w1q, p, pa, sm_limit, st));
+        p.outq = nullptr;
+        p.out_scales = nullptr;
+    } else {
+        ARISTOS_TRY(launch_fp8_gemm(xq, w1q, gated ? w3q : w1q, p, pa, sm_limit, st));
+        // hidden activations: bf16 -> e4m3 per row and 128 columns (valid rows only)
+        quantize_group_rows_fp8_kernel<__nv_bfloat16><<<device_sm_count() * 4, 256, 0, st>>>(
+            static_cast<const __nv_bfloat16*>(h), count, groups, rows_per_group, I, static_cast<uint8_t*>(hq), sh);
+        ARISTOS_COUNT_LAUNCH();
+    }
     p.N = H; p.K = I; p.gated = 0; p.act = ARISTOS_ACT_IDENTITY;
     p.sa = sh; p.sb0 = s2; p.sb1 = s2;
     p.out = static_cast<__nv_bfloat16*>(y);

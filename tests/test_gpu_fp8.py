@@ -182,3 +182,49 @@ def test_config4_full_layer_on_one_gpu(oracle):
     res = parity.check_rank(cfg, L, x, wg, out, n_rows=8, seed=4)
     assert res["ok"], res
     L.close()
+
+
+_FFN_HASH = r"""
+import hashlib, sys
+import numpy as np, torch
+import cuplayground_b200.layer as layer
+out = []
+for (E, rows, H, I, act) in [(4, 640, 1024, 1536, 1), (3, 384, 512, 512, 2), (2, 256, 2048, 1024, 0)]:
+    g = torch.Generator(device="cuda").manual_seed(7)
+    mk = lambda shape, std: (torch.randn(shape, device="cuda", generator=g) * std).to(torch.bfloat16)
+    x, w1, w3, w2 = mk((E, rows, H), 1.0), mk((E, I, H), 0.05), mk((E, I, H), 0.05), mk((E, H, I), 0.05)
+    xq, sx = layer.quantize_fp8(x, 1)
+    w1q, s1 = layer.quantize_fp8(w1, 128)
+    w3q, s3 = layer.quantize_fp8(w3, 128) if act == 2 else (None, None)
+    w2q, s2 = layer.quantize_fp8(w2, 128)
+    cnt = np.array([rows - (37 * e) % rows if e % 3 else rows for e in range(E)], dtype=np.int32)
+    if E == 3: cnt[1] = 0
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    y = layer.expert_ffn_fp8(xq, sx, torch.from_numpy(cnt).cuda(), w1q, s1, w3q, s3, w2q, s2, act, dev_status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    yh = y.float().cpu().numpy()
+    for e in range(E): yh[e, cnt[e]:] = 0
+    assert np.isfinite(yh).all() and np.abs(yh).max() > 0
+    out.append(hashlib.sha256(yh.tobytes()).hexdigest())
+print("HASHES", *out)
+"""
+
+
+def test_hidden_activations_quantised_in_the_epilogue_give_the_same_bits():
+    """The up projection quantises its own output rows; with ARISTOS_FP8_FUSED_QUANT=0 it writes bf16 and a kernel
+    of its own quantises that. Both must give bit-identical expert outputs (ragged counts, an empty expert,
+    ReLU / GELU / SwiGLU)."""
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    got = {}
+    for fused in ("1", "0"):
+        env = dict(os.environ, ARISTOS_FP8_FUSED_QUANT=fused, PYTHONPATH=root)
+        r = subprocess.run([sys.executable, "-c", _FFN_HASH], cwd=root, env=env, capture_output=True, text=True,
+                           timeout=600)
+        assert r.returncode == 0, r.stderr[-2000:]
+        got[fused] = [l for l in r.stdout.splitlines() if l.startswith("HASHES")][-1]
+    assert got["1"] == got["0"]
