@@ -323,6 +323,7 @@ def run_ours(args, cfg, workload_desc):
     # stage times averaged over the timed steps (events recorded inside the timed region, at most the last 64)
     stage = L.stage_ms()
     exchange_out_ms = L.exchange_ms() if world > 1 else 0.0
+    exchange_split = L.exchange_profile() if world > 1 else None
     t = torch.tensor([ms], dtype=torch.float64, device="cuda")
     kept_t = torch.tensor([kept], dtype=torch.float64, device="cuda")
     if world > 1:
@@ -481,6 +482,10 @@ def run_ours(args, cfg, workload_desc):
                                 "gather_gbs": sent_bytes / (exchange_out_ms * 1e-3) / 1e9 if exchange_out_ms > 0 else None,
                                 "what": "rank 0: count + gather kernels storing kept rows into the owning ranks over "
                                         "NVLink, CUDA events inside the forward"}
+            if exchange_split is not None and exchange_split["gemms"] > 0:
+                # the expert-FFN stage of rank 0 split at its cross-rank waits: until every rank's counts have
+                # arrived, the GEMMs (arrival waits per source inside, return fused), until every return has arrived
+                line["exchange"]["stage_split_ms"] = exchange_split
         if parity is not None:
             line["parity"] = parity
         if variants is not None:

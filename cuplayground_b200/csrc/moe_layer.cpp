@@ -90,9 +90,11 @@ struct aristos_moe {
     aristos_training_state_t train_last = {};   // what the last forward saved
     // stage stopwatch
     static constexpr int PROF_SETS = 64;      // ring of event sets: stage times average over the last 64 forwards
+    static constexpr int PROF_EVENTS = 8;     // per set: 5 stage boundaries, "rows sent", "counts arrived", "GEMMs done"
     bool profiling = false;
     int64_t prof_n = 0;
-    std::vector<cudaEvent_t> ev_prof;         // [PROF_SETS][6]: 5 stage boundaries + "rows sent" of the direct exchange
+    std::vector<cudaEvent_t> ev_prof;         // [PROF_SETS][PROF_EVENTS]; 5-7 are marked by the direct exchange only
+    bool prof_exchange = false;               // the last forward marked events 6 and 7
     bool prof_sent = false;                   // this forward recorded event 5
 };
 
@@ -441,8 +443,9 @@ static aristos_status_t forward_impl(aristos_moe_t* L, const void* x, const void
         bias = L->gate_bias;
     }
 
-    const int prof_set = (int)(L->prof_n % aristos_moe::PROF_SETS) * 6;
+    const int prof_set = (int)(L->prof_n % aristos_moe::PROF_SETS) * aristos_moe::PROF_EVENTS;
     L->prof_sent = false;
+    L->prof_exchange = false;
 #define PROF_MARK(i) do { if (L->profiling) ARISTOS_CUDA_TRY(cudaEventRecord(L->ev_prof[prof_set + i], st)); } while (0)
     // NVTX ranges (host side: they bracket the enqueue of each stage, so a profiler timeline groups the stage's
     // launches; the reference links NVTX without calling it, CMakeLists.txt:104-118)
@@ -617,6 +620,7 @@ static aristos_status_t forward_impl(aristos_moe_t* L, const void* x, const void
         }
         if (overlap) ARISTOS_CUDA_TRY(cudaEventRecord(L->ev_in[0], cs));      // joined before the combine
         ARISTOS_TRY(ep_p2p_wait(L->p2p, EP_FLAG_COUNT, 0, st));
+        PROF_MARK(6);                // every rank's counts are here
         const bool tc = dt == ARISTOS_DTYPE_BF16 || dt == ARISTOS_DTYPE_F16 || dt == ARISTOS_DTYPE_TF32;
         for (int c = 0; c < nwin; ++c) {
             const int r0 = c * win_rows, r1 = std::min(L->cap, r0 + win_rows);
@@ -665,6 +669,8 @@ static aristos_status_t forward_impl(aristos_moe_t* L, const void* x, const void
                                              y_dst, cs));
             ARISTOS_TRY(ep_p2p_signal(L->p2p, EP_FLAG_RET, c, cs));
         }
+        PROF_MARK(7);                // this rank's GEMMs (and, fused, its return stores and flags) are done
+        L->prof_exchange = L->profiling;
         for (int c = 0; c < nwin; ++c)
             if (c * win_rows < L->cap) ARISTOS_TRY(ep_p2p_wait(L->p2p, EP_FLAG_RET, c, st));
         // the gather for the other ranks still reads x and the routing tensors: the caller's stream joins it
@@ -846,7 +852,7 @@ aristos_status_t aristos_moe_status(aristos_moe_t* L) {
 aristos_status_t aristos_moe_set_profiling(aristos_moe_t* L, int enable) {
     if (!L) return ARISTOS_ERR_INVALID_ARG;
     if (enable && L->ev_prof.empty()) {
-        L->ev_prof.assign(aristos_moe::PROF_SETS * 6, nullptr);
+        L->ev_prof.assign(aristos_moe::PROF_SETS * aristos_moe::PROF_EVENTS, nullptr);
         for (cudaEvent_t& e : L->ev_prof) ARISTOS_CUDA_TRY(cudaEventCreate(&e));
     }
     L->profiling = enable != 0;
@@ -860,7 +866,7 @@ aristos_status_t aristos_moe_stage_ms(aristos_moe_t* L, float out_ms[5]) {
     const int n = (int)std::min<int64_t>(L->prof_n, aristos_moe::PROF_SETS);
     double acc[5] = {0, 0, 0, 0, 0};
     for (int j = 0; j < n; ++j) {
-        const int set = (int)((L->prof_n - 1 - j) % aristos_moe::PROF_SETS) * 6;
+        const int set = (int)((L->prof_n - 1 - j) % aristos_moe::PROF_SETS) * aristos_moe::PROF_EVENTS;
         ARISTOS_CUDA_TRY(cudaEventSynchronize(L->ev_prof[set + 4]));
         for (int i = 0; i < 5; ++i) {
             float ms = 0.0f;
@@ -880,7 +886,7 @@ aristos_status_t aristos_moe_exchange_ms(aristos_moe_t* L, float* sent_ms) {
     const int n = (int)std::min<int64_t>(L->prof_n, aristos_moe::PROF_SETS);
     double acc = 0;
     for (int j = 0; j < n; ++j) {
-        const int set = (int)((L->prof_n - 1 - j) % aristos_moe::PROF_SETS) * 6;
+        const int set = (int)((L->prof_n - 1 - j) % aristos_moe::PROF_SETS) * aristos_moe::PROF_EVENTS;
         ARISTOS_CUDA_TRY(cudaEventSynchronize(L->ev_prof[set + 4]));
         ARISTOS_CUDA_TRY(cudaEventSynchronize(L->ev_prof[set + 5]));
         float ms = 0.0f;
@@ -888,6 +894,29 @@ aristos_status_t aristos_moe_exchange_ms(aristos_moe_t* L, float* sent_ms) {
         acc += ms;
     }
     *sent_ms = (float)(acc / n);
+    return ARISTOS_OK;
+}
+
+aristos_status_t aristos_moe_exchange_profile(aristos_moe_t* L, float* ms4) {
+    if (!L || !ms4) return ARISTOS_ERR_INVALID_ARG;
+    if (L->prof_n == 0) { set_last_error("exchange_profile: no forward has run since profiling was switched on"); return ARISTOS_ERR_INVALID_ARG; }
+    for (int i = 0; i < 4; ++i) ms4[i] = 0.0f;
+    if (!(L->p2p && L->ep_direct) || L->fp8 || !L->prof_exchange) return ARISTOS_OK;
+    const int n = (int)std::min<int64_t>(L->prof_n, aristos_moe::PROF_SETS);
+    double acc[4] = {0, 0, 0, 0};
+    for (int j = 0; j < n; ++j) {
+        const int set = (int)((L->prof_n - 1 - j) % aristos_moe::PROF_SETS) * aristos_moe::PROF_EVENTS;
+        ARISTOS_CUDA_TRY(cudaEventSynchronize(L->ev_prof[set + 4]));
+        ARISTOS_CUDA_TRY(cudaEventSynchronize(L->ev_prof[set + 5]));
+        // dispatch end -> rows sent | dispatch end -> counts arrived | counts arrived -> GEMMs done | -> returns arrived
+        const int from[4] = {2, 2, 6, 7}, to[4] = {5, 6, 7, 3};
+        for (int i = 0; i < 4; ++i) {
+            float ms = 0.0f;
+            ARISTOS_CUDA_TRY(cudaEventElapsedTime(&ms, L->ev_prof[set + from[i]], L->ev_prof[set + to[i]]));
+            acc[i] += ms;
+        }
+    }
+    for (int i = 0; i < 4; ++i) ms4[i] = (float)(acc[i] / n);
     return ARISTOS_OK;
 }
 

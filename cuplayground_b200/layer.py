@@ -311,6 +311,12 @@ class MoELayer:
         _lib.check(self._lib.aristos_moe_exchange_ms(self._h, C.byref(ms)))
         return float(ms.value)
 
+    def exchange_profile(self) -> dict:
+        """The expert-FFN stage of an expert-parallel layer split at its cross-rank waits (milliseconds)."""
+        ms = (C.c_float * 4)()
+        _lib.check(self._lib.aristos_moe_exchange_profile(self._h, ms))
+        return dict(rows_sent=ms[0], counts_arrived=ms[1], gemms=ms[2], returns_arrived=ms[3])
+
     def status(self) -> None:
         _lib.check(self._lib.aristos_moe_status(self._h))
 

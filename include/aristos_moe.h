@@ -230,6 +230,13 @@ ARISTOS_API aristos_status_t aristos_moe_stage_ms(aristos_moe_t* layer, float ou
  * rank's count and gather kernels have stored its rows into the owning ranks and raised their flags (the part of the
  * "expert FFN" stage that is the outgoing exchange), averaged like aristos_moe_stage_ms; 0 for other layers. */
 ARISTOS_API aristos_status_t aristos_moe_exchange_ms(aristos_moe_t* layer, float* sent_ms);
+/* The same layers, the "expert FFN" stage split at its cross-rank waits (CUDA events on the caller's stream, averaged
+ * like aristos_moe_stage_ms): out_ms = {dispatch end -> own rows sent (as aristos_moe_exchange_ms),
+ * dispatch end -> every rank's row counts have arrived, counts arrived -> this rank's expert GEMMs (with the arrival
+ * waits per source rank, the fused return stores and the return flags) are done, GEMMs done -> every rank's returned
+ * rows have arrived}; zeros for other layers. The reference's overlap prototype times its exchange as a whole
+ * (auditorium/overlap.cuh:206-236). */
+ARISTOS_API aristos_status_t aristos_moe_exchange_profile(aristos_moe_t* layer, float out_ms[4]);
 /* How the rows of an expert-parallel layer travel: "p2p" (the default: kernels store through the peers' CUDA-IPC
  * mapped exchange buffers over NVLink - the gather kernel writes every kept token row into the rank that owns its
  * expert, the down projection's epilogue writes every output tile into the rank the rows came from -, arrival is
