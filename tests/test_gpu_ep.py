@@ -203,9 +203,18 @@ def _worker_real(rank, world, uid, n_config, check_ranks, n_rows, env, q):
         L = layer.MoELayer(cfg, rank, world, uid)
         out = L.forward(x, wg, w1, w3, w2, scales=scales)
         L.status()
+        L.set_profiling(True)
         out2 = L.forward(x, wg, w1, w3, w2, scales=scales)
         L.status()
         assert torch.equal(out, out2), "two forwards must agree bit for bit"
+        stage, split = L.stage_ms(), L.exchange_profile()
+        L.set_profiling(False)
+        assert all(v >= 0.0 for v in split.values()), split
+        if cfg.torch_dtype != 4 and os.environ.get("ARISTOS_EP_TRANSPORT", "p2p") == "p2p" \
+                and os.environ.get("ARISTOS_EP_MODE", "direct") == "direct":
+            # the split of the expert-FFN stage at its cross-rank waits lies inside that stage
+            assert split["gemms"] > 0.0, split
+            assert split["counts_arrived"] + split["gemms"] + split["returns_arrived"] <= stage["ffn"] * 1.05 + 0.05, (split, stage)
         res = None
         if rank in check_ranks:
             res = parity.check_rank(cfg, L, x, wg, out, n_rows=n_rows, seed=rank)
