@@ -48,12 +48,14 @@ struct aristos_moe {
     void *xq = nullptr, *xgq = nullptr, *hq = nullptr;
     float *sx = nullptr, *sxg = nullptr, *sh = nullptr;
     void *dispatch_scratch = nullptr, *xg = nullptr, *xr = nullptr, *h = nullptr, *yr = nullptr, *yg = nullptr;
-    // host-activation path: two staging slots so that the copies of one call overlap the kernels of its neighbours
+    // host-activation path: staging slots, so that the copy-in of one call, the kernels of another and the copy-out
+    // of a third run at once (a forward shorter than its copies needs three in flight to keep both copy engines busy)
+    static constexpr int HOST_SLOTS = 4;
     struct HostSlot {
         void *x_dev = nullptr, *out_dev = nullptr;
         cudaEvent_t h2d_done = nullptr, compute_done = nullptr, d2h_done = nullptr;
         bool busy = false;
-    } slots[2];
+    } slots[HOST_SLOTS];
     int slot_next = 0;
     cudaStream_t h2d_stream = nullptr, d2h_stream = nullptr;
     size_t dispatch_scratch_bytes = 0;
@@ -172,10 +174,10 @@ size_t plan_workspace(aristos_moe* L, char* base) {
         L->xr = L->xg;
         L->yg = L->yr;
     }
-    CARVE(slots[0].x_dev, void*, S * H * elt)
-    CARVE(slots[0].out_dev, void*, S * H * elt)
-    CARVE(slots[1].x_dev, void*, S * H * elt)
-    CARVE(slots[1].out_dev, void*, S * H * elt)
+    for (int i = 0; i < aristos_moe::HOST_SLOTS; ++i) {
+        CARVE(slots[i].x_dev, void*, S * H * elt)
+        CARVE(slots[i].out_dev, void*, S * H * elt)
+    }
 #undef CARVE
     return c.off;
 }
@@ -761,8 +763,8 @@ aristos_status_t aristos_moe_submit_host(aristos_moe_t* L, const void* x_host, c
     }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     aristos_moe::HostSlot& sl = L->slots[L->slot_next];
-    L->slot_next ^= 1;
-    if (sl.busy) {                       // the call that used this slot two submissions ago must have drained
+    L->slot_next = (L->slot_next + 1) % aristos_moe::HOST_SLOTS;
+    if (sl.busy) {                       // the call that used this slot HOST_SLOTS submissions ago must have drained
         sl.busy = false;
         ARISTOS_TRY(wait_event_bounded(L, sl.d2h_done));
     }

@@ -273,7 +273,7 @@ class MoELayer:
         return out_host
 
     def submit_host(self, x_host, w_gate, w1, w3, w2, out_host, gate_bias=None, stream=None, scales=None):
-        """Asynchronous forward_host: returns once the copies and kernels are enqueued (two calls may be in flight);
+        """Asynchronous forward_host: returns once the copies and kernels are enqueued (four calls may be in flight);
         the host tensors must stay alive and untouched until wait_host()."""
         if x_host.is_cuda or out_host.is_cuda:
             raise ValueError("submit_host takes host tensors")

@@ -161,7 +161,7 @@ ARISTOS_API aristos_status_t aristos_moe_forward_host(aristos_moe_t* layer, cons
                                                       void* stream);
 /* The same, split in two so that consecutive calls overlap: aristos_moe_submit_host enqueues the host-to-device copy
  * (own copy stream), the forward (on `stream`) and the device-to-host copy (own copy stream) and returns; the copies
- * of one call run under the kernels of its neighbours. Two calls may be in flight (a third submit first waits for
+ * of one call run under the kernels of its neighbours. Four calls may be in flight (a fifth submit first waits for
  * the oldest); x_host / out_host must stay valid, and should be pinned, until aristos_moe_wait_host returns.
  * aristos_moe_forward_host == submit + wait. */
 ARISTOS_API aristos_status_t aristos_moe_submit_host(aristos_moe_t* layer, const void* x_host, const void* w_gate,

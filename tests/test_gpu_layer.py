@@ -243,24 +243,25 @@ def test_bounded_device_wait_times_out_and_context_survives(oracle):
 
 
 def test_submit_host_pipelines_consecutive_calls(oracle):
-    """Three host-side calls in flight back to back (two staging slots, the third waits for the first): every
-    call's result equals the device-resident forward of the same input."""
+    """Six host-side calls back to back (four staging slots: the fifth waits for the first, the sixth for the
+    second): every call's result equals the device-resident forward of the same input."""
     torch, cp, layer = _mods()
     cfg = cp.AristosConfig(capacity_factor=1.25, drop_tokens=1, expert_top_k=2, hidden_act=2, hidden_size=256,
                            intermediate_size=512, num_experts=8, torch_dtype=2, tokens=1024)
     dt = torch.bfloat16
     _, wg, w1, w3, w2 = make_inputs(1024, 256, 512, 8, 5, swiglu=True, w_std=0.05)
     dev_w = [to_dev(a, dt) for a in (wg, w1, w3, w2)]
-    xs = [make_inputs(1024, 256, 512, 8, 50 + i, w_std=0.05)[0] for i in range(3)]
+    n_calls = 6
+    xs = [make_inputs(1024, 256, 512, 8, 50 + i, w_std=0.05)[0] for i in range(n_calls)]
     L = layer.MoELayer(cfg)
     expect = [L.forward(to_dev(x, dt), *dev_w).cpu() for x in xs]
     xh = [torch.from_numpy(x).to(dt).pin_memory() for x in xs]
     oh = [torch.empty_like(t).pin_memory() for t in xh]
-    for i in range(3):
+    for i in range(n_calls):
         L.submit_host(xh[i], *dev_w, oh[i])
     L.wait_host()
     L.status()
-    for i in range(3):
+    for i in range(n_calls):
         assert torch.equal(oh[i], expect[i]), i
     L.close()
 
