@@ -95,6 +95,13 @@ public:
         check(aristos_moe_stage_ms(h_, ms));
         return StageMs{ms[0], ms[1], ms[2], ms[3], ms[4]};
     }
+    // Expert-parallel peer-memory layers: the expert-FFN stage split at its cross-rank waits (milliseconds).
+    struct ExchangeMs { float rows_sent, counts_arrived, gemms, returns_arrived; };
+    ExchangeMs exchange_profile() {
+        float ms[4];
+        check(aristos_moe_exchange_profile(h_, ms));
+        return ExchangeMs{ms[0], ms[1], ms[2], ms[3]};
+    }
     // Expert-parallel layers: wall-clock limit of status() / destruction when a peer stops taking part.
     void set_timeout_ms(int ms) { check(aristos_moe_set_timeout_ms(h_, ms)); }
     // is_training = 1: what the last forward saved (device pointers), and where the next forwards save.
