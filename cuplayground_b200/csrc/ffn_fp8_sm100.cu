@@ -25,8 +25,12 @@
 // Same tile contract as the 16-bit kernel (ffn_sm100.cu; reference: fGET, mma.cuh:46-179, A (M,K) and B (N,K)
 // row-major, epilogue act(acc)): persistent CTAs, warp 0 = TMA producer (a 128-byte K block is exactly one swizzled
 // row; four 48 KB stages), warps 1 and 10 = MMA issuers, warps 2-9 = promotion + epilogue. SwiGLU tiles hold 128 gate
-// and 128 up columns in one N = 256 instruction. Output is bf16, written with 16-byte stores masked by the group's
-// row count (to this rank's buffer, or straight into the source ranks' buffers through peer pointers).
+// and 128 up columns in one N = 256 instruction. The down projection's output is bf16, written with 16-byte stores
+// masked by the group's row count (to this rank's buffer, or straight into the source ranks' buffers through peer
+// pointers). The up projection's output feeds the down projection as e4m3: its epilogue rounds to bf16, takes each
+// row's amax over the 128-column scale group (held half and half by the two promotion warps of a lane quarter, which
+// meet on an mbarrier with a bounded wait) and writes codes and scales of the valid rows - the same bits as
+// quantising a bf16 copy afterwards, without the copy.
 #include <cuda.h>
 #include <cuda_fp8.h>
 
