@@ -60,7 +60,8 @@ constexpr int f8_threads(int subs) { return 32 * (3 + 4 * subs); }
 constexpr int F8_MAX_GROUPS = 1024;
 constexpr int F8_AUX_BYTES = 256 + (F8_MAX_GROUPS + 1) * 4;
 constexpr int F8_AUX_ALIGNED = (F8_AUX_BYTES + 127) & ~127;
-constexpr int F8_QSTAGE_BYTES_PER_WARP = 32 * 32;            // quantised output: 32 rows x 32 codes per promotion warp
+constexpr int F8_QSTAGE_BYTES_PER_WARP = 2048;               // output staging per promotion warp: 16 rows x 128 bytes of
+                                                             // bf16 (plain output) or 32 rows x 32 codes (quantised)
 constexpr int F8_AMAX_BYTES = 2 * 2 * 128 * 2 * 4;           // [tile parity][scale group][row][warp of the pair]
 constexpr int F8_SMEM_BYTES = 1024 + F8_STAGES * F8_STAGE_BYTES + F8_AUX_ALIGNED + 8 * F8_QSTAGE_BYTES_PER_WARP +
                               F8_AMAX_BYTES;
@@ -285,7 +286,14 @@ ffn_fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
             const float* sb0_row = p.sb0 + ((size_t)e * nblk + blk) * kblocks;
             const float* sb1_row = p.gated ? p.sb1 + ((size_t)e * nblk + blk) * kblocks
                                            : p.sb0 + ((size_t)e * nblk + min(blk + 1, nblk - 1)) * kblocks;
-            float2 acc[CH][16];                              // chunk j = half + SUBS j, 32 columns as 16 pairs
+            // Which 32-column chunks a thread owns: SwiGLU tiles and the quantising epilogue interleave the warps of a
+            // lane quarter (chunk j of a thread = half + SUBS j), so a thread holds matching gate / up columns or half
+            // of each scale group; plain output gives every thread CH adjacent chunks (256 / SUBS contiguous columns),
+            // so that its row leaves in whole 128-byte lines. The sums per output element are the same either way.
+            const bool contig = !QUANT && !p.gated;
+            const uint32_t cbase = contig ? half * (256 / SUBS) : half * 32;
+            const uint32_t cstride = contig ? 32 : 32 * SUBS;
+            float2 acc[CH][16];                              // chunk j at columns cbase + j * cstride, as 16 pairs
 #pragma unroll
             for (int j = 0; j < CH; ++j)
 #pragma unroll
@@ -301,7 +309,7 @@ ffn_fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
                 if (threadIdx.x == 64) ptx::mbar_arrive(bar_empty + 8 * rstage);
                 if (++rstage == F8_STAGES) rstage = 0;
                 ptx::tcgen05_fence_after();
-                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + tbuf * F8_BN + half * 32;
+                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + tbuf * F8_BN + cbase;
                 // 2 CH 16-column loads, one in flight while the previous one is accumulated
                 uint32_t v[2][16];
                 ptx::tmem_ld_32x32b_x16(taddr, v[0]);
@@ -309,8 +317,8 @@ ffn_fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
 #pragma unroll
                 for (int s = 0; s < 2 * CH; ++s) {
                     if (s + 1 < 2 * CH)
-                        ptx::tmem_ld_32x32b_x16(taddr + ((s + 1) >> 1) * (32 * SUBS) + ((s + 1) & 1) * 16, v[(s + 1) & 1]);
-                    const float w = s < CH ? w_lo : w_hi;
+                        ptx::tmem_ld_32x32b_x16(taddr + ((s + 1) >> 1) * cstride + ((s + 1) & 1) * 16, v[(s + 1) & 1]);
+                    const float w = cbase + (s >> 1) * cstride < 128 ? w_lo : w_hi;
                     const float2 w2 = make_float2(w, w);
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
@@ -411,7 +419,7 @@ ffn_fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
                     }
                 }
             } else {
-            if (row_ok) {
+            if (row_ok && (p.gated || SUBS != 2)) {
                 __nv_bfloat16* obase = p.out;
                 int og = g;
                 int orows = p.rows_per_group, orow_idx = row;
@@ -445,10 +453,10 @@ ffn_fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
 #pragma unroll
                         for (int i = 0; i < 4; ++i) dst[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
                     }
-                } else {
+                } else if (SUBS != 2) {
 #pragma unroll
                     for (int j = 0; j < CH; ++j) {
-                        const int col = (half + SUBS * j) * 32;
+                        const int col = cbase + j * 32;
                         if (n0 + col >= p.N) break;
                         uint32_t o[16];
 #pragma unroll
@@ -461,6 +469,67 @@ ffn_fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
                         uint4* dst = reinterpret_cast<uint4*>(orow + col);
 #pragma unroll
                         for (int i = 0; i < 4; ++i) dst[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+                    }
+                }
+            }
+            if (!QUANT && !p.gated && SUBS == 2 && n0 + (int)cbase < p.N) {
+                // Plain output, two promotion warps per lane quarter: a thread holds 128 adjacent columns (256 bytes)
+                // of its row. The rows leave through the warp's staging area, 16 rows x 128 bytes at a time, so that a
+                // store instruction writes four whole 128-byte lines (local memory, or a peer's over NVLink) instead
+                // of 32 separate 16-byte pieces.
+                __nv_bfloat16* my_dst = nullptr;             // where this lane's row goes (column n0 + cbase), if valid
+                if (row_ok) {
+                    __nv_bfloat16* obase = p.out;
+                    int og = g;
+                    int orows = p.rows_per_group, orow_idx = row;
+                    if (pa.peer_world > 0 && pa.src_off != nullptr) {
+                        const int32_t* off = pa.src_off + g * (pa.peer_world + 1);
+                        int src = 0;
+                        while (src + 1 < pa.peer_world && row >= __ldg(off + src + 1)) ++src;
+                        obase = pa.peer_out[src];
+                        og = pa.peer_rank * p.experts + g;
+                        orows = pa.ret_rows;
+                        orow_idx = row - __ldg(off + src);
+                    } else if (pa.peer_world > 0) {
+                        const int src = g / p.experts;
+                        obase = pa.peer_out[src];
+                        og = pa.peer_rank * p.experts + (g - src * p.experts);
+                    }
+                    my_dst = obase + ((size_t)og * orows + orow_idx) * p.N + n0 + cbase;
+                }
+                const uint32_t out_stage = ptx::smem_u32(aux + F8_AUX_ALIGNED) + (warp - 2) * F8_QSTAGE_BYTES_PER_WARP;
+                const int unit = lane & 7;
+#pragma unroll
+                for (int jp = 0; jp < CH / 2; ++jp) {        // chunks 2 jp and 2 jp + 1: 64 columns = one 128-byte line
+                    uint32_t o[32];
+#pragma unroll
+                    for (int jj = 0; jj < 2; ++jj)
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            float v0 = acc[2 * jp + jj][i].x, v1 = acc[2 * jp + jj][i].y;
+                            if (p.act == ARISTOS_ACT_RELU) { v0 = act_relu(v0); v1 = act_relu(v1); }
+                            else if (p.act == ARISTOS_ACT_GELU) { v0 = act_gelu(v0); v1 = act_gelu(v1); }
+                            o[jj * 16 + i] = pack_bf16x2(v0, v1);
+                        }
+#pragma unroll
+                    for (int hr = 0; hr < 2; ++hr) {         // lanes 0-15, then lanes 16-31
+                        if ((lane >> 4) == hr) {
+                            const int r = lane & 15;
+#pragma unroll
+                            for (int u = 0; u < 8; ++u)      // 16-byte unit u of row r lands at unit u ^ (r % 8)
+                                ptx::st_shared_v4(out_stage + r * 128 + ((u ^ (r & 7)) << 4), o[4 * u], o[4 * u + 1],
+                                                  o[4 * u + 2], o[4 * u + 3]);
+                        }
+                        __syncwarp();
+#pragma unroll
+                        for (int it = 0; it < 4; ++it) {
+                            const int r = it * 4 + (lane >> 3);  // staged row; lane hr * 16 + r of the warp owns it
+                            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(
+                                __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(my_dst), hr * 16 + r));
+                            const uint4 val = ptx::ld_shared_v4(out_stage + r * 128 + ((unit ^ (r & 7)) << 4));
+                            if (dst != nullptr) *reinterpret_cast<uint4*>(dst + jp * 64 + unit * 8) = val;
+                        }
+                        __syncwarp();
                     }
                 }
             }
