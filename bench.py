@@ -299,7 +299,8 @@ def run_ours(args, cfg, workload_desc):
     for _ in range(args.warmup):
         L.forward(x, wg, w1, w3, w2, out=out, scales=scales)
     L.status()
-    kept = int(L.routing()["count"].sum())
+    count_mine = L.routing()["count"].to(torch.float64)     # kept rows of this rank's tokens, per (global) expert
+    kept = int(count_mine.sum())
     L.set_profiling(True)      # stage stopwatch: events inside the timed region, averaged over its steps
     # the sampler thread starts before the barrier: NVML start-up on rank 0 must not delay its first timed step
     # (the other ranks would wait for it inside their timed region)
@@ -331,6 +332,13 @@ def run_ours(args, cfg, workload_desc):
         dist.all_reduce(kept_t, op=dist.ReduceOp.SUM)
     ms = float(t.item())
     kept_all = float(kept_t.item())
+    # rows every rank's experts receive (rank r owns experts [r E/world, (r + 1) E/world)): the forward ends when the
+    # busiest rank's GEMMs end, whatever the average is
+    busiest_rows = kept_all
+    if world > 1:
+        per_expert = count_mine.cuda()
+        dist.all_reduce(per_expert, op=dist.ReduceOp.SUM)
+        busiest_rows = float(per_expert.view(world, -1).sum(dim=1).max().item())
     value = S * world * args.steps / (ms * 1e-3)
 
     # ---- end to end: host activations in, host result out, through the public host API. Every step copies its own
@@ -454,6 +462,13 @@ def run_ours(args, cfg, workload_desc):
                     "peak_source": f"{peaks['source']} bf16 burst (cuBLAS 8192^3, best of 10)",
                     "launches_per_step": 2, "flops_per_step": ffn_flops, "ms_per_step": stage["ffn"]}
         t_roof, terms = layer_roofline(cfg, world, kept_all / world)
+        if world > 1:
+            # the same with the rows of the busiest rank in the tensor term (routing decides how many rows an expert,
+            # and with it a rank, gets: up to the capacity factor above the mean, more with a skewed prior)
+            t_busy, _ = layer_roofline(cfg, world, busiest_rows)
+            terms["rows_received"] = {"mean_per_rank": kept_all / world, "busiest_rank": busiest_rows,
+                                      "busiest_over_mean": busiest_rows / (kept_all / world)}
+            terms["frac_busiest_rank"] = t_busy / (ms / args.steps * 1e-3)
         line = {"metric": "moe_fwd_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
                 "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": {0: "f32", 1: "tf32", 2: "bf16", 3: "f16", 4: "fp8_e4m3"}[cfg.torch_dtype],
