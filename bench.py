@@ -296,8 +296,14 @@ def run_ours(args, cfg, workload_desc):
             torch.cuda.synchronize()
 
     # ---- device-resident throughput ---------------------------------------------------------------------------------
+    # Expert placement for a skewed prior: across ranks the experts are held round-robin (expert e by rank e % N), so
+    # the prior's hot experts spread over the ranks instead of all belonging to rank 0. The prior, indexed by expert
+    # slot, is passed as the forward's gate_bias; one GPU: the layer's own prior, unchanged.
+    gate_bias = None
+    if world > 1 and cfg.gate_bias_zipf_s > 0 and not args.contiguous_experts:
+        gate_bias = layer.interleaved_expert_prior(layer.zipf_prior(cfg.num_experts, cfg.gate_bias_zipf_s), world).cuda()
     for _ in range(args.warmup):
-        L.forward(x, wg, w1, w3, w2, out=out, scales=scales)
+        L.forward(x, wg, w1, w3, w2, gate_bias=gate_bias, out=out, scales=scales)
     L.status()
     count_mine = L.routing()["count"].to(torch.float64)     # kept rows of this rank's tokens, per (global) expert
     kept = int(count_mine.sum())
@@ -313,7 +319,7 @@ def run_ours(args, cfg, workload_desc):
     ev0.record()
     t_host0 = time.perf_counter()
     for _ in range(args.steps):
-        L.forward(x, wg, w1, w3, w2, out=out, scales=scales)
+        L.forward(x, wg, w1, w3, w2, gate_bias=gate_bias, out=out, scales=scales)
     host_enqueue_ms = (time.perf_counter() - t_host0) * 1e3 / args.steps   # host time to enqueue one forward
     ev1.record()
     barrier()
@@ -348,14 +354,14 @@ def run_ours(args, cfg, workload_desc):
     NBUF = 4                        # as many host buffer pairs as the host API keeps calls in flight
     xh = [x.cpu().pin_memory() for _ in range(NBUF)]
     oh = [torch.empty_like(xh[0]).pin_memory() for _ in range(NBUF)]
-    L.forward_host(xh[0], wg, w1, w3, w2, oh[0], scales=scales)
+    L.forward_host(xh[0], wg, w1, w3, w2, oh[0], gate_bias=gate_bias, scales=scales)
     # enough steps that filling and draining the three-stage pipeline (copy in | kernels | copy out) is amortised: a
     # forward of a fraction of a millisecond gets 100 steps, the 8 ms forward of the default workload at most 20
     e2e_steps = max(4, min(args.steps, 20)) if ms / args.steps >= 2.0 else 100
     barrier()
     t_start = time.perf_counter()
     for i in range(e2e_steps):
-        L.submit_host(xh[i % NBUF], wg, w1, w3, w2, oh[i % NBUF], scales=scales)
+        L.submit_host(xh[i % NBUF], wg, w1, w3, w2, oh[i % NBUF], gate_bias=gate_bias, scales=scales)
     L.wait_host()
     torch.cuda.synchronize()
     t_e2e = time.perf_counter() - t_start
@@ -368,7 +374,7 @@ def run_ours(args, cfg, workload_desc):
     barrier()
     t_start = time.perf_counter()
     for i in range(4):
-        L.forward_host(xh[i & 1], wg, w1, w3, w2, oh[i & 1], scales=scales)
+        L.forward_host(xh[i & 1], wg, w1, w3, w2, oh[i & 1], gate_bias=gate_bias, scales=scales)
     t_blk = time.perf_counter() - t_start
     tb = torch.tensor([t_blk * 1e3], dtype=torch.float64, device="cuda")
     if world > 1:
@@ -399,7 +405,8 @@ def run_ours(args, cfg, workload_desc):
             oracle.build()
             oracle.use_all_cores()
             try:
-                mine = parity_mod.check_rank(cfg, L, x, wg, out, n_rows=16 if cfg.torch_dtype == 4 else 64, seed=rank)
+                mine = parity_mod.check_rank(cfg, L, x, wg, out, n_rows=16 if cfg.torch_dtype == 4 else 64, seed=rank,
+                                             gate_bias=None if gate_bias is None else gate_bias.cpu().numpy())
             except AssertionError as e:
                 mine = {"ok": False, "routing": f"MISMATCH: {e}", "rows": 0, "max_rel": None, "mean_rel": None}
             mine["rank"] = rank
@@ -423,7 +430,7 @@ def run_ours(args, cfg, workload_desc):
     # ---- both tile shapes of the expert GEMM, timed in this process (one GPU, 16-bit tensor-core workloads)
     variants = None
     if world == 1 and cfg.torch_dtype in (2, 3) and cfg.capacity >= 1024 and not args.no_variants:
-        variants = time_ffn_variants(L, lambda: L.forward(x, wg, w1, w3, w2, out=out, scales=scales), cfg, kept,
+        variants = time_ffn_variants(L, lambda: L.forward(x, wg, w1, w3, w2, gate_bias=gate_bias, out=out, scales=scales), cfg, kept,
                                      local_rank, max(3, min(args.steps, 10)))
 
     if rank == 0:
@@ -474,7 +481,8 @@ def run_ours(args, cfg, workload_desc):
                 "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": {0: "f32", 1: "tf32", 2: "bf16", 3: "f16", 4: "fp8_e4m3"}[cfg.torch_dtype],
                 "data": "synthetic",
                 "config": {"workload": workload_desc, "name": args.workload, "tokens_per_rank": S,
-                           "parallelism": f"ep{world}", "ep_transport": L.ep_transport, "l2": "weights (>= 0.4 GB per rank) exceed the 126 MB L2, "
+                           "parallelism": f"ep{world}", "ep_transport": L.ep_transport,
+                           "expert_placement": "round-robin over the ranks (prior indexed by expert slot)" if gate_bias is not None else "contiguous blocks", "l2": "weights (>= 0.4 GB per rank) exceed the 126 MB L2, "
                            "no flush needed between steps", "kept_assignments": kept_all},
                 "clocks": clocks,
                 "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": xh[0].numel() * xh[0].element_size() * world,
@@ -540,6 +548,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-parity", action="store_true", help="skip the oracle check of the last forward")
     ap.add_argument("--no-variants", action="store_true", help="skip the timing of both GEMM tile shapes")
+    ap.add_argument("--contiguous-experts", action="store_true",
+                    help="N > 1, skewed prior: leave the prior's hot experts on the first rank (no round-robin placement)")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3     # timing rule: at least three warm-up steps

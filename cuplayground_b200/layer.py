@@ -49,6 +49,32 @@ def fill_normal(t: torch.Tensor, mean: float, std: float, seed: int, stream_id: 
     return t
 
 
+def zipf_prior(num_experts: int, s: float) -> torch.Tensor:
+    """The per-expert gate prior of `gate_bias_zipf_s` (-s ln(e + 1), fp32, host) as the layer builds it itself."""
+    b = (C.c_float * num_experts)()
+    _lib.check(_lib.load().aristos_zipf_bias_host(b, num_experts, float(s)))
+    return torch.tensor(list(b), dtype=torch.float32)
+
+
+def interleaved_expert_prior(prior: torch.Tensor, world: int) -> torch.Tensor:
+    """Round-robin expert placement for a per-expert gate prior given in the experts' own order (entry e = expert e).
+
+    A rank owns a contiguous block of E / world expert slots (rank r: slots [r E/world, (r + 1) E/world)). Holding
+    expert e in slot (e % world) * (E / world) + e // world gives consecutive experts to different ranks, so the hot
+    experts of a skewed prior do not all land on rank 0. Returns the prior indexed by slot - the gate_bias argument
+    of the forward; the gate and expert weights of slot p are then those of expert (p % (E/world)) * world +
+    p // (E/world). With world = 1 the prior is returned unchanged."""
+    E = prior.numel()
+    if world <= 1:
+        return prior.clone()
+    if E % world != 0:
+        raise ValueError("the number of experts must be a multiple of the number of ranks")
+    El = E // world
+    slots = torch.arange(E)
+    expert_of_slot = (slots % El) * world + slots // El
+    return prior[expert_of_slot].clone()
+
+
 def synthetic_tensors(cfg: AristosConfig, rank: int = 0, world: int = 1):
     """Seeded synthetic inputs of one rank, generated on the device: x ~ N(0,1) (a different stream per rank),
     gate weights and this rank's expert weights ~ N(0, 0.02). Expert e draws from its own Philox streams, so the

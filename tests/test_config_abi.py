@@ -232,3 +232,24 @@ def test_lazy_package_attributes_resolve_in_a_fresh_interpreter():
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     r = subprocess.run([sys.executable, "-c", code], cwd=root, capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stderr[-2000:]
+
+
+def test_round_robin_expert_placement_of_a_prior():
+    """interleaved_expert_prior: expert e is held in slot (e % world) * (E / world) + e // world, i.e. by rank
+    e % world; the hot experts of a Zipf prior end up one per rank and world = 1 changes nothing."""
+    import torch
+    import cuplayground_b200.layer as layer
+
+    E, world = 128, 8
+    prior = layer.zipf_prior(E, 1.2)
+    assert prior[0] == 0 and all(prior[i] > prior[i + 1] for i in range(E - 1))
+    slots = layer.interleaved_expert_prior(prior, world)
+    El = E // world
+    for e in range(E):
+        assert slots[(e % world) * El + e // world] == prior[e]
+    assert sorted(slots.tolist()) == sorted(prior.tolist())
+    owners_of_hottest = {int(torch.nonzero(slots == prior[e])[0]) // El for e in range(world)}
+    assert owners_of_hottest == set(range(world))
+    assert torch.equal(layer.interleaved_expert_prior(prior, 1), prior)
+    with pytest.raises(ValueError):
+        layer.interleaved_expert_prior(prior[:100], 8)
