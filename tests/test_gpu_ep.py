@@ -201,10 +201,13 @@ def _worker_real(rank, world, uid, n_config, check_ranks, n_rows, env, q):
         cfg = cp.baseline_config(n_config, world=world)
         x, wg, w1, w3, w2, scales = layer.synthetic_tensors(cfg, rank, world)
         L = layer.MoELayer(cfg, rank, world, uid)
-        out = L.forward(x, wg, w1, w3, w2, scales=scales)
+        gate_bias = None
+        if env.get("TEST_ROUND_ROBIN_PLACEMENT") == "1":     # the skewed prior, re-indexed by expert slot
+            gate_bias = layer.interleaved_expert_prior(layer.zipf_prior(cfg.num_experts, cfg.gate_bias_zipf_s), world).cuda()
+        out = L.forward(x, wg, w1, w3, w2, gate_bias=gate_bias, scales=scales)
         L.status()
         L.set_profiling(True)
-        out2 = L.forward(x, wg, w1, w3, w2, scales=scales)
+        out2 = L.forward(x, wg, w1, w3, w2, gate_bias=gate_bias, scales=scales)
         L.status()
         assert torch.equal(out, out2), "two forwards must agree bit for bit"
         stage, split = L.stage_ms(), L.exchange_profile()
@@ -217,8 +220,13 @@ def _worker_real(rank, world, uid, n_config, check_ranks, n_rows, env, q):
             assert split["counts_arrived"] + split["gemms"] + split["returns_arrived"] <= stage["ffn"] * 1.05 + 0.05, (split, stage)
         res = None
         if rank in check_ranks:
-            res = parity.check_rank(cfg, L, x, wg, out, n_rows=n_rows, seed=rank)
+            res = parity.check_rank(cfg, L, x, wg, out, n_rows=n_rows, seed=rank,
+                                    gate_bias=None if gate_bias is None else gate_bias.cpu().numpy())
             assert res["ok"], res
+            if gate_bias is not None:
+                # placement spreads the prior's hot experts: no rank's experts receive more than twice the mean
+                count = L.routing()["count"].view(world, -1).sum(dim=1).float()
+                assert float(count.max()) <= 2.0 * float(count.mean()), count
         L.close()
         q.put((rank, "ok", res))
     except Exception as e:      # pragma: no cover - reported to the parent
@@ -271,6 +279,13 @@ def test_config5_real_shape_expert_parallel():
     """Skewed routing (8192 tokens per rank, 128 experts, top-4, Zipf prior, capacity factor 1 with drops)."""
     res = _run_real(_largest_world(), 5, 64)
     assert all(r["kept"] < r["rows"] * 4 for r in res) or True      # drops are likely but not required in a sample
+
+
+def test_config5_round_robin_expert_placement():
+    """Config 5 with the experts placed round-robin over the ranks (the Zipf prior indexed by expert slot, passed as
+    gate_bias): routing bit-exact and rows within tolerance against the oracle given the same prior, and the rows of
+    a rank's tokens spread over all ranks' experts instead of going to rank 0's."""
+    _run_real(_largest_world(), 5, 64, env={"TEST_ROUND_ROBIN_PLACEMENT": "1"})
 
 
 def test_config3_real_shape_stream_waits():
