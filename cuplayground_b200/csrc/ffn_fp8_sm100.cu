@@ -120,6 +120,29 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
     return *reinterpret_cast<uint32_t*>(&t);
 }
 
+// Where output row `row` of group g goes (column 0 of the N-wide row): this rank's buffer, or - expert parallel - the
+// buffer of the rank the row came from, in that rank's own numbering.
+__device__ __forceinline__ __nv_bfloat16* fp8_output_row(const Fp8GemmParams& p, const Fp8PeerArgs& pa, int g, int row) {
+    __nv_bfloat16* obase = p.out;
+    int og = g;
+    int orows = p.rows_per_group, orow_idx = row;
+    if (pa.peer_world > 0 && pa.src_off != nullptr) {
+        // dense group: find the source rank of this row, return it to that rank's own numbering
+        const int32_t* off = pa.src_off + g * (pa.peer_world + 1);
+        int src = 0;
+        while (src + 1 < pa.peer_world && row >= __ldg(off + src + 1)) ++src;
+        obase = pa.peer_out[src];
+        og = pa.peer_rank * p.experts + g;
+        orows = pa.ret_rows;
+        orow_idx = row - __ldg(off + src);
+    } else if (pa.peer_world > 0) {        // the store is the return all-to-all: straight into the source rank
+        const int src = g / p.experts;
+        obase = pa.peer_out[src];
+        og = pa.peer_rank * p.experts + (g - src * p.experts);
+    }
+    return obase + ((size_t)og * orows + orow_idx) * p.N;
+}
+
 template <int SUBS, bool QUANT>
 __global__ void __launch_bounds__(f8_threads(SUBS), 1)
 ffn_fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB0,
@@ -420,24 +443,7 @@ ffn_fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
                 }
             } else {
             if (row_ok && (p.gated || SUBS != 2)) {
-                __nv_bfloat16* obase = p.out;
-                int og = g;
-                int orows = p.rows_per_group, orow_idx = row;
-                if (pa.peer_world > 0 && pa.src_off != nullptr) {
-                    // dense group: find the source rank of this row, return it to that rank's own numbering
-                    const int32_t* off = pa.src_off + g * (pa.peer_world + 1);
-                    int src = 0;
-                    while (src + 1 < pa.peer_world && row >= __ldg(off + src + 1)) ++src;
-                    obase = pa.peer_out[src];
-                    og = pa.peer_rank * p.experts + g;
-                    orows = pa.ret_rows;
-                    orow_idx = row - __ldg(off + src);
-                } else if (pa.peer_world > 0) {    // the store is the return all-to-all: straight into the source rank
-                    const int src = g / p.experts;
-                    obase = pa.peer_out[src];
-                    og = pa.peer_rank * p.experts + (g - src * p.experts);
-                }
-                __nv_bfloat16* orow = obase + ((size_t)og * orows + orow_idx) * p.N + n0;
+                __nv_bfloat16* orow = fp8_output_row(p, pa, g, row) + n0;
                 if (p.gated) {
                     // gate chunk half + SUBS j pairs with up chunk half + SUBS j + 4: 32 outputs each
 #pragma unroll
@@ -478,25 +484,7 @@ ffn_fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
                 // store instruction writes four whole 128-byte lines (local memory, or a peer's over NVLink) instead
                 // of 32 separate 16-byte pieces.
                 __nv_bfloat16* my_dst = nullptr;             // where this lane's row goes (column n0 + cbase), if valid
-                if (row_ok) {
-                    __nv_bfloat16* obase = p.out;
-                    int og = g;
-                    int orows = p.rows_per_group, orow_idx = row;
-                    if (pa.peer_world > 0 && pa.src_off != nullptr) {
-                        const int32_t* off = pa.src_off + g * (pa.peer_world + 1);
-                        int src = 0;
-                        while (src + 1 < pa.peer_world && row >= __ldg(off + src + 1)) ++src;
-                        obase = pa.peer_out[src];
-                        og = pa.peer_rank * p.experts + g;
-                        orows = pa.ret_rows;
-                        orow_idx = row - __ldg(off + src);
-                    } else if (pa.peer_world > 0) {
-                        const int src = g / p.experts;
-                        obase = pa.peer_out[src];
-                        og = pa.peer_rank * p.experts + (g - src * p.experts);
-                    }
-                    my_dst = obase + ((size_t)og * orows + orow_idx) * p.N + n0 + cbase;
-                }
+                if (row_ok) my_dst = fp8_output_row(p, pa, g, row) + n0 + cbase;
                 const uint32_t out_stage = ptx::smem_u32(aux + F8_AUX_ALIGNED) + (warp - 2) * F8_QSTAGE_BYTES_PER_WARP;
                 const int unit = lane & 7;
 #pragma unroll
