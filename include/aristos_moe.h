@@ -148,6 +148,10 @@ ARISTOS_API aristos_status_t aristos_moe_set_bias(aristos_moe_t* layer, const vo
  * contiguous, as aristos_quantize_fp8(block_rows = 128) writes them. Across ranks the fp8 layer needs the "p2p"
  * transport (the gather stores quantised rows and scales straight into the owning rank's memory).
  * E_local = num_experts / world; rank r owns experts [r*E_local, (r+1)*E_local). Dropped tokens give zero rows.
+ * Expert indices here are slots: which model expert a slot holds is the caller's choice (the rows of w_gate, the
+ * entries of gate_bias and the expert weights follow it). A forward ends when the busiest rank's experts are done,
+ * so a skewed routing prior wants its hot experts in slots of different ranks, e.g. expert e in slot
+ * (e % world) * E_local + e / world (round-robin over the ranks).
  */
 ARISTOS_API aristos_status_t aristos_moe_forward(aristos_moe_t* layer, const void* x, const void* w_gate,
                                                  const float* gate_bias, const void* w1, const void* w3,
