@@ -220,3 +220,30 @@ def test_load_balance_stats_reference(oracle):
     frac, prob, aux, dropped = oracle.load_balance_stats(idx, w, slot, 4)
     assert np.allclose(frac, [3 / 6, 2 / 6, 1 / 6, 0]) and np.allclose(prob, [1.75 / 3, 0.75 / 3, 0.125 / 3, 0])
     assert abs(aux - 4 * (0.5 * 1.75 / 3 + (2 / 6) * 0.25 + (1 / 6) * 0.125 / 3)) < 1e-12 and abs(dropped - 1 / 6) < 1e-12
+
+
+def test_expert_placement_is_a_relabelling(oracle):
+    """Holding expert e in slot p(e) = (e % N) * E/N + e // N (round-robin over N ranks) only renames the experts:
+    with the rows of the gate weights and the prior permuted the same way, every token selects the same experts with
+    the same weights, expert by expert the same rows are kept, and the slots of the N hottest experts of a Zipf
+    prior belong to N different ranks."""
+    from helpers import make_inputs
+    S, H, E, k, N = 512, 256, 32, 4, 8
+    x, wg, *_ = make_inputs(S, H, 64, E, seed=123)
+    prior = oracle.zipf_bias(E, 1.2)
+    El = E // N
+    slot_of_expert = np.array([(e % N) * El + e // N for e in range(E)])
+    expert_of_slot = np.argsort(slot_of_expert)
+    idx, w = oracle.gate_topk(oracle.gate_logits(x, wg, prior), k, 0, 1)
+    idx_s, w_s = oracle.gate_topk(oracle.gate_logits(x, wg[expert_of_slot], prior[expert_of_slot]), k, 0, 1)
+    np.testing.assert_array_equal(expert_of_slot[idx_s], idx)          # no exact ties in random logits
+    np.testing.assert_array_equal(w_s, w)
+    cap = oracle.capacity(S, E, k, 1.0)
+    count, slot, _ = oracle.dispatch(idx, E, cap)
+    count_s, slot_s, _ = oracle.dispatch(idx_s, E, cap)
+    np.testing.assert_array_equal(count_s[slot_of_expert], count)
+    np.testing.assert_array_equal(slot_s >= 0, slot >= 0)              # the same assignments are dropped
+    per_rank = count_s.reshape(N, El).sum(axis=1)
+    per_rank_contiguous = count.reshape(N, El).sum(axis=1)
+    assert per_rank.max() < per_rank_contiguous.max()                  # the hot experts no longer share a rank
+    assert len({slot_of_expert[e] // El for e in range(N)}) == N
