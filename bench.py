@@ -118,6 +118,14 @@ def layer_flops(cfg, kept_assignments: int) -> float:
         2.0 * cfg.S * cfg.hidden_size * cfg.num_experts
 
 
+def busiest_rank_rows(rows_per_expert, world):
+    """Rows the busiest rank's experts receive: rank r owns the contiguous block of E / world expert slots
+    [r E/world, (r + 1) E/world) of rows_per_expert (kept rows per slot, summed over all source ranks)."""
+    E = len(rows_per_expert)
+    El = E // world
+    return max(sum(rows_per_expert[r * El:(r + 1) * El]) for r in range(world))
+
+
 def layer_roofline(cfg, world, kept):
     """The layer roofline: the slowest of FLOPs at the dense tensor peak (2250 TFLOP/s bf16, 4500 TFLOP/s fp8), minimum
     HBM bytes at 8 TB/s and all-to-all bytes at 900 GB/s per direction (dispatch and return summed). Seconds per rank."""
@@ -344,7 +352,7 @@ def run_ours(args, cfg, workload_desc):
     if world > 1:
         per_expert = count_mine.cuda()
         dist.all_reduce(per_expert, op=dist.ReduceOp.SUM)
-        busiest_rows = float(per_expert.view(world, -1).sum(dim=1).max().item())
+        busiest_rows = float(busiest_rank_rows(per_expert.cpu().tolist(), world))
     value = S * world * args.steps / (ms * 1e-3)
 
     # ---- end to end: host activations in, host result out, through the public host API. Every step copies its own
